@@ -1,0 +1,273 @@
+// PyTorch binding of the sm_100a kernels: checks tensors, picks the current CUDA
+// stream and forwards raw pointers to the launchers declared in kernels.h.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "kernels.h"
+
+namespace {
+
+using torch::Tensor;
+
+mb200::DType dtype_of(const Tensor& t) {
+  switch (t.scalar_type()) {
+    case at::kBFloat16: return mb200::kBF16;
+    case at::kHalf: return mb200::kF16;
+    case at::kFloat: return mb200::kF32;
+    default: TORCH_CHECK(false, "mllm_b200: unsupported dtype ", t.scalar_type());
+  }
+}
+
+void check_cuda(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), "mllm_b200: ", name, " must be a CUDA tensor");
+}
+void check_half(const Tensor& t, const char* name) {
+  check_cuda(t, name);
+  TORCH_CHECK(t.scalar_type() == at::kBFloat16 || t.scalar_type() == at::kHalf, "mllm_b200: ", name,
+              " must be bf16 or fp16");
+}
+
+struct DeviceState {
+  Tensor status;     // int32[1]
+  Tensor workspace;  // float, split-K partials
+  Tensor counters;   // int32 tickets
+  int num_sms = 0;
+};
+
+DeviceState& device_state(int device) {
+  static std::mutex mu;
+  static std::unordered_map<int, DeviceState> states;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = states.find(device);
+  if (it == states.end()) {
+    DeviceState st;
+    auto opts_i = torch::TensorOptions().dtype(torch::kInt32).device(torch::kCUDA, device);
+    st.status = torch::zeros({4}, opts_i);
+    st.counters = torch::zeros({4096}, opts_i);
+    st.workspace = torch::empty({static_cast<int64_t>(mb200::gemm_workspace_bytes(0, 0, 0, 0) / 4)},
+                                torch::TensorOptions().dtype(torch::kFloat32).device(torch::kCUDA, device));
+    st.num_sms = at::cuda::getDeviceProperties(device)->multiProcessorCount;
+    it = states.emplace(device, std::move(st)).first;
+  }
+  return it->second;
+}
+
+cudaStream_t stream_of(const Tensor& t) { return at::cuda::getCurrentCUDAStream(t.get_device()).stream(); }
+
+// --------------------------------------------------------------------------------------
+void rmsnorm(const Tensor& x, const Tensor& w, Tensor& out, double eps) {
+  check_half(x, "x");
+  TORCH_CHECK(x.dim() == 2 && out.dim() == 2 && x.stride(1) == 1 && out.stride(1) == 1, "rmsnorm: 2-D row-major");
+  const int hidden = x.size(1);
+  TORCH_CHECK(hidden % 8 == 0 && hidden <= 32768 && w.numel() == hidden && w.is_contiguous(), "rmsnorm: hidden");
+  TORCH_CHECK(x.stride(0) % 8 == 0 && out.stride(0) % 8 == 0, "rmsnorm: row strides must be multiples of 8");
+  c10::cuda::CUDAGuard g(x.device());
+  mb200::launch_rmsnorm(x.data_ptr(), w.data_ptr(), out.data_ptr(), x.size(0), hidden, x.stride(0), out.stride(0),
+                        static_cast<float>(eps), dtype_of(x), stream_of(x));
+}
+
+void fused_add_rmsnorm(Tensor& x, Tensor& residual, const Tensor& w, double eps) {
+  check_half(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && residual.is_contiguous() && residual.sizes() == x.sizes(),
+              "fused_add_rmsnorm: contiguous 2-D tensors of equal shape");
+  const int hidden = x.size(1);
+  TORCH_CHECK(hidden % 8 == 0 && hidden <= 32768 && w.numel() == hidden, "fused_add_rmsnorm: hidden");
+  c10::cuda::CUDAGuard g(x.device());
+  mb200::launch_fused_add_rmsnorm(x.data_ptr(), residual.data_ptr(), w.data_ptr(), x.size(0), hidden,
+                                  static_cast<float>(eps), dtype_of(x), stream_of(x));
+}
+
+void layernorm(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& b, Tensor& out, double eps) {
+  check_half(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && out.is_contiguous(), "layernorm: contiguous 2-D");
+  const int hidden = x.size(1);
+  TORCH_CHECK(hidden % 8 == 0 && hidden <= 32768, "layernorm: hidden");
+  c10::cuda::CUDAGuard g(x.device());
+  mb200::launch_layernorm(x.data_ptr(), w.data_ptr(), b.has_value() ? b->data_ptr() : nullptr, out.data_ptr(),
+                          x.size(0), hidden, static_cast<float>(eps), dtype_of(x), stream_of(x));
+}
+
+void act_and_mul(const Tensor& x, Tensor& out, int64_t act) {
+  check_half(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && out.is_contiguous(), "act_and_mul: contiguous 2-D");
+  const int inter = x.size(1) / 2;
+  TORCH_CHECK(inter % 8 == 0 && out.size(1) == inter, "act_and_mul: width");
+  c10::cuda::CUDAGuard g(x.device());
+  mb200::launch_act_and_mul(x.data_ptr(), out.data_ptr(), x.size(0), inter, static_cast<int>(act), dtype_of(x),
+                            stream_of(x));
+}
+
+void gelu_tanh(const Tensor& x, Tensor& out) {
+  check_half(x, "x");
+  TORCH_CHECK(x.is_contiguous() && out.is_contiguous() && x.numel() % 8 == 0, "gelu_tanh: contiguous, numel % 8");
+  c10::cuda::CUDAGuard g(x.device());
+  mb200::launch_gelu_tanh(x.data_ptr(), out.data_ptr(), x.numel(), dtype_of(x), stream_of(x));
+}
+
+void embedding(const Tensor& ids, const Tensor& table, Tensor& out) {
+  check_half(table, "table");
+  TORCH_CHECK(ids.scalar_type() == at::kLong && ids.is_contiguous() && table.is_contiguous() && out.is_contiguous(),
+              "embedding: int64 ids, contiguous tensors");
+  TORCH_CHECK(table.size(1) % 8 == 0, "embedding: hidden % 8");
+  c10::cuda::CUDAGuard g(table.device());
+  auto& st = device_state(table.get_device());
+  mb200::launch_embedding(ids.data_ptr<int64_t>(), table.data_ptr(), out.data_ptr(), ids.numel(), table.size(1),
+                          table.size(0), dtype_of(table), st.status.data_ptr<int>(), stream_of(table));
+}
+
+void qk_norm_rope_kv_write(Tensor& qkv, const c10::optional<Tensor>& q_w, const c10::optional<Tensor>& k_w,
+                           const Tensor& positions, const c10::optional<Tensor>& axis_map, const Tensor& inv_freq,
+                           const Tensor& cache_loc, Tensor& k_cache, Tensor& v_cache, int64_t hq, int64_t hkv,
+                           int64_t head_dim, double eps) {
+  check_half(qkv, "qkv");
+  TORCH_CHECK(head_dim == 128, "qk_norm_rope_kv_write: head_dim must be 128");
+  TORCH_CHECK(qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.size(1) == (hq + 2 * hkv) * head_dim, "qkv shape");
+  TORCH_CHECK(qkv.stride(0) % 4 == 0, "qkv row stride");
+  TORCH_CHECK(positions.scalar_type() == at::kLong && positions.is_contiguous(), "positions int64 contiguous");
+  TORCH_CHECK(cache_loc.scalar_type() == at::kLong && cache_loc.is_contiguous(), "cache_loc int64 contiguous");
+  TORCH_CHECK(inv_freq.scalar_type() == at::kFloat && inv_freq.numel() == head_dim / 2, "inv_freq fp32 [D/2]");
+  TORCH_CHECK(k_cache.is_contiguous() && v_cache.is_contiguous() && k_cache.scalar_type() == qkv.scalar_type(),
+              "kv cache must be contiguous and of the activation dtype");
+  const int tokens = qkv.size(0);
+  const int pos_rows = positions.dim() == 2 ? positions.size(0) : 1;
+  TORCH_CHECK(positions.numel() == static_cast<int64_t>(pos_rows) * tokens, "positions size");
+  TORCH_CHECK(cache_loc.numel() == tokens, "cache_loc size");
+  c10::cuda::CUDAGuard g(qkv.device());
+  auto& st = device_state(qkv.get_device());
+  mb200::launch_qk_norm_rope_kv_write(
+      qkv.data_ptr(), q_w.has_value() ? q_w->data_ptr() : nullptr, k_w.has_value() ? k_w->data_ptr() : nullptr,
+      positions.data_ptr<int64_t>(), pos_rows, axis_map.has_value() ? axis_map->data_ptr<int8_t>() : nullptr,
+      inv_freq.data_ptr<float>(), cache_loc.data_ptr<int64_t>(), k_cache.data_ptr(), v_cache.data_ptr(), tokens, hq,
+      hkv, head_dim, qkv.stride(0), k_cache.size(0), static_cast<float>(eps), dtype_of(qkv),
+      st.status.data_ptr<int>(), stream_of(qkv));
+}
+
+void kv_write(const Tensor& k, const Tensor& v, const Tensor& loc, Tensor& k_cache, Tensor& v_cache) {
+  check_half(k, "k");
+  TORCH_CHECK(loc.scalar_type() == at::kLong && loc.is_contiguous(), "loc int64 contiguous");
+  const int tokens = loc.numel();
+  const int64_t row = k_cache.numel() / k_cache.size(0);
+  TORCH_CHECK(row % 8 == 0 && k.numel() == tokens * row && v.numel() == tokens * row, "kv_write: row size");
+  auto k2 = k.reshape({tokens, row});
+  auto v2 = v.reshape({tokens, row});
+  TORCH_CHECK(k2.stride(1) == 1 && v2.stride(1) == 1 && k2.stride(0) % 8 == 0 && v2.stride(0) % 8 == 0, "kv strides");
+  c10::cuda::CUDAGuard g(k.device());
+  auto& st = device_state(k.get_device());
+  mb200::launch_kv_write(k2.data_ptr(), v2.data_ptr(), loc.data_ptr<int64_t>(), k_cache.data_ptr(),
+                         v_cache.data_ptr(), tokens, row, k2.stride(0), v2.stride(0), k_cache.size(0), dtype_of(k),
+                         st.status.data_ptr<int>(), stream_of(k));
+}
+
+std::vector<Tensor> per_token_quant_int8(const Tensor& x) {
+  check_half(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && x.size(1) % 16 == 0 && x.size(1) <= 32768, "quant: [M,K], K%16");
+  c10::cuda::CUDAGuard g(x.device());
+  auto q = torch::empty_like(x, x.options().dtype(torch::kInt8));
+  auto scale = torch::empty({x.size(0), 1}, x.options().dtype(torch::kFloat32));
+  mb200::launch_per_token_quant_int8(x.data_ptr(), q.data_ptr<int8_t>(), scale.data_ptr<float>(), x.size(0),
+                                     x.size(1), dtype_of(x), stream_of(x));
+  return {q, scale};
+}
+
+void argmax(const Tensor& logits, Tensor& out) {
+  check_cuda(logits, "logits");
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && out.scalar_type() == at::kLong && out.is_contiguous(),
+              "argmax: [B,V] logits, int64 out");
+  c10::cuda::CUDAGuard g(logits.device());
+  mb200::launch_argmax(logits.data_ptr(), out.data_ptr<int64_t>(), logits.size(0), logits.size(1), logits.stride(0),
+                       dtype_of(logits), stream_of(logits));
+}
+
+// out = a @ b^T (+bias) (+residual) | swiglu.  a [M,K], b [N,K].
+void gemm(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<Tensor>& bias,
+          const c10::optional<Tensor>& residual, bool swiglu, const c10::optional<Tensor>& a_scale,
+          const c10::optional<Tensor>& b_scale) {
+  check_cuda(a, "a");
+  check_cuda(b, "b");
+  const bool is_int8 = a.scalar_type() == at::kChar;
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 &&
+                  out.stride(1) == 1,
+              "gemm: 2-D row-major operands");
+  TORCH_CHECK(a.size(1) == b.size(1) && a.scalar_type() == b.scalar_type(), "gemm: K / dtype mismatch");
+  TORCH_CHECK(out.size(0) == a.size(0) && out.size(1) == (swiglu ? b.size(0) / 2 : b.size(0)), "gemm: out shape");
+  if (is_int8) {
+    TORCH_CHECK(a_scale.has_value() && b_scale.has_value(), "gemm: int8 needs scales");
+    TORCH_CHECK(a_scale->scalar_type() == at::kFloat && b_scale->scalar_type() == at::kFloat &&
+                    a_scale->numel() == a.size(0) && b_scale->numel() == b.size(0) && a_scale->is_contiguous() &&
+                    b_scale->is_contiguous(),
+                "gemm: scale shapes");
+  } else {
+    check_half(a, "a");
+    TORCH_CHECK(out.scalar_type() == a.scalar_type(), "gemm: out dtype");
+  }
+  check_half(out, "out");
+  c10::cuda::CUDAGuard g(a.device());
+  auto& st = device_state(a.get_device());
+  mb200::GemmArgs args{};
+  args.a = a.data_ptr();
+  args.b = b.data_ptr();
+  args.out = out.data_ptr();
+  args.bias = bias.has_value() ? bias->data_ptr() : nullptr;
+  args.residual = residual.has_value() ? residual->data_ptr() : nullptr;
+  if (bias.has_value())
+    TORCH_CHECK(bias->scalar_type() == out.scalar_type() && bias->numel() == b.size(0) && bias->is_contiguous(), "bias");
+  if (residual.has_value())
+    TORCH_CHECK(residual->scalar_type() == out.scalar_type() && residual->sizes() == out.sizes() &&
+                    residual->stride(1) == 1,
+                "residual");
+  args.a_scale = is_int8 ? a_scale->data_ptr<float>() : nullptr;
+  args.b_scale = is_int8 ? b_scale->data_ptr<float>() : nullptr;
+  args.m = a.size(0);
+  args.n = b.size(0);
+  args.k = a.size(1);
+  args.lda = a.stride(0);
+  args.ldb = b.stride(0);
+  args.ldc = out.stride(0);
+  args.ld_res = residual.has_value() ? residual->stride(0) : 0;
+  args.swiglu = swiglu ? 1 : 0;
+  args.dt = dtype_of(out);
+  args.is_int8 = is_int8 ? 1 : 0;
+  args.workspace = st.workspace.data_ptr<float>();
+  args.workspace_bytes = st.workspace.numel() * sizeof(float);
+  args.counters = st.counters.data_ptr<int>();
+  args.num_counters = st.counters.numel();
+  args.status = st.status.data_ptr<int>();
+  args.num_sms = st.num_sms;
+  const int rc = mb200::launch_gemm(args, stream_of(a));
+  TORCH_CHECK(rc == 0, "mllm_b200 gemm: unsupported shape or launch failure (code ", rc, ") for M=", args.m,
+              " N=", args.n, " K=", args.k);
+}
+
+// Reads (and clears) the device status word; non-zero means a kernel gave up on a bounded wait
+// or met an out-of-range index. Synchronises the device.
+int64_t read_status(int64_t device) {
+  auto& st = device_state(static_cast<int>(device));
+  auto host = st.status.cpu();
+  const int v = host.data_ptr<int>()[0];
+  if (v != 0) st.status.zero_();
+  return v;
+}
+
+int64_t launch_count() { return static_cast<int64_t>(mb200::launch_count()); }
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("rmsnorm", &rmsnorm);
+  m.def("fused_add_rmsnorm", &fused_add_rmsnorm);
+  m.def("layernorm", &layernorm);
+  m.def("act_and_mul", &act_and_mul);
+  m.def("gelu_tanh", &gelu_tanh);
+  m.def("embedding", &embedding);
+  m.def("qk_norm_rope_kv_write", &qk_norm_rope_kv_write);
+  m.def("kv_write", &kv_write);
+  m.def("per_token_quant_int8", &per_token_quant_int8);
+  m.def("argmax", &argmax);
+  m.def("gemm", &gemm);
+  m.def("read_status", &read_status);
+  m.def("launch_count", &launch_count);
+}

@@ -1,0 +1,590 @@
+// Memory-bound sm_100a kernels: RMSNorm / fused add+RMSNorm, LayerNorm, gated
+// activations, embedding gather, the fused per-head QK-norm + rotary + KV-cache
+// write, the stand-alone KV write, per-token int8 quantisation and greedy argmax.
+//
+// All of them move 16 bytes per thread per access and touch every byte once
+// (the norm kernels keep a row in registers between the reduction and the
+// scaling pass), so their ceiling is HBM bandwidth.
+#include <atomic>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace mb200 {
+
+static std::atomic<uint64_t> g_launches{0};
+uint64_t launch_count() { return g_launches.load(); }
+void note_launch(int n) { g_launches.fetch_add(n); }
+
+namespace {
+
+template <typename T>
+struct Vec8 {
+  uint4 raw;
+};
+
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]);
+template <>
+__device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4& raw, float (&f)[8]) {
+  const uint32_t* u = reinterpret_cast<const uint32_t*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 p = unpack_bf16x2(u[i]);
+    f[2 * i] = p.x;
+    f[2 * i + 1] = p.y;
+  }
+}
+template <>
+__device__ __forceinline__ void unpack8<__half>(const uint4& raw, float (&f)[8]) {
+  const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 p = __half22float2(h[i]);
+    f[2 * i] = p.x;
+    f[2 * i + 1] = p.y;
+  }
+}
+template <typename T>
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]);
+template <>
+__device__ __forceinline__ uint4 pack8<__nv_bfloat16>(const float (&f)[8]) {
+  uint4 r;
+  uint32_t* u = reinterpret_cast<uint32_t*>(&r);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) u[i] = pack_bf16x2(f[2 * i], f[2 * i + 1]);
+  return r;
+}
+template <>
+__device__ __forceinline__ uint4 pack8<__half>(const float (&f)[8]) {
+  uint4 r;
+  __half2* h = reinterpret_cast<__half2*>(&r);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+  return r;
+}
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+__device__ __forceinline__ float to_f32(float v) { return v; }
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) {
+  return __float2half_rn(v);
+}
+template <typename T>
+__device__ __forceinline__ float round_to(float v);
+template <>
+__device__ __forceinline__ float round_to<__nv_bfloat16>(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+template <>
+__device__ __forceinline__ float round_to<__half>(float v) {
+  return __half2float(__float2half_rn(v));
+}
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  if (lane_id() == 0) red[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < nw) ? red[threadIdx.x] : 0.f;
+  if (w == 0) {
+    t = warp_sum(t);
+    if (lane_id() == 0) red[32] = t;
+  }
+  __syncthreads();
+  float out = red[32];
+  __syncthreads();
+  return out;
+}
+
+constexpr int kMaxVecPerThread = 4;  // row cache: hidden <= 4 * 8 * blockDim
+
+// ---------------------------------------------------------------------------
+// RMSNorm and fused residual-add + RMSNorm. One CTA per row.
+// ---------------------------------------------------------------------------
+template <typename T, bool kAdd>
+__global__ void rmsnorm_kernel(T* __restrict__ x, T* __restrict__ residual, const T* __restrict__ w,
+                               T* __restrict__ out, int hidden, int64_t x_stride, int64_t out_stride, float eps) {
+  __shared__ float red[33];
+  const int row = blockIdx.x;
+  const int nvec = hidden >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * x_stride);
+  uint4* rr = kAdd ? reinterpret_cast<uint4*>(residual + row * x_stride) : nullptr;
+  uint4* orow = reinterpret_cast<uint4*>(out + row * out_stride);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+
+  float cache[kMaxVecPerThread][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < kMaxVecPerThread; ++it) {
+    const int v = threadIdx.x + it * blockDim.x;
+    if (v < nvec) {
+      float f[8];
+      unpack8<T>(xr[v], f);
+      if (kAdd) {
+        float g[8];
+        unpack8<T>(rr[v], g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = round_to<T>(f[i] + g[i]);
+        rr[v] = pack8<T>(f);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        cache[it][i] = f[i];
+        ss += f[i] * f[i];
+      }
+    }
+  }
+  const float rstd = rsqrtf(block_sum(ss, red) / static_cast<float>(hidden) + eps);
+#pragma unroll
+  for (int it = 0; it < kMaxVecPerThread; ++it) {
+    const int v = threadIdx.x + it * blockDim.x;
+    if (v < nvec) {
+      float g[8], o[8];
+      unpack8<T>(wr[v], g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = cache[it][i] * rstd * g[i];
+      orow[v] = pack8<T>(o);
+    }
+  }
+}
+
+template <typename T>
+__global__ void layernorm_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b,
+                                 T* __restrict__ out, int hidden, float eps) {
+  __shared__ float red[33];
+  const int row = blockIdx.x;
+  const int nvec = hidden >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(row) * hidden);
+  uint4* orow = reinterpret_cast<uint4*>(out + static_cast<int64_t>(row) * hidden);
+  float cache[kMaxVecPerThread][8];
+  float s = 0.f;
+#pragma unroll
+  for (int it = 0; it < kMaxVecPerThread; ++it) {
+    const int v = threadIdx.x + it * blockDim.x;
+    if (v < nvec) {
+      unpack8<T>(xr[v], cache[it]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s += cache[it][i];
+    }
+  }
+  const float mean = block_sum(s, red) / static_cast<float>(hidden);
+  float q = 0.f;
+#pragma unroll
+  for (int it = 0; it < kMaxVecPerThread; ++it) {
+    const int v = threadIdx.x + it * blockDim.x;
+    if (v < nvec) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float d = cache[it][i] - mean;
+        q += d * d;
+      }
+    }
+  }
+  const float rstd = rsqrtf(block_sum(q, red) / static_cast<float>(hidden) + eps);
+#pragma unroll
+  for (int it = 0; it < kMaxVecPerThread; ++it) {
+    const int v = threadIdx.x + it * blockDim.x;
+    if (v < nvec) {
+      float g[8], bb[8], o[8];
+      unpack8<T>(reinterpret_cast<const uint4*>(w)[v], g);
+      if (b != nullptr) unpack8<T>(reinterpret_cast<const uint4*>(b)[v], bb);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = (cache[it][i] - mean) * rstd * g[i] + (b != nullptr ? bb[i] : 0.f);
+      orow[v] = pack8<T>(o);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// gated activations
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float silu_f(float v) { return v / (1.f + __expf(-v)); }
+__device__ __forceinline__ float gelu_tanh_f(float v) {
+  const float k = 0.7978845608028654f;
+  return 0.5f * v * (1.f + tanhf(k * (v + 0.044715f * v * v * v)));
+}
+
+template <typename T, int kAct>
+__global__ void act_and_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int rows, int inter) {
+  const int vec_per_row = inter >> 3;
+  const int64_t total = static_cast<int64_t>(rows) * vec_per_row;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / vec_per_row;
+    const int v = static_cast<int>(i - r * vec_per_row);
+    const uint4* row = reinterpret_cast<const uint4*>(x + r * 2 * inter);
+    float g[8], u[8], o[8];
+    unpack8<T>(row[v], g);
+    unpack8<T>(row[vec_per_row + v], u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = (kAct == 0 ? silu_f(g[j]) : gelu_tanh_f(g[j])) * u[j];
+    reinterpret_cast<uint4*>(out + r * inter)[v] = pack8<T>(o);
+  }
+}
+
+template <typename T>
+__global__ void gelu_tanh_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t nvec) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float f[8];
+    unpack8<T>(reinterpret_cast<const uint4*>(x)[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = gelu_tanh_f(f[j]);
+    reinterpret_cast<uint4*>(out)[i] = pack8<T>(f);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// embedding gather: one CTA per token
+// ---------------------------------------------------------------------------
+__global__ void embedding_kernel(const int64_t* __restrict__ ids, const uint4* __restrict__ table,
+                                 uint4* __restrict__ out, int vec_per_row, int vocab, int* status) {
+  const int t = blockIdx.x;
+  int64_t id = ids[t];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0 && status != nullptr) atomicExch(status, kStatusBadIndex);
+    id = 0;
+  }
+  const uint4* src = table + id * vec_per_row;
+  uint4* dst = out + static_cast<int64_t>(t) * vec_per_row;
+  for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) dst[v] = src[v];
+}
+
+// ---------------------------------------------------------------------------
+// fused per-head RMSNorm (q,k) + NeoX RoPE (q,k) + KV-cache write. head_dim = 128.
+// One warp per (token, head); lane l owns features 4l..4l+3, its rotation partner
+// (feature +-64) lives in lane l^16.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const T* __restrict__ q_w,
+                                             const T* __restrict__ k_w, const int64_t* __restrict__ positions,
+                                             int pos_rows, const int8_t* __restrict__ axis_map,
+                                             const float* __restrict__ inv_freq,
+                                             const int64_t* __restrict__ cache_loc, T* __restrict__ k_cache,
+                                             T* __restrict__ v_cache, int tokens, int hq, int hkv,
+                                             int64_t qkv_stride, int64_t num_slots, float eps, int* status) {
+  constexpr int D = 128;
+  const int heads = hq + 2 * hkv;
+  const int64_t warp = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+  if (warp >= static_cast<int64_t>(tokens) * heads) return;
+  const int t = static_cast<int>(warp / heads);
+  const int h = static_cast<int>(warp - static_cast<int64_t>(t) * heads);
+  const int lane = lane_id();
+  T* src = qkv + t * qkv_stride + h * D + lane * 4;
+  uint2 raw = *reinterpret_cast<const uint2*>(src);
+
+  const bool is_q = h < hq, is_k = !is_q && h < hq + hkv;
+  int64_t slot = 0;
+  if (!is_q) {
+    slot = cache_loc[t];
+    if (slot < 0 || slot >= num_slots) {
+      if (lane == 0 && status != nullptr) atomicExch(status, kStatusBadIndex);
+      return;
+    }
+  }
+  if (is_q || is_k) {
+    float f[4];
+    {
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) f[i] = to_f32(e[i]);
+    }
+    const T* w = is_q ? q_w : k_w;
+    if (w != nullptr) {
+      float ss = f[0] * f[0] + f[1] * f[1] + f[2] * f[2] + f[3] * f[3];
+      const float rstd = rsqrtf(warp_sum(ss) / static_cast<float>(D) + eps);
+      uint2 wr = *reinterpret_cast<const uint2*>(w + lane * 4);
+      const T* we = reinterpret_cast<const T*>(&wr);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) f[i] = round_to<T>(f[i] * rstd * to_f32(we[i]));
+    }
+    float o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float partner = __shfl_xor_sync(0xffffffffu, f[i], 16);
+      const int fi = (lane * 4 + i) & 63;
+      const int ax = (axis_map != nullptr && pos_rows > 1) ? axis_map[fi] : 0;
+      const float ang = static_cast<float>(positions[static_cast<int64_t>(ax) * tokens + t]) * inv_freq[fi];
+      float sn, cs;
+      sincosf(ang, &sn, &cs);
+      o[i] = (lane < 16) ? (f[i] * cs - partner * sn) : (f[i] * cs + partner * sn);
+    }
+    T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) e[i] = from_f32<T>(o[i]);
+    *reinterpret_cast<uint2*>(src) = raw;
+  }
+  if (is_k) {
+    *reinterpret_cast<uint2*>(k_cache + (slot * hkv + (h - hq)) * D + lane * 4) = raw;
+  } else if (!is_q) {
+    *reinterpret_cast<uint2*>(v_cache + (slot * hkv + (h - hq - hkv)) * D + lane * 4) = raw;
+  }
+}
+
+// rows of `row_elems` elements (a multiple of 8) copied to slot rows of both caches
+template <typename T>
+__global__ void kv_write_kernel(const T* __restrict__ k, const T* __restrict__ v, const int64_t* __restrict__ loc,
+                                T* __restrict__ k_cache, T* __restrict__ v_cache, int tokens, int row_elems,
+                                int64_t k_stride, int64_t v_stride, int64_t num_slots, int* status) {
+  const int vec = row_elems >> 3;
+  const int64_t total = static_cast<int64_t>(tokens) * vec;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t t = i / vec;
+    const int c = static_cast<int>(i - t * vec);
+    const int64_t slot = loc[t];
+    if (slot < 0 || slot >= num_slots) {
+      if (status != nullptr) atomicExch(status, kStatusBadIndex);
+      continue;
+    }
+    reinterpret_cast<uint4*>(k_cache + slot * row_elems)[c] = reinterpret_cast<const uint4*>(k + t * k_stride)[c];
+    reinterpret_cast<uint4*>(v_cache + slot * row_elems)[c] = reinterpret_cast<const uint4*>(v + t * v_stride)[c];
+  }
+}
+
+// ---------------------------------------------------------------------------
+// per-token symmetric int8 quantisation: scale = absmax / 127
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void per_token_quant_int8_kernel(const T* __restrict__ x, int8_t* __restrict__ q,
+                                            float* __restrict__ scale, int k) {
+  __shared__ float red[33];
+  const int row = blockIdx.x;
+  const int nvec = k >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(row) * k);
+  float cache[kMaxVecPerThread][8];
+  float amax = 0.f;
+#pragma unroll
+  for (int it = 0; it < kMaxVecPerThread; ++it) {
+    const int v = threadIdx.x + it * blockDim.x;
+    if (v < nvec) {
+      unpack8<T>(xr[v], cache[it]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(cache[it][i]));
+    }
+  }
+  amax = warp_max(amax);
+  if (lane_id() == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = (threadIdx.x < ((blockDim.x + 31) >> 5)) ? red[threadIdx.x] : 0.f;
+    t = warp_max(t);
+    if (threadIdx.x == 0) red[32] = t;
+  }
+  __syncthreads();
+  amax = fmaxf(red[32], 1e-10f);
+  const float sc = amax / 127.f;
+  if (threadIdx.x == 0) scale[row] = sc;
+#pragma unroll
+  for (int it = 0; it < kMaxVecPerThread; ++it) {
+    const int v = threadIdx.x + it * blockDim.x;
+    if (v < nvec) {
+      int8_t o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float r = rintf(cache[it][i] / sc);
+        r = fminf(fmaxf(r, -128.f), 127.f);
+        o[i] = static_cast<int8_t>(r);
+      }
+      reinterpret_cast<uint2*>(q + static_cast<int64_t>(row) * k)[v] = *reinterpret_cast<uint2*>(o);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// greedy argmax: one CTA per row, lowest index wins ties
+// ---------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float load_as_float(const T* p) {
+  return to_f32(*p);
+}
+
+template <typename T>
+__global__ void argmax_kernel(const T* __restrict__ logits, int64_t* __restrict__ out, int vocab, int64_t stride) {
+  __shared__ float sval[32];
+  __shared__ int sidx[32];
+  const T* row = logits + blockIdx.x * stride;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float v = load_as_float(row + i);
+    if (v > best || (v == best && i < bi)) {
+      best = v;
+      bi = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  if (lane_id() == 0) {
+    sval[threadIdx.x >> 5] = best;
+    sidx[threadIdx.x >> 5] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int nw = (blockDim.x + 31) >> 5;
+    best = threadIdx.x < nw ? sval[threadIdx.x] : -INFINITY;
+    bi = threadIdx.x < nw ? sidx[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) {
+        best = ov;
+        bi = oi;
+      }
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
+  }
+}
+
+inline int norm_threads(int hidden) {
+  int t = ((hidden >> 3) + 31) / 32 * 32;
+  if (t > 1024) t = 1024;
+  if (t < 32) t = 32;
+  return t;
+}
+
+}  // namespace
+
+#define MB200_DISPATCH_HALF(dt, ...)          \
+  if ((dt) == kBF16) {                        \
+    using T = __nv_bfloat16;                  \
+    __VA_ARGS__;                              \
+  } else {                                    \
+    using T = __half;                         \
+    __VA_ARGS__;                              \
+  }
+
+void launch_rmsnorm(const void* x, const void* w, void* out, int rows, int hidden, int64_t x_stride,
+                    int64_t out_stride, float eps, DType dt, cudaStream_t s) {
+  if (rows == 0) return;
+  const int threads = norm_threads(hidden);
+  MB200_DISPATCH_HALF(dt, (rmsnorm_kernel<T, false><<<rows, threads, 0, s>>>(
+                              const_cast<T*>(static_cast<const T*>(x)), nullptr, static_cast<const T*>(w),
+                              static_cast<T*>(out), hidden, x_stride, out_stride, eps)));
+  note_launch();
+}
+
+void launch_fused_add_rmsnorm(void* x, void* residual, const void* w, int rows, int hidden, float eps, DType dt,
+                              cudaStream_t s) {
+  if (rows == 0) return;
+  const int threads = norm_threads(hidden);
+  MB200_DISPATCH_HALF(dt, (rmsnorm_kernel<T, true><<<rows, threads, 0, s>>>(
+                              static_cast<T*>(x), static_cast<T*>(residual), static_cast<const T*>(w),
+                              static_cast<T*>(x), hidden, hidden, hidden, eps)));
+  note_launch();
+}
+
+void launch_layernorm(const void* x, const void* w, const void* b, void* out, int rows, int hidden, float eps,
+                      DType dt, cudaStream_t s) {
+  if (rows == 0) return;
+  const int threads = norm_threads(hidden);
+  MB200_DISPATCH_HALF(dt, (layernorm_kernel<T><<<rows, threads, 0, s>>>(static_cast<const T*>(x),
+                                                                         static_cast<const T*>(w),
+                                                                         static_cast<const T*>(b),
+                                                                         static_cast<T*>(out), hidden, eps)));
+  note_launch();
+}
+
+void launch_act_and_mul(const void* x, void* out, int rows, int inter, int act, DType dt, cudaStream_t s) {
+  if (rows == 0) return;
+  const int64_t total = static_cast<int64_t>(rows) * (inter >> 3);
+  const int threads = 256;
+  const int blocks = static_cast<int>(std::min<int64_t>((total + threads - 1) / threads, 148 * 16));
+  if (act == 0) {
+    MB200_DISPATCH_HALF(dt, (act_and_mul_kernel<T, 0><<<blocks, threads, 0, s>>>(static_cast<const T*>(x),
+                                                                                  static_cast<T*>(out), rows, inter)));
+  } else {
+    MB200_DISPATCH_HALF(dt, (act_and_mul_kernel<T, 1><<<blocks, threads, 0, s>>>(static_cast<const T*>(x),
+                                                                                  static_cast<T*>(out), rows, inter)));
+  }
+  note_launch();
+}
+
+void launch_gelu_tanh(const void* x, void* out, int64_t n, DType dt, cudaStream_t s) {
+  if (n == 0) return;
+  const int64_t nvec = n >> 3;
+  const int threads = 256;
+  const int blocks = static_cast<int>(std::min<int64_t>((nvec + threads - 1) / threads, 148 * 16));
+  MB200_DISPATCH_HALF(dt, (gelu_tanh_kernel<T><<<blocks, threads, 0, s>>>(static_cast<const T*>(x),
+                                                                           static_cast<T*>(out), nvec)));
+  note_launch();
+}
+
+void launch_embedding(const int64_t* ids, const void* table, void* out, int tokens, int hidden, int vocab,
+                      DType dt, int* status, cudaStream_t s) {
+  if (tokens == 0) return;
+  (void)dt;  // 16-bit element types share the copy
+  const int vec = hidden >> 3;
+  const int threads = vec >= 256 ? 256 : ((vec + 31) / 32 * 32);
+  embedding_kernel<<<tokens, threads, 0, s>>>(ids, static_cast<const uint4*>(table), static_cast<uint4*>(out), vec,
+                                              vocab, status);
+  note_launch();
+}
+
+void launch_qk_norm_rope_kv_write(void* qkv, const void* q_w, const void* k_w, const int64_t* positions,
+                                  int pos_rows, const int8_t* axis_map, const float* inv_freq,
+                                  const int64_t* cache_loc, void* k_cache, void* v_cache, int tokens,
+                                  int num_q_heads, int num_kv_heads, int head_dim, int64_t qkv_stride,
+                                  int64_t num_slots, float eps, DType dt, int* status, cudaStream_t s) {
+  if (tokens == 0 || head_dim != 128) return;
+  const int64_t warps = static_cast<int64_t>(tokens) * (num_q_heads + 2 * num_kv_heads);
+  const int threads = 128;
+  const int blocks = static_cast<int>((warps * 32 + threads - 1) / threads);
+  MB200_DISPATCH_HALF(dt, (qk_norm_rope_kv_write_kernel<T><<<blocks, threads, 0, s>>>(
+                              static_cast<T*>(qkv), static_cast<const T*>(q_w), static_cast<const T*>(k_w),
+                              positions, pos_rows, axis_map, inv_freq, cache_loc, static_cast<T*>(k_cache),
+                              static_cast<T*>(v_cache), tokens, num_q_heads, num_kv_heads, qkv_stride, num_slots,
+                              eps, status)));
+  note_launch();
+}
+
+void launch_kv_write(const void* k, const void* v, const int64_t* loc, void* k_cache, void* v_cache, int tokens,
+                     int row_elems, int64_t k_stride, int64_t v_stride, int64_t num_slots, DType dt, int* status,
+                     cudaStream_t s) {
+  if (tokens == 0) return;
+  const int64_t total = static_cast<int64_t>(tokens) * (row_elems >> 3);
+  const int threads = 256;
+  const int blocks = static_cast<int>(std::min<int64_t>((total + threads - 1) / threads, 148 * 16));
+  MB200_DISPATCH_HALF(dt, (kv_write_kernel<T><<<blocks, threads, 0, s>>>(
+                              static_cast<const T*>(k), static_cast<const T*>(v), loc, static_cast<T*>(k_cache),
+                              static_cast<T*>(v_cache), tokens, row_elems, k_stride, v_stride, num_slots, status)));
+  note_launch();
+}
+
+void launch_per_token_quant_int8(const void* x, int8_t* q, float* scale, int rows, int k, DType dt,
+                                 cudaStream_t s) {
+  if (rows == 0) return;
+  const int threads = norm_threads(k);
+  MB200_DISPATCH_HALF(dt, (per_token_quant_int8_kernel<T><<<rows, threads, 0, s>>>(static_cast<const T*>(x), q,
+                                                                                    scale, k)));
+  note_launch();
+}
+
+void launch_argmax(const void* logits, int64_t* out, int rows, int vocab, int64_t stride, DType dt,
+                   cudaStream_t s) {
+  if (rows == 0) return;
+  if (dt == kF32) {
+    argmax_kernel<float><<<rows, 1024, 0, s>>>(static_cast<const float*>(logits), out, vocab, stride);
+  } else {
+    MB200_DISPATCH_HALF(dt, (argmax_kernel<T><<<rows, 1024, 0, s>>>(static_cast<const T*>(logits), out, vocab,
+                                                                     stride)));
+  }
+  note_launch();
+}
+
+}  // namespace mb200

@@ -1,0 +1,599 @@
+// out[m, n] = a[m, k] * b[n, k]^T (+ bias) (+ residual), or the SwiGLU of it, on the
+// 5th-generation tensor cores: operands staged in shared memory by TMA (128-byte swizzle,
+// no multicast), tcgen05.mma issued by one thread, fp32 / s32 accumulators in tensor
+// memory, epilogue through tcgen05.ld.  bf16 / fp16 inputs use kind::f16, int8 inputs
+// (W8A8 with per-row x per-column scales) use kind::i8; both share this file.
+//
+// Two tilings share one kernel body:
+//   * "normal" (m > 256): 128 activation rows x BN weight rows per tile, persistent CTAs
+//     walking a group-rasterised tile list, two accumulator buffers so the epilogue of
+//     tile i overlaps the main loop of tile i+1.
+//   * "swap" (m <= 256, decode): the weight matrix is the 128-row MMA operand and the
+//     (padded) batch is the MMA N dimension, so tiny batches still use full-width MMAs and
+//     the kernel is a pure weight stream; split-K spreads narrow layers over all SMs, the
+//     last CTA of a tile (ticket counter) sums the fp32 partials from the workspace.
+//
+// Warp roles (256 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warp 2 = TMEM
+// allocator, warps 4-7 = epilogue (warp w reads TMEM lanes 32*(w%4)..).
+// Every mbarrier wait is bounded; on expiry the kernel records kStatusPipelineTimeout in
+// *status and all roles drain out, TMEM is freed, and the host raises.
+#include <algorithm>
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace mb200 {
+namespace {
+
+constexpr int kBM = 128;            // rows of the MMA "M" operand per instruction
+constexpr int kRowBytes = 128;      // bytes of K per pipeline stage row (one swizzle span)
+constexpr int kUmmaKBytes = 32;     // bytes of K consumed by one tcgen05.mma
+constexpr int kThreads = 256;
+
+struct KParams {
+  void* out;
+  const void* bias;
+  const void* residual;
+  const float* a_scale;
+  const float* b_scale;
+  float* workspace;
+  int* counters;
+  int* status;
+  int m, n, k_blocks;
+  int64_t ldc, ld_res;
+  int tiles_r, tiles_c;  // tiles over the row-operand rows / column-operand rows
+  int splits, kb_per_split;
+  int out_f16;           // 0: bf16 output, 1: fp16 output
+  int is_int8;
+  uint32_t idesc;
+};
+
+template <int BN, bool SWAP, bool SWIGLU>
+struct Cfg {
+  static constexpr int R = (SWAP && SWIGLU) ? 2 : 1;         // 128-row MMA tiles per stage
+  static constexpr int kRowTileBytes = kBM * R * kRowBytes;   // 16 KB * R
+  static constexpr int kColTileBytes = BN * kRowBytes;
+  static constexpr int kStageBytes = kRowTileBytes + kColTileBytes;
+  static constexpr int kStagesRaw = SWAP ? (98304 / kStageBytes) : (196608 / kStageBytes);
+  static constexpr int kStages = kStagesRaw < 3 ? 3 : (kStagesRaw > 6 ? 6 : kStagesRaw);
+  static constexpr int kAccBufs = SWAP ? 1 : 2;
+  static constexpr int kAccCols = R * BN;
+  static constexpr int kTmemColsRaw = kAccBufs * kAccCols;
+  static constexpr int kTmemCols =
+      kTmemColsRaw <= 32 ? 32 : (kTmemColsRaw <= 64 ? 64 : (kTmemColsRaw <= 128 ? 128 : (kTmemColsRaw <= 256 ? 256 : 512)));
+  static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 + 256;
+  static_assert(kTmemColsRaw <= 512, "accumulators exceed tensor memory");
+  static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "invalid MMA N");
+};
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.f + __expf(-v)); }
+
+__device__ __forceinline__ uint32_t pack_out2(float lo, float hi, int out_f16) {
+  if (out_f16) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  return pack_bf16x2(lo, hi);
+}
+__device__ __forceinline__ float load_out1(const void* base, int64_t idx, int out_f16) {
+  if (out_f16) return __half2float(static_cast<const __half*>(base)[idx]);
+  return __bfloat162float(static_cast<const __nv_bfloat16*>(base)[idx]);
+}
+__device__ __forceinline__ void store_out1(void* base, int64_t idx, float v, int out_f16) {
+  if (out_f16)
+    static_cast<__half*>(base)[idx] = __float2half_rn(v);
+  else
+    static_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16_rn(v);
+}
+__device__ __forceinline__ float acc_to_float(uint32_t raw, int is_int8) {
+  return is_int8 ? static_cast<float>(static_cast<int32_t>(raw)) : __uint_as_float(raw);
+}
+
+template <int BN, bool SWAP, bool SWIGLU>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_constant__ CUtensorMap tm_col,
+                    const KParams p) {
+  using C = Cfg<BN, SWAP, SWIGLU>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(C::kStages) * C::kStageBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + C::kStages;
+  uint64_t* acc_full = bars + 2 * C::kStages;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  int* ticket_slot = const_cast<int*>(abort_flag) + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 128);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_row);
+    tma_prefetch_desc(&tm_col);
+  }
+  __syncthreads();
+  if (warp == 2) {
+    tmem_alloc(tmem_holder, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const int total_tiles = p.tiles_r * p.tiles_c;
+  const int total_work = total_tiles * p.splits;
+
+  // work item -> (row tile, column tile, k range)
+  auto decode = [&](int w, int& tr, int& tc, int& kb0, int& kb1, int& split) {
+    split = w % p.splits;
+    const int tile = w / p.splits;
+    if (SWAP) {
+      tr = tile;
+      tc = 0;
+    } else {
+      constexpr int kGroup = 16;  // row tiles per raster group: a wave shares ~16 A tiles x ~9 B tiles in L2
+      const int per_group = kGroup * p.tiles_c;
+      const int g = tile / per_group;
+      const int first = g * kGroup;
+      const int gsize = min(p.tiles_r - first, kGroup);
+      const int in = tile - g * per_group;
+      tr = first + in % gsize;
+      tc = in / gsize;
+    }
+    kb0 = split * p.kb_per_split;
+    kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+  };
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+      int tr, tc, kb0, kb1, split;
+      decode(w, tr, tc, kb0, kb1, split);
+      const int k_elems_per_block = p.is_int8 ? kRowBytes : kRowBytes / 2;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (*abort_flag || !mbar_wait(&empty_bar[stage], phase ^ 1)) {
+          ok = false;
+          break;
+        }
+        uint8_t* row_tile = smem + static_cast<size_t>(stage) * C::kStageBytes;
+        uint8_t* col_tile = row_tile + C::kRowTileBytes;
+        mbar_arrive_expect_tx(&full_bar[stage], C::kStageBytes);
+        tma_load_2d(row_tile, &tm_row, &full_bar[stage], kb * k_elems_per_block, tr * kBM * C::R);
+        tma_load_2d(col_tile, &tm_col, &full_bar[stage], kb * k_elems_per_block, tc * BN);
+        if (++stage == C::kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+    if (!ok) {
+      *abort_flag = 1;
+      if (p.status != nullptr) atomicExch(p.status, kStatusPipelineTimeout);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ------------------------------ MMA issuer --------------------------------
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    int it = 0;
+    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++it) {
+      int tr, tc, kb0, kb1, split;
+      decode(w, tr, tc, kb0, kb1, split);
+      const int acc = SWAP ? 0 : (it & 1);
+      const uint32_t acc_phase = SWAP ? (it & 1) : ((it >> 1) & 1);
+      if (*abort_flag || !mbar_wait(&acc_empty[acc], acc_phase ^ 1)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t d_base = tmem_base + acc * C::kAccCols;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (*abort_flag || !mbar_wait(&full_bar[stage], phase)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t row_addr = smem_u32(smem + static_cast<size_t>(stage) * C::kStageBytes);
+        const uint32_t col_addr = row_addr + C::kRowTileBytes;
+#pragma unroll
+        for (int r = 0; r < C::R; ++r) {
+#pragma unroll
+          for (int kk = 0; kk < kRowBytes / kUmmaKBytes; ++kk) {
+            const uint64_t a_desc = umma_desc_k_sw128(row_addr + r * (kBM * kRowBytes) + kk * kUmmaKBytes);
+            const uint64_t b_desc = umma_desc_k_sw128(col_addr + kk * kUmmaKBytes);
+            const uint32_t accum = (kb > kb0 || kk > 0) ? 1u : 0u;
+            if (p.is_int8)
+              umma_i8(d_base + r * BN, a_desc, b_desc, p.idesc, accum);
+            else
+              umma_f16(d_base + r * BN, a_desc, b_desc, p.idesc, accum);
+          }
+        }
+        umma_commit(&empty_bar[stage]);  // stage reusable once these MMAs have read it
+        if (++stage == C::kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (ok) umma_commit(&acc_full[acc]);
+    }
+    if (!ok) {
+      *abort_flag = 1;
+      if (p.status != nullptr) atomicExch(p.status, kStatusPipelineTimeout);
+    }
+  } else if (warp >= 4) {
+    // ------------------------------ epilogue -----------------------------------
+    const int ew = warp - 4;             // TMEM lane quadrant
+    const int row_in_tile = ew * 32 + lane;
+    bool ok = true;
+    int it = 0;
+    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++it) {
+      int tr, tc, kb0, kb1, split;
+      decode(w, tr, tc, kb0, kb1, split);
+      const int acc = SWAP ? 0 : (it & 1);
+      const uint32_t acc_phase = SWAP ? (it & 1) : ((it >> 1) & 1);
+      if (*abort_flag || !mbar_wait(&acc_full[acc], acc_phase)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t t_base = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + acc * C::kAccCols;
+
+      if constexpr (!SWAP) {
+        // thread = one output row; columns in chunks of 32
+        const int64_t row = static_cast<int64_t>(tr) * kBM + row_in_tile;
+        const bool row_ok = row < p.m;
+        const float sa = (p.is_int8 && row_ok) ? p.a_scale[row] : 1.f;
+        constexpr int kOutCols = SWIGLU ? BN / 2 : BN;
+        const int64_t col0 = static_cast<int64_t>(tc) * kOutCols;
+        const int n_out = SWIGLU ? p.n / 2 : p.n;
+#pragma unroll 1
+        for (int c = 0; c < kOutCols; c += 32) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(t_base + c, r0);
+          if constexpr (SWIGLU) tmem_ld_32x32(t_base + BN / 2 + c, r1);
+          tmem_ld_wait();
+          if (!row_ok) continue;
+#pragma unroll
+          for (int v8 = 0; v8 < 4; ++v8) {
+            const int64_t col = col0 + c + v8 * 8;
+            if (col >= n_out) break;
+            float f[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float x = acc_to_float(r0[v8 * 8 + j], p.is_int8);
+              if constexpr (SWIGLU) {
+                float u = acc_to_float(r1[v8 * 8 + j], p.is_int8);
+                if (p.is_int8) {
+                  x *= sa * p.b_scale[tc * BN + c + v8 * 8 + j];
+                  u *= sa * p.b_scale[tc * BN + BN / 2 + c + v8 * 8 + j];
+                }
+                x = silu_f(x) * u;
+              } else {
+                if (p.is_int8) x *= sa * p.b_scale[col + j];
+                if (p.bias != nullptr) x += load_out1(p.bias, col + j, p.out_f16);
+              }
+              f[j] = x;
+            }
+            if (!SWIGLU && p.residual != nullptr) {
+              const uint4 rv = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.residual) +
+                                                               row * p.ld_res + col);
+              const uint32_t* ru = reinterpret_cast<const uint32_t*>(&rv);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float2 q;
+                if (p.out_f16) {
+                  q = __half22float2(*reinterpret_cast<const __half2*>(&ru[j]));
+                } else {
+                  q = unpack_bf16x2(ru[j]);
+                }
+                f[2 * j] += q.x;
+                f[2 * j + 1] += q.y;
+              }
+            }
+            uint4 o;
+            o.x = pack_out2(f[0], f[1], p.out_f16);
+            o.y = pack_out2(f[2], f[3], p.out_f16);
+            o.z = pack_out2(f[4], f[5], p.out_f16);
+            o.w = pack_out2(f[6], f[7], p.out_f16);
+            *reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + row * p.ldc + col) = o;
+          }
+        }
+      } else {
+        // thread = one weight row (output column); accumulator column j = activation row j
+        const int64_t nrow0 = static_cast<int64_t>(tr) * kBM * C::R;  // first weight row of the tile
+        const int m_cols = min(p.m, BN);
+        if (p.splits > 1) {
+          // 1) publish fp32 partials: workspace[split][j][weight_row]
+#pragma unroll 1
+          for (int r = 0; r < C::R; ++r) {
+            const int64_t wrow = nrow0 + r * kBM + row_in_tile;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+              uint32_t v[16];
+              tmem_ld_32x16(t_base + r * BN + c, v);
+              tmem_ld_wait();
+              if (wrow < p.n) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  if (c + j < m_cols)
+                    p.workspace[(static_cast<int64_t>(split) * p.m + (c + j)) * p.n + wrow] =
+                        acc_to_float(v[j], p.is_int8);
+                }
+              }
+            }
+          }
+          __threadfence();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (row_in_tile == 0) {
+            const int t = atomicAdd(&p.counters[tr], 1);
+            *ticket_slot = t;
+            if (t == p.splits - 1) p.counters[tr] = 0;  // self-reset for the next launch
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          const bool last = (*ticket_slot == p.splits - 1);
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (last) {
+            __threadfence();
+            const int64_t wrow = nrow0 + row_in_tile;
+            if (wrow < p.n) {
+              for (int j = 0; j < m_cols; ++j) {
+                float x = 0.f, u = 0.f;
+                for (int s = 0; s < p.splits; ++s) {
+                  const float* ws = p.workspace + (static_cast<int64_t>(s) * p.m + j) * p.n;
+                  x += __ldcg(ws + wrow);
+                  if constexpr (SWIGLU) u += __ldcg(ws + wrow + kBM);
+                }
+                int64_t ocol;
+                if constexpr (SWIGLU) {
+                  if (p.is_int8) {
+                    x *= p.a_scale[j] * p.b_scale[wrow];
+                    u *= p.a_scale[j] * p.b_scale[wrow + kBM];
+                  }
+                  x = silu_f(x) * u;
+                  ocol = static_cast<int64_t>(tr) * kBM + row_in_tile;
+                } else {
+                  if (p.is_int8) x *= p.a_scale[j] * p.b_scale[wrow];
+                  if (p.bias != nullptr) x += load_out1(p.bias, wrow, p.out_f16);
+                  if (p.residual != nullptr) x += load_out1(p.residual, j * p.ld_res + wrow, p.out_f16);
+                  ocol = wrow;
+                }
+                store_out1(p.out, j * p.ldc + ocol, x, p.out_f16);
+              }
+            }
+          }
+        } else {
+          const int64_t wrow = nrow0 + row_in_tile;
+#pragma unroll 1
+          for (int c = 0; c < BN; c += 16) {
+            uint32_t v0[16], v1[16];
+            tmem_ld_32x16(t_base + c, v0);
+            if constexpr (SWIGLU) tmem_ld_32x16(t_base + BN + c, v1);
+            tmem_ld_wait();
+            if (wrow >= p.n) continue;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int mi = c + j;
+              if (mi >= m_cols) break;
+              float x = acc_to_float(v0[j], p.is_int8);
+              int64_t ocol;
+              if constexpr (SWIGLU) {
+                float u = acc_to_float(v1[j], p.is_int8);
+                if (p.is_int8) {
+                  x *= p.a_scale[mi] * p.b_scale[wrow];
+                  u *= p.a_scale[mi] * p.b_scale[wrow + kBM];
+                }
+                x = silu_f(x) * u;
+                ocol = static_cast<int64_t>(tr) * kBM + row_in_tile;
+              } else {
+                if (p.is_int8) x *= p.a_scale[mi] * p.b_scale[wrow];
+                if (p.bias != nullptr) x += load_out1(p.bias, wrow, p.out_f16);
+                if (p.residual != nullptr) x += load_out1(p.residual, mi * p.ld_res + wrow, p.out_f16);
+                ocol = wrow;
+              }
+              store_out1(p.out, mi * p.ldc + ocol, x, p.out_f16);
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&acc_empty[acc]);
+    }
+    if (!ok) {
+      *abort_flag = 1;
+      if (p.status != nullptr) atomicExch(p.status, kStatusPipelineTimeout);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    // give copies that may still be in flight time to land before the CTA's memory is reused
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeFn>(sym);
+    }
+  });
+  return fn;
+}
+
+// 2-D row-major matrix [rows, k] (k contiguous, `ld` elements between rows); box = 128 bytes of k x box_rows.
+bool make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int64_t ld, int elem_bytes,
+                      CUtensorMapDataType type, int box_rows) {
+  EncodeFn fn = get_encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * elem_bytes};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kRowBytes / elem_bytes), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, type, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+template <int BN, bool SWAP, bool SWIGLU>
+int launch_cfg(const CUtensorMap& tr, const CUtensorMap& tc, const KParams& p, int grid, cudaStream_t s) {
+  using C = Cfg<BN, SWAP, SWIGLU>;
+  auto kern = gemm_tcgen05_kernel<BN, SWAP, SWIGLU>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(C::kSmemBytes)) !=
+        cudaSuccess)
+      return -3;
+    attr_set = true;
+  }
+  kern<<<grid, kThreads, C::kSmemBytes, s>>>(tr, tc, p);
+  note_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+int pick_splits(int tiles, int k_blocks, int m, int n, int num_sms, size_t ws_bytes) {
+  if (tiles >= num_sms) return 1;
+  int best = 1;
+  double best_eff = 0.0;
+  const int max_s = std::max(1, std::min(16, k_blocks / 4));
+  for (int s = 1; s <= max_s; ++s) {
+    if (s > 1 && static_cast<size_t>(s) * m * n * sizeof(float) > ws_bytes) break;
+    const int work = tiles * s;
+    const int waves = (work + num_sms - 1) / num_sms;
+    // time model: waves * (k per split) plus a fixed per-CTA cost of ~3 k-blocks
+    const double kper = (k_blocks + s - 1) / s + 3.0;
+    const double eff = 1.0 / (waves * kper);
+    if (eff > best_eff * 1.02) {
+      best_eff = eff;
+      best = s;
+    }
+  }
+  return best;
+}
+
+}  // namespace
+
+size_t gemm_workspace_bytes(int, int, int, int) { return size_t(64) << 20; }
+
+int launch_gemm(const GemmArgs& a, cudaStream_t s) {
+  if (a.m <= 0 || a.n <= 0) return 0;
+  const int eb = a.is_int8 ? 1 : 2;
+  const int k_per_block = kRowBytes / eb;
+  if (a.k % (16 / eb) != 0 || a.lda % (16 / eb) != 0 || a.ldb % (16 / eb) != 0) return -1;
+  if (a.n % 8 != 0 || a.ldc % 8 != 0) return -1;
+  if (a.swiglu && (a.n % 256 != 0 || a.bias != nullptr || a.residual != nullptr)) return -1;
+  if ((reinterpret_cast<uintptr_t>(a.a) | reinterpret_cast<uintptr_t>(a.b) | reinterpret_cast<uintptr_t>(a.out)) & 15)
+    return -1;
+  if (a.residual != nullptr && ((reinterpret_cast<uintptr_t>(a.residual) & 15) || a.ld_res % 8 != 0)) return -1;
+
+  KParams p{};
+  p.out = a.out;
+  p.bias = a.bias;
+  p.residual = a.residual;
+  p.a_scale = a.a_scale;
+  p.b_scale = a.b_scale;
+  p.workspace = a.workspace;
+  p.counters = a.counters;
+  p.status = a.status;
+  p.m = a.m;
+  p.n = a.n;
+  p.k_blocks = (a.k + k_per_block - 1) / k_per_block;
+  p.ldc = a.ldc;
+  p.ld_res = a.ld_res;
+  p.out_f16 = (a.dt == kF16) ? 1 : 0;
+  p.is_int8 = a.is_int8;
+  p.splits = 1;
+  p.kb_per_split = p.k_blocks;
+
+  const CUtensorMapDataType type =
+      a.is_int8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                : (a.dt == kF16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+  const uint32_t ab_fmt = a.is_int8 ? 1u : (a.dt == kF16 ? 0u : 1u);
+  const uint32_t c_fmt = a.is_int8 ? 2u : 1u;
+  const int num_sms = a.num_sms > 0 ? a.num_sms : 148;
+  CUtensorMap tm_row, tm_col;
+
+  if (a.m > 256) {
+    // ---- normal tiling: activations are the 128-row operand ----
+    int bn = 256;
+    if (!a.swiglu) {
+      const int64_t tiles256 = static_cast<int64_t>((a.m + kBM - 1) / kBM) * ((a.n + 255) / 256);
+      if (tiles256 < num_sms || a.n % 256 != 0) bn = 128;
+    }
+    p.tiles_r = (a.m + kBM - 1) / kBM;
+    p.tiles_c = (a.n + bn - 1) / bn;
+    p.idesc = umma_idesc(kBM, bn, c_fmt, ab_fmt, ab_fmt);
+    if (!make_operand_map(&tm_row, a.a, a.m, a.k, a.lda, eb, type, kBM)) return -2;
+    if (!make_operand_map(&tm_col, a.b, a.n, a.k, a.ldb, eb, type, bn)) return -2;
+    const int grid = std::min(p.tiles_r * p.tiles_c, num_sms);
+    if (a.swiglu) return launch_cfg<256, false, true>(tm_row, tm_col, p, grid, s);
+    if (bn == 256) return launch_cfg<256, false, false>(tm_row, tm_col, p, grid, s);
+    return launch_cfg<128, false, false>(tm_row, tm_col, p, grid, s);
+  }
+
+  // ---- swap tiling: weights are the 128-row operand, the batch is MMA N ----
+  int bn = 16;
+  while (bn < a.m) bn <<= 1;
+  const int r = a.swiglu ? 2 : 1;
+  p.tiles_r = (a.n + kBM * r - 1) / (kBM * r);
+  p.tiles_c = 1;
+  p.idesc = umma_idesc(kBM, bn, c_fmt, ab_fmt, ab_fmt);
+  if (a.workspace != nullptr && a.counters != nullptr && p.tiles_r <= a.num_counters) {
+    p.splits = pick_splits(p.tiles_r, p.k_blocks, a.m, a.n, num_sms, a.workspace_bytes);
+    p.kb_per_split = (p.k_blocks + p.splits - 1) / p.splits;
+    p.splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
+  }
+  if (!make_operand_map(&tm_row, a.b, a.n, a.k, a.ldb, eb, type, kBM * r)) return -2;
+  if (!make_operand_map(&tm_col, a.a, a.m, a.k, a.lda, eb, type, bn)) return -2;
+  const int grid = p.tiles_r * p.splits;
+#define MB200_SWAP_CASE(BNV)                                                            \
+  case BNV:                                                                             \
+    return a.swiglu ? launch_cfg<BNV, true, true>(tm_row, tm_col, p, grid, s)           \
+                    : launch_cfg<BNV, true, false>(tm_row, tm_col, p, grid, s);
+  switch (bn) {
+    MB200_SWAP_CASE(16)
+    MB200_SWAP_CASE(32)
+    MB200_SWAP_CASE(64)
+    MB200_SWAP_CASE(128)
+    MB200_SWAP_CASE(256)
+  }
+#undef MB200_SWAP_CASE
+  return -1;
+}
+
+}  // namespace mb200

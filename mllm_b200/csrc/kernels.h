@@ -1,0 +1,78 @@
+// Host-callable launchers of the sm_100a kernels (plain C++ signatures: raw
+// device pointers + a stream, no framework types). The PyTorch binding in
+// bindings.cpp validates tensors and forwards here; other hosts can link the
+// same symbols.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mb200 {
+
+enum DType : int { kBF16 = 0, kF16 = 1, kF32 = 2 };
+
+// Number of kernel launches issued through these launchers since load.
+uint64_t launch_count();
+void note_launch(int n = 1);
+
+// ----- element-wise / normalisation --------------------------------------------------
+void launch_rmsnorm(const void* x, const void* w, void* out, int rows, int hidden, int64_t x_stride,
+                    int64_t out_stride, float eps, DType dt, cudaStream_t s);
+void launch_fused_add_rmsnorm(void* x, void* residual, const void* w, int rows, int hidden, float eps, DType dt,
+                              cudaStream_t s);
+void launch_layernorm(const void* x, const void* w, const void* b, void* out, int rows, int hidden, float eps,
+                      DType dt, cudaStream_t s);
+// act: 0 = silu(gate)*up, 1 = gelu_tanh(gate)*up ; x is [rows, 2*inter] = [gate | up]
+void launch_act_and_mul(const void* x, void* out, int rows, int inter, int act, DType dt, cudaStream_t s);
+void launch_gelu_tanh(const void* x, void* out, int64_t n, DType dt, cudaStream_t s);
+void launch_embedding(const int64_t* ids, const void* table, void* out, int tokens, int hidden, int vocab,
+                      DType dt, int* status, cudaStream_t s);
+
+// Per-head RMSNorm of q and k (weights may be null), NeoX rotary embedding and the
+// write of K (normed, rotated) and V into the slot-indexed cache; q and k are updated
+// in place inside the fused qkv activation. head_dim is 128 or 64.
+// positions: [pos_rows, tokens] int64 with pos_rows 1 (plain RoPE) or 3 (M-RoPE: t,h,w);
+// axis_map[head_dim/2] selects the position row per frequency (null -> row 0).
+void launch_qk_norm_rope_kv_write(void* qkv, const void* q_w, const void* k_w, const int64_t* positions,
+                                  int pos_rows, const int8_t* axis_map, const float* inv_freq,
+                                  const int64_t* cache_loc, void* k_cache, void* v_cache, int tokens,
+                                  int num_q_heads, int num_kv_heads, int head_dim, int64_t qkv_stride,
+                                  int64_t num_slots, float eps, DType dt, int* status, cudaStream_t s);
+void launch_kv_write(const void* k, const void* v, const int64_t* loc, void* k_cache, void* v_cache, int tokens,
+                     int row_elems, int64_t k_stride, int64_t v_stride, int64_t num_slots, DType dt, int* status,
+                     cudaStream_t s);
+
+// ----- quantisation -------------------------------------------------------------------
+void launch_per_token_quant_int8(const void* x, int8_t* q, float* scale, int rows, int k, DType dt,
+                                 cudaStream_t s);
+
+// ----- sampling -------------------------------------------------------------------------
+void launch_argmax(const void* logits, int64_t* out, int rows, int vocab, int64_t stride, DType dt,
+                   cudaStream_t s);
+
+// ----- GEMM (tcgen05 + TMEM + TMA) ---------------------------------------------------
+struct GemmArgs {
+  const void* a;         // [m, k] row-major activations
+  const void* b;         // [n, k] row-major weights (out = a * b^T)
+  void* out;             // [m, n_out] row-major
+  const void* bias;      // [n] or null
+  const void* residual;  // [m, n] or null (added before rounding)
+  const float* a_scale;  // int8 only: per-row scale [m]
+  const float* b_scale;  // int8 only: per-column scale [n]
+  int m, n, k;
+  int64_t lda, ldb, ldc, ld_res;
+  int swiglu;            // 1: b rows alternate 128 gate / 128 up rows; out is [m, n/2]
+  DType dt;              // element type of a, b (kBF16 / kF16) ; out has the same type
+  int is_int8;           // 1: a, b are int8, out type given by dt
+  float* workspace;      // split-K partial sums (small-m path), may be null when not needed
+  size_t workspace_bytes;
+  int* counters;         // split-K tile tickets, zero-initialised, self-resetting
+  int num_counters;
+  int* status;           // device int, set non-zero when a bounded wait ran out
+  int num_sms;
+};
+// Returns 0 on success, a negative code when the shape is unsupported (caller falls back / raises).
+int launch_gemm(const GemmArgs& args, cudaStream_t s);
+size_t gemm_workspace_bytes(int m, int n, int k, int num_sms);
+
+}  // namespace mb200

@@ -1,0 +1,13 @@
+from .base_prefix_cache import (
+    BasePrefixCache, EvictResult, InsertResult, MatchResult, RadixKey,
+    hash_bytes, hash_to_int64, hash_token_ids,
+)
+from .chunk_cache import ChunkCache
+from .memory_pool import KVPool, ReqToTokenPool, TokenToKVPoolAllocator
+from .radix_cache import RadixCache, TreeNode
+
+__all__ = [
+    "BasePrefixCache", "EvictResult", "InsertResult", "MatchResult", "RadixKey",
+    "hash_bytes", "hash_to_int64", "hash_token_ids", "ChunkCache", "KVPool",
+    "ReqToTokenPool", "TokenToKVPoolAllocator", "RadixCache", "TreeNode",
+]

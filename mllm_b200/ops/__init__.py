@@ -1,0 +1,290 @@
+"""Operator front-end: one Python function per hot op.
+
+For tensors on a GPU every function launches the hand-written sm_100a kernel
+from the in-tree ``mllm_b200_C`` extension and raises if that extension cannot
+be loaded — there is no silent framework fallback on a GPU.  For CPU tensors
+(tests, fp32 oracle) the plain-PyTorch statement in :mod:`.reference` runs.
+``MLLM_B200_FORCE_TORCH=1`` forces the PyTorch statement everywhere, which the
+tests use to compare kernel output against it on the same device.
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Optional, Tuple
+
+import torch
+
+from . import reference as ref
+
+_FORCE_TORCH = os.environ.get("MLLM_B200_FORCE_TORCH", "0") == "1"
+_ext = None
+
+
+def ext():
+    """The CUDA extension module (loaded on first use; raises when unavailable)."""
+    global _ext
+    if _ext is None:
+        from .._build import load_extension
+
+        mod = load_extension("mllm_b200_C")
+        if mod is None:
+            raise RuntimeError(
+                "mllm_b200: the sm_100a kernel extension (mllm_b200_C) is not built; "
+                "run `python -m mllm_b200._build` or `__graft_entry__.build()`."
+            )
+        _ext = mod
+    return _ext
+
+
+def use_kernels(t: torch.Tensor) -> bool:
+    return t.is_cuda and not _FORCE_TORCH
+
+
+def force_torch(flag: bool) -> None:
+    """Switch the PyTorch statements on/off at run time (A/B tests)."""
+    global _FORCE_TORCH
+    _FORCE_TORCH = bool(flag)
+
+
+def launch_count() -> int:
+    """Kernels launched by this package's launchers so far (host-side count)."""
+    return int(ext().launch_count()) if _ext is not None or torch.cuda.is_available() else 0
+
+
+def check_status(device: Optional[int] = None) -> None:
+    """Raise if a kernel recorded an error status (bounded wait expired / bad index). Synchronises."""
+    if _ext is None:
+        return
+    dev = torch.cuda.current_device() if device is None else device
+    code = int(_ext.read_status(dev))
+    if code:
+        names = {1: "pipeline wait timed out", 2: "peer flag wait timed out", 3: "index out of range"}
+        raise RuntimeError(f"mllm_b200 kernel error status {code}: {names.get(code, 'unknown')}")
+
+
+# --------------------------------------------------------------------------
+def _2d(x: torch.Tensor) -> torch.Tensor:
+    return x if x.dim() == 2 else x.reshape(-1, x.shape[-1])
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if not use_kernels(x):
+        return ref.rmsnorm(x, weight, eps, out)
+    x2 = _2d(x)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    o = torch.empty(x2.shape, dtype=x.dtype, device=x.device) if out is None else _2d(out)
+    ext().rmsnorm(x2, weight, o, eps)
+    return o.view(x.shape) if out is None else out
+
+
+def fused_add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
+    if not use_kernels(x):
+        return ref.fused_add_rmsnorm(x, residual, weight, eps)
+    ext().fused_add_rmsnorm(_2d(x), _2d(residual), weight, eps)
+
+
+def layernorm(x, weight, bias, eps: float) -> torch.Tensor:
+    if not use_kernels(x):
+        return ref.layernorm(x, weight, bias, eps)
+    x2 = _2d(x).contiguous()
+    out = torch.empty_like(x2)
+    ext().layernorm(x2, weight, bias, out, eps)
+    return out.view(x.shape)
+
+
+def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
+    if not use_kernels(x):
+        return ref.silu_and_mul(x)
+    x2 = _2d(x).contiguous()
+    out = torch.empty((x2.shape[0], x2.shape[1] // 2), dtype=x.dtype, device=x.device)
+    ext().act_and_mul(x2, out, 0)
+    return out.view(*x.shape[:-1], -1)
+
+
+def gelu_tanh_and_mul(x: torch.Tensor) -> torch.Tensor:
+    if not use_kernels(x):
+        return ref.gelu_tanh_and_mul(x)
+    x2 = _2d(x).contiguous()
+    out = torch.empty((x2.shape[0], x2.shape[1] // 2), dtype=x.dtype, device=x.device)
+    ext().act_and_mul(x2, out, 1)
+    return out.view(*x.shape[:-1], -1)
+
+
+def gelu_tanh(x: torch.Tensor) -> torch.Tensor:
+    if not use_kernels(x) or x.numel() % 8:
+        return ref.gelu_tanh(x)
+    xc = x.contiguous()
+    out = torch.empty_like(xc)
+    ext().gelu_tanh(xc, out)
+    return out
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    if not use_kernels(table):
+        return ref.embedding(ids, table)
+    flat = ids.reshape(-1).to(torch.int64).contiguous()
+    out = torch.empty((flat.numel(), table.shape[1]), dtype=table.dtype, device=table.device)
+    ext().embedding(flat, table, out)
+    return out.view(*ids.shape, table.shape[1])
+
+
+# --------------------------------------------------------------------------
+# GEMMs
+# --------------------------------------------------------------------------
+SWIGLU_BLOCK = 128  # row interleave of fused gate/up weights expected by linear_swiglu
+
+
+def linear(
+    x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+    residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """``x @ weight.T (+bias) (+residual)`` — tcgen05 GEMM on GPU."""
+    if not use_kernels(x):
+        y = ref.linear(x, weight, bias, residual)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    x2 = _2d(x)
+    if x2.stride(-1) != 1 or (x2.stride(0) * x2.element_size()) % 16:
+        x2 = x2.contiguous()
+    o = torch.empty((x2.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device) if out is None else _2d(out)
+    r2 = None if residual is None else _2d(residual)
+    ext().gemm(x2, weight, o, bias, r2, False, None, None)
+    return o.view(*x.shape[:-1], weight.shape[0]) if out is None else out
+
+
+def linear_swiglu(x: torch.Tensor, weight: torch.Tensor, block: int = SWIGLU_BLOCK) -> torch.Tensor:
+    """``silu(x Wg^T) * (x Wu^T)`` in one GEMM; ``weight`` rows alternate ``block`` gate / ``block`` up rows."""
+    if not use_kernels(x) or block != SWIGLU_BLOCK or weight.shape[0] % 256:
+        return ref.linear_swiglu(x, weight, block)
+    x2 = _2d(x)
+    if x2.stride(-1) != 1 or (x2.stride(0) * x2.element_size()) % 16:
+        x2 = x2.contiguous()
+    o = torch.empty((x2.shape[0], weight.shape[0] // 2), dtype=x.dtype, device=x.device)
+    ext().gemm(x2, weight, o, None, None, True, None, None)
+    return o.view(*x.shape[:-1], weight.shape[0] // 2)
+
+
+def per_token_quant_int8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    if not use_kernels(x):
+        return ref.per_token_quant_int8(x)
+    q, s = ext().per_token_quant_int8(_2d(x).contiguous())
+    return q.view(x.shape), s.view(*x.shape[:-1], 1)
+
+
+def int8_scaled_mm(a_q, w_q, a_scale, w_scale, out_dtype, bias=None) -> torch.Tensor:
+    """W8A8: ``(a_q @ w_q.T) * a_scale * w_scale`` with s32 accumulation (tcgen05 kind::i8 on GPU)."""
+    if not use_kernels(a_q):
+        return ref.int8_scaled_mm(a_q, w_q, a_scale, w_scale, out_dtype, bias)
+    a2 = _2d(a_q).contiguous()
+    out = torch.empty((a2.shape[0], w_q.shape[0]), dtype=out_dtype, device=a_q.device)
+    ext().gemm(a2, w_q, out, bias, None, False, a_scale.reshape(-1).contiguous(), w_scale.reshape(-1).contiguous())
+    return out.view(*a_q.shape[:-1], w_q.shape[0])
+
+
+def w4a16_gemm(x, qweight, scales, zeros, group: int, bias=None) -> torch.Tensor:
+    return ref.w4a16_gemm(x, qweight, scales, zeros, group, bias)
+
+
+# --------------------------------------------------------------------------
+# rope / kv
+# --------------------------------------------------------------------------
+def rope_inv_freq(head_dim: int, theta: float, device) -> torch.Tensor:
+    return 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
+
+
+def mrope_axis_map(head_dim: int, sections, interleaved: bool, device) -> torch.Tensor:
+    half = head_dim // 2
+    axis = torch.zeros(half, dtype=torch.int8)
+    if interleaved:
+        idx = torch.arange(half)
+        axis[(idx % 3 == 1) & (idx < 3 * sections[1])] = 1
+        axis[(idx % 3 == 2) & (idx < 3 * sections[2])] = 2
+    else:
+        axis[sections[0] : sections[0] + sections[1]] = 1
+        axis[sections[0] + sections[1] : sections[0] + sections[1] + sections[2]] = 2
+    return axis.to(device)
+
+
+def qk_norm_rope_kv_write(
+    qkv, q_weight, k_weight, positions, cache_loc, k_cache, v_cache,
+    num_q_heads: int, num_kv_heads: int, head_dim: int, theta: float, eps: float,
+    mrope_sections=None, mrope_interleaved: bool = False,
+    inv_freq: Optional[torch.Tensor] = None, axis_map: Optional[torch.Tensor] = None,
+) -> None:
+    if not use_kernels(qkv) or head_dim != 128:
+        return ref.qk_norm_rope_kv_write(
+            qkv, q_weight, k_weight, positions, cache_loc, k_cache, v_cache, num_q_heads, num_kv_heads,
+            head_dim, theta, eps, mrope_sections, mrope_interleaved,
+        )
+    if inv_freq is None:
+        inv_freq = rope_inv_freq(head_dim, theta, qkv.device)
+    if mrope_sections is not None and axis_map is None:
+        axis_map = mrope_axis_map(head_dim, mrope_sections, mrope_interleaved, qkv.device)
+    ext().qk_norm_rope_kv_write(
+        qkv, q_weight, k_weight, positions.to(torch.int64).contiguous(), axis_map, inv_freq,
+        cache_loc.to(torch.int64).contiguous(), k_cache, v_cache, num_q_heads, num_kv_heads, head_dim, eps,
+    )
+
+
+def kv_write(k, v, loc, k_cache, v_cache) -> None:
+    if not use_kernels(k):
+        return ref.kv_write(k, v, loc, k_cache, v_cache)
+    ext().kv_write(k, v, loc.to(torch.int64).contiguous(), k_cache, v_cache)
+
+
+# --------------------------------------------------------------------------
+# attention
+# --------------------------------------------------------------------------
+def attention_prefill(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, prefix_lens,
+                      q_start_loc, scale: float, out=None, max_q_len: int = 0) -> torch.Tensor:
+    if use_kernels(q) and hasattr(ext(), "attention_prefill"):
+        if out is None:
+            out = torch.empty((q.shape[0], q.shape[1], q.shape[2]), dtype=q.dtype, device=q.device)
+        ext().attention_prefill(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, prefix_lens,
+                                q_start_loc, scale, out, max_q_len)
+        return out
+    return ref.attention_prefill(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, prefix_lens,
+                                 q_start_loc, scale, out)
+
+
+def attention_decode(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, scale: float,
+                     out=None, max_seq_len: int = 0) -> torch.Tensor:
+    if use_kernels(q) and hasattr(ext(), "attention_decode"):
+        if out is None:
+            out = torch.empty((q.shape[0], q.shape[1], q.shape[2]), dtype=q.dtype, device=q.device)
+        ext().attention_decode(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, scale, out, max_seq_len)
+        return out
+    return ref.attention_decode(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, scale, out)
+
+
+def attention_varlen_bidirectional(q, k, v, cu_seqlens, scale: float) -> torch.Tensor:
+    return ref.attention_varlen_bidirectional(q, k, v, cu_seqlens, scale)
+
+
+# --------------------------------------------------------------------------
+# sampling
+# --------------------------------------------------------------------------
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if not use_kernels(logits):
+        r = ref.argmax(logits)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
+    l2 = _2d(logits)
+    if l2.stride(-1) != 1:
+        l2 = l2.contiguous()
+    o = torch.empty((l2.shape[0],), dtype=torch.int64, device=logits.device) if out is None else out
+    ext().argmax(l2, o)
+    return o
+
+
+apply_penalties = ref.apply_penalties
+
+
+def top_k_top_p_min_p_sample(logits, temperature, top_k, top_p, min_p, uniform) -> torch.Tensor:
+    return ref.top_k_top_p_min_p_sample(logits, temperature, top_k, top_p, min_p, uniform)

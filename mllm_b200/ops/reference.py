@@ -1,0 +1,344 @@
+"""Plain-PyTorch statement of every op in :mod:`mllm_b200.ops`.
+
+These functions are the numerical contract of the CUDA kernels: each kernel's
+test compares against the function of the same name evaluated in fp32.  They
+also run the whole engine on a machine without a GPU (CPU tests, the fp32
+oracle of the Qwen3 model).  They are never used for tensors that live on a
+GPU unless ``MLLM_B200_FORCE_TORCH=1`` is set for A/B comparisons.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+
+def _f32(x: torch.Tensor) -> torch.Tensor:
+    return x.float()
+
+
+# --------------------------------------------------------------------------
+# normalisation / activation / embedding
+# --------------------------------------------------------------------------
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    xf = _f32(x)
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * _f32(weight)
+    y = y.to(x.dtype)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def fused_add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
+    """In place: ``residual += x`` (rounded to the storage dtype), ``x = rmsnorm(residual) * weight``."""
+    s = (_f32(x) + _f32(residual)).to(residual.dtype)
+    residual.copy_(s)
+    x.copy_(rmsnorm(s, weight, eps))
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+    return F.layer_norm(_f32(x), (x.shape[-1],), _f32(weight), None if bias is None else _f32(bias), eps).to(x.dtype)
+
+
+def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
+    d = x.shape[-1] // 2
+    return (F.silu(_f32(x[..., :d])) * _f32(x[..., d:])).to(x.dtype)
+
+
+def gelu_tanh_and_mul(x: torch.Tensor) -> torch.Tensor:
+    d = x.shape[-1] // 2
+    return (F.gelu(_f32(x[..., :d]), approximate="tanh") * _f32(x[..., d:])).to(x.dtype)
+
+
+def gelu_tanh(x: torch.Tensor) -> torch.Tensor:
+    return F.gelu(_f32(x), approximate="tanh").to(x.dtype)
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    return table[ids.long()]
+
+
+# --------------------------------------------------------------------------
+# GEMMs
+# --------------------------------------------------------------------------
+def linear(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+    residual: Optional[torch.Tensor] = None,
+    out_dtype: Optional[torch.dtype] = None,
+) -> torch.Tensor:
+    """``x @ weight.T (+ bias) (+ residual)`` with fp32 accumulation, one rounding at the end."""
+    y = _f32(x) @ _f32(weight).t()
+    if bias is not None:
+        y = y + _f32(bias)
+    if residual is not None:
+        y = y + _f32(residual)
+    return y.to(out_dtype or x.dtype)
+
+
+def deinterleave_gate_up(y: torch.Tensor, block: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Split the columns of a ``[.., 2I]`` tensor whose columns alternate
+    ``block`` gate features, ``block`` up features, ... into (gate, up)."""
+    lead = y.shape[:-1]
+    v = y.reshape(*lead, -1, 2, block)
+    return v[..., 0, :].reshape(*lead, -1), v[..., 1, :].reshape(*lead, -1)
+
+
+def interleave_gate_up(w: torch.Tensor, block: int) -> torch.Tensor:
+    """Rows ``[gate(I) ; up(I)]`` -> rows alternating ``block`` gate, ``block`` up."""
+    i = w.shape[0] // 2
+    g = w[:i].reshape(i // block, 1, block, *w.shape[1:])
+    u = w[i:].reshape(i // block, 1, block, *w.shape[1:])
+    return torch.cat([g, u], dim=1).reshape(w.shape)
+
+
+def linear_swiglu(x: torch.Tensor, weight: torch.Tensor, block: int = 0) -> torch.Tensor:
+    """``silu(x Wg^T) * (x Wu^T)``; ``block`` = row interleave of ``weight`` (0: ``[gate ; up]``)."""
+    y = _f32(x) @ _f32(weight).t()
+    if block:
+        g, u = deinterleave_gate_up(y, block)
+    else:
+        d = y.shape[-1] // 2
+        g, u = y[..., :d], y[..., d:]
+    return (F.silu(g) * u).to(x.dtype)
+
+
+def per_token_quant_int8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Symmetric per-row int8: ``scale = absmax/127``, ``q = round(x/scale)``."""
+    xf = _f32(x)
+    absmax = xf.abs().amax(-1, keepdim=True).clamp_min(1e-10)
+    scale = absmax / 127.0
+    q = torch.round(xf / scale).clamp(-128, 127).to(torch.int8)
+    return q, scale.float()
+
+
+def int8_scaled_mm(
+    a_q: torch.Tensor, w_q: torch.Tensor, a_scale: torch.Tensor, w_scale: torch.Tensor,
+    out_dtype: torch.dtype, bias: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """``(a_q @ w_q.T) * a_scale[M,1] * w_scale[N]`` with exact int32 accumulation."""
+    acc = (a_q.to(torch.int32).cpu() @ w_q.to(torch.int32).cpu().t()).to(a_q.device) if a_q.is_cuda else (
+        a_q.to(torch.int32) @ w_q.to(torch.int32).t())
+    y = acc.float() * a_scale.reshape(-1, 1).float() * w_scale.reshape(1, -1).float()
+    if bias is not None:
+        y = y + _f32(bias)
+    return y.to(out_dtype)
+
+
+def unpack_int4_rows(packed: torch.Tensor) -> torch.Tensor:
+    """int32 ``[N, K/8]`` (nibble i of word j = element 8j+i) -> uint8-valued ``[N, K]`` in 0..15."""
+    shifts = torch.arange(0, 32, 4, device=packed.device, dtype=torch.int32)
+    return ((packed.unsqueeze(-1) >> shifts) & 0xF).reshape(packed.shape[0], -1)
+
+
+def dequant_w4(qweight: torch.Tensor, scales: torch.Tensor, zeros: Optional[torch.Tensor], group: int) -> torch.Tensor:
+    """``qweight`` int32 ``[N, K/8]``, ``scales`` ``[N, K/g]``, ``zeros`` uint8-valued ``[N, K/g]`` or
+    None (symmetric, zero point 8) -> fp32 ``[N, K]``."""
+    q = unpack_int4_rows(qweight).float()
+    s = scales.float().repeat_interleave(group, dim=1)
+    z = 8.0 if zeros is None else zeros.float().repeat_interleave(group, dim=1)
+    return (q - z) * s
+
+
+def w4a16_gemm(x, qweight, scales, zeros, group: int, bias=None) -> torch.Tensor:
+    y = _f32(x) @ dequant_w4(qweight, scales, zeros, group).t()
+    if bias is not None:
+        y = y + _f32(bias)
+    return y.to(x.dtype)
+
+
+# --------------------------------------------------------------------------
+# rotary embedding, QK-norm, cache write
+# --------------------------------------------------------------------------
+def rope_cos_sin(positions: torch.Tensor, head_dim: int, theta: float, rotary_dim: Optional[int] = None):
+    rd = rotary_dim or head_dim
+    inv = 1.0 / (theta ** (torch.arange(0, rd, 2, device=positions.device, dtype=torch.float32) / rd))
+    ang = positions.float().unsqueeze(-1) * inv  # [..., rd/2]
+    return ang.cos(), ang.sin()
+
+
+def apply_rope_neox(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x: [T, H, D] fp32; cos/sin: [T, rd/2]; rotates the first ``rd`` features (half-split pairing)."""
+    half = cos.shape[-1]
+    x1, x2, rest = x[..., :half], x[..., half : 2 * half], x[..., 2 * half :]
+    c, s = cos.unsqueeze(1), sin.unsqueeze(1)
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s, rest], dim=-1)
+
+
+def mrope_cos_sin(positions3: torch.Tensor, head_dim: int, theta: float, sections, interleaved: bool):
+    """positions3: [3, T] (t, h, w).  Returns cos/sin [T, D/2] whose frequency
+    index i takes its position from axis ``a(i)``: consecutive sections
+    ``[t]*s0 + [h]*s1 + [w]*s2`` or, when ``interleaved``, ``a(i) = i % 3`` for
+    ``i < 3*s1`` / ``3*s2`` (h, w) and t elsewhere (pymllm/layers/rope.py:320-408)."""
+    half = head_dim // 2
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=positions3.device, dtype=torch.float32) / head_dim))
+    ang = positions3.float().unsqueeze(-1) * inv  # [3, T, half]
+    axis = torch.zeros(half, dtype=torch.long, device=positions3.device)
+    if interleaved:
+        idx = torch.arange(half, device=positions3.device)
+        axis[(idx % 3 == 1) & (idx < 3 * sections[1])] = 1
+        axis[(idx % 3 == 2) & (idx < 3 * sections[2])] = 2
+    else:
+        axis[sections[0] : sections[0] + sections[1]] = 1
+        axis[sections[0] + sections[1] : sections[0] + sections[1] + sections[2]] = 2
+    sel = ang.permute(1, 2, 0).gather(-1, axis.view(1, half, 1).expand(ang.shape[1], half, 1)).squeeze(-1)
+    return sel.cos(), sel.sin()
+
+
+def qk_norm_rope_kv_write(
+    qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+    positions: torch.Tensor, cache_loc: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+    num_q_heads: int, num_kv_heads: int, head_dim: int, theta: float, eps: float,
+    mrope_sections=None, mrope_interleaved: bool = False,
+) -> None:
+    """In place on ``qkv`` ``[T, (Hq+2Hkv)*D]``: per-head RMSNorm of q and k (if weights
+    given), NeoX RoPE at ``positions`` (``[T]``, or ``[3,T]`` with ``mrope_sections``); then
+    ``k_cache[cache_loc] = k`` (normed, rotated) and ``v_cache[cache_loc] = v``."""
+    T = qkv.shape[0]
+    qd, kd = num_q_heads * head_dim, num_kv_heads * head_dim
+    q = _f32(qkv[:, :qd]).reshape(T, num_q_heads, head_dim)
+    k = _f32(qkv[:, qd : qd + kd]).reshape(T, num_kv_heads, head_dim)
+    v = qkv[:, qd + kd :].reshape(T, num_kv_heads, head_dim)
+    if q_weight is not None:
+        q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * _f32(q_weight)
+        q = q.to(qkv.dtype).float()
+    if k_weight is not None:
+        k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * _f32(k_weight)
+        k = k.to(qkv.dtype).float()
+    if mrope_sections is not None:
+        cos, sin = mrope_cos_sin(positions, head_dim, theta, mrope_sections, mrope_interleaved)
+    else:
+        cos, sin = rope_cos_sin(positions, head_dim, theta)
+    q = apply_rope_neox(q, cos, sin).to(qkv.dtype)
+    k = apply_rope_neox(k, cos, sin).to(qkv.dtype)
+    qkv[:, :qd] = q.reshape(T, qd)
+    qkv[:, qd : qd + kd] = k.reshape(T, kd)
+    loc = cache_loc.long()
+    k_cache[loc] = k.to(k_cache.dtype)
+    v_cache[loc] = v.to(v_cache.dtype)
+
+
+def kv_write(k, v, loc, k_cache, v_cache) -> None:
+    k_cache[loc.long()] = k.to(k_cache.dtype)
+    v_cache[loc.long()] = v.to(v_cache.dtype)
+
+
+# --------------------------------------------------------------------------
+# attention over the slot-indexed KV pool
+# --------------------------------------------------------------------------
+def _attend(q, k, v, scale, causal_offset: Optional[int]):
+    """q [Tq,Hq,D] k,v [Tk,Hkv,D] fp32 -> [Tq,Hq,D]; key j visible to query i iff j <= i + causal_offset."""
+    Hq, Hkv = q.shape[1], k.shape[1]
+    g = Hq // Hkv
+    kk = k.repeat_interleave(g, dim=1)
+    vv = v.repeat_interleave(g, dim=1)
+    s = torch.einsum("qhd,khd->hqk", q, kk) * scale
+    if causal_offset is not None:
+        i = torch.arange(q.shape[0], device=q.device).unsqueeze(-1)
+        j = torch.arange(k.shape[0], device=q.device).unsqueeze(0)
+        s = s.masked_fill(j > i + causal_offset, float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    return torch.einsum("hqk,khd->qhd", p, vv)
+
+
+def attention_prefill(
+    q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, req_to_token: torch.Tensor,
+    req_pool_indices: torch.Tensor, seq_lens: torch.Tensor, prefix_lens: torch.Tensor,
+    q_start_loc: torch.Tensor, scale: float, out: Optional[torch.Tensor] = None, max_q_len: int = 0,
+) -> torch.Tensor:
+    """Causal attention of each request's new tokens over its cached prefix plus itself.
+
+    Request ``b`` owns query rows ``q_start_loc[b] .. +seq_lens[b]-prefix_lens[b]``; its keys
+    are the slots ``req_to_token[req_pool_indices[b], :seq_lens[b]]``; query ``i`` sees keys
+    ``0 .. prefix_lens[b]+i``."""
+    out = torch.empty_like(q) if out is None else out
+    for b in range(req_pool_indices.numel()):
+        sl, pl, qs = int(seq_lens[b]), int(prefix_lens[b]), int(q_start_loc[b])
+        n = sl - pl
+        slots = req_to_token[int(req_pool_indices[b]), :sl].long()
+        o = _attend(_f32(q[qs : qs + n]), _f32(k_cache[slots]), _f32(v_cache[slots]), scale, pl)
+        out[qs : qs + n] = o.to(out.dtype)
+    return out
+
+
+def attention_decode(
+    q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, req_to_token: torch.Tensor,
+    req_pool_indices: torch.Tensor, seq_lens: torch.Tensor, scale: float, out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """One query token per request over ``req_to_token[req, :seq_len]`` (the new token's K/V included)."""
+    out = torch.empty_like(q) if out is None else out
+    for b in range(req_pool_indices.numel()):
+        sl = int(seq_lens[b])
+        slots = req_to_token[int(req_pool_indices[b]), :sl].long()
+        o = _attend(_f32(q[b : b + 1]), _f32(k_cache[slots]), _f32(v_cache[slots]), scale, None)
+        out[b] = o[0].to(out.dtype)
+    return out
+
+
+def attention_varlen_bidirectional(q, k, v, cu_seqlens, scale) -> torch.Tensor:
+    """Full (non-causal) attention inside each segment ``cu_seqlens[i]..cu_seqlens[i+1]``; q,k,v [T,H,D]."""
+    out = torch.empty_like(q)
+    cu = cu_seqlens.tolist()
+    for a, b in zip(cu[:-1], cu[1:]):
+        out[a:b] = _attend(_f32(q[a:b]), _f32(k[a:b]), _f32(v[a:b]), scale, None).to(q.dtype)
+    return out
+
+
+# --------------------------------------------------------------------------
+# sampling
+# --------------------------------------------------------------------------
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    return torch.argmax(logits.float(), dim=-1)
+
+
+def apply_penalties(logits, output_counts, prompt_mask, frequency_penalty, presence_penalty, repetition_penalty):
+    """OpenAI-style frequency/presence penalties on generated-token counts and HF-style
+    repetition penalty on tokens seen in prompt or output.  All per-request vectors are [B]."""
+    lf = logits.float()
+    seen_out = output_counts > 0
+    lf = lf - frequency_penalty.view(-1, 1) * output_counts.float() - presence_penalty.view(-1, 1) * seen_out.float()
+    seen = seen_out | prompt_mask
+    rp = repetition_penalty.view(-1, 1)
+    lf = torch.where(seen, torch.where(lf > 0, lf / rp, lf * rp), lf)
+    return lf
+
+
+def top_k_top_p_min_p_sample(
+    logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+    min_p: Optional[torch.Tensor], uniform: torch.Tensor,
+) -> torch.Tensor:
+    """Sample one id per row. ``temperature<=1e-6`` rows are greedy; ``top_k<=0`` disables top-k.
+    ``uniform`` [B] in [0,1) drives inverse-CDF sampling over the filtered, renormalised
+    distribution taken in descending-probability order (ties broken by lower token id)."""
+    B, V = logits.shape
+    out = torch.empty(B, dtype=torch.long, device=logits.device)
+    for b in range(B):
+        t = float(temperature[b])
+        row = logits[b].float()
+        if t <= 1e-6:
+            out[b] = torch.argmax(row)
+            continue
+        p = torch.softmax(row / t, dim=-1)
+        sp, si = torch.sort(p, descending=True, stable=True)
+        keep = torch.ones(V, dtype=torch.bool, device=logits.device)
+        k = int(top_k[b])
+        if 0 < k < V:
+            keep[k:] = False
+        cum = torch.cumsum(sp, 0)
+        keep &= (cum - sp) < float(top_p[b])
+        if min_p is not None and float(min_p[b]) > 0:
+            keep &= sp >= float(min_p[b]) * sp[0]
+        keep[0] = True
+        sp = torch.where(keep, sp, torch.zeros_like(sp))
+        cdf = torch.cumsum(sp, 0)
+        u = float(uniform[b]) * float(cdf[-1])
+        idx = int(torch.searchsorted(cdf, torch.tensor(u, device=cdf.device), right=True).clamp(max=V - 1))
+        while idx > 0 and not bool(keep[idx]):
+            idx -= 1
+        out[b] = si[idx]
+    return out

@@ -1,0 +1,88 @@
+"""tcgen05 GEMM (bf16 / fp16 / int8, normal and small-batch tilings) against fp32 references."""
+import pytest
+import torch
+
+from mllm_b200 import ops
+from mllm_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rel_err(got, want):
+    return ((got.float() - want.float()).norm() / want.float().norm().clamp_min(1e-6)).item()
+
+
+SHAPES = [
+    # (m, n, k)
+    (1, 1024, 1024), (2, 4096, 4096), (3, 6144, 4096), (17, 4096, 12288), (32, 1024, 3072),
+    (127, 2048, 1024), (128, 4096, 1024), (129, 1024, 2048), (256, 4096, 4096),
+    (257, 1024, 1024), (512, 4096, 4096), (1000, 2048, 1024), (2048, 6144, 4096), (4096, 4096, 12288),
+    (300, 1000, 520),  # ragged n (multiple of 8) and k (multiple of 8)
+    (5, 151936, 1024),  # lm_head
+]
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_gemm_bf16(m, n, k):
+    torch.manual_seed(m * 7 + n + k)
+    x = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(n, k, device=DEV, dtype=torch.bfloat16) * (k ** -0.5)
+    got = ops.linear(x, w)
+    ops.check_status()
+    want = ref.linear(x, w, out_dtype=torch.float32)
+    assert _rel_err(got, want) < 6e-3
+
+
+@pytest.mark.parametrize("m", [4, 64, 300, 1024])
+def test_gemm_fp16_bias_residual(m):
+    torch.manual_seed(m)
+    n, k = 2048, 1024
+    x = torch.randn(m, k, device=DEV, dtype=torch.float16)
+    w = torch.randn(n, k, device=DEV, dtype=torch.float16) * (k ** -0.5)
+    b = torch.randn(n, device=DEV, dtype=torch.float16)
+    r = torch.randn(m, n, device=DEV, dtype=torch.float16)
+    got = ops.linear(x, w, bias=b, residual=r)
+    ops.check_status()
+    want = ref.linear(x, w, b, r, out_dtype=torch.float32)
+    assert _rel_err(got, want) < 2e-3
+
+
+@pytest.mark.parametrize("m", [1, 8, 33, 256, 300, 2048])
+@pytest.mark.parametrize("inter,k", [(3072, 1024), (768, 2048)])
+def test_gemm_swiglu(m, inter, k):
+    torch.manual_seed(m + inter)
+    x = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(2 * inter, k, device=DEV, dtype=torch.bfloat16) * (k ** -0.5)  # [gate ; up]
+    wi = ref.interleave_gate_up(w, ops.SWIGLU_BLOCK).contiguous()
+    got = ops.linear_swiglu(x, wi)
+    ops.check_status()
+    want = ref.linear_swiglu(x.float(), w.float(), 0)
+    assert _rel_err(got, want) < 8e-3
+    # the interleave helper itself
+    torch.testing.assert_close(ref.linear_swiglu(x, wi, ops.SWIGLU_BLOCK).float(), want.bfloat16().float(), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1024, 1024), (16, 4096, 4096), (200, 2048, 3072), (512, 6144, 2048), (2048, 4096, 4096)])
+def test_gemm_w8a8(m, n, k):
+    torch.manual_seed(m + n)
+    x = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    wq = torch.randint(-127, 128, (n, k), device=DEV, dtype=torch.int8)
+    ws = torch.rand(n, device=DEV) * 0.01 + 0.001
+    xq, xs = ops.per_token_quant_int8(x)
+    got = ops.int8_scaled_mm(xq, wq, xs, ws, torch.bfloat16)
+    ops.check_status()
+    acc = torch._int_mm(xq, wq.t()) if m > 16 and m % 8 == 0 else (xq.float() @ wq.float().t())
+    want = acc.float() * xs.reshape(-1, 1) * ws.reshape(1, -1)
+    assert _rel_err(got, want) < 6e-3
+
+
+def test_gemm_repeatable_splitk():
+    """Split-K tickets reset themselves: the same small-batch GEMM gives identical bits twice."""
+    torch.manual_seed(0)
+    x = torch.randn(4, 12288, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(4096, 12288, device=DEV, dtype=torch.bfloat16) * 0.01
+    a = ops.linear(x, w)
+    b = ops.linear(x, w)
+    ops.check_status()
+    assert torch.equal(a, b)
