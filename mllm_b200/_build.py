@@ -128,6 +128,8 @@ def load_extension(name: str, build_if_missing: bool = True) -> Optional[ModuleT
 
 def build_all(verbose: bool = False) -> None:
     for name in EXTENSIONS:
+        if not _existing(EXTENSIONS[name]["sources"]):
+            continue
         if not is_built(name):
             build_extension(name, verbose=verbose)
         load_extension(name)

@@ -1,0 +1,491 @@
+// Attention over the slot-indexed KV pool on tcgen05 tensor cores (head_dim 128).
+//
+// One kernel serves prefill (ragged new tokens after an optional cached prefix, causal) and
+// decode (one token per request, split over the KV length): a CTA owns one request, one KV
+// head and a tile of 128 "rows", where a row is a (query token, query head of the GQA group)
+// pair - the group's heads share every K/V tile that is loaded.  Per 64-token KV tile:
+//   S = Q K^T      tcgen05.mma (M128 N64 K128), fp32 in tensor memory
+//   softmax        one thread per row reads its S row with tcgen05.ld, online max/sum in the
+//                  log2 domain, writes P (bf16) to shared memory in the MMA operand layout
+//   O += P V       tcgen05.mma (M128 N128 K64), V used as an MN-major operand straight from
+//                  the gathered [token, d] rows; O stays in tensor memory and is rescaled
+//                  lazily (only when the running max grows by more than 2^8)
+// K/V rows are gathered with cp.async through the request->slot table (any page size, no
+// flat index list), double buffered, written directly in the 128-byte-swizzled operand
+// layout.  Decode splits the KV range over CTAs; a small merge kernel combines the partial
+// (O, log-sum-exp) pairs.  All mbarrier waits are bounded.
+#include <algorithm>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace mb200 {
+namespace {
+
+constexpr int kD = 128;        // head dim
+constexpr int kRows = 128;     // MMA M
+constexpr int kKV = 64;        // KV tokens per tile
+constexpr int kAttnThreads = 128;
+constexpr int kHalfQ = kRows * 128;  // bytes of one 64-feature half of the Q tile
+constexpr int kHalfKV = kKV * 128;   // bytes of one 64-feature half of a K or V tile
+constexpr int kSmemQ = 2 * kHalfQ;                 // 32 KB
+constexpr int kSmemKVBuf = 2 * kHalfKV;            // 16 KB per tensor per buffer
+constexpr int kSmemP = kRows * 128;                // 16 KB
+constexpr int kAttnSmem = kSmemQ + 4 * kSmemKVBuf + kSmemP + 1024 + 64;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleThreshold = 8.0f;
+
+struct AttnParams {
+  const void* q;      // [T, Hq, D] with row stride q_stride (elements)
+  const void* k_cache;
+  const void* v_cache;
+  void* out;          // [T, Hq, D] contiguous
+  float* part_o;      // decode split: [B, Hq, splits, D]
+  float* part_lse;    // decode split: [B, Hq, splits]
+  const int* req_to_token;
+  const int* req_pool_indices;
+  const int* seq_lens;
+  const int* prefix_lens;  // null in decode
+  const int* q_start;      // null in decode
+  int* status;
+  int64_t q_stride;
+  int64_t rtt_stride;
+  int64_t num_slots;
+  int hq, hkv, group;
+  int tokens_per_tile;     // query tokens per CTA tile = 128 / group (rounded down)
+  int num_splits;          // decode only
+  int is_decode;
+  int out_f16;
+  float scale_log2;        // softmax scale * log2(e)
+  uint32_t idesc_s, idesc_o;
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int sz = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// offset of 16-byte chunk `chunk` (0..15 over 128 features) of row `row` inside a tile made of
+// two 64-feature halves of `half_bytes` each, rows of 128 bytes, 128-byte swizzle
+__device__ __forceinline__ uint32_t swz_off(int row, int chunk, int half_bytes) {
+  return (chunk >> 3) * half_bytes + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+}
+
+__global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + kSmemQ;                 // 2 buffers
+  uint8_t* sV = sK + 2 * kSmemKVBuf;         // 2 buffers
+  uint8_t* sP = sV + 2 * kSmemKVBuf;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kSmemP);
+  uint64_t* bar_s = bars;
+  uint64_t* bar_o = bars + 1;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int b = blockIdx.z;
+  const int hk = blockIdx.y;
+  const int req = p.req_pool_indices[b];
+  const int seq_len = p.seq_lens[b];
+
+  // ---- work range of this CTA ------------------------------------------------------------
+  int q0, q_len, prefix, kv_begin, kv_end, q_row0;
+  if (p.is_decode) {
+    q0 = 0;
+    q_len = 1;
+    prefix = seq_len - 1;
+    q_row0 = b;
+    const int tiles = (seq_len + kKV - 1) / kKV;
+    const int per = (tiles + p.num_splits - 1) / p.num_splits;
+    kv_begin = blockIdx.x * per * kKV;
+    kv_end = min(seq_len, kv_begin + per * kKV);
+  } else {
+    prefix = p.prefix_lens[b];
+    q_len = seq_len - prefix;
+    q0 = blockIdx.x * p.tokens_per_tile;
+    q_row0 = p.q_start[b];
+    kv_begin = 0;
+    kv_end = min(seq_len, prefix + min(q_len, q0 + p.tokens_per_tile));  // causal upper bound of the tile
+    if (q0 >= q_len) return;
+  }
+  const int g = p.group;
+  const int split = blockIdx.x;
+  if (p.is_decode && kv_begin >= kv_end) {
+    // empty split: publish a neutral partial
+    for (int i = tid; i < g * kD; i += kAttnThreads) {
+      const int head = hk * g + i / kD;
+      p.part_o[((static_cast<int64_t>(b) * p.hq + head) * p.num_splits + split) * kD + (i % kD)] = 0.f;
+    }
+    if (tid < g) p.part_lse[(static_cast<int64_t>(b) * p.hq + hk * g + tid) * p.num_splits + split] = -INFINITY;
+    return;
+  }
+  const int n_tiles = (kv_end - kv_begin + kKV - 1) / kKV;
+
+  if (tid == 0) {
+    mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (warp == 0) {
+    tmem_alloc(tmem_holder, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_s = tmem_base;         // 64 columns
+  const uint32_t tmem_o = tmem_base + 64;    // 128 columns
+  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+
+  // ---- this thread's row ------------------------------------------------------------------
+  const int row = tid;
+  const int row_tok = row / g;              // token inside the tile
+  const int row_head = hk * g + row % g;
+  const bool row_valid = (row_tok < p.tokens_per_tile) && (q0 + row_tok < q_len);
+  const int kv_limit = row_valid ? (prefix + q0 + row_tok) : prefix + q0;  // last visible key (inclusive)
+
+  const uint16_t* qbase = static_cast<const uint16_t*>(p.q);
+  const uint16_t* kbase = static_cast<const uint16_t*>(p.k_cache);
+  const uint16_t* vbase = static_cast<const uint16_t*>(p.v_cache);
+  const int* rtt = p.req_to_token + static_cast<int64_t>(req) * p.rtt_stride;
+
+  // ---- Q tile: 128 rows x 256 B, 16 chunks per row -------------------------------------------
+  {
+    const uint32_t sq = smem_u32(sQ);
+    for (int c = tid; c < kRows * 16; c += kAttnThreads) {
+      const int r = c >> 4, ch = c & 15;
+      const int tok = r / g;
+      const bool ok = (tok < p.tokens_per_tile) && (q0 + tok < q_len);
+      const int head = hk * g + r % g;
+      const uint16_t* src = qbase + static_cast<int64_t>(q_row0 + q0 + (ok ? tok : 0)) * p.q_stride +
+                            static_cast<int64_t>(head) * kD + ch * 8;
+      cp_async16(sq + swz_off(r, ch, kHalfQ), src, ok);
+    }
+  }
+
+  // gather of one KV tile: 64 tokens x 16 chunks for K and V; thread handles token (tid>>4)+8*i
+  int slots_next[8];
+  auto fetch_slots = [&](int tile) {
+    const int t0 = kv_begin + tile * kKV;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int t = t0 + (tid >> 4) + 8 * i;
+      int s = -1;
+      if (tile < n_tiles && t < kv_end) {
+        s = rtt[t];
+        if (s < 0 || s >= p.num_slots) {
+          if (p.status != nullptr) atomicExch(p.status, kStatusBadIndex);
+          s = -1;
+        }
+      }
+      slots_next[i] = s;
+    }
+  };
+  auto gather = [&](int buf) {
+    const uint32_t sk = smem_u32(sK + buf * kSmemKVBuf);
+    const uint32_t sv = smem_u32(sV + buf * kSmemKVBuf);
+    const int ch = tid & 15;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = (tid >> 4) + 8 * i;
+      const int s = slots_next[i];
+      const bool ok = s >= 0;
+      const int64_t off = (static_cast<int64_t>(ok ? s : 0) * p.hkv + hk) * kD + ch * 8;
+      const uint32_t so = swz_off(r, ch, kHalfKV);
+      cp_async16(sk + so, kbase + off, ok);
+      cp_async16(sv + so, vbase + off, ok);
+    }
+  };
+
+  fetch_slots(0);
+  gather(0);
+  cp_async_commit();  // group: Q + tile 0
+  fetch_slots(1);
+
+  float m_used = -INFINITY;  // max in use for the exponent (log2 domain)
+  float l_sum = 0.f;
+  bool ok_all = true;
+
+  for (int j = 0; j < n_tiles; ++j) {
+    const int buf = j & 1;
+    cp_async_wait<0>();
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();  // tile j (and Q) visible to the tensor core
+
+    if (tid == 0) {
+      tc_fence_after_sync();
+      const uint32_t qa = smem_u32(sQ);
+      const uint32_t ka = smem_u32(sK + buf * kSmemKVBuf);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        const uint64_t a_desc = umma_desc_k_sw128(qa + (kk >> 2) * kHalfQ + (kk & 3) * 32);
+        const uint64_t b_desc = umma_desc_k_sw128(ka + (kk >> 2) * kHalfKV + (kk & 3) * 32);
+        umma_f16(tmem_s, a_desc, b_desc, p.idesc_s, kk > 0 ? 1u : 0u);
+      }
+      umma_commit(bar_s);
+    }
+    // previous P*V must be finished before P, O and the other KV buffer are touched
+    if (j > 0) {
+      if (!mbar_wait(bar_o, (j - 1) & 1)) ok_all = false;
+      tc_fence_after_sync();
+    }
+    if (j + 1 < n_tiles) {
+      gather(buf ^ 1);
+      cp_async_commit();
+      fetch_slots(j + 2);
+    }
+    if (!mbar_wait(bar_s, j & 1)) ok_all = false;
+    tc_fence_after_sync();
+
+    // ---- softmax on this thread's row --------------------------------------------------
+    uint32_t sraw[2][32];
+    tmem_ld_32x32(tmem_s + lane_base, sraw[0]);
+    tmem_ld_32x32(tmem_s + lane_base + 32, sraw[1]);
+    tmem_ld_wait();
+    const int col0 = kv_begin + j * kKV;
+    const int visible = min(kv_limit, kv_end - 1) - col0;  // columns 0..visible are allowed
+    float sc[64];
+    float m_tile = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < 64; ++c) {
+      float v = __uint_as_float(sraw[c >> 5][c & 31]) * p.scale_log2;
+      v = (c <= visible) ? v : -INFINITY;
+      sc[c] = v;
+      m_tile = fmaxf(m_tile, v);
+    }
+    float factor = 1.f;
+    bool need = false;
+    if (j == 0) {
+      m_used = (m_tile == -INFINITY) ? 0.f : m_tile;
+    } else if (m_tile > m_used + kRescaleThreshold) {
+      factor = exp2f(m_used - m_tile);
+      m_used = m_tile;
+      need = true;
+    }
+    if (__any_sync(0xffffffffu, need)) {
+      // rescale this warp's 32 rows of O in tensor memory
+      l_sum *= factor;
+#pragma unroll 1
+      for (int c = 0; c < kD; c += 32) {
+        uint32_t o[32];
+        tmem_ld_32x32(tmem_o + lane_base + c, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+        tmem_st_32x32(tmem_o + lane_base + c, o);
+      }
+      tmem_st_wait();
+    }
+    float psum = 0.f;
+    {
+      const uint32_t sp = smem_u32(sP);
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float p0 = exp2f(sc[ch * 8 + 2 * i] - m_used);
+          const float p1 = exp2f(sc[ch * 8 + 2 * i + 1] - m_used);
+          // sum what the tensor core will actually see (bf16-rounded probabilities)
+          const uint32_t pk = p.out_f16 ? 0u : pack_bf16x2(p0, p1);
+          if (p.out_f16) {
+            __half2 h = __floats2half2_rn(p0, p1);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+            float2 f = __half22float2(h);
+            psum += f.x + f.y;
+          } else {
+            w[i] = pk;
+            float2 f = unpack_bf16x2(pk);
+            psum += f.x + f.y;
+          }
+        }
+        const uint32_t dst = sp + row * 128 + ((ch ^ (row & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                     : "memory");
+      }
+    }
+    l_sum += psum;
+
+    tc_fence_before_sync();
+    fence_proxy_async_smem();
+    __syncthreads();  // P written by all rows, O rescaled
+
+    if (tid == 0) {
+      tc_fence_after_sync();
+      const uint32_t pa = smem_u32(sP);
+      const uint32_t va = smem_u32(sV + buf * kSmemKVBuf);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const uint64_t a_desc = umma_desc_k_sw128(pa + kk * 32);
+        const uint64_t b_desc = umma_desc_mn_sw128(va + kk * 2048, kHalfKV, 1024);
+        umma_f16(tmem_o, a_desc, b_desc, p.idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+      }
+      umma_commit(bar_o);
+    }
+  }
+
+  if (!mbar_wait(bar_o, (n_tiles - 1) & 1)) ok_all = false;
+  tc_fence_after_sync();
+  if (!ok_all && p.status != nullptr) atomicExch(p.status, kStatusPipelineTimeout);
+
+  // ---- epilogue -----------------------------------------------------------------------------
+  const float inv_l = l_sum > 0.f ? 1.f / l_sum : 0.f;
+  if (p.is_decode && p.num_splits > 1) {
+    float* po = p.part_o + ((static_cast<int64_t>(b) * p.hq + row_head) * p.num_splits + split) * kD;
+#pragma unroll 1
+    for (int c = 0; c < kD; c += 32) {
+      uint32_t o[32];
+      tmem_ld_32x32(tmem_o + lane_base + c, o);
+      tmem_ld_wait();
+      if (row_valid && ok_all) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          float4 v = make_float4(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l,
+                                 __uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
+          *reinterpret_cast<float4*>(po + c + i) = v;
+        }
+      }
+    }
+    if (row_valid)
+      p.part_lse[(static_cast<int64_t>(b) * p.hq + row_head) * p.num_splits + split] =
+          l_sum > 0.f ? (m_used + log2f(l_sum)) : -INFINITY;
+  } else {
+    uint16_t* orow = static_cast<uint16_t*>(p.out) +
+                     (static_cast<int64_t>(q_row0 + q0 + (row_valid ? row_tok : 0)) * p.hq + row_head) * kD;
+#pragma unroll 1
+    for (int c = 0; c < kD; c += 32) {
+      uint32_t o[32];
+      tmem_ld_32x32(tmem_o + lane_base + c, o);
+      tmem_ld_wait();
+      if (row_valid && ok_all) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          uint4 v;
+          uint32_t* vv = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+          for (int k2 = 0; k2 < 4; ++k2) {
+            const float a = __uint_as_float(o[i + 2 * k2]) * inv_l;
+            const float bb = __uint_as_float(o[i + 2 * k2 + 1]) * inv_l;
+            if (p.out_f16) {
+              __half2 h = __floats2half2_rn(a, bb);
+              vv[k2] = *reinterpret_cast<uint32_t*>(&h);
+            } else {
+              vv[k2] = pack_bf16x2(a, bb);
+            }
+          }
+          *reinterpret_cast<uint4*>(orow + c + i) = v;
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+// combine decode partials: out[b, h, :] = sum_s w_s * O_s with w_s = 2^(lse_s - max) / sum
+__global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                                  void* __restrict__ out, int hq, int splits, int out_f16) {
+  const int b = blockIdx.y, h = blockIdx.x, d = threadIdx.x;
+  const int64_t base = (static_cast<int64_t>(b) * hq + h) * splits;
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_lse[base + s]);
+  float den = 0.f, acc = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float l = part_lse[base + s];
+    const float w = (l == -INFINITY) ? 0.f : exp2f(l - m);
+    den += w;
+    acc += w * part_o[(base + s) * kD + d];
+  }
+  const float v = den > 0.f ? acc / den : 0.f;
+  const int64_t o = (static_cast<int64_t>(b) * hq + h) * kD + d;
+  if (out_f16)
+    static_cast<__half*>(out)[o] = __float2half_rn(v);
+  else
+    static_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(v);
+}
+
+bool set_attn_smem() {
+  static bool done = false, ok = false;
+  if (!done) {
+    ok = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) == cudaSuccess;
+    done = true;
+  }
+  return ok;
+}
+
+}  // namespace
+
+int decode_num_splits(int batch, int hkv, int max_seq_len, int num_sms) {
+  const int tiles = std::max(1, (max_seq_len + kKV - 1) / kKV);
+  const int ctas = std::max(1, batch * hkv);
+  int splits = (2 * num_sms + ctas - 1) / ctas;  // two resident CTAs per SM
+  splits = std::min(splits, std::max(1, tiles / 2));
+  return std::max(1, std::min(splits, 64));
+}
+
+int launch_attention(const AttnArgs& a, cudaStream_t s) {
+  if (a.head_dim != kD || a.hq % a.hkv != 0) return -1;
+  const int g = a.hq / a.hkv;
+  if (g > kRows) return -1;
+  if (!set_attn_smem()) return -3;
+  AttnParams p{};
+  p.q = a.q;
+  p.k_cache = a.k_cache;
+  p.v_cache = a.v_cache;
+  p.out = a.out;
+  p.part_o = a.part_o;
+  p.part_lse = a.part_lse;
+  p.req_to_token = a.req_to_token;
+  p.req_pool_indices = a.req_pool_indices;
+  p.seq_lens = a.seq_lens;
+  p.prefix_lens = a.prefix_lens;
+  p.q_start = a.q_start;
+  p.status = a.status;
+  p.q_stride = a.q_stride;
+  p.rtt_stride = a.rtt_stride;
+  p.num_slots = a.num_slots;
+  p.hq = a.hq;
+  p.hkv = a.hkv;
+  p.group = g;
+  p.tokens_per_tile = a.is_decode ? 1 : kRows / g;
+  p.num_splits = a.is_decode ? a.num_splits : 1;
+  p.is_decode = a.is_decode;
+  p.out_f16 = a.dt == kF16 ? 1 : 0;
+  p.scale_log2 = a.scale * kLog2e;
+  const uint32_t fmt = a.dt == kF16 ? 0u : 1u;
+  p.idesc_s = umma_idesc(kRows, kKV, 1, fmt, fmt, 0, 0);
+  p.idesc_o = umma_idesc(kRows, kD, 1, fmt, fmt, 0, 1);
+  if (a.batch <= 0) return 0;
+  dim3 grid;
+  if (a.is_decode) {
+    grid = dim3(p.num_splits, a.hkv, a.batch);
+  } else {
+    const int q_tiles = (a.max_q_len + p.tokens_per_tile - 1) / p.tokens_per_tile;
+    if (q_tiles <= 0) return 0;
+    grid = dim3(q_tiles, a.hkv, a.batch);
+  }
+  attn_fwd_kernel<<<grid, kAttnThreads, kAttnSmem, s>>>(p);
+  note_launch();
+  if (a.is_decode && p.num_splits > 1) {
+    attn_merge_kernel<<<dim3(a.hq, a.batch), kD, 0, s>>>(a.part_o, a.part_lse, a.out, a.hq, p.num_splits, p.out_f16);
+    note_launch();
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace mb200

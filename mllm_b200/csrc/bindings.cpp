@@ -242,6 +242,93 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<Ten
               " N=", args.n, " K=", args.k);
 }
 
+void attention_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& req_to_token,
+                       const Tensor& req_pool_indices, const Tensor& seq_lens, const Tensor& prefix_lens,
+                       const Tensor& q_start, double scale, Tensor& out, int64_t max_q_len) {
+  check_half(q, "q");
+  TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.stride(2) == 1 && q.stride(1) == 128, "q must be [T,Hq,128]");
+  TORCH_CHECK(out.is_contiguous() && out.sizes() == q.sizes() && out.scalar_type() == q.scalar_type(), "out");
+  TORCH_CHECK(k_cache.is_contiguous() && v_cache.is_contiguous() && k_cache.dim() == 3 && k_cache.size(2) == 128 &&
+                  k_cache.scalar_type() == q.scalar_type(),
+              "kv cache [slots,Hkv,128] of q's dtype");
+  for (const Tensor* t : {&req_to_token, &req_pool_indices, &seq_lens, &prefix_lens, &q_start})
+    TORCH_CHECK(t->scalar_type() == at::kInt && t->is_cuda(), "index tensors must be int32 CUDA tensors");
+  TORCH_CHECK(req_to_token.dim() == 2 && req_to_token.stride(1) == 1, "req_to_token layout");
+  c10::cuda::CUDAGuard g(q.device());
+  auto& st = device_state(q.get_device());
+  mb200::AttnArgs a{};
+  a.q = q.data_ptr();
+  a.k_cache = k_cache.data_ptr();
+  a.v_cache = v_cache.data_ptr();
+  a.out = out.data_ptr();
+  a.req_to_token = req_to_token.data_ptr<int>();
+  a.req_pool_indices = req_pool_indices.data_ptr<int>();
+  a.seq_lens = seq_lens.data_ptr<int>();
+  a.prefix_lens = prefix_lens.data_ptr<int>();
+  a.q_start = q_start.data_ptr<int>();
+  a.status = st.status.data_ptr<int>();
+  a.q_stride = q.stride(0);
+  a.rtt_stride = req_to_token.stride(0);
+  a.num_slots = k_cache.size(0);
+  a.batch = req_pool_indices.numel();
+  a.hq = q.size(1);
+  a.hkv = k_cache.size(1);
+  a.head_dim = 128;
+  a.max_q_len = max_q_len > 0 ? max_q_len : q.size(0);
+  a.num_splits = 1;
+  a.is_decode = 0;
+  a.scale = static_cast<float>(scale);
+  a.dt = dtype_of(q);
+  const int rc = mb200::launch_attention(a, stream_of(q));
+  TORCH_CHECK(rc == 0, "mllm_b200 attention_prefill: unsupported configuration (code ", rc, ")");
+}
+
+void attention_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& req_to_token,
+                      const Tensor& req_pool_indices, const Tensor& seq_lens, double scale, Tensor& out,
+                      int64_t max_seq_len) {
+  check_half(q, "q");
+  TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.stride(2) == 1 && q.stride(1) == 128, "q must be [B,Hq,128]");
+  TORCH_CHECK(out.is_contiguous() && out.sizes() == q.sizes() && out.scalar_type() == q.scalar_type(), "out");
+  TORCH_CHECK(k_cache.is_contiguous() && v_cache.is_contiguous() && k_cache.dim() == 3 && k_cache.size(2) == 128 &&
+                  k_cache.scalar_type() == q.scalar_type(),
+              "kv cache [slots,Hkv,128] of q's dtype");
+  for (const Tensor* t : {&req_to_token, &req_pool_indices, &seq_lens})
+    TORCH_CHECK(t->scalar_type() == at::kInt && t->is_cuda(), "index tensors must be int32 CUDA tensors");
+  c10::cuda::CUDAGuard g(q.device());
+  auto& st = device_state(q.get_device());
+  mb200::AttnArgs a{};
+  a.batch = req_pool_indices.numel();
+  TORCH_CHECK(q.size(0) == a.batch, "decode: one query row per request");
+  a.hq = q.size(1);
+  a.hkv = k_cache.size(1);
+  a.num_splits = mb200::decode_num_splits(a.batch, a.hkv, max_seq_len > 0 ? max_seq_len : req_to_token.size(1),
+                                           st.num_sms);
+  Tensor part_o, part_lse;
+  if (a.num_splits > 1) {
+    part_o = torch::empty({a.batch, a.hq, a.num_splits, 128}, q.options().dtype(torch::kFloat32));
+    part_lse = torch::empty({a.batch, a.hq, a.num_splits}, q.options().dtype(torch::kFloat32));
+    a.part_o = part_o.data_ptr<float>();
+    a.part_lse = part_lse.data_ptr<float>();
+  }
+  a.q = q.data_ptr();
+  a.k_cache = k_cache.data_ptr();
+  a.v_cache = v_cache.data_ptr();
+  a.out = out.data_ptr();
+  a.req_to_token = req_to_token.data_ptr<int>();
+  a.req_pool_indices = req_pool_indices.data_ptr<int>();
+  a.seq_lens = seq_lens.data_ptr<int>();
+  a.status = st.status.data_ptr<int>();
+  a.q_stride = q.stride(0);
+  a.rtt_stride = req_to_token.stride(0);
+  a.num_slots = k_cache.size(0);
+  a.head_dim = 128;
+  a.is_decode = 1;
+  a.scale = static_cast<float>(scale);
+  a.dt = dtype_of(q);
+  const int rc = mb200::launch_attention(a, stream_of(q));
+  TORCH_CHECK(rc == 0, "mllm_b200 attention_decode: unsupported configuration (code ", rc, ")");
+}
+
 // Reads (and clears) the device status word; non-zero means a kernel gave up on a bounded wait
 // or met an out-of-range index. Synchronises the device.
 int64_t read_status(int64_t device) {
@@ -268,6 +355,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("per_token_quant_int8", &per_token_quant_int8);
   m.def("argmax", &argmax);
   m.def("gemm", &gemm);
+  m.def("attention_prefill", &attention_prefill);
+  m.def("attention_decode", &attention_decode);
   m.def("read_status", &read_status);
   m.def("launch_count", &launch_count);
 }

@@ -75,4 +75,29 @@ struct GemmArgs {
 int launch_gemm(const GemmArgs& args, cudaStream_t s);
 size_t gemm_workspace_bytes(int m, int n, int k, int num_sms);
 
+// ----- attention over the slot-indexed KV pool (tcgen05, head_dim 128) -----------------
+struct AttnArgs {
+  const void* q;            // [T, Hq, 128], token stride q_stride elements
+  const void* k_cache;      // [slots, Hkv, 128]
+  const void* v_cache;
+  void* out;                // [T, Hq, 128] contiguous
+  float* part_o;            // decode with num_splits > 1: [B, Hq, splits, 128]
+  float* part_lse;          // decode with num_splits > 1: [B, Hq, splits]
+  const int* req_to_token;  // [reqs, rtt_stride]
+  const int* req_pool_indices;  // [B]
+  const int* seq_lens;          // [B]
+  const int* prefix_lens;       // [B], prefill only
+  const int* q_start;           // [B], prefill only: first query row of each request
+  int* status;
+  int64_t q_stride, rtt_stride, num_slots;
+  int batch, hq, hkv, head_dim;
+  int max_q_len;            // prefill: longest run of new tokens in the batch
+  int num_splits;           // decode
+  int is_decode;
+  float scale;
+  DType dt;
+};
+int launch_attention(const AttnArgs& args, cudaStream_t s);
+int decode_num_splits(int batch, int hkv, int max_seq_len, int num_sms);
+
 }  // namespace mb200

@@ -1,0 +1,434 @@
+"""Owner of one GPU's model, KV pools and forward pass.
+
+Responsibilities (those of pymllm/executor/model_runner.py:266-1532): resolve dtype,
+look the architecture up in the registry, resolve the quantisation scheme, build the
+model on the device, stream checkpoint weights in (safetensors / ``.bin`` / ``.mllm`` / seeded
+random init), run the post-load weight re-layout, size the KV pool from free memory
+(``rest = avail_after_load - avail_before_load * (1 - mem_fraction_static)``), create the
+pools, capture CUDA graphs for decode, build ``ForwardBatch`` objects, run the model and
+sample.  Unlike the reference there is no attention "plan" step: the attention kernels read
+the request->slot table and sequence lengths from device memory, so decode is graph-safe
+without host work.
+"""
+
+from __future__ import annotations
+
+import glob
+import json
+import logging
+import os
+from dataclasses import dataclass
+from pathlib import Path
+from types import SimpleNamespace
+from typing import Any, Dict, Iterator, List, Optional, Tuple
+
+import torch
+
+from .. import ops
+from ..configs import ServerConfig
+from ..engine.forward_batch import ForwardBatch, ForwardMode
+from ..mem_cache import KVPool, ReqToTokenPool, TokenToKVPoolAllocator
+from ..models import get_model_class
+from ..models.qwen3 import LogitsProcessorOutput
+from ..parallel import state as pstate
+
+logger = logging.getLogger(__name__)
+
+_DTYPES = {"float16": torch.float16, "half": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32,
+           "float": torch.float32}
+
+
+def get_available_gpu_memory(device: str = "cuda", gpu_id: int = 0) -> float:
+    """Free device memory in GiB."""
+    if device != "cuda" or not torch.cuda.is_available():
+        import psutil
+
+        return psutil.virtual_memory().available / (1 << 30)
+    free, _ = torch.cuda.mem_get_info(gpu_id)
+    return free / (1 << 30)
+
+
+def get_total_gpu_memory(device: str = "cuda", gpu_id: int = 0) -> float:
+    if device != "cuda" or not torch.cuda.is_available():
+        import psutil
+
+        return psutil.virtual_memory().total / (1 << 30)
+    _, total = torch.cuda.mem_get_info(gpu_id)
+    return total / (1 << 30)
+
+
+@dataclass
+class MemoryProfileResult:
+    max_total_num_tokens: int
+    cell_bytes: int
+    rest_gib: float
+
+
+@dataclass
+class SamplingBatchInfo:
+    """Per-request sampling parameters as device vectors; ``all_greedy`` short-circuits to argmax."""
+
+    temperatures: torch.Tensor
+    top_ks: torch.Tensor
+    top_ps: torch.Tensor
+    min_ps: Optional[torch.Tensor] = None
+    all_greedy: bool = True
+    frequency_penalties: Optional[torch.Tensor] = None
+    presence_penalties: Optional[torch.Tensor] = None
+    repetition_penalties: Optional[torch.Tensor] = None
+    output_counts: Optional[torch.Tensor] = None   # [B, V] int32
+    prompt_mask: Optional[torch.Tensor] = None     # [B, V] bool
+    generator: Optional[torch.Generator] = None
+
+    @classmethod
+    def greedy(cls, batch: int, device) -> "SamplingBatchInfo":
+        return cls(torch.zeros(batch, device=device), torch.full((batch,), -1, dtype=torch.int32, device=device),
+                   torch.ones(batch, device=device), None, True)
+
+    @property
+    def has_penalties(self) -> bool:
+        return self.output_counts is not None
+
+
+def load_hf_config(model_path) -> Any:
+    """``config.json`` of a checkpoint directory (through transformers when it knows the model
+    type, else as a plain attribute bag), or a built-in preset for ``preset:<name>``."""
+    s = str(model_path)
+    if s.startswith("preset:"):
+        from ..models.presets import get_preset
+
+        return get_preset(s.split(":", 1)[1])
+    cfg_file = Path(s) / "config.json"
+    try:
+        from transformers import AutoConfig
+
+        return AutoConfig.from_pretrained(s, trust_remote_code=False)
+    except Exception:  # unknown model type for this transformers build
+        with open(cfg_file) as f:
+            raw = json.load(f)
+        from ..models.presets import _to_ns
+
+        return _to_ns(raw)
+
+
+def text_config_of(hf_config) -> Any:
+    return getattr(hf_config, "text_config", None) or hf_config
+
+
+class ModelRunner:
+    def __init__(self, server_config: ServerConfig, hf_config: Any = None, gpu_id: int = 0,
+                 quantization_method: Optional[str] = None, kv_cache_dtype: str = "auto",
+                 device: Optional[str] = None) -> None:
+        self.server_config = server_config
+        self.hf_config = hf_config
+        self.gpu_id = gpu_id
+        self.device = torch.device(device) if device else (
+            torch.device("cuda", gpu_id) if torch.cuda.is_available() else torch.device("cpu"))
+        self.quantization_method = quantization_method
+        self.kv_cache_dtype_name = kv_cache_dtype
+        self.model = None
+        self.quant_config = None
+        self.req_to_token_pool: Optional[ReqToTokenPool] = None
+        self.token_to_kv_pool: Optional[KVPool] = None
+        self.token_to_kv_pool_allocator: Optional[TokenToKVPoolAllocator] = None
+        self.cuda_graph_runner = None
+        self.max_total_num_tokens = 0
+        self.attn_backend = None
+        self._pre_load_avail_gib = 0.0
+
+    # ------------------------------------------------------------------ init
+    def initialize(self) -> None:
+        if self.device.type == "cuda":
+            torch.cuda.set_device(self.device)
+        if self.hf_config is None:
+            self.hf_config = load_hf_config(self.server_config.model_path)
+        self.dtype = self._resolve_dtype()
+        self._pre_load_avail_gib = get_available_gpu_memory(self.device.type, self.gpu_id)
+        self.load_model()
+        self._extract_model_metadata()
+        self._configure_kv_cache_dtype()
+        self.init_memory_pool()
+        self.init_cuda_graphs()
+
+    def _resolve_dtype(self) -> torch.dtype:
+        want = self.server_config.dtype
+        if want != "auto":
+            return _DTYPES[want]
+        cfg_dt = getattr(self.hf_config, "torch_dtype", None) or getattr(self.hf_config, "dtype", None) or \
+            getattr(text_config_of(self.hf_config), "torch_dtype", None)
+        if isinstance(cfg_dt, torch.dtype):
+            dt = cfg_dt
+        else:
+            dt = _DTYPES.get(str(cfg_dt).replace("torch.", ""), torch.bfloat16)
+        if dt == torch.float32 and self.device.type == "cuda":
+            dt = torch.bfloat16
+        return dt
+
+    def _configure_kv_cache_dtype(self) -> None:
+        name = self.kv_cache_dtype_name
+        if name == "auto":
+            self.kv_cache_dtype = self.dtype
+        elif name in ("float16", "bfloat16"):
+            self.kv_cache_dtype = _DTYPES[name]
+        elif name in ("fp8_e4m3", "fp8_e5m2"):
+            raise NotImplementedError("fp8 KV cache: dtype is accepted by the CLI, kernels are not implemented")
+        else:
+            raise ValueError(f"unknown kv_cache_dtype {name!r}")
+
+    def _extract_model_metadata(self) -> None:
+        tc = text_config_of(self.hf_config)
+        tp = pstate.get_tensor_model_parallel_world_size()
+        self.num_hidden_layers = tc.num_hidden_layers
+        self.head_dim = getattr(tc, "head_dim", None) or tc.hidden_size // tc.num_attention_heads
+        self.num_kv_heads_total = tc.num_key_value_heads
+        self.num_kv_heads = max(1, tc.num_key_value_heads // tp)
+        self.num_attention_heads = tc.num_attention_heads // tp
+        self.vocab_size = tc.vocab_size
+        self.hidden_size = tc.hidden_size
+        ctx = self.server_config.context_length or getattr(tc, "max_position_embeddings", 32768)
+        self.context_len = int(ctx)
+
+    # ------------------------------------------------------------------ weights
+    @staticmethod
+    def _load_quant_config_dict(model_path) -> dict:
+        if model_path is None or str(model_path).startswith("preset:"):
+            return {}
+        root = Path(str(model_path))
+        for name in ("quantize_config.json", "quant_config.json"):
+            f = root / name
+            if f.exists():
+                with open(f) as fh:
+                    d = json.load(fh)
+                d.setdefault("quant_method", "awq" if "w_bit" in d or "bits" in d else d.get("quant_method"))
+                return d
+        f = root / "config.json"
+        if f.exists():
+            with open(f) as fh:
+                return json.load(fh).get("quantization_config", {}) or {}
+        return {}
+
+    def _resolve_quant_config(self):
+        from ..quantization import get_quantization_config
+
+        qdict = getattr(self.hf_config, "quantization_config", None)
+        if qdict is not None and not isinstance(qdict, dict):
+            qdict = qdict.to_dict() if hasattr(qdict, "to_dict") else dict(vars(qdict))
+        if not qdict:
+            qdict = self._load_quant_config_dict(self.server_config.model_path)
+        method = self.quantization_method or (qdict or {}).get("quant_method")
+        if not method:
+            return None
+        if method == "awq":
+            method = "awq_marlin"
+        cls = get_quantization_config(method)
+        return cls.from_config(qdict or {})
+
+    def load_model(self) -> None:
+        arch = getattr(self.hf_config, "architectures", ["Qwen3ForCausalLM"])[0]
+        model_cls = get_model_class(arch)
+        self.quant_config = self._resolve_quant_config()
+        load_format = self.server_config.load_format
+        path = self.server_config.model_path
+        is_preset = path is None or str(path).startswith("preset:")
+        prev = torch.get_default_dtype()
+        torch.set_default_dtype(self.dtype)
+        try:
+            with torch.device(self.device):
+                self.model = model_cls(self.hf_config, quant_config=self.quant_config, params_dtype=self.dtype)
+        finally:
+            torch.set_default_dtype(prev)
+        if load_format == "dummy" or is_preset:
+            self.random_init_weights(seed=0 if self.server_config.random_seed is None else 0)
+        else:
+            self.model.load_weights(self._iter_weights(path))
+        for m in self.model.modules():
+            qm = getattr(m, "quant_method", None)
+            if qm is not None:
+                qm.process_weights_after_loading(m)
+        self.model.eval()
+
+    @torch.no_grad()
+    def random_init_weights(self, seed: int = 0, std: float = 0.02) -> None:
+        """Seeded N(0, std) for matrices, ones for norm gains, zeros for biases; integer (quantised)
+        parameters get uniform random codes and positive scales."""
+        gen = torch.Generator(device=self.device)
+        gen.manual_seed(seed)
+        for name, p in self.model.named_parameters():
+            if p.dtype in (torch.int8, torch.int32, torch.int64, torch.uint8):
+                if p.dtype == torch.int8:
+                    p.data.copy_(torch.randint(-127, 128, p.shape, device=self.device, generator=gen, dtype=torch.int32).to(torch.int8))
+                elif "shape" in name:
+                    continue
+                else:
+                    p.data.copy_(torch.randint(-(2 ** 31), 2 ** 31 - 1, p.shape, device=self.device, generator=gen,
+                                               dtype=torch.int64).to(p.dtype))
+            elif "scale" in name:
+                p.data.copy_((torch.rand(p.shape, device=self.device, generator=gen) * 0.5 + 0.75).mul_(std / 64).to(p.dtype))
+            elif name.endswith("norm.weight") or ".norm" in name and name.endswith(".weight") and p.dim() == 1:
+                p.data.fill_(1.0)
+            elif name.endswith(".bias"):
+                p.data.zero_()
+            else:
+                # generate in fp32 chunks to bound peak memory on very large tables
+                flat = p.data.view(-1)
+                step = 1 << 26
+                for s in range(0, flat.numel(), step):
+                    e = min(flat.numel(), s + step)
+                    flat[s:e] = torch.randn(e - s, device=self.device, generator=gen, dtype=torch.float32).mul_(std).to(p.dtype)
+
+    @staticmethod
+    def _iter_weights(model_path) -> Iterator[Tuple[str, torch.Tensor]]:
+        root = str(model_path)
+        st = sorted(glob.glob(os.path.join(root, "*.safetensors")))
+        if st:
+            from safetensors import safe_open
+
+            for f in st:
+                with safe_open(f, framework="pt", device="cpu") as fh:
+                    for k in fh.keys():
+                        yield k, fh.get_tensor(k)
+            return
+        mllm = sorted(glob.glob(os.path.join(root, "*.mllm")))
+        if mllm:
+            from ..io.mllm_file import iter_mllm_tensors
+
+            for f in mllm:
+                yield from iter_mllm_tensors(f)
+            return
+        bins = sorted(glob.glob(os.path.join(root, "*.bin")))
+        if not bins:
+            raise FileNotFoundError(f"no *.safetensors, *.mllm or *.bin under {root}")
+        for f in bins:
+            sd = torch.load(f, map_location="cpu", weights_only=True)
+            yield from sd.items()
+
+    # ------------------------------------------------------------------ memory
+    def cell_bytes(self) -> int:
+        return KVPool.cell_bytes(self.num_hidden_layers, self.num_kv_heads, self.head_dim, self.kv_cache_dtype)
+
+    def _profile_max_num_tokens(self) -> MemoryProfileResult:
+        frac = self.server_config.mem_fraction_static or 0.85
+        avail = get_available_gpu_memory(self.device.type, self.gpu_id)
+        rest = avail - self._pre_load_avail_gib * (1.0 - frac)
+        cell = self.cell_bytes()
+        tokens = int(rest * (1 << 30) // cell)
+        return MemoryProfileResult(max_total_num_tokens=tokens, cell_bytes=cell, rest_gib=rest)
+
+    def init_memory_pool(self) -> None:
+        prof = self._profile_max_num_tokens()
+        tokens = prof.max_total_num_tokens
+        if self.device.type == "cpu":
+            tokens = min(tokens, 1 << 16)
+        if self.server_config.max_total_tokens is not None:
+            tokens = min(tokens, int(self.server_config.max_total_tokens))
+        if tokens <= 0:
+            raise RuntimeError(
+                "Not enough memory for the KV cache: "
+                f"free after load leaves {prof.rest_gib:.2f} GiB at mem_fraction_static="
+                f"{self.server_config.mem_fraction_static or 0.85}; try a larger --server.mem_fraction_static "
+                "or a smaller model.")
+        page = self.server_config.radix_cache_page_size
+        tokens = tokens // page * page
+        self.max_total_num_tokens = tokens
+        max_reqs = self.server_config.max_running_requests or 1
+        max_reqs = max(max_reqs, 1)
+        self.max_running_requests = max_reqs
+        # a few spare rows: requests being prefilled while the running batch is full
+        self.req_to_token_pool = ReqToTokenPool(max_reqs + 8, self.context_len + 4, self.device)
+        self.token_to_kv_pool = KVPool(tokens, self.num_hidden_layers, self.num_kv_heads, self.head_dim,
+                                       self.kv_cache_dtype, self.device, page_size=page)
+        self.token_to_kv_pool_allocator = TokenToKVPoolAllocator(tokens, page_size=page, device=self.device)
+        logger.info("KV pool: %d tokens, %.2f GiB (%d B/token)", tokens, tokens * prof.cell_bytes / (1 << 30),
+                    prof.cell_bytes)
+
+    def init_cuda_graphs(self) -> None:
+        if self.device.type != "cuda" or self.server_config.disable_cuda_graph:
+            return
+        from .cuda_graph_runner import CudaGraphRunner
+
+        self.cuda_graph_runner = CudaGraphRunner(self)
+        self.cuda_graph_runner.capture()
+
+    # ------------------------------------------------------------------ batches
+    def prepare_forward_batch_extend(
+        self, input_ids: torch.Tensor, req_pool_indices: torch.Tensor, seq_lens: torch.Tensor,
+        extend_seq_lens: torch.Tensor, extend_prefix_lens: torch.Tensor, out_cache_loc: torch.Tensor,
+        extend_seq_lens_cpu: Optional[List[int]] = None, extend_prefix_lens_cpu: Optional[List[int]] = None,
+        **extra,
+    ) -> ForwardBatch:
+        """Batch of new tokens (after optional cached prefixes). Passing the ``*_cpu`` lists avoids
+        a device->host sync."""
+        if extend_seq_lens_cpu is None:
+            extend_seq_lens_cpu = extend_seq_lens.tolist()
+        if extend_prefix_lens_cpu is None:
+            extend_prefix_lens_cpu = extend_prefix_lens.tolist()
+        bs = len(extend_seq_lens_cpu)
+        starts, pos_parts, acc = [], [], 0
+        for n, p in zip(extend_seq_lens_cpu, extend_prefix_lens_cpu):
+            starts.append(acc)
+            pos_parts.append(torch.arange(p, p + n, dtype=torch.int64))
+            acc += n
+        positions = (torch.cat(pos_parts) if pos_parts else torch.zeros(0, dtype=torch.int64)).to(self.device, non_blocking=True)
+        start_loc = torch.tensor(starts, dtype=torch.int32).to(self.device, non_blocking=True)
+        seq_cpu = [n + p for n, p in zip(extend_seq_lens_cpu, extend_prefix_lens_cpu)]
+        return ForwardBatch(
+            forward_mode=ForwardMode.EXTEND, batch_size=bs, input_ids=input_ids,
+            req_pool_indices=req_pool_indices.to(torch.int32), seq_lens=seq_lens.to(torch.int32),
+            out_cache_loc=out_cache_loc, positions=positions, seq_lens_sum=sum(seq_cpu),
+            seq_lens_cpu=torch.tensor(seq_cpu, dtype=torch.int32), max_seq_len=max(seq_cpu) if seq_cpu else 0,
+            extend_seq_lens=extend_seq_lens.to(torch.int32), extend_prefix_lens=extend_prefix_lens.to(torch.int32),
+            extend_start_loc=start_loc, extend_seq_lens_cpu=list(extend_seq_lens_cpu),
+            extend_prefix_lens_cpu=list(extend_prefix_lens_cpu),
+            max_extend_len=max(extend_seq_lens_cpu) if extend_seq_lens_cpu else 0,
+            req_to_token_pool=self.req_to_token_pool, token_to_kv_pool=self.token_to_kv_pool,
+            attn_backend=self.attn_backend, **extra,
+        )
+
+    def prepare_forward_batch_decode(
+        self, input_ids: torch.Tensor, req_pool_indices: torch.Tensor, seq_lens: torch.Tensor,
+        out_cache_loc: torch.Tensor, max_seq_len: Optional[int] = None, **extra,
+    ) -> ForwardBatch:
+        """One new token per request; ``seq_lens`` already counts it. No host sync."""
+        bs = input_ids.shape[0]
+        return ForwardBatch(
+            forward_mode=ForwardMode.DECODE, batch_size=bs, input_ids=input_ids,
+            req_pool_indices=req_pool_indices.to(torch.int32), seq_lens=seq_lens.to(torch.int32),
+            out_cache_loc=out_cache_loc, positions=(seq_lens - 1).to(torch.int64),
+            max_seq_len=int(max_seq_len if max_seq_len is not None else self.context_len),
+            req_to_token_pool=self.req_to_token_pool, token_to_kv_pool=self.token_to_kv_pool,
+            attn_backend=self.attn_backend, **extra,
+        )
+
+    # ------------------------------------------------------------------ forward / sample
+    @torch.no_grad()
+    def forward(self, forward_batch: ForwardBatch) -> LogitsProcessorOutput:
+        if forward_batch.forward_mode.is_decode() and self.cuda_graph_runner is not None \
+                and self.cuda_graph_runner.can_run(forward_batch):
+            return self.cuda_graph_runner.replay(forward_batch)
+        return self.model(forward_batch.input_ids, forward_batch.positions, forward_batch)
+
+    @torch.no_grad()
+    def sample(self, logits_output: LogitsProcessorOutput, info: Optional[SamplingBatchInfo] = None) -> torch.Tensor:
+        """penalties -> greedy argmax when every temperature is ~0 -> temperature softmax + top-k/top-p/min-p."""
+        logits = logits_output.next_token_logits
+        if info is None or (info.all_greedy and not info.has_penalties):
+            return ops.argmax(logits)
+        if info.has_penalties:
+            logits = ops.apply_penalties(logits, info.output_counts, info.prompt_mask, info.frequency_penalties,
+                                         info.presence_penalties, info.repetition_penalties)
+            if info.all_greedy:
+                return ops.argmax(logits)
+        u = torch.rand(logits.shape[0], device=logits.device, generator=info.generator)
+        return ops.top_k_top_p_min_p_sample(logits, info.temperatures, info.top_ks, info.top_ps, info.min_ps, u)
+
+    def shutdown(self) -> None:
+        self.cuda_graph_runner = None
+        self.model = None
+        self.token_to_kv_pool = None
+        self.req_to_token_pool = None
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()
+
+    @property
+    def is_generation(self) -> bool:
+        return True

@@ -1,0 +1,29 @@
+"""Architecture-name -> model-class registry with lazy imports (pymllm/models/__init__.py:19-66)."""
+
+from __future__ import annotations
+
+import importlib
+from typing import Dict, Tuple, Type
+
+_REGISTRY: Dict[str, Tuple[str, str]] = {
+    "Qwen3ForCausalLM": ("mllm_b200.models.qwen3", "Qwen3ForCausalLM"),
+    "Qwen3MoeForCausalLM": ("mllm_b200.models.qwen3_moe", "Qwen3MoeForCausalLM"),
+    "Qwen3VLForConditionalGeneration": ("mllm_b200.models.qwen3_vl", "Qwen3VLForConditionalGeneration"),
+    "Qwen3_5ForCausalLM": ("mllm_b200.models.qwen3_5", "Qwen3_5ForCausalLM"),
+    "Qwen3_5ForConditionalGeneration": ("mllm_b200.models.qwen3_5", "Qwen3_5ForConditionalGeneration"),
+}
+
+
+def register_model(arch: str, module: str, cls: str) -> None:
+    _REGISTRY[arch] = (module, cls)
+
+
+def supported_architectures():
+    return sorted(_REGISTRY)
+
+
+def get_model_class(arch: str) -> Type:
+    if arch not in _REGISTRY:
+        raise ValueError(f"Unsupported architecture {arch!r}; supported: {supported_architectures()}")
+    module, cls = _REGISTRY[arch]
+    return getattr(importlib.import_module(module), cls)

@@ -1,0 +1,87 @@
+"""Built-in model shapes so benchmarks and tests can run without a checkpoint directory.
+
+Each preset is a plain attribute bag with the HF ``config.json`` field names the
+models read.  Shapes: Qwen3 dense (0.6B / 1.7B / 4B / 8B / 14B / 32B), Qwen3-30B-A3B
+(MoE) and the Qwen3-VL-2B vision+language pair.
+"""
+
+from __future__ import annotations
+
+import copy
+from types import SimpleNamespace
+from typing import Any, Dict
+
+
+def _dense(hidden, layers, heads, kv, inter, tie, vocab=151936, theta=1e6) -> Dict[str, Any]:
+    return dict(
+        architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=hidden, num_hidden_layers=layers,
+        num_attention_heads=heads, num_key_value_heads=kv, head_dim=128, intermediate_size=inter,
+        vocab_size=vocab, rms_norm_eps=1e-6, rope_theta=theta, tie_word_embeddings=tie,
+        max_position_embeddings=40960, attention_bias=False, hidden_act="silu", torch_dtype="bfloat16",
+        eos_token_id=151645, bos_token_id=151643,
+    )
+
+
+PRESETS: Dict[str, Dict[str, Any]] = {
+    "qwen3-0.6b": _dense(1024, 28, 16, 8, 3072, True),
+    "qwen3-1.7b": _dense(2048, 28, 16, 8, 6144, True),
+    "qwen3-4b": _dense(2560, 36, 32, 8, 9728, True),
+    "qwen3-8b": _dense(4096, 36, 32, 8, 12288, False),
+    "qwen3-14b": _dense(5120, 40, 40, 8, 17408, False),
+    "qwen3-32b": _dense(5120, 64, 64, 8, 25600, False),
+    "qwen3-tiny": _dense(256, 2, 4, 2, 512, True, vocab=1024),
+}
+PRESETS["qwen3-30b-a3b"] = dict(
+    _dense(2048, 48, 32, 4, 6144, False),
+    architectures=["Qwen3MoeForCausalLM"], model_type="qwen3_moe", num_experts=128, num_experts_per_tok=8,
+    moe_intermediate_size=768, norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[],
+)
+PRESETS["qwen3-moe-tiny"] = dict(
+    _dense(256, 2, 4, 2, 512, True, vocab=1024),
+    architectures=["Qwen3MoeForCausalLM"], model_type="qwen3_moe", num_experts=8, num_experts_per_tok=2,
+    moe_intermediate_size=256, norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[],
+)
+_VL_VISION = dict(
+    depth=24, hidden_size=1024, num_heads=16, intermediate_size=4096, patch_size=16, temporal_patch_size=2,
+    spatial_merge_size=2, in_channels=3, out_hidden_size=2048, num_position_embeddings=2304,
+    deepstack_visual_indexes=[5, 11, 17], hidden_act="gelu_pytorch_tanh",
+)
+PRESETS["qwen3-vl-2b"] = dict(
+    architectures=["Qwen3VLForConditionalGeneration"], model_type="qwen3_vl", tie_word_embeddings=True,
+    image_token_id=151655, video_token_id=151656, vision_start_token_id=151652, vision_end_token_id=151653,
+    text_config=dict(_dense(2048, 28, 16, 8, 6144, True, theta=5e6),
+                     rope_scaling=dict(mrope_section=[24, 20, 20], mrope_interleaved=True, rope_type="default")),
+    vision_config=_VL_VISION, torch_dtype="bfloat16", eos_token_id=151645,
+)
+PRESETS["qwen3-vl-tiny"] = dict(
+    architectures=["Qwen3VLForConditionalGeneration"], model_type="qwen3_vl", tie_word_embeddings=True,
+    image_token_id=1001, video_token_id=1002, vision_start_token_id=1003, vision_end_token_id=1004,
+    text_config=dict(_dense(256, 3, 2, 1, 512, True, vocab=1024, theta=5e6),
+                     rope_scaling=dict(mrope_section=[24, 20, 20], mrope_interleaved=True, rope_type="default")),
+    vision_config=dict(depth=3, hidden_size=128, num_heads=2, intermediate_size=256, patch_size=16,
+                       temporal_patch_size=2, spatial_merge_size=2, in_channels=3, out_hidden_size=256,
+                       num_position_embeddings=64, deepstack_visual_indexes=[0, 1],
+                       hidden_act="gelu_pytorch_tanh"),
+    torch_dtype="bfloat16", eos_token_id=1,
+)
+
+
+def _to_ns(d: Dict[str, Any]) -> SimpleNamespace:
+    ns = SimpleNamespace()
+    for k, v in d.items():
+        setattr(ns, k, _to_ns(v) if isinstance(v, dict) and k.endswith("_config") else copy.deepcopy(v))
+    return ns
+
+
+def get_preset(name: str, **overrides) -> SimpleNamespace:
+    key = name.lower()
+    if key not in PRESETS:
+        raise KeyError(f"unknown preset {name!r}; have {sorted(PRESETS)}")
+    d = copy.deepcopy(PRESETS[key])
+    d.update(overrides)
+    return _to_ns(d)
+
+
+def preset_to_config_json(name: str) -> Dict[str, Any]:
+    """The preset as a HF-style ``config.json`` dict (used to materialise random checkpoints)."""
+    return copy.deepcopy(PRESETS[name.lower()])

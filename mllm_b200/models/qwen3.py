@@ -1,0 +1,252 @@
+"""Qwen3 dense decoder (Qwen3ForCausalLM).
+
+Computation order follows pymllm/models/qwen3.py:29-351: embedding -> N x
+(RMSNorm with the residual add carried into it -> fused QKV projection -> per-head
+RMSNorm of q and k -> NeoX RoPE -> attention over the KV pool -> o_proj ->
+fused add + RMSNorm -> SwiGLU MLP) -> final norm -> last-token gather -> lm_head
+(tied to the embedding when the config says so).  Checkpoint names are the HF
+ones; q/k/v and gate/up are stacked into fused parameters by ``load_weights``.
+
+Tensor parallelism: heads and MLP columns are split over the TP ranks (KV heads
+are replicated when there are fewer than ranks); o_proj / down_proj are
+row-parallel.
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+from typing import Iterable, Optional, Tuple
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..engine.forward_batch import ForwardBatch
+from ..layers import MLP, MergedLinear, RMSNorm, RadixAttention, RowParallelLinear, VocabParallelEmbedding
+from ..parallel import state as pstate
+
+
+@dataclass
+class LogitsProcessorOutput:
+    next_token_logits: torch.Tensor
+    hidden_states: Optional[torch.Tensor] = None
+
+
+def _quant_method(quant_config, prefix: str):
+    return quant_config.get_quant_method(None, prefix) if quant_config is not None else None
+
+
+class Qwen3Attention(nn.Module):
+    def __init__(self, config, layer_id: int, quant_config=None, prefix: str = "", params_dtype=None,
+                 mrope_sections=None, mrope_interleaved: bool = False) -> None:
+        super().__init__()
+        tp = pstate.get_tensor_model_parallel_world_size()
+        self.hidden_size = config.hidden_size
+        self.total_heads = config.num_attention_heads
+        self.total_kv_heads = config.num_key_value_heads
+        self.head_dim = getattr(config, "head_dim", None) or config.hidden_size // config.num_attention_heads
+        if self.total_heads % tp:
+            raise ValueError(f"num_attention_heads={self.total_heads} not divisible by tp={tp}")
+        self.num_heads = self.total_heads // tp
+        kv_replicated = self.total_kv_heads < tp
+        self.num_kv_heads = 1 if kv_replicated else self.total_kv_heads // tp
+        self.kv_replicated = kv_replicated
+        self.q_size = self.num_heads * self.head_dim
+        self.kv_size = self.num_kv_heads * self.head_dim
+        eps = getattr(config, "rms_norm_eps", 1e-6)
+        kv_width = self.kv_size if kv_replicated else self.total_kv_heads * self.head_dim
+        self.qkv_proj = MergedLinear(
+            self.hidden_size, [self.total_heads * self.head_dim, kv_width, kv_width],
+            bias=getattr(config, "attention_bias", False), quant_method=_quant_method(quant_config, f"{prefix}.qkv_proj"),
+            params_dtype=params_dtype, prefix=f"{prefix}.qkv_proj", shard_names=["q", "k", "v"],
+            replicated_shards=[False, kv_replicated, kv_replicated],
+        )
+        self.o_proj = RowParallelLinear(self.total_heads * self.head_dim, self.hidden_size, bias=False,
+                                        quant_method=_quant_method(quant_config, f"{prefix}.o_proj"),
+                                        params_dtype=params_dtype, prefix=f"{prefix}.o_proj")
+        self.q_norm = RMSNorm(self.head_dim, eps, params_dtype)
+        self.k_norm = RMSNorm(self.head_dim, eps, params_dtype)
+        rope_theta = _rope_theta(config)
+        self.attn = RadixAttention(self.num_heads, self.head_dim, self.head_dim ** -0.5, self.num_kv_heads, layer_id,
+                                   rope_theta=rope_theta, rms_eps=eps, mrope_sections=mrope_sections,
+                                   mrope_interleaved=mrope_interleaved)
+
+    def kv_shard_for_rank(self, loaded: torch.Tensor) -> torch.Tensor:
+        """With fewer KV heads than ranks, rank r keeps head ``r * Hkv // tp``."""
+        tp = pstate.get_tensor_model_parallel_world_size()
+        r = pstate.get_tensor_model_parallel_rank()
+        head = r * self.total_kv_heads // tp
+        rows = loaded.shape[0] // self.total_kv_heads
+        return loaded.narrow(0, head * rows, rows)
+
+    def forward(self, x: torch.Tensor, forward_batch: ForwardBatch) -> torch.Tensor:
+        qkv = self.qkv_proj(x)
+        a = self.attn(qkv, self.q_norm.weight, self.k_norm.weight, forward_batch)
+        return self.o_proj(a)
+
+
+def _rope_theta(config) -> float:
+    theta = getattr(config, "rope_theta", None)
+    if theta is None:
+        rp = getattr(config, "rope_parameters", None) or getattr(config, "rope_scaling", None) or {}
+        theta = rp.get("rope_theta", 1e6) if isinstance(rp, dict) else 1e6
+    return float(theta)
+
+
+class Qwen3DecoderLayer(nn.Module):
+    def __init__(self, config, layer_id: int, quant_config=None, prefix: str = "", params_dtype=None, **attn_kw):
+        super().__init__()
+        eps = getattr(config, "rms_norm_eps", 1e-6)
+        self.self_attn = Qwen3Attention(config, layer_id, quant_config, f"{prefix}.self_attn", params_dtype, **attn_kw)
+        self.mlp = self._make_mlp(config, layer_id, quant_config, f"{prefix}.mlp", params_dtype)
+        self.input_layernorm = RMSNorm(config.hidden_size, eps, params_dtype)
+        self.post_attention_layernorm = RMSNorm(config.hidden_size, eps, params_dtype)
+
+    def _make_mlp(self, config, layer_id, quant_config, prefix, params_dtype):
+        return MLP(config.hidden_size, config.intermediate_size, quant_config, prefix, params_dtype)
+
+    def forward(self, hidden: torch.Tensor, residual: Optional[torch.Tensor], forward_batch: ForwardBatch
+                ) -> Tuple[torch.Tensor, torch.Tensor]:
+        # residual-carry: the add of the previous block's output happens inside the next norm
+        if residual is None:
+            residual = hidden
+            hidden = self.input_layernorm(hidden)
+        else:
+            hidden, residual = self.input_layernorm(hidden, residual)
+        hidden = self.self_attn(hidden, forward_batch)
+        hidden, residual = self.post_attention_layernorm(hidden, residual)
+        hidden = self.mlp(hidden)
+        return hidden, residual
+
+
+class Qwen3Model(nn.Module):
+    layer_cls = Qwen3DecoderLayer
+
+    def __init__(self, config, quant_config=None, prefix: str = "model", params_dtype=None, **attn_kw) -> None:
+        super().__init__()
+        self.config = config
+        self.embed_tokens = VocabParallelEmbedding(config.vocab_size, config.hidden_size, params_dtype)
+        self.layers = nn.ModuleList(
+            self.layer_cls(config, i, quant_config, f"{prefix}.layers.{i}", params_dtype, **attn_kw)
+            for i in range(config.num_hidden_layers)
+        )
+        self.norm = RMSNorm(config.hidden_size, getattr(config, "rms_norm_eps", 1e-6), params_dtype)
+
+    def forward(self, input_ids: torch.Tensor, positions: torch.Tensor, forward_batch: ForwardBatch,
+                input_embeds: Optional[torch.Tensor] = None, deepstack_embeds=None) -> torch.Tensor:
+        hidden = self.embed_tokens(input_ids) if input_embeds is None else input_embeds
+        residual = None
+        for i, layer in enumerate(self.layers):
+            hidden, residual = layer(hidden, residual, forward_batch)
+            if deepstack_embeds is not None and i < len(deepstack_embeds):
+                hidden = hidden + deepstack_embeds[i]
+        if residual is None:
+            return self.norm(hidden)
+        hidden, _ = self.norm(hidden, residual)
+        return hidden
+
+
+class Qwen3ForCausalLM(nn.Module):
+    model_cls = Qwen3Model
+    # (fused parameter, checkpoint name, shard id)
+    stacked_params_mapping = [
+        (".qkv_proj", ".q_proj", "q"),
+        (".qkv_proj", ".k_proj", "k"),
+        (".qkv_proj", ".v_proj", "v"),
+        (".gate_up_proj", ".gate_proj", 0),
+        (".gate_up_proj", ".up_proj", 1),
+    ]
+
+    def __init__(self, config, quant_config=None, params_dtype: Optional[torch.dtype] = None, **model_kw) -> None:
+        super().__init__()
+        self.config = config
+        self.quant_config = quant_config
+        self.model = self.model_cls(config, quant_config, "model", params_dtype, **model_kw)
+        self.tie = bool(getattr(config, "tie_word_embeddings", False))
+        if not self.tie:
+            self.lm_head = VocabParallelEmbedding(config.vocab_size, config.hidden_size, params_dtype)
+        self.tp_size = pstate.get_tensor_model_parallel_world_size()
+
+    @property
+    def lm_head_weight(self) -> torch.Tensor:
+        return self.model.embed_tokens.weight if self.tie else self.lm_head.weight
+
+    def compute_logits(self, hidden: torch.Tensor, forward_batch: ForwardBatch) -> torch.Tensor:
+        if forward_batch.forward_mode.is_extend() and forward_batch.extend_seq_lens is not None:
+            last = torch.cumsum(forward_batch.extend_seq_lens, 0) - 1
+            hidden = hidden.index_select(0, last)
+        logits = ops.linear(hidden, self.lm_head_weight)
+        if self.tp_size > 1:
+            logits = pstate.tensor_model_parallel_all_gather(logits, dim=-1)
+        return logits[:, : self.config.vocab_size]
+
+    def forward(self, input_ids: torch.Tensor, positions: torch.Tensor, forward_batch: ForwardBatch,
+                input_embeds: Optional[torch.Tensor] = None) -> LogitsProcessorOutput:
+        t0 = time.perf_counter()
+        hidden = self.model(input_ids, positions, forward_batch, input_embeds)
+        out = LogitsProcessorOutput(next_token_logits=self.compute_logits(hidden, forward_batch))
+        ms = (time.perf_counter() - t0) * 1e3
+        if forward_batch.forward_mode.is_decode():
+            forward_batch.llm_decode_ms = ms
+        else:
+            forward_batch.llm_prefill_ms = ms
+        return out
+
+    # ------------------------------------------------------------------ loading
+    @staticmethod
+    def _canonical_name(name: str) -> Optional[str]:
+        for old, new in (("model.language_model.", "model."), ("language_model.model.", "model."),
+                         ("language_model.", "model.")):
+            if name.startswith(old):
+                name = new + name[len(old):]
+                break
+        if "rotary_emb.inv_freq" in name:
+            return None
+        return name
+
+    def load_weights(self, weights: Iterable[Tuple[str, torch.Tensor]]) -> set:
+        params = dict(self.named_parameters())
+        loaded = set()
+        for raw_name, tensor in weights:
+            name = self._canonical_name(raw_name)
+            if name is None or name.startswith("visual.") or name.startswith("model.visual."):
+                continue
+            if name.startswith("lm_head.") and self.tie:
+                continue
+            target, shard = name, None
+            for fused, part, sid in self.stacked_params_mapping:
+                if part in name:
+                    cand = name.replace(part, fused)
+                    if cand in params:
+                        target, shard = cand, sid
+                        break
+            if target not in params:
+                alt = target.replace(".q_norm.", ".self_attn.q_norm.") if False else target
+                if alt not in params:
+                    continue
+            p = params[target]
+            if shard in ("k", "v"):
+                attn = self._attn_of(target)
+                if attn is not None and attn.kv_replicated:
+                    tensor = attn.kv_shard_for_rank(tensor)
+            loader = getattr(p, "weight_loader", None)
+            if loader is None:
+                p.data.copy_(tensor.reshape(p.shape))
+            elif shard is None:
+                loader(p, tensor)
+            else:
+                loader(p, tensor, shard)
+            loaded.add(target)
+        return loaded
+
+    def _attn_of(self, param_name: str) -> Optional[Qwen3Attention]:
+        parts = param_name.split(".")
+        try:
+            i = parts.index("layers")
+            return self.model.layers[int(parts[i + 1])].self_attn
+        except (ValueError, IndexError):
+            return None
+
+
+EntryClass = Qwen3ForCausalLM

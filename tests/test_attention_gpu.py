@@ -1,0 +1,101 @@
+"""tcgen05 attention kernel (prefill with cached prefixes, split decode) vs the fp32 statement."""
+import pytest
+import torch
+
+from mllm_b200 import ops
+from mllm_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+D = 128
+
+
+def _setup(seq_lens, prefix_lens, hq, hkv, dtype=torch.bfloat16, seed=0, ctx=None):
+    torch.manual_seed(seed)
+    B = len(seq_lens)
+    ctx = ctx or max(seq_lens) + 8
+    total = sum(seq_lens)
+    slots = total + 64
+    kc = torch.randn(slots, hkv, D, device=DEV, dtype=dtype)
+    vc = torch.randn(slots, hkv, D, device=DEV, dtype=dtype)
+    rtt = torch.zeros(B + 3, ctx, dtype=torch.int32, device=DEV)
+    perm = torch.randperm(slots - 1, device=DEV)[:total].int() + 1  # scattered slots: page size 1
+    req = torch.arange(B, device=DEV, dtype=torch.int32) + 2
+    off = 0
+    for b, s in enumerate(seq_lens):
+        rtt[req[b], :s] = perm[off:off + s]
+        off += s
+    ext = [s - p for s, p in zip(seq_lens, prefix_lens)]
+    T = sum(ext)
+    q = torch.randn(T, hq, D, device=DEV, dtype=dtype)
+    q_start = torch.tensor([sum(ext[:i]) for i in range(B)], dtype=torch.int32, device=DEV)
+    return dict(q=q, kc=kc, vc=vc, rtt=rtt, req=req, seq=torch.tensor(seq_lens, dtype=torch.int32, device=DEV),
+                pre=torch.tensor(prefix_lens, dtype=torch.int32, device=DEV), q_start=q_start, max_q=max(ext))
+
+
+def _err(a, b):
+    return (a.float() - b.float()).abs().max().item()
+
+
+@pytest.mark.parametrize("seq_lens,prefix_lens", [
+    ([1], [0]), ([2], [0]), ([3], [0]), ([17], [0]), ([64], [0]), ([65], [0]), ([127, 128, 129], [0, 0, 0]),
+    ([300], [0]), ([700, 33], [0, 0]),
+    ([200, 130], [64, 1]), ([513], [511]), ([1000], [873]),
+])
+@pytest.mark.parametrize("hq,hkv", [(8, 2), (16, 8), (4, 4), (8, 1)])
+def test_prefill(seq_lens, prefix_lens, hq, hkv):
+    s = _setup(seq_lens, prefix_lens, hq, hkv)
+    scale = D ** -0.5
+    got = ops.attention_prefill(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], s["pre"], s["q_start"], scale,
+                                max_q_len=s["max_q"])
+    ops.check_status()
+    want = ref.attention_prefill(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], s["pre"], s["q_start"], scale)
+    assert _err(got, want) < 3e-2
+
+
+def test_prefill_strided_q_fp16():
+    """q as a view into a fused qkv activation (row stride larger than Hq*D), fp16."""
+    hq, hkv = 8, 2
+    s = _setup([90, 200], [0, 40], hq, hkv, dtype=torch.float16, seed=3)
+    T = s["q"].shape[0]
+    qkv = torch.randn(T, (hq + 2 * hkv) * D, device=DEV, dtype=torch.float16)
+    qkv[:, : hq * D] = s["q"].view(T, -1)
+    qv = qkv[:, : hq * D].view(T, hq, D)
+    got = ops.attention_prefill(qv, s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], s["pre"], s["q_start"], D ** -0.5,
+                                max_q_len=s["max_q"])
+    want = ref.attention_prefill(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], s["pre"], s["q_start"], D ** -0.5)
+    ops.check_status()
+    assert _err(got, want) < 2e-2
+
+
+@pytest.mark.parametrize("seq_lens", [[1], [2], [63], [64], [65], [500], [2048], [1, 700, 64, 129], [3000] * 3, list(range(1, 34))])
+@pytest.mark.parametrize("hq,hkv", [(32, 8), (8, 1), (4, 4)])
+def test_decode(seq_lens, hq, hkv):
+    s = _setup(seq_lens, [x - 1 for x in seq_lens], hq, hkv, seed=1)
+    scale = D ** -0.5
+    got = ops.attention_decode(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], scale, max_seq_len=max(seq_lens))
+    ops.check_status()
+    want = ref.attention_decode(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], scale)
+    assert _err(got, want) < 3e-2
+
+
+def test_decode_fixed_split_bound():
+    """Graph-style call: the split count comes from the context bound, not the live lengths."""
+    s = _setup([5, 900], [4, 899], 16, 8, seed=2, ctx=4096)
+    got = ops.attention_decode(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], D ** -0.5, max_seq_len=4096)
+    ops.check_status()
+    want = ref.attention_decode(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], D ** -0.5)
+    assert _err(got, want) < 3e-2
+
+
+def test_large_scores_rescale():
+    """Scores that grow along the sequence force the lazy rescale of the output accumulator."""
+    hq = hkv = 2
+    s = _setup([400], [0], hq, hkv, seed=5)
+    ramp = torch.linspace(0.2, 6.0, 400, device=DEV).view(-1, 1, 1)
+    s["kc"][s["rtt"][2, :400].long()] = (s["kc"][s["rtt"][2, :400].long()].float() * ramp).bfloat16()
+    got = ops.attention_prefill(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], s["pre"], s["q_start"], 1.0,
+                                max_q_len=400)
+    want = ref.attention_prefill(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], s["pre"], s["q_start"], 1.0)
+    ops.check_status()
+    assert _err(got, want) < 5e-2
