@@ -77,6 +77,7 @@ __device__ __forceinline__ uint32_t swz_off(int row, int chunk, int half_bytes) 
 }
 
 __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const AttnParams p) {
+  pdl_wait();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
@@ -179,16 +180,17 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const AttnPar
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int t = t0 + (tid >> 4) + 8 * i;
-      int s = -1;
-      if (tile < n_tiles && t < kv_end) {
-        s = rtt[t];
-        if (s < 0 || s >= p.num_slots) {
-          if (p.status != nullptr) atomicExch(p.status, kStatusBadIndex);
-          s = -1;
-        }
-      }
-      slots_next[i] = s;
+      slots_next[i] = (tile < n_tiles && t < kv_end) ? __ldg(rtt + t) : -1;
     }
+    bool bad = false;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (slots_next[i] < -1 || slots_next[i] >= p.num_slots) {
+        bad = true;
+        slots_next[i] = -1;
+      }
+    }
+    if (bad && p.status != nullptr) atomicExch(p.status, kStatusBadIndex);
   };
   auto gather = [&](int buf) {
     const uint32_t sk = smem_u32(sK + buf * kSmemKVBuf);
@@ -294,8 +296,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const AttnPar
         uint32_t w[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float p0 = exp2f(sc[ch * 8 + 2 * i] - m_used);
-          const float p1 = exp2f(sc[ch * 8 + 2 * i + 1] - m_used);
+          const float p0 = fast_exp2(sc[ch * 8 + 2 * i] - m_used);
+          const float p1 = fast_exp2(sc[ch * 8 + 2 * i + 1] - m_used);
           // sum what the tensor core will actually see (bf16-rounded probabilities)
           const uint32_t pk = p.out_f16 ? 0u : pack_bf16x2(p0, p1);
           if (p.out_f16) {
@@ -397,9 +399,359 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const AttnPar
   }
 }
 
+
+template <int N>
+__device__ __forceinline__ float m_used_at(const float (&m)[N], int idx) {
+  float v = 0.f;
+#pragma unroll
+  for (int c = 0; c < N; ++c) v = (c == idx) ? m[c] : v;
+  return v;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Decode-specialised kernel: one query token per request, so the roles of the MMA dimensions are
+// swapped - the 128 KV tokens of a tile are the MMA M dimension and the (padded) query heads of
+// the GQA group are the N dimension:
+//   S^T[tok, q] = K[tok, d] Q^T          (A = K tile, K-major; B = Q, K-major)
+//   O^T[d, q]  += V^T[d, tok] P^T[tok, q] (A = V tile as gathered, used MN-major; B = P^T, K-major)
+// A thread owns one token for the softmax (only the per-head maximum crosses threads, once per
+// tile; the row sums stay per-thread until the end) and one feature d for the output, so the
+// final store is coalesced.  K/V tiles of 128 tokens go through a three-deep cp.async ring: two
+// tiles (128 KB) are in flight while one is being consumed, which is what keeps HBM busy with a
+// single resident CTA per SM.
+// ---------------------------------------------------------------------------------------------
+constexpr int kDT = 128;                       // tokens per decode tile
+constexpr int kDecHalf = kDT * 128;            // bytes of one 64-feature half of a K or V tile
+constexpr int kDecTileBytes = 2 * kDecHalf;    // 32 KB per tensor
+constexpr int kDecBufs = 3;
+
+template <int NQ>
+struct DecCfg {
+  static constexpr int kQBytes = 2 * NQ * 128;   // Q^T operand: two halves of NQ rows x 128 B
+  static constexpr int kPBytes = 2 * NQ * 128;   // P^T operand: two halves (64 tokens each)
+  static constexpr int kSmem = kDecBufs * 2 * kDecTileBytes + kQBytes + kPBytes + 1024 + 64 + 4 * NQ * 4 + 2 * NQ * 4;
+};
+
+template <int NQ>
+__global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const AttnParams p) {
+  using C = DecCfg<NQ>;
+  pdl_wait();
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;                                   // kDecBufs tiles
+  uint8_t* sV = sK + kDecBufs * kDecTileBytes;          // kDecBufs tiles
+  uint8_t* sQ = sV + kDecBufs * kDecTileBytes;
+  uint8_t* sP = sQ + C::kQBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + C::kPBytes);
+  uint64_t* bar_s = bars;                               // two: S^T buffers alternate between tiles
+  uint64_t* bar_o = bars + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 3);
+  float* red = reinterpret_cast<float*>(bars + 4);      // [4 warps][NQ]
+  float* red2 = red + 4 * NQ;                           // [NQ] totals
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int b = blockIdx.z;
+  const int hk = blockIdx.y;
+  const int split = blockIdx.x;
+  const int g = p.group;
+  const int req = p.req_pool_indices[b];
+  const int seq_len = p.seq_lens[b];
+  const int tiles = (seq_len + kDT - 1) / kDT;
+  const int per = (tiles + p.num_splits - 1) / p.num_splits;
+  const int kv_begin = split * per * kDT;
+  const int kv_end = min(seq_len, kv_begin + per * kDT);
+
+  if (kv_begin >= kv_end) {
+    if (p.num_splits > 1) {
+      for (int i = tid; i < g * kD; i += kAttnThreads) {
+        const int head = hk * g + i / kD;
+        p.part_o[((static_cast<int64_t>(b) * p.hq + head) * p.num_splits + split) * kD + (i % kD)] = 0.f;
+      }
+      if (tid < g) p.part_lse[(static_cast<int64_t>(b) * p.hq + hk * g + tid) * p.num_splits + split] = -INFINITY;
+    }
+    return;
+  }
+  const int n_tiles = (kv_end - kv_begin + kDT - 1) / kDT;
+
+  if (tid == 0) {
+    mbar_init(&bar_s[0], 1);
+    mbar_init(&bar_s[1], 1);
+    mbar_init(bar_o, 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (warp == 0) {
+    tmem_alloc(tmem_holder, 128);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_s = tmem_base;            // two buffers of NQ columns
+  const uint32_t tmem_o = tmem_base + 2 * NQ;   // NQ columns
+  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+
+  const uint16_t* qbase = static_cast<const uint16_t*>(p.q);
+  const uint16_t* kbase = static_cast<const uint16_t*>(p.k_cache);
+  const uint16_t* vbase = static_cast<const uint16_t*>(p.v_cache);
+  const int* rtt = p.req_to_token + static_cast<int64_t>(req) * p.rtt_stride;
+
+  // Q^T operand: NQ rows (query heads, zero beyond the group) x 16 chunks
+  {
+    const uint32_t sq = smem_u32(sQ);
+    for (int c = tid; c < NQ * 16; c += kAttnThreads) {
+      const int r = c >> 4, ch = c & 15;
+      const bool ok = r < g;
+      const uint16_t* src = qbase + static_cast<int64_t>(b) * p.q_stride + static_cast<int64_t>(hk * g + (ok ? r : 0)) * kD + ch * 8;
+      cp_async16(sq + swz_off(r, ch, NQ * 128), src, ok);
+    }
+  }
+
+  // gather one 128-token tile of K or of V: thread handles chunk (tid & 15) of tokens (tid >> 4) + 8 i.
+  // Always commits one cp.async group (possibly empty) so that group counting stays uniform.
+  auto gather = [&](int tile, const uint16_t* base, uint8_t* ring) {
+    if (tile < n_tiles) {
+      const uint32_t dst = smem_u32(ring + (tile % kDecBufs) * kDecTileBytes);
+      const int ch = tid & 15;
+      const int t0 = kv_begin + tile * kDT;
+      // all 16 table reads are issued before any of them is checked, so they overlap
+      int slots[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int t = t0 + (tid >> 4) + 8 * i;
+        slots[i] = (t < kv_end) ? __ldg(rtt + t) : -1;
+      }
+      bool bad = false;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        if (slots[i] < -1 || slots[i] >= p.num_slots) {
+          bad = true;
+          slots[i] = -1;
+        }
+      }
+      if (bad && p.status != nullptr) atomicExch(p.status, kStatusBadIndex);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int r = (tid >> 4) + 8 * i;
+        const bool ok = slots[i] >= 0;
+        const int64_t off = (static_cast<int64_t>(ok ? slots[i] : 0) * p.hkv + hk) * kD + ch * 8;
+        cp_async16(dst + swz_off(r, ch, kDecHalf), base + off, ok);
+      }
+    }
+    cp_async_commit();
+  };
+  auto issue_s = [&](int tile) {  // S^T of `tile` into its tensor-memory buffer; one thread
+    tc_fence_after_sync();
+    const uint32_t ka = smem_u32(sK + (tile % kDecBufs) * kDecTileBytes);
+    const uint32_t qa = smem_u32(sQ);
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      const uint64_t a_desc = umma_desc_k_sw128(ka + (kk >> 2) * kDecHalf + (kk & 3) * 32);
+      const uint64_t b_desc = umma_desc_k_sw128(qa + (kk >> 2) * (NQ * 128) + (kk & 3) * 32);
+      umma_f16(tmem_s + (tile & 1) * NQ, a_desc, b_desc, p.idesc_s, kk > 0 ? 1u : 0u);
+    }
+    umma_commit(&bar_s[tile & 1]);
+  };
+
+  // cp.async groups in issue order: [Q + K0] [V0] [K1] [V1] [K2] [V2], then per tile j: [K(j+3)] [V(j+2)]
+  gather(0, kbase, sK);
+  gather(0, vbase, sV);
+  gather(1, kbase, sK);
+  gather(1, vbase, sV);
+  gather(2, kbase, sK);
+  gather(2, vbase, sV);
+
+  float m_used[NQ];
+  float l_part[NQ];
+#pragma unroll
+  for (int c = 0; c < NQ; ++c) {
+    m_used[c] = 0.f;
+    l_part[c] = 0.f;
+  }
+  bool ok_all = true;
+
+  cp_async_wait<5>();  // Q + K0
+  fence_proxy_async_smem();
+  __syncthreads();
+  if (tid == 0) issue_s(0);
+
+  for (int j = 0; j < n_tiles; ++j) {
+    // ---- A: S^T of the next tile is issued before this tile's softmax, so its latency is hidden ----
+    if (j + 1 < n_tiles) {
+      cp_async_wait<3>();  // K(j+1) has landed
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncthreads();
+      if (tid == 0) issue_s(j + 1);
+    }
+    // ---- B: this thread's token of tile j ----
+    if (!mbar_wait(&bar_s[j & 1], (j >> 1) & 1)) ok_all = false;
+    tc_fence_after_sync();
+    gather(j + 3, kbase, sK);  // the K slot of tile j is free now
+    float sc[NQ];
+    {
+      uint32_t raw[16];
+#pragma unroll
+      for (int c0 = 0; c0 < NQ; c0 += 16) {
+        tmem_ld_32x16(tmem_s + (j & 1) * NQ + lane_base + c0, raw);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) sc[c0 + i] = __uint_as_float(raw[i]);
+      }
+    }
+    const bool tok_ok = (kv_begin + j * kDT + tid) < kv_end;
+#pragma unroll
+    for (int c = 0; c < NQ; ++c) {
+      sc[c] = tok_ok ? sc[c] * p.scale_log2 : -INFINITY;
+      if (c < g) {
+        const float wm = warp_max(sc[c]);
+        if (lane == 0) red[warp * NQ + c] = wm;
+      }
+    }
+    // P*V of the previous tile must be done before its V slot, P^T and O^T are touched again
+    if (j > 0) {
+      if (!mbar_wait(bar_o, (j - 1) & 1)) ok_all = false;
+      tc_fence_after_sync();
+      gather(j + 2, vbase, sV);
+    } else {
+      cp_async_commit();  // V2 went out with the prologue; keep the group count uniform
+    }
+    __syncthreads();
+    bool need = false;
+    float factor[NQ];
+#pragma unroll
+    for (int c = 0; c < NQ; ++c) {
+      factor[c] = 1.f;
+      if (c < g) {
+        const float mt = fmaxf(fmaxf(red[c], red[NQ + c]), fmaxf(red[2 * NQ + c], red[3 * NQ + c]));
+        if (j == 0) {
+          m_used[c] = mt;  // the first tile of a non-empty range always holds a visible token
+        } else if (mt > m_used[c] + kRescaleThreshold) {
+          factor[c] = fast_exp2(m_used[c] - mt);
+          m_used[c] = mt;
+          l_part[c] *= factor[c];
+          need = true;
+        }
+      }
+    }
+    if (need) {  // uniform over the CTA: every thread sees the same maxima
+      uint32_t o[16];
+#pragma unroll
+      for (int c0 = 0; c0 < NQ; c0 += 16) {
+        tmem_ld_32x16(tmem_o + lane_base + c0, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor[c0 + i]);
+        tmem_st_32x16(tmem_o + lane_base + c0, o);
+      }
+      tmem_st_wait();
+    }
+    // P^T operand: row = query head, 128 tokens in two 64-token halves; this thread writes column tid
+    {
+      uint8_t* pbase = sP + (tid >> 6) * (NQ * 128);
+      const int tk = tid & 63;
+#pragma unroll
+      for (int c = 0; c < NQ; ++c) {
+        float pv = 0.f;
+        if (c < g) pv = fast_exp2(sc[c] - m_used[c]);
+        uint16_t bits;
+        float back;
+        if (p.out_f16) {
+          const __half ph = __float2half_rn(pv);
+          bits = *reinterpret_cast<const uint16_t*>(&ph);
+          back = __half2float(ph);
+        } else {
+          const __nv_bfloat16 pb = __float2bfloat16_rn(pv);
+          bits = *reinterpret_cast<const uint16_t*>(&pb);
+          back = __bfloat162float(pb);
+        }
+        l_part[c] += back;
+        *reinterpret_cast<uint16_t*>(pbase + c * 128 + (((tk >> 3) ^ (c & 7)) << 4) + (tk & 7) * 2) = bits;
+      }
+    }
+    cp_async_wait<4>();  // V(j) has landed
+    tc_fence_before_sync();
+    fence_proxy_async_smem();
+    __syncthreads();
+
+    if (tid == 0) {
+      tc_fence_after_sync();
+      const uint32_t va = smem_u32(sV + (j % kDecBufs) * kDecTileBytes);
+      const uint32_t pa = smem_u32(sP);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        const uint64_t a_desc = umma_desc_mn_sw128(va + kk * 2048, kDecHalf, 1024);
+        const uint64_t b_desc = umma_desc_k_sw128(pa + (kk >> 2) * (NQ * 128) + (kk & 3) * 32);
+        umma_f16(tmem_o, a_desc, b_desc, p.idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+      }
+      umma_commit(bar_o);
+    }
+  }
+  cp_async_wait<0>();
+  if (!mbar_wait(bar_o, (n_tiles - 1) & 1)) ok_all = false;
+  tc_fence_after_sync();
+  if (!ok_all && p.status != nullptr) atomicExch(p.status, kStatusPipelineTimeout);
+
+  // ---- totals of the row sums over the 128 token-threads ----
+#pragma unroll
+  for (int c = 0; c < NQ; ++c) {
+    if (c < g) {
+      const float ws = warp_sum(l_part[c]);
+      if (lane == 0) red[warp * NQ + c] = ws;
+    }
+  }
+  __syncthreads();
+  if (tid < g) red2[tid] = red[tid] + red[NQ + tid] + red[2 * NQ + tid] + red[3 * NQ + tid];
+  __syncthreads();
+
+  // ---- output: this thread owns feature d = tid of every head of the group ----
+  {
+    uint32_t o[16];
+#pragma unroll
+    for (int c0 = 0; c0 < NQ; c0 += 16) {
+      tmem_ld_32x16(tmem_o + lane_base + c0, o);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int c = c0 + i;
+        if (c < g && ok_all) {
+          const float l = red2[c];
+          const float v = l > 0.f ? __uint_as_float(o[i]) / l : 0.f;
+          const int head = hk * g + c;
+          if (p.num_splits > 1) {
+            p.part_o[((static_cast<int64_t>(b) * p.hq + head) * p.num_splits + split) * kD + tid] = v;
+          } else {
+            const int64_t oi = (static_cast<int64_t>(b) * p.hq + head) * kD + tid;
+            if (p.out_f16)
+              static_cast<__half*>(p.out)[oi] = __float2half_rn(v);
+            else
+              static_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16_rn(v);
+          }
+        }
+      }
+    }
+    if (p.num_splits > 1 && tid < g) {
+      const float l = red2[tid];
+      p.part_lse[(static_cast<int64_t>(b) * p.hq + hk * g + tid) * p.num_splits + split] =
+          l > 0.f ? (m_used_at(m_used, tid) + log2f(l)) : -INFINITY;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 128);
+  }
+}
+
 // combine decode partials: out[b, h, :] = sum_s w_s * O_s with w_s = 2^(lse_s - max) / sum
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                   void* __restrict__ out, int hq, int splits, int out_f16) {
+  pdl_wait();
   const int b = blockIdx.y, h = blockIdx.x, d = threadIdx.x;
   const int64_t base = (static_cast<int64_t>(b) * hq + h) * splits;
   float m = -INFINITY;
@@ -431,11 +783,26 @@ bool set_attn_smem() {
 }  // namespace
 
 int decode_num_splits(int batch, int hkv, int max_seq_len, int num_sms) {
-  const int tiles = std::max(1, (max_seq_len + kKV - 1) / kKV);
+  // one resident CTA per SM: fill a single wave, never start a second one for a remainder
+  const int tiles = std::max(1, (max_seq_len + kDT - 1) / kDT);
   const int ctas = std::max(1, batch * hkv);
-  int splits = (2 * num_sms + ctas - 1) / ctas;  // two resident CTAs per SM
+  int splits = num_sms / ctas;
   splits = std::min(splits, std::max(1, tiles / 2));
   return std::max(1, std::min(splits, 64));
+}
+
+template <int NQ>
+int launch_decode_cfg(const AttnParams& p, dim3 grid, cudaStream_t s) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(attn_decode_kernel<NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             DecCfg<NQ>::kSmem) != cudaSuccess)
+      return -3;
+    attr_set = true;
+  }
+  launch_pdl(attn_decode_kernel<NQ>, grid, dim3(kAttnThreads), DecCfg<NQ>::kSmem, s, p);
+  note_launch();
+  return 0;
 }
 
 int launch_attention(const AttnArgs& a, cudaStream_t s) {
@@ -472,6 +839,19 @@ int launch_attention(const AttnArgs& a, cudaStream_t s) {
   p.idesc_o = umma_idesc(kRows, kD, 1, fmt, fmt, 0, 1);
   if (a.batch <= 0) return 0;
   dim3 grid;
+  if (a.is_decode && g <= 32) {
+    const int nq = g <= 16 ? 16 : 32;
+    p.idesc_s = umma_idesc(kRows, nq, 1, fmt, fmt, 0, 0);
+    p.idesc_o = umma_idesc(kRows, nq, 1, fmt, fmt, 1, 0);
+    grid = dim3(p.num_splits, a.hkv, a.batch);
+    const int rc = nq == 16 ? launch_decode_cfg<16>(p, grid, s) : launch_decode_cfg<32>(p, grid, s);
+    if (rc != 0) return rc;
+    if (p.num_splits > 1) {
+      launch_pdl(attn_merge_kernel, dim3(a.hq, a.batch), dim3(kD), 0, s, a.part_o, a.part_lse, a.out, a.hq, p.num_splits, p.out_f16);
+      note_launch();
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  }
   if (a.is_decode) {
     grid = dim3(p.num_splits, a.hkv, a.batch);
   } else {
@@ -479,10 +859,10 @@ int launch_attention(const AttnArgs& a, cudaStream_t s) {
     if (q_tiles <= 0) return 0;
     grid = dim3(q_tiles, a.hkv, a.batch);
   }
-  attn_fwd_kernel<<<grid, kAttnThreads, kAttnSmem, s>>>(p);
+  launch_pdl(attn_fwd_kernel, grid, dim3(kAttnThreads), kAttnSmem, s, p);
   note_launch();
   if (a.is_decode && p.num_splits > 1) {
-    attn_merge_kernel<<<dim3(a.hq, a.batch), kD, 0, s>>>(a.part_o, a.part_lse, a.out, a.hq, p.num_splits, p.out_f16);
+    launch_pdl(attn_merge_kernel, dim3(a.hq, a.batch), dim3(kD), 0, s, a.part_o, a.part_lse, a.out, a.hq, p.num_splits, p.out_f16);
     note_launch();
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;

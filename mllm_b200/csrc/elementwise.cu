@@ -6,6 +6,7 @@
 // (the norm kernels keep a row in registers between the reduction and the
 // scaling pass), so their ceiling is HBM bandwidth.
 #include <atomic>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -15,6 +16,13 @@ namespace mb200 {
 static std::atomic<uint64_t> g_launches{0};
 uint64_t launch_count() { return g_launches.load(); }
 void note_launch(int n) { g_launches.fetch_add(n); }
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("MLLM_B200_PDL");
+    return !(v != nullptr && v[0] == '0');
+  }();
+  return on;
+}
 
 namespace {
 
@@ -111,6 +119,7 @@ constexpr int kMaxVecPerThread = 4;  // row cache: hidden <= 4 * 8 * blockDim
 template <typename T, bool kAdd>
 __global__ void rmsnorm_kernel(T* __restrict__ x, T* __restrict__ residual, const T* __restrict__ w,
                                T* __restrict__ out, int hidden, int64_t x_stride, int64_t out_stride, float eps) {
+  pdl_wait();
   __shared__ float red[33];
   const int row = blockIdx.x;
   const int nvec = hidden >> 3;
@@ -158,6 +167,7 @@ __global__ void rmsnorm_kernel(T* __restrict__ x, T* __restrict__ residual, cons
 template <typename T>
 __global__ void layernorm_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b,
                                  T* __restrict__ out, int hidden, float eps) {
+  pdl_wait();
   __shared__ float red[33];
   const int row = blockIdx.x;
   const int nvec = hidden >> 3;
@@ -213,6 +223,7 @@ __device__ __forceinline__ float gelu_tanh_f(float v) {
 
 template <typename T, int kAct>
 __global__ void act_and_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int rows, int inter) {
+  pdl_wait();
   const int vec_per_row = inter >> 3;
   const int64_t total = static_cast<int64_t>(rows) * vec_per_row;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
@@ -231,6 +242,7 @@ __global__ void act_and_mul_kernel(const T* __restrict__ x, T* __restrict__ out,
 
 template <typename T>
 __global__ void gelu_tanh_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t nvec) {
+  pdl_wait();
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     float f[8];
@@ -246,6 +258,7 @@ __global__ void gelu_tanh_kernel(const T* __restrict__ x, T* __restrict__ out, i
 // ---------------------------------------------------------------------------
 __global__ void embedding_kernel(const int64_t* __restrict__ ids, const uint4* __restrict__ table,
                                  uint4* __restrict__ out, int vec_per_row, int vocab, int* status) {
+  pdl_wait();
   const int t = blockIdx.x;
   int64_t id = ids[t];
   if (id < 0 || id >= vocab) {
@@ -270,6 +283,7 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const T* __res
                                              const int64_t* __restrict__ cache_loc, T* __restrict__ k_cache,
                                              T* __restrict__ v_cache, int tokens, int hq, int hkv,
                                              int64_t qkv_stride, int64_t num_slots, float eps, int* status) {
+  pdl_wait();
   constexpr int D = 128;
   const int heads = hq + 2 * hkv;
   const int64_t warp = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
@@ -333,6 +347,7 @@ template <typename T>
 __global__ void kv_write_kernel(const T* __restrict__ k, const T* __restrict__ v, const int64_t* __restrict__ loc,
                                 T* __restrict__ k_cache, T* __restrict__ v_cache, int tokens, int row_elems,
                                 int64_t k_stride, int64_t v_stride, int64_t num_slots, int* status) {
+  pdl_wait();
   const int vec = row_elems >> 3;
   const int64_t total = static_cast<int64_t>(tokens) * vec;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
@@ -355,6 +370,7 @@ __global__ void kv_write_kernel(const T* __restrict__ k, const T* __restrict__ v
 template <typename T>
 __global__ void per_token_quant_int8_kernel(const T* __restrict__ x, int8_t* __restrict__ q,
                                             float* __restrict__ scale, int k) {
+  pdl_wait();
   __shared__ float red[33];
   const int row = blockIdx.x;
   const int nvec = k >> 3;
@@ -408,6 +424,7 @@ __device__ __forceinline__ float load_as_float(const T* p) {
 
 template <typename T>
 __global__ void argmax_kernel(const T* __restrict__ logits, int64_t* __restrict__ out, int vocab, int64_t stride) {
+  pdl_wait();
   __shared__ float sval[32];
   __shared__ int sidx[32];
   const T* row = logits + blockIdx.x * stride;
@@ -473,7 +490,7 @@ void launch_rmsnorm(const void* x, const void* w, void* out, int rows, int hidde
                     int64_t out_stride, float eps, DType dt, cudaStream_t s) {
   if (rows == 0) return;
   const int threads = norm_threads(hidden);
-  MB200_DISPATCH_HALF(dt, (rmsnorm_kernel<T, false><<<rows, threads, 0, s>>>(
+  MB200_DISPATCH_HALF(dt, (launch_pdl(rmsnorm_kernel<T, false>, dim3(rows), dim3(threads), 0, s, 
                               const_cast<T*>(static_cast<const T*>(x)), nullptr, static_cast<const T*>(w),
                               static_cast<T*>(out), hidden, x_stride, out_stride, eps)));
   note_launch();
@@ -483,7 +500,7 @@ void launch_fused_add_rmsnorm(void* x, void* residual, const void* w, int rows, 
                               cudaStream_t s) {
   if (rows == 0) return;
   const int threads = norm_threads(hidden);
-  MB200_DISPATCH_HALF(dt, (rmsnorm_kernel<T, true><<<rows, threads, 0, s>>>(
+  MB200_DISPATCH_HALF(dt, (launch_pdl(rmsnorm_kernel<T, true>, dim3(rows), dim3(threads), 0, s, 
                               static_cast<T*>(x), static_cast<T*>(residual), static_cast<const T*>(w),
                               static_cast<T*>(x), hidden, hidden, hidden, eps)));
   note_launch();
@@ -493,7 +510,7 @@ void launch_layernorm(const void* x, const void* w, const void* b, void* out, in
                       DType dt, cudaStream_t s) {
   if (rows == 0) return;
   const int threads = norm_threads(hidden);
-  MB200_DISPATCH_HALF(dt, (layernorm_kernel<T><<<rows, threads, 0, s>>>(static_cast<const T*>(x),
+  MB200_DISPATCH_HALF(dt, (launch_pdl(layernorm_kernel<T>, dim3(rows), dim3(threads), 0, s, static_cast<const T*>(x),
                                                                          static_cast<const T*>(w),
                                                                          static_cast<const T*>(b),
                                                                          static_cast<T*>(out), hidden, eps)));
@@ -506,10 +523,10 @@ void launch_act_and_mul(const void* x, void* out, int rows, int inter, int act, 
   const int threads = 256;
   const int blocks = static_cast<int>(std::min<int64_t>((total + threads - 1) / threads, 148 * 16));
   if (act == 0) {
-    MB200_DISPATCH_HALF(dt, (act_and_mul_kernel<T, 0><<<blocks, threads, 0, s>>>(static_cast<const T*>(x),
+    MB200_DISPATCH_HALF(dt, (launch_pdl(act_and_mul_kernel<T, 0>, dim3(blocks), dim3(threads), 0, s, static_cast<const T*>(x),
                                                                                   static_cast<T*>(out), rows, inter)));
   } else {
-    MB200_DISPATCH_HALF(dt, (act_and_mul_kernel<T, 1><<<blocks, threads, 0, s>>>(static_cast<const T*>(x),
+    MB200_DISPATCH_HALF(dt, (launch_pdl(act_and_mul_kernel<T, 1>, dim3(blocks), dim3(threads), 0, s, static_cast<const T*>(x),
                                                                                   static_cast<T*>(out), rows, inter)));
   }
   note_launch();
@@ -520,7 +537,7 @@ void launch_gelu_tanh(const void* x, void* out, int64_t n, DType dt, cudaStream_
   const int64_t nvec = n >> 3;
   const int threads = 256;
   const int blocks = static_cast<int>(std::min<int64_t>((nvec + threads - 1) / threads, 148 * 16));
-  MB200_DISPATCH_HALF(dt, (gelu_tanh_kernel<T><<<blocks, threads, 0, s>>>(static_cast<const T*>(x),
+  MB200_DISPATCH_HALF(dt, (launch_pdl(gelu_tanh_kernel<T>, dim3(blocks), dim3(threads), 0, s, static_cast<const T*>(x),
                                                                            static_cast<T*>(out), nvec)));
   note_launch();
 }
@@ -531,7 +548,7 @@ void launch_embedding(const int64_t* ids, const void* table, void* out, int toke
   (void)dt;  // 16-bit element types share the copy
   const int vec = hidden >> 3;
   const int threads = vec >= 256 ? 256 : ((vec + 31) / 32 * 32);
-  embedding_kernel<<<tokens, threads, 0, s>>>(ids, static_cast<const uint4*>(table), static_cast<uint4*>(out), vec,
+  launch_pdl(embedding_kernel, dim3(tokens), dim3(threads), 0, s, ids, static_cast<const uint4*>(table), static_cast<uint4*>(out), vec,
                                               vocab, status);
   note_launch();
 }
@@ -545,7 +562,7 @@ void launch_qk_norm_rope_kv_write(void* qkv, const void* q_w, const void* k_w, c
   const int64_t warps = static_cast<int64_t>(tokens) * (num_q_heads + 2 * num_kv_heads);
   const int threads = 128;
   const int blocks = static_cast<int>((warps * 32 + threads - 1) / threads);
-  MB200_DISPATCH_HALF(dt, (qk_norm_rope_kv_write_kernel<T><<<blocks, threads, 0, s>>>(
+  MB200_DISPATCH_HALF(dt, (launch_pdl(qk_norm_rope_kv_write_kernel<T>, dim3(blocks), dim3(threads), 0, s, 
                               static_cast<T*>(qkv), static_cast<const T*>(q_w), static_cast<const T*>(k_w),
                               positions, pos_rows, axis_map, inv_freq, cache_loc, static_cast<T*>(k_cache),
                               static_cast<T*>(v_cache), tokens, num_q_heads, num_kv_heads, qkv_stride, num_slots,
@@ -560,7 +577,7 @@ void launch_kv_write(const void* k, const void* v, const int64_t* loc, void* k_c
   const int64_t total = static_cast<int64_t>(tokens) * (row_elems >> 3);
   const int threads = 256;
   const int blocks = static_cast<int>(std::min<int64_t>((total + threads - 1) / threads, 148 * 16));
-  MB200_DISPATCH_HALF(dt, (kv_write_kernel<T><<<blocks, threads, 0, s>>>(
+  MB200_DISPATCH_HALF(dt, (launch_pdl(kv_write_kernel<T>, dim3(blocks), dim3(threads), 0, s, 
                               static_cast<const T*>(k), static_cast<const T*>(v), loc, static_cast<T*>(k_cache),
                               static_cast<T*>(v_cache), tokens, row_elems, k_stride, v_stride, num_slots, status)));
   note_launch();
@@ -570,7 +587,7 @@ void launch_per_token_quant_int8(const void* x, int8_t* q, float* scale, int row
                                  cudaStream_t s) {
   if (rows == 0) return;
   const int threads = norm_threads(k);
-  MB200_DISPATCH_HALF(dt, (per_token_quant_int8_kernel<T><<<rows, threads, 0, s>>>(static_cast<const T*>(x), q,
+  MB200_DISPATCH_HALF(dt, (launch_pdl(per_token_quant_int8_kernel<T>, dim3(rows), dim3(threads), 0, s, static_cast<const T*>(x), q,
                                                                                     scale, k)));
   note_launch();
 }
@@ -579,9 +596,9 @@ void launch_argmax(const void* logits, int64_t* out, int rows, int vocab, int64_
                    cudaStream_t s) {
   if (rows == 0) return;
   if (dt == kF32) {
-    argmax_kernel<float><<<rows, 1024, 0, s>>>(static_cast<const float*>(logits), out, vocab, stride);
+    launch_pdl(argmax_kernel<float>, dim3(rows), dim3(1024), 0, s, static_cast<const float*>(logits), out, vocab, stride);
   } else {
-    MB200_DISPATCH_HALF(dt, (argmax_kernel<T><<<rows, 1024, 0, s>>>(static_cast<const T*>(logits), out, vocab,
+    MB200_DISPATCH_HALF(dt, (launch_pdl(argmax_kernel<T>, dim3(rows), dim3(1024), 0, s, static_cast<const T*>(logits), out, vocab,
                                                                      stride)));
   }
   note_launch();

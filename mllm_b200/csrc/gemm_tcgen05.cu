@@ -10,14 +10,19 @@
 //     tile i overlaps the main loop of tile i+1.
 //   * "swap" (m <= 256, decode): the weight matrix is the 128-row MMA operand and the
 //     (padded) batch is the MMA N dimension, so tiny batches still use full-width MMAs and
-//     the kernel is a pure weight stream; split-K spreads narrow layers over all SMs, the
-//     last CTA of a tile (ticket counter) sums the fp32 partials from the workspace.
+//     the kernel is a pure weight stream.  Work is scheduled stream-K style: the
+//     (tile, k-block) iteration space is cut into one equal contiguous range per CTA, so
+//     every SM streams the same number of weight bytes in a single persistent wave; a tile
+//     whose k range is shared by several CTAs is finished by the last one to arrive (ticket
+//     counter), which sums the fp32 partials from the workspace in contributor order, so
+//     the result does not depend on timing.
 //
 // Warp roles (256 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warp 2 = TMEM
 // allocator, warps 4-7 = epilogue (warp w reads TMEM lanes 32*(w%4)..).
 // Every mbarrier wait is bounded; on expiry the kernel records kStatusPipelineTimeout in
 // *status and all roles drain out, TMEM is freed, and the host raises.
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -44,26 +49,36 @@ struct KParams {
   int m, n, k_blocks;
   int64_t ldc, ld_res;
   int tiles_r, tiles_c;  // tiles over the row-operand rows / column-operand rows
-  int splits, kb_per_split;
+  int max_contrib;       // swap tiling: upper bound of CTAs sharing one tile (workspace stride)
+  int whole_tiles;       // swap tiling: 1 = CTA ranges are rounded to tile boundaries (no sharing)
+  int stages;            // ring depth in use (<= Cfg::kStages)
   int out_f16;           // 0: bf16 output, 1: fp16 output
   int is_int8;
   uint32_t idesc;
 };
 
-template <int BN, bool SWAP, bool SWIGLU>
+// RT = 128-row MMA tiles of the row operand per stage (small-batch tiling only; SwiGLU needs 2: a
+// gate block and its up block), KD = 128-byte K atoms per stage.  Larger stages mean fewer TMA boxes
+// and barrier round trips per byte streamed.
+template <int BN, bool SWAP, bool SWIGLU, int RT, int KD>
 struct Cfg {
-  static constexpr int R = (SWAP && SWIGLU) ? 2 : 1;         // 128-row MMA tiles per stage
-  static constexpr int kRowTileBytes = kBM * R * kRowBytes;   // 16 KB * R
+  static constexpr int R = SWAP ? RT : 1;
+  static constexpr int kRowTileBytes = kBM * R * kRowBytes;   // 16 KB * R per K atom
   static constexpr int kColTileBytes = BN * kRowBytes;
-  static constexpr int kStageBytes = kRowTileBytes + kColTileBytes;
-  static constexpr int kStagesRaw = SWAP ? (98304 / kStageBytes) : (196608 / kStageBytes);
-  static constexpr int kStages = kStagesRaw < 3 ? 3 : (kStagesRaw > 6 ? 6 : kStagesRaw);
-  static constexpr int kAccBufs = SWAP ? 1 : 2;
+  static constexpr int kAtomBytes = kRowTileBytes + kColTileBytes;
+  static constexpr int kStageBytes = KD * kAtomBytes;
+  // one or two CTAs per SM: the ring takes the shared memory that is left
+  static constexpr int kStagesRaw = 200704 / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 12 ? 12 : kStagesRaw;
+  static constexpr int kSub = SWIGLU ? 1 : R;                 // output rows finalised per epilogue thread
   static constexpr int kAccCols = R * BN;
+  static constexpr int kAccBufs = (2 * kAccCols <= 512) ? 2 : 1;
   static constexpr int kTmemColsRaw = kAccBufs * kAccCols;
   static constexpr int kTmemCols =
       kTmemColsRaw <= 32 ? 32 : (kTmemColsRaw <= 64 ? 64 : (kTmemColsRaw <= 128 ? 128 : (kTmemColsRaw <= 256 ? 256 : 512)));
-  static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 + 256;
+  static_assert(kStages >= 2, "stage too large for shared memory");
+  static_assert(!SWIGLU || !SWAP || RT == 2, "SwiGLU small-batch tiles hold a gate block and an up block");
+  static_assert(SWAP || (RT == 1 && KD == 1), "normal tiling uses single-atom stages");
   static_assert(kTmemColsRaw <= 512, "accumulators exceed tensor memory");
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "invalid MMA N");
 };
@@ -91,17 +106,18 @@ __device__ __forceinline__ float acc_to_float(uint32_t raw, int is_int8) {
   return is_int8 ? static_cast<float>(static_cast<int32_t>(raw)) : __uint_as_float(raw);
 }
 
-template <int BN, bool SWAP, bool SWIGLU>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int BN, bool SWAP, bool SWIGLU, int RT, int KD>
+__global__ void __launch_bounds__(kThreads, SWAP ? 2 : 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_constant__ CUtensorMap tm_col,
                     const KParams p) {
-  using C = Cfg<BN, SWAP, SWIGLU>;
+  using C = Cfg<BN, SWAP, SWIGLU, RT, KD>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(C::kStages) * C::kStageBytes);
+  const int n_stages = p.stages;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(n_stages) * C::kStageBytes);
   uint64_t* full_bar = bars;
-  uint64_t* empty_bar = bars + C::kStages;
-  uint64_t* acc_full = bars + 2 * C::kStages;
+  uint64_t* empty_bar = bars + n_stages;
+  uint64_t* acc_full = bars + 2 * n_stages;
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
@@ -111,7 +127,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::kStages; ++s) {
+    for (int s = 0; s < n_stages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
@@ -133,18 +149,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
+  // set-up above touched no global memory; from here on inputs of earlier kernels are read
+  pdl_wait();
 
   const int total_tiles = p.tiles_r * p.tiles_c;
-  const int total_work = total_tiles * p.splits;
+  // swap tiling: this CTA's contiguous range of the (tile, k-block) iteration space
+  const int64_t total_iters = static_cast<int64_t>(total_tiles) * p.k_blocks;
+  const int64_t it_begin =
+      !SWAP ? 0
+            : (p.whole_tiles ? (static_cast<int64_t>(total_tiles) * blockIdx.x / gridDim.x) * p.k_blocks
+                             : (total_iters * blockIdx.x) / gridDim.x);
+  const int64_t it_end =
+      !SWAP ? 0
+            : (p.whole_tiles ? (static_cast<int64_t>(total_tiles) * (blockIdx.x + 1) / gridDim.x) * p.k_blocks
+                             : (total_iters * (blockIdx.x + 1)) / gridDim.x);
 
-  // work item -> (row tile, column tile, k range)
-  auto decode = [&](int w, int& tr, int& tc, int& kb0, int& kb1, int& split) {
-    split = w % p.splits;
-    const int tile = w / p.splits;
-    if (SWAP) {
-      tr = tile;
-      tc = 0;
+  // idx-th piece of work of this CTA -> (row tile, column tile, k-block range); false when done
+  auto get_work = [&](int idx, int& tr, int& tc, int& kb0, int& kb1) -> bool {
+    if constexpr (SWAP) {
+      int64_t it = it_begin;
+      for (int i = 0;; ++i) {
+        if (it >= it_end) return false;
+        const int tile = static_cast<int>(it / p.k_blocks);
+        const int k0 = static_cast<int>(it - static_cast<int64_t>(tile) * p.k_blocks);
+        const int k1 = static_cast<int>(min(static_cast<int64_t>(p.k_blocks), k0 + (it_end - it)));
+        if (i == idx) {
+          tr = tile;
+          tc = 0;
+          kb0 = k0;
+          kb1 = k1;
+          return true;
+        }
+        it += k1 - k0;
+      }
     } else {
+      const int tile = blockIdx.x + idx * gridDim.x;
+      if (tile >= total_tiles) return false;
       constexpr int kGroup = 16;  // row tiles per raster group: a wave shares ~16 A tiles x ~9 B tiles in L2
       const int per_group = kGroup * p.tiles_c;
       const int g = tile / per_group;
@@ -153,9 +193,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
       const int in = tile - g * per_group;
       tr = first + in % gsize;
       tc = in / gsize;
+      kb0 = 0;
+      kb1 = p.k_blocks;
+      return true;
     }
-    kb0 = split * p.kb_per_split;
-    kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+  };
+  // CTA that owns iteration x of the swap schedule: the largest c with floor(c * I / G) <= x
+  auto cta_of = [&](int64_t x) -> int {
+    return static_cast<int>(min(static_cast<int64_t>(gridDim.x) - 1, ((x + 1) * gridDim.x - 1) / total_iters));
   };
 
   if (warp == 0 && lane == 0) {
@@ -163,21 +208,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-      int tr, tc, kb0, kb1, split;
-      decode(w, tr, tc, kb0, kb1, split);
+    int tr, tc, kb0, kb1;
+    for (int idx = 0; ok && get_work(idx, tr, tc, kb0, kb1); ++idx) {
       const int k_elems_per_block = p.is_int8 ? kRowBytes : kRowBytes / 2;
       for (int kb = kb0; kb < kb1; ++kb) {
         if (*abort_flag || !mbar_wait(&empty_bar[stage], phase ^ 1)) {
           ok = false;
           break;
         }
-        uint8_t* row_tile = smem + static_cast<size_t>(stage) * C::kStageBytes;
-        uint8_t* col_tile = row_tile + C::kRowTileBytes;
+        uint8_t* stage_base = smem + static_cast<size_t>(stage) * C::kStageBytes;
         mbar_arrive_expect_tx(&full_bar[stage], C::kStageBytes);
-        tma_load_2d(row_tile, &tm_row, &full_bar[stage], kb * k_elems_per_block, tr * kBM * C::R);
-        tma_load_2d(col_tile, &tm_col, &full_bar[stage], kb * k_elems_per_block, tc * BN);
-        if (++stage == C::kStages) {
+#pragma unroll
+        for (int kd = 0; kd < KD; ++kd) {
+          uint8_t* row_tile = stage_base + kd * C::kAtomBytes;
+          const int x = (kb * KD + kd) * k_elems_per_block;
+          tma_load_2d(row_tile, &tm_row, &full_bar[stage], x, tr * kBM * C::R);
+          tma_load_2d(row_tile + C::kRowTileBytes, &tm_col, &full_bar[stage], x, tc * BN);
+        }
+        if (++stage == n_stages) {
           stage = 0;
           phase ^= 1;
         }
@@ -192,12 +240,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    int it = 0;
-    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++it) {
-      int tr, tc, kb0, kb1, split;
-      decode(w, tr, tc, kb0, kb1, split);
-      const int acc = SWAP ? 0 : (it & 1);
-      const uint32_t acc_phase = SWAP ? (it & 1) : ((it >> 1) & 1);
+    int tr, tc, kb0, kb1;
+    for (int idx = 0; ok && get_work(idx, tr, tc, kb0, kb1); ++idx) {
+      const int acc = idx % C::kAccBufs;
+      const uint32_t acc_phase = (idx / C::kAccBufs) & 1;
       if (*abort_flag || !mbar_wait(&acc_empty[acc], acc_phase ^ 1)) {
         ok = false;
         break;
@@ -210,23 +256,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
           break;
         }
         tc_fence_after_sync();
-        const uint32_t row_addr = smem_u32(smem + static_cast<size_t>(stage) * C::kStageBytes);
-        const uint32_t col_addr = row_addr + C::kRowTileBytes;
+        const uint32_t stage_addr = smem_u32(smem + static_cast<size_t>(stage) * C::kStageBytes);
 #pragma unroll
-        for (int r = 0; r < C::R; ++r) {
+        for (int kd = 0; kd < KD; ++kd) {
+          const uint32_t row_addr = stage_addr + kd * C::kAtomBytes;
+          const uint64_t a_base = umma_desc_k_sw128(row_addr);
+          const uint64_t b_base = umma_desc_k_sw128(row_addr + C::kRowTileBytes);
 #pragma unroll
-          for (int kk = 0; kk < kRowBytes / kUmmaKBytes; ++kk) {
-            const uint64_t a_desc = umma_desc_k_sw128(row_addr + r * (kBM * kRowBytes) + kk * kUmmaKBytes);
-            const uint64_t b_desc = umma_desc_k_sw128(col_addr + kk * kUmmaKBytes);
-            const uint32_t accum = (kb > kb0 || kk > 0) ? 1u : 0u;
-            if (p.is_int8)
-              umma_i8(d_base + r * BN, a_desc, b_desc, p.idesc, accum);
-            else
-              umma_f16(d_base + r * BN, a_desc, b_desc, p.idesc, accum);
+          for (int r = 0; r < C::R; ++r) {
+#pragma unroll
+            for (int kk = 0; kk < kRowBytes / kUmmaKBytes; ++kk) {
+              // descriptors advance in 16-byte units inside the low word
+              const uint64_t a_desc = a_base + ((r * (kBM * kRowBytes) + kk * kUmmaKBytes) >> 4);
+              const uint64_t b_desc = b_base + ((kk * kUmmaKBytes) >> 4);
+              const uint32_t accum = (kb > kb0 || kd > 0 || kk > 0) ? 1u : 0u;
+              if (p.is_int8)
+                umma_i8(d_base + r * BN, a_desc, b_desc, p.idesc, accum);
+              else
+                umma_f16(d_base + r * BN, a_desc, b_desc, p.idesc, accum);
+            }
           }
         }
         umma_commit(&empty_bar[stage]);  // stage reusable once these MMAs have read it
-        if (++stage == C::kStages) {
+        if (++stage == n_stages) {
           stage = 0;
           phase ^= 1;
         }
@@ -242,12 +294,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
     const int ew = warp - 4;             // TMEM lane quadrant
     const int row_in_tile = ew * 32 + lane;
     bool ok = true;
-    int it = 0;
-    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++it) {
-      int tr, tc, kb0, kb1, split;
-      decode(w, tr, tc, kb0, kb1, split);
-      const int acc = SWAP ? 0 : (it & 1);
-      const uint32_t acc_phase = SWAP ? (it & 1) : ((it >> 1) & 1);
+    int tr, tc, kb0, kb1;
+    for (int idx = 0; ok && get_work(idx, tr, tc, kb0, kb1); ++idx) {
+      const int acc = idx % C::kAccBufs;
+      const uint32_t acc_phase = (idx / C::kAccBufs) & 1;
       if (*abort_flag || !mbar_wait(&acc_full[acc], acc_phase)) {
         ok = false;
         break;
@@ -319,23 +369,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
         // thread = one weight row (output column); accumulator column j = activation row j
         const int64_t nrow0 = static_cast<int64_t>(tr) * kBM * C::R;  // first weight row of the tile
         const int m_cols = min(p.m, BN);
-        if (p.splits > 1) {
-          // 1) publish fp32 partials: workspace[split][j][weight_row]
+        const bool whole_tile = (kb0 == 0 && kb1 == p.k_blocks);
+        if (!whole_tile) {
+          // contributors of this tile are consecutive CTAs; this CTA's position among them
+          const int first_cta = cta_of(static_cast<int64_t>(tr) * p.k_blocks);
+          const int n_contrib = cta_of(static_cast<int64_t>(tr + 1) * p.k_blocks - 1) - first_cta + 1;
+          const int split = static_cast<int>(blockIdx.x) - first_cta;
+          constexpr int kTileRows = kBM * C::R;
+          float* ws_tile = p.workspace + static_cast<int64_t>(tr) * p.max_contrib * kTileRows * BN;
+          // 1) publish fp32 partials: ws_tile[contributor][row in tile][BN] (a thread's row is contiguous)
 #pragma unroll 1
           for (int r = 0; r < C::R; ++r) {
             const int64_t wrow = nrow0 + r * kBM + row_in_tile;
+            float* dst = ws_tile + (static_cast<int64_t>(split) * kTileRows + r * kBM + row_in_tile) * BN;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
               uint32_t v[16];
               tmem_ld_32x16(t_base + r * BN + c, v);
               tmem_ld_wait();
-              if (wrow < p.n) {
+              if (wrow < p.n && c < m_cols) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                  if (c + j < m_cols)
-                    p.workspace[(static_cast<int64_t>(split) * p.m + (c + j)) * p.n + wrow] =
-                        acc_to_float(v[j], p.is_int8);
-                }
+                for (int j = 0; j < 16; j += 4)
+                  *reinterpret_cast<float4*>(dst + c + j) =
+                      make_float4(acc_to_float(v[j], p.is_int8), acc_to_float(v[j + 1], p.is_int8),
+                                  acc_to_float(v[j + 2], p.is_int8), acc_to_float(v[j + 3], p.is_int8));
               }
             }
           }
@@ -344,46 +401,81 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
           if (row_in_tile == 0) {
             const int t = atomicAdd(&p.counters[tr], 1);
             *ticket_slot = t;
-            if (t == p.splits - 1) p.counters[tr] = 0;  // self-reset for the next launch
+            if (t == n_contrib - 1) p.counters[tr] = 0;  // self-reset for the next launch
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
-          const bool last = (*ticket_slot == p.splits - 1);
+          const bool last = (*ticket_slot == n_contrib - 1);
           asm volatile("bar.sync 1, 128;" ::: "memory");
           if (last) {
             __threadfence();
-            const int64_t wrow = nrow0 + row_in_tile;
-            if (wrow < p.n) {
-              for (int j = 0; j < m_cols; ++j) {
-                float x = 0.f, u = 0.f;
-                for (int s = 0; s < p.splits; ++s) {
-                  const float* ws = p.workspace + (static_cast<int64_t>(s) * p.m + j) * p.n;
-                  x += __ldcg(ws + wrow);
-                  if constexpr (SWIGLU) u += __ldcg(ws + wrow + kBM);
+            // sum of the contributions, in contributor order, for 16 batch columns of one weight
+            // row; four contributions (16 independent 16-byte loads) are in flight at a time
+            auto reduce16 = [&](int row_in_super_tile, int c0, float (&acc)[16]) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+              for (int s0 = 0; s0 < n_contrib; s0 += 4) {
+                float4 v[4][4];
+#pragma unroll
+                for (int ss = 0; ss < 4; ++ss) {
+                  const float* src = ws_tile + (static_cast<int64_t>(min(s0 + ss, n_contrib - 1)) * kTileRows + row_in_super_tile) * BN + c0;
+#pragma unroll
+                  for (int q4 = 0; q4 < 4; ++q4) v[ss][q4] = __ldcg(reinterpret_cast<const float4*>(src) + q4);
                 }
-                int64_t ocol;
-                if constexpr (SWIGLU) {
-                  if (p.is_int8) {
-                    x *= p.a_scale[j] * p.b_scale[wrow];
-                    u *= p.a_scale[j] * p.b_scale[wrow + kBM];
+#pragma unroll
+                for (int ss = 0; ss < 4; ++ss) {
+                  if (s0 + ss < n_contrib) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                      acc[4 * q4 + 0] += v[ss][q4].x;
+                      acc[4 * q4 + 1] += v[ss][q4].y;
+                      acc[4 * q4 + 2] += v[ss][q4].z;
+                      acc[4 * q4 + 3] += v[ss][q4].w;
+                    }
                   }
-                  x = silu_f(x) * u;
-                  ocol = static_cast<int64_t>(tr) * kBM + row_in_tile;
-                } else {
-                  if (p.is_int8) x *= p.a_scale[j] * p.b_scale[wrow];
-                  if (p.bias != nullptr) x += load_out1(p.bias, wrow, p.out_f16);
-                  if (p.residual != nullptr) x += load_out1(p.residual, j * p.ld_res + wrow, p.out_f16);
-                  ocol = wrow;
                 }
-                store_out1(p.out, j * p.ldc + ocol, x, p.out_f16);
+              }
+            };
+#pragma unroll 1
+            for (int sub = 0; sub < C::kSub; ++sub) {
+              const int64_t wrow = nrow0 + sub * kBM + row_in_tile;
+              if (wrow >= p.n) continue;
+              for (int c0 = 0; c0 < m_cols; c0 += 16) {
+                float x[16], u[16];
+                reduce16(sub * kBM + row_in_tile, c0, x);
+                if constexpr (SWIGLU) reduce16(kBM + row_in_tile, c0, u);
+#pragma unroll
+                for (int jj = 0; jj < 16; ++jj) {
+                  const int j = c0 + jj;
+                  if (j >= m_cols) break;
+                  float xv = x[jj];
+                  int64_t ocol;
+                  if constexpr (SWIGLU) {
+                    float uv = u[jj];
+                    if (p.is_int8) {
+                      xv *= p.a_scale[j] * p.b_scale[wrow];
+                      uv *= p.a_scale[j] * p.b_scale[wrow + kBM];
+                    }
+                    xv = silu_f(xv) * uv;
+                    ocol = static_cast<int64_t>(tr) * kBM + row_in_tile;
+                  } else {
+                    if (p.is_int8) xv *= p.a_scale[j] * p.b_scale[wrow];
+                    if (p.bias != nullptr) xv += load_out1(p.bias, wrow, p.out_f16);
+                    if (p.residual != nullptr) xv += load_out1(p.residual, j * p.ld_res + wrow, p.out_f16);
+                    ocol = wrow;
+                  }
+                  store_out1(p.out, j * p.ldc + ocol, xv, p.out_f16);
+                }
               }
             }
           }
         } else {
-          const int64_t wrow = nrow0 + row_in_tile;
+#pragma unroll 1
+          for (int sub = 0; sub < C::kSub; ++sub) {
+          const int64_t wrow = nrow0 + sub * kBM + row_in_tile;
 #pragma unroll 1
           for (int c = 0; c < BN; c += 16) {
             uint32_t v0[16], v1[16];
-            tmem_ld_32x16(t_base + c, v0);
+            tmem_ld_32x16(t_base + sub * BN + c, v0);
             if constexpr (SWIGLU) tmem_ld_32x16(t_base + BN + c, v1);
             tmem_ld_wait();
             if (wrow >= p.n) continue;
@@ -410,6 +502,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
               store_out1(p.out, mi * p.ldc + ocol, x, p.out_f16);
             }
           }
+          }
         }
       }
       tc_fence_before_sync();
@@ -421,6 +514,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
     }
   }
 
+  pdl_launch_dependents();  // this CTA's work is done: the next kernel may start its set-up
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag) {
@@ -455,6 +549,18 @@ EncodeFn get_encode_fn() {
   return fn;
 }
 
+int env_int(const char* name, int dflt) {
+  const char* v = std::getenv(name);
+  return (v != nullptr && *v != 0) ? std::atoi(v) : dflt;
+}
+
+CUtensorMapL2promotion l2_promotion() {
+  static const int v = env_int("MLLM_B200_GEMM_L2_PROMO", 256);
+  return v == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+                : (v == 64 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+                           : (v == 128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
+}
+
 // 2-D row-major matrix [rows, k] (k contiguous, `ld` elements between rows); box = 128 bytes of k x box_rows.
 bool make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int64_t ld, int elem_bytes,
                       CUtensorMapDataType type, int box_rows) {
@@ -465,45 +571,30 @@ bool make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t 
   cuuint32_t box[2] = {static_cast<cuuint32_t>(kRowBytes / elem_bytes), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, type, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_SWIZZLE_128B, l2_promotion(),
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
-template <int BN, bool SWAP, bool SWIGLU>
-int launch_cfg(const CUtensorMap& tr, const CUtensorMap& tc, const KParams& p, int grid, cudaStream_t s) {
-  using C = Cfg<BN, SWAP, SWIGLU>;
-  auto kern = gemm_tcgen05_kernel<BN, SWAP, SWIGLU>;
+template <int BN, bool SWAP, bool SWIGLU, int RT = 1, int KD = 1>
+int launch_cfg(const CUtensorMap& tr, const CUtensorMap& tc, KParams p, int grid, cudaStream_t s) {
+  using C = Cfg<BN, SWAP, SWIGLU, RT, KD>;
+  // tuning knob: MLLM_B200_GEMM_STAGES caps the ring depth of the small-batch tiling
+  static const int stage_cap = env_int("MLLM_B200_GEMM_STAGES", 0);
+  p.stages = C::kStages;
+  if (SWAP && stage_cap >= 2 && stage_cap < p.stages) p.stages = stage_cap;
+  auto kern = gemm_tcgen05_kernel<BN, SWAP, SWIGLU, RT, KD>;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(C::kSmemBytes)) !=
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(static_cast<size_t>(C::kStages) * C::kStageBytes + 1024 + 512)) !=
         cudaSuccess)
       return -3;
     attr_set = true;
   }
-  kern<<<grid, kThreads, C::kSmemBytes, s>>>(tr, tc, p);
+  const size_t smem = static_cast<size_t>(p.stages) * C::kStageBytes + 1024 + 512;
+  const cudaError_t err = launch_pdl(kern, dim3(grid), dim3(kThreads), smem, s, tr, tc, p);
   note_launch();
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
-}
-
-int pick_splits(int tiles, int k_blocks, int m, int n, int num_sms, size_t ws_bytes) {
-  if (tiles >= num_sms) return 1;
-  int best = 1;
-  double best_eff = 0.0;
-  const int max_s = std::max(1, std::min(16, k_blocks / 4));
-  for (int s = 1; s <= max_s; ++s) {
-    if (s > 1 && static_cast<size_t>(s) * m * n * sizeof(float) > ws_bytes) break;
-    const int work = tiles * s;
-    const int waves = (work + num_sms - 1) / num_sms;
-    // time model: waves * (k per split) plus a fixed per-CTA cost of ~3 k-blocks
-    const double kper = (k_blocks + s - 1) / s + 3.0;
-    const double eff = 1.0 / (waves * kper);
-    if (eff > best_eff * 1.02) {
-      best_eff = eff;
-      best = s;
-    }
-  }
-  return best;
+  return err == cudaSuccess ? 0 : -4;
 }
 
 }  // namespace
@@ -537,8 +628,7 @@ int launch_gemm(const GemmArgs& a, cudaStream_t s) {
   p.ld_res = a.ld_res;
   p.out_f16 = (a.dt == kF16) ? 1 : 0;
   p.is_int8 = a.is_int8;
-  p.splits = 1;
-  p.kb_per_split = p.k_blocks;
+  p.max_contrib = 1;
 
   const CUtensorMapDataType type =
       a.is_int8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
@@ -569,30 +659,71 @@ int launch_gemm(const GemmArgs& a, cudaStream_t s) {
   // ---- swap tiling: weights are the 128-row operand, the batch is MMA N ----
   int bn = 16;
   while (bn < a.m) bn <<= 1;
-  const int r = a.swiglu ? 2 : 1;
+  // stage shape: two 128-row weight tiles and two K atoms per stage when the batch is small enough
+  // for the stage to fit several times into shared memory (tuning knobs override)
+  static const int rt_knob = env_int("MLLM_B200_GEMM_RT", 0);
+  static const int kd_knob = env_int("MLLM_B200_GEMM_KD", 0);
+  int rt = a.swiglu ? 2 : 1;
+  int kd = (bn <= 64 && a.k >= 1024) ? 2 : 1;
+  if (bn <= 64) {
+    if (rt_knob == 1 && !a.swiglu) rt = 1;
+    if (rt_knob == 2) rt = 2;
+    if (kd_knob == 1 || kd_knob == 2) kd = kd_knob;
+  }
+  const int r = rt;
+  const int k_per_stage = kd * k_per_block;
+  p.k_blocks = (a.k + k_per_stage - 1) / k_per_stage;
   p.tiles_r = (a.n + kBM * r - 1) / (kBM * r);
   p.tiles_c = 1;
   p.idesc = umma_idesc(kBM, bn, c_fmt, ab_fmt, ab_fmt);
-  if (a.workspace != nullptr && a.counters != nullptr && p.tiles_r <= a.num_counters) {
-    p.splits = pick_splits(p.tiles_r, p.k_blocks, a.m, a.n, num_sms, a.workspace_bytes);
-    p.kb_per_split = (p.k_blocks + p.splits - 1) / p.splits;
-    p.splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
-  }
   if (!make_operand_map(&tm_row, a.b, a.n, a.k, a.ldb, eb, type, kBM * r)) return -2;
   if (!make_operand_map(&tm_col, a.a, a.m, a.k, a.lda, eb, type, bn)) return -2;
-  const int grid = p.tiles_r * p.splits;
-#define MB200_SWAP_CASE(BNV)                                                            \
-  case BNV:                                                                             \
-    return a.swiglu ? launch_cfg<BNV, true, true>(tm_row, tm_col, p, grid, s)           \
-                    : launch_cfg<BNV, true, false>(tm_row, tm_col, p, grid, s);
-  switch (bn) {
-    MB200_SWAP_CASE(16)
-    MB200_SWAP_CASE(32)
-    MB200_SWAP_CASE(64)
-    MB200_SWAP_CASE(128)
-    MB200_SWAP_CASE(256)
+  // stream-K: one equal range of (tile, k-block) iterations per CTA, at least kMinBytes of weights each
+  // so the fixed cost of a CTA stays small against its stream; fall back to whole tiles when there is
+  // no room for the partial sums.
+  const int64_t iters = static_cast<int64_t>(p.tiles_r) * p.k_blocks;
+  const int64_t stage_weight_bytes = static_cast<int64_t>(kd) * kBM * r * kRowBytes;
+  const int64_t min_iters = std::max<int64_t>(1, (128 * 1024) / stage_weight_bytes);
+  static const int ctas_per_sm = std::max(1, env_int("MLLM_B200_GEMM_CTAS_PER_SM", 1));
+  int grid = static_cast<int>(std::min<int64_t>(static_cast<int64_t>(num_sms) * ctas_per_sm,
+                                                std::max<int64_t>(1, iters / min_iters)));
+  const bool can_share = a.workspace != nullptr && a.counters != nullptr && p.tiles_r <= a.num_counters;
+  auto contributors = [&](int g) {
+    const int64_t per = std::max<int64_t>(1, iters / g);
+    return static_cast<int>((p.k_blocks + per - 1) / per) + 1;
+  };
+  auto ws_need = [&](int g) {
+    return static_cast<size_t>(p.tiles_r) * contributors(g) * kBM * r * bn * sizeof(float);
+  };
+  p.whole_tiles = 0;
+  if (!can_share || ws_need(grid) > a.workspace_bytes) {
+    grid = std::min(grid, p.tiles_r);  // every CTA gets whole tiles: nothing is shared
+    p.whole_tiles = 1;
   }
-#undef MB200_SWAP_CASE
+  p.max_contrib = contributors(grid);
+#define MB200_SWAP_SMALL(BNV)                                                                       \
+  case BNV:                                                                                         \
+    if (a.swiglu)                                                                                   \
+      return kd == 2 ? launch_cfg<BNV, true, true, 2, 2>(tm_row, tm_col, p, grid, s)                \
+                     : launch_cfg<BNV, true, true, 2, 1>(tm_row, tm_col, p, grid, s);               \
+    if (rt == 2)                                                                                    \
+      return kd == 2 ? launch_cfg<BNV, true, false, 2, 2>(tm_row, tm_col, p, grid, s)               \
+                     : launch_cfg<BNV, true, false, 2, 1>(tm_row, tm_col, p, grid, s);              \
+    return kd == 2 ? launch_cfg<BNV, true, false, 1, 2>(tm_row, tm_col, p, grid, s)                 \
+                   : launch_cfg<BNV, true, false, 1, 1>(tm_row, tm_col, p, grid, s);
+#define MB200_SWAP_LARGE(BNV)                                                                       \
+  case BNV:                                                                                         \
+    return a.swiglu ? launch_cfg<BNV, true, true, 2, 1>(tm_row, tm_col, p, grid, s)                 \
+                    : launch_cfg<BNV, true, false, 1, 1>(tm_row, tm_col, p, grid, s);
+  switch (bn) {
+    MB200_SWAP_SMALL(16)
+    MB200_SWAP_SMALL(32)
+    MB200_SWAP_SMALL(64)
+    MB200_SWAP_LARGE(128)
+    MB200_SWAP_LARGE(256)
+  }
+#undef MB200_SWAP_SMALL
+#undef MB200_SWAP_LARGE
   return -1;
 }
 

@@ -78,11 +78,11 @@ def test_no_alloc_rejects_oversize_and_bad_arguments():
     lib, fn = _lib()
     q, kc, vc, rtt, req, seq = _case([50], 8, 1, 0)
     out = torch.empty_like(q)
-    # 64 requests x 128 heads on one KV head with a 1M-token bound -> 5 splits x 129 floats each = 5.3M floats,
+    # 16 requests x 128 heads on one KV head with a 1M-token bound -> 8 or more splits x 129 floats each (> 2.1M floats),
     # beyond the 2M-float (8 MiB) array: refused before any launch
     stream = torch.cuda.current_stream().cuda_stream
     rc = fn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), rtt.data_ptr(), req.data_ptr(), seq.data_ptr(), out.data_ptr(),
-            64, 128, 1, D, q.stride(0), rtt.stride(0), kc.shape[0], 1 << 20, 1.0, 0, stream)
+            16, 128, 1, D, q.stride(0), rtt.stride(0), kc.shape[0], 1 << 20, 1.0, 0, stream)
     assert rc == 2 and b"scratch" in lib.mllm_b200_noalloc_last_error()
     rc = fn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), rtt.data_ptr(), req.data_ptr(), seq.data_ptr(), out.data_ptr(),
             1, 8, 1, 64, q.stride(0), rtt.stride(0), kc.shape[0], 50, 1.0, 0, stream)
