@@ -414,26 +414,35 @@ __device__ __forceinline__ float m_used_at(const float (&m)[N], int idx) {
 // the GQA group are the N dimension:
 //   S^T[tok, q] = K[tok, d] Q^T          (A = K tile, K-major; B = Q, K-major)
 //   O^T[d, q]  += V^T[d, tok] P^T[tok, q] (A = V tile as gathered, used MN-major; B = P^T, K-major)
-// A thread owns one token for the softmax (only the per-head maximum crosses threads, once per
-// tile; the row sums stay per-thread until the end) and one feature d for the output, so the
-// final store is coalesced.  K/V tiles of 128 tokens go through a three-deep cp.async ring: two
-// tiles (128 KB) are in flight while one is being consumed, which is what keeps HBM busy with a
-// single resident CTA per SM.
+// A softmax thread owns one token (only the per-head maximum crosses threads, once per tile; the
+// row sums stay per-thread until the end) and one feature d of the output, so the final store is
+// coalesced.  The CTA is warp-specialised and coupled by mbarriers only:
+//   warps 0-3  softmax: tcgen05.ld S^T, running max, exponentials, P^T to shared memory
+//   warps 4-7  gather:  slot-table reads and cp.async of K and V tiles into two three-deep rings
+//                       (tile t+2 and t+1 in flight while t is consumed: >= 128 KB per SM)
+//   warp  8    one thread issues the MMAs: S^T of tile t is queued before P*V of tile t-1, so the
+//              tensor-core and barrier latency of S^T hides behind the softmax of the tile before
 // ---------------------------------------------------------------------------------------------
 constexpr int kDT = 128;                       // tokens per decode tile
 constexpr int kDecHalf = kDT * 128;            // bytes of one 64-feature half of a K or V tile
 constexpr int kDecTileBytes = 2 * kDecHalf;    // 32 KB per tensor
 constexpr int kDecBufs = 3;
+constexpr int kDecThreads = 288;
 
 template <int NQ>
 struct DecCfg {
   static constexpr int kQBytes = 2 * NQ * 128;   // Q^T operand: two halves of NQ rows x 128 B
   static constexpr int kPBytes = 2 * NQ * 128;   // P^T operand: two halves (64 tokens each)
-  static constexpr int kSmem = kDecBufs * 2 * kDecTileBytes + kQBytes + kPBytes + 1024 + 64 + 4 * NQ * 4 + 2 * NQ * 4;
+  static constexpr int kSmem = kDecBufs * 2 * kDecTileBytes + kQBytes + kPBytes + 1024 + 256 + 9 * NQ * 4;
 };
 
+__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
+  // the barrier gets one arrival once all cp.async issued so far by this thread have landed
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 template <int NQ>
-__global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kDecThreads, 1) attn_decode_kernel(const AttnParams p) {
   using C = DecCfg<NQ>;
   pdl_wait();
   extern __shared__ uint8_t smem_raw[];
@@ -443,11 +452,18 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const Attn
   uint8_t* sQ = sV + kDecBufs * kDecTileBytes;
   uint8_t* sP = sQ + C::kQBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + C::kPBytes);
-  uint64_t* bar_s = bars;                               // two: S^T buffers alternate between tiles
-  uint64_t* bar_o = bars + 2;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 3);
-  float* red = reinterpret_cast<float*>(bars + 4);      // [4 warps][NQ]
-  float* red2 = red + 4 * NQ;                           // [NQ] totals
+  uint64_t* k_full = bars;            // [3] 128 gather threads
+  uint64_t* k_empty = bars + 3;       // [3] tcgen05.commit
+  uint64_t* v_full = bars + 6;        // [3]
+  uint64_t* v_empty = bars + 9;       // [3]
+  uint64_t* s_full = bars + 12;       // [2] tcgen05.commit
+  uint64_t* s_empty = bars + 14;      // [2] 128 softmax threads
+  uint64_t* p_full = bars + 16;       // 128 softmax threads
+  uint64_t* p_empty = bars + 17;      // tcgen05.commit (P*V of the tile finished)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 18);
+  int* fail_flag = reinterpret_cast<int*>(bars + 19);
+  float* red = reinterpret_cast<float*>(bars + 20);     // [2][4 warps][NQ] tile maxima, double buffered
+  float* red2 = red + 8 * NQ;                           // [NQ] totals
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -465,7 +481,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const Attn
 
   if (kv_begin >= kv_end) {
     if (p.num_splits > 1) {
-      for (int i = tid; i < g * kD; i += kAttnThreads) {
+      for (int i = tid; i < g * kD; i += kDecThreads) {
         const int head = hk * g + i / kD;
         p.part_o[((static_cast<int64_t>(b) * p.hq + head) * p.num_splits + split) * kD + (i % kD)] = 0.f;
       }
@@ -476,13 +492,26 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const Attn
   const int n_tiles = (kv_end - kv_begin + kDT - 1) / kDT;
 
   if (tid == 0) {
-    mbar_init(&bar_s[0], 1);
-    mbar_init(&bar_s[1], 1);
-    mbar_init(bar_o, 1);
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(&k_full[i], 128);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 128);
+      mbar_init(&v_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 128);
+    }
+    mbar_init(p_full, 128);
+    mbar_init(p_empty, 1);
+    *fail_flag = 0;
     fence_barrier_init();
   }
+  // rows of P^T beyond the group are never written again: clear them once
+  for (int i = tid; i < C::kPBytes / 16; i += kDecThreads) reinterpret_cast<uint4*>(sP)[i] = make_uint4(0, 0, 0, 0);
+  fence_proxy_async_smem();
   __syncthreads();
-  if (warp == 0) {
+  if (warp == 8) {
     tmem_alloc(tmem_holder, 128);
     tmem_relinquish();
   }
@@ -492,223 +521,231 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const Attn
   const uint32_t tmem_base = *tmem_holder;
   const uint32_t tmem_s = tmem_base;            // two buffers of NQ columns
   const uint32_t tmem_o = tmem_base + 2 * NQ;   // NQ columns
-  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
 
-  const uint16_t* qbase = static_cast<const uint16_t*>(p.q);
-  const uint16_t* kbase = static_cast<const uint16_t*>(p.k_cache);
-  const uint16_t* vbase = static_cast<const uint16_t*>(p.v_cache);
-  const int* rtt = p.req_to_token + static_cast<int64_t>(req) * p.rtt_stride;
-
-  // Q^T operand: NQ rows (query heads, zero beyond the group) x 16 chunks
-  {
-    const uint32_t sq = smem_u32(sQ);
-    for (int c = tid; c < NQ * 16; c += kAttnThreads) {
-      const int r = c >> 4, ch = c & 15;
-      const bool ok = r < g;
-      const uint16_t* src = qbase + static_cast<int64_t>(b) * p.q_stride + static_cast<int64_t>(hk * g + (ok ? r : 0)) * kD + ch * 8;
-      cp_async16(sq + swz_off(r, ch, NQ * 128), src, ok);
+  if (warp >= 4 && warp < 8) {
+    // =============================== gather warps ===============================
+    const int pt = tid - 128;
+    const uint16_t* qbase = static_cast<const uint16_t*>(p.q);
+    const uint16_t* kbase = static_cast<const uint16_t*>(p.k_cache);
+    const uint16_t* vbase = static_cast<const uint16_t*>(p.v_cache);
+    const int* rtt = p.req_to_token + static_cast<int64_t>(req) * p.rtt_stride;
+    const int ch = pt & 15;
+    {  // Q^T operand: NQ rows (query heads, zero beyond the group) x 16 chunks; lands with K tile 0
+      const uint32_t sq = smem_u32(sQ);
+      for (int c = pt; c < NQ * 16; c += 128) {
+        const int r = c >> 4, qc = c & 15;
+        const bool ok = r < g;
+        const uint16_t* src = qbase + static_cast<int64_t>(b) * p.q_stride +
+                              static_cast<int64_t>(hk * g + (ok ? r : 0)) * kD + qc * 8;
+        cp_async16(sq + swz_off(r, qc, NQ * 128), src, ok);
+      }
     }
-  }
-
-  // gather one 128-token tile of K or of V: thread handles chunk (tid & 15) of tokens (tid >> 4) + 8 i.
-  // Always commits one cp.async group (possibly empty) so that group counting stays uniform.
-  auto gather = [&](int tile, const uint16_t* base, uint8_t* ring) {
-    if (tile < n_tiles) {
-      const uint32_t dst = smem_u32(ring + (tile % kDecBufs) * kDecTileBytes);
-      const int ch = tid & 15;
+    auto load_slots = [&](int tile, int (&slots)[16]) {
       const int t0 = kv_begin + tile * kDT;
-      // all 16 table reads are issued before any of them is checked, so they overlap
-      int slots[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const int t = t0 + (tid >> 4) + 8 * i;
-        slots[i] = (t < kv_end) ? __ldg(rtt + t) : -1;
+        const int t = t0 + (pt >> 4) + 8 * i;
+        slots[i] = (tile < n_tiles && t < kv_end) ? __ldg(rtt + t) : -1;
       }
-      bool bad = false;
+    };
+    int slots[16], next[16];
+    load_slots(0, slots);
+    bool ok_all = true, bad = false;
+    for (int t = 0; t < n_tiles && ok_all; ++t) {
+      const int sl = t % kDecBufs;
+      const uint32_t ph = (t / kDecBufs) & 1;
+      load_slots(t + 1, next);  // consumed one tile from now: never waited for
+      int64_t off[16];
+      uint32_t so[16];
+      bool okv[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        if (slots[i] < -1 || slots[i] >= p.num_slots) {
+        int s_id = slots[i];
+        if (s_id < -1 || s_id >= p.num_slots) {
           bad = true;
-          slots[i] = -1;
+          s_id = -1;
         }
+        okv[i] = s_id >= 0;
+        off[i] = (static_cast<int64_t>(okv[i] ? s_id : 0) * p.hkv + hk) * kD + ch * 8;
+        so[i] = swz_off((pt >> 4) + 8 * i, ch, kDecHalf);
       }
-      if (bad && p.status != nullptr) atomicExch(p.status, kStatusBadIndex);
+      if (!mbar_wait(&k_empty[sl], ph ^ 1)) ok_all = false;
+      const uint32_t dk = smem_u32(sK + sl * kDecTileBytes);
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const int r = (tid >> 4) + 8 * i;
-        const bool ok = slots[i] >= 0;
-        const int64_t off = (static_cast<int64_t>(ok ? slots[i] : 0) * p.hkv + hk) * kD + ch * 8;
-        cp_async16(dst + swz_off(r, ch, kDecHalf), base + off, ok);
+      for (int i = 0; i < 16; ++i) cp_async16(dk + so[i], kbase + off[i], okv[i]);
+      cp_async_arrive_noinc(&k_full[sl]);
+      if (!mbar_wait(&v_empty[sl], ph ^ 1)) ok_all = false;
+      const uint32_t dv = smem_u32(sV + sl * kDecTileBytes);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) cp_async16(dv + so[i], vbase + off[i], okv[i]);
+      cp_async_arrive_noinc(&v_full[sl]);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) slots[i] = next[i];
+    }
+    cp_async_wait<0>();
+    if (bad && p.status != nullptr) atomicExch(p.status, kStatusBadIndex);
+    if (!ok_all) *fail_flag = 1;
+  } else if (warp == 8) {
+    // =============================== MMA issuer ===============================
+    if (lane == 0) {
+      bool ok_all = true;
+      auto issue_pv = [&](int u) {
+        const int sl = u % kDecBufs;
+        if (!mbar_wait(&v_full[sl], (u / kDecBufs) & 1)) ok_all = false;
+        if (!mbar_wait(p_full, u & 1)) ok_all = false;
+        fence_proxy_async_smem();
+        tc_fence_after_sync();
+        const uint32_t va = smem_u32(sV + sl * kDecTileBytes);
+        const uint32_t pa = smem_u32(sP);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t a_desc = umma_desc_mn_sw128(va + kk * 2048, kDecHalf, 1024);
+          const uint64_t b_desc = umma_desc_k_sw128(pa + (kk >> 2) * (NQ * 128) + (kk & 3) * 32);
+          umma_f16(tmem_o, a_desc, b_desc, p.idesc_o, (u > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&v_empty[sl]);
+        umma_commit(p_empty);
+      };
+      for (int t = 0; t < n_tiles && ok_all; ++t) {
+        const int sl = t % kDecBufs;
+        if (!mbar_wait(&k_full[sl], (t / kDecBufs) & 1)) ok_all = false;
+        if (!mbar_wait(&s_empty[t & 1], ((t >> 1) & 1) ^ 1)) ok_all = false;
+        fence_proxy_async_smem();
+        tc_fence_after_sync();
+        const uint32_t ka = smem_u32(sK + sl * kDecTileBytes);
+        const uint32_t qa = smem_u32(sQ);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t a_desc = umma_desc_k_sw128(ka + (kk >> 2) * kDecHalf + (kk & 3) * 32);
+          const uint64_t b_desc = umma_desc_k_sw128(qa + (kk >> 2) * (NQ * 128) + (kk & 3) * 32);
+          umma_f16(tmem_s + (t & 1) * NQ, a_desc, b_desc, p.idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&k_empty[sl]);
+        umma_commit(&s_full[t & 1]);
+        if (t > 0 && ok_all) issue_pv(t - 1);
       }
+      if (ok_all) issue_pv(n_tiles - 1);
+      if (!ok_all) *fail_flag = 1;
     }
-    cp_async_commit();
-  };
-  auto issue_s = [&](int tile) {  // S^T of `tile` into its tensor-memory buffer; one thread
-    tc_fence_after_sync();
-    const uint32_t ka = smem_u32(sK + (tile % kDecBufs) * kDecTileBytes);
-    const uint32_t qa = smem_u32(sQ);
-#pragma unroll
-    for (int kk = 0; kk < 8; ++kk) {
-      const uint64_t a_desc = umma_desc_k_sw128(ka + (kk >> 2) * kDecHalf + (kk & 3) * 32);
-      const uint64_t b_desc = umma_desc_k_sw128(qa + (kk >> 2) * (NQ * 128) + (kk & 3) * 32);
-      umma_f16(tmem_s + (tile & 1) * NQ, a_desc, b_desc, p.idesc_s, kk > 0 ? 1u : 0u);
-    }
-    umma_commit(&bar_s[tile & 1]);
-  };
-
-  // cp.async groups in issue order: [Q + K0] [V0] [K1] [V1] [K2] [V2], then per tile j: [K(j+3)] [V(j+2)]
-  gather(0, kbase, sK);
-  gather(0, vbase, sV);
-  gather(1, kbase, sK);
-  gather(1, vbase, sV);
-  gather(2, kbase, sK);
-  gather(2, vbase, sV);
-
-  float m_used[NQ];
-  float l_part[NQ];
-#pragma unroll
-  for (int c = 0; c < NQ; ++c) {
-    m_used[c] = 0.f;
-    l_part[c] = 0.f;
-  }
-  bool ok_all = true;
-
-  cp_async_wait<5>();  // Q + K0
-  fence_proxy_async_smem();
-  __syncthreads();
-  if (tid == 0) issue_s(0);
-
-  for (int j = 0; j < n_tiles; ++j) {
-    // ---- A: S^T of the next tile is issued before this tile's softmax, so its latency is hidden ----
-    if (j + 1 < n_tiles) {
-      cp_async_wait<3>();  // K(j+1) has landed
-      fence_proxy_async_smem();
-      tc_fence_before_sync();
-      __syncthreads();
-      if (tid == 0) issue_s(j + 1);
-    }
-    // ---- B: this thread's token of tile j ----
-    if (!mbar_wait(&bar_s[j & 1], (j >> 1) & 1)) ok_all = false;
-    tc_fence_after_sync();
-    gather(j + 3, kbase, sK);  // the K slot of tile j is free now
-    float sc[NQ];
-    {
-      uint32_t raw[16];
-#pragma unroll
-      for (int c0 = 0; c0 < NQ; c0 += 16) {
-        tmem_ld_32x16(tmem_s + (j & 1) * NQ + lane_base + c0, raw);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) sc[c0 + i] = __uint_as_float(raw[i]);
-      }
-    }
-    const bool tok_ok = (kv_begin + j * kDT + tid) < kv_end;
+  } else {
+    // =============================== softmax warps ===============================
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    float m_used[NQ];
+    float l_part[NQ];
 #pragma unroll
     for (int c = 0; c < NQ; ++c) {
-      sc[c] = tok_ok ? sc[c] * p.scale_log2 : -INFINITY;
-      if (c < g) {
-        const float wm = warp_max(sc[c]);
-        if (lane == 0) red[warp * NQ + c] = wm;
-      }
+      m_used[c] = 0.f;
+      l_part[c] = 0.f;
     }
-    // P*V of the previous tile must be done before its V slot, P^T and O^T are touched again
-    if (j > 0) {
-      if (!mbar_wait(bar_o, (j - 1) & 1)) ok_all = false;
+    bool ok_all = true;
+    for (int t = 0; t < n_tiles; ++t) {
+      if (!mbar_wait(&s_full[t & 1], (t >> 1) & 1)) ok_all = false;
       tc_fence_after_sync();
-      gather(j + 2, vbase, sV);
-    } else {
-      cp_async_commit();  // V2 went out with the prologue; keep the group count uniform
-    }
-    __syncthreads();
-    bool need = false;
-    float factor[NQ];
+      float sc[NQ];
+      {
+        uint32_t raw[16];
 #pragma unroll
-    for (int c = 0; c < NQ; ++c) {
-      factor[c] = 1.f;
-      if (c < g) {
-        const float mt = fmaxf(fmaxf(red[c], red[NQ + c]), fmaxf(red[2 * NQ + c], red[3 * NQ + c]));
-        if (j == 0) {
-          m_used[c] = mt;  // the first tile of a non-empty range always holds a visible token
-        } else if (mt > m_used[c] + kRescaleThreshold) {
-          factor[c] = fast_exp2(m_used[c] - mt);
-          m_used[c] = mt;
-          l_part[c] *= factor[c];
-          need = true;
+        for (int c0 = 0; c0 < NQ; c0 += 16) {
+          tmem_ld_32x16(tmem_s + (t & 1) * NQ + lane_base + c0, raw);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) sc[c0 + i] = __uint_as_float(raw[i]);
         }
       }
-    }
-    if (need) {  // uniform over the CTA: every thread sees the same maxima
-      uint32_t o[16];
-#pragma unroll
-      for (int c0 = 0; c0 < NQ; c0 += 16) {
-        tmem_ld_32x16(tmem_o + lane_base + c0, o);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor[c0 + i]);
-        tmem_st_32x16(tmem_o + lane_base + c0, o);
-      }
-      tmem_st_wait();
-    }
-    // P^T operand: row = query head, 128 tokens in two 64-token halves; this thread writes column tid
-    {
-      uint8_t* pbase = sP + (tid >> 6) * (NQ * 128);
-      const int tk = tid & 63;
+      tc_fence_before_sync();
+      mbar_arrive(&s_empty[t & 1]);  // the S^T buffer may be overwritten by tile t+2
+      const bool tok_ok = (kv_begin + t * kDT + tid) < kv_end;
+      float* redt = red + (t & 1) * 4 * NQ;
 #pragma unroll
       for (int c = 0; c < NQ; ++c) {
-        float pv = 0.f;
-        if (c < g) pv = fast_exp2(sc[c] - m_used[c]);
-        uint16_t bits;
-        float back;
-        if (p.out_f16) {
-          const __half ph = __float2half_rn(pv);
-          bits = *reinterpret_cast<const uint16_t*>(&ph);
-          back = __half2float(ph);
-        } else {
-          const __nv_bfloat16 pb = __float2bfloat16_rn(pv);
-          bits = *reinterpret_cast<const uint16_t*>(&pb);
-          back = __bfloat162float(pb);
+        if (c < g) {
+          sc[c] = tok_ok ? sc[c] * p.scale_log2 : -INFINITY;
+          const float wm = warp_max(sc[c]);
+          if (lane == 0) redt[warp * NQ + c] = wm;
         }
-        l_part[c] += back;
-        *reinterpret_cast<uint16_t*>(pbase + c * 128 + (((tk >> 3) ^ (c & 7)) << 4) + (tk & 7) * 2) = bits;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      bool need = false;
+      float factor[NQ];
+#pragma unroll
+      for (int c = 0; c < NQ; ++c) {
+        factor[c] = 1.f;
+        if (c < g) {
+          const float mt = fmaxf(fmaxf(redt[c], redt[NQ + c]), fmaxf(redt[2 * NQ + c], redt[3 * NQ + c]));
+          if (t == 0) {
+            m_used[c] = mt;  // the first tile of a non-empty range always holds a visible token
+          } else if (mt > m_used[c] + kRescaleThreshold) {
+            factor[c] = fast_exp2(m_used[c] - mt);
+            m_used[c] = mt;
+            l_part[c] *= factor[c];
+            need = true;
+          }
+        }
+      }
+      // P*V of the previous tile must be finished before P^T and O^T are touched again
+      if (t > 0) {
+        if (!mbar_wait(p_empty, (t - 1) & 1)) ok_all = false;
+        tc_fence_after_sync();
+      }
+      if (need) {  // uniform over the four warps: every thread sees the same maxima
+        uint32_t o[16];
+#pragma unroll
+        for (int c0 = 0; c0 < NQ; c0 += 16) {
+          tmem_ld_32x16(tmem_o + lane_base + c0, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor[c0 + i]);
+          tmem_st_32x16(tmem_o + lane_base + c0, o);
+        }
+        tmem_st_wait();
+      }
+      // P^T operand: row = query head, 128 tokens in two 64-token halves; this thread writes column tid
+      {
+        uint8_t* pbase = sP + (tid >> 6) * (NQ * 128);
+        const int tk = tid & 63;
+#pragma unroll
+        for (int c = 0; c < NQ; ++c) {
+          if (c < g) {
+            const float pv = fast_exp2(sc[c] - m_used[c]);
+            uint16_t bits;
+            float back;
+            if (p.out_f16) {
+              const __half ph = __float2half_rn(pv);
+              bits = *reinterpret_cast<const uint16_t*>(&ph);
+              back = __half2float(ph);
+            } else {
+              const __nv_bfloat16 pb = __float2bfloat16_rn(pv);
+              bits = *reinterpret_cast<const uint16_t*>(&pb);
+              back = __bfloat162float(pb);
+            }
+            l_part[c] += back;
+            *reinterpret_cast<uint16_t*>(pbase + c * 128 + (((tk >> 3) ^ (c & 7)) << 4) + (tk & 7) * 2) = bits;
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(p_full);
+    }
+    if (!mbar_wait(p_empty, (n_tiles - 1) & 1)) ok_all = false;
+    tc_fence_after_sync();
+    if (!ok_all) *fail_flag = 1;
+
+    // ---- totals of the row sums over the 128 token-threads ----
+    float* redt = red;
+#pragma unroll
+    for (int c = 0; c < NQ; ++c) {
+      if (c < g) {
+        const float ws = warp_sum(l_part[c]);
+        if (lane == 0) redt[warp * NQ + c] = ws;
       }
     }
-    cp_async_wait<4>();  // V(j) has landed
-    tc_fence_before_sync();
-    fence_proxy_async_smem();
-    __syncthreads();
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (tid < g) red2[tid] = redt[tid] + redt[NQ + tid] + redt[2 * NQ + tid] + redt[3 * NQ + tid];
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const bool good = ok_all && (*fail_flag == 0);
 
-    if (tid == 0) {
-      tc_fence_after_sync();
-      const uint32_t va = smem_u32(sV + (j % kDecBufs) * kDecTileBytes);
-      const uint32_t pa = smem_u32(sP);
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {
-        const uint64_t a_desc = umma_desc_mn_sw128(va + kk * 2048, kDecHalf, 1024);
-        const uint64_t b_desc = umma_desc_k_sw128(pa + (kk >> 2) * (NQ * 128) + (kk & 3) * 32);
-        umma_f16(tmem_o, a_desc, b_desc, p.idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-      }
-      umma_commit(bar_o);
-    }
-  }
-  cp_async_wait<0>();
-  if (!mbar_wait(bar_o, (n_tiles - 1) & 1)) ok_all = false;
-  tc_fence_after_sync();
-  if (!ok_all && p.status != nullptr) atomicExch(p.status, kStatusPipelineTimeout);
-
-  // ---- totals of the row sums over the 128 token-threads ----
-#pragma unroll
-  for (int c = 0; c < NQ; ++c) {
-    if (c < g) {
-      const float ws = warp_sum(l_part[c]);
-      if (lane == 0) red[warp * NQ + c] = ws;
-    }
-  }
-  __syncthreads();
-  if (tid < g) red2[tid] = red[tid] + red[NQ + tid] + red[2 * NQ + tid] + red[3 * NQ + tid];
-  __syncthreads();
-
-  // ---- output: this thread owns feature d = tid of every head of the group ----
-  {
+    // ---- output: this thread owns feature d = tid of every head of the group ----
     uint32_t o[16];
 #pragma unroll
     for (int c0 = 0; c0 < NQ; c0 += 16) {
@@ -717,7 +754,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const Attn
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const int c = c0 + i;
-        if (c < g && ok_all) {
+        if (c < g && good) {
           const float l = red2[c];
           const float v = l > 0.f ? __uint_as_float(o[i]) / l : 0.f;
           const int head = hk * g + c;
@@ -742,7 +779,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const Attn
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 0) {
+  if (*fail_flag && tid == 0 && p.status != nullptr) atomicExch(p.status, kStatusPipelineTimeout);
+  if (warp == 8) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 128);
   }
@@ -751,6 +789,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const Attn
 // combine decode partials: out[b, h, :] = sum_s w_s * O_s with w_s = 2^(lse_s - max) / sum
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                   void* __restrict__ out, int hq, int splits, int out_f16) {
+  pdl_launch_dependents();
   pdl_wait();
   const int b = blockIdx.y, h = blockIdx.x, d = threadIdx.x;
   const int64_t base = (static_cast<int64_t>(b) * hq + h) * splits;
@@ -800,7 +839,7 @@ int launch_decode_cfg(const AttnParams& p, dim3 grid, cudaStream_t s) {
       return -3;
     attr_set = true;
   }
-  launch_pdl(attn_decode_kernel<NQ>, grid, dim3(kAttnThreads), DecCfg<NQ>::kSmem, s, p);
+  launch_pdl(attn_decode_kernel<NQ>, grid, dim3(kDecThreads), DecCfg<NQ>::kSmem, s, p);
   note_launch();
   return 0;
 }

@@ -119,6 +119,7 @@ constexpr int kMaxVecPerThread = 4;  // row cache: hidden <= 4 * 8 * blockDim
 template <typename T, bool kAdd>
 __global__ void rmsnorm_kernel(T* __restrict__ x, T* __restrict__ residual, const T* __restrict__ w,
                                T* __restrict__ out, int hidden, int64_t x_stride, int64_t out_stride, float eps) {
+  pdl_launch_dependents();
   pdl_wait();
   __shared__ float red[33];
   const int row = blockIdx.x;
@@ -167,6 +168,7 @@ __global__ void rmsnorm_kernel(T* __restrict__ x, T* __restrict__ residual, cons
 template <typename T>
 __global__ void layernorm_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b,
                                  T* __restrict__ out, int hidden, float eps) {
+  pdl_launch_dependents();
   pdl_wait();
   __shared__ float red[33];
   const int row = blockIdx.x;
@@ -223,6 +225,7 @@ __device__ __forceinline__ float gelu_tanh_f(float v) {
 
 template <typename T, int kAct>
 __global__ void act_and_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int rows, int inter) {
+  pdl_launch_dependents();
   pdl_wait();
   const int vec_per_row = inter >> 3;
   const int64_t total = static_cast<int64_t>(rows) * vec_per_row;
@@ -242,6 +245,7 @@ __global__ void act_and_mul_kernel(const T* __restrict__ x, T* __restrict__ out,
 
 template <typename T>
 __global__ void gelu_tanh_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t nvec) {
+  pdl_launch_dependents();
   pdl_wait();
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -258,6 +262,7 @@ __global__ void gelu_tanh_kernel(const T* __restrict__ x, T* __restrict__ out, i
 // ---------------------------------------------------------------------------
 __global__ void embedding_kernel(const int64_t* __restrict__ ids, const uint4* __restrict__ table,
                                  uint4* __restrict__ out, int vec_per_row, int vocab, int* status) {
+  pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
   int64_t id = ids[t];
@@ -283,6 +288,7 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const T* __res
                                              const int64_t* __restrict__ cache_loc, T* __restrict__ k_cache,
                                              T* __restrict__ v_cache, int tokens, int hq, int hkv,
                                              int64_t qkv_stride, int64_t num_slots, float eps, int* status) {
+  pdl_launch_dependents();
   pdl_wait();
   constexpr int D = 128;
   const int heads = hq + 2 * hkv;
@@ -347,6 +353,7 @@ template <typename T>
 __global__ void kv_write_kernel(const T* __restrict__ k, const T* __restrict__ v, const int64_t* __restrict__ loc,
                                 T* __restrict__ k_cache, T* __restrict__ v_cache, int tokens, int row_elems,
                                 int64_t k_stride, int64_t v_stride, int64_t num_slots, int* status) {
+  pdl_launch_dependents();
   pdl_wait();
   const int vec = row_elems >> 3;
   const int64_t total = static_cast<int64_t>(tokens) * vec;
@@ -370,6 +377,7 @@ __global__ void kv_write_kernel(const T* __restrict__ k, const T* __restrict__ v
 template <typename T>
 __global__ void per_token_quant_int8_kernel(const T* __restrict__ x, int8_t* __restrict__ q,
                                             float* __restrict__ scale, int k) {
+  pdl_launch_dependents();
   pdl_wait();
   __shared__ float red[33];
   const int row = blockIdx.x;
@@ -424,6 +432,7 @@ __device__ __forceinline__ float load_as_float(const T* p) {
 
 template <typename T>
 __global__ void argmax_kernel(const T* __restrict__ logits, int64_t* __restrict__ out, int vocab, int64_t stride) {
+  pdl_launch_dependents();
   pdl_wait();
   __shared__ float sval[32];
   __shared__ int sidx[32];
