@@ -329,6 +329,26 @@ void attention_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
   TORCH_CHECK(rc == 0, "mllm_b200 attention_decode: unsupported configuration (code ", rc, ")");
 }
 
+// partial sums of every rank (peer pointers) -> residual += sum ; out = rmsnorm(residual) * weight
+void tp_reduce_add_rmsnorm(std::vector<int64_t> peer_data, std::vector<int64_t> peer_flags, Tensor& local_seq,
+                           const c10::optional<Tensor>& residual, const c10::optional<Tensor>& weight, Tensor& out,
+                           int64_t rank, int64_t row_stride, double eps) {
+  check_half(out, "out");
+  TORCH_CHECK(out.dim() == 2 && out.is_contiguous(), "out must be [rows, hidden] contiguous");
+  TORCH_CHECK(peer_data.size() == peer_flags.size() && !peer_data.empty() && peer_data.size() <= 8, "peer lists");
+  TORCH_CHECK(local_seq.scalar_type() == at::kInt && local_seq.numel() >= out.size(0), "local_seq int32 [>= rows]");
+  if (residual.has_value()) TORCH_CHECK(residual->is_contiguous() && residual->sizes() == out.sizes(), "residual");
+  c10::cuda::CUDAGuard g(out.device());
+  auto& st = device_state(out.get_device());
+  std::vector<uint64_t> d(peer_data.begin(), peer_data.end()), f(peer_flags.begin(), peer_flags.end());
+  const int rc = mb200::launch_tp_reduce_add_rmsnorm(
+      d.data(), f.data(), reinterpret_cast<uint32_t*>(local_seq.data_ptr<int>()),
+      residual.has_value() ? residual->data_ptr() : nullptr, weight.has_value() ? weight->data_ptr() : nullptr,
+      out.data_ptr(), out.size(0), out.size(1), static_cast<int>(d.size()), static_cast<int>(rank), row_stride,
+      static_cast<float>(eps), dtype_of(out), st.status.data_ptr<int>(), stream_of(out));
+  TORCH_CHECK(rc == 0, "mllm_b200 tp_reduce_add_rmsnorm: unsupported configuration (code ", rc, ")");
+}
+
 // Reads (and clears) the device status word; non-zero means a kernel gave up on a bounded wait
 // or met an out-of-range index. Synchronises the device.
 int64_t read_status(int64_t device) {
@@ -357,6 +377,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
   m.def("attention_prefill", &attention_prefill);
   m.def("attention_decode", &attention_decode);
+  m.def("tp_reduce_add_rmsnorm", &tp_reduce_add_rmsnorm);
   m.def("read_status", &read_status);
   m.def("launch_count", &launch_count);
 }

@@ -1,0 +1,179 @@
+// Tensor-parallel reduction fused with the residual add and RMSNorm, over NVLink peer memory.
+//
+// Every rank's row-parallel GEMM (o_proj / down_proj) leaves its partial sums in a buffer that all
+// ranks have mapped (symmetric memory).  This kernel replaces "all-reduce, then add + RMSNorm":
+// one CTA per token row signals the same-row CTA of every peer with a system-scope release
+// increment, waits (bounded) until all peers have signalled, then pulls the row's partials from
+// every rank with plain 16-byte peer loads, sums them in rank order in fp32 (so all ranks compute
+// bit-identical results), adds the residual, writes the new residual and the normalised row.
+// Flags are monotonically increasing counters and the expected value lives in device memory, so
+// the kernel is CUDA-graph safe: nothing changes between replays.  No multimem, no TMA: plain
+// ld/st/red on peer pointers only.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace mb200 {
+namespace {
+
+constexpr int kMaxTp = 8;
+
+struct PeerPtrs {
+  const void* data[kMaxTp];
+  uint32_t* flags[kMaxTp];
+};
+
+__device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+
+template <typename T>
+__device__ __forceinline__ void unpack8v(const uint4& raw, float (&f)[8]) {
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = to_f(e[i]);
+}
+template <typename T>
+__device__ __forceinline__ T from_f(float v);
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+template <>
+__device__ __forceinline__ __half from_f<__half>(float v) {
+  return __float2half_rn(v);
+}
+template <typename T>
+__device__ __forceinline__ uint4 pack8v(const float (&f)[8]) {
+  uint4 r;
+  T* e = reinterpret_cast<T*>(&r);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) e[i] = from_f<T>(f[i]);
+  return r;
+}
+
+constexpr int kVecPerThread = 4;
+
+// grid = rows, block = hidden / 8 threads (<= 1024), hidden <= 8 * 1024 * kVecPerThread
+template <typename T>
+__global__ void tp_reduce_add_rmsnorm_kernel(PeerPtrs peers, uint32_t* __restrict__ local_seq, T* __restrict__ residual,
+                                             const T* __restrict__ weight, T* __restrict__ out, int hidden, int tp,
+                                             int rank, int64_t row_stride, float eps, int* status) {
+  __shared__ float red[33];
+  __shared__ int wait_ok;
+  pdl_wait();
+  const int row = blockIdx.x;
+  if (threadIdx.x == 0) wait_ok = 1;
+  __syncthreads();
+  // 1) tell every rank (myself included) that my partial of this row is in place
+  if (threadIdx.x < tp) red_add_release_sys(peers.flags[threadIdx.x] + row * kMaxTp + rank, 1u);
+  // 2) wait for every rank's signal; the expected count advances by one per call
+  const uint32_t expect = local_seq[row] + 1u;
+  if (threadIdx.x < tp) {
+    if (!wait_flag_ge(peers.flags[rank] + row * kMaxTp + threadIdx.x, expect)) {
+      wait_ok = 0;
+      if (status != nullptr) atomicExch(status, kStatusPeerTimeout);
+    }
+  }
+  __syncthreads();
+  if (!wait_ok) {  // leave the outputs untouched; the host raises on the status word
+    if (threadIdx.x == 0) local_seq[row] = expect;
+    return;
+  }
+  // 3) pull, sum in rank order, add the residual
+  const int nvec = hidden >> 3;
+  float cache[kVecPerThread][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < kVecPerThread; ++it) {
+    const int v = threadIdx.x + it * blockDim.x;
+    if (v < nvec) {
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      for (int r = 0; r < tp; ++r) {
+        const uint4 raw = *(reinterpret_cast<const uint4*>(static_cast<const T*>(peers.data[r]) + row * row_stride) + v);
+        float f[8];
+        unpack8v<T>(raw, f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += f[i];
+      }
+      if (residual != nullptr) {
+        uint4* rp = reinterpret_cast<uint4*>(residual + static_cast<int64_t>(row) * hidden) + v;
+        float g[8];
+        unpack8v<T>(*rp, g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = to_f(from_f<T>(acc[i] + g[i]));
+        *rp = pack8v<T>(acc);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = to_f(from_f<T>(acc[i]));
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        cache[it][i] = acc[i];
+        ss += acc[i] * acc[i];
+      }
+    }
+  }
+  float rstd = 1.f;
+  if (weight != nullptr) {
+    ss = warp_sum(ss);
+    if (lane_id() == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      float t = threadIdx.x < ((blockDim.x + 31) >> 5) ? red[threadIdx.x] : 0.f;
+      t = warp_sum(t);
+      if (threadIdx.x == 0) red[32] = t;
+    }
+    __syncthreads();
+    rstd = rsqrtf(red[32] / static_cast<float>(hidden) + eps);
+  }
+#pragma unroll
+  for (int it = 0; it < kVecPerThread; ++it) {
+    const int v = threadIdx.x + it * blockDim.x;
+    if (v < nvec) {
+      float o[8];
+      if (weight != nullptr) {
+        float g[8];
+        unpack8v<T>(reinterpret_cast<const uint4*>(weight)[v], g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = cache[it][i] * rstd * g[i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = cache[it][i];
+      }
+      reinterpret_cast<uint4*>(out + static_cast<int64_t>(row) * hidden)[v] = pack8v<T>(o);
+    }
+  }
+  if (threadIdx.x == 0) local_seq[row] = expect;
+}
+
+}  // namespace
+
+int launch_tp_reduce_add_rmsnorm(const uint64_t* peer_data, const uint64_t* peer_flags, uint32_t* local_seq,
+                                 void* residual, const void* weight, void* out, int rows, int hidden, int tp, int rank,
+                                 int64_t row_stride, float eps, DType dt, int* status, cudaStream_t s) {
+  if (rows == 0) return 0;
+  if (tp < 1 || tp > kMaxTp || hidden % 8 != 0 || hidden > 8 * 1024 * kVecPerThread) return -1;
+  PeerPtrs pp{};
+  for (int r = 0; r < tp; ++r) {
+    pp.data[r] = reinterpret_cast<const void*>(peer_data[r]);
+    pp.flags[r] = reinterpret_cast<uint32_t*>(peer_flags[r]);
+  }
+  int threads = ((hidden >> 3) + 31) / 32 * 32;
+  if (threads > 1024) threads = 1024;
+  if (threads < 32) threads = 32;
+  cudaError_t err;
+  if (dt == kBF16) {
+    err = launch_pdl(tp_reduce_add_rmsnorm_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, s, pp, local_seq,
+                     static_cast<__nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(weight),
+                     static_cast<__nv_bfloat16*>(out), hidden, tp, rank, row_stride, eps, status);
+  } else {
+    err = launch_pdl(tp_reduce_add_rmsnorm_kernel<__half>, dim3(rows), dim3(threads), 0, s, pp, local_seq,
+                     static_cast<__half*>(residual), static_cast<const __half*>(weight), static_cast<__half*>(out),
+                     hidden, tp, rank, row_stride, eps, status);
+  }
+  note_launch();
+  return err == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace mb200

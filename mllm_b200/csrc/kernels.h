@@ -100,4 +100,12 @@ struct AttnArgs {
 int launch_attention(const AttnArgs& args, cudaStream_t s);
 int decode_num_splits(int batch, int hkv, int max_seq_len, int num_sms);
 
+// ----- tensor-parallel reduction + residual add + RMSNorm over peer memory ----------------
+// peer_data / peer_flags: host arrays of `tp` device addresses (every rank's partial-sum buffer
+// and flag block, mapped into this process).  flags: uint32 [max_rows][8] per rank, zero-initialised;
+// local_seq: uint32 [max_rows] on this device, zero-initialised.  weight may be null (plain sum).
+int launch_tp_reduce_add_rmsnorm(const uint64_t* peer_data, const uint64_t* peer_flags, uint32_t* local_seq,
+                                 void* residual, const void* weight, void* out, int rows, int hidden, int tp, int rank,
+                                 int64_t row_stride, float eps, DType dt, int* status, cudaStream_t s);
+
 }  // namespace mb200

@@ -146,9 +146,19 @@ class ModelRunner:
         self._pre_load_avail_gib = get_available_gpu_memory(self.device.type, self.gpu_id)
         self.load_model()
         self._extract_model_metadata()
+        self._init_tp_comm()
         self._configure_kv_cache_dtype()
         self.init_memory_pool()
         self.init_cuda_graphs()
+
+    def _init_tp_comm(self) -> None:
+        """Peer-mapped buffers for the fused tensor-parallel kernels (``comm_backend == "fused"``)."""
+        from ..parallel.symm import TPComm, set_tp_comm
+
+        set_tp_comm(None)
+        if pstate.get_tensor_model_parallel_world_size() > 1 and self.server_config.comm_backend == "fused":
+            rows = max(256, min(1024, self.server_config.max_running_requests or 1))
+            set_tp_comm(TPComm.create(self.hidden_size, self.dtype, self.device, max_rows=256 if rows <= 256 else rows))
 
     def _resolve_dtype(self) -> torch.dtype:
         want = self.server_config.dtype

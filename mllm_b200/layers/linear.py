@@ -128,6 +128,24 @@ class RowParallelLinear(LinearBase):
             loaded = loaded.reshape(-1)
         param.data.copy_(loaded.reshape(param.shape))
 
+    def forward_partial(self, x: torch.Tensor) -> torch.Tensor:
+        """This rank's partial sums, left for the following norm to reduce.  When peer-mapped buffers
+        exist and the batch fits, the GEMM writes straight into one of them."""
+        from ..parallel.symm import get_tp_comm
+
+        comm = get_tp_comm()
+        rows = x.numel() // x.shape[-1]
+        buf = comm.partial_buffer(rows) if (comm is not None and x.is_cuda and self.bias is None) else None
+        if buf is not None and isinstance(self.quant_method, UnquantizedLinearMethod):
+            from .. import ops
+
+            return ops.linear(x, self.weight, out=buf)
+        y = self.quant_method.apply(self, x, self.bias if self.tp_rank == 0 else None)
+        if buf is not None:
+            buf.copy_(y.reshape(buf.shape))
+            return buf
+        return y
+
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         if self.tp_size == 1 or not self.reduce_results:
             return self.quant_method.apply(self, x, self.bias, residual)

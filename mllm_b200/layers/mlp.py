@@ -14,7 +14,7 @@ from .linear import MergedLinear, RowParallelLinear
 
 class MLP(nn.Module):
     def __init__(self, hidden_size: int, intermediate_size: int, quant_config=None, prefix: str = "",
-                 params_dtype: Optional[torch.dtype] = None, reduce_results: bool = True) -> None:
+                 params_dtype: Optional[torch.dtype] = None, reduce_results: bool = False) -> None:
         super().__init__()
 
         def qm(name):
@@ -29,7 +29,10 @@ class MLP(nn.Module):
                                            reduce_results=reduce_results)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.down_proj(self.gate_up_proj.forward_swiglu(x))
+        h = self.gate_up_proj.forward_swiglu(x)
+        if self.down_proj.tp_size > 1 and not self.down_proj.reduce_results:
+            return self.down_proj.forward_partial(h)
+        return self.down_proj(h)
 
 
 ParallelMLP = MLP

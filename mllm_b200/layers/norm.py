@@ -18,10 +18,14 @@ class RMSNorm(nn.Module):
                                    requires_grad=False)
         self.eps = eps
 
-    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, partial: bool = False
                 ) -> Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]:
         """Without ``residual``: returns the normed tensor.  With it: in place ``residual += x`` and
-        ``x = norm(residual)``; returns ``(x, residual)``."""
+        ``x = norm(residual)``; returns ``(x, residual)``.  ``partial=True`` says ``x`` holds this
+        tensor-parallel rank's partial sums: the reduction over ranks is fused into the same step."""
+        if partial:
+            assert residual is not None
+            return ops.tp_reduce_add_rmsnorm(x, residual, self.weight, self.eps), residual
         if residual is None:
             return ops.rmsnorm(x, self.weight, self.eps)
         ops.fused_add_rmsnorm(x, residual, self.weight, self.eps)

@@ -83,7 +83,8 @@ class Qwen3Attention(nn.Module):
     def forward(self, x: torch.Tensor, forward_batch: ForwardBatch) -> torch.Tensor:
         qkv = self.qkv_proj(x)
         a = self.attn(qkv, self.q_norm.weight, self.k_norm.weight, forward_batch)
-        return self.o_proj(a)
+        # under tensor parallelism the partial sums go to the next norm, which reduces them
+        return self.o_proj.forward_partial(a) if self.o_proj.tp_size > 1 else self.o_proj(a)
 
 
 def _rope_theta(config) -> float:
@@ -113,10 +114,11 @@ class Qwen3DecoderLayer(nn.Module):
             residual = hidden
             hidden = self.input_layernorm(hidden)
         else:
-            hidden, residual = self.input_layernorm(hidden, residual)
+            hidden, residual = self.input_layernorm(hidden, residual, partial=self.self_attn.o_proj.tp_size > 1)
+        tp = self.self_attn.o_proj.tp_size > 1
         hidden = self.self_attn(hidden, forward_batch)
-        hidden, residual = self.post_attention_layernorm(hidden, residual)
-        hidden = self.mlp(hidden)
+        hidden, residual = self.post_attention_layernorm(hidden, residual, partial=tp)
+        hidden = self.mlp(hidden)  # partial sums again when tp > 1
         return hidden, residual
 
 
@@ -140,10 +142,13 @@ class Qwen3Model(nn.Module):
         for i, layer in enumerate(self.layers):
             hidden, residual = layer(hidden, residual, forward_batch)
             if deepstack_embeds is not None and i < len(deepstack_embeds):
-                hidden = hidden + deepstack_embeds[i]
+                # the MLP output is a partial sum under TP: inject on one rank only so it is counted once
+                if pstate.get_tensor_model_parallel_rank() == 0:
+                    hidden = hidden + deepstack_embeds[i]
         if residual is None:
             return self.norm(hidden)
-        hidden, _ = self.norm(hidden, residual)
+        tp = pstate.get_tensor_model_parallel_world_size() > 1
+        hidden, _ = self.norm(hidden, residual, partial=tp)
         return hidden
 
 

@@ -237,6 +237,38 @@ def kv_write(k, v, loc, k_cache, v_cache) -> None:
 
 
 # --------------------------------------------------------------------------
+# tensor-parallel reduction fused with residual add + RMSNorm
+# --------------------------------------------------------------------------
+def tp_reduce_add_rmsnorm(partial: torch.Tensor, residual: Optional[torch.Tensor], weight: Optional[torch.Tensor],
+                          eps: float) -> torch.Tensor:
+    """``residual += sum over TP ranks of partial`` (in place when given); returns
+    ``rmsnorm(residual) * weight`` (or the plain sum when ``weight`` is None).
+
+    On GPUs with peer-mapped buffers this is one kernel that pulls every rank's partial sums over
+    NVLink; otherwise it is the process group's all-reduce followed by the local add + norm."""
+    from ..parallel import state as pstate
+    from ..parallel.symm import get_tp_comm
+
+    comm = get_tp_comm()
+    slot = comm.slot_of(partial) if (comm is not None and use_kernels(partial)) else None
+    if slot is not None:
+        p2 = _2d(partial)
+        out = torch.empty((p2.shape[0], p2.shape[1]), dtype=partial.dtype, device=partial.device)
+        ext().tp_reduce_add_rmsnorm(slot.data_ptrs, slot.flag_ptrs, slot.seq,
+                                    None if residual is None else _2d(residual), weight, out, comm.rank,
+                                    slot.data.stride(0), eps)
+        return out.view(partial.shape)
+    total = pstate.tensor_model_parallel_all_reduce(partial.contiguous() if slot is None else partial.clone())
+    if residual is None:
+        return total if weight is None else rmsnorm(total, weight, eps)
+    if weight is None:
+        residual.add_(total)
+        return residual
+    fused_add_rmsnorm(total, residual, weight, eps)
+    return total
+
+
+# --------------------------------------------------------------------------
 # attention
 # --------------------------------------------------------------------------
 def attention_prefill(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, prefix_lens,

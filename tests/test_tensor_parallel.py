@@ -1,0 +1,39 @@
+"""Tensor parallelism: TP=2 gives the logits of TP=1 (gloo ranks on CPU; NCCL + fused peer-memory
+kernels on GPUs).  Every rank is a child process; a rank that fails ends the run by exit code."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _launch(world, out, device, dtype, port, extra_env=None):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE=str(world),
+               NCCL_NVLS_ENABLE="0", **(extra_env or {}))
+    procs = []
+    for r in range(world):
+        e = dict(env, RANK=str(r), LOCAL_RANK=str(r))
+        procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "tp_worker.py"), out, device, dtype], env=e))
+    codes = [p.wait(timeout=600) for p in procs]
+    assert codes == [0] * world, f"rank exit codes {codes}"
+    return torch.load(out)
+
+
+def test_tp2_matches_tp1_on_cpu(tmp_path):
+    one = _launch(1, str(tmp_path / "tp1.pt"), "cpu", "float32", 29611)
+    two = _launch(2, str(tmp_path / "tp2.pt"), "cpu", "float32", 29612)
+    torch.testing.assert_close(two, one, atol=2e-4, rtol=2e-4)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("graph", ["0", "1"])
+def test_tp2_matches_tp1_on_gpu(tmp_path, graph):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    one = _launch(1, str(tmp_path / "tp1.pt"), "cuda", "bfloat16", 29613)
+    two = _launch(2, str(tmp_path / "tp2.pt"), "cuda", "bfloat16", 29614, {"TP_TEST_GRAPH": graph})
+    assert (two - one).abs().max().item() < 0.15
+    assert (two.argmax(-1) == one.argmax(-1)).float().mean().item() > 0.8

@@ -1,0 +1,94 @@
+"""Child process of the tensor-parallel tests: one rank of a gloo (CPU) or NCCL (GPU) job.
+
+Builds the tiny Qwen3 preset from a seeded full state dict (so every TP degree sees the same
+weights), runs one prefill and two decode steps and, on rank 0, saves the logits."""
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def full_state_dict(cfg, seed=0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    H, D = cfg.hidden_size, cfg.head_dim
+    hq, hkv, I, V = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.intermediate_size, cfg.vocab_size
+
+    def r(*shape):
+        return (torch.randn(*shape, generator=g) * 0.05).to(dtype)
+
+    sd = {"model.embed_tokens.weight": r(V, H), "model.norm.weight": torch.ones(H, dtype=dtype) + r(H)}
+    for i in range(cfg.num_hidden_layers):
+        p = f"model.layers.{i}."
+        sd.update({
+            p + "self_attn.q_proj.weight": r(hq * D, H), p + "self_attn.k_proj.weight": r(hkv * D, H),
+            p + "self_attn.v_proj.weight": r(hkv * D, H), p + "self_attn.o_proj.weight": r(H, hq * D),
+            p + "self_attn.q_norm.weight": torch.ones(D, dtype=dtype) + r(D),
+            p + "self_attn.k_norm.weight": torch.ones(D, dtype=dtype) + r(D),
+            p + "input_layernorm.weight": torch.ones(H, dtype=dtype) + r(H),
+            p + "post_attention_layernorm.weight": torch.ones(H, dtype=dtype) + r(H),
+            p + "mlp.gate_proj.weight": r(I, H), p + "mlp.up_proj.weight": r(I, H), p + "mlp.down_proj.weight": r(H, I),
+        })
+    return sd
+
+
+def run(out_path: str, device: str, dtype_name: str) -> None:
+    from mllm_b200.configs import ServerConfig
+    from mllm_b200.executor import ModelRunner
+    from mllm_b200.models.presets import get_preset
+    from mllm_b200.parallel import state as pstate
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    pstate.init_distributed(backend="gloo" if device == "cpu" else "nccl", timeout_s=120)
+    if world > 1:
+        pstate.initialize_model_parallel(tp_size=world)
+    dev = device if device == "cpu" else f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}"
+    cfg = get_preset("qwen3-tiny", num_attention_heads=4, num_key_value_heads=2)
+    sc = ServerConfig(model_path="preset:qwen3-tiny", dtype=dtype_name, max_running_requests=4, max_total_tokens=1024,
+                      tp_size=world, disable_cuda_graph=os.environ.get("TP_TEST_GRAPH", "0") != "1")
+    mr = ModelRunner(sc, hf_config=cfg, device=dev)
+    mr.initialize()
+    dtype = mr.dtype
+    mr.model.load_weights(full_state_dict(cfg, dtype=dtype).items())
+    for m in mr.model.modules():
+        if hasattr(m, "quant_method"):
+            m._gate_up_interleaved = False
+            m.quant_method.process_weights_after_loading(m)
+
+    torch.manual_seed(3)
+    B, L = 2, 9
+    ids = torch.randint(0, cfg.vocab_size, (B, L))
+    slots = mr.req_to_token_pool.alloc(B)
+    loc = mr.token_to_kv_pool_allocator.alloc(B * L)
+    sl = torch.tensor(slots, device=dev)
+    mr.req_to_token_pool.req_to_token[sl.long(), :L] = loc.view(B, L).int()
+    lens = torch.full((B,), L, device=dev)
+    fb = mr.prepare_forward_batch_extend(ids.reshape(-1).to(dev), sl, lens, lens, torch.zeros_like(lens), loc,
+                                         extend_seq_lens_cpu=[L] * B, extend_prefix_lens_cpu=[0] * B)
+    outs = [mr.forward(fb).next_token_logits.float().cpu()]
+    nxt = outs[-1].argmax(-1).to(dev)
+    cur = L
+    for _ in range(2):
+        loc1 = mr.token_to_kv_pool_allocator.alloc(B)
+        mr.req_to_token_pool.req_to_token[sl.long(), cur] = loc1.int()
+        cur += 1
+        fb = mr.prepare_forward_batch_decode(nxt, sl, torch.full((B,), cur, device=dev), loc1, max_seq_len=cur)
+        outs.append(mr.forward(fb).next_token_logits.float().cpu())
+        nxt = outs[-1].argmax(-1).to(dev)
+    if device != "cpu":
+        from mllm_b200 import ops
+
+        ops.check_status()
+    if rank == 0:
+        torch.save(torch.stack(outs), out_path)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    run(sys.argv[1], sys.argv[2], sys.argv[3])
