@@ -60,6 +60,7 @@ class CudaGraphRunner:
         self.replays = 0
         self.replayed_kernels = 0
         self.uses_mrope = bool(getattr(model_runner.model, "uses_mrope", False))
+        self.tp_sharded_logits = getattr(model_runner.model, "tp_size", 1) > 1
 
     def _batch(self, bs: int) -> ForwardBatch:
         return ForwardBatch(
@@ -74,6 +75,8 @@ class CudaGraphRunner:
     def _run(self, bs: int):
         fb = self._batch(bs)
         out = self.mr.model(fb.input_ids, fb.positions, fb)
+        if self.tp_sharded_logits:
+            return out.next_token_logits, None  # vocabulary slice; gathered and sampled after the replay
         return out.next_token_logits, ops.argmax(out.next_token_logits)
 
     @torch.no_grad()
@@ -123,6 +126,8 @@ class CudaGraphRunner:
         self.graphs[bs].replay()
         self.replays += 1
         self.replayed_kernels += self.kernels_per_graph.get(bs, 0)
+        if self.tp_sharded_logits:
+            return LogitsProcessorOutput(next_token_logits=self.mr.model.gather_logits(self.logits[bs][:raw]))
         out = LogitsProcessorOutput(next_token_logits=self.logits[bs][:raw])
         out.next_token_ids = self.next_ids[bs][:raw]
         return out

@@ -38,6 +38,8 @@ class VocabParallelEmbedding(nn.Module):
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
         if self.tp_size == 1:
             return ops.embedding(ids, self.weight)
+        if torch.cuda.is_available() and ids.is_cuda and torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("a vocabulary-sharded embedding lookup needs a collective and cannot be graph-captured")
         mask = (ids < self.vocab_start) | (ids >= self.vocab_end)
         local = torch.where(mask, torch.zeros_like(ids), ids - self.vocab_start)
         out = ops.embedding(local, self.weight)

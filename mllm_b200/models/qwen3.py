@@ -128,7 +128,11 @@ class Qwen3Model(nn.Module):
     def __init__(self, config, quant_config=None, prefix: str = "model", params_dtype=None, **attn_kw) -> None:
         super().__init__()
         self.config = config
-        self.embed_tokens = VocabParallelEmbedding(config.vocab_size, config.hidden_size, params_dtype)
+        # Tied weights double as the (vocabulary-sharded) lm_head, so they stay sharded; an untied
+        # input table is replicated under tensor parallelism: the lookup then needs no collective
+        # and the decode step can be captured in a CUDA graph without library collectives inside.
+        tied = bool(getattr(config, "tie_word_embeddings", False))
+        self.embed_tokens = VocabParallelEmbedding(config.vocab_size, config.hidden_size, params_dtype, shard=tied)
         self.layers = nn.ModuleList(
             self.layer_cls(config, i, quant_config, f"{prefix}.layers.{i}", params_dtype, **attn_kw)
             for i in range(config.num_hidden_layers)
@@ -183,8 +187,16 @@ class Qwen3ForCausalLM(nn.Module):
             hidden = hidden.index_select(0, last)
         logits = ops.linear(hidden, self.lm_head_weight)
         if self.tp_size > 1:
+            if logits.is_cuda and torch.cuda.is_current_stream_capturing():
+                return logits  # this rank's vocabulary slice; gathered by the caller after the replay
             logits = pstate.tensor_model_parallel_all_gather(logits, dim=-1)
         return logits[:, : self.config.vocab_size]
+
+    def gather_logits(self, local_logits: torch.Tensor) -> torch.Tensor:
+        """Full-vocabulary logits from per-rank slices (used after a graph replay)."""
+        if self.tp_size == 1:
+            return local_logits
+        return pstate.tensor_model_parallel_all_gather(local_logits, dim=-1)[:, : self.config.vocab_size]
 
     def forward(self, input_ids: torch.Tensor, positions: torch.Tensor, forward_batch: ForwardBatch,
                 input_embeds: Optional[torch.Tensor] = None) -> LogitsProcessorOutput:

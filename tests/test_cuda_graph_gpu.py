@@ -1,0 +1,34 @@
+"""CUDA-graph decode gives the tokens and logits of eager decode (single GPU)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(disable_graph: bool):
+    from mllm_b200.bench_one_batch import BenchRunner, make_synthetic_input_ids
+    from mllm_b200.configs import GlobalConfig
+
+    GlobalConfig.reset()
+    cfg = GlobalConfig.get_instance()
+    sc = cfg.server
+    sc.model_path = "preset:qwen3-0.6b"
+    sc.dtype = "bfloat16"
+    sc.max_running_requests = 8
+    sc.max_total_tokens = 8192
+    sc.disable_cuda_graph = disable_graph
+    br = BenchRunner.create(cfg, device="cuda:0")
+    ids = make_synthetic_input_ids(batch_size=3, input_len=70, vocab_size=br.runner.vocab_size, seed=5)
+    toks = [br.extend(ids)]
+    for _ in range(6):
+        toks.append(br.decode(toks[-1]))
+    torch.cuda.synchronize()
+    graphs = br.runner.cuda_graph_runner
+    return torch.stack([t.cpu() for t in toks]), (graphs.replays if graphs is not None else 0)
+
+
+def test_graph_decode_equals_eager_decode():
+    eager, n0 = _run(True)
+    graph, n1 = _run(False)
+    assert n0 == 0 and n1 == 6
+    assert torch.equal(eager, graph)

@@ -17,7 +17,12 @@ def _launch(world, out, device, dtype, port, extra_env=None):
     for r in range(world):
         e = dict(env, RANK=str(r), LOCAL_RANK=str(r))
         procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "tp_worker.py"), out, device, dtype], env=e))
-    codes = [p.wait(timeout=600) for p in procs]
+    try:
+        codes = [p.wait(timeout=150) for p in procs]
+    except subprocess.TimeoutExpired:
+        for p in procs:
+            p.kill()
+        raise
     assert codes == [0] * world, f"rank exit codes {codes}"
     return torch.load(out)
 

@@ -18,7 +18,8 @@ def full_state_dict(cfg, seed=0, dtype=torch.float32):
     def r(*shape):
         return (torch.randn(*shape, generator=g) * 0.05).to(dtype)
 
-    sd = {"model.embed_tokens.weight": r(V, H), "model.norm.weight": torch.ones(H, dtype=dtype) + r(H)}
+    sd = {"model.embed_tokens.weight": r(V, H), "lm_head.weight": r(V, H),
+          "model.norm.weight": torch.ones(H, dtype=dtype) + r(H)}
     for i in range(cfg.num_hidden_layers):
         p = f"model.layers.{i}."
         sd.update({
@@ -45,9 +46,10 @@ def run(out_path: str, device: str, dtype_name: str) -> None:
     if world > 1:
         pstate.initialize_model_parallel(tp_size=world)
     dev = device if device == "cpu" else f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}"
-    cfg = get_preset("qwen3-tiny", num_attention_heads=4, num_key_value_heads=2)
+    cfg = get_preset("qwen3-tiny", num_attention_heads=4, num_key_value_heads=2, tie_word_embeddings=False)
     sc = ServerConfig(model_path="preset:qwen3-tiny", dtype=dtype_name, max_running_requests=4, max_total_tokens=1024,
-                      tp_size=world, disable_cuda_graph=os.environ.get("TP_TEST_GRAPH", "0") != "1")
+                      tp_size=world, disable_cuda_graph=os.environ.get("TP_TEST_GRAPH", "0") != "1",
+                      comm_backend=os.environ.get("TP_TEST_COMM", "fused"))
     mr = ModelRunner(sc, hf_config=cfg, device=dev)
     mr.initialize()
     dtype = mr.dtype
@@ -56,6 +58,9 @@ def run(out_path: str, device: str, dtype_name: str) -> None:
         if hasattr(m, "quant_method"):
             m._gate_up_interleaved = False
             m.quant_method.process_weights_after_loading(m)
+    if mr.cuda_graph_runner is not None:  # graphs hold the addresses of the weights they were captured with
+        mr.cuda_graph_runner = None
+        mr.init_cuda_graphs()
 
     torch.manual_seed(3)
     B, L = 2, 9
