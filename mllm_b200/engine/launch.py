@@ -1,0 +1,354 @@
+"""Engine: the object a program (or the HTTP server) talks to.
+
+Public surface of pymllm/engine/launch.py:130-658 — ``launch()``, ``generate()``,
+``generate_async()``, ``shutdown()``, ``is_healthy`` — over two deployments:
+
+* ``mode="multiproc"`` (the reference's layout): tokenizer, scheduler(+GPU) and detokenizer run
+  as spawned daemon processes connected by ZMQ ``ipc://`` sockets; each child reports
+  ``{"status": "ready"}`` on a pipe; a health thread polls ``is_alive`` every 5 s.
+* ``mode="inproc"``: the same three workers run inside this process, the scheduler loop on a
+  thread.  No serialisation on the hot path; used by tests, benchmarks and single-GPU embedding.
+
+Both deliver results through :class:`RequestResponseProcess`, so streaming, abort and
+back-pressure behave identically.
+"""
+
+from __future__ import annotations
+
+import asyncio
+import logging
+import multiprocessing as mp
+import os
+import threading
+import time
+import uuid
+from typing import Any, AsyncIterator, Dict, Iterator, List, Optional, Union
+
+from ..configs import GlobalConfig, ServerConfig, get_global_config
+from ..orchestrator.request_response_process import ReqState, RequestResponseProcess
+from .io_struct import AbortReq, FlushCacheReq, GenerateReqInput
+
+logger = logging.getLogger(__name__)
+DEFAULT_MAX_NEW_TOKENS = 128
+
+
+class Engine:
+    def __init__(self, config: Optional[Union[GlobalConfig, ServerConfig]] = None, mode: str = "inproc",
+                 hf_config: Any = None, device: Optional[str] = None) -> None:
+        if config is None:
+            config = get_global_config()
+        if isinstance(config, GlobalConfig):
+            self.server_config = config.server
+            self.quant_method = config.quantization.method
+            self.kv_cache_dtype = config.quantization.kv_cache_dtype
+        else:
+            self.server_config = config
+            self.quant_method, self.kv_cache_dtype = None, "auto"
+        if mode not in ("inproc", "multiproc"):
+            raise ValueError("mode must be 'inproc' or 'multiproc'")
+        self.mode = mode
+        self.hf_config = hf_config
+        self.device = device
+        self._launched = False
+        self._healthy = False
+        self._procs: List[mp.Process] = []
+        self._threads: List[threading.Thread] = []
+        self._stop = threading.Event()
+        self.rr: Optional[RequestResponseProcess] = None
+        self.scheduler = None
+        self._addrs: List[str] = []
+
+    # ------------------------------------------------------------------ lifecycle
+    def launch(self) -> "Engine":
+        if self._launched:
+            return self
+        logging.getLogger("mllm_b200").setLevel(getattr(logging, self.server_config.log_level.upper(), logging.INFO))
+        if self.mode == "inproc":
+            self._launch_inproc()
+        else:
+            self._launch_processes()
+        self._launched = self._healthy = True
+        return self
+
+    def _vocab_size(self) -> int:
+        from ..executor import load_hf_config, text_config_of
+
+        if self.hf_config is None:
+            self.hf_config = load_hf_config(self.server_config.model_path)
+        return int(getattr(text_config_of(self.hf_config), "vocab_size", 1024))
+
+    def _launch_inproc(self) -> None:
+        from ..orchestrator.detokenizer_process import DetokenizerWorker
+        from ..orchestrator.scheduler_process import build_scheduler
+        from ..orchestrator.tokenizer_process import TokenizerWorker
+
+        sc = self.server_config
+        vocab = self._vocab_size()
+        self.tokenizer_worker = TokenizerWorker(sc.tokenizer_path, sc.context_length, vocab, sc.tokenizer_mode,
+                                                sc.trust_remote_code)
+        self.detokenizer_worker = DetokenizerWorker(sc.tokenizer_path, vocab, sc.tokenizer_mode, sc.trust_remote_code)
+        self.scheduler = build_scheduler(sc, self.hf_config, self.quant_method, self.kv_cache_dtype, self.device)
+        tok = self.tokenizer_worker.tokenizer
+        if getattr(tok, "eos_token_id", None) is not None and not self.scheduler.eos_token_ids:
+            self.scheduler.eos_token_ids = {int(tok.eos_token_id)}
+        self._inbox: List[Any] = []
+        self._inbox_lock = threading.Lock()
+        self._wake = threading.Event()
+        self.rr = RequestResponseProcess(self._inproc_send, sc.max_queued_requests)
+        t = threading.Thread(target=self._inproc_loop, name="mllm_b200-scheduler", daemon=True)
+        t.start()
+        self._threads.append(t)
+
+    def _inproc_send(self, msg: Any) -> None:
+        with self._inbox_lock:
+            self._inbox.append(msg)
+        self._wake.set()
+
+    def _inproc_loop(self) -> None:
+        import torch
+
+        sched = self.scheduler
+        if sched.mrp.device.type == "cuda":
+            torch.cuda.set_device(sched.mrp.device)
+        try:
+            while not self._stop.is_set():
+                with self._inbox_lock:
+                    msgs, self._inbox = self._inbox, []
+                for m in msgs:
+                    if isinstance(m, AbortReq):
+                        if sched.abort(m.rid):
+                            self.rr.handle_output(self.detokenizer_worker.detokenize(sched.abort_outputs([m.rid])))
+                    elif isinstance(m, FlushCacheReq):
+                        sched.flush_cache()
+                    else:
+                        try:
+                            err = sched.add_request(self.tokenizer_worker.tokenize(m))
+                        except Exception as exc:  # bad request: report, keep serving
+                            err = f"{type(exc).__name__}: {exc}"
+                        if err is not None:
+                            self.rr.handle_output({"error": err, "rid": m["rid"]})
+                if not sched.has_work():
+                    self._wake.wait(timeout=0.5)
+                    self._wake.clear()
+                    continue
+                out = sched.step()
+                if out is not None:
+                    self.rr.handle_output(self.detokenizer_worker.detokenize(out))
+        except Exception:
+            logger.exception("scheduler loop died")
+            self._healthy = False
+
+    def _launch_processes(self) -> None:
+        import zmq
+
+        from ..orchestrator.detokenizer_process import run_detokenizer_process
+        from ..orchestrator.ipc_utils import make_ipc_address, make_socket
+        from ..orchestrator.scheduler_process import run_scheduler_process
+        from ..orchestrator.tokenizer_process import run_tokenizer_process
+
+        sc = self.server_config
+        vocab = self._vocab_size()
+        uid = f"{os.getpid()}_{uuid.uuid4().hex[:8]}"
+        a_rr_tok, a_tok_sched, a_sched_detok, a_detok_rr = (make_ipc_address(n, uid) for n in
+                                                            ("rr_tok", "tok_sched", "sched_detok", "detok_rr"))
+        self._addrs = [a_rr_tok, a_tok_sched, a_sched_detok, a_detok_rr]
+        ctx = mp.get_context("spawn")
+        pipes = []
+
+        def spawn(target, kwargs):
+            r, w = ctx.Pipe(duplex=False)
+            p = ctx.Process(target=target, kwargs=dict(kwargs, pipe_writer=w), daemon=True)
+            p.start()
+            self._procs.append(p)
+            pipes.append((p, r))
+
+        self._zmq = zmq.Context()
+        self._to_tok = make_socket(self._zmq, zmq.PUSH, a_rr_tok, bind=True)
+        spawn(run_tokenizer_process, dict(tokenizer_path=sc.tokenizer_path, recv_addr=a_rr_tok, send_addr=a_tok_sched,
+                                          context_length=sc.context_length, vocab_size=vocab,
+                                          tokenizer_mode=sc.tokenizer_mode, trust_remote_code=sc.trust_remote_code,
+                                          log_level=sc.log_level))
+        spawn(run_scheduler_process, dict(server_config=sc, recv_addr=a_tok_sched, send_addr=a_sched_detok,
+                                          hf_config=self.hf_config, quantization_method=self.quant_method,
+                                          kv_cache_dtype=self.kv_cache_dtype, device=self.device))
+        spawn(run_detokenizer_process, dict(tokenizer_path=sc.tokenizer_path, recv_addr=a_sched_detok,
+                                            send_addr=a_detok_rr, vocab_size=vocab, tokenizer_mode=sc.tokenizer_mode,
+                                            trust_remote_code=sc.trust_remote_code, log_level=sc.log_level))
+        for p, r in pipes:  # readiness handshake; EOF or an error message fails the launch
+            try:
+                if not r.poll(600):
+                    raise RuntimeError(f"process {p.name} did not become ready")
+                msg = r.recv()
+            except EOFError as exc:
+                raise RuntimeError(f"process {p.name} exited during start-up") from exc
+            if msg.get("status") != "ready":
+                raise RuntimeError(f"process {p.name} failed to start: {msg}")
+        self._from_detok = make_socket(self._zmq, zmq.PULL, a_detok_rr, bind=False)
+        self._send_lock = threading.Lock()
+
+        def send(msg):
+            with self._send_lock:
+                self._to_tok.send_pyobj(msg)
+
+        self.rr = RequestResponseProcess(send, sc.max_queued_requests)
+        t = threading.Thread(target=self._recv_loop, name="mllm_b200-recv", daemon=True)
+        t.start()
+        h = threading.Thread(target=self._health_loop, name="mllm_b200-health", daemon=True)
+        h.start()
+        self._threads += [t, h]
+
+    def _recv_loop(self) -> None:
+        import zmq
+
+        poller = zmq.Poller()
+        poller.register(self._from_detok, zmq.POLLIN)
+        while not self._stop.is_set():
+            if dict(poller.poll(200)):
+                self.rr.handle_output(self._from_detok.recv_pyobj())
+
+    def _health_loop(self) -> None:
+        while not self._stop.wait(5.0):
+            if any(not p.is_alive() for p in self._procs):
+                self._healthy = False
+            self.rr.gc()
+
+    @property
+    def is_healthy(self) -> bool:
+        return self._launched and self._healthy and not self._stop.is_set()
+
+    def shutdown(self) -> None:
+        if not self._launched:
+            return
+        self._stop.set()
+        if self.mode == "inproc":
+            self._wake.set()
+            for t in self._threads:
+                t.join(timeout=10)
+            if self.scheduler is not None:
+                self.scheduler.mrp.runner.shutdown()
+        else:
+            try:
+                self._to_tok.send_pyobj(None)
+            except Exception:
+                pass
+            for p in self._procs:
+                p.join(timeout=5)
+                if p.is_alive():
+                    p.terminate()
+            from ..orchestrator.ipc_utils import cleanup_ipc
+
+            cleanup_ipc(self._addrs)
+        self._launched = self._healthy = False
+
+    # ------------------------------------------------------------------ requests
+    def _submit(self, obj: GenerateReqInput) -> List[tuple]:
+        obj.normalize_batch_and_arguments()
+        out = []
+        for i in range(obj.batch_size):
+            one = obj[i]
+            sp = dict(one.sampling_params or {})
+            sp.setdefault("max_new_tokens", sp.pop("max_tokens", DEFAULT_MAX_NEW_TOKENS))
+            req = one.to_request_dict()
+            req["sampling_params"] = sp
+            req["rid"] = one.rid
+            req["created_time"] = time.time()
+            out.append((one.rid, self.rr.add_request(req)))
+        return out
+
+    @staticmethod
+    def _final(rid: str, st: ReqState) -> Dict[str, Any]:
+        if st.error is not None:
+            raise ValueError(st.error)
+        last = st.out_list[-1]
+        return {"rid": rid, "text": last["text"], "output_ids": last["output_ids"],
+                "meta_info": {"finish_reason": last["finish_reason"], "prompt_tokens": last["prompt_tokens"],
+                              "completion_tokens": last["completion_tokens"], "cached_tokens": last["cached_tokens"],
+                              "timing": last["timing"]}}
+
+    def generate(self, prompt: Optional[Union[str, List[str]]] = None, sampling_params=None, input_ids=None,
+                 image_data=None, stream: bool = False, rid=None, timeout: Optional[float] = None):
+        """Blocking generation. One prompt -> dict, a list -> list of dicts; ``stream=True`` (single
+        prompt) returns an iterator of incremental dicts with a ``delta`` field."""
+        obj = GenerateReqInput(rid=rid, text=prompt, input_ids=input_ids, sampling_params=sampling_params,
+                               image_data=image_data, stream=stream)
+        subs = self._submit(obj)
+        if stream:
+            if len(subs) != 1:
+                raise ValueError("stream=True takes a single prompt")
+            return self._stream_sync(*subs[0], timeout)
+        results = []
+        for r, st in subs:
+            deadline = None if timeout is None else time.time() + timeout
+            while not st.finished:
+                st.event.wait(0.05 if deadline is None else max(0.0, min(0.05, deadline - time.time())))
+                st.event.clear()
+                if not self.is_healthy:
+                    raise RuntimeError("engine is not healthy")
+                if deadline is not None and time.time() > deadline:
+                    self.rr.abort(r)
+                    raise TimeoutError(f"request {r} timed out")
+            try:
+                results.append(self._final(r, st))
+            finally:
+                self.rr.pop(r)
+        return results[0] if obj.is_single else results
+
+    def _stream_sync(self, rid: str, st: ReqState, timeout) -> Iterator[Dict[str, Any]]:
+        sent = 0
+        try:
+            while True:
+                st.event.wait(0.05)
+                st.event.clear()
+                if st.error is not None:
+                    raise ValueError(st.error)
+                while sent < len(st.out_list):
+                    o = st.out_list[sent]
+                    sent += 1
+                    yield {"rid": rid, "text": o["text"], "delta": o["delta"], "output_ids": o["output_ids"],
+                           "meta_info": {k: o[k] for k in ("finish_reason", "prompt_tokens", "completion_tokens",
+                                                           "cached_tokens", "timing")}}
+                if st.finished and sent >= len(st.out_list):
+                    return
+                if not self.is_healthy:
+                    raise RuntimeError("engine is not healthy")
+        finally:
+            if not st.finished:
+                self.rr.abort(rid)
+            self.rr.pop(rid)
+
+    async def generate_async(self, obj: GenerateReqInput) -> AsyncIterator[Dict[str, Any]]:
+        """Async generation for the HTTP layer: yields incremental dicts when ``obj.stream`` else the
+        final dict of every request of the batch.  Cancelling the consumer aborts the request."""
+        subs = self._submit(obj)
+        loop = asyncio.get_running_loop()
+        for rid, st in subs:
+            sent = 0
+            try:
+                while True:
+                    await loop.run_in_executor(None, st.event.wait, 0.05)
+                    st.event.clear()
+                    if st.error is not None:
+                        raise ValueError(st.error)
+                    if obj.stream:
+                        while sent < len(st.out_list):
+                            o = st.out_list[sent]
+                            sent += 1
+                            yield {"rid": rid, "text": o["text"], "delta": o["delta"], "output_ids": o["output_ids"],
+                                   "meta_info": {k: o[k] for k in ("finish_reason", "prompt_tokens",
+                                                                   "completion_tokens", "cached_tokens", "timing")}}
+                    if st.finished and (not obj.stream or sent >= len(st.out_list)):
+                        if not obj.stream:
+                            yield self._final(rid, st)
+                        break
+                    if not self.is_healthy:
+                        raise RuntimeError("engine is not healthy")
+            finally:
+                if not st.finished:
+                    self.rr.abort(rid)
+                self.rr.pop(rid)
+
+    def abort(self, rid: str) -> None:
+        self.rr.abort(rid)
+
+    def flush_cache(self) -> None:
+        self.rr._send(FlushCacheReq())

@@ -1,0 +1,68 @@
+"""Detokenizer worker (role of pymllm/orchestrator/detokenizer_process.py:20-233): decodes the full
+list of generated ids of every request on every message and emits the text added since the
+previous message (``delta``); incomplete UTF-8 tails are held back until they complete."""
+
+from __future__ import annotations
+
+import logging
+from typing import Dict, Optional
+
+from ..engine.io_struct import BatchStrOutput, BatchTokenIDOutput
+from ..utils.tokenizer import get_tokenizer
+
+logger = logging.getLogger(__name__)
+
+
+class DetokenizerWorker:
+    def __init__(self, tokenizer_path, vocab_size: int = 1024, tokenizer_mode: str = "auto",
+                 trust_remote_code: bool = False) -> None:
+        self.tokenizer = get_tokenizer(tokenizer_path, vocab_size, tokenizer_mode, trust_remote_code)
+        self.sent: Dict[str, str] = {}
+
+    def detokenize(self, batch: BatchTokenIDOutput) -> BatchStrOutput:
+        out = BatchStrOutput([], [], [], [], [], [], [], [], [])
+        for i, rid in enumerate(batch.rids):
+            ids = batch.output_ids[i]
+            text = self.tokenizer.decode(ids, skip_special_tokens=batch.skip_special_tokens[i]) if ids else ""
+            finished = batch.finished_reasons[i]
+            if finished is None and text.endswith("�"):
+                text = text.rstrip("�")  # an incomplete multi-byte character: wait for the rest
+            prev = self.sent.get(rid, "")
+            delta = text[len(prev):] if text.startswith(prev) else text
+            if finished is None:
+                self.sent[rid] = text
+            else:
+                self.sent.pop(rid, None)
+            out.rids.append(rid)
+            out.finished_reasons.append(finished)
+            out.output_strs.append(text)
+            out.deltas.append(delta)
+            out.output_ids.append(ids)
+            out.prompt_tokens.append(batch.prompt_tokens[i])
+            out.completion_tokens.append(batch.completion_tokens[i])
+            out.cached_tokens.append(batch.cached_tokens[i] if batch.cached_tokens else 0)
+            out.timing.append(batch.timing[i] if batch.timing else None)
+        return out
+
+
+def run_detokenizer_process(tokenizer_path, recv_addr: str, send_addr: str, pipe_writer=None, vocab_size: int = 1024,
+                            tokenizer_mode: str = "auto", trust_remote_code: bool = False, log_level: str = "info") -> None:
+    import zmq
+
+    from .ipc_utils import make_socket, setup_subprocess_logging
+
+    setup_subprocess_logging(log_level)
+    worker = DetokenizerWorker(tokenizer_path, vocab_size, tokenizer_mode, trust_remote_code)
+    ctx = zmq.Context()
+    recv = make_socket(ctx, zmq.PULL, recv_addr, bind=False)
+    send = make_socket(ctx, zmq.PUSH, send_addr, bind=True)
+    if pipe_writer is not None:
+        pipe_writer.send({"status": "ready"})
+    while True:
+        msg = recv.recv_pyobj()
+        if msg is None:
+            return
+        if isinstance(msg, BatchTokenIDOutput):
+            send.send_pyobj(worker.detokenize(msg))
+        else:
+            send.send_pyobj(msg)  # errors and control replies pass through

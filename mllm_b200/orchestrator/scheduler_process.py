@@ -1,0 +1,365 @@
+"""Continuous-batching scheduler: one iteration of its loop is one forward pass.
+
+Policy of pymllm/orchestrator/scheduler_process.py:662-736 (first come first served; prefill
+before decode; admit while ``running < max_running_requests``, the KV budget and the prefill token
+budget allow), extended with what the reference declares but does not implement: **chunked
+prefill** (a prompt longer than ``chunked_prefill_size`` is prefilled over several passes) and
+**mixed batches** (running requests ride along in a prefill pass as one-token rows, so decode does
+not stall behind long prompts).  The class is plain host logic around
+:class:`ModelRunnerProcess`; :func:`run_scheduler_process` wraps it in the ZMQ event loop used by
+the multi-process engine, and the in-process engine drives it from a thread.
+
+With tensor parallelism every rank runs the same scheduler on the same request stream (rank 0
+receives requests and broadcasts them), so all ranks build identical batches without a per-step
+metadata exchange.
+"""
+
+from __future__ import annotations
+
+import logging
+import time
+from collections import deque
+from dataclasses import dataclass
+from typing import Any, Deque, Dict, List, Optional, Tuple
+
+import torch
+
+from ..configs import ServerConfig
+from ..engine.io_struct import AbortReq, BatchTokenIDOutput, FlushCacheReq, TokenizedGenerateReqInput
+from ..engine.sampling_params import SamplingParams
+from .model_runner_process import KVAllocationError, ModelRunnerProcess, Req
+
+logger = logging.getLogger(__name__)
+
+
+@dataclass
+class SchedulerStats:
+    num_prefill_batches: int = 0
+    num_decode_batches: int = 0
+    num_mixed_batches: int = 0
+    prefill_tokens: int = 0
+    cached_tokens: int = 0
+    decode_tokens: int = 0
+    finished: int = 0
+    aborted: int = 0
+    last_prefill_tok_s: float = 0.0
+    last_decode_tok_s: float = 0.0
+
+
+class Scheduler:
+    def __init__(self, mrp: ModelRunnerProcess, server_config: ServerConfig, eos_token_ids: Optional[List[int]] = None,
+                 enable_mixed: bool = True) -> None:
+        self.mrp = mrp
+        self.cfg = server_config
+        self.eos_token_ids = set(eos_token_ids or [])
+        self.enable_mixed = enable_mixed
+        self.waiting: Deque[Req] = deque()
+        self.prefilling: List[Req] = []   # admitted, prompt not fully computed yet
+        self.running: List[Req] = []      # generating
+        self.stats = SchedulerStats()
+        self.max_running = server_config.max_running_requests or 1
+        self.chunk = server_config.chunked_prefill_size
+        self.max_prefill_tokens = server_config.max_prefill_tokens or 16384
+        self.stream_interval = server_config.stream_interval
+        self.context_len = mrp.runner.context_len
+        self._decode_steps = 0
+
+    # ------------------------------------------------------------------ intake
+    def add_request(self, t: TokenizedGenerateReqInput) -> Optional[str]:
+        """Queue a request. Returns an error string when it cannot be served at all."""
+        sp = SamplingParams.from_dict(t.sampling_params)
+        ids = list(t.input_ids)
+        if not ids:
+            return "empty prompt"
+        if len(ids) >= self.context_len:
+            ids = ids[: self.context_len - 1]
+        sp.max_new_tokens = max(0, min(sp.max_new_tokens, self.context_len - len(ids)))
+        if len(ids) + 1 > self.mrp.runner.max_total_num_tokens:
+            return f"prompt of {len(ids)} tokens exceeds the KV pool ({self.mrp.runner.max_total_num_tokens} tokens)"
+        if self.cfg.max_queued_requests is not None and len(self.waiting) >= self.cfg.max_queued_requests:
+            return "queue full"
+        stop_ids = set(sp.stop_token_ids or [])
+        if not sp.ignore_eos:
+            stop_ids |= self.eos_token_ids
+        extra_key = None
+        if t.mm_inputs and t.mm_inputs.get("image_hash"):
+            extra_key = str(t.mm_inputs["image_hash"])
+        req = Req(rid=t.rid, input_ids=ids, sampling=sp, stream=t.stream, input_text=t.input_text,
+                  mm_inputs=t.mm_inputs, extra_key=extra_key, stop_token_ids=stop_ids,
+                  created_time=t.created_time or time.time())
+        if t.mm_inputs and "mrope_position_delta" in t.mm_inputs:
+            req.mrope_delta = int(t.mm_inputs["mrope_position_delta"])
+        self.waiting.append(req)
+        return None
+
+    def abort(self, rid: str) -> bool:
+        for q in list(self.waiting):
+            if q.rid == rid:
+                self.waiting.remove(q)
+                q.finished_reason = "abort"
+                self.stats.aborted += 1
+                return True
+        for group in (self.prefilling, self.running):
+            for q in group:
+                if q.rid == rid and not q.finished:
+                    q.finished_reason = "abort"
+                    return True
+        return False
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.prefilling or self.running)
+
+    # ------------------------------------------------------------------ batch selection
+    def _admit_waiting(self) -> None:
+        """Move requests from the queue into `prefilling` while the budgets allow."""
+        while self.waiting:
+            if len(self.running) + len(self.prefilling) >= self.max_running:
+                break
+            req = self.waiting[0]
+            # conservative KV budget: the whole prompt plus its generation must fit beside what is reserved
+            reserved = sum(q.sampling.max_new_tokens - len(q.output_ids) for q in self.running) + \
+                sum(len(q.input_ids) - q.num_computed + q.sampling.max_new_tokens for q in self.prefilling)
+            need = len(req.input_ids) + req.sampling.max_new_tokens
+            budget = self.mrp.available_tokens() / self.cfg.schedule_conservativeness
+            if self.mrp.free_req_slots() == 0 or (need + reserved > budget and (self.running or self.prefilling)):
+                break
+            self.waiting.popleft()
+            try:
+                self.mrp.admit(req)
+            except KVAllocationError:
+                self.waiting.appendleft(req)
+                break
+            self.stats.cached_tokens += req.cached_tokens
+            self.prefilling.append(req)
+
+    def get_next_batch_to_run(self) -> Tuple[str, List[Tuple[Req, int]]]:
+        """("extend" | "decode" | "idle", rows).  Extend rows: (request, new tokens in this pass)."""
+        self._sweep_finished()
+        self._admit_waiting()
+        if self.prefilling:
+            rows: List[Tuple[Req, int]] = []
+            budget = min(self.max_prefill_tokens, self.chunk or self.max_prefill_tokens)
+            for req in self.prefilling:
+                if budget <= 0:
+                    break
+                n = min(len(req.input_ids) - req.num_computed, budget)
+                if n > 0:
+                    rows.append((req, n))
+                    budget -= n
+            if self.enable_mixed and self.running:
+                rows.extend((q, 1) for q in self.running)
+            return "extend", rows
+        if self.running:
+            return "decode", [(q, 1) for q in self.running]
+        return "idle", []
+
+    # ------------------------------------------------------------------ one iteration
+    def step(self) -> Optional[BatchTokenIDOutput]:
+        kind, rows = self.get_next_batch_to_run()
+        if kind == "idle":
+            return None
+        t0 = time.perf_counter()
+        try:
+            if kind == "extend":
+                next_ids, produced, _ = self.mrp.extend(rows)
+                reqs = [rows[i][0] for i in produced]
+            else:
+                reqs = [q for q, _ in rows]
+                next_ids, _ = self.mrp.decode(reqs)
+        except KVAllocationError as exc:
+            return self._shed_load(str(exc))
+        ids = next_ids.tolist() if next_ids is not None and len(reqs) else []  # the step's one device->host sync
+        dt = time.perf_counter() - t0
+        now = time.time()
+        n_prefill = sum(n for q, n in rows if q in self.prefilling) if kind == "extend" else 0
+        if kind == "extend":
+            mixed = any(q in self.running for q, _ in rows)
+            self.stats.num_mixed_batches += int(mixed)
+            self.stats.num_prefill_batches += 1
+            self.stats.prefill_tokens += n_prefill
+            self.stats.last_prefill_tok_s = n_prefill / dt if dt > 0 else 0.0
+            if self.cfg.log_level in ("debug", "info"):
+                logger.info("Prefill batch: #new-token %d, #cached-token %d, #running %d, #queue %d, input tok/s %.1f",
+                            n_prefill, sum(q.cached_tokens for q, _ in rows if q in self.prefilling),
+                            len(self.running), len(self.waiting), self.stats.last_prefill_tok_s)
+        else:
+            self.stats.num_decode_batches += 1
+            self._decode_steps += 1
+            self.stats.last_decode_tok_s = len(reqs) / dt if dt > 0 else 0.0
+            iv = self.cfg.decode_log_interval
+            if iv and self._decode_steps % iv == 0:
+                logger.info("Decode batch: #running %d, #token %d, gen tok/s %.1f, #queue %d", len(self.running),
+                            sum(q.seq_len for q in self.running), self.stats.last_decode_tok_s, len(self.waiting))
+        for req, tok in zip(reqs, ids):
+            if req.finished:  # aborted while the pass ran
+                continue
+            req.output_ids.append(int(tok))
+            self.stats.decode_tokens += 1
+            if len(req.output_ids) == 1:
+                req.first_token_time = now
+            self._check_finished(req, now)
+        # prompts that completed their prefill start generating
+        still = []
+        for q in self.prefilling:
+            if q.finished or q.num_computed >= len(q.input_ids):
+                if not q.finished:
+                    self.running.append(q)
+            else:
+                still.append(q)
+        self.prefilling = still
+        return self._collect_output(reqs)
+
+    def _check_finished(self, req: Req, now: float) -> None:
+        tok = req.output_ids[-1]
+        if tok in req.stop_token_ids:
+            req.finished_reason = "stop"
+        elif len(req.output_ids) >= req.sampling.max_new_tokens:
+            req.finished_reason = "length"
+        elif req.seq_len >= self.context_len:
+            req.finished_reason = "length"
+        if req.finished:
+            req.finish_time = now
+
+    def _sweep_finished(self) -> None:
+        for group_name in ("running", "prefilling"):
+            group = getattr(self, group_name)
+            keep = []
+            for q in group:
+                if q.finished:
+                    self.mrp.release(q, cache=q.finished_reason != "abort")
+                    if q.finished_reason == "abort":
+                        self.stats.aborted += 1
+                    else:
+                        self.stats.finished += 1
+                else:
+                    keep.append(q)
+            setattr(self, group_name, keep)
+
+    def _shed_load(self, why: str) -> Optional[BatchTokenIDOutput]:
+        """The pool ran dry mid-flight: retract the youngest running request back to the queue."""
+        logger.warning("KV allocation failed (%s); retracting a request", why)
+        victims = self.prefilling or self.running
+        if not victims:
+            raise RuntimeError(why)
+        q = victims[-1]
+        (self.prefilling if q in self.prefilling else self.running).remove(q)
+        self.mrp.release(q, cache=True)
+        q.input_ids = q.all_ids()
+        q.sampling.max_new_tokens = max(0, q.sampling.max_new_tokens - len(q.output_ids))
+        retained, q.output_ids = q.output_ids, []
+        q.num_computed = q.prefix_len = 0
+        q.__dict__.setdefault("_retained", []).extend(retained)
+        self.waiting.appendleft(q)
+        return None
+
+    def _collect_output(self, reqs: List[Req]) -> Optional[BatchTokenIDOutput]:
+        out = BatchTokenIDOutput([], [], [], [], [], [])
+        for q in reqs:
+            if not q.output_ids and not q.finished:
+                continue
+            due = q.finished or (q.stream and len(q.output_ids) - q.last_stream_len >= self.stream_interval)
+            if not due:
+                continue
+            q.last_stream_len = len(q.output_ids)
+            prior = q.__dict__.get("_retained", [])
+            out.rids.append(q.rid)
+            out.finished_reasons.append(q.finished_reason)
+            out.output_ids.append(prior + list(q.output_ids))
+            out.skip_special_tokens.append(q.sampling.skip_special_tokens)
+            out.prompt_tokens.append(len(q.input_ids) - len(prior))
+            out.completion_tokens.append(len(prior) + len(q.output_ids))
+            out.cached_tokens.append(q.cached_tokens)
+            timing = None
+            if q.finished:
+                ttft = max(0.0, q.first_token_time - q.created_time)
+                n = len(q.output_ids)
+                tpot = (q.finish_time - q.first_token_time) / (n - 1) if n > 1 else 0.0
+                timing = {"ttft_s": ttft, "tpot_s": tpot, "e2e_s": q.finish_time - q.created_time}
+            out.timing.append(timing)
+        return out if out.rids else None
+
+    def abort_outputs(self, rids: List[str]) -> BatchTokenIDOutput:
+        return BatchTokenIDOutput(rids, ["abort"] * len(rids), [[] for _ in rids], [True] * len(rids), [0] * len(rids),
+                                  [0] * len(rids), [0] * len(rids), [None] * len(rids))
+
+    def flush_cache(self) -> bool:
+        if self.has_work():
+            return False
+        return self.mrp.flush_cache()
+
+
+# ----------------------------------------------------------------------------------------------
+# process wrapper (multi-process engine): ZMQ in from the tokenizer, ZMQ out to the detokenizer
+# ----------------------------------------------------------------------------------------------
+def build_scheduler(server_config: ServerConfig, hf_config=None, quantization_method=None, kv_cache_dtype="auto",
+                    device: Optional[str] = None, eos_token_ids: Optional[List[int]] = None) -> Scheduler:
+    import os
+
+    from ..executor import ModelRunner
+    from ..parallel import state as pstate
+
+    if server_config.world_size > 1:
+        pstate.init_distributed()
+        if not pstate.model_parallel_is_initialized():
+            pstate.initialize_model_parallel(tp_size=server_config.tp_size, ep_size=server_config.ep_size)
+    gpu = server_config.base_gpu_id + int(os.environ.get("LOCAL_RANK", "0"))
+    runner = ModelRunner(server_config, hf_config=hf_config, gpu_id=gpu, quantization_method=quantization_method,
+                         kv_cache_dtype=kv_cache_dtype, device=device)
+    runner.initialize()
+    if eos_token_ids is None:
+        eos_token_ids = resolve_eos_token_ids(runner.hf_config)
+    mrp = ModelRunnerProcess(runner, disable_radix_cache=server_config.disable_radix_cache)
+    return Scheduler(mrp, server_config, eos_token_ids)
+
+
+def resolve_eos_token_ids(hf_config) -> List[int]:
+    """config -> text_config -> generation defaults (pymllm/engine/launch.py:46-127)."""
+    for cfg in (hf_config, getattr(hf_config, "text_config", None)):
+        eos = getattr(cfg, "eos_token_id", None) if cfg is not None else None
+        if eos is not None:
+            return [int(e) for e in eos] if isinstance(eos, (list, tuple)) else [int(eos)]
+    return []
+
+
+def run_scheduler_process(server_config: ServerConfig, recv_addr: str, send_addr: str, pipe_writer=None,
+                          hf_config=None, quantization_method=None, kv_cache_dtype: str = "auto",
+                          device: Optional[str] = None) -> None:
+    """Event loop: receive -> schedule -> forward -> stream out (one forward per iteration)."""
+    import zmq
+
+    from .ipc_utils import make_socket, setup_subprocess_logging
+
+    setup_subprocess_logging(server_config.log_level)
+    try:
+        sched = build_scheduler(server_config, hf_config, quantization_method, kv_cache_dtype, device)
+    except Exception as exc:  # readiness handshake carries the failure to the parent
+        if pipe_writer is not None:
+            pipe_writer.send({"status": "error", "error": repr(exc)})
+        raise
+    ctx = zmq.Context()
+    recv = make_socket(ctx, zmq.PULL, recv_addr, bind=False)
+    send = make_socket(ctx, zmq.PUSH, send_addr, bind=True)
+    if pipe_writer is not None:
+        pipe_writer.send({"status": "ready", "max_total_num_tokens": sched.mrp.runner.max_total_num_tokens})
+    poller = zmq.Poller()
+    poller.register(recv, zmq.POLLIN)
+    while True:
+        # drain the inbox; sleep on the socket when there is nothing to run
+        timeout = 0 if sched.has_work() else 1000
+        while dict(poller.poll(timeout)):
+            msg = recv.recv_pyobj()
+            if msg is None:
+                return
+            if isinstance(msg, TokenizedGenerateReqInput):
+                err = sched.add_request(msg)
+                if err is not None:
+                    send.send_pyobj({"error": err, "rid": msg.rid})
+            elif isinstance(msg, AbortReq):
+                if sched.abort(msg.rid):
+                    send.send_pyobj(sched.abort_outputs([msg.rid]))
+            elif isinstance(msg, FlushCacheReq):
+                send.send_pyobj({"flush_cache": sched.flush_cache()})
+            timeout = 0
+        out = sched.step()
+        if out is not None:
+            send.send_pyobj(out)

