@@ -235,6 +235,16 @@ class Engine:
                 p.join(timeout=5)
                 if p.is_alive():
                     p.terminate()
+                    p.join(timeout=2)
+                if p.is_alive():
+                    p.kill()
+                    p.join(timeout=2)
+            for t in self._threads:
+                t.join(timeout=2)
+            try:
+                self._zmq.destroy(linger=0)
+            except Exception:
+                pass
             from ..orchestrator.ipc_utils import cleanup_ipc
 
             cleanup_ipc(self._addrs)
