@@ -182,6 +182,134 @@ void argmax(const Tensor& logits, Tensor& out) {
                        dtype_of(logits), stream_of(logits));
 }
 
+void sample(const Tensor& logits, const Tensor& temperature, const Tensor& top_k, const Tensor& top_p,
+            const c10::optional<Tensor>& min_p, const Tensor& uniform, Tensor& out) {
+  check_cuda(logits, "logits");
+  const int64_t rows = logits.size(0);
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && out.scalar_type() == at::kLong && out.is_contiguous() &&
+                  out.numel() == rows,
+              "sample: [B,V] logits, int64 out [B]");
+  TORCH_CHECK(temperature.scalar_type() == at::kFloat && top_p.scalar_type() == at::kFloat &&
+                  uniform.scalar_type() == at::kFloat && top_k.scalar_type() == at::kInt && temperature.numel() == rows &&
+                  top_p.numel() == rows && top_k.numel() == rows && uniform.numel() == rows && temperature.is_cuda() &&
+                  top_k.is_cuda() && top_p.is_cuda() && uniform.is_cuda(),
+              "sample: per-row parameter vectors on the device");
+  if (min_p.has_value())
+    TORCH_CHECK(min_p->scalar_type() == at::kFloat && min_p->numel() == rows && min_p->is_cuda(), "sample: min_p");
+  c10::cuda::CUDAGuard g(logits.device());
+  mb200::launch_sample(logits.data_ptr(), logits.stride(0), rows, logits.size(1), temperature.data_ptr<float>(),
+                       top_k.data_ptr<int>(), top_p.data_ptr<float>(), min_p.has_value() ? min_p->data_ptr<float>() : nullptr,
+                       uniform.data_ptr<float>(), out.data_ptr<int64_t>(), dtype_of(logits), stream_of(logits));
+}
+
+void apply_penalties(Tensor& logits, const Tensor& counts, const c10::optional<Tensor>& prompt_mask, const Tensor& freq,
+                     const Tensor& presence, const Tensor& repetition) {
+  check_cuda(logits, "logits");
+  TORCH_CHECK(logits.dim() == 2 && logits.is_contiguous() && logits.scalar_type() == at::kFloat && counts.is_contiguous() &&
+                  counts.scalar_type() == at::kInt && counts.sizes() == logits.sizes() && counts.is_cuda(),
+              "apply_penalties: fp32 logits and int32 counts [B,V]");
+  if (prompt_mask.has_value())
+    TORCH_CHECK(prompt_mask->scalar_type() == at::kByte && prompt_mask->is_contiguous() &&
+                    prompt_mask->sizes() == logits.sizes() && prompt_mask->is_cuda(),
+                "apply_penalties: uint8 prompt mask [B,V]");
+  const int64_t rows = logits.size(0);
+  for (const Tensor* t : {&freq, &presence, &repetition})
+    TORCH_CHECK(t->scalar_type() == at::kFloat && t->numel() == rows && t->is_cuda() && t->is_contiguous(),
+                "apply_penalties: fp32 [B] penalties");
+  c10::cuda::CUDAGuard g(logits.device());
+  mb200::launch_apply_penalties(logits.data_ptr<float>(), counts.data_ptr<int>(),
+                                prompt_mask.has_value() ? prompt_mask->data_ptr<uint8_t>() : nullptr,
+                                freq.data_ptr<float>(), presence.data_ptr<float>(), repetition.data_ptr<float>(), rows,
+                                logits.size(1), stream_of(logits));
+}
+
+// ---- mixture of experts ----
+void moe_router_topk(const Tensor& logits, Tensor& w, Tensor& ids, bool renorm) {
+  check_cuda(logits, "logits");
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && logits.size(1) <= 256, "moe_router_topk: [T,E<=256] logits");
+  TORCH_CHECK(w.scalar_type() == at::kFloat && ids.scalar_type() == at::kInt && w.is_contiguous() && ids.is_contiguous() &&
+                  w.dim() == 2 && w.size(0) == logits.size(0) && w.size(1) <= 32 && ids.sizes() == w.sizes(),
+              "moe_router_topk: fp32 weights / int32 ids [T,k<=32]");
+  c10::cuda::CUDAGuard g(logits.device());
+  mb200::launch_moe_router_topk(logits.data_ptr(), logits.stride(0), w.data_ptr<float>(), ids.data_ptr<int>(),
+                                logits.size(0), logits.size(1), w.size(1), renorm ? 1 : 0, dtype_of(logits),
+                                stream_of(logits));
+}
+
+void moe_align(const Tensor& topk_ids, int64_t expert_offset, int64_t experts, int64_t bn, Tensor& sorted_pos,
+               Tensor& src_token, Tensor& expert_offsets, Tensor& work, Tensor& n_work) {
+  check_cuda(topk_ids, "topk_ids");
+  TORCH_CHECK(topk_ids.scalar_type() == at::kInt && topk_ids.is_contiguous() && topk_ids.dim() == 2, "moe_align: int32 [T,k] ids");
+  TORCH_CHECK(experts >= 1 && experts <= 256, "moe_align: 1..256 local experts");
+  const int64_t pairs = topk_ids.numel();
+  for (const Tensor* t : {&sorted_pos, &src_token, &expert_offsets, &work, &n_work})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kInt && t->is_contiguous(), "moe_align: int32 outputs");
+  TORCH_CHECK(sorted_pos.numel() >= pairs && src_token.numel() >= pairs && expert_offsets.numel() >= experts + 1 &&
+                  work.dim() == 2 && work.size(1) == 2 && n_work.numel() >= 1,
+              "moe_align: output sizes");
+  c10::cuda::CUDAGuard g(topk_ids.device());
+  mb200::launch_moe_align(topk_ids.data_ptr<int>(), pairs, topk_ids.size(1), expert_offset, experts, bn,
+                          sorted_pos.data_ptr<int>(), src_token.data_ptr<int>(), expert_offsets.data_ptr<int>(),
+                          work.data_ptr<int>(), n_work.data_ptr<int>(), work.size(0), stream_of(topk_ids));
+}
+
+void moe_gather(const Tensor& x, const Tensor& src_token, const Tensor& expert_offsets, Tensor& xs) {
+  check_cuda(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && x.size(1) % 8 == 0 && x.stride(0) % 8 == 0 && xs.is_contiguous() &&
+                  xs.size(1) == x.size(1) && x.element_size() == 2 && xs.scalar_type() == x.scalar_type(),
+              "moe_gather: 16-bit rows, hidden % 8 == 0");
+  c10::cuda::CUDAGuard g(x.device());
+  mb200::launch_moe_gather(x.data_ptr(), x.stride(0), src_token.data_ptr<int>(), expert_offsets.data_ptr<int>(),
+                           expert_offsets.numel() - 1, xs.data_ptr(), xs.size(0), x.size(1), stream_of(x));
+}
+
+void moe_combine(const Tensor& y, const Tensor& sorted_pos, const Tensor& topk_w, Tensor& out) {
+  check_cuda(y, "y");
+  TORCH_CHECK(y.is_contiguous() && out.is_contiguous() && y.size(1) == out.size(1) && y.size(1) % 8 == 0 &&
+                  topk_w.scalar_type() == at::kFloat && topk_w.is_contiguous() && topk_w.size(0) == out.size(0) &&
+                  sorted_pos.numel() >= topk_w.numel() && y.scalar_type() == out.scalar_type() && y.element_size() == 2,
+              "moe_combine: shapes");
+  c10::cuda::CUDAGuard g(y.device());
+  mb200::launch_moe_combine(y.data_ptr(), sorted_pos.data_ptr<int>(), topk_w.data_ptr<float>(), out.data_ptr(),
+                            out.size(0), out.size(1), topk_w.size(1), dtype_of(y), stream_of(y));
+}
+
+// out[rows of e] = x[rows of e] @ w[e]^T (SwiGLU-fused when swiglu) over the expert-sorted rows
+void moe_grouped_gemm(const Tensor& x, const Tensor& w, Tensor& out, const Tensor& expert_offsets, const Tensor& work,
+                      const Tensor& n_work, int64_t bn, bool swiglu) {
+  check_cuda(x, "x");
+  check_cuda(w, "w");
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 3 && out.dim() == 2 && x.stride(1) == 1 && w.is_contiguous() && out.stride(1) == 1 &&
+                  x.size(1) == w.size(2) && x.scalar_type() == w.scalar_type() && out.scalar_type() == x.scalar_type() &&
+                  x.element_size() == 2,
+              "moe_grouped_gemm: x [R,K], w [E,N,K], 16-bit");
+  TORCH_CHECK(out.size(0) == x.size(0) && out.size(1) == (swiglu ? w.size(1) / 2 : w.size(1)), "moe_grouped_gemm: out shape");
+  TORCH_CHECK(expert_offsets.numel() == w.size(0) + 1, "moe_grouped_gemm: offsets");
+  c10::cuda::CUDAGuard g(x.device());
+  DeviceState& st = device_state(x.get_device());
+  mb200::MoeGemmArgs a{};
+  a.x = x.data_ptr();
+  a.w = w.data_ptr();
+  a.out = out.data_ptr();
+  a.expert_offsets = expert_offsets.data_ptr<int>();
+  a.work = work.data_ptr<int>();
+  a.n_work = n_work.data_ptr<int>();
+  a.status = st.status.data_ptr<int>();
+  a.ldx = x.stride(0);
+  a.ldc = out.stride(0);
+  a.rows_cap = x.size(0);
+  a.experts = w.size(0);
+  a.n = w.size(1);
+  a.k = w.size(2);
+  a.bn = bn;
+  a.max_work = work.size(0);
+  a.swiglu = swiglu ? 1 : 0;
+  a.num_sms = st.num_sms;
+  a.dt = dtype_of(x);
+  const int rc = mb200::launch_moe_grouped_gemm(a, stream_of(x));
+  TORCH_CHECK(rc == 0, "moe_grouped_gemm: unsupported shape or launch failure (code ", rc, ")");
+}
+
 // out = a @ b^T (+bias) (+residual) | swiglu.  a [M,K], b [N,K].
 void gemm(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<Tensor>& bias,
           const c10::optional<Tensor>& residual, bool swiglu, const c10::optional<Tensor>& a_scale,
@@ -374,7 +502,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("kv_write", &kv_write);
   m.def("per_token_quant_int8", &per_token_quant_int8);
   m.def("argmax", &argmax);
+  m.def("sample", &sample);
+  m.def("apply_penalties", &apply_penalties);
   m.def("gemm", &gemm);
+  m.def("moe_router_topk", &moe_router_topk);
+  m.def("moe_align", &moe_align);
+  m.def("moe_gather", &moe_gather);
+  m.def("moe_combine", &moe_combine);
+  m.def("moe_grouped_gemm", &moe_grouped_gemm);
   m.def("attention_prefill", &attention_prefill);
   m.def("attention_decode", &attention_decode);
   m.def("tp_reduce_add_rmsnorm", &tp_reduce_add_rmsnorm);

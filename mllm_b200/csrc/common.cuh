@@ -312,6 +312,20 @@ __device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
   return __bfloat1622float2(v);
 }
 
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+__device__ __forceinline__ float to_f32(float v) { return v; }
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) {
+  return __float2half_rn(v);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -322,6 +336,16 @@ __device__ __forceinline__ float warp_max(float v) {
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
 }
+
+// run a statement with T bound to the 16-bit element type named by a DType value
+#define MB200_DISPATCH_HALF(dt, ...)          \
+  if ((dt) == ::mb200::kBF16) {               \
+    using T = __nv_bfloat16;                  \
+    __VA_ARGS__;                              \
+  } else {                                    \
+    using T = __half;                         \
+    __VA_ARGS__;                              \
+  }
 
 // Host side: launch with the programmatic-stream-serialization attribute (MLLM_B200_PDL=0 turns
 // it off).  Works under stream capture: the dependency becomes a programmatic graph edge.

@@ -71,19 +71,6 @@ __device__ __forceinline__ uint4 pack8<__half>(const float (&f)[8]) {
   for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
   return r;
 }
-__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
-__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
-__device__ __forceinline__ float to_f32(float v) { return v; }
-template <typename T>
-__device__ __forceinline__ T from_f32(float v);
-template <>
-__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
-  return __float2bfloat16_rn(v);
-}
-template <>
-__device__ __forceinline__ __half from_f32<__half>(float v) {
-  return __float2half_rn(v);
-}
 template <typename T>
 __device__ __forceinline__ float round_to(float v);
 template <>
@@ -486,14 +473,6 @@ inline int norm_threads(int hidden) {
 
 }  // namespace
 
-#define MB200_DISPATCH_HALF(dt, ...)          \
-  if ((dt) == kBF16) {                        \
-    using T = __nv_bfloat16;                  \
-    __VA_ARGS__;                              \
-  } else {                                    \
-    using T = __half;                         \
-    __VA_ARGS__;                              \
-  }
 
 void launch_rmsnorm(const void* x, const void* w, void* out, int rows, int hidden, int64_t x_stride,
                     int64_t out_stride, float eps, DType dt, cudaStream_t s) {

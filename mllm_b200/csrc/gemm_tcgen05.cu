@@ -599,6 +599,13 @@ int launch_cfg(const CUtensorMap& tr, const CUtensorMap& tc, KParams p, int grid
 
 }  // namespace
 
+bool make_tma_operand_map(void* map, const void* base, int64_t rows, int64_t k, int64_t ld, int elem_bytes, int type,
+                          int box_rows) {
+  const CUtensorMapDataType t = type == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                          : (type == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+  return make_operand_map(static_cast<CUtensorMap*>(map), base, rows, k, ld, elem_bytes, t, box_rows);
+}
+
 size_t gemm_workspace_bytes(int, int, int, int) { return size_t(64) << 20; }
 
 int launch_gemm(const GemmArgs& a, cudaStream_t s) {

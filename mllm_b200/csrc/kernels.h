@@ -50,6 +50,13 @@ void launch_per_token_quant_int8(const void* x, int8_t* q, float* scale, int row
 void launch_argmax(const void* logits, int64_t* out, int rows, int vocab, int64_t stride, DType dt,
                    cudaStream_t s);
 
+// one token per row: temperature (<= 1e-6: greedy), top-k (<= 0: off), top-p, min-p (may be null),
+// inverse-CDF draw with uniform[row] in [0, 1)
+void launch_sample(const void* logits, int64_t stride, int rows, int vocab, const float* temperature, const int* top_k,
+                   const float* top_p, const float* min_p, const float* uniform, int64_t* out, DType dt, cudaStream_t s);
+void launch_apply_penalties(float* logits, const int* counts, const uint8_t* prompt_mask, const float* freq,
+                            const float* presence, const float* repetition, int rows, int vocab, cudaStream_t s);
+
 // ----- GEMM (tcgen05 + TMEM + TMA) ---------------------------------------------------
 struct GemmArgs {
   const void* a;         // [m, k] row-major activations
@@ -74,6 +81,38 @@ struct GemmArgs {
 // Returns 0 on success, a negative code when the shape is unsupported (caller falls back / raises).
 int launch_gemm(const GemmArgs& args, cudaStream_t s);
 size_t gemm_workspace_bytes(int m, int n, int k, int num_sms);
+
+// 128-byte-swizzled 2-D tensor map over a row-major [rows, k] matrix (box = 128 bytes of k x box_rows);
+// map points at a CUtensorMap.  type: 0 bf16, 1 fp16, 2 uint8.
+bool make_tma_operand_map(void* map, const void* base, int64_t rows, int64_t k, int64_t ld, int elem_bytes, int type,
+                          int box_rows);
+
+// ----- mixture of experts ----------------------------------------------------------------
+// router: fp32 softmax over `experts` (<= 256) logits -> top_k (<= 32, sorted, lowest index wins ties)
+void launch_moe_router_topk(const void* logits, int64_t stride, float* w, int* ids, int tokens, int experts, int top_k,
+                            int renorm, DType dt, cudaStream_t s);
+// counting sort of the (token, choice) pairs by local expert.  sorted_pos[pair] = row in the sorted
+// matrix or -1 (expert on another rank); src_token[row] = token; expert_offsets[experts + 1];
+// work[i] = (expert, chunk of bn rows), *n_work items.
+void launch_moe_align(const int* topk_ids, int pairs, int top_k, int expert_offset, int experts, int bn, int* sorted_pos,
+                      int* src_token, int* expert_offsets, int* work, int* n_work, int max_work, cudaStream_t s);
+void launch_moe_gather(const void* x, int64_t x_stride, const int* src_token, const int* expert_offsets, int experts,
+                       void* xs, int pairs, int hidden, cudaStream_t s);
+void launch_moe_combine(const void* y, const int* sorted_pos, const float* topk_w, void* out, int tokens, int hidden,
+                        int top_k, DType dt, cudaStream_t s);
+struct MoeGemmArgs {
+  const void* x;    // [rows_cap, k] expert-sorted activations
+  const void* w;    // [experts, n, k]
+  void* out;        // [rows_cap, n_out]
+  const int* expert_offsets;
+  const int* work;
+  const int* n_work;
+  int* status;
+  int64_t ldx, ldc;
+  int rows_cap, experts, n, k, bn, max_work, swiglu, num_sms;
+  DType dt;
+};
+int launch_moe_grouped_gemm(const MoeGemmArgs& args, cudaStream_t s);
 
 // ----- attention over the slot-indexed KV pool (tcgen05, head_dim 128) -----------------
 struct AttnArgs {

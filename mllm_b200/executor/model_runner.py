@@ -255,6 +255,8 @@ class ModelRunner:
             qm = getattr(m, "quant_method", None)
             if qm is not None:
                 qm.process_weights_after_loading(m)
+        if hasattr(self.model, "post_load"):
+            self.model.post_load()
         self.model.eval()
 
     @torch.no_grad()

@@ -298,6 +298,75 @@ def attention_varlen_bidirectional(q, k, v, cu_seqlens, scale: float) -> torch.T
 
 
 # --------------------------------------------------------------------------
+# mixture of experts
+# --------------------------------------------------------------------------
+def moe_router_topk(hidden: torch.Tensor, gate_weight: torch.Tensor, top_k: int, renormalize: bool = True):
+    """Router: fp32 softmax over experts -> sorted top-k -> optional renormalisation."""
+    if use_kernels(hidden) and hasattr(ext(), "moe_router_topk") and gate_weight.shape[0] <= 256 and top_k <= 8:
+        logits = linear(hidden, gate_weight)  # [T, E] on the tensor cores; the kernel does the rest in fp32
+        T = hidden.shape[0]
+        w = torch.empty((T, top_k), dtype=torch.float32, device=hidden.device)
+        ids = torch.empty((T, top_k), dtype=torch.int32, device=hidden.device)
+        ext().moe_router_topk(logits, w, ids, renormalize)
+        return w, ids
+    return ref.moe_router_topk(hidden, gate_weight, top_k, renormalize)
+
+
+def moe_chunk_rows(tokens: int, top_k: int, num_experts_global: int) -> int:
+    """MMA N (rows of one expert handled per work item) for the grouped GEMM: about twice the mean
+    number of rows per expert, within the instruction's 16..128 range."""
+    avg = max(1, (tokens * top_k + num_experts_global - 1) // num_experts_global)
+    for bn in (16, 32, 64):
+        if 2 * avg <= bn + bn // 2:
+            return bn
+    return 128
+
+
+def moe_experts(x, w13, w2, topk_w, topk_ids, expert_offset: int = 0, swiglu_block: int = 0,
+                num_experts_global: Optional[int] = None) -> torch.Tensor:
+    """Grouped expert MLPs.  On the GPU everything stays on the device (no host read of the routing,
+    so the step can be captured in a CUDA graph): pairs are counting-sorted by expert, activations
+    gathered into expert order, both expert GEMMs run as one grouped tcgen05 launch each (SwiGLU fused
+    into the first when ``w13`` is stored in 128-row gate/up blocks), and the k results per token are
+    summed with the router weights."""
+    if not use_kernels(x):
+        return ref.moe_experts(x, w13, w2, topk_w, topk_ids, expert_offset, swiglu_block)
+    if swiglu_block not in (0, SWIGLU_BLOCK):
+        raise ValueError(f"w13 interleave block must be 0 or {SWIGLU_BLOCK}")
+    T, H = x.shape
+    E, N13, _ = w13.shape
+    inter = N13 // 2
+    k = topk_ids.shape[1]
+    P = T * k
+    dev = x.device
+    bn = moe_chunk_rows(T, k, num_experts_global or E)
+    max_work = E + (P + bn - 1) // bn
+    i32 = dict(dtype=torch.int32, device=dev)
+    sorted_pos = torch.empty(P, **i32)
+    src_token = torch.empty(P, **i32)
+    offsets = torch.empty(E + 1, **i32)
+    work = torch.empty((max_work, 2), **i32)
+    n_work = torch.empty(1, **i32)
+    e = ext()
+    ids = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
+    e.moe_align(ids.contiguous(), int(expert_offset), E, bn, sorted_pos, src_token, offsets, work, n_work)
+    xs = torch.empty((P, H), dtype=x.dtype, device=dev)
+    e.moe_gather(x, src_token, offsets, xs)
+    h = torch.empty((P, inter), dtype=x.dtype, device=dev)
+    if swiglu_block:
+        e.moe_grouped_gemm(xs, w13, h, offsets, work, n_work, bn, True)
+    else:
+        gu = torch.empty((P, N13), dtype=x.dtype, device=dev)
+        e.moe_grouped_gemm(xs, w13, gu, offsets, work, n_work, bn, False)
+        e.act_and_mul(gu, h, 0)
+    ys = torch.empty((P, H), dtype=x.dtype, device=dev)
+    e.moe_grouped_gemm(h, w2, ys, offsets, work, n_work, bn, False)
+    out = torch.empty((T, H), dtype=x.dtype, device=dev)
+    e.moe_combine(ys, sorted_pos, topk_w.contiguous(), out)
+    return out
+
+
+# --------------------------------------------------------------------------
 # sampling
 # --------------------------------------------------------------------------
 def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -315,8 +384,28 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
     return o
 
 
-apply_penalties = ref.apply_penalties
+def apply_penalties(logits, output_counts, prompt_mask, frequency_penalty, presence_penalty, repetition_penalty):
+    """Frequency / presence / repetition penalties; returns fp32 logits."""
+    if not use_kernels(logits):
+        return ref.apply_penalties(logits, output_counts, prompt_mask, frequency_penalty, presence_penalty,
+                                   repetition_penalty)
+    lf = logits.float().contiguous()
+    if lf.data_ptr() == logits.data_ptr():
+        lf = lf.clone()
+    pm = None if prompt_mask is None else prompt_mask.to(torch.uint8).contiguous()
+    ext().apply_penalties(lf, output_counts.to(torch.int32).contiguous(), pm, frequency_penalty.float().contiguous(),
+                          presence_penalty.float().contiguous(), repetition_penalty.float().contiguous())
+    return lf
 
 
 def top_k_top_p_min_p_sample(logits, temperature, top_k, top_p, min_p, uniform) -> torch.Tensor:
-    return ref.top_k_top_p_min_p_sample(logits, temperature, top_k, top_p, min_p, uniform)
+    """One token per row: temperature, top-k, top-p, min-p, inverse-CDF draw (one kernel, no sort)."""
+    if not use_kernels(logits):
+        return ref.top_k_top_p_min_p_sample(logits, temperature, top_k, top_p, min_p, uniform)
+    l2 = _2d(logits)
+    if l2.stride(-1) != 1:
+        l2 = l2.contiguous()
+    out = torch.empty((l2.shape[0],), dtype=torch.int64, device=logits.device)
+    ext().sample(l2, temperature.float().contiguous(), top_k.to(torch.int32).contiguous(), top_p.float().contiguous(),
+                 None if min_p is None else min_p.float().contiguous(), uniform.float().contiguous(), out)
+    return out

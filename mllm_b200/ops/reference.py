@@ -312,9 +312,13 @@ def top_k_top_p_min_p_sample(
     logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
     min_p: Optional[torch.Tensor], uniform: torch.Tensor,
 ) -> torch.Tensor:
-    """Sample one id per row. ``temperature<=1e-6`` rows are greedy; ``top_k<=0`` disables top-k.
-    ``uniform`` [B] in [0,1) drives inverse-CDF sampling over the filtered, renormalised
-    distribution taken in descending-probability order (ties broken by lower token id)."""
+    """Sample one id per row.  ``temperature <= 1e-6`` rows are greedy; ``top_k <= 0`` disables top-k.
+
+    With ``e = exp((logits - max) / T)`` every filter is a cut-off on ``e`` (values equal to the cut-off
+    are all kept): top-k keeps ``e >= k-th largest``; top-p keeps the values whose strictly-larger mass
+    is below ``top_p * sum(e)``; min-p keeps ``e >= min_p`` (the largest ``e`` is 1).  ``uniform`` [B]
+    in [0,1) drives inverse-CDF sampling over the kept set in token-id order: the first id whose running
+    kept mass exceeds ``u * kept_mass``."""
     B, V = logits.shape
     out = torch.empty(B, dtype=torch.long, device=logits.device)
     for b in range(B):
@@ -323,22 +327,57 @@ def top_k_top_p_min_p_sample(
         if t <= 1e-6:
             out[b] = torch.argmax(row)
             continue
-        p = torch.softmax(row / t, dim=-1)
-        sp, si = torch.sort(p, descending=True, stable=True)
-        keep = torch.ones(V, dtype=torch.bool, device=logits.device)
+        e = torch.exp((row - row.max()) / t).double()
+        tau = 0.0
         k = int(top_k[b])
+        se = torch.sort(e, descending=True).values
         if 0 < k < V:
-            keep[k:] = False
-        cum = torch.cumsum(sp, 0)
-        keep &= (cum - sp) < float(top_p[b])
+            tau = max(tau, float(se[k - 1]))
+        tp = float(top_p[b])
+        if tp < 1.0:
+            before = torch.cumsum(se, 0) - se
+            n = int((before < max(tp * float(se.sum()), 1e-30)).sum())
+            tau = max(tau, float(se[max(n, 1) - 1]))
         if min_p is not None and float(min_p[b]) > 0:
-            keep &= sp >= float(min_p[b]) * sp[0]
-        keep[0] = True
-        sp = torch.where(keep, sp, torch.zeros_like(sp))
-        cdf = torch.cumsum(sp, 0)
-        u = float(uniform[b]) * float(cdf[-1])
-        idx = int(torch.searchsorted(cdf, torch.tensor(u, device=cdf.device), right=True).clamp(max=V - 1))
-        while idx > 0 and not bool(keep[idx]):
-            idx -= 1
-        out[b] = si[idx]
+            tau = max(tau, min(float(min_p[b]), 1.0))
+        kept = torch.where(e >= tau, e, torch.zeros_like(e))
+        cdf = torch.cumsum(kept, 0)
+        target = float(uniform[b]) * float(cdf[-1])
+        idx = int((cdf > target).nonzero()[0]) if bool((cdf > target).any()) else int((kept > 0).nonzero()[-1])
+        out[b] = idx
     return out
+
+
+# --------------------------------------------------------------------------
+# mixture of experts
+# --------------------------------------------------------------------------
+def moe_router_topk(hidden: torch.Tensor, gate_weight: torch.Tensor, top_k: int, renormalize: bool = True):
+    """fp32 ``softmax(hidden @ gate_weight.T)`` over all experts -> top-k (sorted by weight) ->
+    optional renormalisation of the k weights (mllm/models/qwen3_moe/modeling_qwen3_moe_fa2.hpp:121-138).
+    Returns (weights fp32 [T, k], expert ids int32 [T, k])."""
+    logits = _f32(hidden) @ _f32(gate_weight).t()
+    scores = torch.softmax(logits, dim=-1)
+    w, idx = torch.topk(scores, top_k, dim=-1, sorted=True)
+    if renormalize:
+        w = w / w.sum(-1, keepdim=True)
+    return w, idx.to(torch.int32)
+
+
+def moe_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor,
+                expert_offset: int = 0, swiglu_block: int = 0) -> torch.Tensor:
+    """Sum over the k routed experts of ``w * down_e(silu(gate_e(x)) * up_e(x))``.
+
+    ``w13`` [E_local, 2I, H] (rows ``[gate ; up]``, or interleaved in ``swiglu_block`` rows), ``w2``
+    [E_local, H, I]; expert ids outside ``[expert_offset, expert_offset + E_local)`` contribute
+    nothing (they live on another expert-parallel rank)."""
+    T, H = x.shape
+    out = torch.zeros((T, H), dtype=torch.float32, device=x.device)
+    E = w13.shape[0]
+    for e in range(E):
+        tok, slot = (topk_ids == (e + expert_offset)).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        h = linear_swiglu(x[tok], w13[e], swiglu_block)
+        y = linear(h, w2[e], out_dtype=torch.float32)
+        out.index_add_(0, tok, y * topk_w[tok, slot].unsqueeze(-1).float())
+    return out.to(x.dtype)

@@ -134,9 +134,9 @@ def test_residual_carry_order():
     from mllm_b200.layers import norm as norm_mod
     orig = norm_mod.RMSNorm.forward
 
-    def spy(self, x, residual=None):
+    def spy(self, x, residual=None, **kw):
         calls.append(residual is not None)
-        return orig(self, x, residual)
+        return orig(self, x, residual, **kw)
 
     norm_mod.RMSNorm.forward = spy
     try:
