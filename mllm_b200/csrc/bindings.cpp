@@ -275,7 +275,7 @@ void moe_combine(const Tensor& y, const Tensor& sorted_pos, const Tensor& topk_w
 }
 
 // out[rows of e] = x[rows of e] @ w[e]^T (SwiGLU-fused when swiglu) over the expert-sorted rows
-void moe_grouped_gemm(const Tensor& x, const Tensor& w, Tensor& out, const Tensor& expert_offsets, const Tensor& work,
+int64_t moe_grouped_gemm(const Tensor& x, const Tensor& w, Tensor& out, const Tensor& expert_offsets, const Tensor& work,
                       const Tensor& n_work, int64_t bn, bool swiglu) {
   check_cuda(x, "x");
   check_cuda(w, "w");
@@ -306,12 +306,11 @@ void moe_grouped_gemm(const Tensor& x, const Tensor& w, Tensor& out, const Tenso
   a.swiglu = swiglu ? 1 : 0;
   a.num_sms = st.num_sms;
   a.dt = dtype_of(x);
-  const int rc = mb200::launch_moe_grouped_gemm(a, stream_of(x));
-  TORCH_CHECK(rc == 0, "moe_grouped_gemm: unsupported shape or launch failure (code ", rc, ")");
+  return mb200::launch_moe_grouped_gemm(a, stream_of(x));
 }
 
 // out = a @ b^T (+bias) (+residual) | swiglu.  a [M,K], b [N,K].
-void gemm(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<Tensor>& bias,
+int64_t gemm(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<Tensor>& bias,
           const c10::optional<Tensor>& residual, bool swiglu, const c10::optional<Tensor>& a_scale,
           const c10::optional<Tensor>& b_scale) {
   check_cuda(a, "a");
@@ -365,9 +364,8 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<Ten
   args.num_counters = st.counters.numel();
   args.status = st.status.data_ptr<int>();
   args.num_sms = st.num_sms;
-  const int rc = mb200::launch_gemm(args, stream_of(a));
-  TORCH_CHECK(rc == 0, "mllm_b200 gemm: unsupported shape or launch failure (code ", rc, ") for M=", args.m,
-              " N=", args.n, " K=", args.k);
+  // 0 on success; a negative code (unsupported shape / launch failure) is raised by the Python caller
+  return mb200::launch_gemm(args, stream_of(a));
 }
 
 void attention_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& req_to_token,

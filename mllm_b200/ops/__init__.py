@@ -133,6 +133,19 @@ def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
 # --------------------------------------------------------------------------
 # GEMMs
 # --------------------------------------------------------------------------
+def _gemm(a, b, out, bias, residual, swiglu, a_scale, b_scale) -> None:
+    rc = ext().gemm(a, b, out, bias, residual, swiglu, a_scale, b_scale)
+    if rc != 0:
+        raise RuntimeError(f"mllm_b200 gemm: unsupported shape or launch failure (code {rc}) for "
+                           f"M={a.shape[0]} N={b.shape[0]} K={a.shape[1]}")
+
+
+def _gemm_shape_ok(x2: torch.Tensor, weight: torch.Tensor) -> bool:
+    """The tcgen05 GEMM needs 16-byte aligned rows on every operand and the output."""
+    per16 = 16 // x2.element_size()
+    return weight.shape[0] % 8 == 0 and x2.shape[1] % per16 == 0 and weight.stride(0) % per16 == 0 and weight.stride(1) == 1
+
+
 SWIGLU_BLOCK = 128  # row interleave of fused gate/up weights expected by linear_swiglu
 
 
@@ -150,9 +163,17 @@ def linear(
     x2 = _2d(x)
     if x2.stride(-1) != 1 or (x2.stride(0) * x2.element_size()) % 16:
         x2 = x2.contiguous()
+    if not _gemm_shape_ok(x2, weight):  # odd tiny shapes (e.g. a 4-expert router): library matmul
+        y = torch.nn.functional.linear(x2, weight, bias)
+        if residual is not None:
+            y = y + _2d(residual)
+        if out is not None:
+            out.copy_(y.view(out.shape))
+            return out
+        return y.view(*x.shape[:-1], weight.shape[0])
     o = torch.empty((x2.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device) if out is None else _2d(out)
     r2 = None if residual is None else _2d(residual)
-    ext().gemm(x2, weight, o, bias, r2, False, None, None)
+    _gemm(x2, weight, o, bias, r2, False, None, None)
     return o.view(*x.shape[:-1], weight.shape[0]) if out is None else out
 
 
@@ -164,7 +185,7 @@ def linear_swiglu(x: torch.Tensor, weight: torch.Tensor, block: int = SWIGLU_BLO
     if x2.stride(-1) != 1 or (x2.stride(0) * x2.element_size()) % 16:
         x2 = x2.contiguous()
     o = torch.empty((x2.shape[0], weight.shape[0] // 2), dtype=x.dtype, device=x.device)
-    ext().gemm(x2, weight, o, None, None, True, None, None)
+    _gemm(x2, weight, o, None, None, True, None, None)
     return o.view(*x.shape[:-1], weight.shape[0] // 2)
 
 
@@ -181,7 +202,7 @@ def int8_scaled_mm(a_q, w_q, a_scale, w_scale, out_dtype, bias=None) -> torch.Te
         return ref.int8_scaled_mm(a_q, w_q, a_scale, w_scale, out_dtype, bias)
     a2 = _2d(a_q).contiguous()
     out = torch.empty((a2.shape[0], w_q.shape[0]), dtype=out_dtype, device=a_q.device)
-    ext().gemm(a2, w_q, out, bias, None, False, a_scale.reshape(-1).contiguous(), w_scale.reshape(-1).contiguous())
+    _gemm(a2, w_q, out, bias, None, False, a_scale.reshape(-1).contiguous(), w_scale.reshape(-1).contiguous())
     return out.view(*a_q.shape[:-1], w_q.shape[0])
 
 
@@ -322,6 +343,13 @@ def moe_chunk_rows(tokens: int, top_k: int, num_experts_global: int) -> int:
     return 128
 
 
+def _moe_gemm(x, w, out, offsets, work, n_work, bn, swiglu) -> None:
+    rc = ext().moe_grouped_gemm(x, w, out, offsets, work, n_work, bn, swiglu)
+    if rc != 0:
+        raise RuntimeError(f"mllm_b200 moe_grouped_gemm: unsupported shape or launch failure (code {rc}) for "
+                           f"x={tuple(x.shape)} w={tuple(w.shape)}")
+
+
 def moe_experts(x, w13, w2, topk_w, topk_ids, expert_offset: int = 0, swiglu_block: int = 0,
                 num_experts_global: Optional[int] = None) -> torch.Tensor:
     """Grouped expert MLPs.  On the GPU everything stays on the device (no host read of the routing,
@@ -354,13 +382,13 @@ def moe_experts(x, w13, w2, topk_w, topk_ids, expert_offset: int = 0, swiglu_blo
     e.moe_gather(x, src_token, offsets, xs)
     h = torch.empty((P, inter), dtype=x.dtype, device=dev)
     if swiglu_block:
-        e.moe_grouped_gemm(xs, w13, h, offsets, work, n_work, bn, True)
+        _moe_gemm(xs, w13, h, offsets, work, n_work, bn, True)
     else:
         gu = torch.empty((P, N13), dtype=x.dtype, device=dev)
-        e.moe_grouped_gemm(xs, w13, gu, offsets, work, n_work, bn, False)
+        _moe_gemm(xs, w13, gu, offsets, work, n_work, bn, False)
         e.act_and_mul(gu, h, 0)
     ys = torch.empty((P, H), dtype=x.dtype, device=dev)
-    e.moe_grouped_gemm(h, w2, ys, offsets, work, n_work, bn, False)
+    _moe_gemm(h, w2, ys, offsets, work, n_work, bn, False)
     out = torch.empty((T, H), dtype=x.dtype, device=dev)
     e.moe_combine(ys, sorted_pos, topk_w.contiguous(), out)
     return out
