@@ -310,9 +310,19 @@ int64_t moe_grouped_gemm(const Tensor& x, const Tensor& w, Tensor& out, const Te
 }
 
 // out = a @ b^T (+bias) (+residual) | swiglu.  a [M,K], b [N,K].
-int64_t gemm(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<Tensor>& bias,
-          const c10::optional<Tensor>& residual, bool swiglu, const c10::optional<Tensor>& a_scale,
-          const c10::optional<Tensor>& b_scale) {
+struct TpFusion {
+  const uint32_t* gate_flags = nullptr;
+  uint32_t gate_epoch = 0;
+  int rs_tp = 0, rs_rank = 0;
+  uint32_t rs_epoch = 0;
+  int64_t rs_ld = 0;
+  uint64_t rs_out[8] = {0}, rs_flags[8] = {0};
+  int* rs_count = nullptr;
+};
+
+int64_t gemm_impl(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<Tensor>& bias,
+                  const c10::optional<Tensor>& residual, bool swiglu, const c10::optional<Tensor>& a_scale,
+                  const c10::optional<Tensor>& b_scale, const TpFusion* tp) {
   check_cuda(a, "a");
   check_cuda(b, "b");
   const bool is_int8 = a.scalar_type() == at::kChar;
@@ -364,8 +374,92 @@ int64_t gemm(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<
   args.num_counters = st.counters.numel();
   args.status = st.status.data_ptr<int>();
   args.num_sms = st.num_sms;
+  if (tp != nullptr) {
+    args.gate_flags = tp->gate_flags;
+    args.gate_epoch = tp->gate_epoch;
+    args.rs_tp = tp->rs_tp;
+    args.rs_rank = tp->rs_rank;
+    args.rs_epoch = tp->rs_epoch;
+    args.rs_ld = tp->rs_ld;
+    args.rs_count = tp->rs_count;
+    for (int r = 0; r < 8; ++r) {
+      args.rs_out[r] = tp->rs_out[r];
+      args.rs_flags[r] = tp->rs_flags[r];
+    }
+  }
   // 0 on success; a negative code (unsupported shape / launch failure) is raised by the Python caller
   return mb200::launch_gemm(args, stream_of(a));
+}
+
+int64_t gemm(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<Tensor>& bias,
+             const c10::optional<Tensor>& residual, bool swiglu, const c10::optional<Tensor>& a_scale,
+             const c10::optional<Tensor>& b_scale) {
+  return gemm_impl(a, b, out, bias, residual, swiglu, a_scale, b_scale, nullptr);
+}
+
+// Tensor-parallel prefill GEMM.  gate_flags (uint32 as int32 tensor, one per 128-row tile of a) delays
+// the load of a row tile until its flag reaches gate_epoch.  With rs_out_ptrs (one address per rank: this
+// rank's slot in that rank's inbox) the output tiles are stored into the owners' inboxes instead of
+// `out` (which only supplies shape and dtype) and rs_flag_ptrs[owner][local tile * 8 + rank] is set to
+// rs_epoch per completed row tile.
+int64_t gemm_tp(const Tensor& a, const Tensor& b, Tensor& out, bool swiglu, const c10::optional<Tensor>& gate_flags,
+                int64_t gate_epoch, std::vector<int64_t> rs_out_ptrs, std::vector<int64_t> rs_flag_ptrs,
+                const c10::optional<Tensor>& rs_count, int64_t rs_rank, int64_t rs_epoch, int64_t rs_ld) {
+  TpFusion tp;
+  if (gate_flags.has_value()) {
+    TORCH_CHECK(gate_flags->is_cuda() && gate_flags->scalar_type() == at::kInt && gate_flags->is_contiguous() &&
+                    gate_flags->numel() * 128 >= a.size(0),
+                "gemm_tp: gate flags");
+    tp.gate_flags = reinterpret_cast<const uint32_t*>(gate_flags->data_ptr<int>());
+    tp.gate_epoch = static_cast<uint32_t>(gate_epoch);
+  }
+  if (!rs_out_ptrs.empty()) {
+    TORCH_CHECK(rs_out_ptrs.size() == rs_flag_ptrs.size() && rs_out_ptrs.size() <= 8 && rs_count.has_value() &&
+                    rs_count->is_cuda() && rs_count->scalar_type() == at::kInt && rs_count->numel() * 128 >= a.size(0),
+                "gemm_tp: reduce-scatter arguments");
+    tp.rs_tp = static_cast<int>(rs_out_ptrs.size());
+    tp.rs_rank = static_cast<int>(rs_rank);
+    tp.rs_epoch = static_cast<uint32_t>(rs_epoch);
+    tp.rs_ld = rs_ld;
+    tp.rs_count = rs_count->data_ptr<int>();
+    for (size_t r = 0; r < rs_out_ptrs.size(); ++r) {
+      tp.rs_out[r] = static_cast<uint64_t>(rs_out_ptrs[r]);
+      tp.rs_flags[r] = static_cast<uint64_t>(rs_flag_ptrs[r]);
+    }
+  }
+  return gemm_impl(a, b, out, c10::nullopt, c10::nullopt, swiglu, c10::nullopt, c10::nullopt, &tp);
+}
+
+int64_t tp_rs_add_rmsnorm_ag(const Tensor& inbox, const Tensor& tile_flags, Tensor& residual_shard, const Tensor& weight,
+                             std::vector<int64_t> peer_hidden, std::vector<int64_t> peer_gather_flags, Tensor& ag_count,
+                             int64_t rank, int64_t epoch, double eps) {
+  check_half(residual_shard, "residual_shard");
+  TORCH_CHECK(inbox.dim() == 3 && inbox.is_contiguous() && residual_shard.dim() == 2 && residual_shard.is_contiguous() &&
+                  inbox.size(2) == residual_shard.size(1) && inbox.size(1) >= residual_shard.size(0) &&
+                  inbox.scalar_type() == residual_shard.scalar_type() && weight.scalar_type() == residual_shard.scalar_type(),
+              "tp_rs_add_rmsnorm_ag: inbox [tp, rows_cap, hidden], residual shard [rows, hidden]");
+  TORCH_CHECK(peer_hidden.size() == peer_gather_flags.size() && static_cast<int64_t>(peer_hidden.size()) == inbox.size(0) &&
+                  peer_hidden.size() <= 8,
+              "tp_rs_add_rmsnorm_ag: peer lists");
+  TORCH_CHECK(tile_flags.scalar_type() == at::kInt && ag_count.scalar_type() == at::kInt &&
+                  ag_count.numel() * 128 >= residual_shard.size(0) && tile_flags.numel() * 16 >= residual_shard.size(0),
+              "tp_rs_add_rmsnorm_ag: flag blocks");
+  c10::cuda::CUDAGuard g(residual_shard.device());
+  auto& st = device_state(residual_shard.get_device());
+  std::vector<uint64_t> h(peer_hidden.begin(), peer_hidden.end()), f(peer_gather_flags.begin(), peer_gather_flags.end());
+  return mb200::launch_tp_rs_add_rmsnorm_ag(
+      inbox.data_ptr(), inbox.size(1), reinterpret_cast<const uint32_t*>(tile_flags.data_ptr<int>()),
+      residual_shard.data_ptr(), weight.data_ptr(), h.data(), f.data(), ag_count.data_ptr<int>(), residual_shard.size(0),
+      residual_shard.size(1), static_cast<int>(h.size()), static_cast<int>(rank), static_cast<uint32_t>(epoch),
+      static_cast<float>(eps), dtype_of(residual_shard), st.status.data_ptr<int>(), stream_of(residual_shard));
+}
+
+int64_t tp_wait_flags(const Tensor& flags, int64_t n, int64_t epoch) {
+  TORCH_CHECK(flags.is_cuda() && flags.scalar_type() == at::kInt && flags.numel() >= n, "tp_wait_flags: int32 flags");
+  c10::cuda::CUDAGuard g(flags.device());
+  auto& st = device_state(flags.get_device());
+  return mb200::launch_tp_wait_flags(reinterpret_cast<const uint32_t*>(flags.data_ptr<int>()), static_cast<int>(n),
+                                     static_cast<uint32_t>(epoch), st.status.data_ptr<int>(), stream_of(flags));
 }
 
 void attention_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& req_to_token,
@@ -503,6 +597,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sample", &sample);
   m.def("apply_penalties", &apply_penalties);
   m.def("gemm", &gemm);
+  m.def("gemm_tp", &gemm_tp);
+  m.def("tp_rs_add_rmsnorm_ag", &tp_rs_add_rmsnorm_ag);
+  m.def("tp_wait_flags", &tp_wait_flags);
   m.def("moe_router_topk", &moe_router_topk);
   m.def("moe_align", &moe_align);
   m.def("moe_gather", &moe_gather);

@@ -147,7 +147,157 @@ __global__ void tp_reduce_add_rmsnorm_kernel(PeerPtrs peers, uint32_t* __restric
   if (threadIdx.x == 0) local_seq[row] = expect;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// prefill: reduce-scatter (from the inbox the peers' GEMM epilogues filled) + residual add + RMSNorm
+// + all-gather by peer stores.  grid = own rows, block = hidden / 8 threads (<= 1024).
+// ---------------------------------------------------------------------------------------------
+struct GatherPtrs {
+  void* hidden[kMaxTp];
+  uint32_t* flags[kMaxTp];
+};
+
+template <typename T>
+__global__ void tp_rs_add_rmsnorm_ag_kernel(const T* __restrict__ inbox, int64_t inbox_rows_cap,
+                                            const uint32_t* __restrict__ tile_flags, T* __restrict__ residual,
+                                            const T* __restrict__ weight, GatherPtrs peers, int* __restrict__ ag_count,
+                                            int rows, int hidden, int tp, int rank, uint32_t epoch, float eps,
+                                            int* status) {
+  __shared__ float red[33];
+  __shared__ int wait_ok;
+  pdl_wait();
+  const int row = blockIdx.x;
+  const int tile = row >> 7;
+  if (threadIdx.x == 0) wait_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < tp) {
+    if (!wait_flag_ge(tile_flags + tile * kMaxTp + threadIdx.x, epoch)) {
+      wait_ok = 0;
+      if (status != nullptr) atomicExch(status, kStatusPeerTimeout);
+    }
+  }
+  __syncthreads();
+  if (!wait_ok) return;
+  const int nvec = hidden >> 3;
+  float cache[kVecPerThread][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < kVecPerThread; ++it) {
+    const int v = threadIdx.x + it * blockDim.x;
+    if (v < nvec) {
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      for (int r = 0; r < tp; ++r) {
+        const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(inbox + (static_cast<int64_t>(r) * inbox_rows_cap + row) * hidden) + v);
+        float f[8];
+        unpack8v<T>(raw, f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += f[i];
+      }
+      uint4* rp = reinterpret_cast<uint4*>(residual + static_cast<int64_t>(row) * hidden) + v;
+      float g[8];
+      unpack8v<T>(*rp, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = to_f(from_f<T>(acc[i] + g[i]));
+      *rp = pack8v<T>(acc);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        cache[it][i] = acc[i];
+        ss += acc[i] * acc[i];
+      }
+    }
+  }
+  ss = warp_sum(ss);
+  if (lane_id() == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < ((blockDim.x + 31) >> 5) ? red[threadIdx.x] : 0.f;
+    t = warp_sum(t);
+    if (threadIdx.x == 0) red[32] = t;
+  }
+  __syncthreads();
+  const float rstd = rsqrtf(red[32] / static_cast<float>(hidden) + eps);
+  const int64_t grow = static_cast<int64_t>(rank) * rows + row;
+#pragma unroll
+  for (int it = 0; it < kVecPerThread; ++it) {
+    const int v = threadIdx.x + it * blockDim.x;
+    if (v < nvec) {
+      float g[8], o[8];
+      unpack8v<T>(reinterpret_cast<const uint4*>(weight)[v], g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = cache[it][i] * rstd * g[i];
+      const uint4 packed = pack8v<T>(o);
+      for (int r = 0; r < tp; ++r) {
+        const int dst = (rank + r) % tp;  // start with the local copy, spread the peers
+        reinterpret_cast<uint4*>(static_cast<T*>(peers.hidden[dst]) + grow * hidden)[v] = packed;
+      }
+    }
+  }
+  // publish the row; the last row of a 128-row tile raises the tile's flag on every rank
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int old = atomicAdd(&ag_count[tile], 1);
+    const int rows_in_tile = min(128, rows - tile * 128);
+    if (old == rows_in_tile - 1) {
+      ag_count[tile] = 0;
+      __threadfence_system();
+      const int gtile = static_cast<int>(grow >> 7);
+      for (int r = 0; r < tp; ++r) st_release_sys(peers.flags[r] + gtile, epoch);
+    }
+  }
+}
+
+__global__ void tp_wait_flags_kernel(const uint32_t* __restrict__ flags, int n, uint32_t epoch, int* status) {
+  pdl_wait();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    if (!wait_flag_ge(flags + i, epoch)) {
+      if (status != nullptr) atomicExch(status, kStatusPeerTimeout);
+      return;
+    }
+  }
+}
+
 }  // namespace
+
+int launch_tp_rs_add_rmsnorm_ag(const void* inbox, int64_t inbox_rows_cap, const uint32_t* tile_flags,
+                                void* residual_shard, const void* weight, const uint64_t* peer_hidden,
+                                const uint64_t* peer_gather_flags, int* ag_count, int rows, int hidden, int tp,
+                                int rank, uint32_t epoch, float eps, DType dt, int* status, cudaStream_t s) {
+  if (rows == 0) return 0;
+  if (tp < 1 || tp > kMaxTp || hidden % 8 != 0 || hidden > 8 * 1024 * kVecPerThread || rows % 128 != 0 ||
+      residual_shard == nullptr || weight == nullptr)
+    return -1;
+  GatherPtrs gp{};
+  for (int r = 0; r < tp; ++r) {
+    gp.hidden[r] = reinterpret_cast<void*>(peer_hidden[r]);
+    gp.flags[r] = reinterpret_cast<uint32_t*>(peer_gather_flags[r]);
+  }
+  int threads = ((hidden >> 3) + 31) / 32 * 32;
+  if (threads > 1024) threads = 1024;
+  if (threads < 32) threads = 32;
+  cudaError_t err;
+  if (dt == kBF16) {
+    err = launch_pdl(tp_rs_add_rmsnorm_ag_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, s,
+                     static_cast<const __nv_bfloat16*>(inbox), inbox_rows_cap, tile_flags,
+                     static_cast<__nv_bfloat16*>(residual_shard), static_cast<const __nv_bfloat16*>(weight), gp, ag_count,
+                     rows, hidden, tp, rank, epoch, eps, status);
+  } else {
+    err = launch_pdl(tp_rs_add_rmsnorm_ag_kernel<__half>, dim3(rows), dim3(threads), 0, s,
+                     static_cast<const __half*>(inbox), inbox_rows_cap, tile_flags, static_cast<__half*>(residual_shard),
+                     static_cast<const __half*>(weight), gp, ag_count, rows, hidden, tp, rank, epoch, eps, status);
+  }
+  note_launch();
+  return err == cudaSuccess ? 0 : -4;
+}
+
+int launch_tp_wait_flags(const uint32_t* flags, int n, uint32_t epoch, int* status, cudaStream_t s) {
+  if (n <= 0) return 0;
+  const cudaError_t err = launch_pdl(tp_wait_flags_kernel, dim3(1), dim3(256), 0, s, flags, n, epoch, status);
+  note_launch();
+  return err == cudaSuccess ? 0 : -4;
+}
 
 int launch_tp_reduce_add_rmsnorm(const uint64_t* peer_data, const uint64_t* peer_flags, uint32_t* local_seq,
                                  void* residual, const void* weight, void* out, int rows, int hidden, int tp, int rank,
@@ -175,5 +325,6 @@ int launch_tp_reduce_add_rmsnorm(const uint64_t* peer_data, const uint64_t* peer
   note_launch();
   return err == cudaSuccess ? 0 : -4;
 }
+
 
 }  // namespace mb200

@@ -55,7 +55,23 @@ struct KParams {
   int out_f16;           // 0: bf16 output, 1: fp16 output
   int is_int8;
   uint32_t idesc;
+  // ---- tensor-parallel fusion (normal tiling only) ----
+  // all-gather -> GEMM: row tile t of the activations may be read once gate_flags[t] >= gate_epoch
+  const uint32_t* gate_flags;
+  uint32_t gate_epoch;
+  // GEMM -> reduce-scatter: row tile t belongs to rank t / rs_tiles_per_rank; the tile is stored into
+  // that rank's inbox (rs_out[owner], this rank's slot) and, once all column tiles of the row tile
+  // have been stored, rs_flags[owner][local tile * 8 + rs_rank] is set to rs_epoch
+  int rs_tp, rs_rank, rs_tiles_per_rank;
+  uint32_t rs_epoch;
+  int64_t rs_ld;
+  void* rs_out[8];
+  uint32_t* rs_flags[8];
+  int* rs_count;
 };
+
+constexpr int kStageRowBytes = 144;                      // 128 bytes of output + 16 bytes of padding
+constexpr int kEpiStagingBytes = 4 * 32 * kStageRowBytes;  // four epilogue warps x 32 rows
 
 // RT = 128-row MMA tiles of the row operand per stage (small-batch tiling only; SwiGLU needs 2: a
 // gate block and its up block), KD = 128-byte K atoms per stage.  Larger stages mean fewer TMA boxes
@@ -122,6 +138,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   int* ticket_slot = const_cast<int*>(abort_flag) + 1;
+  uint8_t* epi_staging = reinterpret_cast<uint8_t*>(bars) + 512;  // normal tiling only
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -211,6 +228,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
     int tr, tc, kb0, kb1;
     for (int idx = 0; ok && get_work(idx, tr, tc, kb0, kb1); ++idx) {
       const int k_elems_per_block = p.is_int8 ? kRowBytes : kRowBytes / 2;
+      if constexpr (!SWAP) {
+        if (p.gate_flags != nullptr) {
+          // rows of this tile are written by peers (generic proxy); the TMA engine reads them
+          if (!wait_flag_ge(p.gate_flags + tr, p.gate_epoch)) {
+            ok = false;
+            if (p.status != nullptr) atomicExch(p.status, kStatusPeerTimeout);
+            break;
+          }
+          fence_proxy_async_all();
+        }
+      }
       for (int kb = kb0; kb < kb1; ++kb) {
         if (*abort_flag || !mbar_wait(&empty_bar[stage], phase ^ 1)) {
           ok = false;
@@ -306,13 +334,95 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
       const uint32_t t_base = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + acc * C::kAccCols;
 
       if constexpr (!SWAP) {
+        constexpr int kOutCols = SWIGLU ? BN / 2 : BN;
+        const int64_t col0 = static_cast<int64_t>(tc) * kOutCols;
+        const int n_out = SWIGLU ? p.n / 2 : p.n;
+        if (p.residual == nullptr) {
+          // Staged epilogue: a thread owns one accumulator row; 64 output columns at a time are
+          // rounded, parked in shared memory and written back so that eight lanes cover 128
+          // contiguous bytes of one output row (full-line stores, local or to a peer's inbox).
+          uint8_t* stage_buf = epi_staging + ew * (32 * kStageRowBytes);
+          const int64_t tile_row0 = static_cast<int64_t>(tr) * kBM + ew * 32;
+          const float sa = (p.is_int8 && tile_row0 + lane < p.m) ? p.a_scale[tile_row0 + lane] : 1.f;
+          uint16_t* dst_base = static_cast<uint16_t*>(p.out);
+          int64_t dst_ld = p.ldc;
+          int64_t dst_row0 = tile_row0;
+          int owner = 0, local_tile = 0;
+          if (p.rs_tp > 0) {
+            owner = tr / p.rs_tiles_per_rank;
+            local_tile = tr - owner * p.rs_tiles_per_rank;
+            dst_base = static_cast<uint16_t*>(p.rs_out[owner]);
+            dst_ld = p.rs_ld;
+            dst_row0 = static_cast<int64_t>(local_tile) * kBM + ew * 32;
+          }
+#pragma unroll 1
+          for (int c = 0; c < kOutCols; c += 64) {
+            uint32_t packed[32];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t r0[32], r1[32];
+              tmem_ld_32x32(t_base + c + h * 32, r0);
+              if constexpr (SWIGLU) tmem_ld_32x32(t_base + BN / 2 + c + h * 32, r1);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; j += 2) {
+                float f[2];
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                  const int cc = c + h * 32 + j + q;  // column inside the tile's output
+                  float x = acc_to_float(r0[j + q], p.is_int8);
+                  if constexpr (SWIGLU) {
+                    float u = acc_to_float(r1[j + q], p.is_int8);
+                    if (p.is_int8) {
+                      x *= sa * p.b_scale[tc * BN + cc];
+                      u *= sa * p.b_scale[tc * BN + BN / 2 + cc];
+                    }
+                    x = silu_f(x) * u;
+                  } else {
+                    const int64_t col = col0 + cc;
+                    if (p.is_int8 && col < n_out) x *= sa * p.b_scale[col];
+                    if (p.bias != nullptr && col < n_out) x += load_out1(p.bias, col, p.out_f16);
+                  }
+                  f[q] = x;
+                }
+                packed[h * 16 + j / 2] = pack_out2(f[0], f[1], p.out_f16);
+              }
+            }
+            uint4* my_row = reinterpret_cast<uint4*>(stage_buf + lane * kStageRowBytes);
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              my_row[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = i * 4 + (lane >> 3);
+              const int piece = lane & 7;
+              const int64_t col = col0 + c + piece * 8;
+              if (tile_row0 + r < p.m && col < n_out) {
+                const uint4 v = *reinterpret_cast<const uint4*>(stage_buf + r * kStageRowBytes + piece * 16);
+                *reinterpret_cast<uint4*>(dst_base + (dst_row0 + r) * dst_ld + col) = v;
+              }
+            }
+            __syncwarp();
+          }
+          if (p.rs_tp > 0) {
+            // publish: every epilogue thread orders its peer stores, then one thread counts the tile in
+            __threadfence_system();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (row_in_tile == 0) {
+              const int old = atomicAdd(&p.rs_count[tr], 1);
+              if (old == p.tiles_c - 1) {
+                p.rs_count[tr] = 0;  // self-reset for the next launch
+                __threadfence_system();
+                st_release_sys(p.rs_flags[owner] + local_tile * 8 + p.rs_rank, p.rs_epoch);
+              }
+            }
+          }
+        } else {
         // thread = one output row; columns in chunks of 32
         const int64_t row = static_cast<int64_t>(tr) * kBM + row_in_tile;
         const bool row_ok = row < p.m;
         const float sa = (p.is_int8 && row_ok) ? p.a_scale[row] : 1.f;
-        constexpr int kOutCols = SWIGLU ? BN / 2 : BN;
-        const int64_t col0 = static_cast<int64_t>(tc) * kOutCols;
-        const int n_out = SWIGLU ? p.n / 2 : p.n;
 #pragma unroll 1
         for (int c = 0; c < kOutCols; c += 32) {
           uint32_t r0[32], r1[32];
@@ -364,6 +474,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
             o.w = pack_out2(f[6], f[7], p.out_f16);
             *reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + row * p.ldc + col) = o;
           }
+        }
         }
       } else {
         // thread = one weight row (output column); accumulator column j = activation row j
@@ -586,12 +697,12 @@ int launch_cfg(const CUtensorMap& tr, const CUtensorMap& tc, KParams p, int grid
   auto kern = gemm_tcgen05_kernel<BN, SWAP, SWIGLU, RT, KD>;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(static_cast<size_t>(C::kStages) * C::kStageBytes + 1024 + 512)) !=
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(static_cast<size_t>(C::kStages) * C::kStageBytes + 1024 + 512 + (SWAP ? 0 : kEpiStagingBytes))) !=
         cudaSuccess)
       return -3;
     attr_set = true;
   }
-  const size_t smem = static_cast<size_t>(p.stages) * C::kStageBytes + 1024 + 512;
+  const size_t smem = static_cast<size_t>(p.stages) * C::kStageBytes + 1024 + 512 + (SWAP ? 0 : kEpiStagingBytes);
   const cudaError_t err = launch_pdl(kern, dim3(grid), dim3(kThreads), smem, s, tr, tc, p);
   note_launch();
   return err == cudaSuccess ? 0 : -4;
@@ -645,6 +756,24 @@ int launch_gemm(const GemmArgs& a, cudaStream_t s) {
   const int num_sms = a.num_sms > 0 ? a.num_sms : 148;
   CUtensorMap tm_row, tm_col;
 
+  const bool tp_fused = a.gate_flags != nullptr || a.rs_tp > 0;
+  if (tp_fused && (a.m <= 256 || a.residual != nullptr)) return -5;
+  if (a.rs_tp > 0) {
+    if (a.rs_tp > 8 || a.m % (kBM * a.rs_tp) != 0 || a.rs_count == nullptr || a.rs_ld % 8 != 0) return -5;
+    p.rs_tp = a.rs_tp;
+    p.rs_rank = a.rs_rank;
+    p.rs_tiles_per_rank = a.m / kBM / a.rs_tp;
+    p.rs_epoch = a.rs_epoch;
+    p.rs_ld = a.rs_ld;
+    p.rs_count = a.rs_count;
+    for (int r = 0; r < a.rs_tp; ++r) {
+      p.rs_out[r] = reinterpret_cast<void*>(a.rs_out[r]);
+      p.rs_flags[r] = reinterpret_cast<uint32_t*>(a.rs_flags[r]);
+      if (a.rs_out[r] & 15) return -5;
+    }
+  }
+  p.gate_flags = a.gate_flags;
+  p.gate_epoch = a.gate_epoch;
   if (a.m > 256) {
     // ---- normal tiling: activations are the 128-row operand ----
     int bn = 256;

@@ -77,6 +77,20 @@ struct GemmArgs {
   int num_counters;
   int* status;           // device int, set non-zero when a bounded wait ran out
   int num_sms;
+  // ---- tensor-parallel fusion, large-m tiling only (all zero = off) ----
+  // all-gather -> GEMM: 128-row tile t of `a` is read only once gate_flags[t] >= gate_epoch
+  const uint32_t* gate_flags;
+  uint32_t gate_epoch;
+  // GEMM -> reduce-scatter: m must be a multiple of 128 * rs_tp; 128-row tile t goes to rank
+  // t / (m / 128 / rs_tp): stored at rs_out[owner] + local_row * rs_ld (this rank's slot of the owner's
+  // inbox), and rs_flags[owner][local_tile * 8 + rs_rank] is set to rs_epoch when the row tile is complete.
+  // rs_count: local int[m / 128], zero-initialised, self-resetting.  `out` is ignored.
+  int rs_tp, rs_rank;
+  uint32_t rs_epoch;
+  int64_t rs_ld;
+  uint64_t rs_out[8];
+  uint64_t rs_flags[8];
+  int* rs_count;
 };
 // Returns 0 on success, a negative code when the shape is unsupported (caller falls back / raises).
 int launch_gemm(const GemmArgs& args, cudaStream_t s);
@@ -146,5 +160,22 @@ int decode_num_splits(int batch, int hkv, int max_seq_len, int num_sms);
 int launch_tp_reduce_add_rmsnorm(const uint64_t* peer_data, const uint64_t* peer_flags, uint32_t* local_seq,
                                  void* residual, const void* weight, void* out, int rows, int hidden, int tp, int rank,
                                  int64_t row_stride, float eps, DType dt, int* status, cudaStream_t s);
+
+
+// ----- tensor-parallel prefill: reduce-scatter + residual add + RMSNorm + all-gather -------
+// This rank owns `rows` consecutive token rows (global rows rank * rows ...).  inbox: local
+// [tp][inbox_rows_cap][hidden] partial sums written by every rank's GEMM epilogue; tile_flags: local
+// uint32 [tiles][8], slot (tile, src) holds the epoch of src's last completed delivery of that 128-row
+// tile.  For each own row: sum the tp partials in rank order, add the residual shard (in place; when
+// residual is null the sum itself is the new residual... the caller passes the shard), normalise, and
+// store the row into every rank's gathered buffer (peer_hidden[r] + global_row * hidden).  When a
+// 128-row tile is complete, gather_flags[global tile] on every rank is set to `epoch`.
+// ag_count: local int[tiles], zero-initialised, self-resetting.  rows must be a multiple of 128.
+int launch_tp_rs_add_rmsnorm_ag(const void* inbox, int64_t inbox_rows_cap, const uint32_t* tile_flags,
+                                void* residual_shard, const void* weight, const uint64_t* peer_hidden,
+                                const uint64_t* peer_gather_flags, int* ag_count, int rows, int hidden, int tp,
+                                int rank, uint32_t epoch, float eps, DType dt, int* status, cudaStream_t s);
+// Bounded wait until flags[i] >= epoch for all i < n (makes peers' deliveries visible to later kernels).
+int launch_tp_wait_flags(const uint32_t* flags, int n, uint32_t epoch, int* status, cudaStream_t s);
 
 }  // namespace mb200

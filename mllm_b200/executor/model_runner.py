@@ -158,7 +158,10 @@ class ModelRunner:
         set_tp_comm(None)
         if pstate.get_tensor_model_parallel_world_size() > 1 and self.server_config.comm_backend == "fused":
             rows = max(256, min(1024, self.server_config.max_running_requests or 1))
-            set_tp_comm(TPComm.create(self.hidden_size, self.dtype, self.device, max_rows=256 if rows <= 256 else rows))
+            prefill_rows = int(self.server_config.chunked_prefill_size or 0) or 16384
+            prefill_rows = max(prefill_rows, int(getattr(self.server_config, "max_prefill_tokens", 0) or 0))
+            set_tp_comm(TPComm.create(self.hidden_size, self.dtype, self.device, max_rows=256 if rows <= 256 else rows,
+                                      prefill_rows=min(prefill_rows, 65536)))
 
     def _resolve_dtype(self) -> torch.dtype:
         want = self.server_config.dtype

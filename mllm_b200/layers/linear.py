@@ -135,6 +135,12 @@ class RowParallelLinear(LinearBase):
 
         comm = get_tp_comm()
         rows = x.numel() // x.shape[-1]
+        if (comm is not None and x.is_cuda and self.bias is None and comm.prefill_eligible(rows)
+                and isinstance(self.quant_method, UnquantizedLinearMethod) and self.out_features == comm.hidden):
+            from .. import ops
+
+            # prefill: the GEMM's epilogue scatters the tiles to the ranks that own the rows
+            return ops.tp_gemm_reduce_scatter(x, self.weight, comm)
         buf = comm.partial_buffer(rows) if (comm is not None and x.is_cuda and self.bias is None) else None
         if buf is not None and isinstance(self.quant_method, UnquantizedLinearMethod):
             from .. import ops

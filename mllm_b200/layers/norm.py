@@ -18,13 +18,26 @@ class RMSNorm(nn.Module):
                                    requires_grad=False)
         self.eps = eps
 
-    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, partial: bool = False
+    def forward(self, x, residual: Optional[torch.Tensor] = None, partial: bool = False, gated: bool = False
                 ) -> Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]:
         """Without ``residual``: returns the normed tensor.  With it: in place ``residual += x`` and
         ``x = norm(residual)``; returns ``(x, residual)``.  ``partial=True`` says ``x`` holds this
-        tensor-parallel rank's partial sums: the reduction over ranks is fused into the same step."""
+        tensor-parallel rank's partial sums: the reduction over ranks is fused into the same step.
+
+        When ``x`` is a ``PrefillPartial`` (the row-parallel GEMM scattered its tiles to the owning ranks)
+        the step is reduce-scatter + add + norm + all-gather; the returned residual is then this rank's
+        row shard, and ``gated=True`` promises that the consumer of the normed rows is a GEMM that waits
+        per row tile (otherwise the stream waits for the whole gather here)."""
+        from ..parallel.symm import PrefillPartial, get_tp_comm
+
+        if isinstance(x, PrefillPartial):
+            assert residual is not None
+            return ops.tp_rs_add_rmsnorm_ag(x, residual, self.weight, self.eps, get_tp_comm(), gated)
         if partial:
             assert residual is not None
+            if residual.shape[0] != x.shape[0]:
+                raise RuntimeError("row-sharded residual met a full partial sum: fused and plain tensor-parallel "
+                                   "steps were mixed inside one forward pass")
             return ops.tp_reduce_add_rmsnorm(x, residual, self.weight, self.eps), residual
         if residual is None:
             return ops.rmsnorm(x, self.weight, self.eps)

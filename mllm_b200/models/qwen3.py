@@ -25,6 +25,7 @@ from .. import ops
 from ..engine.forward_batch import ForwardBatch
 from ..layers import MLP, MergedLinear, RMSNorm, RadixAttention, RowParallelLinear, VocabParallelEmbedding
 from ..parallel import state as pstate
+from ..parallel.symm import get_tp_comm
 
 
 @dataclass
@@ -103,6 +104,12 @@ class Qwen3DecoderLayer(nn.Module):
         self.mlp = self._make_mlp(config, layer_id, quant_config, f"{prefix}.mlp", params_dtype)
         self.input_layernorm = RMSNorm(config.hidden_size, eps, params_dtype)
         self.post_attention_layernorm = RMSNorm(config.hidden_size, eps, params_dtype)
+        # the consumers of the two norms are plain tcgen05 GEMMs that can wait per gathered row tile
+        from ..layers.quantize_base import UnquantizedLinearMethod
+
+        self._gated_qkv = isinstance(self.self_attn.qkv_proj.quant_method, UnquantizedLinearMethod) and \
+            self.self_attn.qkv_proj.bias is None
+        self._gated_mlp = isinstance(self.mlp, MLP) and isinstance(self.mlp.gate_up_proj.quant_method, UnquantizedLinearMethod)
 
     def _make_mlp(self, config, layer_id, quant_config, prefix, params_dtype):
         return MLP(config.hidden_size, config.intermediate_size, quant_config, prefix, params_dtype)
@@ -114,10 +121,11 @@ class Qwen3DecoderLayer(nn.Module):
             residual = hidden
             hidden = self.input_layernorm(hidden)
         else:
-            hidden, residual = self.input_layernorm(hidden, residual, partial=self.self_attn.o_proj.tp_size > 1)
+            hidden, residual = self.input_layernorm(hidden, residual, partial=self.self_attn.o_proj.tp_size > 1,
+                                                    gated=self._gated_qkv)
         tp = self.self_attn.o_proj.tp_size > 1
         hidden = self.self_attn(hidden, forward_batch)
-        hidden, residual = self.post_attention_layernorm(hidden, residual, partial=tp)
+        hidden, residual = self.post_attention_layernorm(hidden, residual, partial=tp, gated=self._gated_mlp)
         hidden = self.mlp(hidden)  # partial sums again when tp > 1
         return hidden, residual
 
@@ -143,6 +151,10 @@ class Qwen3Model(nn.Module):
                 input_embeds: Optional[torch.Tensor] = None, deepstack_embeds=None) -> torch.Tensor:
         hidden = self.embed_tokens(input_ids) if input_embeds is None else input_embeds
         residual = None
+        comm = get_tp_comm()
+        if comm is not None:
+            # deepstack injection adds to the block output, which the fused prefill step never materialises
+            comm.prefill_fusion = deepstack_embeds is None
         for i, layer in enumerate(self.layers):
             hidden, residual = layer(hidden, residual, forward_batch)
             if deepstack_embeds is not None and i < len(deepstack_embeds):

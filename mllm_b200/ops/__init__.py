@@ -140,6 +140,89 @@ def _gemm(a, b, out, bias, residual, swiglu, a_scale, b_scale) -> None:
                            f"M={a.shape[0]} N={b.shape[0]} K={a.shape[1]}")
 
 
+def _take_gate(x2: torch.Tensor, gated_ok: bool):
+    """If ``x2`` is the gathered activation buffer of a fused tensor-parallel prefill step whose rows may
+    still be in flight, either hand the GEMM the flags to gate its loads on (returned) or wait here."""
+    from ..parallel.symm import get_tp_comm
+
+    comm = get_tp_comm()
+    if comm is None or comm.pending_gate is None or comm.prefill is None:
+        return None
+    if x2.data_ptr() != comm.prefill.hidden_full.data_ptr():
+        return None
+    epoch, rows = comm.pending_gate
+    comm.pending_gate = None
+    if gated_ok and x2.shape[0] == rows and rows > 256 and x2.dtype in (torch.bfloat16, torch.float16):
+        return (comm.prefill.gather_flags, epoch)
+    tp_wait_gather(comm, epoch, rows)
+    return None
+
+
+def tp_wait_gather(comm, epoch: int, rows: int) -> None:
+    """Block the stream until every 128-row tile of the gathered buffer has arrived."""
+    rc = ext().tp_wait_flags(comm.prefill.gather_flags, (rows + 127) // 128, epoch)
+    if rc != 0:
+        raise RuntimeError(f"mllm_b200 tp_wait_flags failed (code {rc})")
+
+
+def _gemm_tp(x2, weight, out, swiglu: bool, gate=None, rs=None) -> None:
+    """Tensor-parallel prefill GEMM: ``gate`` = (flags, epoch) delays row tiles until they have been
+    gathered; ``rs`` = (comm, epoch) sends output tiles to the owners' inboxes instead of ``out``."""
+    gflags, gepoch = (gate if gate is not None else (None, 0))
+    if rs is not None:
+        comm, epoch = rs
+        p = comm.prefill
+        own_cap = p.inbox.shape[1]
+        slot_bytes = own_cap * p.inbox.shape[2] * p.inbox.element_size()
+        outs = [ptr + comm.rank * slot_bytes for ptr in p.inbox_ptrs]
+        rc = ext().gemm_tp(x2, weight, out, swiglu, gflags, gepoch, outs, p.tile_flag_ptrs, p.rs_count, comm.rank, epoch,
+                           p.inbox.shape[2])
+    else:
+        rc = ext().gemm_tp(x2, weight, out, swiglu, gflags, gepoch, [], [], None, 0, 0, 0)
+    if rc != 0:
+        raise RuntimeError(f"mllm_b200 gemm_tp: unsupported shape or launch failure (code {rc}) for "
+                           f"M={x2.shape[0]} N={weight.shape[0]} K={x2.shape[1]}")
+
+
+def tp_gemm_reduce_scatter(x: torch.Tensor, weight: torch.Tensor, comm):
+    """Row-parallel GEMM whose epilogue stores each 128-row tile into the inbox of the rank that owns
+    those rows (reduce-scatter fused into the GEMM).  Returns a ``PrefillPartial`` token."""
+    from ..parallel.symm import PrefillPartial
+
+    x2 = _2d(x)
+    if x2.stride(-1) != 1 or (x2.stride(0) * x2.element_size()) % 16:
+        x2 = x2.contiguous()
+    epoch = comm.next_epoch()
+    shape_only = comm.prefill.hidden_full[: x2.shape[0]]  # supplies [M, N] shape / dtype; never written
+    gate = _take_gate(x2, gated_ok=True)
+    _gemm_tp(x2, weight, shape_only, False, gate=gate, rs=(comm, epoch))
+    return PrefillPartial(x2.shape[0], epoch, x.dtype, x.device)
+
+
+def tp_rs_add_rmsnorm_ag(partial, residual: torch.Tensor, weight: torch.Tensor, eps: float, comm, gated: bool):
+    """Second half of the fused prefill step: this rank sums the partials of the rows it owns, adds its
+    residual shard (``residual`` may still be the full ``[M, hidden]`` tensor: the own rows are split
+    off), normalises and stores the rows into every rank's gathered buffer.  Returns
+    ``(hidden_full[:M], residual_shard)``.  With ``gated`` the next GEMM waits per row tile; otherwise the
+    stream waits here for the whole gather."""
+    p = comm.prefill
+    rows = partial.rows
+    own = rows // comm.world
+    if residual.shape[0] == rows and comm.world > 1:
+        residual = residual[comm.rank * own:(comm.rank + 1) * own].clone()
+    assert residual.shape[0] == own and residual.is_contiguous()
+    inbox_view = p.inbox
+    rc = ext().tp_rs_add_rmsnorm_ag(inbox_view, p.tile_flags, residual, weight, p.hidden_ptrs, p.gather_flag_ptrs,
+                                    p.ag_count, comm.rank, partial.epoch, eps)
+    if rc != 0:
+        raise RuntimeError(f"mllm_b200 tp_rs_add_rmsnorm_ag failed (code {rc})")
+    if gated:
+        comm.pending_gate = (partial.epoch, rows)
+    else:
+        tp_wait_gather(comm, partial.epoch, rows)
+    return p.hidden_full[:rows], residual
+
+
 def _gemm_shape_ok(x2: torch.Tensor, weight: torch.Tensor) -> bool:
     """The tcgen05 GEMM needs 16-byte aligned rows on every operand and the output."""
     per16 = 16 // x2.element_size()
@@ -173,7 +256,11 @@ def linear(
         return y.view(*x.shape[:-1], weight.shape[0])
     o = torch.empty((x2.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device) if out is None else _2d(out)
     r2 = None if residual is None else _2d(residual)
-    _gemm(x2, weight, o, bias, r2, False, None, None)
+    gate = _take_gate(x2, gated_ok=bias is None and r2 is None)
+    if gate is not None:
+        _gemm_tp(x2, weight, o, False, gate=gate)
+    else:
+        _gemm(x2, weight, o, bias, r2, False, None, None)
     return o.view(*x.shape[:-1], weight.shape[0]) if out is None else out
 
 
@@ -185,7 +272,11 @@ def linear_swiglu(x: torch.Tensor, weight: torch.Tensor, block: int = SWIGLU_BLO
     if x2.stride(-1) != 1 or (x2.stride(0) * x2.element_size()) % 16:
         x2 = x2.contiguous()
     o = torch.empty((x2.shape[0], weight.shape[0] // 2), dtype=x.dtype, device=x.device)
-    _gemm(x2, weight, o, None, None, True, None, None)
+    gate = _take_gate(x2, gated_ok=True)
+    if gate is not None:
+        _gemm_tp(x2, weight, o, True, gate=gate)
+    else:
+        _gemm(x2, weight, o, None, None, True, None, None)
     return o.view(*x.shape[:-1], weight.shape[0] // 2)
 
 

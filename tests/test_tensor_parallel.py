@@ -42,3 +42,17 @@ def test_tp2_matches_tp1_on_gpu(tmp_path, graph):
     two = _launch(2, str(tmp_path / "tp2.pt"), "cuda", "bfloat16", 29614, {"TP_TEST_GRAPH": graph})
     assert (two - one).abs().max().item() < 0.15
     assert (two.argmax(-1) == one.argmax(-1)).float().mean().item() > 0.8
+
+
+@pytest.mark.gpu
+def test_tp2_fused_prefill_matches_nccl_on_gpu(tmp_path):
+    """A prefill large enough for the sequence-sharded path (GEMM epilogue scatters tiles to the owning
+    rank, reduce-scatter + add + norm + all-gather kernel, flag-gated consumer GEMM) gives the logits of
+    the plain all-reduce path, for the prefill and the decode steps that follow it."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = {"TP_TEST_PREFILL_LEN": "256"}
+    ref = _launch(2, str(tmp_path / "nccl.pt"), "cuda", "bfloat16", 29615, dict(env, TP_TEST_COMM="nccl"))
+    fused = _launch(2, str(tmp_path / "fused.pt"), "cuda", "bfloat16", 29616, dict(env, TP_TEST_COMM="fused"))
+    assert (fused - ref).abs().max().item() < 0.15
+    assert (fused.argmax(-1) == ref.argmax(-1)).float().mean().item() > 0.8

@@ -47,7 +47,9 @@ def run(out_path: str, device: str, dtype_name: str) -> None:
         pstate.initialize_model_parallel(tp_size=world)
     dev = device if device == "cpu" else f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}"
     cfg = get_preset("qwen3-tiny", num_attention_heads=4, num_key_value_heads=2, tie_word_embeddings=False)
-    sc = ServerConfig(model_path="preset:qwen3-tiny", dtype=dtype_name, max_running_requests=4, max_total_tokens=1024,
+    L = int(os.environ.get("TP_TEST_PREFILL_LEN", "9"))
+    sc = ServerConfig(model_path="preset:qwen3-tiny", dtype=dtype_name, max_running_requests=4,
+                      max_total_tokens=max(1024, 4 * L), chunked_prefill_size=max(2048, 2 * L),
                       tp_size=world, disable_cuda_graph=os.environ.get("TP_TEST_GRAPH", "0") != "1",
                       comm_backend=os.environ.get("TP_TEST_COMM", "fused"))
     mr = ModelRunner(sc, hf_config=cfg, device=dev)
@@ -63,7 +65,7 @@ def run(out_path: str, device: str, dtype_name: str) -> None:
         mr.init_cuda_graphs()
 
     torch.manual_seed(3)
-    B, L = 2, 9
+    B = 2
     ids = torch.randint(0, cfg.vocab_size, (B, L))
     slots = mr.req_to_token_pool.alloc(B)
     loc = mr.token_to_kv_pool_allocator.alloc(B * L)
