@@ -157,17 +157,19 @@ struct GatherPtrs {
   uint32_t* flags[kMaxTp];
 };
 
-template <typename T>
+constexpr int kRsRowsPerCta = 8;  // divides 128: a CTA's rows lie in one 128-row tile
+
+template <typename T, int VPT>
 __global__ void tp_rs_add_rmsnorm_ag_kernel(const T* __restrict__ inbox, int64_t inbox_rows_cap,
                                             const uint32_t* __restrict__ tile_flags, T* __restrict__ residual,
                                             const T* __restrict__ weight, GatherPtrs peers, int* __restrict__ ag_count,
                                             int rows, int hidden, int tp, int rank, uint32_t epoch, float eps,
                                             int* status) {
-  __shared__ float red[33];
+  __shared__ float red[2][33];
   __shared__ int wait_ok;
   pdl_wait();
-  const int row = blockIdx.x;
-  const int tile = row >> 7;
+  const int row0 = blockIdx.x * kRsRowsPerCta;
+  const int tile = row0 >> 7;
   if (threadIdx.x == 0) wait_ok = 1;
   __syncthreads();
   if (threadIdx.x < tp) {
@@ -179,71 +181,82 @@ __global__ void tp_rs_add_rmsnorm_ag_kernel(const T* __restrict__ inbox, int64_t
   __syncthreads();
   if (!wait_ok) return;
   const int nvec = hidden >> 3;
-  float cache[kVecPerThread][8];
-  float ss = 0.f;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  // the norm weight is the same for every row of the CTA
+  float gw[VPT][8];
 #pragma unroll
-  for (int it = 0; it < kVecPerThread; ++it) {
+  for (int it = 0; it < VPT; ++it) {
     const int v = threadIdx.x + it * blockDim.x;
-    if (v < nvec) {
-      float acc[8];
+    if (v < nvec) unpack8v<T>(reinterpret_cast<const uint4*>(weight)[v], gw[it]);
+  }
+#pragma unroll 1
+  for (int rr = 0; rr < kRsRowsPerCta; ++rr) {
+    const int row = row0 + rr;
+    float cache[VPT][8];
+    float ss = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-      for (int r = 0; r < tp; ++r) {
-        const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(inbox + (static_cast<int64_t>(r) * inbox_rows_cap + row) * hidden) + v);
-        float f[8];
-        unpack8v<T>(raw, f);
+    for (int it = 0; it < VPT; ++it) {
+      const int v = threadIdx.x + it * blockDim.x;
+      if (v < nvec) {
+        float acc[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] += f[i];
-      }
-      uint4* rp = reinterpret_cast<uint4*>(residual + static_cast<int64_t>(row) * hidden) + v;
-      float g[8];
-      unpack8v<T>(*rp, g);
+        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+        for (int r = 0; r < tp; ++r) {
+          const uint4 raw =
+              __ldcg(reinterpret_cast<const uint4*>(inbox + (static_cast<int64_t>(r) * inbox_rows_cap + row) * hidden) + v);
+          float f[8];
+          unpack8v<T>(raw, f);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = to_f(from_f<T>(acc[i] + g[i]));
-      *rp = pack8v<T>(acc);
+          for (int i = 0; i < 8; ++i) acc[i] += f[i];
+        }
+        uint4* rp = reinterpret_cast<uint4*>(residual + static_cast<int64_t>(row) * hidden) + v;
+        float g[8];
+        unpack8v<T>(*rp, g);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        cache[it][i] = acc[i];
-        ss += acc[i] * acc[i];
+        for (int i = 0; i < 8; ++i) acc[i] = to_f(from_f<T>(acc[i] + g[i]));
+        *rp = pack8v<T>(acc);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          cache[it][i] = acc[i];
+          ss += acc[i] * acc[i];
+        }
       }
     }
-  }
-  ss = warp_sum(ss);
-  if (lane_id() == 0) red[threadIdx.x >> 5] = ss;
-  __syncthreads();
-  if (threadIdx.x < 32) {
-    float t = threadIdx.x < ((blockDim.x + 31) >> 5) ? red[threadIdx.x] : 0.f;
+    // block sum of squares; the two halves of `red` alternate so one barrier per row suffices
+    float* rbuf = red[rr & 1];
+    ss = warp_sum(ss);
+    if (lane_id() == 0) rbuf[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float t = lane_id() < nwarps ? rbuf[lane_id()] : 0.f;
     t = warp_sum(t);
-    if (threadIdx.x == 0) red[32] = t;
-  }
-  __syncthreads();
-  const float rstd = rsqrtf(red[32] / static_cast<float>(hidden) + eps);
-  const int64_t grow = static_cast<int64_t>(rank) * rows + row;
+    const float rstd = rsqrtf(t / static_cast<float>(hidden) + eps);
+    const int64_t grow = static_cast<int64_t>(rank) * rows + row;
 #pragma unroll
-  for (int it = 0; it < kVecPerThread; ++it) {
-    const int v = threadIdx.x + it * blockDim.x;
-    if (v < nvec) {
-      float g[8], o[8];
-      unpack8v<T>(reinterpret_cast<const uint4*>(weight)[v], g);
+    for (int it = 0; it < VPT; ++it) {
+      const int v = threadIdx.x + it * blockDim.x;
+      if (v < nvec) {
+        float o[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) o[i] = cache[it][i] * rstd * g[i];
-      const uint4 packed = pack8v<T>(o);
-      for (int r = 0; r < tp; ++r) {
-        const int dst = (rank + r) % tp;  // start with the local copy, spread the peers
-        reinterpret_cast<uint4*>(static_cast<T*>(peers.hidden[dst]) + grow * hidden)[v] = packed;
+        for (int i = 0; i < 8; ++i) o[i] = cache[it][i] * rstd * gw[it][i];
+        const uint4 packed = pack8v<T>(o);
+        for (int r = 0; r < tp; ++r) {
+          const int dst = (rank + r) % tp;  // start with the local copy, spread the peers
+          reinterpret_cast<uint4*>(static_cast<T*>(peers.hidden[dst]) + grow * hidden)[v] = packed;
+        }
       }
     }
   }
-  // publish the row; the last row of a 128-row tile raises the tile's flag on every rank
-  __threadfence_system();
+  // publish: the barrier orders every thread's stores before thread 0's system-scope fence; the CTA
+  // that completes a 128-row tile raises the tile's flag on every rank
   __syncthreads();
   if (threadIdx.x == 0) {
-    const int old = atomicAdd(&ag_count[tile], 1);
+    __threadfence_system();
+    const int old = atomicAdd(&ag_count[tile], kRsRowsPerCta);
     const int rows_in_tile = min(128, rows - tile * 128);
-    if (old == rows_in_tile - 1) {
+    if (old == rows_in_tile - kRsRowsPerCta) {
       ag_count[tile] = 0;
       __threadfence_system();
-      const int gtile = static_cast<int>(grow >> 7);
+      const int gtile = static_cast<int>((static_cast<int64_t>(rank) * rows + row0) >> 7);
       for (int r = 0; r < tp; ++r) st_release_sys(peers.flags[r] + gtile, epoch);
     }
   }
@@ -277,17 +290,23 @@ int launch_tp_rs_add_rmsnorm_ag(const void* inbox, int64_t inbox_rows_cap, const
   int threads = ((hidden >> 3) + 31) / 32 * 32;
   if (threads > 1024) threads = 1024;
   if (threads < 32) threads = 32;
-  cudaError_t err;
+  const int vpt = ((hidden >> 3) + threads - 1) / threads;
+  cudaError_t err = cudaErrorInvalidValue;
+  const dim3 grid(rows / kRsRowsPerCta), block(threads);
+#define MB200_RS_LAUNCH(TT, V)                                                                                      \
+  err = launch_pdl(tp_rs_add_rmsnorm_ag_kernel<TT, V>, grid, block, 0, s, static_cast<const TT*>(inbox), inbox_rows_cap, \
+                   tile_flags, static_cast<TT*>(residual_shard), static_cast<const TT*>(weight), gp, ag_count, rows,   \
+                   hidden, tp, rank, epoch, eps, status)
   if (dt == kBF16) {
-    err = launch_pdl(tp_rs_add_rmsnorm_ag_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, s,
-                     static_cast<const __nv_bfloat16*>(inbox), inbox_rows_cap, tile_flags,
-                     static_cast<__nv_bfloat16*>(residual_shard), static_cast<const __nv_bfloat16*>(weight), gp, ag_count,
-                     rows, hidden, tp, rank, epoch, eps, status);
+    if (vpt == 1) MB200_RS_LAUNCH(__nv_bfloat16, 1);
+    else if (vpt == 2) MB200_RS_LAUNCH(__nv_bfloat16, 2);
+    else MB200_RS_LAUNCH(__nv_bfloat16, 4);
   } else {
-    err = launch_pdl(tp_rs_add_rmsnorm_ag_kernel<__half>, dim3(rows), dim3(threads), 0, s,
-                     static_cast<const __half*>(inbox), inbox_rows_cap, tile_flags, static_cast<__half*>(residual_shard),
-                     static_cast<const __half*>(weight), gp, ag_count, rows, hidden, tp, rank, epoch, eps, status);
+    if (vpt == 1) MB200_RS_LAUNCH(__half, 1);
+    else if (vpt == 2) MB200_RS_LAUNCH(__half, 2);
+    else MB200_RS_LAUNCH(__half, 4);
   }
+#undef MB200_RS_LAUNCH
   note_launch();
   return err == cudaSuccess ? 0 : -4;
 }

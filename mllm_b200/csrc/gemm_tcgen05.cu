@@ -135,7 +135,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
   uint64_t* empty_bar = bars + n_stages;
   uint64_t* acc_full = bars + 2 * n_stages;
   uint64_t* acc_empty = acc_full + 2;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* rs_done = acc_empty + 2;  // reduce-scatter: epilogue stores of an accumulator buffer issued
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(rs_done + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   int* ticket_slot = const_cast<int*>(abort_flag) + 1;
   uint8_t* epi_staging = reinterpret_cast<uint8_t*>(bars) + 512;  // normal tiling only
@@ -151,6 +152,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 128);
+      mbar_init(&rs_done[a], 128);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -317,6 +319,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
       *abort_flag = 1;
       if (p.status != nullptr) atomicExch(p.status, kStatusPipelineTimeout);
     }
+  } else if (warp == 3 && lane == 0 && !SWAP && p.rs_tp > 0) {
+    // ------------------------------ reduce-scatter publisher ------------------
+    // Waits until the epilogue threads have issued a tile's stores (mbarrier arrive / wait orders them
+    // before this thread), makes them visible system-wide with one fence, counts the tile in and, when the
+    // last column tile of a 128-row tile is done, raises the owner's flag.
+    int tr, tc, kb0, kb1;
+    for (int idx = 0; get_work(idx, tr, tc, kb0, kb1); ++idx) {
+      const int acc = idx % C::kAccBufs;
+      const uint32_t ph = (idx / C::kAccBufs) & 1;
+      if (*abort_flag || !mbar_wait(&rs_done[acc], ph)) {
+        *abort_flag = 1;
+        if (p.status != nullptr) atomicExch(p.status, kStatusPipelineTimeout);
+        break;
+      }
+      __threadfence_system();
+      const int owner = tr / p.rs_tiles_per_rank;
+      const int local_tile = tr - owner * p.rs_tiles_per_rank;
+      const int old = atomicAdd(&p.rs_count[tr], 1);
+      if (old == p.tiles_c - 1) {
+        p.rs_count[tr] = 0;  // self-reset for the next launch
+        __threadfence_system();
+        st_release_sys(p.rs_flags[owner] + local_tile * 8 + p.rs_rank, p.rs_epoch);
+      }
+    }
   } else if (warp >= 4) {
     // ------------------------------ epilogue -----------------------------------
     const int ew = warp - 4;             // TMEM lane quadrant
@@ -337,8 +363,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
         constexpr int kOutCols = SWIGLU ? BN / 2 : BN;
         const int64_t col0 = static_cast<int64_t>(tc) * kOutCols;
         const int n_out = SWIGLU ? p.n / 2 : p.n;
-        if (p.residual == nullptr) {
-          // Staged epilogue: a thread owns one accumulator row; 64 output columns at a time are
+        if (p.rs_tp > 0) {
+          // Staged epilogue (reduce-scatter stores only): a thread owns one accumulator row; 64 output columns at a time are
           // rounded, parked in shared memory and written back so that eight lanes cover 128
           // contiguous bytes of one output row (full-line stores, local or to a peer's inbox).
           uint8_t* stage_buf = epi_staging + ew * (32 * kStageRowBytes);
@@ -405,19 +431,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
             }
             __syncwarp();
           }
-          if (p.rs_tp > 0) {
-            // publish: every epilogue thread orders its peer stores, then one thread counts the tile in
-            __threadfence_system();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (row_in_tile == 0) {
-              const int old = atomicAdd(&p.rs_count[tr], 1);
-              if (old == p.tiles_c - 1) {
-                p.rs_count[tr] = 0;  // self-reset for the next launch
-                __threadfence_system();
-                st_release_sys(p.rs_flags[owner] + local_tile * 8 + p.rs_rank, p.rs_epoch);
-              }
-            }
-          }
+          // hand the tile to the publisher warp, which fences and signals off the epilogue's critical path
+          mbar_arrive(&rs_done[acc]);
         } else {
         // thread = one output row; columns in chunks of 32
         const int64_t row = static_cast<int64_t>(tr) * kBM + row_in_tile;

@@ -53,6 +53,6 @@ def test_tp2_fused_prefill_matches_nccl_on_gpu(tmp_path):
         pytest.skip("needs 2 GPUs")
     env = {"TP_TEST_PREFILL_LEN": "256"}
     ref = _launch(2, str(tmp_path / "nccl.pt"), "cuda", "bfloat16", 29615, dict(env, TP_TEST_COMM="nccl"))
-    fused = _launch(2, str(tmp_path / "fused.pt"), "cuda", "bfloat16", 29616, dict(env, TP_TEST_COMM="fused"))
+    fused = _launch(2, str(tmp_path / "fused.pt"), "cuda", "bfloat16", 29616, dict(env, TP_TEST_COMM="fused", TP_TEST_EXPECT_FUSED_PREFILL="1"))
     assert (fused - ref).abs().max().item() < 0.15
     assert (fused.argmax(-1) == ref.argmax(-1)).float().mean().item() > 0.8

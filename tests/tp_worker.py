@@ -88,6 +88,10 @@ def run(out_path: str, device: str, dtype_name: str) -> None:
         from mllm_b200 import ops
 
         ops.check_status()
+    if os.environ.get("TP_TEST_EXPECT_FUSED_PREFILL") == "1":
+        from mllm_b200.parallel.symm import get_tp_comm
+
+        assert get_tp_comm() is not None and get_tp_comm().epoch > 0, "fused prefill path was not taken"
     if rank == 0:
         torch.save(torch.stack(outs), out_path)
     if world > 1:
