@@ -54,6 +54,7 @@ class BenchArgs:
     profile_steps: int = 1
     skip_warmup: bool = False
     image_path: Optional[Path] = None
+    synthetic_image: bool = False
     prompt: str = "Describe this image."
     input_len_was_provided: bool = False
     correctness_test: bool = False
@@ -98,6 +99,8 @@ def add_bench_args(parser: argparse.ArgumentParser) -> argparse.ArgumentParser:
     g.add_argument("--profile-steps", type=_positive_int, default=1)
     g.add_argument("--skip-warmup", action="store_true")
     g.add_argument("--image", "--image-path", dest="image_path", type=Path, default=None)
+    g.add_argument("--synthetic-image", action="store_true",
+                   help="multimodal run with a seeded uniform-random 448x448 image per request")
     g.add_argument("--prompt", default=BenchArgs.prompt)
     g.add_argument("--correct", "--correctness-test", dest="correctness_test", action="store_true")
     return parser
@@ -124,7 +127,7 @@ def parse_args(argv: Optional[Sequence[str]] = None):
         profile_record_shapes=ns.profile_record_shapes, profile_activities=list(ns.profile_activities),
         profile_stage=ns.profile_stage, profile_filename_prefix=ns.profile_filename_prefix,
         profile_start_step=ns.profile_start_step, profile_steps=ns.profile_steps, skip_warmup=ns.skip_warmup,
-        image_path=ns.image_path, prompt=ns.prompt, input_len_was_provided=given,
+        image_path=ns.image_path, synthetic_image=ns.synthetic_image, prompt=ns.prompt, input_len_was_provided=given,
         correctness_test=ns.correctness_test,
     )
     return cfg, args
@@ -145,6 +148,51 @@ def make_synthetic_input_ids(*, batch_size: int, input_len: int, vocab_size: int
     if pin and torch.cuda.is_available():
         ids = ids.pin_memory()
     return ids if str(device) == "cpu" else ids.to(device)
+
+
+def make_multimodal_inputs(*, hf_config, batch_size: int, input_len: int, image: Optional[torch.Tensor], seed: int):
+    """One image per request followed/preceded by seeded text ids so that every request has ``input_len``
+    tokens (``input_len == 0``: just the image block and a short text tail).  ``image`` is uint8 [H, W, 3];
+    None makes a seeded uniform-random 448 x 448 one.  Returns ``(ids [B, L], pixel_values, grid_thw)``."""
+    from .utils.image_processor import image_token_count, preprocess_image
+
+    vc = hf_config.vision_config
+    g = torch.Generator(device="cpu")
+    g.manual_seed(seed)
+    if image is None:
+        image = torch.randint(0, 256, (448, 448, 3), generator=g, dtype=torch.uint8)
+    merge = getattr(vc, "spatial_merge_size", 2)
+    pix, grid = preprocess_image(image, vc.patch_size, merge, getattr(vc, "temporal_patch_size", 2))
+    n_img = image_token_count(grid, merge)
+    block = [hf_config.vision_start_token_id] + [hf_config.image_token_id] * n_img + [hf_config.vision_end_token_id]
+    L = max(input_len, len(block) + 8)
+    tc = getattr(hf_config, "text_config", hf_config)
+    special = {hf_config.image_token_id, hf_config.vision_start_token_id, hf_config.vision_end_token_id,
+               getattr(hf_config, "video_token_id", -1)}
+    upper = max(2, min(int(tc.vocab_size), 10000))
+    rows = []
+    for _ in range(batch_size):
+        text = torch.randint(0, upper, (L - len(block),), generator=g, dtype=torch.int64).tolist()
+        text = [t if t not in special else 0 for t in text]
+        head = min(4, len(text))
+        rows.append(text[:head] + block + text[head:])
+    ids = torch.tensor(rows, dtype=torch.int32)
+    return ids, pix.repeat(batch_size, 1), grid.repeat(batch_size, 1)
+
+
+def load_image(path) -> torch.Tensor:
+    """uint8 [H, W, 3] from an image file (PIL if present) or a ``.npy`` / ``.pt`` array."""
+    p = str(path)
+    if p.endswith(".npy"):
+        import numpy as np
+
+        return torch.from_numpy(np.load(p)).to(torch.uint8)
+    if p.endswith(".pt"):
+        return torch.load(p).to(torch.uint8)
+    from PIL import Image
+    import numpy as np
+
+    return torch.from_numpy(np.asarray(Image.open(p).convert("RGB"))).to(torch.uint8)
 
 
 def _safe_div(a: float, b: float) -> float:
@@ -225,6 +273,8 @@ class BenchRunner:
             ids, self._slots_dev, lens, lens, torch.zeros_like(lens), loc,
             extend_seq_lens_cpu=[L] * bs, extend_prefix_lens_cpu=[0] * bs, **extra)
         out = r.forward(fb)
+        self._mrope_deltas = fb.mrope_position_deltas
+        self.last_forward_batch = fb
         return r.sample(out)
 
     @torch.no_grad()
@@ -237,8 +287,14 @@ class BenchRunner:
         r.req_to_token_pool.req_to_token[self._slots_dev.long(), self.seq_len] = loc.to(torch.int32)
         self.seq_len += 1
         self._seq_lens += 1
+        extra = {}
+        if getattr(r.model, "uses_mrope", False):
+            pos = (self._seq_lens - 1).to(torch.int64)
+            if getattr(self, "_mrope_deltas", None) is not None:
+                pos = pos + self._mrope_deltas
+            extra["mrope_positions"] = pos.unsqueeze(0).expand(3, -1).contiguous()
         fb = r.prepare_forward_batch_decode(last_ids.to(self.device, non_blocking=True).to(torch.int64),
-                                            self._slots_dev, self._seq_lens, loc, max_seq_len=self.seq_len)
+                                            self._slots_dev, self._seq_lens, loc, max_seq_len=self.seq_len, **extra)
         out = r.forward(fb)
         ids = getattr(out, "next_token_ids", None)
         return ids if ids is not None else r.sample(out)
@@ -276,14 +332,24 @@ def run_single_setting(*, bench_runner: BenchRunner, args: BenchArgs, setting: B
         logger.info("skipping (batch_size=%d, input_len=%d, output_len=%d): exceeds KV capacity %d tokens",
                     setting.batch_size, setting.input_len, setting.output_len, br.runner.max_total_num_tokens)
         return None
-    ids = make_synthetic_input_ids(batch_size=setting.batch_size, input_len=setting.input_len,
-                                   vocab_size=br.runner.vocab_size, seed=seed, device=dev)
+    mm: Dict[str, Any] = {}
+    is_vl = hasattr(br.runner.hf_config, "vision_config") and getattr(br.runner.model, "visual", None) is not None
+    if is_vl and (args.image_path is not None or getattr(args, "synthetic_image", False)):
+        image = load_image(args.image_path) if args.image_path is not None else None
+        ids, pix, grid = make_multimodal_inputs(hf_config=br.runner.hf_config, batch_size=setting.batch_size,
+                                                input_len=setting.input_len, image=image, seed=seed)
+        setting = BenchSetting(setting.batch_size, ids.shape[1], setting.output_len)
+        mm = {"pixel_values": pix.to(dev), "image_grid_thw": grid.to(dev), "benchmark_vision_timing": True}
+        ids = ids.to(dev)
+    else:
+        ids = make_synthetic_input_ids(batch_size=setting.batch_size, input_len=setting.input_len,
+                                       vocab_size=br.runner.vocab_size, seed=seed, device=dev)
     use_events = dev.type == "cuda"
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(setting.output_len + 1)] if use_events else []
     if use_events:
         _sync(dev)
         ev[0].record()
-    prefill_latency, nxt = _timed_call(dev, lambda: br.extend(ids))
+    prefill_latency, nxt = _timed_call(dev, lambda: br.extend(ids, **mm))
     if use_events:
         ev[1].record()
     decode_lat: List[float] = []
@@ -296,6 +362,12 @@ def run_single_setting(*, bench_runner: BenchRunner, args: BenchArgs, setting: B
             logger.info("decode step %d: %.3f ms, %.1f tok/s", step + 1, lat * 1e3, setting.batch_size / lat)
     _sync(dev)
     extra: Dict[str, Any] = {"tp_size": pstate.get_tensor_model_parallel_world_size()}
+    if mm:
+        fb0 = br.last_forward_batch
+        vit_ms, vit_tok = float(fb0.vit_prefill_ms or 0.0), int(fb0.vit_prefill_tokens or 0)
+        extra.update(vit_prefill_ms=vit_ms, vit_prefill_tokens=vit_tok,
+                     vit_prefill_tps=_safe_div(vit_tok, vit_ms / 1e3), llm_prefill_ms=float(fb0.llm_prefill_ms or 0.0),
+                     multimodal_prefill_tps=_safe_div(setting.batch_size * setting.input_len, prefill_latency))
     if use_events:
         dp = ev[0].elapsed_time(ev[1]) / 1e3
         dd = [ev[i + 1].elapsed_time(ev[i + 2]) / 1e3 for i in range(setting.output_len - 1)]

@@ -46,6 +46,7 @@ struct AttnParams {
   const int* req_pool_indices;
   const int* seq_lens;
   const int* prefix_lens;  // null in decode
+  int non_causal;          // prefill only: every query row sees the whole sequence
   const int* q_start;      // null in decode
   int* status;
   int64_t q_stride;
@@ -113,7 +114,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const AttnPar
     q0 = blockIdx.x * p.tokens_per_tile;
     q_row0 = p.q_start[b];
     kv_begin = 0;
-    kv_end = min(seq_len, prefix + min(q_len, q0 + p.tokens_per_tile));  // causal upper bound of the tile
+    kv_end = p.non_causal ? seq_len
+                          : min(seq_len, prefix + min(q_len, q0 + p.tokens_per_tile));  // causal upper bound of the tile
     if (q0 >= q_len) return;
   }
   const int g = p.group;
@@ -152,7 +154,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const AttnPar
   const int row_tok = row / g;              // token inside the tile
   const int row_head = hk * g + row % g;
   const bool row_valid = (row_tok < p.tokens_per_tile) && (q0 + row_tok < q_len);
-  const int kv_limit = row_valid ? (prefix + q0 + row_tok) : prefix + q0;  // last visible key (inclusive)
+  const int kv_limit = (p.non_causal && !p.is_decode) ? seq_len - 1
+                                                      : (row_valid ? (prefix + q0 + row_tok) : prefix + q0);  // last visible key (inclusive)
 
   const uint16_t* qbase = static_cast<const uint16_t*>(p.q);
   const uint16_t* kbase = static_cast<const uint16_t*>(p.k_cache);
@@ -860,6 +863,7 @@ int launch_attention(const AttnArgs& a, cudaStream_t s) {
   p.req_pool_indices = a.req_pool_indices;
   p.seq_lens = a.seq_lens;
   p.prefix_lens = a.prefix_lens;
+  p.non_causal = a.non_causal;
   p.q_start = a.q_start;
   p.status = a.status;
   p.q_stride = a.q_stride;

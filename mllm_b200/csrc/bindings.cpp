@@ -223,6 +223,44 @@ void apply_penalties(Tensor& logits, const Tensor& counts, const c10::optional<T
                                 logits.size(1), stream_of(logits));
 }
 
+// ---- vision tower ----
+void vision_rope_split_pad(const Tensor& qkv, const Tensor& cos, const Tensor& sin, Tensor& q, Tensor& k, Tensor& v) {
+  check_half(qkv, "qkv");
+  TORCH_CHECK(qkv.dim() == 4 && qkv.size(1) == 3 && qkv.is_contiguous() && qkv.size(3) <= 128 && qkv.size(3) % 2 == 0,
+              "vision_rope_split_pad: qkv [T, 3, H, D <= 128]");
+  const int64_t T = qkv.size(0), H = qkv.size(2), D = qkv.size(3);
+  TORCH_CHECK(cos.is_cuda() && cos.scalar_type() == at::kFloat && cos.is_contiguous() && cos.size(0) == T &&
+                  cos.size(1) == D / 2 && sin.sizes() == cos.sizes() && sin.scalar_type() == at::kFloat && sin.is_contiguous(),
+              "vision_rope_split_pad: fp32 cos / sin [T, D/2]");
+  for (Tensor* t : {&q, &k, &v})
+    TORCH_CHECK(t->is_contiguous() && t->dim() == 3 && t->size(0) == T && t->size(1) == H && t->size(2) == 128 &&
+                    t->scalar_type() == qkv.scalar_type(),
+                "vision_rope_split_pad: outputs [T, H, 128]");
+  c10::cuda::CUDAGuard g(qkv.device());
+  mb200::launch_vision_rope_split_pad(qkv.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(), q.data_ptr(),
+                                      k.data_ptr(), v.data_ptr(), T, H, D, dtype_of(qkv), stream_of(qkv));
+}
+
+void vision_pos_embed_add(Tensor& x, const Tensor& table, const Tensor& idx, const Tensor& w) {
+  check_half(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && table.is_contiguous() && table.size(1) == x.size(1) &&
+                  table.scalar_type() == x.scalar_type() && idx.scalar_type() == at::kLong && idx.is_contiguous() &&
+                  idx.size(0) == 4 && idx.size(1) == x.size(0) && w.scalar_type() == at::kFloat && w.is_contiguous() &&
+                  w.sizes() == idx.sizes() && idx.is_cuda() && w.is_cuda(),
+              "vision_pos_embed_add: x [T, E], table [P, E], idx int64 [4, T], w fp32 [4, T]");
+  c10::cuda::CUDAGuard g(x.device());
+  mb200::launch_vision_pos_embed_add(x.data_ptr(), table.data_ptr(), idx.data_ptr<int64_t>(), w.data_ptr<float>(),
+                                     x.size(0), x.size(1), dtype_of(x), stream_of(x));
+}
+
+void gelu_erf(const Tensor& x, Tensor& out) {
+  check_half(x, "x");
+  TORCH_CHECK(x.is_contiguous() && out.is_contiguous() && out.numel() == x.numel() && out.scalar_type() == x.scalar_type(),
+              "gelu_erf: contiguous tensors of one shape");
+  c10::cuda::CUDAGuard g(x.device());
+  mb200::launch_gelu_erf(x.data_ptr(), out.data_ptr(), x.numel(), dtype_of(x), stream_of(x));
+}
+
 // ---- mixture of experts ----
 void moe_router_topk(const Tensor& logits, Tensor& w, Tensor& ids, bool renorm) {
   check_cuda(logits, "logits");
@@ -464,7 +502,7 @@ int64_t tp_wait_flags(const Tensor& flags, int64_t n, int64_t epoch) {
 
 void attention_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& req_to_token,
                        const Tensor& req_pool_indices, const Tensor& seq_lens, const Tensor& prefix_lens,
-                       const Tensor& q_start, double scale, Tensor& out, int64_t max_q_len) {
+                       const Tensor& q_start, double scale, Tensor& out, int64_t max_q_len, bool causal) {
   check_half(q, "q");
   TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.stride(2) == 1 && q.stride(1) == 128, "q must be [T,Hq,128]");
   TORCH_CHECK(out.is_contiguous() && out.sizes() == q.sizes() && out.scalar_type() == q.scalar_type(), "out");
@@ -497,6 +535,7 @@ void attention_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_c
   a.max_q_len = max_q_len > 0 ? max_q_len : q.size(0);
   a.num_splits = 1;
   a.is_decode = 0;
+  a.non_causal = causal ? 0 : 1;
   a.scale = static_cast<float>(scale);
   a.dt = dtype_of(q);
   const int rc = mb200::launch_attention(a, stream_of(q));
@@ -600,6 +639,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_tp", &gemm_tp);
   m.def("tp_rs_add_rmsnorm_ag", &tp_rs_add_rmsnorm_ag);
   m.def("tp_wait_flags", &tp_wait_flags);
+  m.def("vision_rope_split_pad", &vision_rope_split_pad);
+  m.def("vision_pos_embed_add", &vision_pos_embed_add);
+  m.def("gelu_erf", &gelu_erf);
   m.def("moe_router_topk", &moe_router_topk);
   m.def("moe_align", &moe_align);
   m.def("moe_gather", &moe_gather);

@@ -389,7 +389,7 @@ def attention_prefill(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_l
         if out is None:
             out = torch.empty((q.shape[0], q.shape[1], q.shape[2]), dtype=q.dtype, device=q.device)
         ext().attention_prefill(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, prefix_lens,
-                                q_start_loc, scale, out, max_q_len)
+                                q_start_loc, scale, out, max_q_len, True)
         return out
     return ref.attention_prefill(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, prefix_lens,
                                  q_start_loc, scale, out)
@@ -406,7 +406,66 @@ def attention_decode(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_le
 
 
 def attention_varlen_bidirectional(q, k, v, cu_seqlens, scale: float) -> torch.Tensor:
-    return ref.attention_varlen_bidirectional(q, k, v, cu_seqlens, scale)
+    """Bidirectional attention inside each segment; q, k, v [T, H, D].  On the GPU the head dimension is
+    zero-padded to 128 and the tcgen05 prefill kernel runs without its causal mask, every segment being
+    one "request" whose keys sit at rows ``cu[i]..cu[i+1]`` of k / v."""
+    if not use_kernels(q) or q.shape[-1] > 128:
+        return ref.attention_varlen_bidirectional(q, k, v, cu_seqlens, scale)
+    D = q.shape[-1]
+    if D != 128:
+        pad = (0, 128 - D)
+        q, k, v = (torch.nn.functional.pad(t, pad) for t in (q, k, v))
+    return _varlen_bidirectional_padded(q.contiguous(), k.contiguous(), v.contiguous(), cu_seqlens, scale)[..., :D]
+
+
+def _varlen_bidirectional_padded(q, k, v, cu_seqlens, scale: float) -> torch.Tensor:
+    cu = cu_seqlens.to(device=q.device, dtype=torch.int32)
+    lens = cu[1:] - cu[:-1]
+    lens_host = (cu_seqlens[1:] - cu_seqlens[:-1]).tolist() if not cu_seqlens.is_cuda else lens.tolist()
+    max_len = int(max(lens_host)) if lens_host else 0
+    n = len(lens_host)
+    rtt = (cu[:-1].unsqueeze(1) + torch.arange(max_len, device=q.device, dtype=torch.int32).unsqueeze(0)).contiguous()
+    rtt.clamp_(max=q.shape[0] - 1)
+    out = torch.empty_like(q)
+    ext().attention_prefill(q, k, v, rtt, torch.arange(n, device=q.device, dtype=torch.int32), lens.contiguous(),
+                            torch.zeros(n, device=q.device, dtype=torch.int32), cu[:-1].contiguous(), scale, out, max_len,
+                            False)
+    return out
+
+
+def vision_attention(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, cu_seqlens: torch.Tensor, num_heads: int,
+                     scale: float) -> torch.Tensor:
+    """ViT attention block core: qkv [T, 3 * H * D] -> 2-D rotary on q, k -> bidirectional attention per
+    image -> [T, H * D]."""
+    T = qkv.shape[0]
+    D = qkv.shape[1] // (3 * num_heads)
+    q4 = qkv.view(T, 3, num_heads, D)
+    if use_kernels(qkv) and D <= 128 and D % 2 == 0:
+        q = torch.empty((T, num_heads, 128), dtype=qkv.dtype, device=qkv.device)
+        k, v = torch.empty_like(q), torch.empty_like(q)
+        ext().vision_rope_split_pad(q4.contiguous(), cos.float().contiguous(), sin.float().contiguous(), q, k, v)
+        o = _varlen_bidirectional_padded(q, k, v, cu_seqlens, scale)
+        return o[..., :D].reshape(T, num_heads * D)
+    q, k, v = q4.unbind(1)
+    q, k = ref.vision_rope(q, cos, sin), ref.vision_rope(k, cos, sin)
+    return ref.attention_varlen_bidirectional(q, k, v, cu_seqlens, scale).reshape(T, num_heads * D)
+
+
+def vision_pos_embed_add(x: torch.Tensor, table: torch.Tensor, idx: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    if not use_kernels(x):
+        return ref.vision_pos_embed_add(x, table, idx, w)
+    x = x.contiguous()
+    ext().vision_pos_embed_add(x, table, idx.contiguous(), w.float().contiguous())
+    return x
+
+
+def gelu_erf(x: torch.Tensor) -> torch.Tensor:
+    if not use_kernels(x):
+        return ref.gelu_erf(x)
+    xc = x.contiguous()
+    out = torch.empty_like(xc)
+    ext().gelu_erf(xc, out)
+    return out
 
 
 # --------------------------------------------------------------------------

@@ -58,6 +58,27 @@ def gelu_tanh(x: torch.Tensor) -> torch.Tensor:
     return F.gelu(_f32(x), approximate="tanh").to(x.dtype)
 
 
+def gelu_erf(x: torch.Tensor) -> torch.Tensor:
+    return F.gelu(_f32(x)).to(x.dtype)
+
+
+def vision_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """2-D rotary embedding of the vision tower: x [T, H, D], cos/sin [T, D/2] (first quarter of the
+    frequencies from the row position, second from the column position); pairs (i, i + D/2)
+    (pymllm/models/qwen3_vl.py:118-167)."""
+    xf = _f32(x)
+    half = x.shape[-1] // 2
+    c, s = _f32(cos).unsqueeze(1), _f32(sin).unsqueeze(1)
+    x1, x2 = xf[..., :half], xf[..., half:]
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).to(x.dtype)
+
+
+def vision_pos_embed_add(x: torch.Tensor, table: torch.Tensor, idx: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x + sum_i w[i] * table[idx[i]]`` over the four bilinear corners (pymllm/models/qwen3_vl.py:456-491)."""
+    pe = (_f32(table)[idx] * w.float().unsqueeze(-1)).sum(0)
+    return (_f32(x) + pe).to(x.dtype)
+
+
 def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     return table[ids.long()]
 
