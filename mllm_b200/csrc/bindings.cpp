@@ -223,6 +223,50 @@ void apply_penalties(Tensor& logits, const Tensor& counts, const c10::optional<T
                                 logits.size(1), stream_of(logits));
 }
 
+int64_t w4a16_gemm(const Tensor& x, const Tensor& qweight, const Tensor& scales, const c10::optional<Tensor>& zeros,
+                   int64_t group, const c10::optional<Tensor>& bias, Tensor& out) {
+  check_half(x, "x");
+  check_cuda(qweight, "qweight");
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && qweight.dim() == 2 && qweight.is_contiguous() &&
+                  qweight.scalar_type() == at::kInt && qweight.size(1) * 8 == x.size(1),
+              "w4a16_gemm: x [M, K], qweight int32 [N, K/8]");
+  const int64_t N = qweight.size(0), K = x.size(1);
+  TORCH_CHECK(scales.is_cuda() && scales.is_contiguous() && scales.scalar_type() == x.scalar_type() && scales.dim() == 2 &&
+                  scales.size(0) == N && scales.size(1) * group == K,
+              "w4a16_gemm: scales [N, K/group] of x's dtype");
+  if (zeros.has_value())
+    TORCH_CHECK(zeros->is_cuda() && zeros->is_contiguous() && zeros->scalar_type() == at::kByte &&
+                    zeros->sizes() == scales.sizes(),
+                "w4a16_gemm: uint8 zeros [N, K/group]");
+  if (bias.has_value())
+    TORCH_CHECK(bias->is_cuda() && bias->is_contiguous() && bias->scalar_type() == x.scalar_type() && bias->numel() == N,
+                "w4a16_gemm: bias [N]");
+  TORCH_CHECK(out.dim() == 2 && out.size(0) == x.size(0) && out.size(1) == N && out.stride(1) == 1 &&
+                  out.scalar_type() == x.scalar_type(),
+              "w4a16_gemm: out [M, N]");
+  c10::cuda::CUDAGuard g(x.device());
+  auto& st = device_state(x.get_device());
+  mb200::W4A16Args a{};
+  a.x = x.data_ptr();
+  a.qweight = qweight.data_ptr();
+  a.scales = scales.data_ptr();
+  a.zeros = zeros.has_value() ? zeros->data_ptr<uint8_t>() : nullptr;
+  a.bias = bias.has_value() ? bias->data_ptr() : nullptr;
+  a.out = out.data_ptr();
+  a.workspace = st.workspace.data_ptr<float>();
+  a.workspace_bytes = st.workspace.numel() * sizeof(float);
+  a.status = st.status.data_ptr<int>();
+  a.m = x.size(0);
+  a.n = N;
+  a.k = K;
+  a.group = group;
+  a.ldx = x.stride(0);
+  a.ldc = out.stride(0);
+  a.dt = dtype_of(x);
+  a.num_sms = st.num_sms;
+  return mb200::launch_w4a16_gemm(a, stream_of(x));
+}
+
 // ---- vision tower ----
 void vision_rope_split_pad(const Tensor& qkv, const Tensor& cos, const Tensor& sin, Tensor& q, Tensor& k, Tensor& v) {
   check_half(qkv, "qkv");
@@ -637,6 +681,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("apply_penalties", &apply_penalties);
   m.def("gemm", &gemm);
   m.def("gemm_tp", &gemm_tp);
+  m.def("w4a16_gemm", &w4a16_gemm);
   m.def("tp_rs_add_rmsnorm_ag", &tp_rs_add_rmsnorm_ag);
   m.def("tp_wait_flags", &tp_wait_flags);
   m.def("vision_rope_split_pad", &vision_rope_split_pad);

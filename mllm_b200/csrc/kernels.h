@@ -96,6 +96,24 @@ struct GemmArgs {
 int launch_gemm(const GemmArgs& args, cudaStream_t s);
 size_t gemm_workspace_bytes(int m, int n, int k, int num_sms);
 
+// ----- W4A16 GEMM (4-bit weights expanded in shared memory, tcgen05) ----------------------------
+struct W4A16Args {
+  const void* x;        // [m, k] activations (bf16 / fp16), row stride ldx
+  const void* qweight;  // int32 [n, k/8], nibble i of word j = element 8j + i
+  const void* scales;   // [n, k/group] in the activation type
+  const uint8_t* zeros; // [n, k/group] or null (zero point 8)
+  const void* bias;     // [n] or null
+  void* out;            // [m, n] row stride ldc
+  float* workspace;     // split-K partials (may be null: no split)
+  size_t workspace_bytes;
+  int* status;
+  int m, n, k, group;
+  int64_t ldx, ldc;
+  DType dt;
+  int num_sms;
+};
+int launch_w4a16_gemm(const W4A16Args& args, cudaStream_t s);
+
 // 128-byte-swizzled 2-D tensor map over a row-major [rows, k] matrix (box = 128 bytes of k x box_rows);
 // map points at a CUtensorMap.  type: 0 bf16, 1 fp16, 2 uint8.
 bool make_tma_operand_map(void* map, const void* base, int64_t rows, int64_t k, int64_t ld, int elem_bytes, int type,

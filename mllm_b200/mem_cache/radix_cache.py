@@ -127,15 +127,17 @@ class RadixCache(BasePrefixCache):
             child = node.children.get(self._child_key(tokens[pos:], key.extra_key))
             if child is None:
                 break
-            child.last_access_time = now
             m = _common_prefix_len(child.key, tokens[pos:], self.page_size)
             if m < len(child.key):
                 if m > 0:
+                    # only the matched part of a partially matched edge counts as used
                     upper = self._split(child, m, key.extra_key)
+                    upper.last_access_time = now
                     parts.append(upper.value)
                     node = upper
                     pos += m
                 break
+            child.last_access_time = now
             parts.append(child.value)
             node = child
             pos += m
@@ -167,10 +169,10 @@ class RadixCache(BasePrefixCache):
                 node.children[ck] = leaf
                 self._evictable += len(leaf.value)
                 return InsertResult(prefix_len=pos, last_node=leaf)
-            child.last_access_time = now
             m = _common_prefix_len(child.key, tokens[pos:], self.page_size)
             if m < len(child.key):
                 child = self._split(child, m, key.extra_key)
+            child.last_access_time = now
             node = child
             pos += m
         return InsertResult(prefix_len=n, last_node=node)

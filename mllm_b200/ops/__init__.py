@@ -298,7 +298,25 @@ def int8_scaled_mm(a_q, w_q, a_scale, w_scale, out_dtype, bias=None) -> torch.Te
 
 
 def w4a16_gemm(x, qweight, scales, zeros, group: int, bias=None) -> torch.Tensor:
-    return ref.w4a16_gemm(x, qweight, scales, zeros, group, bias)
+    """``x @ dequant(qweight).T (+bias)``: 4-bit weights with group-wise scales (and optional zero points).
+    On the GPU the nibbles are expanded inside the tcgen05 GEMM kernel; the weights are never
+    materialised in 16 bits in device memory."""
+    x2 = _2d(x)
+    K = x2.shape[1]
+    ok = (use_kernels(x) and x.dtype in (torch.bfloat16, torch.float16) and K % 64 == 0 and group % 64 == 0
+          and K % group == 0 and qweight.dtype == torch.int32)
+    if not ok:
+        return ref.w4a16_gemm(x, qweight, scales, zeros, group, bias)
+    if x2.stride(-1) != 1 or (x2.stride(0) * x2.element_size()) % 16:
+        x2 = x2.contiguous()
+    out = torch.empty((x2.shape[0], qweight.shape[0]), dtype=x.dtype, device=x.device)
+    z = None if zeros is None else zeros.to(torch.uint8).contiguous()
+    rc = ext().w4a16_gemm(x2, qweight.contiguous(), scales.to(x.dtype).contiguous(), z, int(group),
+                          None if bias is None else bias.to(x.dtype).contiguous(), out)
+    if rc != 0:
+        raise RuntimeError(f"mllm_b200 w4a16_gemm: unsupported shape or launch failure (code {rc}) for "
+                           f"M={x2.shape[0]} N={qweight.shape[0]} K={K} group={group}")
+    return out.view(*x.shape[:-1], qweight.shape[0])
 
 
 # --------------------------------------------------------------------------

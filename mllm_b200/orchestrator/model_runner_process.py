@@ -75,6 +75,21 @@ class KVAllocationError(RuntimeError):
     pass
 
 
+def _make_radix_cache(alloc, page_size: int):
+    """The C++ radix tree when the host extension is available (``MLLM_B200_PY_RADIX=1`` forces the
+    Python tree, which has the same interface and eviction order)."""
+    import os
+
+    if os.environ.get("MLLM_B200_PY_RADIX") != "1":
+        try:
+            from ..mem_cache.native import NativeRadixCache
+
+            return NativeRadixCache(alloc, page_size)
+        except Exception as exc:  # extension not built on this machine
+            logger.warning("native radix tree unavailable (%s); using the Python tree", exc)
+    return RadixCache(alloc, page_size)
+
+
 class ModelRunnerProcess:
     def __init__(self, runner: ModelRunner, disable_radix_cache: bool = False) -> None:
         self.runner = runner
@@ -82,7 +97,7 @@ class ModelRunnerProcess:
         self.page_size = runner.server_config.radix_cache_page_size
         alloc = runner.token_to_kv_pool_allocator
         self.prefix_cache = (ChunkCache(alloc, self.page_size) if disable_radix_cache
-                             else RadixCache(alloc, self.page_size))
+                             else _make_radix_cache(alloc, self.page_size))
         self.stats = {"prefix_hit_tokens": 0, "prefill_tokens": 0, "evicted_tokens": 0}
 
     # ------------------------------------------------------------------ capacity

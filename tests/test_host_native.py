@@ -1,0 +1,212 @@
+"""Host-native C++ components against their Python twins: randomised differential tests of the radix
+tree and the slot allocator, byte-level fixtures of the .mllm reader/writer, GGUF block expansion."""
+import random
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+from mllm_b200.io.mllm_file import MllmFileReader, iter_mllm_tensors, write_mllm, write_mllm_v1
+from mllm_b200.mem_cache import RadixCache, RadixKey, TokenToKVPoolAllocator
+from mllm_b200.mem_cache.native import NativeRadixCache, NativeTokenToKVPoolAllocator, host_ext
+
+
+@pytest.mark.parametrize("page", [1, 4])
+def test_radix_tree_matches_python(page, monkeypatch):
+    # a logical clock on the Python side too, so both trees evict in exactly the same order
+    import itertools
+
+    from mllm_b200.mem_cache import radix_cache as rc_mod
+
+    ticks = itertools.count(1)
+    monkeypatch.setattr(rc_mod.time, "monotonic", lambda: float(next(ticks)))
+    rng = random.Random(page)
+    py_alloc, nat_alloc = TokenToKVPoolAllocator(4096, page), TokenToKVPoolAllocator(4096, page)
+    py, nat = RadixCache(py_alloc, page), NativeRadixCache(nat_alloc, page)
+    locked = []
+    for step in range(400):
+        op = rng.random()
+        base = [rng.randrange(3) for _ in range(rng.randrange(1, 6) * page)]
+        toks = base + [rng.randrange(50) for _ in range(rng.randrange(0, 5) * page)]
+        extra = rng.choice([None, None, "lora-a"])
+        key = RadixKey(toks, extra)
+        if op < 0.45:
+            n = len(toks) - len(toks) % page
+            slots = py_alloc.alloc_host(n)
+            slots2 = nat_alloc.alloc_host(n)
+            if slots is None:
+                continue
+            a, b = py.insert(key, slots), nat.insert(key, slots2)
+            assert a.prefix_len == b.prefix_len
+            # duplicates (already cached) go back to the pool, as the scheduler does
+            py_alloc.free(slots[: a.prefix_len])
+            nat_alloc.free(slots2[: b.prefix_len])
+        elif op < 0.8:
+            a, b = py.match_prefix(key), nat.match_prefix(key)
+            assert a.prefix_len == b.prefix_len
+            if rng.random() < 0.3 and a.prefix_len:
+                py.inc_lock_ref(a.last_node)
+                nat.inc_lock_ref(b.last_node)
+                locked.append((a.last_node, b.last_node))
+        elif op < 0.9 and locked:
+            a, b = locked.pop(rng.randrange(len(locked)))
+            py.dec_lock_ref(a)
+            nat.dec_lock_ref(b)
+        else:
+            n = rng.randrange(1, 20) * page
+            a, b = py.evict(n), nat.evict(n)
+            assert (a.full_evicted >= n or py.evictable_size() == 0) and (b.full_evicted >= n or nat.evictable_size() == 0)
+        assert py.protected_size() == nat.protected_size(), step
+        assert py.protected_size() + py.evictable_size() == py.total_size()
+        assert nat.protected_size() + nat.evictable_size() == nat.total_size()
+        # every cached token is backed by a slot that is not free: sizes + free slots add up
+        assert nat.total_size() + nat_alloc.available_size() == 4096 // page * page
+    for a, b in locked:
+        py.dec_lock_ref(a)
+        nat.dec_lock_ref(b)
+    nat.evict(10 ** 9)
+    assert nat.total_size() == 0 and nat_alloc.available_size() == 4096 // page * page
+
+
+def test_native_lru_order_and_lock_protection():
+    nat = NativeRadixCache(None, 1)
+    nat.insert(RadixKey([1, 2, 3]), np.array([10, 11, 12]))
+    nat.insert(RadixKey([1, 2, 4]), np.array([10, 11, 13]))
+    nat.insert(RadixKey([7, 8]), np.array([20, 21]))
+    m = nat.match_prefix(RadixKey([1, 2, 3]))          # touches [1,2] and [3]
+    assert m.indices.tolist() == [10, 11, 12]
+    nat.inc_lock_ref(m.last_node)
+    assert nat.protected_size() == 3 and nat.evictable_size() == 3
+    freed = []
+    nat.on_evict = lambda s: freed.extend(s.tolist())
+    nat.evict(100)
+    assert sorted(freed) == [13, 20, 21]              # the locked path survives
+    nat.dec_lock_ref(m.last_node)
+    nat.evict(100)
+    assert sorted(freed) == [10, 11, 12, 13, 20, 21] and nat.total_size() == 0
+
+
+@pytest.mark.parametrize("page", [1, 8])
+def test_allocator_matches_python(page):
+    rng = random.Random(0)
+    py, nat = TokenToKVPoolAllocator(1024, page), NativeTokenToKVPoolAllocator(1024, page)
+    held = []
+    for _ in range(300):
+        if rng.random() < 0.6 or not held:
+            n = rng.randrange(1, 40)
+            a, b = py.alloc_host(n), nat.alloc_host(n)
+            assert (a is None) == (b is None)
+            if a is not None:
+                assert len(a) == len(b) and len(set(b.tolist())) == len(b) and min(b) >= page
+                held.append((a, b))
+        else:
+            a, b = held.pop(rng.randrange(len(held)))
+            py.free(a)
+            nat.free(b)
+        assert py.available_size() == nat.available_size()
+    live = np.concatenate([b for _, b in held]) if held else np.empty(0, dtype=np.int64)
+    assert len(set(live.tolist())) == len(live)
+
+
+def test_mllm_v2_roundtrip_and_layout(tmp_path):
+    torch.manual_seed(0)
+    tensors = [("model.embed_tokens.weight", torch.randn(7, 5).to(torch.bfloat16)),
+               ("model.layers.0.self_attn.q_proj.weight", torch.randn(4, 6)),
+               ("w.int8", torch.randint(-128, 127, (3, 9), dtype=torch.int8)),
+               ("scale.f16", torch.randn(11).to(torch.float16)), ("idx", torch.arange(5, dtype=torch.int32))]
+    path = str(tmp_path / "m.mllm")
+    write_mllm(path, tensors, model_name="tiny")
+    raw = open(path, "rb").read()
+    magic, ver, name, n, desc = struct.unpack_from("<II512sIQ", raw, 0)
+    assert (magic, ver, n, desc) == (0x519A, 2, 5, 532) and name.rstrip(b"\0") == b"tiny"
+    pid, dt, size, off, rank, *rest = struct.unpack_from("<IIQQQ16i256s", raw, 532)
+    assert (pid, dt, size, rank, rest[:2]) == (0, 128, 70, 2, [7, 5]) and rest[16].rstrip(b"\0") == b"model.embed_tokens.weight"
+    assert off % 64 == 0 and raw[off:off + 70] == tensors[0][1].view(torch.uint8).numpy().tobytes()
+    r = MllmFileReader(path)
+    assert r.version == 2 and r.model_name == "tiny" and r.names() == [n for n, _ in tensors]
+    for (name, want), (name2, got) in zip(tensors, iter_mllm_tensors(path)):
+        assert name == name2 and got.dtype == want.dtype and torch.equal(got, want)
+
+
+def test_mllm_v1_read(tmp_path):
+    tensors = [("a.weight", torch.randn(3, 4)), ("b.bias", torch.randn(6).to(torch.float16))]
+    path = str(tmp_path / "old.mllm")
+    write_mllm_v1(path, tensors)
+    r = MllmFileReader(path)
+    assert r.version == 1 and r.names() == ["a.weight", "b.bias"]
+    got = dict(iter_mllm_tensors(path))
+    assert torch.equal(got["a.weight"], tensors[0][1].reshape(-1))       # V1 stores no shapes
+    assert torch.equal(got["b.bias"], tensors[1][1])
+
+
+def test_mllm_rejects_garbage(tmp_path):
+    p = tmp_path / "bad.mllm"
+    p.write_bytes(b"\x01\x02\x03\x04" * 10)
+    with pytest.raises(RuntimeError):
+        MllmFileReader(str(p))
+
+
+def _q4_0_blocks(x: np.ndarray) -> bytes:
+    out = b""
+    for blk in x.reshape(-1, 32):
+        amax_idx = np.abs(blk).argmax()
+        d = blk[amax_idx] / -8.0 if blk[amax_idx] != 0 else 1.0
+        d16 = np.float16(d)
+        q = np.clip(np.round(blk / np.float32(d16)) + 8, 0, 15).astype(np.uint8)
+        out += d16.tobytes() + (q[:16] | (q[16:] << 4)).astype(np.uint8).tobytes()
+    return out
+
+
+def test_gguf_q4_0_and_q8_0_expansion():
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal(64 * 32).astype(np.float32)
+    raw = np.frombuffer(_q4_0_blocks(x), dtype=np.uint8)
+    got = host_ext().gguf_dequantize(2, raw, 2)
+    # independent restatement of the block layout: value j = ((nibble) - 8) * d, low nibbles first
+    want = []
+    for b in raw.reshape(-1, 18):
+        d = np.frombuffer(b[:2].tobytes(), dtype=np.float16)[0].astype(np.float32)
+        qs = b[2:]
+        want += [((qs & 15).astype(np.int32) - 8) * d, ((qs >> 4).astype(np.int32) - 8) * d]
+    np.testing.assert_array_equal(got, np.concatenate(want).astype(np.float32))
+    assert np.abs(got - x).max() < 0.6
+    # Q8_0
+    blocks = b""
+    xs = x.reshape(-1, 32)
+    for blk in xs:
+        d16 = np.float16(np.abs(blk).max() / 127.0)
+        blocks += d16.tobytes() + np.clip(np.round(blk / np.float32(d16)), -127, 127).astype(np.int8).tobytes()
+    got8 = host_ext().gguf_dequantize(8, np.frombuffer(blocks, dtype=np.uint8), 1)
+    assert np.abs(got8 - x).max() < 0.05
+
+
+def test_gguf_k_quants_known_blocks():
+    """Q4_K / Q6_K super-blocks built by hand from the published layout; expansion must give back
+    d * scale * q - dmin * min (Q4_K) and d * scale * (q - 32) (Q6_K)."""
+    # Q4_K: all 8 sub-block scales = 2, mins = 1 (6-bit fields), nibbles = position mod 16
+    d, dmin = np.float16(0.5), np.float16(0.25)
+    scales = bytearray(12)
+    for j in range(4):
+        scales[j] = 2
+        scales[j + 4] = 1
+    for j in range(4, 8):
+        scales[j + 4] = (2 & 0xF) | ((1 & 0xF) << 4)   # high two bits of both fields are zero
+    qs = bytearray(128)
+    vals = np.arange(256) % 16
+    for grp in range(4):
+        lo, hi = vals[grp * 64: grp * 64 + 32], vals[grp * 64 + 32: grp * 64 + 64]
+        for l in range(32):
+            qs[grp * 32 + l] = int(lo[l]) | (int(hi[l]) << 4)
+    blk = d.tobytes() + dmin.tobytes() + bytes(scales) + bytes(qs)
+    assert len(blk) == 144
+    got = host_ext().gguf_dequantize(12, np.frombuffer(blk, dtype=np.uint8), 1)
+    np.testing.assert_allclose(got, 0.5 * 2 * vals - 0.25 * 1, rtol=0, atol=1e-6)
+    # Q6_K: scales = 3, q = 40 everywhere (low nibble 8, high bits 2) -> d * 3 * (40 - 32)
+    ql = bytes([8 | (8 << 4)] * 128)
+    qh = bytes([2 | (2 << 2) | (2 << 4) | (2 << 6)] * 64)
+    sc = bytes([3] * 16)
+    blk6 = ql + qh + sc + np.float16(0.125).tobytes()
+    assert len(blk6) == 210
+    got6 = host_ext().gguf_dequantize(14, np.frombuffer(blk6, dtype=np.uint8), 1)
+    np.testing.assert_allclose(got6, np.full(256, 0.125 * 3 * 8, dtype=np.float32))

@@ -67,12 +67,14 @@ def test_qwen3_vl_tiny_gpu_matches_cpu_oracle():
         mr.initialize()
         return mr
 
-    gpu, cpu = build("cuda", "bfloat16"), build("cpu", "float32")
+    gpu, cpu = build("cuda:0", "bfloat16"), build("cpu", "float32")
     sd = {k: v.detach().float().cpu() for k, v in gpu.model.state_dict().items()}
     # undo the gate/up interleave the GPU model applied after loading
     for name, m in gpu.model.named_modules():
         if getattr(m, "_gate_up_interleaved", False):
-            sd[name + ".weight"] = ref.deinterleave_gate_up(sd[name + ".weight"], ops.SWIGLU_BLOCK)
+            w = sd[name + ".weight"]
+            v = w.reshape(-1, 2, ops.SWIGLU_BLOCK, w.shape[1])
+            sd[name + ".weight"] = torch.cat([v[:, 0].reshape(-1, w.shape[1]), v[:, 1].reshape(-1, w.shape[1])], 0)
     cpu.model.load_state_dict(sd, strict=False)
     image = torch.randint(0, 256, (64, 96, 3), dtype=torch.uint8, generator=torch.Generator().manual_seed(0))
     ids, pix, grid = make_multimodal_inputs(hf_config=cfg, batch_size=1, input_len=40, image=image, seed=0)
