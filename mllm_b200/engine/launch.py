@@ -32,6 +32,14 @@ logger = logging.getLogger(__name__)
 DEFAULT_MAX_NEW_TOKENS = 128
 
 
+def _free_port() -> int:
+    import socket
+
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        return int(sk.getsockname()[1])
+
+
 class Engine:
     def __init__(self, config: Optional[Union[GlobalConfig, ServerConfig]] = None, mode: str = "inproc",
                  hf_config: Any = None, device: Optional[str] = None) -> None:
@@ -168,9 +176,14 @@ class Engine:
                                           context_length=sc.context_length, vocab_size=vocab,
                                           tokenizer_mode=sc.tokenizer_mode, trust_remote_code=sc.trust_remote_code,
                                           log_level=sc.log_level))
-        spawn(run_scheduler_process, dict(server_config=sc, recv_addr=a_tok_sched, send_addr=a_sched_detok,
-                                          hf_config=self.hf_config, quantization_method=self.quant_method,
-                                          kv_cache_dtype=self.kv_cache_dtype, device=self.device))
+        world = sc.world_size
+        port = _free_port() if world > 1 else None
+        for rank in range(world):  # one scheduler + model runner per GPU; rank 0 owns the sockets
+            spawn(run_scheduler_process, dict(server_config=sc, recv_addr=a_tok_sched if rank == 0 else None,
+                                              send_addr=a_sched_detok if rank == 0 else None,
+                                              hf_config=self.hf_config, quantization_method=self.quant_method,
+                                              kv_cache_dtype=self.kv_cache_dtype, device=self.device, rank=rank,
+                                              world_size=world, master_port=port))
         spawn(run_detokenizer_process, dict(tokenizer_path=sc.tokenizer_path, recv_addr=a_sched_detok,
                                             send_addr=a_detok_rr, vocab_size=vocab, tokenizer_mode=sc.tokenizer_mode,
                                             trust_remote_code=sc.trust_remote_code, log_level=sc.log_level))

@@ -150,7 +150,8 @@ class Qwen3VLVisionModel(nn.Module):
             for _ in self.deepstack_visual_indexes)
         head_dim = vc.hidden_size // vc.num_heads
         rotary_dim = head_dim // 2
-        self._inv_freq = 1.0 / (10000.0 ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32) / rotary_dim))
+        # host-side table (the module may be constructed under a device context)
+        self._inv_freq = torch.from_numpy(1.0 / (10000.0 ** (np.arange(0, rotary_dim, 2, dtype=np.float32) / rotary_dim)))
 
     # -- host-side index building (cheap; depends only on the grids) --
     def rotary_cos_sin(self, grids: List[List[int]], device) -> Tuple[torch.Tensor, torch.Tensor]:

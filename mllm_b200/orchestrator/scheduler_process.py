@@ -321,45 +321,80 @@ def resolve_eos_token_ids(hf_config) -> List[int]:
     return []
 
 
-def run_scheduler_process(server_config: ServerConfig, recv_addr: str, send_addr: str, pipe_writer=None,
+def run_scheduler_process(server_config: ServerConfig, recv_addr: Optional[str], send_addr: Optional[str], pipe_writer=None,
                           hf_config=None, quantization_method=None, kv_cache_dtype: str = "auto",
-                          device: Optional[str] = None) -> None:
-    """Event loop: receive -> schedule -> forward -> stream out (one forward per iteration)."""
+                          device: Optional[str] = None, rank: int = 0, world_size: int = 1,
+                          master_port: Optional[int] = None) -> None:
+    """Event loop: receive -> schedule -> forward -> stream out (one forward per iteration).
+
+    With ``world_size > 1`` one such process runs per rank.  Rank 0 owns the sockets; at the top of
+    every iteration it hands the messages it received to the other ranks (object broadcast over a gloo
+    group, never over the GPU), so every rank applies the same requests in the same order and the
+    schedulers stay in lock step without exchanging batch metadata.  Only rank 0 answers."""
+    import os
+
     import zmq
 
     from .ipc_utils import make_socket, setup_subprocess_logging
 
     setup_subprocess_logging(server_config.log_level)
+    if world_size > 1:
+        os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world_size), MASTER_ADDR="127.0.0.1",
+                          MASTER_PORT=str(master_port or 29577))
     try:
         sched = build_scheduler(server_config, hf_config, quantization_method, kv_cache_dtype, device)
+        ctrl = None
+        if world_size > 1:
+            import torch.distributed as dist
+
+            ctrl = dist.new_group(backend="gloo")  # host-side control plane
     except Exception as exc:  # readiness handshake carries the failure to the parent
         if pipe_writer is not None:
             pipe_writer.send({"status": "error", "error": repr(exc)})
         raise
     ctx = zmq.Context()
-    recv = make_socket(ctx, zmq.PULL, recv_addr, bind=False)
-    send = make_socket(ctx, zmq.PUSH, send_addr, bind=True)
+    recv = send = poller = None
+    if rank == 0:
+        recv = make_socket(ctx, zmq.PULL, recv_addr, bind=False)
+        send = make_socket(ctx, zmq.PUSH, send_addr, bind=True)
+        poller = zmq.Poller()
+        poller.register(recv, zmq.POLLIN)
     if pipe_writer is not None:
         pipe_writer.send({"status": "ready", "max_total_num_tokens": sched.mrp.runner.max_total_num_tokens})
-    poller = zmq.Poller()
-    poller.register(recv, zmq.POLLIN)
+    scheduler_event_loop(sched, recv, send, poller, rank, world_size, ctrl)
+
+
+def scheduler_event_loop(sched: "Scheduler", recv, send, poller, rank: int = 0, world_size: int = 1, ctrl_group=None) -> None:
+    idle_ms = 1000 if world_size == 1 else 50  # followers wait in the broadcast: keep the heartbeat short
     while True:
-        # drain the inbox; sleep on the socket when there is nothing to run
-        timeout = 0 if sched.has_work() else 1000
-        while dict(poller.poll(timeout)):
-            msg = recv.recv_pyobj()
+        msgs: Optional[list] = None
+        if rank == 0:
+            msgs = []
+            # drain the inbox; sleep on the socket when there is nothing to run
+            timeout = 0 if sched.has_work() else idle_ms
+            while dict(poller.poll(timeout)):
+                msgs.append(recv.recv_pyobj())
+                timeout = 0
+        if world_size > 1:
+            import torch.distributed as dist
+
+            box = [msgs]
+            dist.broadcast_object_list(box, src=0, group=ctrl_group)
+            msgs = box[0]
+        for msg in msgs:
             if msg is None:
                 return
             if isinstance(msg, TokenizedGenerateReqInput):
                 err = sched.add_request(msg)
-                if err is not None:
+                if err is not None and rank == 0:
                     send.send_pyobj({"error": err, "rid": msg.rid})
             elif isinstance(msg, AbortReq):
-                if sched.abort(msg.rid):
+                if sched.abort(msg.rid) and rank == 0:
                     send.send_pyobj(sched.abort_outputs([msg.rid]))
             elif isinstance(msg, FlushCacheReq):
-                send.send_pyobj({"flush_cache": sched.flush_cache()})
-            timeout = 0
+                ok = sched.flush_cache()
+                if rank == 0:
+                    send.send_pyobj({"flush_cache": ok})
         out = sched.step()
-        if out is not None:
+        if out is not None and rank == 0:
             send.send_pyobj(out)

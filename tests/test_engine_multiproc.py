@@ -23,9 +23,9 @@ def test_multiproc_generate_matches_inproc_and_detects_dead_worker():
         assert got["output_ids"] == want and got["meta_info"]["finish_reason"] == "length"
         chunks = list(eng.generate("hello", {"max_new_tokens": 5, "temperature": 0.0}, stream=True))
         assert chunks[-1]["output_ids"] == want
-        # host-side failure injection: kill the detokenizer process
-        eng._procs[2].terminate()
-        eng._procs[2].join(10)
+        # host-side failure injection: kill the detokenizer process (the last one spawned)
+        eng._procs[-1].terminate()
+        eng._procs[-1].join(10)
         eng._health_loop.__func__  # the monitor thread polls every 5 s
         deadline = time.time() + 12
         while eng.is_healthy and time.time() < deadline:
@@ -33,5 +33,30 @@ def test_multiproc_generate_matches_inproc_and_detects_dead_worker():
         assert not eng.is_healthy
         with pytest.raises((RuntimeError, TimeoutError)):
             eng.generate("x", {"max_new_tokens": 2}, timeout=5)
+    finally:
+        eng.shutdown()
+
+
+def test_two_rank_tensor_parallel_engine_on_cpu():
+    """Two scheduler/model-runner ranks (gloo, CPU) run in lock step behind one tokenizer/detokenizer
+    pair: requests complete, repeated prompts (prefix-cache hits on both ranks) reproduce their tokens,
+    and killing the follower rank turns the engine unhealthy.  (Numerical agreement of tensor-parallel
+    and single-rank models is covered by the tensor-parallel tests, which load one set of weights.)"""
+    prompts = ["hello", "the quick brown fox", "a"]
+    cfg = _cfg()
+    cfg.tp_size = 2
+    eng = Engine(cfg, mode="multiproc", device="cpu").launch()
+    try:
+        assert len(eng._procs) == 4      # tokenizer, two scheduler ranks, detokenizer
+        first = [eng.generate(p, {"max_new_tokens": 6, "temperature": 0.0}, timeout=180) for p in prompts]
+        assert all(len(r["output_ids"]) == 6 and r["meta_info"]["finish_reason"] == "length" for r in first)
+        again = [eng.generate(p, {"max_new_tokens": 6, "temperature": 0.0}, timeout=180)["output_ids"] for p in prompts]
+        assert again == [r["output_ids"] for r in first]
+        eng._procs[2].terminate()        # the follower rank: its peers' next control broadcast fails
+        eng._procs[2].join(10)
+        deadline = time.time() + 15
+        while eng.is_healthy and time.time() < deadline:
+            time.sleep(0.25)
+        assert not eng.is_healthy
     finally:
         eng.shutdown()
