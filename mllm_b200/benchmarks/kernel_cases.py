@@ -57,11 +57,17 @@ def _kv(batch, seq, hkv, dev):
 
 def attn_decode(a) -> dict:
     dev = "cuda"
-    kc, vc, rtt, req = _kv(a.batch, a.seq, a.hkv, dev)
+    # several KV sets used in turn (like the layers of a model) so the working set exceeds L2
+    sets = [_kv(a.batch, a.seq, a.hkv, dev) for _ in range(max(1, a.kv_sets))]
     seq = torch.full((a.batch,), a.seq, dtype=torch.int32, device=dev)
     q = torch.randn(a.batch, a.hq, 128, device=dev, dtype=torch.bfloat16)
     out = torch.empty_like(q)
-    ms = _time(lambda: ops.attention_decode(q, kc, vc, rtt, req, seq, 128 ** -0.5, out=out, max_seq_len=a.seq), a.iters)
+
+    def run():
+        for kc, vc, rtt, req in sets:
+            ops.attention_decode(q, kc, vc, rtt, req, seq, 128 ** -0.5, out=out, max_seq_len=a.seq)
+
+    ms = _time(run, a.iters) / len(sets)
     byts = 2 * a.batch * a.seq * a.hkv * 128 * 2
     return {"case": "attn_decode", "batch": a.batch, "seq": a.seq, "hq": a.hq, "hkv": a.hkv, "ms": ms,
             "gbs": byts / ms / 1e6}
@@ -102,9 +108,50 @@ def gemm(a) -> dict:
             "tflops": 2 * a.m * a.n * a.k / ms / 1e9, "gbs": byts / ms / 1e6}
 
 
+def moe(a) -> dict:
+    """Qwen3-30B-A3B-shaped expert block on one rank: hidden 2048, expert width 768, top-8 of 128 experts,
+    ``--experts`` of them local (16 = one of eight expert-parallel ranks)."""
+    dev = "cuda"
+    H, I, E, k = 2048, 768, a.experts, 8
+    x = torch.randn(a.m, H, device=dev, dtype=torch.bfloat16)
+    w13 = torch.stack([ref.interleave_gate_up(torch.randn(2 * I, H, device=dev, dtype=torch.bfloat16) * H ** -0.5,
+                                              ops.SWIGLU_BLOCK) for _ in range(E)]).contiguous()
+    w2 = (torch.randn(E, H, I, device=dev, dtype=torch.bfloat16) * I ** -0.5).contiguous()
+    logits = torch.randn(a.m, 128, device=dev, dtype=torch.bfloat16)
+    tw = torch.empty(a.m, k, dtype=torch.float32, device=dev)
+    ti = torch.empty(a.m, k, dtype=torch.int32, device=dev)
+    ops.ext().moe_router_topk(logits, tw, ti, True)
+    ms = _time(lambda: ops.moe_experts(x, w13, w2, tw, ti, 0, ops.SWIGLU_BLOCK, num_experts_global=128), a.iters)
+    local_pairs = int((ti < E).sum())
+    flops = 2 * local_pairs * 3 * I * H
+    return {"case": "moe", "tokens": a.m, "local_experts": E, "local_pairs": local_pairs, "ms": ms,
+            "tflops": flops / ms / 1e9, "weight_gbs": E * 3 * I * H * 2 / ms / 1e6}
+
+
+def w4a16(a) -> dict:
+    dev = "cuda"
+    g = 128
+    x = torch.randn(a.m, a.k, device=dev, dtype=torch.bfloat16)
+    copies = max(1, min(8, int(3e8 // (a.n * a.k // 2)) + 1)) if a.m <= 256 else 1
+    qws = [torch.randint(-(2 ** 31), 2 ** 31 - 1, (a.n, a.k // 8), device=dev, dtype=torch.int64).to(torch.int32)
+           for _ in range(copies)]
+    sc = (torch.rand(a.n, a.k // g, device=dev) * 0.02 + 0.005).to(torch.bfloat16)
+    state = {"i": 0}
+
+    def run():
+        w = qws[state["i"] % copies]
+        state["i"] += 1
+        return ops.w4a16_gemm(x, w, sc, None, g)
+
+    ms = _time(run, a.iters)
+    return {"case": "w4a16", "m": a.m, "n": a.n, "k": a.k, "ms": ms, "tflops": 2 * a.m * a.n * a.k / ms / 1e9,
+            "weight_gbs": a.n * a.k / 2 / ms / 1e6}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["attn_decode", "attn_prefill", "gemm"])
+    ap.add_argument("case", choices=["attn_decode", "attn_prefill", "gemm", "moe", "w4a16"])
+    ap.add_argument("--experts", type=int, default=16, help="moe: local experts")
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--seq", type=int, default=2050)
     ap.add_argument("--hq", type=int, default=32)
@@ -114,8 +161,9 @@ def main() -> None:
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--swiglu", action="store_true")
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--kv-sets", type=int, default=4, help="attn_decode: KV caches used in turn (working set > L2)")
     a = ap.parse_args()
-    out = {"attn_decode": attn_decode, "attn_prefill": attn_prefill, "gemm": gemm}[a.case](a)
+    out = {"attn_decode": attn_decode, "attn_prefill": attn_prefill, "gemm": gemm, "moe": moe, "w4a16": w4a16}[a.case](a)
     ops.check_status()
     print(json.dumps(out))
 

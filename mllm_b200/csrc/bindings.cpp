@@ -178,8 +178,17 @@ void argmax(const Tensor& logits, Tensor& out) {
   TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && out.scalar_type() == at::kLong && out.is_contiguous(),
               "argmax: [B,V] logits, int64 out");
   c10::cuda::CUDAGuard g(logits.device());
-  mb200::launch_argmax(logits.data_ptr(), out.data_ptr<int64_t>(), logits.size(0), logits.size(1), logits.stride(0),
-                       dtype_of(logits), stream_of(logits));
+  const int64_t rows = logits.size(0), vocab = logits.size(1);
+  if (rows <= 64 && vocab >= 32768) {
+    // few rows of a wide vocabulary: spread every row over 32 CTAs (scratch from the caching allocator)
+    auto pv = torch::empty({rows * 32}, torch::TensorOptions().dtype(torch::kFloat32).device(logits.device()));
+    auto pi = torch::empty({rows * 32}, torch::TensorOptions().dtype(torch::kInt32).device(logits.device()));
+    mb200::launch_argmax_split(logits.data_ptr(), out.data_ptr<int64_t>(), pv.data_ptr<float>(), pi.data_ptr<int>(), rows,
+                               vocab, logits.stride(0), dtype_of(logits), stream_of(logits));
+    return;
+  }
+  mb200::launch_argmax(logits.data_ptr(), out.data_ptr<int64_t>(), rows, vocab, logits.stride(0), dtype_of(logits),
+                       stream_of(logits));
 }
 
 void sample(const Tensor& logits, const Tensor& temperature, const Tensor& top_k, const Tensor& top_p,

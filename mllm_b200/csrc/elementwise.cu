@@ -471,6 +471,79 @@ inline int norm_threads(int hidden) {
   return t;
 }
 
+constexpr int kArgmaxChunks = 32;
+
+template <typename T>
+__global__ void argmax_partial_kernel(const T* __restrict__ logits, float* __restrict__ part_val, int* __restrict__ part_idx,
+                                      int vocab, int64_t stride) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float sval[32];
+  __shared__ int sidx[32];
+  const T* row = logits + blockIdx.y * stride;
+  const int per = (vocab + kArgmaxChunks - 1) / kArgmaxChunks;
+  const int lo = blockIdx.x * per, hi = min(vocab, lo + per);
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const float v = load_as_float(row + i);
+    if (v > best || (v == best && i < bi)) {
+      best = v;
+      bi = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  if (lane_id() == 0) {
+    sval[threadIdx.x >> 5] = best;
+    sidx[threadIdx.x >> 5] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int nw = (blockDim.x + 31) >> 5;
+    best = threadIdx.x < nw ? sval[threadIdx.x] : -INFINITY;
+    bi = threadIdx.x < nw ? sidx[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) {
+        best = ov;
+        bi = oi;
+      }
+    }
+    if (threadIdx.x == 0) {
+      part_val[blockIdx.y * kArgmaxChunks + blockIdx.x] = best;
+      part_idx[blockIdx.y * kArgmaxChunks + blockIdx.x] = bi;
+    }
+  }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx,
+                                    int64_t* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  float best = part_val[blockIdx.x * kArgmaxChunks + threadIdx.x];
+  int bi = part_idx[blockIdx.x * kArgmaxChunks + threadIdx.x];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  if (threadIdx.x == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
+}
+
 }  // namespace
 
 
@@ -590,6 +663,24 @@ void launch_argmax(const void* logits, int64_t* out, int rows, int vocab, int64_
                                                                      stride)));
   }
   note_launch();
+}
+
+// Wide vocabularies, few rows: kArgmaxChunks CTAs per row reduce a slice each, a second tiny kernel
+// picks the winner (lowest index wins ties in both stages, so the result equals the one-kernel path).
+int launch_argmax_split(const void* logits, int64_t* out, float* part_val, int* part_idx, int rows, int vocab,
+                        int64_t stride, DType dt, cudaStream_t s) {
+  if (rows == 0) return 0;
+  if (dt == kF32) {
+    launch_pdl(argmax_partial_kernel<float>, dim3(kArgmaxChunks, rows), dim3(512), 0, s, static_cast<const float*>(logits),
+               part_val, part_idx, vocab, stride);
+  } else {
+    MB200_DISPATCH_HALF(dt, (launch_pdl(argmax_partial_kernel<T>, dim3(kArgmaxChunks, rows), dim3(512), 0, s,
+                                        static_cast<const T*>(logits), part_val, part_idx, vocab, stride)));
+  }
+  launch_pdl(argmax_final_kernel, dim3(rows), dim3(32), 0, s, static_cast<const float*>(part_val),
+             static_cast<const int*>(part_idx), out);
+  note_launch(2);
+  return kArgmaxChunks;
 }
 
 }  // namespace mb200

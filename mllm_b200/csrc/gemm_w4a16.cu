@@ -228,45 +228,73 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
       const uint32_t* wrow = p.qweight + (row_ok ? row : 0) * words_per_row;
       int cur_group = -1;
       uint32_t scale2 = 0, off2 = 0;
-      for (int kb = kb0; kb < kb1; ++kb) {
-        uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0;
-        if (row_ok) {  // issue the loads before waiting for the stage
-          w0 = __ldg(reinterpret_cast<const uint4*>(wrow + kb * 8));
-          w1 = __ldg(reinterpret_cast<const uint4*>(wrow + kb * 8) + 1);
-          const int gidx = (kb * 64) / p.group;
-          if (gidx != cur_group) {
-            cur_group = gidx;
-            const float s = to_f32(static_cast<const T*>(p.scales)[row * groups_per_row + gidx]);
-            const float z = p.zeros != nullptr ? static_cast<float>(p.zeros[row * groups_per_row + gidx]) : 8.f;
-            scale2 = splat2<T>(s);
-            off2 = splat2<T>(W4Magic<T>::kBase + z);
-          }
-        }
-        if (*abort_flag || !mbar_wait(&empty_bar[stage], phase ^ 1)) {
-          ok = false;
-          break;
-        }
-        uint8_t* dst = smem + static_cast<size_t>(stage) * C::kStageBytes + r * kRowBytes;
-        const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      // The packed weights of kPf k-blocks are requested ahead of their use (two register sets:
+      // the set being expanded and the set in flight), so a CTA keeps several 32-byte loads per row
+      // outstanding instead of paying one DRAM latency per k-block.
+      constexpr int kPf = 4;
+      uint4 cur[kPf][2], nxt[kPf][2];
+      auto fetch = [&](int kb_first, uint4 (&dst)[kPf][2]) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          uint4 o;
-          if (row_ok) {
-            const uint32_t w = words[j];
-            o.x = dequant_pair<T>(w, off2, scale2);
-            o.y = dequant_pair<T>(w >> 8, off2, scale2);
-            o.z = dequant_pair<T>(w >> 16, off2, scale2);
-            o.w = dequant_pair<T>(w >> 24, off2, scale2);
+        for (int u = 0; u < kPf; ++u) {
+          const int kb = kb_first + u;
+          if (row_ok && kb < kb1) {
+            dst[u][0] = __ldg(reinterpret_cast<const uint4*>(wrow + kb * 8));
+            dst[u][1] = __ldg(reinterpret_cast<const uint4*>(wrow + kb * 8) + 1);
           } else {
-            o = make_uint4(0, 0, 0, 0);
+            dst[u][0] = make_uint4(0, 0, 0, 0);
+            dst[u][1] = make_uint4(0, 0, 0, 0);
           }
-          *reinterpret_cast<uint4*>(dst + ((j ^ (r & 7)) << 4)) = o;
         }
-        fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
-        mbar_arrive(&full_w[stage]);
-        if (++stage == C::kStages) {
-          stage = 0;
-          phase ^= 1;
+      };
+      fetch(kb0, cur);
+      for (int kbg = kb0; kbg < kb1 && ok; kbg += kPf) {
+        fetch(kbg + kPf, nxt);
+#pragma unroll
+        for (int u = 0; u < kPf; ++u) {
+          const int kb = kbg + u;
+          if (kb >= kb1) break;
+          if (row_ok) {
+            const int gidx = (kb * 64) / p.group;
+            if (gidx != cur_group) {
+              cur_group = gidx;
+              const float sv = to_f32(static_cast<const T*>(p.scales)[row * groups_per_row + gidx]);
+              const float z = p.zeros != nullptr ? static_cast<float>(p.zeros[row * groups_per_row + gidx]) : 8.f;
+              scale2 = splat2<T>(sv);
+              off2 = splat2<T>(W4Magic<T>::kBase + z);
+            }
+          }
+          if (*abort_flag || !mbar_wait(&empty_bar[stage], phase ^ 1)) {
+            ok = false;
+            break;
+          }
+          uint8_t* dst = smem + static_cast<size_t>(stage) * C::kStageBytes + r * kRowBytes;
+          const uint32_t words[8] = {cur[u][0].x, cur[u][0].y, cur[u][0].z, cur[u][0].w,
+                                     cur[u][1].x, cur[u][1].y, cur[u][1].z, cur[u][1].w};
+#pragma unroll
+          for (int jj = 0; jj < 8; ++jj) {
+            uint4 o4;
+            if (row_ok) {
+              const uint32_t w = words[jj];
+              o4.x = dequant_pair<T>(w, off2, scale2);
+              o4.y = dequant_pair<T>(w >> 8, off2, scale2);
+              o4.z = dequant_pair<T>(w >> 16, off2, scale2);
+              o4.w = dequant_pair<T>(w >> 24, off2, scale2);
+            } else {
+              o4 = make_uint4(0, 0, 0, 0);
+            }
+            *reinterpret_cast<uint4*>(dst + ((jj ^ (r & 7)) << 4)) = o4;
+          }
+          fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+          mbar_arrive(&full_w[stage]);
+          if (++stage == C::kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kPf; ++u) {
+          cur[u][0] = nxt[u][0];
+          cur[u][1] = nxt[u][1];
         }
       }
     }

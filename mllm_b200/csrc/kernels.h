@@ -49,6 +49,9 @@ void launch_per_token_quant_int8(const void* x, int8_t* q, float* scale, int row
 // ----- sampling -------------------------------------------------------------------------
 void launch_argmax(const void* logits, int64_t* out, int rows, int vocab, int64_t stride, DType dt,
                    cudaStream_t s);
+// two-stage variant for few rows x wide vocabulary; part_val / part_idx hold rows * 32 entries
+int launch_argmax_split(const void* logits, int64_t* out, float* part_val, int* part_idx, int rows, int vocab,
+                        int64_t stride, DType dt, cudaStream_t s);
 
 // one token per row: temperature (<= 1e-6: greedy), top-k (<= 0: off), top-p, min-p (may be null),
 // inverse-CDF draw with uniform[row] in [0, 1)
