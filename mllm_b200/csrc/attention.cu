@@ -815,189 +815,6 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
     static_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(v);
 }
 
-// -----------------------------------------------------------------------------------------------
-// Decode attention for small GQA groups (G <= 4 query heads per KV head): a bandwidth kernel.
-// Decode attention reads every K and V row once and does ~4*G FLOP per byte, far below what the
-// tensor cores need to matter, so this kernel is organised around keeping HBM requests in flight:
-// a half-warp owns one token row (16 lanes x 16 bytes = the 256-byte row), a warp walks token pairs,
-// four pairs (8 independent 16-byte loads per lane) are requested before any is used, and several
-// CTAs with 8 warps each are resident per SM.  Scores are fp32 dot products reduced over the 16 lanes,
-// softmax is online per half-warp with lazy rescaling, P*V accumulates in registers; half-warps and
-// warps are merged through shared memory and splits through attn_merge_kernel.
-// -----------------------------------------------------------------------------------------------
-constexpr int kStreamWarps = 8;
-constexpr int kStreamThreads = kStreamWarps * 32;
-constexpr int kStreamUnroll = 4;
-
-__device__ __forceinline__ void unpack8(const uint4& raw, int is_f16, float (&f)[8]) {
-  const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    if (is_f16) {
-      const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&u[i]));
-      f[2 * i] = v.x;
-      f[2 * i + 1] = v.y;
-    } else {
-      f[2 * i] = __uint_as_float(u[i] << 16);
-      f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
-    }
-  }
-}
-
-template <int G>
-__global__ void __launch_bounds__(kStreamThreads, 2) attn_decode_stream_kernel(const AttnParams p) {
-  pdl_wait();
-  __shared__ float sm_m[kStreamWarps * 2][G];
-  __shared__ float sm_l[kStreamWarps * 2][G];
-  __shared__ float sm_o[kStreamWarps * 2][G][kD];
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int half = lane >> 4, ch = lane & 15;
-  const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
-  const int req = p.req_pool_indices[b];
-  const int seq_len = p.seq_lens[b];
-  // contiguous token range of this split (multiples of 16 tokens = one pass of the CTA)
-  const int per = ((seq_len + p.num_splits - 1) / p.num_splits + 15) & ~15;
-  const int kv_begin = split * per;
-  const int kv_end = min(seq_len, kv_begin + per);
-  const int* rtt = p.req_to_token + static_cast<int64_t>(req) * p.rtt_stride;
-  const uint16_t* kbase = static_cast<const uint16_t*>(p.k_cache) + static_cast<int64_t>(hk) * kD + ch * 8;
-  const uint16_t* vbase = static_cast<const uint16_t*>(p.v_cache) + static_cast<int64_t>(hk) * kD + ch * 8;
-
-  // this lane's 8 features of every query head of the group, pre-scaled
-  float q[G][8];
-#pragma unroll
-  for (int gi = 0; gi < G; ++gi) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.q) + static_cast<int64_t>(b) * p.q_stride +
-                                                      static_cast<int64_t>(hk * G + gi) * kD + ch * 8);
-    unpack8(raw, p.out_f16, q[gi]);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) q[gi][e] *= p.scale_log2;
-  }
-  float m[G], l[G], o[G][8];
-#pragma unroll
-  for (int gi = 0; gi < G; ++gi) {
-    m[gi] = -INFINITY;
-    l[gi] = 0.f;
-#pragma unroll
-    for (int e = 0; e < 8; ++e) o[gi][e] = 0.f;
-  }
-  bool bad = false;
-  // token of (warp, half) in pass `it`: kv_begin + it * 16 + warp * 2 + half
-  const int n_pass = (kv_end - kv_begin + 15) >> 4;
-  for (int it0 = 0; it0 < n_pass; it0 += kStreamUnroll) {
-    int slot[kStreamUnroll];
-    uint4 kr[kStreamUnroll], vr[kStreamUnroll];
-#pragma unroll
-    for (int u = 0; u < kStreamUnroll; ++u) {
-      const int t = kv_begin + (it0 + u) * 16 + warp * 2 + half;
-      slot[u] = (it0 + u < n_pass && t < kv_end) ? __ldg(rtt + t) : -1;
-    }
-#pragma unroll
-    for (int u = 0; u < kStreamUnroll; ++u) {
-      if (slot[u] < -1 || slot[u] >= p.num_slots) {
-        bad = true;
-        slot[u] = -1;
-      }
-      if (slot[u] >= 0) {
-        const int64_t off = static_cast<int64_t>(slot[u]) * p.hkv * kD;
-        kr[u] = __ldcs(reinterpret_cast<const uint4*>(kbase + off));
-        vr[u] = __ldcs(reinterpret_cast<const uint4*>(vbase + off));
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < kStreamUnroll; ++u) {
-      const bool valid = slot[u] >= 0;
-      float kf[8], vf[8];
-      if (valid) {
-        unpack8(kr[u], p.out_f16, kf);
-        unpack8(vr[u], p.out_f16, vf);
-      }
-      float sc[G];
-#pragma unroll
-      for (int gi = 0; gi < G; ++gi) {
-        float d = 0.f;
-        if (valid) {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) d = fmaf(kf[e], q[gi][e], d);
-        }
-        // sum over the 16 lanes of the half-warp
-        d += __shfl_xor_sync(0xffffffffu, d, 8);
-        d += __shfl_xor_sync(0xffffffffu, d, 4);
-        d += __shfl_xor_sync(0xffffffffu, d, 2);
-        d += __shfl_xor_sync(0xffffffffu, d, 1);
-        sc[gi] = valid ? d : -INFINITY;
-      }
-      // lazy rescale: only when some head's maximum grew noticeably (uniform decision per warp)
-      bool grow = false;
-#pragma unroll
-      for (int gi = 0; gi < G; ++gi) grow |= sc[gi] > m[gi] + kRescaleThreshold;
-      if (__any_sync(0xffffffffu, grow)) {
-#pragma unroll
-        for (int gi = 0; gi < G; ++gi) {
-          if (sc[gi] > m[gi] + kRescaleThreshold) {
-            const float f = (m[gi] == -INFINITY) ? 0.f : fast_exp2(m[gi] - sc[gi]);
-            m[gi] = sc[gi];
-            l[gi] *= f;
-#pragma unroll
-            for (int e = 0; e < 8; ++e) o[gi][e] *= f;
-          }
-        }
-      }
-      if (valid) {
-#pragma unroll
-        for (int gi = 0; gi < G; ++gi) {
-          const float pw = fast_exp2(sc[gi] - m[gi]);
-          l[gi] += pw;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) o[gi][e] = fmaf(pw, vf[e], o[gi][e]);
-        }
-      }
-    }
-  }
-  if (bad && p.status != nullptr) atomicExch(p.status, kStatusBadIndex);
-
-  // ---- merge the 16 half-warp streams of the CTA ----
-  const int stream = warp * 2 + half;
-#pragma unroll
-  for (int gi = 0; gi < G; ++gi) {
-    if (ch == 0) {
-      sm_m[stream][gi] = m[gi];
-      sm_l[stream][gi] = l[gi];
-    }
-#pragma unroll
-    for (int e = 0; e < 8; ++e) sm_o[stream][gi][ch * 8 + e] = o[gi][e];
-  }
-  __syncthreads();
-  for (int idx = tid; idx < G * kD; idx += kStreamThreads) {
-    const int gi = idx / kD, d = idx % kD;
-    float mm = -INFINITY;
-#pragma unroll
-    for (int sidx = 0; sidx < kStreamWarps * 2; ++sidx) mm = fmaxf(mm, sm_m[sidx][gi]);
-    float den = 0.f, acc = 0.f;
-#pragma unroll
-    for (int sidx = 0; sidx < kStreamWarps * 2; ++sidx) {
-      const float ms = sm_m[sidx][gi];
-      const float w = (ms == -INFINITY) ? 0.f : fast_exp2(ms - mm);
-      den += w * sm_l[sidx][gi];
-      acc += w * sm_o[sidx][gi][d];
-    }
-    const float v = den > 0.f ? acc / den : 0.f;
-    const int head = hk * G + gi;
-    if (p.num_splits > 1) {
-      p.part_o[((static_cast<int64_t>(b) * p.hq + head) * p.num_splits + split) * kD + d] = v;
-      if (d == 0)
-        p.part_lse[(static_cast<int64_t>(b) * p.hq + head) * p.num_splits + split] = den > 0.f ? mm + log2f(den) : -INFINITY;
-    } else {
-      const int64_t oi = (static_cast<int64_t>(b) * p.hq + head) * kD + d;
-      if (p.out_f16)
-        static_cast<__half*>(p.out)[oi] = __float2half_rn(v);
-      else
-        static_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16_rn(v);
-    }
-  }
-}
-
-
 bool set_attn_smem() {
   static bool done = false, ok = false;
   if (!done) {
@@ -1009,23 +826,8 @@ bool set_attn_smem() {
 
 }  // namespace
 
-// MLLM_B200_DECODE_STREAM=1 routes small GQA groups to the bandwidth kernel instead of the tensor-core one.
-bool stream_decode_enabled() {
-  static const bool on = [] {
-    const char* v = std::getenv("MLLM_B200_DECODE_STREAM");
-    return v != nullptr && std::atoi(v) != 0;
-  }();
-  return on;
-}
-
 int decode_num_splits(int batch, int hkv, int max_seq_len, int num_sms) {
   const int ctas = std::max(1, batch * hkv);
-  if (stream_decode_enabled()) {
-    // bandwidth kernel: about four 8-warp CTAs per SM, at least 256 tokens per split
-    int splits = (4 * num_sms + ctas - 1) / ctas;
-    splits = std::min(splits, std::max(1, max_seq_len / 256));
-    return std::max(1, std::min(splits, 64));
-  }
   // one resident CTA per SM: fill a single wave, never start a second one for a remainder
   const int tiles = std::max(1, (max_seq_len + kDT - 1) / kDT);
   int splits = num_sms / ctas;
@@ -1082,20 +884,6 @@ int launch_attention(const AttnArgs& a, cudaStream_t s) {
   p.idesc_o = umma_idesc(kRows, kD, 1, fmt, fmt, 0, 1);
   if (a.batch <= 0) return 0;
   dim3 grid;
-  if (a.is_decode && (g == 1 || g == 2 || g == 4) && stream_decode_enabled()) {
-    grid = dim3(p.num_splits, a.hkv, a.batch);
-    switch (g) {
-      case 1: launch_pdl(attn_decode_stream_kernel<1>, grid, dim3(kStreamThreads), 0, s, p); break;
-      case 2: launch_pdl(attn_decode_stream_kernel<2>, grid, dim3(kStreamThreads), 0, s, p); break;
-      default: launch_pdl(attn_decode_stream_kernel<4>, grid, dim3(kStreamThreads), 0, s, p); break;
-    }
-    note_launch();
-    if (p.num_splits > 1) {
-      launch_pdl(attn_merge_kernel, dim3(a.hq, a.batch), dim3(kD), 0, s, a.part_o, a.part_lse, a.out, a.hq, p.num_splits, p.out_f16);
-      note_launch();
-    }
-    return cudaGetLastError() == cudaSuccess ? 0 : -4;
-  }
   if (a.is_decode && g <= 32) {
     const int nq = g <= 16 ? 16 : 32;
     p.idesc_s = umma_idesc(kRows, nq, 1, fmt, fmt, 0, 0);

@@ -233,22 +233,29 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
       // outstanding instead of paying one DRAM latency per k-block.
       constexpr int kPf = 4;
       uint4 cur[kPf][2], nxt[kPf][2];
-      auto fetch = [&](int kb_first, uint4 (&dst)[kPf][2]) {
+      T cur_s[kPf], nxt_s[kPf];        // group scale (and zero point) of each prefetched k-block
+      uint8_t cur_z[kPf], nxt_z[kPf];
+      auto fetch = [&](int kb_first, uint4 (&dst)[kPf][2], T (&ds)[kPf], uint8_t (&dz)[kPf]) {
 #pragma unroll
         for (int u = 0; u < kPf; ++u) {
           const int kb = kb_first + u;
           if (row_ok && kb < kb1) {
             dst[u][0] = __ldg(reinterpret_cast<const uint4*>(wrow + kb * 8));
             dst[u][1] = __ldg(reinterpret_cast<const uint4*>(wrow + kb * 8) + 1);
+            const int64_t gi = row * groups_per_row + (kb * 64) / p.group;
+            ds[u] = static_cast<const T*>(p.scales)[gi];
+            dz[u] = p.zeros != nullptr ? p.zeros[gi] : static_cast<uint8_t>(8);
           } else {
             dst[u][0] = make_uint4(0, 0, 0, 0);
             dst[u][1] = make_uint4(0, 0, 0, 0);
+            ds[u] = from_f32<T>(0.f);
+            dz[u] = 8;
           }
         }
       };
-      fetch(kb0, cur);
+      fetch(kb0, cur, cur_s, cur_z);
       for (int kbg = kb0; kbg < kb1 && ok; kbg += kPf) {
-        fetch(kbg + kPf, nxt);
+        fetch(kbg + kPf, nxt, nxt_s, nxt_z);
 #pragma unroll
         for (int u = 0; u < kPf; ++u) {
           const int kb = kbg + u;
@@ -257,10 +264,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
             const int gidx = (kb * 64) / p.group;
             if (gidx != cur_group) {
               cur_group = gidx;
-              const float sv = to_f32(static_cast<const T*>(p.scales)[row * groups_per_row + gidx]);
-              const float z = p.zeros != nullptr ? static_cast<float>(p.zeros[row * groups_per_row + gidx]) : 8.f;
-              scale2 = splat2<T>(sv);
-              off2 = splat2<T>(W4Magic<T>::kBase + z);
+              scale2 = splat2<T>(to_f32(cur_s[u]));
+              off2 = splat2<T>(W4Magic<T>::kBase + static_cast<float>(cur_z[u]));
             }
           }
           if (*abort_flag || !mbar_wait(&empty_bar[stage], phase ^ 1)) {
@@ -295,6 +300,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
         for (int u = 0; u < kPf; ++u) {
           cur[u][0] = nxt[u][0];
           cur[u][1] = nxt[u][1];
+          cur_s[u] = nxt_s[u];
+          cur_z[u] = nxt_z[u];
         }
       }
     }

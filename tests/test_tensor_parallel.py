@@ -56,3 +56,24 @@ def test_tp2_fused_prefill_matches_nccl_on_gpu(tmp_path):
     fused = _launch(2, str(tmp_path / "fused.pt"), "cuda", "bfloat16", 29616, dict(env, TP_TEST_COMM="fused", TP_TEST_EXPECT_FUSED_PREFILL="1"))
     assert (fused - ref).abs().max().item() < 0.15
     assert (fused.argmax(-1) == ref.argmax(-1)).float().mean().item() > 0.8
+
+
+@pytest.mark.parametrize("ep", ["0", "1"])
+def test_moe_tp2_and_ep2_match_single_rank_on_cpu(tmp_path, ep):
+    """Qwen3-MoE on two gloo ranks: experts sharded along their width (tensor parallel) or split between
+    the ranks (expert parallel, attention stays tensor parallel); logits equal the single-rank model."""
+    env = {"TP_TEST_PRESET": "qwen3-moe-tiny"}
+    one = _launch(1, str(tmp_path / "moe1.pt"), "cpu", "float32", 29621, env)
+    two = _launch(2, str(tmp_path / "moe2.pt"), "cpu", "float32", 29622 + int(ep), dict(env, TP_TEST_EP=ep))
+    torch.testing.assert_close(two, one, atol=3e-4, rtol=3e-4)
+
+
+@pytest.mark.gpu
+def test_moe_ep2_matches_single_rank_on_gpu(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = {"TP_TEST_PRESET": "qwen3-moe-tiny"}
+    one = _launch(1, str(tmp_path / "moe1.pt"), "cuda", "bfloat16", 29625, env)
+    two = _launch(2, str(tmp_path / "moe2.pt"), "cuda", "bfloat16", 29626, dict(env, TP_TEST_EP="1"))
+    assert (two - one).abs().max().item() < 0.2
+    assert (two.argmax(-1) == one.argmax(-1)).float().mean().item() > 0.8

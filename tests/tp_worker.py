@@ -31,6 +31,18 @@ def full_state_dict(cfg, seed=0, dtype=torch.float32):
             p + "post_attention_layernorm.weight": torch.ones(H, dtype=dtype) + r(H),
             p + "mlp.gate_proj.weight": r(I, H), p + "mlp.up_proj.weight": r(I, H), p + "mlp.down_proj.weight": r(H, I),
         })
+    E = getattr(cfg, "num_experts", 0)
+    if E:
+        Im = cfg.moe_intermediate_size
+        for i in range(cfg.num_hidden_layers):
+            p = f"model.layers.{i}.mlp."
+            for k in ("gate_proj.weight", "up_proj.weight", "down_proj.weight"):
+                sd.pop(p + k, None)
+            sd[p + "gate.weight"] = r(E, H) * 10
+            for e in range(E):
+                sd[p + f"experts.{e}.gate_proj.weight"] = r(Im, H)
+                sd[p + f"experts.{e}.up_proj.weight"] = r(Im, H)
+                sd[p + f"experts.{e}.down_proj.weight"] = r(H, Im)
     return sd
 
 
@@ -44,13 +56,14 @@ def run(out_path: str, device: str, dtype_name: str) -> None:
     rank = int(os.environ.get("RANK", "0"))
     pstate.init_distributed(backend="gloo" if device == "cpu" else "nccl", timeout_s=120)
     if world > 1:
-        pstate.initialize_model_parallel(tp_size=world)
+        pstate.initialize_model_parallel(tp_size=world, ep_size=world if os.environ.get("TP_TEST_EP") == "1" else 1)
     dev = device if device == "cpu" else f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}"
-    cfg = get_preset("qwen3-tiny", num_attention_heads=4, num_key_value_heads=2, tie_word_embeddings=False)
+    preset = os.environ.get("TP_TEST_PRESET", "qwen3-tiny")
+    cfg = get_preset(preset, num_attention_heads=4, num_key_value_heads=2, tie_word_embeddings=False)
     L = int(os.environ.get("TP_TEST_PREFILL_LEN", "9"))
-    sc = ServerConfig(model_path="preset:qwen3-tiny", dtype=dtype_name, max_running_requests=4,
+    sc = ServerConfig(model_path=f"preset:{preset}", dtype=dtype_name, max_running_requests=4,
                       max_total_tokens=max(1024, 4 * L), chunked_prefill_size=max(2048, 2 * L),
-                      tp_size=world, disable_cuda_graph=os.environ.get("TP_TEST_GRAPH", "0") != "1",
+                      tp_size=world, ep_size=world if os.environ.get("TP_TEST_EP") == "1" else 1, disable_cuda_graph=os.environ.get("TP_TEST_GRAPH", "0") != "1",
                       comm_backend=os.environ.get("TP_TEST_COMM", "fused"))
     mr = ModelRunner(sc, hf_config=cfg, device=dev)
     mr.initialize()
@@ -60,6 +73,10 @@ def run(out_path: str, device: str, dtype_name: str) -> None:
         if hasattr(m, "quant_method"):
             m._gate_up_interleaved = False
             m.quant_method.process_weights_after_loading(m)
+        if hasattr(m, "swiglu_block") and hasattr(m, "w13"):
+            m.swiglu_block = 0
+    if hasattr(mr.model, "post_load"):
+        mr.model.post_load()
     if mr.cuda_graph_runner is not None:  # graphs hold the addresses of the weights they were captured with
         mr.cuda_graph_runner = None
         mr.init_cuda_graphs()
