@@ -115,6 +115,18 @@ def text_config_of(hf_config) -> Any:
     return getattr(hf_config, "text_config", None) or hf_config
 
 
+_SHORTHAND_SCHEMES = {
+    # per-channel symmetric int8 weights, per-token dynamic int8 activations
+    "w8a8": dict(quant_method="compressed-tensors", format="int-quantized", ignore=["lm_head"], config_groups=dict(group_0=dict(
+        weights=dict(num_bits=8, type="int", symmetric=True, strategy="channel", dynamic=False),
+        input_activations=dict(num_bits=8, type="int", symmetric=True, strategy="token", dynamic=True)))),
+    # 4-bit symmetric weights in groups of 128, 16-bit activations
+    "w4a16": dict(quant_method="compressed-tensors", format="pack-quantized", ignore=["lm_head"], config_groups=dict(group_0=dict(
+        weights=dict(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128, dynamic=False),
+        input_activations=None))),
+}
+
+
 class ModelRunner:
     def __init__(self, server_config: ServerConfig, hf_config: Any = None, gpu_id: int = 0,
                  quantization_method: Optional[str] = None, kv_cache_dtype: str = "auto",
@@ -231,6 +243,9 @@ class ModelRunner:
         method = self.quantization_method or (qdict or {}).get("quant_method")
         if not method:
             return None
+        if method in _SHORTHAND_SCHEMES and not qdict:
+            # random-init / bench runs: the scheme by name, laid out as compressed-tensors writes it
+            qdict, method = dict(_SHORTHAND_SCHEMES[method]), "compressed-tensors"
         if method == "awq":
             method = "awq_marlin"
         cls = get_quantization_config(method)
