@@ -91,6 +91,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   return false;
 }
 
+// Bounded wait for warps that share their scheduler with working warps: backs off from the first
+// failed poll so that the polling loop does not compete for issue slots.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, uint32_t sleep_ns = 200) {
+  for (uint32_t i = 0; i < kMaxPolls; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(sleep_ns);
+  }
+  return false;
+}
+
 // ---------------------------------------------------------------------------
 // fences between the generic proxy, the async proxy (TMA / tcgen05) and threads
 // ---------------------------------------------------------------------------

@@ -4,8 +4,8 @@
 // qweight int32 [N, K/8] (nibble i of word j of a row = element 8j + i), scales [N, K/group] in the
 // activation type, zeros uint8 [N, K/group] or null (symmetric: zero point 8).
 //
-// The packed weights are the 128-row MMA operand: four "dequant" warps (thread = weight row) load 32
-// bytes of nibbles per 64-element K block, expand them with the exponent-bias trick (bf16 0x4300 | q is
+// The packed weights are the 128-row MMA operand: TMA stages 128 bytes of nibbles per row (four
+// 64-element K blocks) in shared memory, four "dequant" warps (thread = weight row) expand them with the exponent-bias trick (bf16 0x4300 | q is
 // exactly 128 + q; fp16 0x6400 | q is 1024 + q), subtract the offset exactly, multiply by the group scale
 // (one rounding, the same value as rounding the fp32 dequantised weight) and store the block in the
 // 128-byte-swizzled K-major layout the MMA reads; activations arrive by TMA as the MMA N operand
@@ -50,7 +50,9 @@ struct W4Cfg {
   static constexpr int kWBytes = kBM * kRowBytes;  // 16 KB of expanded weights per stage
   static constexpr int kXBytes = BN * kRowBytes;
   static constexpr int kStageBytes = kWBytes + kXBytes;
-  static constexpr int kStagesRaw = 196608 / kStageBytes;
+  static constexpr int kRawStages = BN >= 128 ? 2 : 4;   // packed-weight ring: 128 rows x 128 B = four k-blocks each
+  static constexpr int kRawBytes = kBM * kRowBytes;      // 16 KB
+  static constexpr int kStagesRaw = (196608 - kRawStages * kRawBytes) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kTmemColsRaw = 2 * BN;
   static constexpr int kTmemCols =
@@ -105,17 +107,20 @@ __device__ __forceinline__ uint32_t splat2<__half>(float v) {
 
 template <typename T, int BN>
 __global__ void __launch_bounds__(kW4Threads, 1)
-w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
+w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const W4Params p) {
   using C = W4Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(C::kStages) * C::kStageBytes);
+  uint8_t* raw_ring = smem + static_cast<size_t>(C::kStages) * C::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(raw_ring + C::kRawStages * C::kRawBytes);
   uint64_t* full_x = bars;
   uint64_t* full_w = bars + C::kStages;
   uint64_t* empty_bar = bars + 2 * C::kStages;
   uint64_t* acc_full = bars + 3 * C::kStages;
   uint64_t* acc_empty = acc_full + 2;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* raw_full = acc_empty + 2;                 // [kRawStages] TMA bytes landed
+  uint64_t* raw_empty = raw_full + C::kRawStages;     // [kRawStages] the four expansion warps have copied their rows out
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(raw_empty + C::kRawStages);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -123,16 +128,21 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(&full_x[s], 1);
-      mbar_init(&full_w[s], 128);
+      mbar_init(&full_w[s], 4);  // one arrival per expansion warp
       mbar_init(&empty_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 128);
     }
+    for (int s = 0; s < C::kRawStages; ++s) {
+      mbar_init(&raw_full[s], 1);
+      mbar_init(&raw_empty[s], 4);
+    }
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_x);
+    tma_prefetch_desc(&tm_w);
   }
   __syncthreads();
   if (warp == 2) {
@@ -155,14 +165,26 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
   };
 
   if (warp == 0 && lane == 0) {
-    // ---------------- TMA producer: activations ----------------
-    int stage = 0;
-    uint32_t phase = 0;
+    // ---------------- TMA producer: activations and packed weights ----------------
+    int stage = 0, rstage = 0;
+    uint32_t phase = 0, rphase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-      const int tm = tile % p.tiles_m;
+      const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
       for (int kb = kb0; kb < kb1; ++kb) {
-        if (*abort_flag || !mbar_wait(&empty_bar[stage], phase ^ 1)) {
+        if (((kb - kb0) & 3) == 0) {  // kb0 is a multiple of four: one 128-byte column block of nibbles
+          if (*abort_flag || !mbar_wait_relaxed(&raw_empty[rstage], rphase ^ 1)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&raw_full[rstage], C::kRawBytes);
+          tma_load_2d(raw_ring + rstage * C::kRawBytes, &tm_w, &raw_full[rstage], (kb >> 2) * kRowBytes, tn * kBM);
+          if (++rstage == C::kRawStages) {
+            rstage = 0;
+            rphase ^= 1;
+          }
+        }
+        if (*abort_flag || !mbar_wait_relaxed(&empty_bar[stage], phase ^ 1)) {
           ok = false;
           break;
         }
@@ -184,14 +206,14 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
     int idx = 0;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++idx) {
       const int acc = idx & 1;
-      if (*abort_flag || !mbar_wait(&acc_empty[acc], ((idx >> 1) & 1) ^ 1)) {
+      if (*abort_flag || !mbar_wait_relaxed(&acc_empty[acc], ((idx >> 1) & 1) ^ 1)) {
         ok = false;
         break;
       }
       tc_fence_after_sync();
       const uint32_t d_base = tmem_base + acc * BN;
       for (int kb = kb0; kb < kb1; ++kb) {
-        if (*abort_flag || !mbar_wait(&full_x[stage], phase) || !mbar_wait(&full_w[stage], phase)) {
+        if (*abort_flag || !mbar_wait_relaxed(&full_x[stage], phase, 40) || !mbar_wait_relaxed(&full_w[stage], phase, 40)) {
           ok = false;
           break;
         }
@@ -215,66 +237,57 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
     if (!ok) fail();
   } else if (warp >= 4 && warp < 8) {
     // ---------------- weight expansion: thread = weight row of the tile ----------------
+    // The packed rows arrive by TMA, 128 bytes (four k-blocks) per row at a time, so DRAM sees whole
+    // 128-byte lines; a thread copies its row out of the (128-byte swizzled) staging tile, releases it,
+    // and expands one k-block per operand stage.
     const int r = threadIdx.x - 128;
-    int stage = 0;
-    uint32_t phase = 0;
+    int stage = 0, rstage = 0;
+    uint32_t phase = 0, rphase = 0;
     bool ok = true;
-    const int words_per_row = p.k >> 3;
     const int groups_per_row = p.k / p.group;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
       const int tn = tile / p.tiles_m;
       const int64_t row = static_cast<int64_t>(tn) * kBM + r;
       const bool row_ok = row < p.n;
-      const uint32_t* wrow = p.qweight + (row_ok ? row : 0) * words_per_row;
-      int cur_group = -1;
-      uint32_t scale2 = 0, off2 = 0;
-      // The packed weights of kPf k-blocks are requested ahead of their use (two register sets:
-      // the set being expanded and the set in flight), so a CTA keeps several 32-byte loads per row
-      // outstanding instead of paying one DRAM latency per k-block.
-      constexpr int kPf = 4;
-      uint4 cur[kPf][2], nxt[kPf][2];
-      T cur_s[kPf], nxt_s[kPf];        // group scale (and zero point) of each prefetched k-block
-      uint8_t cur_z[kPf], nxt_z[kPf];
-      auto fetch = [&](int kb_first, uint4 (&dst)[kPf][2], T (&ds)[kPf], uint8_t (&dz)[kPf]) {
+      for (int kbg = kb0; kbg < kb1 && ok; kbg += 4) {
+        // scales / zero points of the (up to four) groups touched by this column block: requested first
+        T sc[4];
+        uint8_t zp[4];
 #pragma unroll
-        for (int u = 0; u < kPf; ++u) {
-          const int kb = kb_first + u;
-          if (row_ok && kb < kb1) {
-            dst[u][0] = __ldg(reinterpret_cast<const uint4*>(wrow + kb * 8));
-            dst[u][1] = __ldg(reinterpret_cast<const uint4*>(wrow + kb * 8) + 1);
-            const int64_t gi = row * groups_per_row + (kb * 64) / p.group;
-            ds[u] = static_cast<const T*>(p.scales)[gi];
-            dz[u] = p.zeros != nullptr ? p.zeros[gi] : static_cast<uint8_t>(8);
-          } else {
-            dst[u][0] = make_uint4(0, 0, 0, 0);
-            dst[u][1] = make_uint4(0, 0, 0, 0);
-            ds[u] = from_f32<T>(0.f);
-            dz[u] = 8;
-          }
+        for (int u = 0; u < 4; ++u) {
+          const int kb = min(kbg + u, kb1 - 1);
+          const int64_t gi = (row_ok ? row : 0) * groups_per_row + (kb * 64) / p.group;
+          sc[u] = static_cast<const T*>(p.scales)[gi];
+          zp[u] = p.zeros != nullptr ? p.zeros[gi] : static_cast<uint8_t>(8);
         }
-      };
-      fetch(kb0, cur, cur_s, cur_z);
-      for (int kbg = kb0; kbg < kb1 && ok; kbg += kPf) {
-        fetch(kbg + kPf, nxt, nxt_s, nxt_z);
+        if (*abort_flag || !mbar_wait(&raw_full[rstage], rphase)) {
+          ok = false;
+          break;
+        }
+        uint4 raw[8];
+        {
+          const uint8_t* src = raw_ring + rstage * C::kRawBytes + r * kRowBytes;
 #pragma unroll
-        for (int u = 0; u < kPf; ++u) {
-          const int kb = kbg + u;
-          if (kb >= kb1) break;
-          if (row_ok) {
-            const int gidx = (kb * 64) / p.group;
-            if (gidx != cur_group) {
-              cur_group = gidx;
-              scale2 = splat2<T>(to_f32(cur_s[u]));
-              off2 = splat2<T>(W4Magic<T>::kBase + static_cast<float>(cur_z[u]));
-            }
-          }
+          for (int c = 0; c < 8; ++c) raw[c] = *reinterpret_cast<const uint4*>(src + ((c ^ (r & 7)) << 4));
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&raw_empty[rstage]);  // arrivals on one barrier serialise: one per warp
+        if (++rstage == C::kRawStages) {
+          rstage = 0;
+          rphase ^= 1;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (kbg + u >= kb1) break;
+          const uint32_t scale2 = splat2<T>(to_f32(sc[u]));
+          const uint32_t off2 = splat2<T>(W4Magic<T>::kBase + static_cast<float>(zp[u]));
           if (*abort_flag || !mbar_wait(&empty_bar[stage], phase ^ 1)) {
             ok = false;
             break;
           }
           uint8_t* dst = smem + static_cast<size_t>(stage) * C::kStageBytes + r * kRowBytes;
-          const uint32_t words[8] = {cur[u][0].x, cur[u][0].y, cur[u][0].z, cur[u][0].w,
-                                     cur[u][1].x, cur[u][1].y, cur[u][1].z, cur[u][1].w};
+          const uint32_t words[8] = {raw[2 * u].x, raw[2 * u].y, raw[2 * u].z, raw[2 * u].w,
+                                     raw[2 * u + 1].x, raw[2 * u + 1].y, raw[2 * u + 1].z, raw[2 * u + 1].w};
 #pragma unroll
           for (int jj = 0; jj < 8; ++jj) {
             uint4 o4;
@@ -290,18 +303,12 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
             *reinterpret_cast<uint4*>(dst + ((jj ^ (r & 7)) << 4)) = o4;
           }
           fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
-          mbar_arrive(&full_w[stage]);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full_w[stage]);
           if (++stage == C::kStages) {
             stage = 0;
             phase ^= 1;
           }
-        }
-#pragma unroll
-        for (int u = 0; u < kPf; ++u) {
-          cur[u][0] = nxt[u][0];
-          cur[u][1] = nxt[u][1];
-          cur_s[u] = nxt_s[u];
-          cur_z[u] = nxt_z[u];
         }
       }
     }
@@ -315,7 +322,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++idx) {
       const int tn = tile / p.tiles_m, tm = tile % p.tiles_m;
       const int acc = idx & 1;
-      if (*abort_flag || !mbar_wait(&acc_full[acc], (idx >> 1) & 1)) {
+      if (*abort_flag || !mbar_wait_relaxed(&acc_full[acc], (idx >> 1) & 1, 500)) {
         ok = false;
         break;
       }
@@ -378,17 +385,17 @@ __global__ void w4a16_splitk_reduce_kernel(const float* __restrict__ ws, T* __re
 }
 
 template <typename T, int BN>
-int launch_w4_cfg(const CUtensorMap& tx, const W4Params& p, dim3 grid, cudaStream_t s) {
+int launch_w4_cfg(const CUtensorMap& tx, const CUtensorMap& tw, const W4Params& p, dim3 grid, cudaStream_t s) {
   using C = W4Cfg<BN>;
   auto kern = w4a16_gemm_kernel<T, BN>;
-  const size_t smem = static_cast<size_t>(C::kStages) * C::kStageBytes + 1024 + 512;
+  const size_t smem = static_cast<size_t>(C::kStages) * C::kStageBytes + C::kRawStages * C::kRawBytes + 1024 + 512;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
       return -3;
     attr_set = true;
   }
-  const cudaError_t err = launch_pdl(kern, grid, dim3(kW4Threads), smem, s, tx, p);
+  const cudaError_t err = launch_pdl(kern, grid, dim3(kW4Threads), smem, s, tx, tw, p);
   note_launch();
   return err == cudaSuccess ? 0 : -4;
 }
@@ -403,7 +410,7 @@ size_t w4a16_workspace_bytes(int m, int n, int k, int num_sms) {
 
 int launch_w4a16_gemm(const W4A16Args& a, cudaStream_t s) {
   if (a.m <= 0 || a.n <= 0) return 0;
-  if (a.k % 64 != 0 || a.group % 64 != 0 || a.k % a.group != 0 || a.ldx % 8 != 0) return -1;
+  if (a.k % 64 != 0 || a.group % 64 != 0 || a.k % a.group != 0 || a.ldx % 8 != 0 || (a.k / 2) % 16 != 0) return -1;
   if ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.qweight)) & 15) return -1;
   int bn = 16;
   while (bn < a.m && bn < 256) bn <<= 1;
@@ -433,17 +440,19 @@ int launch_w4a16_gemm(const W4A16Args& a, cudaStream_t s) {
     splits = std::min({16, std::max(1, num_sms / tiles), std::max(1, p.k_blocks / 4)});
     while (splits > 1 && static_cast<size_t>(splits) * a.m * a.n * sizeof(float) > a.workspace_bytes) --splits;
   }
-  p.kb_per_split = (p.k_blocks + splits - 1) / splits;
+  p.kb_per_split = ((p.k_blocks + splits - 1) / splits + 3) / 4 * 4;  // whole 128-byte column blocks per split
   splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
   p.splits = splits;
-  CUtensorMap tx;
+  CUtensorMap tx, tw;
   if (!make_tma_operand_map(&tx, a.x, a.m, a.k, a.ldx, 2, a.dt == kF16 ? 1 : 0, bn)) return -2;
+  // packed weights as bytes: [n, k/2], 128-byte x 128-row boxes
+  if (!make_tma_operand_map(&tw, a.qweight, a.n, a.k / 2, a.k / 2, 1, 2, kBM)) return -2;
   const dim3 grid(std::min(tiles, num_sms), splits);
   int rc = -1;
 #define MB200_W4_CASE(BNV)                                                             \
   case BNV:                                                                            \
-    rc = a.dt == kF16 ? launch_w4_cfg<__half, BNV>(tx, p, grid, s)                     \
-                      : launch_w4_cfg<__nv_bfloat16, BNV>(tx, p, grid, s);             \
+    rc = a.dt == kF16 ? launch_w4_cfg<__half, BNV>(tx, tw, p, grid, s)                     \
+                      : launch_w4_cfg<__nv_bfloat16, BNV>(tx, tw, p, grid, s);             \
     break;
   switch (bn) {
     MB200_W4_CASE(16)

@@ -210,3 +210,65 @@ def test_gguf_k_quants_known_blocks():
     assert len(blk6) == 210
     got6 = host_ext().gguf_dequantize(14, np.frombuffer(blk6, dtype=np.uint8), 1)
     np.testing.assert_allclose(got6, np.full(256, 0.125 * 3 * 8, dtype=np.float32))
+
+
+def test_convert_roundtrip_and_model_load(tmp_path):
+    """safetensors -> .mllm -> model: a tiny Qwen3 loaded from the .mllm file gives the logits of the same
+    weights loaded from safetensors (the loader path the server takes for ``*.mllm`` checkpoints)."""
+    from safetensors.torch import save_file
+
+    from mllm_b200.configs import ServerConfig
+    from mllm_b200.executor import ModelRunner
+    from mllm_b200.io.convert import main as convert_main
+    from mllm_b200.models.presets import get_preset, preset_to_config_json
+
+    import json
+
+    cfg = get_preset("qwen3-tiny")
+    sc = ServerConfig(model_path="preset:qwen3-tiny", dtype="float32", max_running_requests=2, max_total_tokens=256)
+    src = ModelRunner(sc, hf_config=cfg, device="cpu")
+    src.initialize()
+    hf_names = {}
+    for name, p in src.model.named_parameters():
+        hf_names[name] = p.detach().clone()
+    # un-fuse into HF names so both loaders exercise their stacking logic
+    sd = {}
+    for name, t in hf_names.items():
+        if ".qkv_proj." in name:
+            q = cfg.num_attention_heads * cfg.head_dim
+            kv = cfg.num_key_value_heads * cfg.head_dim
+            sd[name.replace("qkv_proj", "q_proj")] = t[:q].clone()
+            sd[name.replace("qkv_proj", "k_proj")] = t[q:q + kv].clone()
+            sd[name.replace("qkv_proj", "v_proj")] = t[q + kv:].clone()
+        elif ".gate_up_proj." in name:
+            from mllm_b200 import ops
+
+            v = t.reshape(-1, 2, ops.SWIGLU_BLOCK, t.shape[1]) if t.shape[0] % (2 * ops.SWIGLU_BLOCK) == 0 else None
+            g = v[:, 0].reshape(-1, t.shape[1]) if v is not None else t[: t.shape[0] // 2]
+            u = v[:, 1].reshape(-1, t.shape[1]) if v is not None else t[t.shape[0] // 2:]
+            sd[name.replace("gate_up_proj", "gate_proj")] = g.clone()
+            sd[name.replace("gate_up_proj", "up_proj")] = u.clone()
+        else:
+            sd[name] = t
+    st_dir, ml_dir = tmp_path / "st", tmp_path / "ml"
+    st_dir.mkdir()
+    ml_dir.mkdir()
+    save_file(sd, str(st_dir / "model.safetensors"))
+    for d in (st_dir, ml_dir):
+        (d / "config.json").write_text(json.dumps(preset_to_config_json("qwen3-tiny")))
+    convert_main(["--input", str(st_dir), "--output", str(ml_dir / "model.mllm"), "--model-name", "tiny"])
+    convert_main(["--input", str(ml_dir / "model.mllm"), "--output", str(tmp_path / "x"), "--list"])
+
+    def logits(path):
+        mr = ModelRunner(ServerConfig(model_path=str(path), dtype="float32", max_running_requests=2, max_total_tokens=256),
+                         device="cpu")
+        mr.initialize()
+        ids = torch.arange(5, 14)
+        slots = mr.req_to_token_pool.alloc(1)
+        loc = mr.token_to_kv_pool_allocator.alloc(9)
+        mr.req_to_token_pool.req_to_token[slots[0], :9] = loc.int()
+        lens = torch.tensor([9])
+        fb = mr.prepare_forward_batch_extend(ids, torch.tensor(slots), lens, lens, torch.zeros_like(lens), loc)
+        return mr.forward(fb).next_token_logits
+
+    torch.testing.assert_close(logits(ml_dir), logits(st_dir))
