@@ -276,6 +276,60 @@ int64_t w4a16_gemm(const Tensor& x, const Tensor& qweight, const Tensor& scales,
   return mb200::launch_w4a16_gemm(a, stream_of(x));
 }
 
+// ---- gated delta net ----
+void rmsnorm_gated(const Tensor& x, const Tensor& gate, const Tensor& w, Tensor& out, double eps) {
+  check_half(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && gate.is_contiguous() && gate.sizes() == x.sizes() && out.is_contiguous() &&
+                  out.sizes() == x.sizes() && w.numel() == x.size(1) && w.scalar_type() == x.scalar_type() &&
+                  gate.scalar_type() == x.scalar_type() && out.scalar_type() == x.scalar_type(),
+              "rmsnorm_gated: x, gate, out [R, W] and weight [W] of one 16-bit type");
+  c10::cuda::CUDAGuard g(x.device());
+  mb200::launch_rmsnorm_gated(x.data_ptr(), gate.data_ptr(), w.data_ptr(), out.data_ptr(), x.size(0), x.size(1),
+                              static_cast<float>(eps), dtype_of(x), stream_of(x));
+}
+
+static void check_ragged(const Tensor& slots, const Tensor& lens, const Tensor& has, const Tensor& q_start) {
+  for (const Tensor* t : {&slots, &lens, &has, &q_start})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kInt && t->is_contiguous() && t->numel() == slots.numel(),
+                "ragged metadata: int32 device vectors of one length");
+}
+
+void gdn_conv1d_silu(const Tensor& x, const Tensor& w, Tensor& conv_state, const Tensor& slots, const Tensor& lens,
+                     const Tensor& has, const Tensor& q_start, Tensor& out) {
+  check_half(x, "x");
+  check_ragged(slots, lens, has, q_start);
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && out.is_contiguous() && out.sizes() == x.sizes() && w.dim() == 2 &&
+                  w.is_contiguous() && w.size(0) == x.size(1) && conv_state.dim() == 3 && conv_state.is_contiguous() &&
+                  conv_state.size(1) == x.size(1) && conv_state.size(2) == w.size(1) - 1 &&
+                  w.scalar_type() == x.scalar_type() && conv_state.scalar_type() == x.scalar_type(),
+              "gdn_conv1d_silu: x [T, C], w [C, K], conv_state [slots, C, K-1]");
+  c10::cuda::CUDAGuard g(x.device());
+  const int rc = mb200::launch_gdn_conv1d_silu(x.data_ptr(), w.data_ptr(), conv_state.data_ptr(), slots.data_ptr<int>(),
+                                               lens.data_ptr<int>(), has.data_ptr<int>(), q_start.data_ptr<int>(),
+                                               out.data_ptr(), slots.numel(), x.size(0), x.size(1), w.size(1), dtype_of(x),
+                                               stream_of(x));
+  TORCH_CHECK(rc == 0, "gdn_conv1d_silu: unsupported kernel width");
+}
+
+void gdn_recurrent(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& g, const Tensor& beta, Tensor& state,
+                   const Tensor& slots, const Tensor& lens, const Tensor& has, const Tensor& q_start, Tensor& out) {
+  check_half(q, "q");
+  check_ragged(slots, lens, has, q_start);
+  TORCH_CHECK(q.dim() == 3 && q.is_contiguous() && k.is_contiguous() && v.is_contiguous() && k.sizes() == q.sizes() &&
+                  v.size(0) == q.size(0) && v.size(1) == q.size(1) && out.is_contiguous() && out.sizes() == v.sizes() &&
+                  g.scalar_type() == at::kFloat && beta.scalar_type() == at::kFloat && g.is_contiguous() && beta.is_contiguous() &&
+                  g.numel() == q.size(0) * q.size(1) && beta.numel() == g.numel() && state.scalar_type() == at::kFloat &&
+                  state.is_contiguous() && state.dim() == 4 && state.size(1) == q.size(1) && state.size(2) == q.size(2) &&
+                  state.size(3) == v.size(2),
+              "gdn_recurrent: q, k [T, H, Dk], v [T, H, Dv], g / beta fp32 [T, H], state fp32 [slots, H, Dk, Dv]");
+  c10::cuda::CUDAGuard gd(q.device());
+  const int rc = mb200::launch_gdn_recurrent(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr<float>(), beta.data_ptr<float>(),
+                                             state.data_ptr<float>(), slots.data_ptr<int>(), lens.data_ptr<int>(),
+                                             has.data_ptr<int>(), q_start.data_ptr<int>(), out.data_ptr(), slots.numel(),
+                                             q.size(1), q.size(2), v.size(2), dtype_of(q), stream_of(q));
+  TORCH_CHECK(rc == 0, "gdn_recurrent: head dims must be 128");
+}
+
 // ---- vision tower ----
 void vision_rope_split_pad(const Tensor& qkv, const Tensor& cos, const Tensor& sin, Tensor& q, Tensor& k, Tensor& v) {
   check_half(qkv, "qkv");
@@ -693,6 +747,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("w4a16_gemm", &w4a16_gemm);
   m.def("tp_rs_add_rmsnorm_ag", &tp_rs_add_rmsnorm_ag);
   m.def("tp_wait_flags", &tp_wait_flags);
+  m.def("rmsnorm_gated", &rmsnorm_gated);
+  m.def("gdn_conv1d_silu", &gdn_conv1d_silu);
+  m.def("gdn_recurrent", &gdn_recurrent);
   m.def("vision_rope_split_pad", &vision_rope_split_pad);
   m.def("vision_pos_embed_add", &vision_pos_embed_add);
   m.def("gelu_erf", &gelu_erf);

@@ -175,6 +175,18 @@ struct AttnArgs {
 int launch_attention(const AttnArgs& args, cudaStream_t s);
 int decode_num_splits(int batch, int hkv, int max_seq_len, int num_sms);
 
+// ----- gated delta net (hybrid models) -----------------------------------------------------------
+// Ragged sequences: request b owns rows q_start[b] .. q_start[b] + lens[b] of the token-major inputs and
+// row slots[b] of the state tensors; has_state[b] != 0 resumes from the stored state.
+int launch_gdn_conv1d_silu(const void* x, const void* w, void* conv_state, const int* slots, const int* lens,
+                           const int* has_state, const int* q_start, void* out, int batch, int max_tokens, int channels, int K,
+                           DType dt, cudaStream_t s);
+int launch_gdn_recurrent(const void* q, const void* k, const void* v, const float* g, const float* beta, float* state,
+                         const int* slots, const int* lens, const int* has_state, const int* q_start, void* out, int batch,
+                         int heads, int dk, int dv, DType dt, cudaStream_t s);
+void launch_rmsnorm_gated(const void* x, const void* gate, const void* w, void* out, int rows, int width, float eps, DType dt,
+                          cudaStream_t s);
+
 // ----- vision tower helpers ------------------------------------------------------------------
 // qkv [T, 3, H, D] (D <= 128, D % 8 == 0) -> q, k, v [T, H, 128] zero-padded; q and k get the 2-D rotary
 // embedding: out[i] = x[i] c[i] - x[i + D/2] s[i], out[i + D/2] = x[i + D/2] c[i] + x[i] s[i], cos/sin fp32 [T, D/2].

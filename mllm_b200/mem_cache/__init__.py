@@ -3,11 +3,11 @@ from .base_prefix_cache import (
     hash_bytes, hash_to_int64, hash_token_ids,
 )
 from .chunk_cache import ChunkCache
-from .memory_pool import KVPool, ReqToTokenPool, TokenToKVPoolAllocator
+from .memory_pool import GDNPool, KVPool, ReqToTokenPool, TokenToKVPoolAllocator
 from .radix_cache import RadixCache, TreeNode
 
 __all__ = [
     "BasePrefixCache", "EvictResult", "InsertResult", "MatchResult", "RadixKey",
-    "hash_bytes", "hash_to_int64", "hash_token_ids", "ChunkCache", "KVPool",
+    "hash_bytes", "hash_to_int64", "hash_token_ids", "ChunkCache", "KVPool", "GDNPool",
     "ReqToTokenPool", "TokenToKVPoolAllocator", "RadixCache", "TreeNode",
 ]

@@ -174,6 +174,33 @@ class TokenToKVPoolAllocator:
             self._released.append(np.concatenate(groups))
 
 
+class GDNPool:
+    """Per-request state of the gated-delta-net layers of a hybrid model: the fp32 recurrent matrix
+    ``[layers, slots, Hv, Dk, Dv]`` and the last ``K-1`` convolution inputs ``[layers, slots, C, K-1]``.
+    A request uses the row of its ``req_to_token`` slot, so no separate allocator is needed
+    (role of pymllm/mem_cache/memory_pool.py:479-631)."""
+
+    def __init__(self, num_layers: int, slots: int, num_v_heads: int, head_k_dim: int, head_v_dim: int, conv_dim: int,
+                 conv_kernel: int, device, conv_dtype: torch.dtype = torch.bfloat16) -> None:
+        self.num_layers, self.slots = num_layers, slots
+        self.recurrent = torch.zeros((num_layers, slots, num_v_heads, head_k_dim, head_v_dim), dtype=torch.float32, device=device)
+        self.conv = torch.zeros((num_layers, slots, conv_dim, conv_kernel - 1), dtype=conv_dtype, device=device)
+
+    def layer(self, idx: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        return self.recurrent[idx], self.conv[idx]
+
+    def reset(self, slot) -> None:
+        self.recurrent[:, slot] = 0
+        self.conv[:, slot] = 0
+
+    def copy(self, src: int, dst: int) -> None:
+        self.recurrent[:, dst] = self.recurrent[:, src]
+        self.conv[:, dst] = self.conv[:, src]
+
+    def bytes(self) -> int:
+        return self.recurrent.numel() * 4 + self.conv.numel() * self.conv.element_size()
+
+
 class ReqToTokenPool:
     """Request slot -> KV slot table (device) plus a host free list of request slots."""
 

@@ -41,6 +41,23 @@ PRESETS["qwen3-moe-tiny"] = dict(
     architectures=["Qwen3MoeForCausalLM"], model_type="qwen3_moe", num_experts=8, num_experts_per_tok=2,
     moe_intermediate_size=256, norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[],
 )
+def _hybrid(hidden, layers, heads, kv_heads, inter, head_dim, lin_k_heads, lin_v_heads, vocab=151936):
+    return dict(
+        architectures=["Qwen3_5ForCausalLM"], model_type="qwen3_5_text", vocab_size=vocab, hidden_size=hidden,
+        intermediate_size=inter, num_hidden_layers=layers, num_attention_heads=heads, num_key_value_heads=kv_heads,
+        head_dim=head_dim, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=32768, attention_bias=False,
+        hidden_act="silu", linear_conv_kernel_dim=4, linear_key_head_dim=128, linear_value_head_dim=128,
+        linear_num_key_heads=lin_k_heads, linear_num_value_heads=lin_v_heads, full_attention_interval=4,
+        layer_types=["full_attention" if (i + 1) % 4 == 0 else "linear_attention" for i in range(layers)],
+        rope_parameters=dict(rope_theta=1e7, partial_rotary_factor=0.25, rope_type="default", mrope_section=[11, 11, 10]),
+        torch_dtype="bfloat16", eos_token_id=151645,
+    )
+
+
+PRESETS["qwen3.5-2b"] = _hybrid(2048, 24, 8, 2, 6144, 256, 16, 16)
+PRESETS["qwen3.5-tiny"] = dict(_hybrid(256, 4, 2, 1, 512, 128, 1, 2, vocab=1024),
+                               rope_parameters=dict(rope_theta=1e4, partial_rotary_factor=0.25, rope_type="default",
+                                                    mrope_section=[6, 5, 5]))
 _VL_VISION = dict(
     depth=24, hidden_size=1024, num_heads=16, intermediate_size=4096, patch_size=16, temporal_patch_size=2,
     spatial_merge_size=2, in_channels=3, out_hidden_size=2048, num_position_embeddings=2304,

@@ -1,0 +1,261 @@
+"""Qwen3.5 hybrid decoder (Qwen3_5ForCausalLM): gated-delta-net layers interleaved with gated full
+attention (roles of pymllm/models/qwen3_5.py:71-1087; math checked against HF ``modeling_qwen3_5``).
+
+Per layer: ``x += mixer(norm(x)); x += mlp(norm(x))`` with zero-centred RMSNorm gains (``1 + w``, folded
+into the stored weight at load).  The mixer is :class:`GatedDeltaNet` or full attention with per-head
+q/k norm, partial rotary embedding on the first ``head_dim * partial_rotary_factor`` features (interleaved
+M-RoPE axes when 3-D positions are given), KV cache, and an output gate ``attn * sigmoid(gate)`` whose
+gate comes from the doubled q projection.
+
+Status of the device path: the GEMMs, norms, SwiGLU MLP, KV write, conv / recurrent-state kernels and
+(for head_dim 128) attention run on the sm_100a kernels; head_dim 256 attention (the published Qwen3.5
+shape) falls back to the PyTorch statement of attention, and the layers are not tensor-parallel yet.
+"""
+
+from __future__ import annotations
+
+import time
+from typing import Iterable, Optional, Tuple
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..engine.forward_batch import ForwardBatch
+from ..layers import MLP, GemmaRMSNorm, VocabParallelEmbedding
+from ..layers.gdn import GatedDeltaNet
+from ..mem_cache import GDNPool
+from ..ops import reference as ref
+from .qwen3 import LogitsProcessorOutput
+
+
+def _rope_params(config) -> dict:
+    rp = getattr(config, "rope_parameters", None) or getattr(config, "rope_scaling", None) or {}
+    return rp if isinstance(rp, dict) else vars(rp)
+
+
+class Qwen3_5Attention(nn.Module):
+    def __init__(self, config, layer_id: int, params_dtype=None) -> None:
+        super().__init__()
+        dt = params_dtype or torch.get_default_dtype()
+        self.layer_id = layer_id
+        self.num_heads, self.num_kv_heads = config.num_attention_heads, config.num_key_value_heads
+        self.head_dim = getattr(config, "head_dim", None) or config.hidden_size // config.num_attention_heads
+        H = config.hidden_size
+        rp = _rope_params(config)
+        self.theta = float(rp.get("rope_theta", getattr(config, "rope_theta", 1e4)))
+        self.rotary_dim = int(self.head_dim * float(rp.get("partial_rotary_factor", getattr(config, "partial_rotary_factor", 1.0))))
+        self.mrope_section = rp.get("mrope_section", [11, 11, 10])
+        eps = getattr(config, "rms_norm_eps", 1e-6)
+
+        def lin(o, i):
+            m = nn.Module()
+            m.weight = nn.Parameter(torch.empty(o, i, dtype=dt), requires_grad=False)
+            return m
+
+        self.q_proj = lin(self.num_heads * self.head_dim * 2, H)   # per head: [query(D) | gate(D)]
+        self.k_proj = lin(self.num_kv_heads * self.head_dim, H)
+        self.v_proj = lin(self.num_kv_heads * self.head_dim, H)
+        self.o_proj = lin(H, self.num_heads * self.head_dim)
+        self.q_norm = GemmaRMSNorm(self.head_dim, eps, dt)
+        self.k_norm = GemmaRMSNorm(self.head_dim, eps, dt)
+        self.scale = self.head_dim ** -0.5
+
+    def _cos_sin(self, fb: ForwardBatch):
+        half = self.rotary_dim // 2
+        inv = 1.0 / (self.theta ** (torch.arange(0, self.rotary_dim, 2, device=fb.positions.device, dtype=torch.float32) / self.rotary_dim))
+        if fb.mrope_positions is not None:
+            ang = fb.mrope_positions.float().unsqueeze(-1) * inv           # [3, T, half]
+            out = ang[0].clone()
+            for axis, offset in ((1, 1), (2, 2)):                           # interleaved t/h/w layout
+                n = min(self.mrope_section[axis] * 3, half)
+                idx = torch.arange(offset, n, 3, device=out.device)
+                out[:, idx] = ang[axis][:, idx]
+            ang = out
+        else:
+            ang = fb.positions.float().unsqueeze(-1) * inv
+        return ang.cos(), ang.sin()
+
+    def forward(self, x: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
+        T, D = x.shape[0], self.head_dim
+        qg = ops.linear(x, self.q_proj.weight).view(T, self.num_heads, 2 * D)
+        q, gate = qg[..., :D], qg[..., D:].reshape(T, self.num_heads * D)
+        k = ops.linear(x, self.k_proj.weight).view(T, self.num_kv_heads, D)
+        v = ops.linear(x, self.v_proj.weight).view(T, self.num_kv_heads, D)
+        q = self.q_norm(q.reshape(-1, D)).view(T, self.num_heads, D)
+        k = self.k_norm(k.reshape(-1, D)).view(T, self.num_kv_heads, D)
+        cos, sin = self._cos_sin(fb)
+        q = ref.apply_rope_neox(q.float(), cos, sin).to(x.dtype).contiguous()
+        k = ref.apply_rope_neox(k.float(), cos, sin).to(x.dtype).contiguous()
+        kc, vc = fb.token_to_kv_pool.get_kv_buffer(self.layer_id)
+        ops.kv_write(k.reshape(T, -1), v.reshape(T, -1), fb.out_cache_loc, kc, vc)
+        rtt = fb.req_to_token_pool.req_to_token
+        fast = D == 128
+        if fb.forward_mode.is_decode():
+            if fast:
+                o = ops.attention_decode(q, kc, vc, rtt, fb.req_pool_indices, fb.seq_lens, self.scale, max_seq_len=fb.max_seq_len)
+            else:
+                o = ref.attention_decode(q, kc, vc, rtt, fb.req_pool_indices, fb.seq_lens, self.scale)
+        else:
+            if fast:
+                o = ops.attention_prefill(q, kc, vc, rtt, fb.req_pool_indices, fb.seq_lens, fb.extend_prefix_lens,
+                                          fb.extend_start_loc, self.scale, max_q_len=fb.max_extend_len)
+            else:
+                o = ref.attention_prefill(q, kc, vc, rtt, fb.req_pool_indices, fb.seq_lens, fb.extend_prefix_lens,
+                                          fb.extend_start_loc, self.scale)
+        o = o.reshape(T, self.num_heads * D) * torch.sigmoid(gate.float()).to(x.dtype)
+        return ops.linear(o, self.o_proj.weight)
+
+
+class Qwen3_5DecoderLayer(nn.Module):
+    def __init__(self, config, layer_id: int, attn_index: int, gdn_index: int, quant_config=None, params_dtype=None) -> None:
+        super().__init__()
+        eps = getattr(config, "rms_norm_eps", 1e-6)
+        self.layer_type = config.layer_types[layer_id]
+        if self.layer_type == "linear_attention":
+            self.linear_attn = GatedDeltaNet(config, layer_id, gdn_index, params_dtype)
+        else:
+            self.self_attn = Qwen3_5Attention(config, attn_index, params_dtype)
+        self.mlp = MLP(config.hidden_size, config.intermediate_size, quant_config, f"model.layers.{layer_id}.mlp",
+                       params_dtype, reduce_results=True)
+        self.input_layernorm = GemmaRMSNorm(config.hidden_size, eps, params_dtype)
+        self.post_attention_layernorm = GemmaRMSNorm(config.hidden_size, eps, params_dtype)
+
+    def forward(self, hidden, residual, fb):
+        if residual is None:
+            residual = hidden
+            hidden = self.input_layernorm(hidden)
+        else:
+            hidden, residual = self.input_layernorm(hidden, residual)
+        hidden = self.linear_attn(hidden, fb) if self.layer_type == "linear_attention" else self.self_attn(hidden, fb)
+        hidden, residual = self.post_attention_layernorm(hidden, residual)
+        return self.mlp(hidden), residual
+
+
+class Qwen3_5Model(nn.Module):
+    def __init__(self, config, quant_config=None, params_dtype=None) -> None:
+        super().__init__()
+        self.embed_tokens = VocabParallelEmbedding(config.vocab_size, config.hidden_size, params_dtype, shard=False)
+        layers, a, g = [], 0, 0
+        for i in range(config.num_hidden_layers):
+            layers.append(Qwen3_5DecoderLayer(config, i, a, g, quant_config, params_dtype))
+            if config.layer_types[i] == "linear_attention":
+                g += 1
+            else:
+                a += 1
+        self.layers = nn.ModuleList(layers)
+        self.num_attn_layers, self.num_gdn_layers = a, g
+        self.norm = GemmaRMSNorm(config.hidden_size, getattr(config, "rms_norm_eps", 1e-6), params_dtype)
+
+    def forward(self, input_ids, fb, input_embeds=None):
+        hidden = self.embed_tokens(input_ids) if input_embeds is None else input_embeds
+        residual = None
+        for layer in self.layers:
+            hidden, residual = layer(hidden, residual, fb)
+        hidden, _ = self.norm(hidden, residual)
+        return hidden
+
+
+class Qwen3_5ForCausalLM(nn.Module):
+    """Text model.  ``kv_layers`` tells the runner to size the KV pool for the full-attention layers only;
+    the gated-delta-net state pool is created on first use, one row per request slot."""
+
+    def __init__(self, config, quant_config=None, params_dtype: Optional[torch.dtype] = None) -> None:
+        super().__init__()
+        config = getattr(config, "text_config", config)
+        if not getattr(config, "layer_types", None):
+            interval = getattr(config, "full_attention_interval", 4)
+            config.layer_types = ["full_attention" if (i + 1) % interval == 0 else "linear_attention"
+                                  for i in range(config.num_hidden_layers)]
+        self.config = config
+        self.model = Qwen3_5Model(config, quant_config, params_dtype)
+        self.tie = bool(getattr(config, "tie_word_embeddings", False))
+        if not self.tie:
+            self.lm_head = VocabParallelEmbedding(config.vocab_size, config.hidden_size, params_dtype, shard=False)
+        self.kv_layers = self.model.num_attn_layers
+        self._gdn_pool: Optional[GDNPool] = None
+
+    def gdn_pool(self, fb: ForwardBatch) -> GDNPool:
+        slots = fb.req_to_token_pool.req_to_token.shape[0]
+        if self._gdn_pool is None or self._gdn_pool.slots != slots:
+            c = self.config
+            w = self.model.embed_tokens.weight
+            conv_dim = 2 * c.linear_key_head_dim * c.linear_num_key_heads + c.linear_value_head_dim * c.linear_num_value_heads
+            self._gdn_pool = GDNPool(self.model.num_gdn_layers, slots, c.linear_num_value_heads, c.linear_key_head_dim,
+                                     c.linear_value_head_dim, conv_dim, c.linear_conv_kernel_dim, w.device, w.dtype)
+        return self._gdn_pool
+
+    @property
+    def lm_head_weight(self) -> torch.Tensor:
+        return self.model.embed_tokens.weight if self.tie else self.lm_head.weight
+
+    def forward(self, input_ids, positions, forward_batch: ForwardBatch, input_embeds=None) -> LogitsProcessorOutput:
+        fb = forward_batch
+        fb.extra["gdn_pool"] = self.gdn_pool(fb)
+        t0 = time.perf_counter()
+        hidden = self.model(input_ids, fb, input_embeds)
+        if fb.forward_mode.is_extend() and fb.extend_seq_lens is not None:
+            hidden = hidden.index_select(0, torch.cumsum(fb.extend_seq_lens, 0) - 1)
+        logits = ops.linear(hidden, self.lm_head_weight)
+        ms = (time.perf_counter() - t0) * 1e3
+        if fb.forward_mode.is_decode():
+            fb.llm_decode_ms = ms
+        else:
+            fb.llm_prefill_ms = ms
+        return LogitsProcessorOutput(next_token_logits=logits[:, : self.config.vocab_size])
+
+    # ------------------------------------------------------------------ loading
+    _OFFSET_NORMS = ("input_layernorm.weight", "post_attention_layernorm.weight", "q_norm.weight", "k_norm.weight")
+
+    def load_weights(self, weights: Iterable[Tuple[str, torch.Tensor]]) -> set:
+        params = dict(self.named_parameters())
+        loaded = set()
+        for name, t in weights:
+            for old, new in (("model.language_model.", "model."), ("language_model.model.", "model."), ("language_model.", "model.")):
+                if name.startswith(old):
+                    name = new + name[len(old):]
+                    break
+            if name.startswith(("visual.", "model.visual.", "mtp.")) or "rotary_emb.inv_freq" in name:
+                continue
+            if name.startswith("lm_head.") and self.tie:
+                continue
+            target = name
+            if ".mlp.gate_proj." in name or ".mlp.up_proj." in name:
+                is_gate = ".mlp.gate_proj." in name
+                target = name.replace(".mlp.gate_proj.", ".mlp.gate_up_proj.") if is_gate else \
+                    name.replace(".mlp.up_proj.", ".mlp.gate_up_proj.")
+                p = params.get(target)
+                if p is None:
+                    continue
+                p.weight_loader(p, t, 0 if is_gate else 1)
+                loaded.add(target + (":gate" if is_gate else ":up"))
+                continue
+            p = params.get(target)
+            if p is None:
+                continue
+            if name.endswith(self._OFFSET_NORMS) or name == "model.norm.weight":
+                p.data.copy_((t.float() + 1.0).to(p.dtype))          # zero-centred gain: store 1 + w
+            elif name.endswith("conv1d.weight"):
+                p.data.copy_(t.reshape(p.shape))                      # [C, 1, K] -> [C, K]
+            elif hasattr(p, "weight_loader"):
+                p.weight_loader(p, t)
+            else:
+                p.data.copy_(t.reshape(p.shape))
+            loaded.add(target)
+        # both halves of every fused gate/up weight must have arrived
+        halves = {n.rsplit(':', 1)[0] for n in loaded if n.endswith((':gate', ':up'))}
+        for h in halves:
+            if h + ':gate' in loaded and h + ':up' in loaded:
+                loaded.add(h)
+        return {n for n in loaded if not n.endswith((':gate', ':up'))}
+
+    def post_load(self) -> None:
+        for m in self.modules():
+            if isinstance(m, GatedDeltaNet):
+                m.fuse_small_projections()
+
+
+EntryClass = Qwen3_5ForCausalLM
+
+# The multimodal checkpoint layout is accepted for text serving: vision tensors are skipped at load.
+Qwen3_5ForConditionalGeneration = Qwen3_5ForCausalLM

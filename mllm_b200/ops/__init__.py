@@ -487,6 +487,56 @@ def gelu_erf(x: torch.Tensor) -> torch.Tensor:
 
 
 # --------------------------------------------------------------------------
+# gated delta net (linear attention of the hybrid models)
+# --------------------------------------------------------------------------
+def rmsnorm_gated(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    if use_kernels(x) and hasattr(ext(), "rmsnorm_gated") and x.shape[-1] % 8 == 0:
+        x2, g2 = _2d(x).contiguous(), _2d(gate).contiguous()
+        out = torch.empty_like(x2)
+        ext().rmsnorm_gated(x2, g2, weight, out, eps)
+        return out.view(x.shape)
+    return ref.rmsnorm_gated(x, gate, weight, eps)
+
+
+def causal_conv1d_silu(x, weight, conv_state, state_indices, seq_lens, has_state, q_start=None) -> torch.Tensor:
+    """Depth-wise causal conv (kernel K) + SiLU over the new tokens of every request, reading / updating
+    the per-request history rows of ``conv_state``.  ``seq_lens`` / ``has_state`` may be host lists (CPU
+    path) or device int32 tensors (GPU path, no host sync; ``q_start`` = first row of each request)."""
+    if use_kernels(x) and hasattr(ext(), "gdn_conv1d_silu"):
+        dev = x.device
+        lens = seq_lens if isinstance(seq_lens, torch.Tensor) else torch.tensor(list(seq_lens), dtype=torch.int32, device=dev)
+        has = has_state if isinstance(has_state, torch.Tensor) else torch.tensor([int(h) for h in has_state], dtype=torch.int32, device=dev)
+        if q_start is None:
+            q_start = torch.cumsum(lens, 0, dtype=torch.int32) - lens
+        out = torch.empty_like(x)
+        ext().gdn_conv1d_silu(x.contiguous(), weight.contiguous(), conv_state, state_indices.to(torch.int32), lens.to(torch.int32),
+                              has.to(torch.int32), q_start.to(torch.int32), out)
+        return out
+    lens = seq_lens.tolist() if isinstance(seq_lens, torch.Tensor) else seq_lens
+    has = has_state.tolist() if isinstance(has_state, torch.Tensor) else has_state
+    return ref.causal_conv1d_silu(x, weight, conv_state, state_indices, lens, has)
+
+
+def gated_delta_rule(q, k, v, g, beta, state, state_indices, seq_lens, has_state, q_start=None) -> torch.Tensor:
+    """Gated delta rule over ragged sequences with per-request recurrent state (read when ``has_state``,
+    always written back).  q, k [T, H, Dk], v [T, H, Dv], g / beta [T, H] fp32."""
+    if use_kernels(q) and hasattr(ext(), "gdn_recurrent") and q.shape[-1] == 128 and v.shape[-1] == 128:
+        dev = q.device
+        lens = seq_lens if isinstance(seq_lens, torch.Tensor) else torch.tensor(list(seq_lens), dtype=torch.int32, device=dev)
+        has = has_state if isinstance(has_state, torch.Tensor) else torch.tensor([int(h) for h in has_state], dtype=torch.int32, device=dev)
+        if q_start is None:
+            q_start = torch.cumsum(lens, 0, dtype=torch.int32) - lens
+        out = torch.empty_like(v)
+        ext().gdn_recurrent(q.contiguous(), k.contiguous(), v.contiguous(), g.float().contiguous(), beta.float().contiguous(),
+                            state, state_indices.to(torch.int32), lens.to(torch.int32), has.to(torch.int32),
+                            q_start.to(torch.int32), out)
+        return out
+    lens = seq_lens.tolist() if isinstance(seq_lens, torch.Tensor) else seq_lens
+    has = has_state.tolist() if isinstance(has_state, torch.Tensor) else has_state
+    return ref.gated_delta_rule(q, k, v, g, beta, state, state_indices, lens, has)
+
+
+# --------------------------------------------------------------------------
 # mixture of experts
 # --------------------------------------------------------------------------
 def moe_router_topk(hidden: torch.Tensor, gate_weight: torch.Tensor, top_k: int, renormalize: bool = True):

@@ -245,8 +245,9 @@ def qk_norm_rope_kv_write(
 
 
 def kv_write(k, v, loc, k_cache, v_cache) -> None:
-    k_cache[loc.long()] = k.to(k_cache.dtype)
-    v_cache[loc.long()] = v.to(v_cache.dtype)
+    """k, v: [T, Hkv * D] or [T, Hkv, D] rows written to the cache slots ``loc``."""
+    k_cache[loc.long()] = k.reshape(k.shape[0], *k_cache.shape[1:]).to(k_cache.dtype)
+    v_cache[loc.long()] = v.reshape(v.shape[0], *v_cache.shape[1:]).to(v_cache.dtype)
 
 
 # --------------------------------------------------------------------------
@@ -402,3 +403,65 @@ def moe_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: to
         y = linear(h, w2[e], out_dtype=torch.float32)
         out.index_add_(0, tok, y * topk_w[tok, slot].unsqueeze(-1).float())
     return out.to(x.dtype)
+
+
+# --------------------------------------------------------------------------
+# gated delta net (linear attention of the Qwen3.5 hybrid models)
+# --------------------------------------------------------------------------
+def rmsnorm_gated(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """``weight * round(rmsnorm(x)) * silu(gate)`` over the last dimension (norm before gate)."""
+    xf = _f32(x)
+    n = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
+    return (_f32(weight) * _f32(n) * F.silu(_f32(gate))).to(x.dtype)
+
+
+def causal_conv1d_silu(x: torch.Tensor, weight: torch.Tensor, conv_state: torch.Tensor, state_indices: torch.Tensor,
+                       seq_lens, has_state) -> torch.Tensor:
+    """Depth-wise causal convolution (kernel K) + SiLU over ragged sequences.
+
+    ``x`` [T, C] holds the new tokens of every request back to back (``seq_lens`` each); ``weight`` [C, K];
+    ``conv_state`` [slots, C, K-1] keeps the last K-1 inputs of each request (row ``state_indices[b]``),
+    read when ``has_state[b]`` (a continuation) and always written back."""
+    K = weight.shape[1]
+    out = torch.empty_like(x)
+    off = 0
+    for b, n in enumerate(list(seq_lens)):
+        n = int(n)
+        slot = int(state_indices[b])
+        hist = _f32(conv_state[slot]) if bool(has_state[b]) else torch.zeros_like(conv_state[slot], dtype=torch.float32)
+        seq = torch.cat([hist, _f32(x[off:off + n]).t()], dim=1)          # [C, K-1+n]
+        y = F.conv1d(seq.unsqueeze(0), _f32(weight).unsqueeze(1), None, groups=weight.shape[0]).squeeze(0)  # [C, n]
+        out[off:off + n] = F.silu(y).t().to(x.dtype)
+        conv_state[slot] = seq[:, -(K - 1):].to(conv_state.dtype)
+        off += n
+    return out
+
+
+def gated_delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor,
+                     state: torch.Tensor, state_indices: torch.Tensor, seq_lens, has_state) -> torch.Tensor:
+    """Recurrent gated delta rule, one token at a time (the definition the chunked forms must match).
+
+    q, k [T, H, Dk] (l2-normalised here, q scaled by Dk^-0.5), v [T, H, Dv], g (log decay) and beta [T, H];
+    ``state`` [slots, H, Dk, Dv] fp32 is read when ``has_state[b]`` and always written back:
+    ``S *= exp(g); S += k (x) ((v - S^T k) * beta); o = S^T q``."""
+    T, H, Dk = q.shape
+    qf = _f32(q)
+    kf = _f32(k)
+    qf = qf * torch.rsqrt((qf * qf).sum(-1, keepdim=True) + 1e-6) * Dk ** -0.5
+    kf = kf * torch.rsqrt((kf * kf).sum(-1, keepdim=True) + 1e-6)
+    vf, gf, bf = _f32(v), _f32(g), _f32(beta)
+    out = torch.empty(T, H, v.shape[-1], dtype=torch.float32, device=q.device)
+    off = 0
+    for b, n in enumerate(list(seq_lens)):
+        n = int(n)
+        slot = int(state_indices[b])
+        S = state[slot].float().clone() if bool(has_state[b]) else torch.zeros_like(state[slot], dtype=torch.float32)
+        for t in range(off, off + n):
+            S = S * gf[t].exp().view(H, 1, 1)
+            mem = (S * kf[t].unsqueeze(-1)).sum(-2)                        # [H, Dv]
+            delta = (vf[t] - mem) * bf[t].unsqueeze(-1)
+            S = S + kf[t].unsqueeze(-1) * delta.unsqueeze(-2)
+            out[t] = (S * qf[t].unsqueeze(-1)).sum(-2)
+        state[slot] = S.to(state.dtype)
+        off += n
+    return out.to(v.dtype)

@@ -1,0 +1,98 @@
+"""Qwen3.5 hybrid (gated delta net + gated attention) on CPU against HF transformers on a tiny config:
+prefill, a chunked continuation of the prefill, and decode steps (which exercise the recurrent and
+convolution state carried per request)."""
+import types
+
+import pytest
+import torch
+
+from mllm_b200.configs import ServerConfig
+from mllm_b200.executor import ModelRunner
+from mllm_b200.ops import reference as ref
+
+
+def test_gated_delta_rule_state_carry():
+    torch.manual_seed(0)
+    T, H, D = 7, 2, 8
+    q, k, v = torch.randn(T, H, D), torch.randn(T, H, D), torch.randn(T, H, D)
+    g, beta = -torch.rand(T, H), torch.rand(T, H)
+    st = torch.zeros(3, H, D, D)
+    idx = torch.tensor([1])
+    whole = ref.gated_delta_rule(q, k, v, g, beta, st, idx, [T], [False])
+    st2 = torch.zeros(3, H, D, D)
+    a = ref.gated_delta_rule(q[:4], k[:4], v[:4], g[:4], beta[:4], st2, idx, [4], [False])
+    b = ref.gated_delta_rule(q[4:], k[4:], v[4:], g[4:], beta[4:], st2, idx, [3], [True])
+    torch.testing.assert_close(torch.cat([a, b]), whole)
+    torch.testing.assert_close(st2[1], st[1])
+
+
+def test_causal_conv_state_carry():
+    torch.manual_seed(1)
+    T, C, K = 9, 6, 4
+    x, w = torch.randn(T, C), torch.randn(C, K)
+    st = torch.zeros(2, C, K - 1)
+    whole = ref.causal_conv1d_silu(x, w, st, torch.tensor([0]), [T], [False])
+    st2 = torch.zeros(2, C, K - 1)
+    a = ref.causal_conv1d_silu(x[:5], w, st2, torch.tensor([0]), [5], [False])
+    b = ref.causal_conv1d_silu(x[5:], w, st2, torch.tensor([0]), [4], [True])
+    torch.testing.assert_close(torch.cat([a, b]), whole)
+    want = torch.nn.functional.silu(torch.nn.functional.conv1d(
+        torch.nn.functional.pad(x.t().unsqueeze(0), (K - 1, 0)), w.unsqueeze(1), groups=C)).squeeze(0).t()
+    torch.testing.assert_close(whole, want)
+
+
+def test_matches_hf_qwen3_5():
+    tr = pytest.importorskip("transformers")
+    cfgd = dict(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=2,
+                num_key_value_heads=1, head_dim=32, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=256,
+                attention_bias=False, linear_conv_kernel_dim=4, linear_key_head_dim=16, linear_value_head_dim=16,
+                linear_num_key_heads=2, linear_num_value_heads=4, hidden_act="silu",
+                layer_types=["linear_attention", "linear_attention", "linear_attention", "full_attention"],
+                rope_parameters=dict(rope_theta=10000.0, partial_rotary_factor=0.25, rope_type="default", mrope_section=[2, 1, 1]))
+    try:
+        hf = tr.Qwen3_5ForCausalLM(tr.Qwen3_5TextConfig(**cfgd)).float().eval()
+    except Exception as e:  # pragma: no cover
+        pytest.skip(f"transformers Qwen3.5 unavailable: {e}")
+    with torch.no_grad():   # make the zero-centred norm gains and decay parameters non-trivial
+        for n, p in hf.named_parameters():
+            if n.endswith(("layernorm.weight", "q_norm.weight", "k_norm.weight", "model.norm.weight")):
+                p.copy_(torch.randn_like(p) * 0.1)
+            if n.endswith("linear_attn.norm.weight"):
+                p.copy_(1 + torch.randn_like(p) * 0.1)
+    ns = types.SimpleNamespace(architectures=["Qwen3_5ForCausalLM"], **cfgd)
+    mr = ModelRunner(ServerConfig(model_path="preset:x", dtype="float32", max_running_requests=2, max_total_tokens=256),
+                     hf_config=ns, device="cpu")
+    mr.initialize()
+    loaded = mr.model.load_weights(hf.state_dict().items())
+    assert len(loaded) == len(dict(mr.model.named_parameters())), set(dict(mr.model.named_parameters())) - loaded
+    for m in mr.model.modules():
+        if hasattr(m, "quant_method"):
+            m._gate_up_interleaved = False
+            m.quant_method.process_weights_after_loading(m)
+    mr.model.post_load()
+    torch.manual_seed(0)
+    ids = torch.randint(0, 320, (1, 12))
+    slots = mr.req_to_token_pool.alloc(1)
+    sl = torch.tensor(slots)
+    # prefill in two chunks (7 + 5 tokens): the second resumes from the stored conv / recurrent state
+    loc = mr.token_to_kv_pool_allocator.alloc(12)
+    mr.req_to_token_pool.req_to_token[slots[0], :12] = loc.int()
+    fb = mr.prepare_forward_batch_extend(ids[0, :7], sl, torch.tensor([7]), torch.tensor([7]), torch.tensor([0]), loc[:7])
+    mr.forward(fb)
+    fb = mr.prepare_forward_batch_extend(ids[0, 7:], sl, torch.tensor([12]), torch.tensor([5]), torch.tensor([7]), loc[7:])
+    got = mr.forward(fb).next_token_logits
+    with torch.no_grad():
+        want = hf(ids).logits[:, -1]
+    torch.testing.assert_close(got, want, atol=5e-4, rtol=5e-4)
+    cur, seq = 12, ids
+    for _ in range(2):
+        nxt = got.argmax(-1)
+        loc1 = mr.token_to_kv_pool_allocator.alloc(1)
+        mr.req_to_token_pool.req_to_token[slots[0], cur] = loc1.int()
+        cur += 1
+        fbd = mr.prepare_forward_batch_decode(nxt, sl, torch.tensor([cur]), loc1)
+        got = mr.forward(fbd).next_token_logits
+        seq = torch.cat([seq, nxt[:, None]], 1)
+        with torch.no_grad():
+            want = hf(seq).logits[:, -1]
+        torch.testing.assert_close(got, want, atol=5e-4, rtol=5e-4)
