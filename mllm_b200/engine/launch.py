@@ -85,6 +85,17 @@ class Engine:
             self.hf_config = load_hf_config(self.server_config.model_path)
         return int(getattr(text_config_of(self.hf_config), "vocab_size", 1024))
 
+    def _mm_config(self):
+        """Vision-token ids and patch geometry for the tokenizer's built-in image path (None: text model)."""
+        cfg = self.hf_config
+        vc = getattr(cfg, "vision_config", None)
+        if vc is None or getattr(cfg, "image_token_id", None) is None:
+            return None
+        return dict(image_token_id=int(cfg.image_token_id), vision_start_token_id=int(cfg.vision_start_token_id),
+                    vision_end_token_id=int(getattr(cfg, "vision_end_token_id", cfg.vision_start_token_id)),
+                    patch_size=int(vc.patch_size), merge_size=int(getattr(vc, "spatial_merge_size", 2)),
+                    temporal_patch_size=int(getattr(vc, "temporal_patch_size", 2)))
+
     def _launch_inproc(self) -> None:
         from ..orchestrator.detokenizer_process import DetokenizerWorker
         from ..orchestrator.scheduler_process import build_scheduler
@@ -93,7 +104,7 @@ class Engine:
         sc = self.server_config
         vocab = self._vocab_size()
         self.tokenizer_worker = TokenizerWorker(sc.tokenizer_path, sc.context_length, vocab, sc.tokenizer_mode,
-                                                sc.trust_remote_code)
+                                                sc.trust_remote_code, self._mm_config())
         self.detokenizer_worker = DetokenizerWorker(sc.tokenizer_path, vocab, sc.tokenizer_mode, sc.trust_remote_code)
         self.scheduler = build_scheduler(sc, self.hf_config, self.quant_method, self.kv_cache_dtype, self.device)
         tok = self.tokenizer_worker.tokenizer
@@ -175,7 +186,7 @@ class Engine:
         spawn(run_tokenizer_process, dict(tokenizer_path=sc.tokenizer_path, recv_addr=a_rr_tok, send_addr=a_tok_sched,
                                           context_length=sc.context_length, vocab_size=vocab,
                                           tokenizer_mode=sc.tokenizer_mode, trust_remote_code=sc.trust_remote_code,
-                                          log_level=sc.log_level))
+                                          log_level=sc.log_level, mm_config=self._mm_config()))
         world = sc.world_size
         port = _free_port() if world > 1 else None
         for rank in range(world):  # one scheduler + model runner per GPU; rank 0 owns the sockets

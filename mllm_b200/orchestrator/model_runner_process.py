@@ -131,6 +131,9 @@ class ModelRunnerProcess:
         req.req_pool_idx = slots[0]
         # never reuse the whole prompt: the last prompt token must be computed to get logits
         key = RadixKey(req.input_ids[: max(0, len(req.input_ids) - 1)], req.extra_key)
+        if req.mm_inputs and req.mm_inputs.get("pixel_values") is not None:
+            # image prompts are prefilled whole: the 3-D positions after an image depend on its grid
+            key = RadixKey([], req.extra_key)
         m = self.prefix_cache.match_prefix(key)
         req.prefix_len = req.cached_tokens = req.num_computed = m.prefix_len
         req.last_node = m.last_node
@@ -170,9 +173,15 @@ class ModelRunnerProcess:
         t_pre = torch.tensor(pre_lens, dtype=torch.int32).to(dev, non_blocking=True)
         t_pool = torch.tensor(pool_idx, dtype=torch.int32).to(dev, non_blocking=True)
         extra = self._mm_kwargs(items)
+        uses_mrope = bool(getattr(r.model, "uses_mrope", False))
+        if uses_mrope:  # position offsets already known for continued requests
+            extra["mrope_position_deltas"] = torch.tensor([q.mrope_delta for q, _ in items], dtype=torch.int64).to(dev)
         fb = r.prepare_forward_batch_extend(t_ids, t_pool, t_ext + t_pre, t_ext, t_pre, loc,
                                             extend_seq_lens_cpu=ext_lens, extend_prefix_lens_cpu=pre_lens, **extra)
         out = r.forward(fb)
+        if uses_mrope and fb.mrope_position_deltas is not None:
+            for (q, _), d in zip(items, fb.mrope_position_deltas.tolist()):
+                q.mrope_delta = int(d)
         self.stats["prefill_tokens"] += total
         produced = []
         for i, (req, n) in enumerate(items):

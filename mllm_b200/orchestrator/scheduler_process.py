@@ -143,6 +143,9 @@ class Scheduler:
                 if budget <= 0:
                     break
                 n = min(len(req.input_ids) - req.num_computed, budget)
+                if req.mm_inputs and req.mm_inputs.get("pixel_values") is not None and req.num_computed == 0:
+                    # the vision tower needs every image token of the prompt in one pass: no chunking
+                    n = len(req.input_ids)
                 if n > 0:
                     rows.append((req, n))
                     budget -= n

@@ -19,10 +19,13 @@ logger = logging.getLogger(__name__)
 
 class TokenizerWorker:
     def __init__(self, tokenizer_path, context_length: Optional[int] = None, vocab_size: int = 1024,
-                 tokenizer_mode: str = "auto", trust_remote_code: bool = False) -> None:
+                 tokenizer_mode: str = "auto", trust_remote_code: bool = False, mm_config: Optional[Dict[str, Any]] = None) -> None:
         self.tokenizer = get_tokenizer(tokenizer_path, vocab_size, tokenizer_mode, trust_remote_code)
         self.context_length = context_length
         self.processor = self._load_processor(tokenizer_path, trust_remote_code)
+        # ids and patch geometry of the model's vision tokens: lets images be served without a HF
+        # processor (random-init presets, checkpoints shipped without preprocessor_config.json)
+        self.mm_config = mm_config
 
     @staticmethod
     def _load_processor(path, trust_remote_code):
@@ -58,6 +61,29 @@ class TokenizerWorker:
 
         return Image.fromarray(np.asarray(item).astype("uint8")).convert("RGB")
 
+    def _builtin_image_inputs(self, images, text, ids):
+        """Built-in preprocessing: every image becomes ``<vision_start> <image_pad> * n <vision_end>`` in
+        front of the text tokens; pixels are patchified by :mod:`mllm_b200.utils.image_processor`."""
+        import numpy as np
+        import torch
+
+        from ..utils.image_processor import image_token_count, preprocess_image
+
+        mc = self.mm_config
+        text_ids = list(ids) if ids is not None else self.tokenizer.encode(text or "")
+        pix, grids, block, h = [], [], [], hashlib.sha256()
+        for item in (images if isinstance(images, list) else [images]):
+            arr = item if isinstance(item, (np.ndarray, torch.Tensor)) else np.asarray(self.load_image(item))
+            img = torch.as_tensor(np.asarray(arr)).to(torch.uint8)
+            h.update(img.numpy().tobytes())
+            pv, g = preprocess_image(img, mc["patch_size"], mc["merge_size"], mc["temporal_patch_size"])
+            pix.append(pv)
+            grids.append(g)
+            block += [mc["vision_start_token_id"]] + [mc["image_token_id"]] * image_token_count(g, mc["merge_size"]) + \
+                [mc["vision_end_token_id"]]
+        mm = {"pixel_values": torch.cat(pix), "image_grid_thw": torch.cat(grids), "image_hash": h.hexdigest()[:16]}
+        return block + text_ids, mm
+
     def tokenize(self, req: Dict[str, Any]) -> TokenizedGenerateReqInput:
         text = req.get("text")
         ids = req.get("input_ids")
@@ -72,6 +98,8 @@ class TokenizerWorker:
                 h.update(im.tobytes())
             mm_inputs = {"pixel_values": out.get("pixel_values"), "image_grid_thw": out.get("image_grid_thw"),
                          "image_hash": h.hexdigest()[:16]}
+        elif images is not None and self.mm_config is not None:
+            ids, mm_inputs = self._builtin_image_inputs(images, text, ids)
         elif ids is None:
             ids = self.tokenizer.encode(text or "")
         ids = list(ids)
@@ -85,13 +113,14 @@ class TokenizerWorker:
 
 def run_tokenizer_process(tokenizer_path, recv_addr: str, send_addr: str, pipe_writer=None,
                           context_length: Optional[int] = None, vocab_size: int = 1024, tokenizer_mode: str = "auto",
-                          trust_remote_code: bool = False, log_level: str = "info") -> None:
+                          trust_remote_code: bool = False, log_level: str = "info",
+                          mm_config: Optional[Dict[str, Any]] = None) -> None:
     import zmq
 
     from .ipc_utils import make_socket, setup_subprocess_logging
 
     setup_subprocess_logging(log_level)
-    worker = TokenizerWorker(tokenizer_path, context_length, vocab_size, tokenizer_mode, trust_remote_code)
+    worker = TokenizerWorker(tokenizer_path, context_length, vocab_size, tokenizer_mode, trust_remote_code, mm_config)
     ctx = zmq.Context()
     recv = make_socket(ctx, zmq.PULL, recv_addr, bind=False)
     send = make_socket(ctx, zmq.PUSH, send_addr, bind=True)

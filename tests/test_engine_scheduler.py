@@ -161,3 +161,52 @@ def test_seeded_sampling_is_reproducible():
         assert pen["meta_info"]["completion_tokens"] == 6
     finally:
         eng.shutdown()
+
+
+def test_image_request_through_the_engine_on_cpu():
+    """An image request served end to end without a HF processor: built-in patchify, vision tokens in
+    the prompt, vision tower + deepstack in the prefill, decode positions shifted by the image's
+    position delta; the answer equals driving the model runner by hand with the same inputs."""
+    import numpy as np
+    import torch
+
+    from mllm_b200.configs import ServerConfig
+    from mllm_b200.engine.launch import Engine
+
+    cfg = ServerConfig(model_path="preset:qwen3-vl-tiny", dtype="float32", max_running_requests=2, max_total_tokens=1024,
+                       context_length=512, log_level="warning", chunked_prefill_size=16)
+    eng = Engine(cfg, mode="inproc", device="cpu").launch()
+    try:
+        img = np.random.default_rng(0).integers(0, 256, (64, 96, 3), dtype=np.uint8)
+        out = eng.generate("describe", {"max_new_tokens": 4, "temperature": 0.0}, image_data=img)
+        assert len(out["output_ids"]) == 4
+        runner = eng.scheduler.mrp.runner
+        tok = eng.tokenizer_worker.tokenize({"rid": "x", "text": "describe", "image_data": img})
+        n_img = sum(1 for t in tok.input_ids if t == runner.hf_config.image_token_id)
+        g = tok.mm_inputs["image_grid_thw"][0].tolist()      # the small image is scaled up to the pixel floor
+        assert n_img == g[0] * (g[1] // 2) * (g[2] // 2) and tok.mm_inputs["pixel_values"].shape[0] == n_img * 4
+        # the same request by hand
+        ids = torch.tensor(tok.input_ids)
+        L = len(ids)
+        slots = runner.req_to_token_pool.alloc(1)
+        sl = torch.tensor(slots)
+        loc = runner.token_to_kv_pool_allocator.alloc(L)
+        runner.req_to_token_pool.req_to_token[slots[0], :L] = loc.int()
+        lens = torch.tensor([L])
+        fb = runner.prepare_forward_batch_extend(ids, sl, lens, lens, torch.zeros_like(lens), loc,
+                                                 pixel_values=tok.mm_inputs["pixel_values"],
+                                                 image_grid_thw=tok.mm_inputs["image_grid_thw"])
+        logits = runner.forward(fb).next_token_logits
+        want = [int(logits.argmax(-1))]
+        delta = fb.mrope_position_deltas
+        cur = L
+        for _ in range(3):
+            loc1 = runner.token_to_kv_pool_allocator.alloc(1)
+            runner.req_to_token_pool.req_to_token[slots[0], cur] = loc1.int()
+            cur += 1
+            pos = (torch.tensor([cur - 1]) + delta).unsqueeze(0).expand(3, -1).contiguous()
+            fbd = runner.prepare_forward_batch_decode(torch.tensor([want[-1]]), sl, torch.tensor([cur]), loc1, mrope_positions=pos)
+            want.append(int(runner.forward(fbd).next_token_logits.argmax(-1)))
+        assert out["output_ids"] == want
+    finally:
+        eng.shutdown()
