@@ -7,6 +7,7 @@
 
 #include <memory>
 
+#include "host/cpu_oracle.h"
 #include "host/mllm_file.h"
 #include "host/page_allocator.h"
 #include "host/radix_tree.h"
@@ -122,6 +123,34 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           return out;
         },
         py::arg("dtype"), py::arg("raw"), py::arg("threads") = 0);
+
+  m.def("qwen3_cpu_generate",
+        [](const std::string& path, py::dict cfg, std::vector<int64_t> prompt, int new_tokens, int threads) {
+          OracleConfig c;
+          c.vocab = cfg["vocab_size"].cast<int>();
+          c.hidden = cfg["hidden_size"].cast<int>();
+          c.inter = cfg["intermediate_size"].cast<int>();
+          c.layers = cfg["num_hidden_layers"].cast<int>();
+          c.heads = cfg["num_attention_heads"].cast<int>();
+          c.kv_heads = cfg["num_key_value_heads"].cast<int>();
+          c.head_dim = cfg["head_dim"].cast<int>();
+          c.eps = cfg["rms_norm_eps"].cast<float>();
+          c.theta = cfg["rope_theta"].cast<float>();
+          c.tie = cfg["tie_word_embeddings"].cast<bool>();
+          OracleResult r;
+          {
+            py::gil_scoped_release rel;
+            r = qwen3_cpu_generate(path, c, prompt, new_tokens, threads);
+          }
+          py::dict out;
+          out["tokens"] = r.tokens;
+          out["prefill_logits"] = py::array_t<float>(r.prefill_logits.size(), r.prefill_logits.data());
+          out["last_logits"] = py::array_t<float>(r.last_logits.size(), r.last_logits.data());
+          out["prefill_seconds"] = r.prefill_seconds;
+          out["decode_seconds"] = r.decode_seconds;
+          return out;
+        },
+        py::arg("mllm_path"), py::arg("config"), py::arg("prompt"), py::arg("new_tokens"), py::arg("threads") = 0);
 
   m.def("write_mllm_v2",
         [](const std::string& path, const std::string& model_name, py::list entries) {

@@ -272,3 +272,20 @@ def test_convert_roundtrip_and_model_load(tmp_path):
         return mr.forward(fb).next_token_logits
 
     torch.testing.assert_close(logits(ml_dir), logits(st_dir))
+
+
+def test_cpp_cpu_oracle_matches_pytorch_oracle(tmp_path):
+    """The stand-alone C++ Qwen3 (no PyTorch, weights from a .mllm file) and the engine's model on the
+    PyTorch statements of the ops produce the same greedy tokens and logits."""
+    from mllm_b200.benchmarks.cpu_oracle import run_cpp, run_torch, seeded_weights
+    from mllm_b200.models.presets import get_preset
+
+    cfg = get_preset("qwen3-tiny", tie_word_embeddings=False)
+    path = str(tmp_path / "model.mllm")
+    write_mllm(path, seeded_weights(cfg, seed=1, std=0.05), model_name="tiny")
+    prompt = torch.randint(0, cfg.vocab_size, (24,), generator=torch.Generator().manual_seed(1)).tolist()
+    a = run_cpp(path, cfg, prompt, 6, threads=2)
+    b = run_torch(path, cfg, prompt, 6)
+    assert list(a["tokens"]) == b["tokens"]
+    torch.testing.assert_close(torch.from_numpy(a["prefill_logits"]), b["prefill_logits"], atol=2e-4, rtol=2e-4)
+    torch.testing.assert_close(torch.from_numpy(a["last_logits"]), b["last_logits"], atol=2e-4, rtol=2e-4)
