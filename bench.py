@@ -1,6 +1,11 @@
 """Flagship benchmark: Qwen3-8B-shaped decoder, bf16, one batch of `--batch-size` requests with
 input_len 2048 and output_len 128 (prefill + 127 greedy decode steps) — the reference's
-``bench_one_batch`` workload — on N GPUs of one node with tensor parallelism TP=N.
+``bench_one_batch`` workload — on N GPUs of one node.  With N > 1 the default is data parallelism
+(``--parallelism dp``): one full replica of the model per GPU, each serving its own batch of
+`--batch-size` requests, so the global batch is N x batch and per-GPU work is fixed (weak scaling);
+this is the layout that serves the most tokens per second for a model that fits one GPU.
+``--parallelism tp`` shards the one batch over the N GPUs instead (tensor parallelism with the
+fused NVLink kernels; strong scaling, lower latency per batch).
 
     python bench.py --gpus 1 --steps 5 --warmup 3
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
@@ -45,6 +50,12 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--input-len", type=int, default=2048)
     ap.add_argument("--output-len", type=int, default=128)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--parallelism", choices=["dp", "tp"], default="dp",
+                    help="N > 1: dp = one replica and one batch per GPU (weak scaling), tp = one batch sharded over N GPUs")
+    ap.add_argument("--device", choices=["cuda", "cpu"], default="cuda",
+                    help="cpu runs the same control flow on the host reference ops (flow tests; not a measurement)")
+    ap.add_argument("--watchdog-s", type=float, default=1500.0,
+                    help="give up (stack dump, error line, exit 3) when the whole run takes longer than this")
     return ap.parse_args()
 
 
@@ -115,6 +126,50 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------------
 # our implementation
 # --------------------------------------------------------------------------------------------
+class _HostEvent:
+    """Stand-in for a CUDA event when the flow runs on the host."""
+
+    def __init__(self, enable_timing: bool = True) -> None:
+        self.t = 0.0
+
+    def record(self) -> None:
+        self.t = time.perf_counter()
+
+    def elapsed_time(self, other: "_HostEvent") -> float:
+        return (other.t - self.t) * 1e3
+
+
+class Watchdog:
+    """Bounds the whole run: past the deadline every thread's Python stack goes to stderr, rank 0
+    prints a JSON line with an ``error`` field, and the process leaves with status 3 even if a CUDA
+    or collective call never returns."""
+
+    def __init__(self, seconds: float, rank: int, gpus: int) -> None:
+        self.t0 = time.perf_counter()
+        self.phase = "start"
+        self.rank = rank
+        self.gpus = gpus
+        self.done = threading.Event()
+        if seconds > 0:
+            threading.Thread(target=self._run, args=(seconds,), daemon=True).start()
+
+    def log(self, phase: str) -> None:
+        self.phase = phase
+        print(f"[bench rank {self.rank} +{time.perf_counter() - self.t0:7.1f}s] {phase}", file=sys.stderr, flush=True)
+
+    def _run(self, seconds: float) -> None:
+        if self.done.wait(seconds):
+            return
+        import faulthandler
+
+        print(f"[bench rank {self.rank}] no result after {seconds:.0f} s, last phase: {self.phase}", file=sys.stderr, flush=True)
+        faulthandler.dump_traceback(file=sys.stderr, all_threads=True)
+        if self.rank == 0:
+            print(json.dumps({"metric": METRIC, "value": None, "n_gpus": self.gpus, "impl": "ours",
+                              "error": f"run exceeded {seconds:.0f} s in phase '{self.phase}'"}), flush=True)
+        os._exit(3)
+
+
 def run_ours(a: argparse.Namespace) -> dict:
     import torch
     import torch.distributed as dist
@@ -122,36 +177,62 @@ def run_ours(a: argparse.Namespace) -> dict:
     from mllm_b200 import ops
     from mllm_b200.bench_one_batch import BenchRunner, make_synthetic_input_ids
     from mllm_b200.configs import GlobalConfig
-    from mllm_b200.parallel import state as pstate
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if world != a.gpus:
         raise SystemExit(f"--gpus {a.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {a.gpus}")
-    torch.cuda.set_device(local_rank)
+    wd = Watchdog(a.watchdog_s, rank, a.gpus)
+    on_gpu = a.device == "cuda"
+    if on_gpu:
+        torch.cuda.set_device(local_rank)
+    Event = torch.cuda.Event if on_gpu else _HostEvent
+
+    def sync() -> None:
+        if on_gpu:
+            torch.cuda.synchronize()
+    use_tp = world > 1 and a.parallelism == "tp"
+    replicas = 1 if (use_tp or world == 1) else world
+    if world > 1:
+        # host-side group (gloo) for barriers and for reducing the timings; NCCL is brought up
+        # only by the tensor-parallel layout, which moves activations between the GPUs
+        import datetime
+
+        dist.init_process_group(backend="cpu:gloo,cuda:nccl" if on_gpu else "gloo", timeout=datetime.timedelta(seconds=600))
+    wd.log(f"process group ready (world {world}, {'tp' if use_tp else 'dp'})")
 
     GlobalConfig.reset()
     cfg = GlobalConfig.get_instance()
     sc = cfg.server
     sc.model_path = f"preset:{a.model}"
     sc.dtype = "bfloat16"
-    sc.tp_size = a.gpus
+    sc.tp_size = a.gpus if use_tp else 1
+    sc.dp_size = replicas
     sc.max_running_requests = a.batch_size
     sc.max_total_tokens = a.batch_size * (a.input_len + a.output_len) + 4096
     sc.context_length = a.input_len + a.output_len + 64
-    br = BenchRunner.create(cfg)
+    br = BenchRunner.create(cfg, device=None if on_gpu else "cpu")
+    wd.log("model runner ready")
     dev = br.device
     bs, L, out_len = a.batch_size, a.input_len, a.output_len
-    tokens_per_step = bs * (L + out_len)
+    tokens_per_step = replicas * bs * (L + out_len)   # whole job: every replica serves its own batch
 
-    ids_pinned = make_synthetic_input_ids(batch_size=bs, input_len=L, vocab_size=br.runner.vocab_size, seed=42, pin=True)
+    ids_pinned = make_synthetic_input_ids(batch_size=bs, input_len=L, vocab_size=br.runner.vocab_size,
+                                          seed=42 + (rank if replicas > 1 else 0), pin=True)
     ids_dev = ids_pinned.to(dev)
 
+    def reduce_host(v: float, op) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64)
+        dist.all_reduce(t, op=op)
+        return float(t.item())
+
     def barrier() -> None:
+        sync()
         if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
+            reduce_host(0.0, dist.ReduceOp.SUM)
 
     def one_pass(ids, readback: bool):
         br.clear()
@@ -163,18 +244,19 @@ def run_ours(a: argparse.Namespace) -> dict:
                 host.append(nxt.cpu())
         return nxt, host
 
-    for _ in range(max(a.warmup, 3)):
+    for i in range(max(a.warmup, 3)):
         one_pass(ids_dev, False)
+        sync()
+        wd.log(f"warm-up {i + 1} done")
     barrier()
 
     # ---- device-timed region --------------------------------------------------------------
     sampler = ClockSampler(local_rank)
-    if rank == 0:
+    if rank == 0 and on_gpu:
         sampler.start()
     graphs = br.runner.cuda_graph_runner
     l0 = ops.launch_count() + (graphs.replayed_kernels if graphs else 0)
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * a.steps + 1)]
-    pre_ev = []
+    ev = [Event(enable_timing=True) for _ in range(2 * a.steps + 1)]
     barrier()
     ev[0].record()
     for s in range(a.steps):
@@ -189,19 +271,17 @@ def run_ours(a: argparse.Namespace) -> dict:
     prefill_ms = [ev[2 * s].elapsed_time(ev[2 * s + 1]) for s in range(a.steps)]
     decode_ms = [ev[2 * s + 1].elapsed_time(ev[2 * s + 2]) for s in range(a.steps)]
     launches = ops.launch_count() + (graphs.replayed_kernels if graphs else 0) - l0
-    clocks = sampler.stop() if rank == 0 else None
-    ops.check_status(dev.index)
+    sync()
+    clocks = sampler.stop() if rank == 0 and on_gpu else None
+    if on_gpu:
+        ops.check_status(dev.index)
+    wd.log("timed region done")
 
-    def max_over_ranks(v: float) -> float:
-        if world == 1:
-            return v
-        t = torch.tensor([v], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    total_ms = max_over_ranks(total_ms)
-    prefill_med = max_over_ranks(statistics.median(prefill_ms))
-    decode_med = max_over_ranks(statistics.median(decode_ms))
+    MAX, SUM = (dist.ReduceOp.MAX, dist.ReduceOp.SUM) if world > 1 else (None, None)
+    total_ms = reduce_host(total_ms, MAX)
+    prefill_med = reduce_host(statistics.median(prefill_ms), MAX)
+    decode_med = reduce_host(statistics.median(decode_ms), MAX)
+    launches_all = int(reduce_host(float(launches), SUM))
     ms_per_step = total_ms / a.steps
 
     # ---- end-to-end through the public API: pinned host ids in, sampled ids out every step --------
@@ -213,31 +293,36 @@ def run_ours(a: argparse.Namespace) -> dict:
         for _ in range(a.steps):
             one_pass(ids_pinned, True)
         barrier()
-        e2e_s = max_over_ranks(time.perf_counter() - t0)
+        e2e_s = reduce_host(time.perf_counter() - t0, MAX)
         e2e = {
             "value": tokens_per_step * a.steps / e2e_s, "unit": "tokens/s",
-            "h2d_bytes_per_step": int(ids_pinned.numel() * ids_pinned.element_size()),
-            "d2h_bytes_per_step": int(out_len * bs * 8),
+            "h2d_bytes_per_step": int(replicas * ids_pinned.numel() * ids_pinned.element_size()),
+            "d2h_bytes_per_step": int(replicas * out_len * bs * 8),
             "ms_per_step": e2e_s * 1e3 / a.steps,
             "api": "mllm_b200.bench_one_batch.BenchRunner.extend/decode",
         }
+        wd.log("end-to-end region done")
 
+    layout = f"tp{a.gpus}" if use_tp else f"dp{a.gpus}"
     result = {
         "metric": METRIC, "value": tokens_per_step / (ms_per_step / 1e3), "unit": "tokens/s", "n_gpus": a.gpus,
         "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded random ids, random-init weights)",
-        "impl": "ours",
-        "config": {"model": a.model, "global_batch": bs, "seq_len": L, "output_len": out_len,
-                   "parallelism": f"tp{a.gpus}", "cuda_graph_decode": graphs is not None,
-                   "l2_policy": "inputs larger than L2: every step streams the full weight set (>= 16 GB at TP=1) and the KV pool"},
-        "prefill_tokens_per_s": bs * L / (prefill_med / 1e3),
-        "decode_tokens_per_s": bs * (out_len - 1) / (decode_med / 1e3),
+        "scaling": "strong" if use_tp else "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic (seeded random ids, random-init weights)",
+        "impl": "ours", **({} if on_gpu else {"device": "cpu", "note": "host flow run: not a measurement"}),
+        "config": {"model": a.model, "global_batch": replicas * bs, "per_gpu_batch": bs if not use_tp else None,
+                   "seq_len": L, "output_len": out_len,
+                   "parallelism": layout, "cuda_graph_decode": graphs is not None,
+                   "l2_policy": "inputs larger than L2: every step streams the full weight set (>= 16 GB per replica) and the KV pool"},
+        "prefill_tokens_per_s": replicas * bs * L / (prefill_med / 1e3),
+        "decode_tokens_per_s": replicas * bs * (out_len - 1) / (decode_med / 1e3),
         "prefill_ms": prefill_med, "decode_ms_per_token": decode_med / (out_len - 1),
-        "gpu_launches": int(launches), "clocks": clocks, "e2e": e2e,
+        "gpu_launches": launches_all, "gpu_launches_per_rank": int(launches), "clocks": clocks, "e2e": e2e,
     }
     if world > 1:
-        dist.barrier()
+        barrier()
         dist.destroy_process_group()
+    wd.done.set()
     return result if rank == 0 else {}
 
 

@@ -115,6 +115,7 @@ def main(argv=None) -> None:
     a = ap.parse_args(argv)
     cfg = get_preset(a.preset)
     work = a.workdir or tempfile.mkdtemp(prefix="mllm_b200_oracle_")
+    os.makedirs(work, exist_ok=True)
     path = os.path.join(work, "model.mllm")
     if not os.path.exists(path):
         write_mllm(path, seeded_weights(cfg, a.seed), model_name=a.preset)

@@ -68,7 +68,7 @@ __global__ void tp_reduce_add_rmsnorm_kernel(PeerPtrs peers, uint32_t* __restric
   // 2) wait for every rank's signal; the expected count advances by one per call
   const uint32_t expect = local_seq[row] + 1u;
   if (threadIdx.x < tp) {
-    if (!wait_flag_ge(peers.flags[rank] + row * kMaxTp + threadIdx.x, expect)) {
+    if (!wait_flag_ge(peers.flags[rank] + row * kMaxTp + threadIdx.x, expect, status)) {
       wait_ok = 0;
       if (status != nullptr) atomicExch(status, kStatusPeerTimeout);
     }
@@ -173,7 +173,7 @@ __global__ void tp_rs_add_rmsnorm_ag_kernel(const T* __restrict__ inbox, int64_t
   if (threadIdx.x == 0) wait_ok = 1;
   __syncthreads();
   if (threadIdx.x < tp) {
-    if (!wait_flag_ge(tile_flags + tile * kMaxTp + threadIdx.x, epoch)) {
+    if (!wait_flag_ge(tile_flags + tile * kMaxTp + threadIdx.x, epoch, status)) {
       wait_ok = 0;
       if (status != nullptr) atomicExch(status, kStatusPeerTimeout);
     }
@@ -265,7 +265,7 @@ __global__ void tp_rs_add_rmsnorm_ag_kernel(const T* __restrict__ inbox, int64_t
 __global__ void tp_wait_flags_kernel(const uint32_t* __restrict__ flags, int n, uint32_t epoch, int* status) {
   pdl_wait();
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-    if (!wait_flag_ge(flags + i, epoch)) {
+    if (!wait_flag_ge(flags + i, epoch, status)) {
       if (status != nullptr) atomicExch(status, kStatusPeerTimeout);
       return;
     }

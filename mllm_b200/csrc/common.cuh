@@ -290,11 +290,17 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 __device__ __forceinline__ void red_add_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-// Bounded spin until *p >= want. False on timeout.
-__device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t want) {
+// Bounded spin until *p >= want. False on timeout.  When `status` is given the wait also gives up
+// as soon as that word is non-zero: once one wait of the process has run out (a peer is gone or
+// far behind) the later ones return after a few hundred polls instead of spending their full
+// bound each, so the host reaches its status check quickly.
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t want, const int* status = nullptr) {
   for (uint32_t i = 0; i < kMaxPolls; ++i) {
     if (ld_acquire_sys(p) >= want) return true;
-    if (i > 64) __nanosleep(64);
+    if (i > 64) {
+      __nanosleep(64);
+      if (status != nullptr && (i & 255u) == 128u && *reinterpret_cast<const volatile int*>(status) != 0) return false;
+    }
   }
   return false;
 }

@@ -233,7 +233,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
       if constexpr (!SWAP) {
         if (p.gate_flags != nullptr) {
           // rows of this tile are written by peers (generic proxy); the TMA engine reads them
-          if (!wait_flag_ge(p.gate_flags + tr, p.gate_epoch)) {
+          if (!wait_flag_ge(p.gate_flags + tr, p.gate_epoch, p.status)) {
             ok = false;
             if (p.status != nullptr) atomicExch(p.status, kStatusPeerTimeout);
             break;

@@ -161,7 +161,17 @@ class ModelRunner:
         self._init_tp_comm()
         self._configure_kv_cache_dtype()
         self.init_memory_pool()
+        # the warm-up runs before graph capture use kernels that wait on peer flags with a bound of
+        # a few seconds: the ranks enter them together, and leave initialisation together
+        self._tp_rendezvous()
         self.init_cuda_graphs()
+        self._tp_rendezvous()
+
+    def _tp_rendezvous(self) -> None:
+        if pstate.get_tensor_model_parallel_world_size() > 1:
+            if self.device.type == "cuda":
+                torch.cuda.synchronize(self.device)
+            pstate.get_tp_group().barrier()
 
     def _init_tp_comm(self) -> None:
         """Peer-mapped buffers for the fused tensor-parallel kernels (``comm_backend == "fused"``)."""
@@ -172,8 +182,39 @@ class ModelRunner:
             rows = max(256, min(1024, self.server_config.max_running_requests or 1))
             prefill_rows = int(self.server_config.chunked_prefill_size or 0) or 16384
             prefill_rows = max(prefill_rows, int(getattr(self.server_config, "max_prefill_tokens", 0) or 0))
-            set_tp_comm(TPComm.create(self.hidden_size, self.dtype, self.device, max_rows=256 if rows <= 256 else rows,
-                                      prefill_rows=min(prefill_rows, 65536)))
+            comm = TPComm.create(self.hidden_size, self.dtype, self.device, max_rows=256 if rows <= 256 else rows,
+                                 prefill_rows=min(prefill_rows, 65536))
+            set_tp_comm(comm)
+            if comm is not None and not self._tp_comm_self_test(comm):
+                logger.warning("fused tensor-parallel kernels failed their start-up check on this system; "
+                               "tensor-parallel layers use NCCL collectives")
+                set_tp_comm(None)
+
+    def _tp_comm_self_test(self, comm) -> bool:
+        """One fused reduce over the peer-mapped buffers with a known answer (rank r contributes r + 1
+        everywhere, so every element must come back as tp (tp + 1) / 2).  The verdict is agreed over the
+        process group so that every rank keeps, or drops, the fused path together."""
+        from .. import ops
+
+        group = pstate.get_tp_group()
+        rows, ok = min(8, comm.max_rows), True
+        try:
+            part = comm.partial_buffer(rows)
+            part.fill_(float(comm.rank + 1))
+            resid = torch.zeros(rows, self.hidden_size, dtype=self.dtype, device=self.device)
+            torch.cuda.synchronize(self.device)
+            group.barrier()
+            ops.tp_reduce_add_rmsnorm(part, resid, None, 1e-6)
+            torch.cuda.synchronize(self.device)
+            ops.check_status(self.device.index)
+            want = comm.world * (comm.world + 1) / 2
+            ok = bool((resid.float() == want).all().item())
+        except Exception as exc:
+            logger.warning("fused tensor-parallel start-up check: %s", exc)
+            ok = False
+        verdict = torch.tensor([0 if ok else 1], dtype=torch.int32, device=self.device)
+        group.all_reduce(verdict)
+        return int(verdict.item()) == 0
 
     def _resolve_dtype(self) -> torch.dtype:
         want = self.server_config.dtype
