@@ -16,6 +16,7 @@ back-pressure behave identically.
 from __future__ import annotations
 
 import asyncio
+import copy
 import logging
 import multiprocessing as mp
 import os
@@ -71,6 +72,8 @@ class Engine:
         if self._launched:
             return self
         logging.getLogger("mllm_b200").setLevel(getattr(logging, self.server_config.log_level.upper(), logging.INFO))
+        if self.mode == "inproc" and (self.server_config.dp_size > 1 or self.server_config.world_size > 1):
+            raise ValueError("tensor / data parallel engines run as processes: use mode='multiproc'")
         if self.mode == "inproc":
             self._launch_inproc()
         else:
@@ -168,9 +171,11 @@ class Engine:
         sc = self.server_config
         vocab = self._vocab_size()
         uid = f"{os.getpid()}_{uuid.uuid4().hex[:8]}"
-        a_rr_tok, a_tok_sched, a_sched_detok, a_detok_rr = (make_ipc_address(n, uid) for n in
-                                                            ("rr_tok", "tok_sched", "sched_detok", "detok_rr"))
-        self._addrs = [a_rr_tok, a_tok_sched, a_sched_detok, a_detok_rr]
+        world, replicas = sc.world_size, max(1, int(sc.dp_size))
+        a_rr_tok, a_detok_rr = make_ipc_address("rr_tok", uid), make_ipc_address("detok_rr", uid)
+        a_tok_sched = [make_ipc_address(f"tok_sched{r}", uid) for r in range(replicas)]
+        a_sched_detok = [make_ipc_address(f"sched_detok{r}", uid) for r in range(replicas)]
+        self._addrs = [a_rr_tok, a_detok_rr, *a_tok_sched, *a_sched_detok]
         ctx = mp.get_context("spawn")
         pipes = []
 
@@ -187,14 +192,18 @@ class Engine:
                                           context_length=sc.context_length, vocab_size=vocab,
                                           tokenizer_mode=sc.tokenizer_mode, trust_remote_code=sc.trust_remote_code,
                                           log_level=sc.log_level, mm_config=self._mm_config()))
-        world = sc.world_size
-        port = _free_port() if world > 1 else None
-        for rank in range(world):  # one scheduler + model runner per GPU; rank 0 owns the sockets
-            spawn(run_scheduler_process, dict(server_config=sc, recv_addr=a_tok_sched if rank == 0 else None,
-                                              send_addr=a_sched_detok if rank == 0 else None,
-                                              hf_config=self.hf_config, quantization_method=self.quant_method,
-                                              kv_cache_dtype=self.kv_cache_dtype, device=self.device, rank=rank,
-                                              world_size=world, master_port=port))
+        # data parallelism: `dp_size` complete replicas (each `world` GPUs wide) behind the tokenizer's
+        # router; replica r uses GPUs base + r * world ... base + (r + 1) * world - 1
+        for rep in range(replicas):
+            rsc = copy.copy(sc)
+            rsc.base_gpu_id = sc.base_gpu_id + rep * world
+            port = _free_port() if world > 1 else None
+            for rank in range(world):  # one scheduler + model runner per GPU; rank 0 owns the sockets
+                spawn(run_scheduler_process, dict(server_config=rsc, recv_addr=a_tok_sched[rep] if rank == 0 else None,
+                                                  send_addr=a_sched_detok[rep] if rank == 0 else None,
+                                                  hf_config=self.hf_config, quantization_method=self.quant_method,
+                                                  kv_cache_dtype=self.kv_cache_dtype, device=self.device, rank=rank,
+                                                  world_size=world, master_port=port))
         spawn(run_detokenizer_process, dict(tokenizer_path=sc.tokenizer_path, recv_addr=a_sched_detok,
                                             send_addr=a_detok_rr, vocab_size=vocab, tokenizer_mode=sc.tokenizer_mode,
                                             trust_remote_code=sc.trust_remote_code, log_level=sc.log_level))

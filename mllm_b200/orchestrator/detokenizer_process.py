@@ -45,7 +45,7 @@ class DetokenizerWorker:
         return out
 
 
-def run_detokenizer_process(tokenizer_path, recv_addr: str, send_addr: str, pipe_writer=None, vocab_size: int = 1024,
+def run_detokenizer_process(tokenizer_path, recv_addr, send_addr: str, pipe_writer=None, vocab_size: int = 1024,
                             tokenizer_mode: str = "auto", trust_remote_code: bool = False, log_level: str = "info") -> None:
     import zmq
 
@@ -54,14 +54,22 @@ def run_detokenizer_process(tokenizer_path, recv_addr: str, send_addr: str, pipe
     setup_subprocess_logging(log_level)
     worker = DetokenizerWorker(tokenizer_path, vocab_size, tokenizer_mode, trust_remote_code)
     ctx = zmq.Context()
-    recv = make_socket(ctx, zmq.PULL, recv_addr, bind=False)
+    # one endpoint per engine replica (data parallelism): a PULL socket fair-queues over all of them
+    addrs = [recv_addr] if isinstance(recv_addr, str) else list(recv_addr)
+    recv = make_socket(ctx, zmq.PULL, addrs[0], bind=False)
+    for a in addrs[1:]:
+        recv.connect(a)
     send = make_socket(ctx, zmq.PUSH, send_addr, bind=True)
     if pipe_writer is not None:
         pipe_writer.send({"status": "ready"})
+    open_replicas = len(addrs)
     while True:
         msg = recv.recv_pyobj()
-        if msg is None:
-            return
+        if msg is None:  # a replica's scheduler has shut down
+            open_replicas -= 1
+            if open_replicas <= 0:
+                return
+            continue
         if isinstance(msg, BatchTokenIDOutput):
             send.send_pyobj(worker.detokenize(msg))
         else:

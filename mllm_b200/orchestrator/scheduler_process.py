@@ -386,6 +386,8 @@ def scheduler_event_loop(sched: "Scheduler", recv, send, poller, rank: int = 0, 
             msgs = box[0]
         for msg in msgs:
             if msg is None:
+                if rank == 0 and send is not None:
+                    send.send_pyobj(None)  # lets the detokenizer count this replica out
                 return
             if isinstance(msg, TokenizedGenerateReqInput):
                 err = sched.add_request(msg)

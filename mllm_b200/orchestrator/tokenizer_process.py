@@ -1,7 +1,8 @@
 """Tokenizer worker (role of pymllm/orchestrator/tokenizer_process.py:44-523): text -> ids with
 truncation to the context length; images (path / bytes / PIL / arrays) go through the model's
 processor when one exists, whose ``input_ids`` then replace the text ids; forwards
-``TokenizedGenerateReqInput`` to the scheduler and passes aborts through."""
+``TokenizedGenerateReqInput`` to the scheduler and passes aborts through.  In a data-parallel
+deployment (several engine replicas) the worker is also the router that spreads the requests."""
 
 from __future__ import annotations
 
@@ -9,7 +10,8 @@ import hashlib
 import io
 import logging
 import time
-from typing import Any, Dict, List, Optional
+from collections import OrderedDict
+from typing import Any, Dict, List, Optional, Sequence, Union
 
 from ..engine.io_struct import AbortReq, FlushCacheReq, TokenizedGenerateReqInput
 from ..utils.tokenizer import get_tokenizer
@@ -111,10 +113,60 @@ class TokenizerWorker:
             return_logprob=bool(req.get("return_logprob") or False), created_time=req.get("created_time") or time.time())
 
 
-def run_tokenizer_process(tokenizer_path, recv_addr: str, send_addr: str, pipe_writer=None,
+class ReplicaRouter:
+    """Hands tokenised requests to the engine replicas of a data-parallel deployment.
+
+    Every replica is a complete scheduler + model runner (group) with its own KV pool and prefix
+    cache.  Requests go to the replica with the fewest prompt tokens assigned so far among those
+    dispatched in the current window (ties: round robin), which keeps long and short prompts spread
+    evenly without feedback from the schedulers; an abort follows its request; cache flushes and the
+    shutdown marker go to every replica."""
+
+    WINDOW = 64        # requests after which the per-replica token tallies start again
+    MAX_TRACKED = 1 << 16
+
+    def __init__(self, senders: Sequence[Any]) -> None:
+        self.senders = list(senders)
+        self.load = [0] * len(self.senders)
+        self.count = 0
+        self.next = 0
+        self.owner: "OrderedDict[str, int]" = OrderedDict()
+
+    def pick(self, tokens: int) -> int:
+        n = len(self.senders)
+        if self.count % self.WINDOW == 0:
+            self.load = [0] * n
+        self.count += 1
+        order = [(self.next + i) % n for i in range(n)]
+        best = min(order, key=lambda r: self.load[r])
+        self.load[best] += max(1, tokens)
+        self.next = (best + 1) % n
+        return best
+
+    def route(self, msg: Any) -> List[int]:
+        """Sends ``msg`` and returns the replica indices it went to."""
+        n = len(self.senders)
+        if msg is None or isinstance(msg, FlushCacheReq):
+            targets = list(range(n))
+        elif isinstance(msg, AbortReq):
+            r = self.owner.pop(msg.rid, None)
+            targets = [r] if r is not None else list(range(n))
+        else:
+            r = self.pick(len(getattr(msg, "input_ids", None) or ()))
+            self.owner[msg.rid] = r
+            while len(self.owner) > self.MAX_TRACKED:
+                self.owner.popitem(last=False)
+            targets = [r]
+        for r in targets:
+            self.senders[r].send_pyobj(msg)
+        return targets
+
+
+def run_tokenizer_process(tokenizer_path, recv_addr: str, send_addr: Union[str, Sequence[str]], pipe_writer=None,
                           context_length: Optional[int] = None, vocab_size: int = 1024, tokenizer_mode: str = "auto",
                           trust_remote_code: bool = False, log_level: str = "info",
                           mm_config: Optional[Dict[str, Any]] = None) -> None:
+    """``send_addr``: one endpoint, or one per data-parallel replica."""
     import zmq
 
     from .ipc_utils import make_socket, setup_subprocess_logging
@@ -123,19 +175,20 @@ def run_tokenizer_process(tokenizer_path, recv_addr: str, send_addr: str, pipe_w
     worker = TokenizerWorker(tokenizer_path, context_length, vocab_size, tokenizer_mode, trust_remote_code, mm_config)
     ctx = zmq.Context()
     recv = make_socket(ctx, zmq.PULL, recv_addr, bind=False)
-    send = make_socket(ctx, zmq.PUSH, send_addr, bind=True)
+    addrs = [send_addr] if isinstance(send_addr, str) else list(send_addr)
+    router = ReplicaRouter([make_socket(ctx, zmq.PUSH, a, bind=True) for a in addrs])
     if pipe_writer is not None:
         pipe_writer.send({"status": "ready"})
     while True:
         msg = recv.recv_pyobj()
         if msg is None:
-            send.send_pyobj(None)
+            router.route(None)
             return
         if isinstance(msg, (AbortReq, FlushCacheReq)):
-            send.send_pyobj(msg)
+            router.route(msg)
             continue
         try:
-            send.send_pyobj(worker.tokenize(msg))
+            router.route(worker.tokenize(msg))
         except Exception as exc:
             logger.exception("tokenization failed")
-            send.send_pyobj(AbortReq(rid=msg.get("rid", "")))
+            router.route(AbortReq(rid=msg.get("rid", "")))

@@ -60,3 +60,70 @@ def test_two_rank_tensor_parallel_engine_on_cpu():
         assert not eng.is_healthy
     finally:
         eng.shutdown()
+
+
+def test_two_data_parallel_replicas_on_cpu():
+    """Two complete replicas behind the tokenizer's router: same seeded weights, so every prompt gets
+    the tokens the single engine gives, whichever replica serves it; concurrent requests spread over
+    both; an abort reaches the replica that holds the request."""
+    import threading
+
+    prompts = ["hello", "the quick brown fox", "a", "lorem ipsum dolor", "hello"]
+    ref = Engine(_cfg(), mode="inproc", device="cpu").launch()
+    want = [ref.generate(p, {"max_new_tokens": 5, "temperature": 0.0})["output_ids"] for p in prompts]
+    ref.shutdown()
+    cfg = _cfg()
+    cfg.dp_size = 2
+    with pytest.raises(ValueError):
+        Engine(cfg, mode="inproc", device="cpu").launch()
+    eng = Engine(cfg, mode="multiproc", device="cpu").launch()
+    try:
+        assert len(eng._procs) == 4      # tokenizer, two replicas, detokenizer
+        got = [None] * len(prompts)
+
+        def one(i):
+            got[i] = eng.generate(prompts[i], {"max_new_tokens": 5, "temperature": 0.0}, timeout=180)["output_ids"]
+
+        threads = [threading.Thread(target=one, args=(i,)) for i in range(len(prompts))]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join(200)
+        assert got == want
+        chunks = eng.generate("abort me", {"max_new_tokens": 100, "temperature": 0.0}, stream=True)
+        first = next(chunks)
+        chunks.close()                   # closing the stream aborts the request on its replica
+        assert first["output_ids"]
+        assert eng.generate("a", {"max_new_tokens": 3, "temperature": 0.0}, timeout=120)["output_ids"] == want[2][:3]
+        assert eng.is_healthy
+    finally:
+        eng.shutdown()
+
+
+def test_replica_router_spreads_requests_and_follows_aborts():
+    from mllm_b200.engine.io_struct import AbortReq, FlushCacheReq, TokenizedGenerateReqInput
+    from mllm_b200.orchestrator.tokenizer_process import ReplicaRouter
+
+    class Sink:
+        def __init__(self):
+            self.got = []
+
+        def send_pyobj(self, m):
+            self.got.append(m)
+
+    sinks = [Sink(), Sink(), Sink()]
+    router = ReplicaRouter(sinks)
+
+    def req(rid, n):
+        return TokenizedGenerateReqInput(rid=rid, input_text="", input_ids=[1] * n, mm_inputs=None, sampling_params={},
+                                         stream=False, return_logprob=False, created_time=0.0)
+
+    where = {f"r{i}": router.route(req(f"r{i}", n))[0] for i, n in enumerate([100, 10, 10, 10, 10, 10])}
+    assert where["r0"] == 0 and where["r1"] == 1 and where["r2"] == 2
+    assert where["r3"] != 0 and where["r4"] != 0     # the replica holding the long prompt is skipped
+    tokens = [sum(len(m.input_ids) for m in s.got) for s in sinks]
+    assert max(tokens) == 100 and min(tokens) >= 20
+    assert router.route(AbortReq(rid="r1")) == [1]
+    assert router.route(AbortReq(rid="unknown")) == [0, 1, 2]
+    assert router.route(FlushCacheReq()) == [0, 1, 2]
+    assert router.route(None) == [0, 1, 2] and all(s.got[-1] is None for s in sinks)
