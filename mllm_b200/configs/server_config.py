@@ -88,6 +88,7 @@ class ServerConfig:
     radix_cache_page_size: int = 1
     page_size: Optional[int] = None  # alias of radix_cache_page_size
     enable_mamba_cache: bool = False
+    mamba_cache_slots: Optional[int] = None  # snapshot rows of the hybrid prefix cache (None: from max_running_requests)
     tensor_transport_mode: str = "default"
     cuda_ipc_pool_size_mb: int = 512
     cuda_ipc_recycle_interval: float = 0.1

@@ -161,11 +161,27 @@ class ModelRunner:
         self._init_tp_comm()
         self._configure_kv_cache_dtype()
         self.init_memory_pool()
+        self._init_state_pool()
         # the warm-up runs before graph capture use kernels that wait on peer flags with a bound of
         # a few seconds: the ranks enter them together, and leave initialisation together
         self._tp_rendezvous()
         self.init_cuda_graphs()
         self._tp_rendezvous()
+
+    def _init_state_pool(self) -> None:
+        """Hybrid models: recurrent-state rows for every request slot and, when the state-aware prefix
+        cache is on, snapshot rows for it (``mamba_cache_slots``; default 4 per running request,
+        between 16 and 256)."""
+        self.gdn_pool = None
+        if not hasattr(self.model, "make_gdn_pool"):
+            return
+        sc = self.server_config
+        track = 0
+        if getattr(sc, "enable_mamba_cache", False) and not sc.disable_radix_cache:
+            track = getattr(sc, "mamba_cache_slots", None)
+            if track is None:
+                track = max(16, min(256, 4 * int(sc.max_running_requests or 1)))
+        self.gdn_pool = self.model.make_gdn_pool(self.req_to_token_pool.size, int(track))
 
     def _tp_rendezvous(self) -> None:
         if pstate.get_tensor_model_parallel_world_size() > 1:

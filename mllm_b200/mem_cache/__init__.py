@@ -3,11 +3,12 @@ from .base_prefix_cache import (
     hash_bytes, hash_to_int64, hash_token_ids,
 )
 from .chunk_cache import ChunkCache
+from .mamba_radix_cache import MambaRadixCache, MambaTreeNode
 from .memory_pool import GDNPool, KVPool, ReqToTokenPool, TokenToKVPoolAllocator
 from .radix_cache import RadixCache, TreeNode
 
 __all__ = [
     "BasePrefixCache", "EvictResult", "InsertResult", "MatchResult", "RadixKey",
     "hash_bytes", "hash_to_int64", "hash_token_ids", "ChunkCache", "KVPool", "GDNPool",
-    "ReqToTokenPool", "TokenToKVPoolAllocator", "RadixCache", "TreeNode",
+    "ReqToTokenPool", "TokenToKVPoolAllocator", "RadixCache", "TreeNode", "MambaRadixCache", "MambaTreeNode",
 ]

@@ -64,6 +64,7 @@ class MatchResult:
     last_node: Any = None
     prefix_len: int = 0
     mamba_branching_seqlen: Optional[int] = None
+    state_slot: Optional[int] = None  # hybrid models: snapshot row holding the state at the end of the prefix
 
 
 @dataclass

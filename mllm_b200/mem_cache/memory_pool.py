@@ -176,15 +176,18 @@ class TokenToKVPoolAllocator:
 
 class GDNPool:
     """Per-request state of the gated-delta-net layers of a hybrid model: the fp32 recurrent matrix
-    ``[layers, slots, Hv, Dk, Dv]`` and the last ``K-1`` convolution inputs ``[layers, slots, C, K-1]``.
-    A request uses the row of its ``req_to_token`` slot, so no separate allocator is needed
-    (role of pymllm/mem_cache/memory_pool.py:479-631)."""
+    ``[layers, rows, Hv, Dk, Dv]`` and the last ``K-1`` convolution inputs ``[layers, rows, C, K-1]``.
+    A request uses the row of its ``req_to_token`` slot, so no separate allocator is needed for the
+    first ``slots`` rows; ``track_slots`` further rows hold snapshots that the hybrid prefix cache
+    keeps at the ends of cached prefixes (role of pymllm/mem_cache/memory_pool.py:479-631)."""
 
     def __init__(self, num_layers: int, slots: int, num_v_heads: int, head_k_dim: int, head_v_dim: int, conv_dim: int,
-                 conv_kernel: int, device, conv_dtype: torch.dtype = torch.bfloat16) -> None:
-        self.num_layers, self.slots = num_layers, slots
-        self.recurrent = torch.zeros((num_layers, slots, num_v_heads, head_k_dim, head_v_dim), dtype=torch.float32, device=device)
-        self.conv = torch.zeros((num_layers, slots, conv_dim, conv_kernel - 1), dtype=conv_dtype, device=device)
+                 conv_kernel: int, device, conv_dtype: torch.dtype = torch.bfloat16, track_slots: int = 0) -> None:
+        self.num_layers, self.slots, self.track_slots = num_layers, slots, int(track_slots)
+        rows = slots + self.track_slots
+        self.recurrent = torch.zeros((num_layers, rows, num_v_heads, head_k_dim, head_v_dim), dtype=torch.float32, device=device)
+        self.conv = torch.zeros((num_layers, rows, conv_dim, conv_kernel - 1), dtype=conv_dtype, device=device)
+        self._free_track: List[int] = list(range(slots, rows))
 
     def layer(self, idx: int) -> Tuple[torch.Tensor, torch.Tensor]:
         return self.recurrent[idx], self.conv[idx]
@@ -196,6 +199,21 @@ class GDNPool:
     def copy(self, src: int, dst: int) -> None:
         self.recurrent[:, dst] = self.recurrent[:, src]
         self.conv[:, dst] = self.conv[:, src]
+
+    copy_states = copy
+
+    # ---- snapshot rows ----
+    def track_available(self) -> int:
+        return len(self._free_track)
+
+    def alloc_track_slot(self) -> Optional[int]:
+        return self._free_track.pop() if self._free_track else None
+
+    def free_track_slot(self, slot: int) -> None:
+        slot = int(slot)
+        if not (self.slots <= slot < self.slots + self.track_slots) or slot in self._free_track:
+            raise ValueError(f"row {slot} is not an allocated snapshot row")
+        self._free_track.append(slot)
 
     def bytes(self) -> int:
         return self.recurrent.numel() * 4 + self.conv.numel() * self.conv.element_size()

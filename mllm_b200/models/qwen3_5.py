@@ -175,14 +175,20 @@ class Qwen3_5ForCausalLM(nn.Module):
         self.kv_layers = self.model.num_attn_layers
         self._gdn_pool: Optional[GDNPool] = None
 
+    def make_gdn_pool(self, slots: int, track_slots: int = 0) -> GDNPool:
+        """State rows for ``slots`` requests plus ``track_slots`` snapshot rows for the prefix cache."""
+        c = self.config
+        w = self.model.embed_tokens.weight
+        conv_dim = 2 * c.linear_key_head_dim * c.linear_num_key_heads + c.linear_value_head_dim * c.linear_num_value_heads
+        self._gdn_pool = GDNPool(self.model.num_gdn_layers, slots, c.linear_num_value_heads, c.linear_key_head_dim,
+                                 c.linear_value_head_dim, conv_dim, c.linear_conv_kernel_dim, w.device, w.dtype,
+                                 track_slots=track_slots)
+        return self._gdn_pool
+
     def gdn_pool(self, fb: ForwardBatch) -> GDNPool:
         slots = fb.req_to_token_pool.req_to_token.shape[0]
         if self._gdn_pool is None or self._gdn_pool.slots != slots:
-            c = self.config
-            w = self.model.embed_tokens.weight
-            conv_dim = 2 * c.linear_key_head_dim * c.linear_num_key_heads + c.linear_value_head_dim * c.linear_num_value_heads
-            self._gdn_pool = GDNPool(self.model.num_gdn_layers, slots, c.linear_num_value_heads, c.linear_key_head_dim,
-                                     c.linear_value_head_dim, conv_dim, c.linear_conv_kernel_dim, w.device, w.dtype)
+            self.make_gdn_pool(slots)
         return self._gdn_pool
 
     @property

@@ -28,7 +28,7 @@ import torch
 
 from ..engine.sampling_params import SamplingParams
 from ..executor.model_runner import ModelRunner, SamplingBatchInfo
-from ..mem_cache import ChunkCache, RadixCache, RadixKey
+from ..mem_cache import ChunkCache, MambaRadixCache, RadixCache, RadixKey
 
 logger = logging.getLogger(__name__)
 
@@ -96,8 +96,17 @@ class ModelRunnerProcess:
         self.device = runner.device
         self.page_size = runner.server_config.radix_cache_page_size
         alloc = runner.token_to_kv_pool_allocator
-        self.prefix_cache = (ChunkCache(alloc, self.page_size) if disable_radix_cache
-                             else _make_radix_cache(alloc, self.page_size))
+        self.state_pool = getattr(runner, "gdn_pool", None)  # hybrid models: recurrent state per request row
+        if disable_radix_cache:
+            self.prefix_cache = ChunkCache(alloc, self.page_size)
+        elif self.state_pool is not None:
+            # a cached prefix of a hybrid model is reusable only where the recurrent state at its end was
+            # kept: the state-aware tree when snapshot rows exist, no reuse otherwise
+            self.prefix_cache = (MambaRadixCache(alloc, self.page_size, self.state_pool)
+                                 if self.state_pool.track_slots > 0 else ChunkCache(alloc, self.page_size))
+        else:
+            self.prefix_cache = _make_radix_cache(alloc, self.page_size)
+        self.hybrid_cache = isinstance(self.prefix_cache, MambaRadixCache)
         self.stats = {"prefix_hit_tokens": 0, "prefill_tokens": 0, "evicted_tokens": 0}
 
     # ------------------------------------------------------------------ capacity
@@ -142,6 +151,8 @@ class ModelRunnerProcess:
             self.runner.req_to_token_pool.req_to_token[req.req_pool_idx, : m.prefix_len] = torch.from_numpy(
                 m.indices.astype(np.int32)).to(self.device, non_blocking=True)
             self.stats["prefix_hit_tokens"] += m.prefix_len
+            if self.hybrid_cache:  # resume the recurrent layers from the snapshot taken at the prefix's end
+                self.state_pool.copy(m.state_slot, req.req_pool_idx)
 
     # ------------------------------------------------------------------ forward passes
     def extend(self, items: Sequence[Tuple[Req, int]], sampling: bool = True):
@@ -234,8 +245,17 @@ class ModelRunnerProcess:
         n -= n % self.page_size
         if n <= req.prefix_len or isinstance(self.prefix_cache, ChunkCache):
             return
+        extra = {}
+        if self.hybrid_cache:
+            # the request's state row describes exactly `num_computed` tokens: only a prefix of that
+            # length can be cached, and only if a snapshot row can be had for it
+            snap = self.prefix_cache.alloc_state_slot() if n == req.num_computed else None
+            if snap is None:
+                return
+            self.state_pool.copy(req.req_pool_idx, snap)
+            extra["mamba_value"] = snap
         slots = self.runner.req_to_token_pool.req_to_token[req.req_pool_idx, :n].to("cpu", torch.int64).numpy()
-        res = self.prefix_cache.insert(RadixKey(tokens[:n], req.extra_key), slots)
+        res = self.prefix_cache.insert(RadixKey(tokens[:n], req.extra_key), slots, **extra)
         # [prefix_len, res.prefix_len): the tree already had these tokens under other slots -> ours are duplicates
         if res.prefix_len > req.prefix_len:
             self.runner.token_to_kv_pool_allocator.free(slots[req.prefix_len : res.prefix_len])
