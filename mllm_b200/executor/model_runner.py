@@ -175,6 +175,9 @@ class ModelRunner:
         self.gdn_pool = None
         if not hasattr(self.model, "make_gdn_pool"):
             return
+        from .. import ops
+
+        ops.set_gdn_extend_backend(getattr(self.server_config, "gdn_extend_backend", "auto"))
         sc = self.server_config
         track = 0
         if getattr(sc, "enable_mamba_cache", False) and not sc.disable_radix_cache:

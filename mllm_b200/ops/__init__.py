@@ -517,10 +517,21 @@ def causal_conv1d_silu(x, weight, conv_state, state_indices, seq_lens, has_state
     return ref.causal_conv1d_silu(x, weight, conv_state, state_indices, lens, has)
 
 
+_GDN_EXTEND_BACKEND = "auto"
+
+
+def set_gdn_extend_backend(name: str) -> None:
+    """``pytorch``: the chunk-parallel PyTorch form on every device; anything else: the CUDA kernel where
+    it applies (``--server.gdn_extend_backend``)."""
+    global _GDN_EXTEND_BACKEND
+    _GDN_EXTEND_BACKEND = str(name)
+
+
 def gated_delta_rule(q, k, v, g, beta, state, state_indices, seq_lens, has_state, q_start=None) -> torch.Tensor:
     """Gated delta rule over ragged sequences with per-request recurrent state (read when ``has_state``,
     always written back).  q, k [T, H, Dk], v [T, H, Dv], g / beta [T, H] fp32."""
-    if use_kernels(q) and hasattr(ext(), "gdn_recurrent") and q.shape[-1] == 128 and v.shape[-1] == 128:
+    if (use_kernels(q) and hasattr(ext(), "gdn_recurrent") and q.shape[-1] == 128 and v.shape[-1] == 128
+            and _GDN_EXTEND_BACKEND != "pytorch"):
         dev = q.device
         lens = seq_lens if isinstance(seq_lens, torch.Tensor) else torch.tensor(list(seq_lens), dtype=torch.int32, device=dev)
         has = has_state if isinstance(has_state, torch.Tensor) else torch.tensor([int(h) for h in has_state], dtype=torch.int32, device=dev)
@@ -533,6 +544,8 @@ def gated_delta_rule(q, k, v, g, beta, state, state_indices, seq_lens, has_state
         return out
     lens = seq_lens.tolist() if isinstance(seq_lens, torch.Tensor) else seq_lens
     has = has_state.tolist() if isinstance(has_state, torch.Tensor) else has_state
+    if max(lens, default=0) > 16:  # prefill: the chunk-parallel form (matrix products) instead of a token loop
+        return ref.gated_delta_rule_chunked(q, k, v, g, beta, state, state_indices, lens, has)
     return ref.gated_delta_rule(q, k, v, g, beta, state, state_indices, lens, has)
 
 

@@ -465,3 +465,52 @@ def gated_delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch
         state[slot] = S.to(state.dtype)
         off += n
     return out.to(v.dtype)
+
+
+
+def gated_delta_rule_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor,
+                             state: torch.Tensor, state_indices: torch.Tensor, seq_lens, has_state,
+                             chunk: int = 64) -> torch.Tensor:
+    """The same rule as :func:`gated_delta_rule`, evaluated ``chunk`` tokens at a time with matrix
+    products (the chunk-parallel form used for prefill; role of pymllm's ``gdn_chunkwise`` reference).
+
+    Inside a chunk with cumulative log decay ``G_i = sum_{j<=i} g_j`` and incoming state ``S0``:
+
+        A[i, j] = exp(G_i - G_j) (k_i . k_j)  for j < i          (strictly lower triangular)
+        U       = (I + diag(beta) A)^-1 diag(beta) (V - exp(G) * (K S0))      # the per-token updates
+        O       = exp(G) * (Q S0) + (M * (Q K^T)) U,   M[i, j] = exp(G_i - G_j) for j <= i
+        S_end   = exp(G_C) S0 + (exp(G_C - G) * K)^T U
+
+    All exponents are of non-positive numbers (``g <= 0``), so nothing overflows."""
+    T, H, Dk = q.shape
+    qf = _f32(q)
+    kf = _f32(k)
+    qf = qf * torch.rsqrt((qf * qf).sum(-1, keepdim=True) + 1e-6) * Dk ** -0.5
+    kf = kf * torch.rsqrt((kf * kf).sum(-1, keepdim=True) + 1e-6)
+    vf, gf, bf = _f32(v), _f32(g), _f32(beta)
+    out = torch.empty(T, H, v.shape[-1], dtype=torch.float32, device=q.device)
+    off = 0
+    for b, n in enumerate(list(seq_lens)):
+        n = int(n)
+        slot = int(state_indices[b])
+        S = state[slot].float().clone() if bool(has_state[b]) else torch.zeros_like(state[slot], dtype=torch.float32)
+        for c0 in range(off, off + n, chunk):
+            c1 = min(off + n, c0 + chunk)
+            C = c1 - c0
+            Q, K, V = (t[c0:c1].transpose(0, 1) for t in (qf, kf, vf))          # [H, C, D]
+            G = gf[c0:c1].transpose(0, 1).cumsum(-1)                            # [H, C]
+            B = bf[c0:c1].transpose(0, 1)                                       # [H, C]
+            diff = G.unsqueeze(-1) - G.unsqueeze(-2)                            # G_i - G_j
+            lower = torch.ones(C, C, dtype=torch.bool, device=q.device).tril()
+            M = torch.where(lower, diff, torch.full_like(diff, float("-inf"))).exp()   # j <= i
+            A = (M * (K @ K.transpose(-1, -2))).tril(-1)
+            eG = G.exp().unsqueeze(-1)
+            rhs = B.unsqueeze(-1) * (V - eG * (K @ S))
+            lhs = torch.eye(C, device=q.device, dtype=torch.float32) + B.unsqueeze(-1) * A
+            U = torch.linalg.solve_triangular(lhs, rhs, upper=False, unitriangular=True)
+            out[c0:c1] = (eG * (Q @ S) + (M * (Q @ K.transpose(-1, -2))) @ U).transpose(0, 1)
+            tail = (G[:, -1:] - G).exp().unsqueeze(-1)                          # exp(G_C - G_j)
+            S = G[:, -1].exp().view(H, 1, 1) * S + (tail * K).transpose(-1, -2) @ U
+        state[slot] = S.to(state.dtype)
+        off += n
+    return out.to(v.dtype)

@@ -96,3 +96,27 @@ def test_matches_hf_qwen3_5():
         with torch.no_grad():
             want = hf(seq).logits[:, -1]
         torch.testing.assert_close(got, want, atol=5e-4, rtol=5e-4)
+
+
+def test_chunked_delta_rule_matches_the_token_loop():
+    """The chunk-parallel (matrix product) form against the one-token-at-a-time definition: ragged
+    batch, incoming state on some requests, several chunk sizes including one that leaves a short tail."""
+    import torch
+
+    from mllm_b200.ops import reference as ref
+
+    torch.manual_seed(0)
+    H, Dk, Dv = 4, 32, 48
+    lens = [150, 7, 64, 129]
+    T = sum(lens)
+    q, k, v = torch.randn(T, H, Dk), torch.randn(T, H, Dk), torch.randn(T, H, Dv)
+    g, beta = -torch.rand(T, H) * 0.3, torch.rand(T, H)
+    st = torch.randn(6, H, Dk, Dv) * 0.1
+    idx, has = torch.tensor([3, 0, 5, 1]), [1, 0, 1, 0]
+    s_ref = st.clone()
+    o_ref = ref.gated_delta_rule(q, k, v, g, beta, s_ref, idx, lens, has)
+    for chunk in (16, 64, 128):
+        s = st.clone()
+        o = ref.gated_delta_rule_chunked(q, k, v, g, beta, s, idx, lens, has, chunk=chunk)
+        assert (o - o_ref).abs().max() < 2e-6 and (s - s_ref).abs().max() < 2e-6
+        assert torch.equal(s[2], st[2]) and torch.equal(s[4], st[4])   # rows of no request are untouched
