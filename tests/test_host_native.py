@@ -289,3 +289,43 @@ def test_cpp_cpu_oracle_matches_pytorch_oracle(tmp_path):
     assert list(a["tokens"]) == b["tokens"]
     torch.testing.assert_close(torch.from_numpy(a["prefill_logits"]), b["prefill_logits"], atol=2e-4, rtol=2e-4)
     torch.testing.assert_close(torch.from_numpy(a["last_logits"]), b["last_logits"], atol=2e-4, rtol=2e-4)
+
+
+def test_quantizer_and_inspector_tools(tmp_path, capsys):
+    """Block quantiser CLI -> .mllm with Q4_0 / Q8_0 entries -> the reader expands them within the
+    scheme's error bound; the inspector lists dtypes, shapes and sizes."""
+    from mllm_b200.io import inspect as insp
+    from mllm_b200.io import quantize as quant
+    from mllm_b200.io.mllm_file import MllmFileReader, write_mllm
+
+    g = torch.Generator().manual_seed(0)
+    tensors = [("model.layers.0.mlp.down_proj.weight", torch.randn(48, 64, generator=g)),
+               ("model.layers.0.input_layernorm.weight", torch.ones(64)),
+               ("model.embed_tokens.weight", torch.randn(100, 64, generator=g)),
+               ("model.layers.0.self_attn.q_proj.weight", torch.randn(64, 96, generator=g).to(torch.bfloat16)),
+               ("odd.weight", torch.randn(8, 20, generator=g))]
+    src = tmp_path / "src.mllm"
+    write_mllm(str(src), tensors, model_name="toy")
+    for scheme, tol in (("q8_0", 1 / 127), ("q4_0", 2 / 8)):   # q4_0: half a step, a whole one where +8 clips to +7
+        dst = tmp_path / f"{scheme}.mllm"
+        quant.main(["--input", str(src), "--output", str(dst), "--scheme", scheme, "--model-name", "toy-q"])
+        d = insp.describe(str(dst))
+        kinds = {x["name"]: x["dtype"] for x in d["tensors"]}
+        assert d["model_name"] == "toy-q" and d["version"] == 2
+        assert kinds["model.layers.0.mlp.down_proj.weight"] == f"gguf_{scheme}"
+        assert kinds["model.layers.0.self_attn.q_proj.weight"] == f"gguf_{scheme}"
+        assert kinds["model.embed_tokens.weight"] == "float32" and kinds["odd.weight"] == "float32"
+        assert kinds["model.layers.0.input_layernorm.weight"] == "float32"
+        per_block = 34 if scheme == "q8_0" else 18
+        sizes = {x["name"]: x["bytes"] for x in d["tensors"]}
+        assert sizes["model.layers.0.mlp.down_proj.weight"] == 48 * 64 // 32 * per_block
+        r = MllmFileReader(str(dst))
+        for name, t in tensors[:1] + tensors[3:4]:
+            back = r.tensor(name, torch.float32)
+            assert back.shape == t.shape
+            blocks = t.float().reshape(-1, 32)
+            bound = blocks.abs().max(dim=1, keepdim=True).values * tol * 0.51 + 1e-3
+            assert ((back.reshape(-1, 32) - blocks).abs() <= bound).all()
+    insp.main([str(tmp_path / "q4_0.mllm"), "--filter", "down_proj"])
+    out = capsys.readouterr().out
+    assert "gguf_q4_0" in out and "down_proj" in out and "embed_tokens" not in out
