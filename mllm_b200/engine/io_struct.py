@@ -104,6 +104,13 @@ class TokenizedGenerateReqInput(BaseReq):
 
 
 @dataclass
+class SharedQueueNotice:
+    """Sent over the control socket in place of a request whose body went through the shared-memory
+    queue (``--server.enable_shared_queue``): keeps the arrival order and wakes an idle scheduler."""
+    rid: str = ""
+
+
+@dataclass
 class BatchTokenizedGenerateReqInput:
     reqs: List[TokenizedGenerateReqInput]
 

@@ -188,10 +188,18 @@ class Engine:
 
         self._zmq = zmq.Context()
         self._to_tok = make_socket(self._zmq, zmq.PUSH, a_rr_tok, bind=True)
+        # shared-memory fast path for requests that carry tensors (images): one queue per replica,
+        # handed to the tokenizer (writer) and to the replica's rank 0 (reader) at spawn time
+        self._tensor_queues = None
+        if sc.enable_shared_queue:
+            from ..orchestrator.shared_memory_queue import TensorQueue
+
+            self._tensor_queues = [TensorQueue(transport_mode=sc.tensor_transport_mode, ctx=ctx) for _ in range(replicas)]
         spawn(run_tokenizer_process, dict(tokenizer_path=sc.tokenizer_path, recv_addr=a_rr_tok, send_addr=a_tok_sched,
                                           context_length=sc.context_length, vocab_size=vocab,
                                           tokenizer_mode=sc.tokenizer_mode, trust_remote_code=sc.trust_remote_code,
-                                          log_level=sc.log_level, mm_config=self._mm_config()))
+                                          log_level=sc.log_level, mm_config=self._mm_config(),
+                                          shared_queues=self._tensor_queues))
         # data parallelism: `dp_size` complete replicas (each `world` GPUs wide) behind the tokenizer's
         # router; replica r uses GPUs base + r * world ... base + (r + 1) * world - 1
         for rep in range(replicas):
@@ -203,7 +211,8 @@ class Engine:
                                                   send_addr=a_sched_detok[rep] if rank == 0 else None,
                                                   hf_config=self.hf_config, quantization_method=self.quant_method,
                                                   kv_cache_dtype=self.kv_cache_dtype, device=self.device, rank=rank,
-                                                  world_size=world, master_port=port))
+                                                  world_size=world, master_port=port,
+                                                  tensor_queue=self._tensor_queues[rep] if self._tensor_queues and rank == 0 else None))
         spawn(run_detokenizer_process, dict(tokenizer_path=sc.tokenizer_path, recv_addr=a_sched_detok,
                                             send_addr=a_detok_rr, vocab_size=vocab, tokenizer_mode=sc.tokenizer_mode,
                                             trust_remote_code=sc.trust_remote_code, log_level=sc.log_level))

@@ -25,7 +25,7 @@ from typing import Any, Deque, Dict, List, Optional, Tuple
 import torch
 
 from ..configs import ServerConfig
-from ..engine.io_struct import AbortReq, BatchTokenIDOutput, FlushCacheReq, TokenizedGenerateReqInput
+from ..engine.io_struct import AbortReq, BatchTokenIDOutput, FlushCacheReq, SharedQueueNotice, TokenizedGenerateReqInput
 from ..engine.sampling_params import SamplingParams
 from .model_runner_process import KVAllocationError, ModelRunnerProcess, Req
 
@@ -327,7 +327,7 @@ def resolve_eos_token_ids(hf_config) -> List[int]:
 def run_scheduler_process(server_config: ServerConfig, recv_addr: Optional[str], send_addr: Optional[str], pipe_writer=None,
                           hf_config=None, quantization_method=None, kv_cache_dtype: str = "auto",
                           device: Optional[str] = None, rank: int = 0, world_size: int = 1,
-                          master_port: Optional[int] = None) -> None:
+                          master_port: Optional[int] = None, tensor_queue=None) -> None:
     """Event loop: receive -> schedule -> forward -> stream out (one forward per iteration).
 
     With ``world_size > 1`` one such process runs per rank.  Rank 0 owns the sockets; at the top of
@@ -364,10 +364,25 @@ def run_scheduler_process(server_config: ServerConfig, recv_addr: Optional[str],
         poller.register(recv, zmq.POLLIN)
     if pipe_writer is not None:
         pipe_writer.send({"status": "ready", "max_total_num_tokens": sched.mrp.runner.max_total_num_tokens})
-    scheduler_event_loop(sched, recv, send, poller, rank, world_size, ctrl)
+    scheduler_event_loop(sched, recv, send, poller, rank, world_size, ctrl, tensor_queue if rank == 0 else None)
 
 
-def scheduler_event_loop(sched: "Scheduler", recv, send, poller, rank: int = 0, world_size: int = 1, ctrl_group=None) -> None:
+def _take_from_shared_queue(tensor_queue, notice):
+    """The request announced by ``notice``: its metadata from shared memory, its tensors from the queue."""
+    import queue as _queue
+
+    if tensor_queue is None:
+        return {"error": "request body was sent through a shared-memory queue this scheduler does not have", "rid": notice.rid}
+    try:
+        rid, meta, mm = tensor_queue.get(timeout=30)
+    except _queue.Empty:
+        return {"error": "shared-memory queue: announced request never arrived", "rid": notice.rid}
+    meta.mm_inputs = mm
+    return meta
+
+
+def scheduler_event_loop(sched: "Scheduler", recv, send, poller, rank: int = 0, world_size: int = 1, ctrl_group=None,
+                         tensor_queue=None) -> None:
     idle_ms = 1000 if world_size == 1 else 50  # followers wait in the broadcast: keep the heartbeat short
     while True:
         msgs: Optional[list] = None
@@ -376,7 +391,13 @@ def scheduler_event_loop(sched: "Scheduler", recv, send, poller, rank: int = 0, 
             # drain the inbox; sleep on the socket when there is nothing to run
             timeout = 0 if sched.has_work() else idle_ms
             while dict(poller.poll(timeout)):
-                msgs.append(recv.recv_pyobj())
+                m = recv.recv_pyobj()
+                if isinstance(m, SharedQueueNotice):
+                    m = _take_from_shared_queue(tensor_queue, m)
+                    if isinstance(m, dict):  # could not be fetched: answer, do not hand on to the other ranks
+                        send.send_pyobj(m)
+                        continue
+                msgs.append(m)
                 timeout = 0
         if world_size > 1:
             import torch.distributed as dist

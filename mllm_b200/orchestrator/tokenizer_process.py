@@ -13,7 +13,7 @@ import time
 from collections import OrderedDict
 from typing import Any, Dict, List, Optional, Sequence, Union
 
-from ..engine.io_struct import AbortReq, FlushCacheReq, TokenizedGenerateReqInput
+from ..engine.io_struct import AbortReq, FlushCacheReq, SharedQueueNotice, TokenizedGenerateReqInput
 from ..utils.tokenizer import get_tokenizer
 
 logger = logging.getLogger(__name__)
@@ -125,8 +125,11 @@ class ReplicaRouter:
     WINDOW = 64        # requests after which the per-replica token tallies start again
     MAX_TRACKED = 1 << 16
 
-    def __init__(self, senders: Sequence[Any]) -> None:
+    def __init__(self, senders: Sequence[Any], shared_queues: Optional[Sequence[Any]] = None) -> None:
         self.senders = list(senders)
+        # one shared-memory queue per replica: requests that carry tensors (images) take it, the socket
+        # then only carries a notice
+        self.shared_queues = list(shared_queues) if shared_queues else None
         self.load = [0] * len(self.senders)
         self.count = 0
         self.next = 0
@@ -158,15 +161,23 @@ class ReplicaRouter:
                 self.owner.popitem(last=False)
             targets = [r]
         for r in targets:
-            self.senders[r].send_pyobj(msg)
+            if (self.shared_queues is not None and isinstance(msg, TokenizedGenerateReqInput)
+                    and msg.mm_inputs is not None):
+                import dataclasses
+
+                self.shared_queues[r].put(msg.rid, dataclasses.replace(msg, mm_inputs=None), msg.mm_inputs)
+                self.senders[r].send_pyobj(SharedQueueNotice(rid=msg.rid))
+            else:
+                self.senders[r].send_pyobj(msg)
         return targets
 
 
 def run_tokenizer_process(tokenizer_path, recv_addr: str, send_addr: Union[str, Sequence[str]], pipe_writer=None,
                           context_length: Optional[int] = None, vocab_size: int = 1024, tokenizer_mode: str = "auto",
                           trust_remote_code: bool = False, log_level: str = "info",
-                          mm_config: Optional[Dict[str, Any]] = None) -> None:
-    """``send_addr``: one endpoint, or one per data-parallel replica."""
+                          mm_config: Optional[Dict[str, Any]] = None, shared_queues: Optional[Sequence[Any]] = None) -> None:
+    """``send_addr``: one endpoint, or one per data-parallel replica; ``shared_queues``: the matching
+    ``TensorQueue`` objects when the shared-memory fast path is on."""
     import zmq
 
     from .ipc_utils import make_socket, setup_subprocess_logging
@@ -176,7 +187,7 @@ def run_tokenizer_process(tokenizer_path, recv_addr: str, send_addr: Union[str, 
     ctx = zmq.Context()
     recv = make_socket(ctx, zmq.PULL, recv_addr, bind=False)
     addrs = [send_addr] if isinstance(send_addr, str) else list(send_addr)
-    router = ReplicaRouter([make_socket(ctx, zmq.PUSH, a, bind=True) for a in addrs])
+    router = ReplicaRouter([make_socket(ctx, zmq.PUSH, a, bind=True) for a in addrs], shared_queues)
     if pipe_writer is not None:
         pipe_writer.send({"status": "ready"})
     while True:

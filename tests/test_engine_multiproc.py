@@ -127,3 +127,67 @@ def test_replica_router_spreads_requests_and_follows_aborts():
     assert router.route(AbortReq(rid="unknown")) == [0, 1, 2]
     assert router.route(FlushCacheReq()) == [0, 1, 2]
     assert router.route(None) == [0, 1, 2] and all(s.got[-1] is None for s in sinks)
+
+
+def test_image_request_takes_the_shared_memory_queue():
+    """``enable_shared_queue``: the tokenizer hands an image request's tensors to the scheduler through
+    the shared-memory queue (the socket carries only a notice); the answer equals the in-process engine's,
+    text requests still use the socket, and no shared-memory segment is left behind."""
+    import glob
+
+    import numpy as np
+
+    def cfg(shared):
+        return ServerConfig(model_path="preset:qwen3-vl-tiny", dtype="float32", max_running_requests=2,
+                            max_total_tokens=1024, context_length=512, log_level="warning", enable_shared_queue=shared)
+
+    img = np.random.default_rng(0).integers(0, 256, (64, 96, 3), dtype=np.uint8)
+    sp = {"max_new_tokens": 4, "temperature": 0.0}
+    ref = Engine(cfg(False), mode="inproc", device="cpu").launch()
+    want_img = ref.generate("describe", sp, image_data=img)["output_ids"]
+    want_txt = ref.generate("hello there", sp)["output_ids"]
+    ref.shutdown()
+    eng = Engine(cfg(True), mode="multiproc", device="cpu").launch()
+    try:
+        assert eng._tensor_queues is not None and len(eng._tensor_queues) == 1
+        assert eng.generate("describe", sp, image_data=img, timeout=180)["output_ids"] == want_img
+        assert eng.generate("hello there", sp, timeout=120)["output_ids"] == want_txt
+        assert eng.generate("describe", sp, image_data=img, timeout=180)["output_ids"] == want_img
+    finally:
+        eng.shutdown()
+    assert not glob.glob("/dev/shm/mllm_b200_meta_*")
+
+
+def test_router_sends_tensor_requests_through_the_shared_queue():
+    from mllm_b200.engine.io_struct import SharedQueueNotice, TokenizedGenerateReqInput
+    from mllm_b200.orchestrator.scheduler_process import _take_from_shared_queue
+    from mllm_b200.orchestrator.tokenizer_process import ReplicaRouter
+
+    class Sink:
+        def __init__(self):
+            self.got = []
+
+        def send_pyobj(self, m):
+            self.got.append(m)
+
+    class FakeQueue:
+        def __init__(self):
+            self.items = []
+
+        def put(self, rid, meta, mm):
+            self.items.append((rid, meta, mm))
+
+        def get(self, timeout=None):
+            return self.items.pop(0)
+
+    sink, q = Sink(), FakeQueue()
+    router = ReplicaRouter([sink], [q])
+    mk = lambda rid, mm: TokenizedGenerateReqInput(rid=rid, input_text="", input_ids=[1, 2, 3], mm_inputs=mm,
+                                                   sampling_params={}, stream=False, return_logprob=False, created_time=0.0)
+    router.route(mk("text", None))
+    router.route(mk("img", {"pixel_values": [1.0, 2.0]}))
+    assert isinstance(sink.got[0], TokenizedGenerateReqInput) and isinstance(sink.got[1], SharedQueueNotice)
+    assert len(q.items) == 1 and q.items[0][1].mm_inputs is None      # the body on the queue, tensors beside it
+    back = _take_from_shared_queue(q, sink.got[1])
+    assert back.rid == "img" and back.mm_inputs == {"pixel_values": [1.0, 2.0]} and back.input_ids == [1, 2, 3]
+    assert "error" in _take_from_shared_queue(None, sink.got[1])
