@@ -41,8 +41,8 @@ EXTENSIONS: Dict[str, Dict[str, List[str]]] = {
         "cuda": True,
     },
     "mllm_b200_host": {
-        "sources": ["host/host_bindings.cpp", "host/radix_tree.cpp", "host/page_allocator.cpp", "host/mllm_file.cpp", "host/cpu_oracle.cpp"],
-        "headers": ["host/radix_tree.h", "host/page_allocator.h", "host/mllm_file.h", "host/cpu_oracle.h"],
+        "sources": ["host/host_bindings.cpp", "host/radix_tree.cpp", "host/page_allocator.cpp", "host/mllm_file.cpp", "host/cpu_oracle.cpp", "host/symm_heap.cpp"],
+        "headers": ["host/radix_tree.h", "host/page_allocator.h", "host/mllm_file.h", "host/cpu_oracle.h", "host/symm_heap.h"],
         "cuda": False,
     },
 }

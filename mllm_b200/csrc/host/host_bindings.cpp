@@ -11,6 +11,7 @@
 #include "host/mllm_file.h"
 #include "host/page_allocator.h"
 #include "host/radix_tree.h"
+#include "host/symm_heap.h"
 
 namespace py = pybind11;
 using namespace mb200host;
@@ -24,6 +25,17 @@ static py::array_t<int64_t> to_array(const std::vector<int64_t>& v) {
 }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  py::class_<SymmHeapAllocator>(m, "SymmHeapAllocator")
+      .def(py::init<int64_t, int64_t>(), py::arg("capacity"), py::arg("min_align") = 256)
+      .def("alloc", &SymmHeapAllocator::alloc, py::arg("bytes"), py::arg("align") = 0)
+      .def("free", &SymmHeapAllocator::free_block)
+      .def("reset", &SymmHeapAllocator::reset)
+      .def("block_size", &SymmHeapAllocator::block_size)
+      .def_property_readonly("capacity", &SymmHeapAllocator::capacity)
+      .def_property_readonly("used", &SymmHeapAllocator::used)
+      .def_property_readonly("largest_free", &SymmHeapAllocator::largest_free)
+      .def_property_readonly("num_blocks", &SymmHeapAllocator::num_blocks);
+
   py::class_<PageAllocator>(m, "PageAllocator")
       .def(py::init<int64_t, int>(), py::arg("num_slots"), py::arg("page_size") = 1)
       .def("clear", &PageAllocator::clear)

@@ -165,6 +165,14 @@ def tp_wait_gather(comm, epoch: int, rows: int) -> None:
         raise RuntimeError(f"mllm_b200 tp_wait_flags failed (code {rc})")
 
 
+def rs_inbox_targets(comm) -> list:
+    """Where this rank's partial sums go on every owner: the owner's inbox is ``[source rank][row][hidden]``,
+    so the target is the owner's inbox base plus this rank's slot."""
+    p = comm.prefill
+    slot_bytes = p.inbox.shape[1] * p.inbox.shape[2] * p.inbox.element_size()
+    return [ptr + comm.rank * slot_bytes for ptr in p.inbox_ptrs]
+
+
 def _gemm_tp(x2, weight, out, swiglu: bool, gate=None, rs=None) -> None:
     """Tensor-parallel prefill GEMM: ``gate`` = (flags, epoch) delays row tiles until they have been
     gathered; ``rs`` = (comm, epoch) sends output tiles to the owners' inboxes instead of ``out``."""
@@ -172,9 +180,7 @@ def _gemm_tp(x2, weight, out, swiglu: bool, gate=None, rs=None) -> None:
     if rs is not None:
         comm, epoch = rs
         p = comm.prefill
-        own_cap = p.inbox.shape[1]
-        slot_bytes = own_cap * p.inbox.shape[2] * p.inbox.element_size()
-        outs = [ptr + comm.rank * slot_bytes for ptr in p.inbox_ptrs]
+        outs = rs_inbox_targets(comm)
         rc = ext().gemm_tp(x2, weight, out, swiglu, gflags, gepoch, outs, p.tile_flag_ptrs, p.rs_count, comm.rank, epoch,
                            p.inbox.shape[2])
     else:

@@ -18,6 +18,10 @@ store the normalised rows into every rank's copy) and two blocks of epoch flags.
 the same sequence of fused calls, so a per-process call counter (``epoch``) is the expected flag
 value on every rank.
 
+All of these live in one :class:`SymmetricHeap`: a single peer-mapped allocation per rank (one
+rendezvous), carved up by a deterministic host-side offset allocator (C++), so a buffer's address on
+rank ``r`` is that rank's heap base plus the same offset.
+
 When symmetric memory is not available (CPU / gloo ranks, a single GPU) ``TPComm.create``
 returns ``None`` and callers use the collective of the process group instead.
 """
@@ -35,6 +39,67 @@ from . import state as pstate
 
 logger = logging.getLogger(__name__)
 _FLAG_STRIDE = 8
+_HEAP_ALIGN = 256
+
+
+class SymmetricHeap:
+    """One byte buffer per rank, mapped into every peer, plus the offset allocator that carves it.
+
+    Every rank must make the same ``tensor`` / ``free`` calls in the same order (the allocator is
+    deterministic), which gives every buffer the same offset on every rank."""
+
+    def __init__(self, buf: torch.Tensor, base_ptrs: List[int]) -> None:
+        from ..mem_cache.native import host_ext
+
+        assert buf.dtype == torch.uint8 and buf.dim() == 1
+        self.buf = buf
+        self.base_ptrs = [int(p) for p in base_ptrs]
+        self.alloc = host_ext().SymmHeapAllocator(int(buf.numel()), _HEAP_ALIGN)
+        self._offsets = {}
+
+    @classmethod
+    def create(cls, nbytes: int, device: torch.device, group) -> "SymmetricHeap":
+        """Collective over ``group``: allocates, zeroes and exchanges the mappings once."""
+        import torch.distributed._symmetric_memory as symm
+
+        buf = symm.empty((int(nbytes),), dtype=torch.uint8, device=device)
+        buf.zero_()
+        handle = symm.rendezvous(buf, group)
+        return cls(buf, [int(p) for p in handle.buffer_ptrs])
+
+    @classmethod
+    def local(cls, nbytes: int, world: int = 1, device="cpu") -> "SymmetricHeap":
+        """A heap without peers (tests, single rank): every "peer" base is the local buffer."""
+        buf = torch.zeros(int(nbytes), dtype=torch.uint8, device=device)
+        return cls(buf, [buf.data_ptr()] * world)
+
+    @staticmethod
+    def bytes_for(shapes_dtypes) -> int:
+        """Capacity that fits the given ``(shape, dtype)`` buffers, each rounded to the heap alignment."""
+        total = 0
+        for shape, dtype in shapes_dtypes:
+            n = torch.empty((), dtype=dtype).element_size()
+            for d in shape:
+                n *= int(d)
+            total += (n + _HEAP_ALIGN - 1) // _HEAP_ALIGN * _HEAP_ALIGN
+        return total
+
+    def tensor(self, shape, dtype: torch.dtype):
+        """A zero-copy view of a fresh block, and its address on every rank."""
+        n = torch.empty((), dtype=dtype).element_size()
+        for d in shape:
+            n *= int(d)
+        off = int(self.alloc.alloc(n))
+        if off < 0:
+            raise MemoryError(f"symmetric heap: no room for {n} bytes ({self.alloc.used} of {self.alloc.capacity} used)")
+        t = self.buf[off:off + n].view(dtype).view(*shape)
+        self._offsets[t.data_ptr()] = off
+        return t, [b + off for b in self.base_ptrs]
+
+    def free(self, t: torch.Tensor) -> None:
+        off = self._offsets.pop(t.data_ptr(), None)
+        if off is None or not self.alloc.free(off):
+            raise ValueError("tensor does not start a block of this heap")
 
 
 @dataclass
@@ -91,6 +156,45 @@ class TPComm:
         self.epoch += 1
         return self.epoch
 
+    @staticmethod
+    def _plan(hidden: int, dtype: torch.dtype, tp: int, max_rows: int, prefill_rows: int):
+        """Shapes of the shared buffers in allocation order, plus (rows_cap, rows per owner)."""
+        i32 = torch.int32
+        plan = [((max_rows, hidden), dtype), ((max_rows * _FLAG_STRIDE,), i32)] * 2
+        cap = own = 0
+        if prefill_rows > 0:
+            cap = (prefill_rows + 128 * tp - 1) // (128 * tp) * (128 * tp)
+            own = cap // tp
+            plan += [((tp, own, hidden), dtype), ((own // 128 * _FLAG_STRIDE,), i32), ((cap, hidden), dtype),
+                     ((cap // 128,), i32)]
+        return plan, cap, own
+
+    @classmethod
+    def heap_bytes(cls, hidden: int, dtype: torch.dtype, tp: int, max_rows: int = 256, prefill_rows: int = 0) -> int:
+        return SymmetricHeap.bytes_for(cls._plan(hidden, dtype, tp, max_rows, prefill_rows)[0])
+
+    @classmethod
+    def from_heap(cls, heap: SymmetricHeap, hidden: int, dtype: torch.dtype, device, rank: int, tp: int,
+                  max_rows: int = 256, prefill_rows: int = 0) -> "TPComm":
+        """Carves the buffers out of a (zeroed) heap; every rank calls this with the same arguments."""
+        i32 = torch.int32
+        plan, cap, own = cls._plan(hidden, dtype, tp, max_rows, prefill_rows)
+        cut = [heap.tensor(shape, dt) for shape, dt in plan]
+        slots = [_Slot(data=cut[2 * i][0], flags=cut[2 * i + 1][0], seq=torch.zeros(max_rows, dtype=i32, device=device),
+                       data_ptrs=cut[2 * i][1], flag_ptrs=cut[2 * i + 1][1]) for i in range(2)]
+        prefill = None
+        if prefill_rows > 0:
+            (inbox, inbox_ptrs), (tile_flags, tile_flag_ptrs), (hidden_full, hidden_ptrs), (gather_flags, gather_flag_ptrs) = cut[4:8]
+            prefill = PrefillBuffers(
+                rows_cap=cap, inbox=inbox, tile_flags=tile_flags, hidden_full=hidden_full, gather_flags=gather_flags,
+                rs_count=torch.zeros(cap // 128, dtype=i32, device=device),
+                ag_count=torch.zeros(own // 128, dtype=i32, device=device),
+                inbox_ptrs=inbox_ptrs, tile_flag_ptrs=tile_flag_ptrs, hidden_ptrs=hidden_ptrs,
+                gather_flag_ptrs=gather_flag_ptrs)
+        comm = cls(slots, max_rows, hidden, dtype, rank, tp, prefill)
+        comm.heap = heap
+        return comm
+
     @classmethod
     def create(cls, hidden: int, dtype: torch.dtype, device: torch.device, max_rows: int = 256,
                prefill_rows: int = 0) -> Optional["TPComm"]:
@@ -98,41 +202,12 @@ class TPComm:
         if group.world_size == 1 or device.type != "cuda" or not dist.is_initialized():
             return None
         try:
-            import torch.distributed._symmetric_memory as symm
-
-            slots = []
-            for _ in range(2):
-                data = symm.empty((max_rows, hidden), dtype=dtype, device=device)
-                flags = symm.empty((max_rows * _FLAG_STRIDE,), dtype=torch.int32, device=device)
-                data.zero_()
-                flags.zero_()
-                hd = symm.rendezvous(data, group.group)
-                hf = symm.rendezvous(flags, group.group)
-                slots.append(_Slot(data=data, flags=flags, seq=torch.zeros(max_rows, dtype=torch.int32, device=device),
-                                   data_ptrs=[int(p) for p in hd.buffer_ptrs], flag_ptrs=[int(p) for p in hf.buffer_ptrs]))
-            prefill = None
             tp = group.world_size
-            if prefill_rows > 0:
-                cap = (prefill_rows + 128 * tp - 1) // (128 * tp) * (128 * tp)
-                own = cap // tp
-                inbox = symm.empty((tp, own, hidden), dtype=dtype, device=device)
-                tile_flags = symm.empty((own // 128 * _FLAG_STRIDE,), dtype=torch.int32, device=device)
-                hidden_full = symm.empty((cap, hidden), dtype=dtype, device=device)
-                gather_flags = symm.empty((cap // 128,), dtype=torch.int32, device=device)
-                for t in (inbox, tile_flags, hidden_full, gather_flags):
-                    t.zero_()
-                handles = [symm.rendezvous(t, group.group) for t in (inbox, tile_flags, hidden_full, gather_flags)]
-                prefill = PrefillBuffers(
-                    rows_cap=cap, inbox=inbox, tile_flags=tile_flags, hidden_full=hidden_full, gather_flags=gather_flags,
-                    rs_count=torch.zeros(cap // 128, dtype=torch.int32, device=device),
-                    ag_count=torch.zeros(own // 128, dtype=torch.int32, device=device),
-                    inbox_ptrs=[int(p) for p in handles[0].buffer_ptrs],
-                    tile_flag_ptrs=[int(p) for p in handles[1].buffer_ptrs],
-                    hidden_ptrs=[int(p) for p in handles[2].buffer_ptrs],
-                    gather_flag_ptrs=[int(p) for p in handles[3].buffer_ptrs])
+            heap = SymmetricHeap.create(cls.heap_bytes(hidden, dtype, tp, max_rows, prefill_rows), device, group.group)
+            comm = cls.from_heap(heap, hidden, dtype, device, group.rank_in_group, tp, max_rows, prefill_rows)
             torch.cuda.synchronize(device)
             group.barrier()
-            return cls(slots, max_rows, hidden, dtype, group.rank_in_group, group.world_size, prefill)
+            return comm
         except Exception as exc:  # symmetric memory unsupported on this system
             logger.warning("symmetric memory unavailable (%s); tensor-parallel layers use NCCL collectives", exc)
             return None

@@ -329,3 +329,57 @@ def test_quantizer_and_inspector_tools(tmp_path, capsys):
     insp.main([str(tmp_path / "q4_0.mllm"), "--filter", "down_proj"])
     out = capsys.readouterr().out
     assert "gguf_q4_0" in out and "down_proj" in out and "embed_tokens" not in out
+
+
+def test_symmetric_heap_allocator_and_views():
+    """Offset allocator of the symmetric heap (C++): deterministic first fit, alignment, coalescing;
+    and the Python heap on top of it: typed views at the allocator's offsets, the same offset added to
+    every rank's base."""
+    import random
+
+    from mllm_b200.parallel.symm import SymmetricHeap
+
+    A = host_ext().SymmHeapAllocator(1 << 20, 256)
+    a, b, c = A.alloc(1000), A.alloc(5000, 4096), A.alloc(100)
+    assert (a, b, c) == (0, 4096, 1024) and A.used == 1024 + 5120 + 256 and A.num_blocks == 3
+    assert A.free(b) and not A.free(b) and not A.free(12345)
+    assert A.free(a) and A.free(c) and A.used == 0 and A.largest_free == 1 << 20     # everything merged back
+    assert A.alloc(0) == -1 and A.alloc((1 << 20) + 1) == -1
+    # two allocators fed the same calls agree (what makes offsets symmetric across ranks); blocks never overlap
+    rng = random.Random(0)
+    X, Y = host_ext().SymmHeapAllocator(1 << 16, 64), host_ext().SymmHeapAllocator(1 << 16, 64)
+    live = {}
+    for _ in range(2000):
+        if live and rng.random() < 0.45:
+            off = rng.choice(list(live))
+            assert X.free(off) and Y.free(off)
+            del live[off]
+        else:
+            n, al = rng.randrange(1, 3000), rng.choice([0, 64, 256, 1024])
+            ox, oy = X.alloc(n, al), Y.alloc(n, al)
+            assert ox == oy
+            if ox >= 0:
+                assert ox % max(al, 64) == 0 and X.block_size(ox) >= n
+                for o, ln in live.items():
+                    assert ox + X.block_size(ox) <= o or o + ln <= ox
+                live[ox] = X.block_size(ox)
+        assert X.used == sum(live.values())
+    # the heap: exact capacity planning, typed views, peer addresses
+    plan = [((5, 64), torch.bfloat16), ((40,), torch.int32), ((2, 3, 64), torch.bfloat16), ((7,), torch.int32)]
+    heap = SymmetricHeap.local(SymmetricHeap.bytes_for(plan), world=3)
+    heap.base_ptrs = [1 << 40, 2 << 40, 3 << 40]
+    views = [heap.tensor(shape, dt) for shape, dt in plan]
+    assert heap.alloc.used == heap.alloc.capacity
+    offs = [p[0] - (1 << 40) for _, p in views]
+    assert offs == sorted(offs) and all(o % 256 == 0 for o in offs)
+    for (t, ptrs), (shape, dt) in zip(views, plan):
+        assert tuple(t.shape) == tuple(shape) and t.dtype == dt and t.is_contiguous()
+        assert t.data_ptr() - heap.buf.data_ptr() == ptrs[0] - (1 << 40) == ptrs[2] - (3 << 40)
+    views[0][0].fill_(1.5)
+    views[1][0].fill_(7)
+    assert float(views[0][0].sum()) == 1.5 * 320 and int(views[1][0].sum()) == 280 and int(views[3][0].sum()) == 0
+    with pytest.raises(MemoryError):
+        heap.tensor((1,), torch.int32)
+    heap.free(views[1][0])
+    t, _ = heap.tensor((8,), torch.int32)
+    assert t.data_ptr() == views[1][0].data_ptr()
