@@ -24,37 +24,66 @@ from ..parallel import state as pstate
 class GatedDeltaNet(nn.Module):
     def __init__(self, config, layer_id: int, gdn_index: int, params_dtype=None, prefix: str = "") -> None:
         super().__init__()
-        if pstate.get_tensor_model_parallel_world_size() != 1:
-            raise NotImplementedError("gated delta net layers are not tensor-parallel in this build")
         dt = params_dtype or torch.get_default_dtype()
         H = config.hidden_size
         self.layer_id, self.gdn_index = layer_id, gdn_index
-        self.num_v_heads, self.num_k_heads = config.linear_num_value_heads, config.linear_num_key_heads
+        # tensor parallelism: every rank owns num_heads / tp value heads with their key heads (the
+        # recurrent state, the convolution channels and the gates are per head, so nothing is exchanged
+        # until the row-parallel output projection, whose partial sums are all-reduced)
+        self.tp, self.tp_rank = pstate.get_tensor_model_parallel_world_size(), pstate.get_tensor_model_parallel_rank()
+        hv, hk = config.linear_num_value_heads, config.linear_num_key_heads
+        if hv % self.tp or hk % self.tp:
+            raise ValueError(f"gated delta net: {hk} key / {hv} value heads do not divide over {self.tp} ranks")
+        self.total_k_heads, self.total_v_heads = hk, hv
+        self.num_v_heads, self.num_k_heads = hv // self.tp, hk // self.tp
         self.head_k_dim, self.head_v_dim = config.linear_key_head_dim, config.linear_value_head_dim
         self.key_dim, self.value_dim = self.head_k_dim * self.num_k_heads, self.head_v_dim * self.num_v_heads
         self.conv_dim = 2 * self.key_dim + self.value_dim
         self.conv_kernel = config.linear_conv_kernel_dim
         self.eps = getattr(config, "rms_norm_eps", 1e-6)
 
-        def w(*shape):
-            return nn.Parameter(torch.empty(*shape, dtype=dt), requires_grad=False)
+        def w(*shape, loader=None, dtype=dt, init=None):
+            t = torch.empty(*shape, dtype=dtype) if init is None else torch.full(shape, init, dtype=dtype)
+            p = nn.Parameter(t, requires_grad=False)
+            if loader is not None:
+                p.weight_loader = loader
+            return p
 
         self.in_proj_qkv = nn.Module()
-        self.in_proj_qkv.weight = w(self.conv_dim, H)
+        self.in_proj_qkv.weight = w(self.conv_dim, H, loader=self._load_qkv_rows)
         self.in_proj_z = nn.Module()
-        self.in_proj_z.weight = w(self.value_dim, H)
+        self.in_proj_z.weight = w(self.value_dim, H, loader=self._load_v_rows)
         self.in_proj_b = nn.Module()
-        self.in_proj_b.weight = w(self.num_v_heads, H)
+        self.in_proj_b.weight = w(self.num_v_heads, H, loader=self._load_v_rows)
         self.in_proj_a = nn.Module()
-        self.in_proj_a.weight = w(self.num_v_heads, H)
+        self.in_proj_a.weight = w(self.num_v_heads, H, loader=self._load_v_rows)
         self.conv1d = nn.Module()
-        self.conv1d.weight = w(self.conv_dim, self.conv_kernel)
-        self.dt_bias = nn.Parameter(torch.ones(self.num_v_heads, dtype=torch.float32), requires_grad=False)
-        self.A_log = nn.Parameter(torch.zeros(self.num_v_heads, dtype=torch.float32), requires_grad=False)
+        self.conv1d.weight = w(self.conv_dim, self.conv_kernel, loader=self._load_qkv_rows)
+        self.dt_bias = w(self.num_v_heads, loader=self._load_v_rows, dtype=torch.float32, init=1.0)
+        self.A_log = w(self.num_v_heads, loader=self._load_v_rows, dtype=torch.float32, init=0.0)
         self.norm = nn.Module()
         self.norm.weight = nn.Parameter(torch.ones(self.head_v_dim, dtype=dt), requires_grad=False)
         self.out_proj = nn.Module()
-        self.out_proj.weight = w(H, self.value_dim)
+        self.out_proj.weight = w(H, self.value_dim, loader=self._load_v_cols)
+
+    # ---- loading: slices of the full (unsharded) checkpoint tensors ----
+    def _load_qkv_rows(self, param, full, shard_id=None) -> None:
+        """Rows are [q heads | k heads | v heads]; take this rank's heads of each block (also the layout
+        of the convolution channels, whose checkpoint shape is [C, 1, K])."""
+        full = full.reshape(full.shape[0], -1)
+        kd, vd = self.head_k_dim * self.total_k_heads, self.head_v_dim * self.total_v_heads
+        q, k, v = full[:kd], full[kd:2 * kd], full[2 * kd:2 * kd + vd]
+        r = self.tp_rank
+        param.data.copy_(torch.cat([q[r * self.key_dim:(r + 1) * self.key_dim], k[r * self.key_dim:(r + 1) * self.key_dim],
+                                    v[r * self.value_dim:(r + 1) * self.value_dim]], 0).reshape(param.shape))
+
+    def _load_v_rows(self, param, full, shard_id=None) -> None:
+        n = param.shape[0]
+        param.data.copy_(full[self.tp_rank * n:(self.tp_rank + 1) * n].reshape(param.shape))
+
+    def _load_v_cols(self, param, full, shard_id=None) -> None:
+        n = param.shape[1]
+        param.data.copy_(full[:, self.tp_rank * n:(self.tp_rank + 1) * n])
 
     def forward(self, x: torch.Tensor, fb) -> torch.Tensor:
         pool = fb.extra["gdn_pool"]
@@ -88,7 +117,8 @@ class GatedDeltaNet(nn.Module):
         g = -torch.exp(self.A_log.float()) * torch.nn.functional.softplus(a.float() + self.dt_bias.float())
         o = ops.gated_delta_rule(q, k, v, g, beta, recurrent, slots, lens, has, q_start)
         o = ops.rmsnorm_gated(o.reshape(-1, self.head_v_dim), z.reshape(-1, self.head_v_dim), self.norm.weight, self.eps)
-        return ops.linear(o.reshape(T, self.value_dim), self.out_proj.weight)
+        y = ops.linear(o.reshape(T, self.value_dim), self.out_proj.weight)
+        return pstate.tensor_model_parallel_all_reduce(y) if self.tp > 1 else y
 
     def fuse_small_projections(self) -> None:
         """One GEMM for the beta / decay projections (call after loading)."""

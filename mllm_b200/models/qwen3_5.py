@@ -26,6 +26,7 @@ from ..layers import MLP, GemmaRMSNorm, VocabParallelEmbedding
 from ..layers.gdn import GatedDeltaNet
 from ..mem_cache import GDNPool
 from ..ops import reference as ref
+from ..parallel import state as pstate
 from .qwen3 import LogitsProcessorOutput
 
 
@@ -39,7 +40,15 @@ class Qwen3_5Attention(nn.Module):
         super().__init__()
         dt = params_dtype or torch.get_default_dtype()
         self.layer_id = layer_id
-        self.num_heads, self.num_kv_heads = config.num_attention_heads, config.num_key_value_heads
+        # tensor parallelism: query heads are split over the ranks; KV heads too, or replicated when there
+        # are fewer of them than ranks; the output projection is row-parallel (all-reduce of partial sums)
+        self.tp, self.tp_rank = pstate.get_tensor_model_parallel_world_size(), pstate.get_tensor_model_parallel_rank()
+        hq, hkv = config.num_attention_heads, config.num_key_value_heads
+        if hq % self.tp or (hkv % self.tp and self.tp % hkv):
+            raise ValueError(f"attention: {hq} query / {hkv} KV heads do not divide over {self.tp} ranks")
+        self.total_heads, self.total_kv_heads = hq, hkv
+        self.num_heads, self.num_kv_heads = hq // self.tp, max(1, hkv // self.tp)
+        self.kv_head_start = (self.tp_rank * hkv) // self.tp
         self.head_dim = getattr(config, "head_dim", None) or config.hidden_size // config.num_attention_heads
         H = config.hidden_size
         rp = _rope_params(config)
@@ -47,16 +56,22 @@ class Qwen3_5Attention(nn.Module):
         self.rotary_dim = int(self.head_dim * float(rp.get("partial_rotary_factor", getattr(config, "partial_rotary_factor", 1.0))))
         self.mrope_section = rp.get("mrope_section", [11, 11, 10])
         eps = getattr(config, "rms_norm_eps", 1e-6)
+        D = self.head_dim
 
-        def lin(o, i):
+        def lin(o, i, loader):
             m = nn.Module()
             m.weight = nn.Parameter(torch.empty(o, i, dtype=dt), requires_grad=False)
+            m.weight.weight_loader = loader
             return m
 
-        self.q_proj = lin(self.num_heads * self.head_dim * 2, H)   # per head: [query(D) | gate(D)]
-        self.k_proj = lin(self.num_kv_heads * self.head_dim, H)
-        self.v_proj = lin(self.num_kv_heads * self.head_dim, H)
-        self.o_proj = lin(H, self.num_heads * self.head_dim)
+        def rows(start, count):
+            return lambda p, full, shard_id=None: p.data.copy_(full[start:start + count])
+
+        self.q_proj = lin(self.num_heads * D * 2, H, rows(self.tp_rank * self.num_heads * 2 * D, self.num_heads * 2 * D))  # per head: [query(D) | gate(D)]
+        self.k_proj = lin(self.num_kv_heads * D, H, rows(self.kv_head_start * D, self.num_kv_heads * D))
+        self.v_proj = lin(self.num_kv_heads * D, H, rows(self.kv_head_start * D, self.num_kv_heads * D))
+        c0, cn = self.tp_rank * self.num_heads * D, self.num_heads * D
+        self.o_proj = lin(H, self.num_heads * D, lambda p, full, shard_id=None: p.data.copy_(full[:, c0:c0 + cn]))
         self.q_norm = GemmaRMSNorm(self.head_dim, eps, dt)
         self.k_norm = GemmaRMSNorm(self.head_dim, eps, dt)
         self.scale = self.head_dim ** -0.5
@@ -104,7 +119,8 @@ class Qwen3_5Attention(nn.Module):
                 o = ref.attention_prefill(q, kc, vc, rtt, fb.req_pool_indices, fb.seq_lens, fb.extend_prefix_lens,
                                           fb.extend_start_loc, self.scale)
         o = o.reshape(T, self.num_heads * D) * torch.sigmoid(gate.float()).to(x.dtype)
-        return ops.linear(o, self.o_proj.weight)
+        y = ops.linear(o, self.o_proj.weight)
+        return pstate.tensor_model_parallel_all_reduce(y) if self.tp > 1 else y
 
 
 class Qwen3_5DecoderLayer(nn.Module):
@@ -176,12 +192,13 @@ class Qwen3_5ForCausalLM(nn.Module):
         self._gdn_pool: Optional[GDNPool] = None
 
     def make_gdn_pool(self, slots: int, track_slots: int = 0) -> GDNPool:
-        """State rows for ``slots`` requests plus ``track_slots`` snapshot rows for the prefix cache."""
+        """State rows for ``slots`` requests plus ``track_slots`` snapshot rows for the prefix cache
+        (this rank's heads only under tensor parallelism)."""
         c = self.config
         w = self.model.embed_tokens.weight
-        conv_dim = 2 * c.linear_key_head_dim * c.linear_num_key_heads + c.linear_value_head_dim * c.linear_num_value_heads
-        self._gdn_pool = GDNPool(self.model.num_gdn_layers, slots, c.linear_num_value_heads, c.linear_key_head_dim,
-                                 c.linear_value_head_dim, conv_dim, c.linear_conv_kernel_dim, w.device, w.dtype,
+        gdn = next(m for m in self.modules() if isinstance(m, GatedDeltaNet))
+        self._gdn_pool = GDNPool(self.model.num_gdn_layers, slots, gdn.num_v_heads, c.linear_key_head_dim,
+                                 c.linear_value_head_dim, gdn.conv_dim, c.linear_conv_kernel_dim, w.device, w.dtype,
                                  track_slots=track_slots)
         return self._gdn_pool
 
@@ -241,10 +258,8 @@ class Qwen3_5ForCausalLM(nn.Module):
                 continue
             if name.endswith(self._OFFSET_NORMS) or name == "model.norm.weight":
                 p.data.copy_((t.float() + 1.0).to(p.dtype))          # zero-centred gain: store 1 + w
-            elif name.endswith("conv1d.weight"):
-                p.data.copy_(t.reshape(p.shape))                      # [C, 1, K] -> [C, K]
             elif hasattr(p, "weight_loader"):
-                p.weight_loader(p, t)
+                p.weight_loader(p, t)                                 # sharded / reshaped by the layer
             else:
                 p.data.copy_(t.reshape(p.shape))
             loaded.add(target)

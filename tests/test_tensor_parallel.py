@@ -58,6 +58,18 @@ def test_tp2_fused_prefill_matches_nccl_on_gpu(tmp_path):
     assert (fused.argmax(-1) == ref.argmax(-1)).float().mean().item() > 0.8
 
 
+@pytest.mark.parametrize("kv_heads", ["2", "1"])
+def test_hybrid_tp2_matches_single_rank_on_cpu(tmp_path, kv_heads):
+    """Qwen3.5-style hybrid model on two gloo ranks: gated-delta-net heads (projections, convolution
+    channels, gates, recurrent state) and attention heads split over the ranks, KV heads split or, when
+    there is only one, replicated; prefill (chunk-parallel delta rule) and decode logits equal the
+    single-rank model's."""
+    env = {"TP_TEST_PRESET": "qwen3.5-tiny", "TP_TEST_KV_HEADS": kv_heads, "TP_TEST_PREFILL_LEN": "21"}
+    one = _launch(1, str(tmp_path / "h1.pt"), "cpu", "float32", 29631, env)
+    two = _launch(2, str(tmp_path / "h2.pt"), "cpu", "float32", 29632 + int(kv_heads), env)
+    torch.testing.assert_close(two, one, atol=3e-4, rtol=3e-4)
+
+
 @pytest.mark.parametrize("ep", ["0", "1"])
 def test_moe_tp2_and_ep2_match_single_rank_on_cpu(tmp_path, ep):
     """Qwen3-MoE on two gloo ranks: experts sharded along their width (tensor parallel) or split between

@@ -46,6 +46,37 @@ def full_state_dict(cfg, seed=0, dtype=torch.float32):
     return sd
 
 
+def hybrid_state_dict(cfg, seed=0, dtype=torch.float32):
+    """Full (unsharded) weights of a Qwen3.5-style hybrid model under their checkpoint names."""
+    g = torch.Generator().manual_seed(seed)
+    H, D, I, V = cfg.hidden_size, cfg.head_dim, cfg.intermediate_size, cfg.vocab_size
+    hq, hkv = cfg.num_attention_heads, cfg.num_key_value_heads
+    kd = cfg.linear_key_head_dim * cfg.linear_num_key_heads
+    vd = cfg.linear_value_head_dim * cfg.linear_num_value_heads
+    hv, K = cfg.linear_num_value_heads, cfg.linear_conv_kernel_dim
+
+    def r(*shape, s=0.05):
+        return (torch.randn(*shape, generator=g) * s).to(dtype)
+
+    sd = {"model.embed_tokens.weight": r(V, H), "lm_head.weight": r(V, H), "model.norm.weight": r(H)}
+    for i, kind in enumerate(cfg.layer_types):
+        p = f"model.layers.{i}."
+        sd.update({p + "input_layernorm.weight": r(H), p + "post_attention_layernorm.weight": r(H),
+                   p + "mlp.gate_proj.weight": r(I, H), p + "mlp.up_proj.weight": r(I, H), p + "mlp.down_proj.weight": r(H, I)})
+        if kind == "linear_attention":
+            a = p + "linear_attn."
+            sd.update({a + "in_proj_qkv.weight": r(2 * kd + vd, H), a + "in_proj_z.weight": r(vd, H),
+                       a + "in_proj_b.weight": r(hv, H), a + "in_proj_a.weight": r(hv, H),
+                       a + "conv1d.weight": r(2 * kd + vd, 1, K, s=0.3), a + "dt_bias": r(hv, s=0.5).float(),
+                       a + "A_log": r(hv, s=0.5).float(), a + "norm.weight": torch.ones(cfg.linear_value_head_dim, dtype=dtype) + r(cfg.linear_value_head_dim),
+                       a + "out_proj.weight": r(H, vd)})
+        else:
+            a = p + "self_attn."
+            sd.update({a + "q_proj.weight": r(hq * D * 2, H), a + "k_proj.weight": r(hkv * D, H), a + "v_proj.weight": r(hkv * D, H),
+                       a + "o_proj.weight": r(H, hq * D), a + "q_norm.weight": r(D), a + "k_norm.weight": r(D)})
+    return sd
+
+
 def run(out_path: str, device: str, dtype_name: str) -> None:
     from mllm_b200.configs import ServerConfig
     from mllm_b200.executor import ModelRunner
@@ -59,7 +90,12 @@ def run(out_path: str, device: str, dtype_name: str) -> None:
         pstate.initialize_model_parallel(tp_size=world, ep_size=world if os.environ.get("TP_TEST_EP") == "1" else 1)
     dev = device if device == "cpu" else f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}"
     preset = os.environ.get("TP_TEST_PRESET", "qwen3-tiny")
-    cfg = get_preset(preset, num_attention_heads=4, num_key_value_heads=2, tie_word_embeddings=False)
+    hybrid = preset.startswith("qwen3.5")
+    if hybrid:   # enough heads of every kind for two ranks; TP_TEST_KV_HEADS=1 exercises KV-head replication
+        cfg = get_preset(preset, num_attention_heads=4, num_key_value_heads=int(os.environ.get("TP_TEST_KV_HEADS", "2")),
+                         linear_num_key_heads=2, linear_num_value_heads=4, tie_word_embeddings=False)
+    else:
+        cfg = get_preset(preset, num_attention_heads=4, num_key_value_heads=2, tie_word_embeddings=False)
     L = int(os.environ.get("TP_TEST_PREFILL_LEN", "9"))
     sc = ServerConfig(model_path=f"preset:{preset}", dtype=dtype_name, max_running_requests=4,
                       max_total_tokens=max(1024, 4 * L), chunked_prefill_size=max(2048, 2 * L),
@@ -68,7 +104,7 @@ def run(out_path: str, device: str, dtype_name: str) -> None:
     mr = ModelRunner(sc, hf_config=cfg, device=dev)
     mr.initialize()
     dtype = mr.dtype
-    mr.model.load_weights(full_state_dict(cfg, dtype=dtype).items())
+    mr.model.load_weights((hybrid_state_dict if hybrid else full_state_dict)(cfg, dtype=dtype).items())
     for m in mr.model.modules():
         if hasattr(m, "quant_method"):
             m._gate_up_interleaved = False
