@@ -28,6 +28,7 @@ from ..mem_cache import GDNPool
 from ..ops import reference as ref
 from ..parallel import state as pstate
 from .qwen3 import LogitsProcessorOutput
+from .qwen3_vl import VisionLanguageMixin
 
 
 def _rope_params(config) -> dict:
@@ -276,7 +277,37 @@ class Qwen3_5ForCausalLM(nn.Module):
                 m.fuse_small_projections()
 
 
-EntryClass = Qwen3_5ForCausalLM
+class Qwen3_5ForConditionalGeneration(VisionLanguageMixin, Qwen3_5ForCausalLM):
+    """Vision-language variant: the Qwen3-VL style vision tower (no deepstack taps) in front of the hybrid
+    text model; image features replace the image-token rows of the input embeddings and the full-attention
+    layers rotate with 3-D (t, h, w) positions.  A checkpoint of this layout without a ``vision_config``
+    is served as text only (its vision tensors, if any, are skipped)."""
 
-# The multimodal checkpoint layout is accepted for text serving: vision tensors are skipped at load.
-Qwen3_5ForConditionalGeneration = Qwen3_5ForCausalLM
+    def __init__(self, config, quant_config=None, params_dtype: Optional[torch.dtype] = None) -> None:
+        tc = getattr(config, "text_config", config)
+        if not hasattr(tc, "tie_word_embeddings"):
+            tc.tie_word_embeddings = bool(getattr(config, "tie_word_embeddings", False))
+        Qwen3_5ForCausalLM.__init__(self, config, quant_config, params_dtype)
+        self.hidden_size = tc.hidden_size
+        self.has_vision = getattr(config, "vision_config", None) is not None and getattr(config, "image_token_id", None) is not None
+        if self.has_vision:
+            self._init_vision(config, params_dtype or torch.get_default_dtype())
+        self.uses_mrope = self.has_vision
+
+    def forward(self, input_ids, positions, forward_batch: ForwardBatch, input_embeds=None) -> LogitsProcessorOutput:
+        fb = forward_batch
+        if self.has_vision:
+            self._set_mrope_positions(input_ids, fb)
+            embeds, _ = self._vision_embeds(input_ids, fb)
+            if embeds is not None:
+                input_embeds = embeds
+        return Qwen3_5ForCausalLM.forward(self, input_ids, positions, fb, input_embeds)
+
+    def load_weights(self, weights: Iterable[Tuple[str, torch.Tensor]]) -> set:
+        if not self.has_vision:
+            return Qwen3_5ForCausalLM.load_weights(self, weights)
+        loaded, rest = self._load_visual(weights)
+        return loaded | Qwen3_5ForCausalLM.load_weights(self, rest)
+
+
+EntryClass = Qwen3_5ForCausalLM

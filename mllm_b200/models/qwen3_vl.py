@@ -231,29 +231,84 @@ def get_rope_index(input_ids: torch.Tensor, image_grid_thw, image_token_id: int,
     return torch.from_numpy(pos).to(input_ids.device), cur - start - T
 
 
-class Qwen3VLForConditionalGeneration(Qwen3ForCausalLM):
+class VisionLanguageMixin:
+    """What the vision-language variants share on top of their text model: 3-D rope positions of a
+    prompt with image blocks, and image features written over the image-token rows of the input
+    embeddings.  The host class provides ``visual``, ``image_token_id``, ``vision_start_token_id``,
+    ``spatial_merge_size``, ``hidden_size``, ``num_deepstack`` and ``model.embed_tokens``."""
+
     uses_mrope = True
 
-    def __init__(self, config, quant_config=None, params_dtype: Optional[torch.dtype] = None) -> None:
-        tc = _text_config(config)
-        rs = getattr(tc, "rope_scaling", None) or getattr(tc, "rope_parameters", None) or {}
-        if not isinstance(rs, dict):
-            rs = vars(rs)
-        sections = rs.get("mrope_section", [24, 20, 20])
-        interleaved = bool(rs.get("mrope_interleaved", True))
-        if not hasattr(tc, "tie_word_embeddings"):
-            tc.tie_word_embeddings = bool(getattr(config, "tie_word_embeddings", False))
-        super().__init__(tc, quant_config, params_dtype, mrope_sections=sections, mrope_interleaved=interleaved)
+    def _init_vision(self, config, dtype) -> None:
         self.full_config = config
-        dt = params_dtype or torch.get_default_dtype()
-        self.visual = Qwen3VLVisionModel(config.vision_config, dt)
+        self.visual = Qwen3VLVisionModel(config.vision_config, dtype)
         self.image_token_id = config.image_token_id
         self.vision_start_token_id = config.vision_start_token_id
         self.spatial_merge_size = getattr(config.vision_config, "spatial_merge_size", 2)
         self.num_deepstack = len(self.visual.deepstack_visual_indexes)
-        self.hidden_size = tc.hidden_size
 
-    # ------------------------------------------------------------------ forward
+    def _set_mrope_positions(self, input_ids, fb: ForwardBatch) -> None:
+        if fb.forward_mode.is_extend():
+            fb.mrope_positions = self._extend_positions(input_ids, fb)
+        elif fb.mrope_positions is None:
+            pos = fb.positions if fb.mrope_position_deltas is None else fb.positions + fb.mrope_position_deltas
+            fb.mrope_positions = pos.unsqueeze(0).expand(3, -1).contiguous()
+
+    def _vision_embeds(self, input_ids, fb: ForwardBatch):
+        """(input embeddings with the image features in place, per-level deepstack embeddings) — or
+        (None, None) when the batch carries no image."""
+        if fb.pixel_values is None or fb.image_grid_thw is None or fb.forward_mode.is_decode():
+            return None, None
+        sync = bool(getattr(fb, "benchmark_vision_timing", False)) and input_ids.is_cuda
+        if sync:
+            torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        feats = self.visual(fb.pixel_values, fb.image_grid_thw)
+        if sync:
+            torch.cuda.synchronize()
+        fb.vit_prefill_ms = (time.perf_counter() - t0) * 1e3
+        mask = input_ids == self.image_token_id
+        n_tok = int(mask.sum())
+        fb.vit_prefill_tokens = n_tok
+        if n_tok != feats.shape[0]:
+            raise ValueError(f"Image features and image tokens do not match, tokens: {n_tok}, features: {feats.shape[0]}")
+        input_embeds = self.model.embed_tokens(input_ids)
+        where = mask.nonzero(as_tuple=True)[0]
+        input_embeds.index_copy_(0, where, feats[:, : self.hidden_size].to(input_embeds.dtype))
+        deepstack = None
+        if self.num_deepstack:
+            deepstack = []
+            for j in range(self.num_deepstack):
+                d = torch.zeros_like(input_embeds)
+                d.index_copy_(0, where, feats[:, self.hidden_size * (j + 1): self.hidden_size * (j + 2)].to(d.dtype))
+                deepstack.append(d)
+        return input_embeds, deepstack
+
+    @staticmethod
+    def _visual_name(name: str) -> Optional[str]:
+        for pre in ("model.visual.", "visual."):
+            if name.startswith(pre):
+                return name[len(pre):]
+        return None
+
+    def _load_visual(self, weights: Iterable[Tuple[str, torch.Tensor]]):
+        """Loads the vision tower's tensors; returns (names loaded, the remaining (name, tensor) pairs)."""
+        vparams = {n: p for n, p in self.visual.named_parameters()}
+        loaded, rest = set(), []
+        for name, tensor in weights:
+            vn = self._visual_name(name)
+            if vn is None:
+                rest.append((name, tensor))
+                continue
+            # reference checkpoints converted for pymllm use qkv_proj / out_proj for the attention weights
+            vn = vn.replace(".attn.qkv_proj.", ".attn.qkv.").replace(".attn.out_proj.", ".attn.proj.")
+            p = vparams.get(vn)
+            if p is None:
+                continue
+            p.data.copy_(tensor.reshape(p.shape) if tensor.numel() == p.numel() else tensor)
+            loaded.add("visual." + vn)
+        return loaded, rest
+
     def _extend_positions(self, input_ids, fb: ForwardBatch) -> torch.Tensor:
         lens = fb.extend_seq_lens_cpu if getattr(fb, "extend_seq_lens_cpu", None) is not None else fb.extend_seq_lens.tolist()
         prefix = fb.extend_prefix_lens_cpu if getattr(fb, "extend_prefix_lens_cpu", None) is not None else (
@@ -275,38 +330,29 @@ class Qwen3VLForConditionalGeneration(Qwen3ForCausalLM):
         fb.mrope_position_deltas = torch.tensor(deltas, dtype=torch.int64, device=input_ids.device)
         return torch.cat(out, 1).to(input_ids.device)
 
+
+class Qwen3VLForConditionalGeneration(VisionLanguageMixin, Qwen3ForCausalLM):
+    def __init__(self, config, quant_config=None, params_dtype: Optional[torch.dtype] = None) -> None:
+        tc = _text_config(config)
+        rs = getattr(tc, "rope_scaling", None) or getattr(tc, "rope_parameters", None) or {}
+        if not isinstance(rs, dict):
+            rs = vars(rs)
+        sections = rs.get("mrope_section", [24, 20, 20])
+        interleaved = bool(rs.get("mrope_interleaved", True))
+        if not hasattr(tc, "tie_word_embeddings"):
+            tc.tie_word_embeddings = bool(getattr(config, "tie_word_embeddings", False))
+        super().__init__(tc, quant_config, params_dtype, mrope_sections=sections, mrope_interleaved=interleaved)
+        self._init_vision(config, params_dtype or torch.get_default_dtype())
+        self.hidden_size = tc.hidden_size
+
+    # ------------------------------------------------------------------ forward
     def forward(self, input_ids: torch.Tensor, positions: torch.Tensor, forward_batch: ForwardBatch,
                 input_embeds: Optional[torch.Tensor] = None) -> LogitsProcessorOutput:
         fb = forward_batch
-        if fb.forward_mode.is_extend():
-            fb.mrope_positions = self._extend_positions(input_ids, fb)
-        elif fb.mrope_positions is None:
-            pos = fb.positions if fb.mrope_position_deltas is None else fb.positions + fb.mrope_position_deltas
-            fb.mrope_positions = pos.unsqueeze(0).expand(3, -1).contiguous()
-        deepstack = None
-        if fb.pixel_values is not None and fb.image_grid_thw is not None and not fb.forward_mode.is_decode():
-            sync = bool(getattr(fb, "benchmark_vision_timing", False)) and input_ids.is_cuda
-            if sync:
-                torch.cuda.synchronize()
-            t0 = time.perf_counter()
-            feats = self.visual(fb.pixel_values, fb.image_grid_thw)
-            if sync:
-                torch.cuda.synchronize()
-            fb.vit_prefill_ms = (time.perf_counter() - t0) * 1e3
-            mask = input_ids == self.image_token_id
-            n_tok = int(mask.sum())
-            fb.vit_prefill_tokens = n_tok
-            if n_tok != feats.shape[0]:
-                raise ValueError(f"Image features and image tokens do not match, tokens: {n_tok}, features: {feats.shape[0]}")
-            input_embeds = self.model.embed_tokens(input_ids)
-            where = mask.nonzero(as_tuple=True)[0]
-            input_embeds.index_copy_(0, where, feats[:, : self.hidden_size].to(input_embeds.dtype))
-            if self.num_deepstack:
-                deepstack = []
-                for j in range(self.num_deepstack):
-                    d = torch.zeros_like(input_embeds)
-                    d.index_copy_(0, where, feats[:, self.hidden_size * (j + 1): self.hidden_size * (j + 2)].to(d.dtype))
-                    deepstack.append(d)
+        self._set_mrope_positions(input_ids, fb)
+        embeds, deepstack = self._vision_embeds(input_ids, fb)
+        if embeds is not None:
+            input_embeds = embeds
         t0 = time.perf_counter()
         hidden = self.model(input_ids, positions, fb, input_embeds, deepstack_embeds=deepstack)
         out = LogitsProcessorOutput(next_token_logits=self.compute_logits(hidden, fb))
@@ -318,30 +364,9 @@ class Qwen3VLForConditionalGeneration(Qwen3ForCausalLM):
         return out
 
     # ------------------------------------------------------------------ loading
-    @staticmethod
-    def _visual_name(name: str) -> Optional[str]:
-        for pre in ("model.visual.", "visual."):
-            if name.startswith(pre):
-                return name[len(pre):]
-        return None
-
     def load_weights(self, weights: Iterable[Tuple[str, torch.Tensor]]) -> set:
-        vparams = {n: p for n, p in self.visual.named_parameters()}
-        loaded, rest = set(), []
-        for name, tensor in weights:
-            vn = self._visual_name(name)
-            if vn is None:
-                rest.append((name, tensor))
-                continue
-            # reference checkpoints converted for pymllm use qkv_proj / out_proj for the attention weights
-            vn = vn.replace(".attn.qkv_proj.", ".attn.qkv.").replace(".attn.out_proj.", ".attn.proj.")
-            p = vparams.get(vn)
-            if p is None:
-                continue
-            p.data.copy_(tensor.reshape(p.shape) if tensor.numel() == p.numel() else tensor)
-            loaded.add("visual." + vn)
-        loaded |= super().load_weights(rest)
-        return loaded
+        loaded, rest = self._load_visual(weights)
+        return loaded | super().load_weights(rest)
 
 
 EntryClass = Qwen3VLForConditionalGeneration

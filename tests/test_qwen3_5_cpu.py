@@ -120,3 +120,77 @@ def test_chunked_delta_rule_matches_the_token_loop():
         o = ref.gated_delta_rule_chunked(q, k, v, g, beta, s, idx, lens, has, chunk=chunk)
         assert (o - o_ref).abs().max() < 2e-6 and (s - s_ref).abs().max() < 2e-6
         assert torch.equal(s[2], st[2]) and torch.equal(s[4], st[4])   # rows of no request are untouched
+
+
+def test_multimodal_variant_matches_hf():
+    """Qwen3_5ForConditionalGeneration (vision tower + hybrid text model) against HF transformers on an
+    image prompt: prefill logits, the image's position delta, and one decode step."""
+    import types
+
+    import pytest
+    import torch
+
+    from mllm_b200.configs import ServerConfig
+    from mllm_b200.executor import ModelRunner
+
+    tr = pytest.importorskip("transformers")
+    IMG, VSTART, VEND = 301, 302, 303
+    text = dict(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=2,
+                num_key_value_heads=1, head_dim=32, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=256,
+                attention_bias=False, linear_conv_kernel_dim=4, linear_key_head_dim=16, linear_value_head_dim=16,
+                linear_num_key_heads=2, linear_num_value_heads=4, hidden_act="silu",
+                layer_types=["linear_attention", "linear_attention", "linear_attention", "full_attention"],
+                rope_parameters=dict(rope_theta=10000.0, partial_rotary_factor=0.5, rope_type="default", mrope_section=[4, 2, 2]))
+    vision = dict(depth=2, hidden_size=32, hidden_act="gelu_pytorch_tanh", intermediate_size=64, num_heads=2, in_channels=3,
+                  patch_size=16, spatial_merge_size=2, temporal_patch_size=2, out_hidden_size=64, num_position_embeddings=16)
+    try:
+        hf_cfg = tr.Qwen3_5Config(text_config=dict(text), vision_config=dict(vision), image_token_id=IMG, video_token_id=304,
+                                  vision_start_token_id=VSTART, vision_end_token_id=VEND, tie_word_embeddings=False)
+        hf = tr.Qwen3_5ForConditionalGeneration(hf_cfg).float().eval()
+    except Exception as e:  # pragma: no cover
+        pytest.skip(f"transformers Qwen3.5 (multimodal) unavailable: {e}")
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith(("layernorm.weight", "q_norm.weight", "k_norm.weight", "language_model.norm.weight")):
+                p.copy_(torch.randn_like(p) * 0.1)
+    ns = types.SimpleNamespace(architectures=["Qwen3_5ForConditionalGeneration"], model_type="qwen3_5", tie_word_embeddings=False,
+                               image_token_id=IMG, video_token_id=304, vision_start_token_id=VSTART, vision_end_token_id=VEND,
+                               text_config=types.SimpleNamespace(**text), vision_config=types.SimpleNamespace(**vision))
+    mr = ModelRunner(ServerConfig(model_path="preset:x", dtype="float32", max_running_requests=2, max_total_tokens=256),
+                     hf_config=ns, device="cpu")
+    mr.initialize()
+    loaded = mr.model.load_weights(hf.state_dict().items())
+    assert any(k.startswith("visual.") for k in loaded)
+    missing = set(dict(mr.model.named_parameters())) - loaded
+    assert not missing, missing
+    for m in mr.model.modules():
+        if hasattr(m, "quant_method"):
+            m._gate_up_interleaved = False
+            m.quant_method.process_weights_after_loading(m)
+    mr.model.post_load()
+    torch.manual_seed(0)
+    grid = torch.tensor([[1, 4, 6]])                     # 24 patches -> 6 merged tokens
+    pixels = torch.randn(24, 3 * 2 * 16 * 16)
+    ids = torch.tensor([[11, 12, VSTART] + [IMG] * 6 + [VEND, 13, 14, 15]])
+    L = ids.shape[1]
+    slots = mr.req_to_token_pool.alloc(1)
+    loc = mr.token_to_kv_pool_allocator.alloc(L)
+    mr.req_to_token_pool.req_to_token[slots[0], :L] = loc.int()
+    lens = torch.tensor([L])
+    fb = mr.prepare_forward_batch_extend(ids.reshape(-1), torch.tensor(slots), lens, lens, torch.zeros_like(lens), loc,
+                                         pixel_values=pixels, image_grid_thw=grid)
+    got = mr.forward(fb).next_token_logits
+    with torch.no_grad():
+        want = hf(input_ids=ids, pixel_values=pixels, image_grid_thw=grid, mm_token_type_ids=(ids == IMG).int()).logits[:, -1]
+    torch.testing.assert_close(got, want, atol=5e-4, rtol=5e-4)
+    assert fb.vit_prefill_tokens == 6 and int(fb.mrope_position_deltas[0]) == (3 + 3 + 4) - L
+    nxt = got.argmax(-1)
+    loc1 = mr.token_to_kv_pool_allocator.alloc(1)
+    mr.req_to_token_pool.req_to_token[slots[0], L] = loc1.int()
+    fbd = mr.prepare_forward_batch_decode(nxt, torch.tensor(slots), torch.tensor([L + 1]), loc1,
+                                          mrope_position_deltas=fb.mrope_position_deltas)
+    got2 = mr.forward(fbd).next_token_logits
+    with torch.no_grad():
+        ids2 = torch.cat([ids, nxt[:, None]], 1)
+        want2 = hf(input_ids=ids2, pixel_values=pixels, image_grid_thw=grid, mm_token_type_ids=(ids2 == IMG).int()).logits[:, -1]
+    torch.testing.assert_close(got2, want2, atol=5e-4, rtol=5e-4)
