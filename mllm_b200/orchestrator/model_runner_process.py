@@ -70,6 +70,9 @@ class Req:
     def all_ids(self) -> List[int]:
         return self.input_ids + self.output_ids
 
+    def last_id(self) -> int:
+        return self.output_ids[-1] if self.output_ids else self.input_ids[-1]
+
 
 class KVAllocationError(RuntimeError):
     pass
@@ -219,7 +222,7 @@ class ModelRunnerProcess:
         loc = self._alloc_kv_with_eviction(bs)
         pool = torch.tensor([q.req_pool_idx for q in reqs], dtype=torch.int32).to(dev, non_blocking=True)
         pos = torch.tensor([q.num_computed for q in reqs], dtype=torch.int64).to(dev, non_blocking=True)
-        last = torch.tensor([q.all_ids()[-1] for q in reqs], dtype=torch.int64).to(dev, non_blocking=True)
+        last = torch.tensor([q.last_id() for q in reqs], dtype=torch.int64).to(dev, non_blocking=True)
         r.req_to_token_pool.req_to_token[pool.long(), pos] = loc.to(torch.int32)
         seq_lens = (pos + 1).to(torch.int32)
         max_len = max(q.num_computed for q in reqs) + 1
