@@ -373,6 +373,16 @@ class ModelRunner:
         if st:
             from safetensors import safe_open
 
+            # sharded models: hand out slice handles, so a rank reads only the part of each matrix it keeps
+            lazy = os.environ.get("MLLM_B200_LAZY_LOAD", "1" if pstate.get_tensor_model_parallel_world_size() > 1 else "0") == "1"
+            if lazy:
+                from ..io.lazy_tensor import LazyTensor
+
+                for f in st:
+                    fh = safe_open(f, framework="pt", device="cpu")  # kept open by the tensors that refer to it
+                    for k in fh.keys():
+                        yield k, LazyTensor(fh.get_slice(k), fh)
+                return
             for f in st:
                 with safe_open(f, framework="pt", device="cpu") as fh:
                     for k in fh.keys():

@@ -58,6 +58,44 @@ def test_tp2_fused_prefill_matches_nccl_on_gpu(tmp_path):
     assert (fused.argmax(-1) == ref.argmax(-1)).float().mean().item() > 0.8
 
 
+def test_tp2_loads_only_its_slices_from_safetensors(tmp_path):
+    """Two ranks loading one safetensors file through slice handles: logits equal the single-rank model
+    loaded from the same tensors, and each rank reads clearly less than the whole file (the sharded
+    matrices by halves; embeddings, norms and the replicated head in full)."""
+    one = _launch(1, str(tmp_path / "tp1.pt"), "cpu", "float32", 29641)
+    ck = tmp_path / "ckpt"
+    two = _launch(2, str(tmp_path / "tp2.pt"), "cpu", "float32", 29642, {"TP_TEST_FROM_FILES": str(ck)})
+    torch.testing.assert_close(two, one, atol=2e-4, rtol=2e-4)
+    for r in range(2):
+        read, total = (int(x) for x in (ck / f"bytes_read_rank{r}_of2.txt").read_text().split())
+        assert 0 < read < 0.85 * total, (read, total)
+
+
+def test_lazy_tensor_reads_what_is_used(tmp_path):
+    from safetensors import safe_open
+    from safetensors.torch import save_file
+
+    from mllm_b200.io.lazy_tensor import LazyTensor
+
+    a = torch.arange(24.).reshape(4, 6)
+    save_file({"a": a, "v": torch.arange(5)}, str(tmp_path / "t.safetensors"))
+    fh = safe_open(str(tmp_path / "t.safetensors"), framework="pt", device="cpu")
+    base = LazyTensor.bytes_read
+    t = LazyTensor(fh.get_slice("a"), fh)
+    assert tuple(t.shape) == (4, 6) and t.dim() == 2 and t.dtype == torch.float32 and t.numel() == 24
+    assert LazyTensor.bytes_read == base                                  # metadata costs nothing
+    assert torch.equal(t.narrow(1, 2, 2), a[:, 2:4]) and LazyTensor.bytes_read == base + 32
+    assert torch.equal(t[1:3], a[1:3]) and torch.equal(t[:, :3], a[:, :3])
+    p = torch.zeros(4, 6)
+    p.copy_(t)                                                            # a torch function: whole tensor, once
+    assert torch.equal(p, a)
+    after = LazyTensor.bytes_read
+    assert torch.equal(t.reshape(-1), a.reshape(-1)) and torch.equal(torch.cat([t, p], 0), torch.cat([a, a], 0))
+    assert LazyTensor.bytes_read == after                                 # cached after the first full read
+    v = LazyTensor(fh.get_slice("v"), fh)
+    assert v.dtype == torch.int64 and int((v.float() + 1).sum()) == 15 and len(v) == 5
+
+
 @pytest.mark.parametrize("kv_heads", ["2", "1"])
 def test_hybrid_tp2_matches_single_rank_on_cpu(tmp_path, kv_heads):
     """Qwen3.5-style hybrid model on two gloo ranks: gated-delta-net heads (projections, convolution

@@ -104,7 +104,25 @@ def run(out_path: str, device: str, dtype_name: str) -> None:
     mr = ModelRunner(sc, hf_config=cfg, device=dev)
     mr.initialize()
     dtype = mr.dtype
-    mr.model.load_weights((hybrid_state_dict if hybrid else full_state_dict)(cfg, dtype=dtype).items())
+    sd = (hybrid_state_dict if hybrid else full_state_dict)(cfg, dtype=dtype)
+    files = os.environ.get("TP_TEST_FROM_FILES")
+    if files:   # through the checkpoint reader (slice handles under tensor parallelism) instead of a dict
+        from safetensors.torch import save_file
+
+        from mllm_b200.io.lazy_tensor import LazyTensor
+
+        if rank == 0:
+            os.makedirs(files, exist_ok=True)
+            save_file({k: v.contiguous() for k, v in sd.items()}, os.path.join(files, "model.safetensors"))
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
+        mr.model.load_weights(mr._iter_weights(files))
+        with open(os.path.join(files, f"bytes_read_rank{rank}_of{world}.txt"), "w") as fh:
+            fh.write(f"{LazyTensor.bytes_read} {sum(v.numel() * v.element_size() for v in sd.values())}")
+    else:
+        mr.model.load_weights(sd.items())
     for m in mr.model.modules():
         if hasattr(m, "quant_method"):
             m._gate_up_interleaved = False
