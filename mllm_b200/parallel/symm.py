@@ -40,13 +40,17 @@ from . import state as pstate
 logger = logging.getLogger(__name__)
 _FLAG_STRIDE = 8
 _HEAP_ALIGN = 256
+_GUARD = 256          # canary bytes in front of and behind every heap block
+_GUARD_BYTE = 0xA5
 
 
 class SymmetricHeap:
     """One byte buffer per rank, mapped into every peer, plus the offset allocator that carves it.
 
     Every rank must make the same ``tensor`` / ``free`` calls in the same order (the allocator is
-    deterministic), which gives every buffer the same offset on every rank."""
+    deterministic), which gives every buffer the same offset on every rank.  Each block sits between two
+    runs of canary bytes; :meth:`check_guards` tells whether a kernel (local or a peer's) wrote outside a
+    buffer — the multi-rank tests call it after their collectives."""
 
     def __init__(self, buf: torch.Tensor, base_ptrs: List[int]) -> None:
         from ..mem_cache.native import host_ext
@@ -81,7 +85,7 @@ class SymmetricHeap:
             n = torch.empty((), dtype=dtype).element_size()
             for d in shape:
                 n *= int(d)
-            total += (n + _HEAP_ALIGN - 1) // _HEAP_ALIGN * _HEAP_ALIGN
+            total += (n + 2 * _GUARD + _HEAP_ALIGN - 1) // _HEAP_ALIGN * _HEAP_ALIGN
         return total
 
     def tensor(self, shape, dtype: torch.dtype):
@@ -89,16 +93,29 @@ class SymmetricHeap:
         n = torch.empty((), dtype=dtype).element_size()
         for d in shape:
             n *= int(d)
-        off = int(self.alloc.alloc(n))
-        if off < 0:
+        blk = int(self.alloc.alloc(n + 2 * _GUARD))
+        if blk < 0:
             raise MemoryError(f"symmetric heap: no room for {n} bytes ({self.alloc.used} of {self.alloc.capacity} used)")
+        off = blk + _GUARD
+        self.buf[blk:off] = _GUARD_BYTE
+        self.buf[off + n:off + n + _GUARD] = _GUARD_BYTE
         t = self.buf[off:off + n].view(dtype).view(*shape)
-        self._offsets[t.data_ptr()] = off
+        self._offsets[t.data_ptr()] = (blk, n)
         return t, [b + off for b in self.base_ptrs]
 
+    def check_guards(self) -> List[int]:
+        """Offsets of the live buffers whose canary bytes were overwritten (empty: all intact)."""
+        bad = []
+        for blk, n in self._offsets.values():
+            front = self.buf[blk:blk + _GUARD]
+            back = self.buf[blk + _GUARD + n:blk + 2 * _GUARD + n]
+            if bool((front != _GUARD_BYTE).any()) or bool((back != _GUARD_BYTE).any()):
+                bad.append(blk + _GUARD)
+        return bad
+
     def free(self, t: torch.Tensor) -> None:
-        off = self._offsets.pop(t.data_ptr(), None)
-        if off is None or not self.alloc.free(off):
+        entry = self._offsets.pop(t.data_ptr(), None)
+        if entry is None or not self.alloc.free(entry[0]):
             raise ValueError("tensor does not start a block of this heap")
 
 

@@ -372,6 +372,7 @@ def test_symmetric_heap_allocator_and_views():
     assert heap.alloc.used == heap.alloc.capacity
     offs = [p[0] - (1 << 40) for _, p in views]
     assert offs == sorted(offs) and all(o % 256 == 0 for o in offs)
+    assert heap.check_guards() == []
     for (t, ptrs), (shape, dt) in zip(views, plan):
         assert tuple(t.shape) == tuple(shape) and t.dtype == dt and t.is_contiguous()
         assert t.data_ptr() - heap.buf.data_ptr() == ptrs[0] - (1 << 40) == ptrs[2] - (3 << 40)
@@ -380,6 +381,15 @@ def test_symmetric_heap_allocator_and_views():
     assert float(views[0][0].sum()) == 1.5 * 320 and int(views[1][0].sum()) == 280 and int(views[3][0].sum()) == 0
     with pytest.raises(MemoryError):
         heap.tensor((1,), torch.int32)
+    # canary bytes: a write one element past a buffer's end (or before its start) is reported
+    assert heap.check_guards() == []
+    end_of_first = offs[0] + 5 * 64 * 2
+    heap.buf[end_of_first] = 0
+    assert heap.check_guards() == [offs[0]]
+    heap.buf[end_of_first] = 0xA5
+    heap.buf[offs[2] - 1] = 7
+    assert heap.check_guards() == [offs[2]]
+    heap.buf[offs[2] - 1] = 0xA5
     heap.free(views[1][0])
     t, _ = heap.tensor((8,), torch.int32)
     assert t.data_ptr() == views[1][0].data_ptr()

@@ -111,6 +111,7 @@ def test_fused_prefill_step_over_fake_transport(tp, prefill_rows, M):
             assert bool((p.gather_flags[: M // 128] == epoch).all())
             assert bool((p.gather_flags[M // 128:] == 0).all())          # tiles beyond the batch are untouched
             assert bool((p.hidden_full[M:] == 0).all())
+    assert all(h.check_guards() == [] for h in fab.heaps)       # nothing was written outside a buffer
 
 
 def test_decode_buffers_alternate_and_resolve_on_every_rank():

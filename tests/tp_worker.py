@@ -159,6 +159,12 @@ def run(out_path: str, device: str, dtype_name: str) -> None:
         from mllm_b200 import ops
 
         ops.check_status()
+    from mllm_b200.parallel.symm import get_tp_comm as _comm
+
+    if _comm() is not None and getattr(_comm(), "heap", None) is not None:
+        if device != "cpu":
+            torch.cuda.synchronize()
+        assert _comm().heap.check_guards() == [], "a kernel wrote outside a symmetric buffer"
     if os.environ.get("TP_TEST_EXPECT_FUSED_PREFILL") == "1":
         from mllm_b200.parallel.symm import get_tp_comm
 
