@@ -19,8 +19,9 @@ from .. import ops
 class RadixAttention(nn.Module):
     def __init__(self, num_heads: int, head_dim: int, scaling: float, num_kv_heads: int, layer_id: int,
                  rope_theta: float = 1e6, rms_eps: float = 1e-6, mrope_sections=None,
-                 mrope_interleaved: bool = False) -> None:
+                 mrope_interleaved: bool = False, rope_scaling: Optional[dict] = None) -> None:
         super().__init__()
+        self.rope_scaling = rope_scaling
         self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
         self.scaling, self.layer_id = scaling, layer_id
         self.rope_theta, self.rms_eps = rope_theta, rms_eps
@@ -30,7 +31,7 @@ class RadixAttention(nn.Module):
 
     def _tables(self, device):
         if self._inv_freq is None or self._inv_freq.device != device:
-            self._inv_freq = ops.rope_inv_freq(self.head_dim, self.rope_theta, device)
+            self._inv_freq = ops.rope_inv_freq(self.head_dim, self.rope_theta, device, self.rope_scaling)
             if self.mrope_sections is not None:
                 self._axis_map = ops.mrope_axis_map(self.head_dim, self.mrope_sections, self.mrope_interleaved, device)
         return self._inv_freq, self._axis_map

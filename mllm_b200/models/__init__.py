@@ -11,6 +11,9 @@ _REGISTRY: Dict[str, Tuple[str, str]] = {
     "Qwen3VLForConditionalGeneration": ("mllm_b200.models.qwen3_vl", "Qwen3VLForConditionalGeneration"),
     "Qwen3_5ForCausalLM": ("mllm_b200.models.qwen3_5", "Qwen3_5ForCausalLM"),
     "Qwen3_5ForConditionalGeneration": ("mllm_b200.models.qwen3_5", "Qwen3_5ForConditionalGeneration"),
+    "LlamaForCausalLM": ("mllm_b200.models.llama", "LlamaForCausalLM"),
+    "MistralForCausalLM": ("mllm_b200.models.llama", "MistralForCausalLM"),
+    "Qwen2ForCausalLM": ("mllm_b200.models.llama", "Qwen2ForCausalLM"),
 }
 
 

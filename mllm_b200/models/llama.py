@@ -1,0 +1,47 @@
+"""Llama-family and Qwen2-family decoders (the architectures the reference's C++ runtime ships beside
+Qwen3: ``mllm/models/llama``, ``mllm/models/qwen2``-style configs).  Both are the Qwen3 decoder stack
+without the per-head q/k RMSNorm: same fused QKV + RoPE + KV-write prologue (norm weights absent), same
+attention and SwiGLU kernels, same tensor-parallel sharding and quantised linears.
+
+* ``LlamaForCausalLM`` (also Mistral-style configs without a sliding window): no attention bias unless
+  ``attention_bias``; ``rope_scaling`` of type ``llama3`` / ``linear`` is applied to the rotary
+  frequencies.
+* ``Qwen2ForCausalLM`` (Qwen2 / Qwen2.5): bias on the q, k and v projections.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .qwen3 import Qwen3ForCausalLM
+
+
+def _unsupported(config, what: str, ok) -> None:
+    v = getattr(config, what, None)
+    if v is not None and not ok(v):
+        raise NotImplementedError(f"{type(config).__name__}.{what}={v!r} is not supported")
+
+
+class LlamaForCausalLM(Qwen3ForCausalLM):
+    def __init__(self, config, quant_config=None, params_dtype: Optional[torch.dtype] = None, **model_kw) -> None:
+        config.use_qk_norm = False
+        if getattr(config, "attention_bias", None) is None:
+            config.attention_bias = False
+        _unsupported(config, "mlp_bias", lambda v: not v)
+        _unsupported(config, "sliding_window", lambda v: not v)
+        super().__init__(config, quant_config, params_dtype, **model_kw)
+
+
+class Qwen2ForCausalLM(Qwen3ForCausalLM):
+    def __init__(self, config, quant_config=None, params_dtype: Optional[torch.dtype] = None, **model_kw) -> None:
+        config.use_qk_norm = False
+        config.attention_bias = True          # Qwen2 always has q/k/v biases; the config does not say so
+        if getattr(config, "use_sliding_window", False):
+            raise NotImplementedError("Qwen2 sliding-window attention is not supported")
+        super().__init__(config, quant_config, params_dtype, **model_kw)
+
+
+MistralForCausalLM = LlamaForCausalLM
+EntryClass = LlamaForCausalLM

@@ -41,6 +41,22 @@ PRESETS["qwen3-moe-tiny"] = dict(
     architectures=["Qwen3MoeForCausalLM"], model_type="qwen3_moe", num_experts=8, num_experts_per_tok=2,
     moe_intermediate_size=256, norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[],
 )
+# Llama / Qwen2 families (same decoder stack without q/k norms; published shapes)
+PRESETS["llama-3.1-8b"] = dict(
+    _dense(4096, 32, 32, 8, 14336, False, vocab=128256, theta=5e5),
+    architectures=["LlamaForCausalLM"], model_type="llama", rms_norm_eps=1e-5, max_position_embeddings=131072,
+    rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=8192), eos_token_id=128009, bos_token_id=128000,
+)
+PRESETS["qwen2.5-7b"] = dict(
+    _dense(3584, 28, 28, 4, 18944, False, vocab=152064, theta=1e6),
+    architectures=["Qwen2ForCausalLM"], model_type="qwen2", max_position_embeddings=32768,
+)
+PRESETS["llama-tiny"] = dict(_dense(256, 2, 4, 2, 512, True, vocab=1024, theta=1e4),
+                             architectures=["LlamaForCausalLM"], model_type="llama")
+PRESETS["qwen2-tiny"] = dict(_dense(256, 2, 4, 2, 512, True, vocab=1024), architectures=["Qwen2ForCausalLM"], model_type="qwen2")
+
+
 def _hybrid(hidden, layers, heads, kv_heads, inter, head_dim, lin_k_heads, lin_v_heads, vocab=151936):
     return dict(
         architectures=["Qwen3_5ForCausalLM"], model_type="qwen3_5_text", vocab_size=vocab, hidden_size=hidden,

@@ -66,12 +66,15 @@ class Qwen3Attention(nn.Module):
         self.o_proj = RowParallelLinear(self.total_heads * self.head_dim, self.hidden_size, bias=False,
                                         quant_method=_quant_method(quant_config, f"{prefix}.o_proj"),
                                         params_dtype=params_dtype, prefix=f"{prefix}.o_proj")
-        self.q_norm = RMSNorm(self.head_dim, eps, params_dtype)
-        self.k_norm = RMSNorm(self.head_dim, eps, params_dtype)
+        # per-head RMSNorm of q and k: Qwen3 has it, the Llama / Qwen2 families (served by subclasses) do not
+        self.use_qk_norm = bool(getattr(config, "use_qk_norm", True))
+        if self.use_qk_norm:
+            self.q_norm = RMSNorm(self.head_dim, eps, params_dtype)
+            self.k_norm = RMSNorm(self.head_dim, eps, params_dtype)
         rope_theta = _rope_theta(config)
         self.attn = RadixAttention(self.num_heads, self.head_dim, self.head_dim ** -0.5, self.num_kv_heads, layer_id,
                                    rope_theta=rope_theta, rms_eps=eps, mrope_sections=mrope_sections,
-                                   mrope_interleaved=mrope_interleaved)
+                                   mrope_interleaved=mrope_interleaved, rope_scaling=_rope_scaling(config))
 
     def kv_shard_for_rank(self, loaded: torch.Tensor) -> torch.Tensor:
         """With fewer KV heads than ranks, rank r keeps head ``r * Hkv // tp``."""
@@ -83,7 +86,8 @@ class Qwen3Attention(nn.Module):
 
     def forward(self, x: torch.Tensor, forward_batch: ForwardBatch) -> torch.Tensor:
         qkv = self.qkv_proj(x)
-        a = self.attn(qkv, self.q_norm.weight, self.k_norm.weight, forward_batch)
+        qw, kw = (self.q_norm.weight, self.k_norm.weight) if self.use_qk_norm else (None, None)
+        a = self.attn(qkv, qw, kw, forward_batch)
         # under tensor parallelism the partial sums go to the next norm, which reduces them
         return self.o_proj.forward_partial(a) if self.o_proj.tp_size > 1 else self.o_proj(a)
 
@@ -94,6 +98,17 @@ def _rope_theta(config) -> float:
         rp = getattr(config, "rope_parameters", None) or getattr(config, "rope_scaling", None) or {}
         theta = rp.get("rope_theta", 1e6) if isinstance(rp, dict) else 1e6
     return float(theta)
+
+
+def _rope_scaling(config) -> Optional[dict]:
+    """The checkpoint's frequency rescaling (``rope_scaling`` / ``rope_parameters``) when it has one that
+    changes the frequencies; M-RoPE sections are handled separately."""
+    rs = getattr(config, "rope_scaling", None) or getattr(config, "rope_parameters", None)
+    if rs is None:
+        return None
+    rs = rs if isinstance(rs, dict) else vars(rs)
+    kind = rs.get("rope_type", rs.get("type", "default"))
+    return dict(rs) if kind in ("linear", "llama3", "yarn", "dynamic", "longrope") else None
 
 
 class Qwen3DecoderLayer(nn.Module):

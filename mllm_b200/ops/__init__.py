@@ -328,8 +328,27 @@ def w4a16_gemm(x, qweight, scales, zeros, group: int, bias=None) -> torch.Tensor
 # --------------------------------------------------------------------------
 # rope / kv
 # --------------------------------------------------------------------------
-def rope_inv_freq(head_dim: int, theta: float, device) -> torch.Tensor:
-    return 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
+def rope_inv_freq(head_dim: int, theta: float, device, scaling: Optional[dict] = None) -> torch.Tensor:
+    """Rotary frequencies ``theta^(-2i/D)``, optionally rescaled the way the checkpoint's ``rope_scaling``
+    asks: ``linear`` (all frequencies divided by ``factor``) or ``llama3`` (long wavelengths divided by
+    ``factor``, short ones kept, a smooth blend between ``original_max_position_embeddings /
+    low_freq_factor`` and ``/ high_freq_factor``)."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
+    kind = (scaling or {}).get("rope_type", (scaling or {}).get("type", "default"))
+    if not scaling or kind in (None, "default", "mrope"):
+        return inv
+    if kind == "linear":
+        return inv / float(scaling["factor"])
+    if kind == "llama3":
+        import math
+
+        factor, lo, hi = float(scaling["factor"]), float(scaling["low_freq_factor"]), float(scaling["high_freq_factor"])
+        old_len = float(scaling["original_max_position_embeddings"])
+        wavelen = 2 * math.pi / inv
+        smooth = ((old_len / wavelen - lo) / (hi - lo)).clamp(0.0, 1.0)
+        blended = (1 - smooth) * inv / factor + smooth * inv
+        return torch.where(wavelen > old_len / lo, inv / factor, torch.where(wavelen < old_len / hi, inv, blended))
+    raise NotImplementedError(f"rope scaling type {kind!r}")
 
 
 def mrope_axis_map(head_dim: int, sections, interleaved: bool, device) -> torch.Tensor:
@@ -354,7 +373,7 @@ def qk_norm_rope_kv_write(
     if not use_kernels(qkv) or head_dim != 128:
         return ref.qk_norm_rope_kv_write(
             qkv, q_weight, k_weight, positions, cache_loc, k_cache, v_cache, num_q_heads, num_kv_heads,
-            head_dim, theta, eps, mrope_sections, mrope_interleaved,
+            head_dim, theta, eps, mrope_sections, mrope_interleaved, inv_freq=inv_freq,
         )
     if inv_freq is None:
         inv_freq = rope_inv_freq(head_dim, theta, qkv.device)

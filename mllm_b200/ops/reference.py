@@ -176,9 +176,11 @@ def w4a16_gemm(x, qweight, scales, zeros, group: int, bias=None) -> torch.Tensor
 # --------------------------------------------------------------------------
 # rotary embedding, QK-norm, cache write
 # --------------------------------------------------------------------------
-def rope_cos_sin(positions: torch.Tensor, head_dim: int, theta: float, rotary_dim: Optional[int] = None):
+def rope_cos_sin(positions: torch.Tensor, head_dim: int, theta: float, rotary_dim: Optional[int] = None,
+                 inv_freq: Optional[torch.Tensor] = None):
     rd = rotary_dim or head_dim
-    inv = 1.0 / (theta ** (torch.arange(0, rd, 2, device=positions.device, dtype=torch.float32) / rd))
+    inv = inv_freq.to(positions.device) if inv_freq is not None else \
+        1.0 / (theta ** (torch.arange(0, rd, 2, device=positions.device, dtype=torch.float32) / rd))
     ang = positions.float().unsqueeze(-1) * inv  # [..., rd/2]
     return ang.cos(), ang.sin()
 
@@ -215,7 +217,7 @@ def qk_norm_rope_kv_write(
     qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
     positions: torch.Tensor, cache_loc: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     num_q_heads: int, num_kv_heads: int, head_dim: int, theta: float, eps: float,
-    mrope_sections=None, mrope_interleaved: bool = False,
+    mrope_sections=None, mrope_interleaved: bool = False, inv_freq: Optional[torch.Tensor] = None,
 ) -> None:
     """In place on ``qkv`` ``[T, (Hq+2Hkv)*D]``: per-head RMSNorm of q and k (if weights
     given), NeoX RoPE at ``positions`` (``[T]``, or ``[3,T]`` with ``mrope_sections``); then
@@ -234,7 +236,7 @@ def qk_norm_rope_kv_write(
     if mrope_sections is not None:
         cos, sin = mrope_cos_sin(positions, head_dim, theta, mrope_sections, mrope_interleaved)
     else:
-        cos, sin = rope_cos_sin(positions, head_dim, theta)
+        cos, sin = rope_cos_sin(positions, head_dim, theta, inv_freq=inv_freq)
     q = apply_rope_neox(q, cos, sin).to(qkv.dtype)
     k = apply_rope_neox(k, cos, sin).to(qkv.dtype)
     qkv[:, :qd] = q.reshape(T, qd)
