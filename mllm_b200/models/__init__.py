@@ -14,6 +14,7 @@ _REGISTRY: Dict[str, Tuple[str, str]] = {
     "LlamaForCausalLM": ("mllm_b200.models.llama", "LlamaForCausalLM"),
     "MistralForCausalLM": ("mllm_b200.models.llama", "MistralForCausalLM"),
     "Qwen2ForCausalLM": ("mllm_b200.models.llama", "Qwen2ForCausalLM"),
+    "SmolLM3ForCausalLM": ("mllm_b200.models.llama", "SmolLM3ForCausalLM"),
 }
 
 

@@ -7,6 +7,8 @@ attention and SwiGLU kernels, same tensor-parallel sharding and quantised linear
   ``attention_bias``; ``rope_scaling`` of type ``llama3`` / ``linear`` is applied to the rotary
   frequencies.
 * ``Qwen2ForCausalLM`` (Qwen2 / Qwen2.5): bias on the q, k and v projections.
+* ``SmolLM3ForCausalLM``: Llama with ``no_rope_layers`` — every n-th layer attends without positional
+  rotation (the prologue kernel gets all-zero frequencies there).
 """
 
 from __future__ import annotations
@@ -40,6 +42,16 @@ class Qwen2ForCausalLM(Qwen3ForCausalLM):
         config.attention_bias = True          # Qwen2 always has q/k/v biases; the config does not say so
         if getattr(config, "use_sliding_window", False):
             raise NotImplementedError("Qwen2 sliding-window attention is not supported")
+        super().__init__(config, quant_config, params_dtype, **model_kw)
+
+
+class SmolLM3ForCausalLM(LlamaForCausalLM):
+    def __init__(self, config, quant_config=None, params_dtype: Optional[torch.dtype] = None, **model_kw) -> None:
+        if getattr(config, "use_sliding_window", False):
+            raise NotImplementedError("SmolLM3 sliding-window attention is not supported")
+        if getattr(config, "no_rope_layers", None) is None:
+            n = int(getattr(config, "no_rope_layer_interval", 4))
+            config.no_rope_layers = [int((i + 1) % n != 0) for i in range(config.num_hidden_layers)]
         super().__init__(config, quant_config, params_dtype, **model_kw)
 
 

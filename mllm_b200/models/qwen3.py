@@ -74,7 +74,7 @@ class Qwen3Attention(nn.Module):
         rope_theta = _rope_theta(config)
         self.attn = RadixAttention(self.num_heads, self.head_dim, self.head_dim ** -0.5, self.num_kv_heads, layer_id,
                                    rope_theta=rope_theta, rms_eps=eps, mrope_sections=mrope_sections,
-                                   mrope_interleaved=mrope_interleaved, rope_scaling=_rope_scaling(config))
+                                   mrope_interleaved=mrope_interleaved, rope_scaling=_rope_scaling(config, layer_id))
 
     def kv_shard_for_rank(self, loaded: torch.Tensor) -> torch.Tensor:
         """With fewer KV heads than ranks, rank r keeps head ``r * Hkv // tp``."""
@@ -100,9 +100,13 @@ def _rope_theta(config) -> float:
     return float(theta)
 
 
-def _rope_scaling(config) -> Optional[dict]:
+def _rope_scaling(config, layer_id: int = 0) -> Optional[dict]:
     """The checkpoint's frequency rescaling (``rope_scaling`` / ``rope_parameters``) when it has one that
-    changes the frequencies; M-RoPE sections are handled separately."""
+    changes the frequencies; M-RoPE sections are handled separately.  ``no_rope_layers`` (1 = rotate,
+    0 = no positional rotation in that layer) turns the rotation off per layer."""
+    use = getattr(config, "no_rope_layers", None)
+    if use is not None and layer_id < len(use) and not use[layer_id]:
+        return {"rope_type": "none"}
     rs = getattr(config, "rope_scaling", None) or getattr(config, "rope_parameters", None)
     if rs is None:
         return None

@@ -335,6 +335,8 @@ def rope_inv_freq(head_dim: int, theta: float, device, scaling: Optional[dict] =
     low_freq_factor`` and ``/ high_freq_factor``)."""
     inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
     kind = (scaling or {}).get("rope_type", (scaling or {}).get("type", "default"))
+    if kind == "none":          # a layer without positional rotation: angle 0 everywhere
+        return torch.zeros_like(inv)
     if not scaling or kind in (None, "default", "mrope"):
         return inv
     if kind == "linear":

@@ -82,6 +82,23 @@ def test_qwen2_matches_hf():
     _run_and_compare(hf, ns, 320)
 
 
+def test_smollm3_matches_hf():
+    """Every fourth layer attends without rotary embedding."""
+    tr = pytest.importorskip("transformers")
+    cfgd = dict(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
+                num_key_value_heads=2, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=256,
+                attention_bias=False, mlp_bias=False, hidden_act="silu", use_sliding_window=False)
+    try:
+        hf_cfg = tr.SmolLM3Config(**cfgd, pad_token_id=0, rope_parameters=dict(rope_theta=10000.0, rope_type="default"))
+        hf = tr.SmolLM3ForCausalLM(hf_cfg).float().eval()
+    except Exception as e:  # pragma: no cover
+        pytest.skip(f"transformers SmolLM3 unavailable: {e}")
+    assert list(hf_cfg.no_rope_layers) == [1, 1, 1, 0]
+    ns = types.SimpleNamespace(architectures=["SmolLM3ForCausalLM"], head_dim=16, rope_theta=10000.0,
+                               no_rope_layers=[1, 1, 1, 0], **cfgd)
+    _run_and_compare(hf, ns, 320)
+
+
 def test_unsupported_variants_are_refused():
     from mllm_b200.models import get_model_class
 
