@@ -345,6 +345,51 @@ class Engine:
                 self.rr.pop(r)
         return results[0] if obj.is_single else results
 
+    # ---- conversation helpers (roles of ARGeneration::chat / perfSummary in the reference's C++ runtime) ----
+    def _chat_tokenizer(self):
+        tok = getattr(self, "_chat_tok", None)
+        if tok is None:
+            w = getattr(self, "tokenizer_worker", None)
+            if w is not None:
+                tok = w.tokenizer
+            else:
+                from ..utils.tokenizer import get_tokenizer
+
+                sc = self.server_config
+                tok = get_tokenizer(sc.tokenizer_path, self._vocab_size(), sc.tokenizer_mode, sc.trust_remote_code)
+            self._chat_tok = tok
+        return tok
+
+    def chat(self, messages: List[Dict[str, Any]], sampling_params=None, stream: bool = False, tools=None,
+             image_data=None, timeout: Optional[float] = None, **template_kwargs):
+        """Renders ``messages`` (``[{"role": ..., "content": ...}, ...]``) with the tokenizer's chat template
+        (ChatML when it has none) and generates the assistant turn; same return types as ``generate``."""
+        from ..utils.tokenizer import render_chatml
+
+        tok = self._chat_tokenizer()
+        prompt = None
+        if getattr(tok, "chat_template", None):
+            try:
+                prompt = tok.apply_chat_template(messages, tokenize=False, add_generation_prompt=True, tools=tools,
+                                                 **template_kwargs)
+            except Exception as exc:
+                logger.warning("chat template failed (%s); using ChatML", exc)
+        if prompt is None:
+            prompt = render_chatml(messages, add_generation_prompt=True)
+        return self.generate(prompt, sampling_params, image_data=image_data, stream=stream, timeout=timeout)
+
+    @staticmethod
+    def perf_summary(result: Dict[str, Any]) -> Dict[str, float]:
+        """Time to first token and prefill / decode rates of one finished request, from its timing record."""
+        meta = result["meta_info"]
+        t = meta.get("timing") or {}
+        p, c = meta.get("prompt_tokens", 0), meta.get("completion_tokens", 0)
+        ttft, tpot, e2e = t.get("ttft_s", 0.0), t.get("tpot_s", 0.0), t.get("e2e_s", 0.0)
+        return {"ttft_ms": ttft * 1e3, "tpot_ms": tpot * 1e3, "e2e_ms": e2e * 1e3,
+                "prefill_tokens": p, "cached_tokens": meta.get("cached_tokens", 0), "decode_tokens": c,
+                "prefill_tokens_per_s": p / ttft if ttft > 0 else 0.0,
+                "decode_tokens_per_s": 1.0 / tpot if tpot > 0 else 0.0}
+
     def _stream_sync(self, rid: str, st: ReqState, timeout) -> Iterator[Dict[str, Any]]:
         sent = 0
         try:

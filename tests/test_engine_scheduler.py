@@ -277,3 +277,22 @@ def test_recorded_trace_replays_deterministically():
         for rid, v in kept.items():
             if final_c[rid][0] != "aborted":     # an abort may land before or after the finish in another schedule
                 assert final_c[rid] == v, (variant, rid)
+
+
+def test_chat_and_perf_summary():
+    eng = Engine(_cfg(), mode="inproc", device="cpu").launch()
+    try:
+        msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi"}]
+        out = eng.chat(msgs, {"max_new_tokens": 5, "temperature": 0.0})
+        # the same prompt by hand: ChatML (the byte tokenizer of the presets has no chat template)
+        want = eng.generate("<|im_start|>system\nbe brief<|im_end|>\n<|im_start|>user\nhi<|im_end|>\n<|im_start|>assistant\n",
+                            {"max_new_tokens": 5, "temperature": 0.0})
+        assert out["output_ids"] == want["output_ids"] and len(out["output_ids"]) == 5
+        assert want["meta_info"]["cached_tokens"] > 0          # the second request reused the first one's prompt
+        perf = Engine.perf_summary(out)
+        assert perf["decode_tokens"] == 5 and perf["prefill_tokens"] == out["meta_info"]["prompt_tokens"]
+        assert perf["ttft_ms"] > 0 and perf["e2e_ms"] >= perf["ttft_ms"] and perf["prefill_tokens_per_s"] > 0
+        chunks = list(eng.chat(msgs, {"max_new_tokens": 5, "temperature": 0.0}, stream=True))
+        assert chunks[-1]["output_ids"] == out["output_ids"]
+    finally:
+        eng.shutdown()
