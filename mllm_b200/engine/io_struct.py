@@ -146,6 +146,8 @@ class BatchTokenIDOutput:
     completion_tokens: List[int]
     cached_tokens: List[int] = field(default_factory=list)
     timing: List[Optional[Dict[str, float]]] = field(default_factory=list)
+    # per request: None, or {"token_logprobs": [lp per generated token], "top_logprobs": [[(id, lp), ...] per token]}
+    logprobs: List[Optional[Dict[str, Any]]] = field(default_factory=list)
 
 
 @dataclass
@@ -161,3 +163,4 @@ class BatchStrOutput:
     completion_tokens: List[int]
     cached_tokens: List[int] = field(default_factory=list)
     timing: List[Optional[Dict[str, float]]] = field(default_factory=list)
+    logprobs: List[Optional[Dict[str, Any]]] = field(default_factory=list)

@@ -312,17 +312,23 @@ class Engine:
         if st.error is not None:
             raise ValueError(st.error)
         last = st.out_list[-1]
-        return {"rid": rid, "text": last["text"], "output_ids": last["output_ids"],
-                "meta_info": {"finish_reason": last["finish_reason"], "prompt_tokens": last["prompt_tokens"],
-                              "completion_tokens": last["completion_tokens"], "cached_tokens": last["cached_tokens"],
-                              "timing": last["timing"]}}
+        meta = {"finish_reason": last["finish_reason"], "prompt_tokens": last["prompt_tokens"],
+                "completion_tokens": last["completion_tokens"], "cached_tokens": last["cached_tokens"],
+                "timing": last["timing"]}
+        if last.get("logprobs") is not None:
+            meta["output_token_logprobs"] = last["logprobs"]
+        return {"rid": rid, "text": last["text"], "output_ids": last["output_ids"], "meta_info": meta}
 
     def generate(self, prompt: Optional[Union[str, List[str]]] = None, sampling_params=None, input_ids=None,
-                 image_data=None, stream: bool = False, rid=None, timeout: Optional[float] = None):
+                 image_data=None, stream: bool = False, rid=None, timeout: Optional[float] = None,
+                 return_logprob: bool = False, top_logprobs_num: int = 0):
         """Blocking generation. One prompt -> dict, a list -> list of dicts; ``stream=True`` (single
-        prompt) returns an iterator of incremental dicts with a ``delta`` field."""
+        prompt) returns an iterator of incremental dicts with a ``delta`` field.  With ``return_logprob``
+        ``meta_info["output_token_logprobs"]`` holds the log-probability (and text) of every generated token
+        and, per token, the ``top_logprobs_num`` most likely alternatives."""
         obj = GenerateReqInput(rid=rid, text=prompt, input_ids=input_ids, sampling_params=sampling_params,
-                               image_data=image_data, stream=stream)
+                               image_data=image_data, stream=stream, return_logprob=return_logprob or None,
+                               top_logprobs_num=top_logprobs_num or None)
         subs = self._submit(obj)
         if stream:
             if len(subs) != 1:

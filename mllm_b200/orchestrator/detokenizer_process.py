@@ -20,7 +20,7 @@ class DetokenizerWorker:
         self.sent: Dict[str, str] = {}
 
     def detokenize(self, batch: BatchTokenIDOutput) -> BatchStrOutput:
-        out = BatchStrOutput([], [], [], [], [], [], [], [], [])
+        out = BatchStrOutput([], [], [], [], [], [], [], [], [], [])
         for i, rid in enumerate(batch.rids):
             ids = batch.output_ids[i]
             text = self.tokenizer.decode(ids, skip_special_tokens=batch.skip_special_tokens[i]) if ids else ""
@@ -42,6 +42,11 @@ class DetokenizerWorker:
             out.completion_tokens.append(batch.completion_tokens[i])
             out.cached_tokens.append(batch.cached_tokens[i] if batch.cached_tokens else 0)
             out.timing.append(batch.timing[i] if batch.timing else None)
+            lp = batch.logprobs[i] if batch.logprobs else None
+            if lp is not None:  # add the text of every token so clients need no tokenizer
+                lp = dict(lp, tokens=[self.tokenizer.decode([t]) for t in ids[: len(lp["token_logprobs"])]],
+                          top_tokens=[[self.tokenizer.decode([t]) for t, _ in row] for row in lp["top_logprobs"]])
+            out.logprobs.append(lp)
         return out
 
 

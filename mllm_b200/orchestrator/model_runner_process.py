@@ -58,6 +58,11 @@ class Req:
     finish_time: float = 0.0
     last_stream_len: int = 0
     mrope_delta: int = 0
+    # log-probabilities of the generated tokens (when the request asked for them)
+    return_logprob: bool = False
+    top_logprobs_num: int = 0
+    output_logprobs: List[float] = field(default_factory=list)
+    output_top_logprobs: List[List[Tuple[int, float]]] = field(default_factory=list)
 
     @property
     def seq_len(self) -> int:
@@ -208,6 +213,7 @@ class ModelRunnerProcess:
             logits = out.next_token_logits.index_select(0, rows)
             out.next_token_logits = logits
             next_ids = r.sample(out, self._sampling_info([items[i][0] for i in produced]))
+            self._record_logprobs([items[i][0] for i in produced], logits, next_ids)
         for i in produced:  # the prompt (and what was generated so far) becomes reusable
             req = items[i][0]
             if not req.output_ids:
@@ -237,8 +243,33 @@ class ModelRunnerProcess:
         info = self._sampling_info(reqs)
         pre = getattr(out, "next_token_ids", None)
         if pre is not None and info.all_greedy and not info.has_penalties:
-            return pre, fb
-        return r.sample(out, info), fb
+            nxt = pre
+        else:
+            nxt = r.sample(out, info)
+        self._record_logprobs(reqs, out.next_token_logits, nxt)
+        return nxt, fb
+
+    @staticmethod
+    def _record_logprobs(reqs: Sequence[Req], logits: torch.Tensor, next_ids: torch.Tensor) -> None:
+        """For the requests that asked: log-probability of the sampled token (and the ``top_logprobs_num``
+        most likely tokens) under the model's distribution — softmax of the logits the sampler saw,
+        before temperature / top-k / top-p.  Row i of ``logits`` / ``next_ids`` belongs to ``reqs[i]``."""
+        want = [i for i, q in enumerate(reqs) if q.return_logprob]
+        if not want:
+            return
+        rows = torch.tensor(want, device=logits.device)
+        lp = torch.log_softmax(logits.index_select(0, rows).float(), dim=-1)
+        chosen = lp.gather(1, next_ids.index_select(0, rows).long().view(-1, 1)).view(-1).tolist()
+        k = max(reqs[i].top_logprobs_num for i in want)
+        top_v = top_i = None
+        if k > 0:
+            tv, ti = lp.topk(min(k, lp.shape[-1]), dim=-1)
+            top_v, top_i = tv.tolist(), ti.tolist()
+        for j, i in enumerate(want):
+            q = reqs[i]
+            q.output_logprobs.append(float(chosen[j]))
+            n = q.top_logprobs_num
+            q.output_top_logprobs.append([(int(top_i[j][c]), float(top_v[j][c])) for c in range(n)] if n > 0 else [])
 
     # ------------------------------------------------------------------ finish / cache
     def _insert(self, req: Req, tokens: List[int]) -> None:

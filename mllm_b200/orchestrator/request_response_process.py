@@ -57,6 +57,7 @@ class RequestResponseProcess:
                     "completion_tokens": msg.completion_tokens[i],
                     "cached_tokens": msg.cached_tokens[i] if msg.cached_tokens else 0,
                     "timing": msg.timing[i] if msg.timing else None,
+                    "logprobs": msg.logprobs[i] if msg.logprobs else None,
                 })
                 if msg.finished_reasons[i] is not None:
                     st.finished = True

@@ -86,7 +86,8 @@ class Scheduler:
             extra_key = str(t.mm_inputs["image_hash"])
         req = Req(rid=t.rid, input_ids=ids, sampling=sp, stream=t.stream, input_text=t.input_text,
                   mm_inputs=t.mm_inputs, extra_key=extra_key, stop_token_ids=stop_ids,
-                  created_time=t.created_time or time.time())
+                  created_time=t.created_time or time.time(), return_logprob=bool(t.return_logprob),
+                  top_logprobs_num=int(t.top_logprobs_num or 0))
         if t.mm_inputs and "mrope_position_delta" in t.mm_inputs:
             req.mrope_delta = int(t.mm_inputs["mrope_position_delta"])
         self.waiting.append(req)
@@ -279,6 +280,8 @@ class Scheduler:
                 tpot = (q.finish_time - q.first_token_time) / (n - 1) if n > 1 else 0.0
                 timing = {"ttft_s": ttft, "tpot_s": tpot, "e2e_s": q.finish_time - q.created_time}
             out.timing.append(timing)
+            out.logprobs.append({"token_logprobs": list(q.output_logprobs), "top_logprobs": list(q.output_top_logprobs)}
+                                if q.return_logprob else None)
         return out if out.rids else None
 
     def abort_outputs(self, rids: List[str]) -> BatchTokenIDOutput:

@@ -110,7 +110,8 @@ class TokenizerWorker:
         return TokenizedGenerateReqInput(
             rid=req["rid"], input_text=text or "", input_ids=ids, mm_inputs=mm_inputs,
             sampling_params=req.get("sampling_params") or {}, stream=bool(req.get("stream", False)),
-            return_logprob=bool(req.get("return_logprob") or False), created_time=req.get("created_time") or time.time())
+            return_logprob=bool(req.get("return_logprob") or False), top_logprobs_num=int(req.get("top_logprobs_num") or 0),
+            created_time=req.get("created_time") or time.time())
 
 
 class ReplicaRouter:

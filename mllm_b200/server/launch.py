@@ -48,6 +48,7 @@ class GenerateRequest(BaseModel):
     stream: bool = False
     rid: Optional[Union[str, List[str]]] = None
     return_logprob: Optional[bool] = None
+    top_logprobs_num: Optional[int] = None
 
 
 class StreamOptions(BaseModel):
@@ -103,6 +104,7 @@ class ChatCompletionRequest(BaseModel):
     repetition_penalty: float = 1.0
     seed: Optional[int] = None
     logprobs: Optional[bool] = None
+    top_logprobs: Optional[int] = None
     tools: Optional[List[Dict[str, Any]]] = None
     tool_choice: Optional[Any] = None
     separate_reasoning: bool = True
@@ -170,6 +172,35 @@ def _usage(meta: Dict[str, Any]) -> Dict[str, Any]:
     p, c = meta.get("prompt_tokens", 0), meta.get("completion_tokens", 0)
     return {"prompt_tokens": p, "completion_tokens": c, "total_tokens": p + c,
             "prompt_tokens_details": {"cached_tokens": meta.get("cached_tokens", 0)}}
+
+
+def _chat_logprobs(lp: Optional[Dict[str, Any]]) -> Optional[Dict[str, Any]]:
+    """Chat-completions layout: one entry per generated token with its alternatives."""
+    if lp is None:
+        return None
+
+    def entry(tok: str, val: float) -> Dict[str, Any]:
+        return {"token": tok, "logprob": val, "bytes": list(tok.encode("utf-8"))}
+
+    content = []
+    for i, val in enumerate(lp["token_logprobs"]):
+        e = entry(lp["tokens"][i], val)
+        e["top_logprobs"] = [entry(t, v) for t, (_, v) in zip(lp["top_tokens"][i], lp["top_logprobs"][i])]
+        content.append(e)
+    return {"content": content}
+
+
+def _completion_logprobs(lp: Optional[Dict[str, Any]]) -> Optional[Dict[str, Any]]:
+    """Legacy completions layout: parallel lists plus character offsets into the returned text."""
+    if lp is None:
+        return None
+    offsets, pos = [], 0
+    for t in lp["tokens"]:
+        offsets.append(pos)
+        pos += len(t)
+    tops = [{t: v for t, (_, v) in zip(lp["top_tokens"][i], lp["top_logprobs"][i])} or None
+            for i in range(len(lp["token_logprobs"]))]
+    return {"tokens": lp["tokens"], "token_logprobs": lp["token_logprobs"], "top_logprobs": tops, "text_offset": offsets}
 
 
 def _debug_timing(meta: Dict[str, Any]) -> Optional[Dict[str, Any]]:
@@ -314,9 +345,8 @@ def create_app(engine: Engine, cfg: Optional[GlobalConfig] = None) -> FastAPI:
     @app.post("/generate")
     async def generate(body: GenerateRequest, request: Request):
         obj = GenerateReqInput(rid=body.rid, text=body.text, input_ids=body.input_ids, sampling_params=body.sampling_params,
-                               image_data=body.image_data, stream=body.stream)
-        if body.return_logprob:
-            return _error(400, "return_logprob is not supported")
+                               image_data=body.image_data, stream=body.stream, return_logprob=body.return_logprob or None,
+                               top_logprobs_num=body.top_logprobs_num or None)
         if body.stream:
             async def sse():
                 try:
@@ -337,8 +367,11 @@ def create_app(engine: Engine, cfg: Optional[GlobalConfig] = None) -> FastAPI:
     async def completions(body: CompletionRequest, request: Request):
         if body.n != 1:
             return _error(400, "n > 1 is not supported")
-        if body.logprobs:
-            return _error(400, "logprobs are not supported")
+        want_lp = body.logprobs is not None
+        if want_lp and body.stream:
+            return _error(400, "logprobs are not supported together with stream")
+        if want_lp and not 0 <= int(body.logprobs) <= 20:
+            return _error(400, "logprobs must be between 0 and 20")
         if body.echo:
             return _error(400, "echo is not supported")
         sp = _sampling(body, 16)
@@ -347,7 +380,8 @@ def create_app(engine: Engine, cfg: Optional[GlobalConfig] = None) -> FastAPI:
             kw["input_ids"] = body.prompt
         else:
             kw["text"] = body.prompt
-        obj = GenerateReqInput(sampling_params=sp, stream=body.stream, **kw)
+        obj = GenerateReqInput(sampling_params=sp, stream=body.stream, return_logprob=True if want_lp else None,
+                               top_logprobs_num=int(body.logprobs) if want_lp and body.logprobs else None, **kw)
         cid = f"cmpl-{uuid.uuid4().hex}"
         if body.stream:
             include_usage = bool(body.stream_options and body.stream_options.include_usage)
@@ -378,7 +412,8 @@ def create_app(engine: Engine, cfg: Optional[GlobalConfig] = None) -> FastAPI:
         for i, o in enumerate(outs):
             for k in total:
                 total[k] += o["meta_info"].get(k, 0)
-            choices.append({"index": i, "text": o["text"], "finish_reason": o["meta_info"]["finish_reason"], "logprobs": None})
+            choices.append({"index": i, "text": o["text"], "finish_reason": o["meta_info"]["finish_reason"],
+                            "logprobs": _completion_logprobs(o["meta_info"].get("output_token_logprobs"))})
         resp = {"id": cid, "object": "text_completion", "created": int(time.time()), "model": model_name,
                 "choices": choices, "usage": _usage(total)}
         if sc.enable_debug_timing and outs:
@@ -390,15 +425,18 @@ def create_app(engine: Engine, cfg: Optional[GlobalConfig] = None) -> FastAPI:
     async def chat_completions(body: ChatCompletionRequest, request: Request):
         if body.n != 1:
             return _error(400, "n > 1 is not supported")
-        if body.logprobs:
-            return _error(400, "logprobs are not supported")
+        if body.logprobs and body.stream:
+            return _error(400, "logprobs are not supported together with stream")
+        if body.top_logprobs is not None and not (body.logprobs and 0 <= body.top_logprobs <= 20):
+            return _error(400, "top_logprobs needs logprobs=true and a value between 0 and 20")
         try:
             prompt = messages_to_prompt(tokenizer(), body.messages, body.tools, body.chat_template_kwargs)
         except Exception as exc:
             return _error(400, f"could not render the chat template: {exc}")
         images = _extract_images(body.messages)
         obj = GenerateReqInput(text=prompt, sampling_params=_sampling(body, 128), stream=body.stream,
-                               image_data=images or None)
+                               image_data=images or None, return_logprob=True if body.logprobs else None,
+                               top_logprobs_num=body.top_logprobs or None)
         cid = f"chatcmpl-{uuid.uuid4().hex}"
         use_reasoning = bool(sc.reasoning_parser) and body.separate_reasoning
         use_tools = bool(sc.tool_call_parser) and bool(body.tools)
@@ -466,7 +504,8 @@ def create_app(engine: Engine, cfg: Optional[GlobalConfig] = None) -> FastAPI:
                     finish = "tool_calls"
         message["content"] = text
         resp = {"id": cid, "object": "chat.completion", "created": int(time.time()), "model": model_name,
-                "choices": [{"index": 0, "message": message, "finish_reason": finish, "logprobs": None}],
+                "choices": [{"index": 0, "message": message, "finish_reason": finish,
+                             "logprobs": _chat_logprobs(o["meta_info"].get("output_token_logprobs"))}],
                 "usage": _usage(o["meta_info"])}
         if sc.enable_debug_timing:
             resp["debug_timing"] = _debug_timing(o["meta_info"])

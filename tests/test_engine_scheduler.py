@@ -296,3 +296,35 @@ def test_chat_and_perf_summary():
         assert chunks[-1]["output_ids"] == out["output_ids"]
     finally:
         eng.shutdown()
+
+
+def test_logprobs_match_the_models_distribution():
+    """Sampled-token and top-k log-probabilities reported by the engine equal log_softmax of the logits of a
+    hand-driven forward pass; requests that did not ask get none, also inside the same batch."""
+    eng = Engine(_cfg(), mode="inproc", device="cpu").launch()
+    try:
+        ids = [5, 9, 2, 7, 11, 3]
+        res = eng.generate(input_ids=[ids, ids[:4]], sampling_params={"max_new_tokens": 3, "temperature": 0.0},
+                           return_logprob=[True, False], top_logprobs_num=[2, 0])
+        assert "output_token_logprobs" not in res[1]["meta_info"]
+        lp = res[0]["meta_info"]["output_token_logprobs"]
+        runner = eng.scheduler.mrp.runner
+        seq = list(ids)
+        for step in range(3):
+            L = len(seq)
+            slots = runner.req_to_token_pool.alloc(1)
+            loc = runner.token_to_kv_pool_allocator.alloc(L)
+            runner.req_to_token_pool.req_to_token[slots[0], :L] = loc.int()
+            lens = torch.tensor([L])
+            fb = runner.prepare_forward_batch_extend(torch.tensor(seq), torch.tensor(slots), lens, lens, torch.zeros_like(lens), loc)
+            want = torch.log_softmax(runner.forward(fb).next_token_logits.float(), -1)[0]
+            runner.token_to_kv_pool_allocator.free(loc)
+            runner.req_to_token_pool.free(slots[0])
+            tok = res[0]["output_ids"][step]
+            assert abs(lp["token_logprobs"][step] - float(want[tok])) < 1e-4
+            tv, ti = want.topk(2)
+            assert [i for i, _ in lp["top_logprobs"][step]] == ti.tolist()
+            assert lp["top_logprobs"][step][1][1] == pytest.approx(float(tv[1]), abs=1e-4)
+            seq.append(tok)
+    finally:
+        eng.shutdown()

@@ -64,7 +64,7 @@ def test_chat_completions(client):
     assert body["usage"]["completion_tokens"] == 6 and "reasoning_content" in body["choices"][0]["message"]
     s = _sse(client.post("/v1/chat/completions", json={"messages": msgs, "max_tokens": 6, "temperature": 0, "stream": True}))
     assert s[0]["choices"][0]["delta"]["role"] == "assistant" and s[-1]["choices"][0]["finish_reason"] == "length"
-    assert client.post("/v1/chat/completions", json={"messages": msgs, "logprobs": True}).status_code == 400
+    assert client.post("/v1/chat/completions", json={"messages": msgs, "logprobs": True, "stream": True}).status_code == 400
 
 
 def test_abort_flush_metrics(client):
@@ -72,3 +72,35 @@ def test_abort_flush_metrics(client):
     assert client.post("/flush_cache").status_code == 200
     text = client.get("/metrics").text
     assert "mllm_b200_requests_total" in text and "mllm_b200_ttft_seconds_bucket" in text and "mllm_b200_kv_usage_ratio" in text
+
+
+def test_logprobs_in_all_three_endpoints(client):
+    import math
+
+    r = client.post("/generate", json={"text": "hello", "sampling_params": {"max_new_tokens": 4, "temperature": 0},
+                                       "return_logprob": True, "top_logprobs_num": 3}).json()
+    lp = r["meta_info"]["output_token_logprobs"]
+    assert len(lp["token_logprobs"]) == 4 and len(lp["tokens"]) == 4 and all(len(t) == 3 for t in lp["top_logprobs"])
+    for chosen, top in zip(lp["token_logprobs"], lp["top_logprobs"]):
+        assert chosen <= 0 and abs(chosen - top[0][1]) < 1e-6        # greedy: the sampled token is the most likely one
+        assert top[0][1] >= top[1][1] >= top[2][1]
+    assert [t[0][0] for t in lp["top_logprobs"]] == r["output_ids"]
+
+    body = client.post("/v1/completions", json={"prompt": "hello", "max_tokens": 4, "temperature": 0, "logprobs": 2}).json()
+    clp = body["choices"][0]["logprobs"]
+    assert clp["token_logprobs"] == pytest.approx(lp["token_logprobs"], abs=1e-5)
+    assert len(clp["top_logprobs"]) == 4 and all(len(d) <= 2 for d in clp["top_logprobs"]) and clp["text_offset"][0] == 0
+    assert "".join(clp["tokens"]) == body["choices"][0]["text"]
+    plain = client.post("/v1/completions", json={"prompt": "hello", "max_tokens": 4, "temperature": 0}).json()
+    assert plain["choices"][0]["logprobs"] is None and plain["choices"][0]["text"] == body["choices"][0]["text"]
+
+    chat = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 3,
+                                                     "temperature": 0, "logprobs": True, "top_logprobs": 2}).json()
+    content = chat["choices"][0]["logprobs"]["content"]
+    assert len(content) == 3 and all(len(c["top_logprobs"]) == 2 and c["logprob"] <= 0 for c in content)
+    assert all(bytes(c["bytes"]).decode("utf-8", "ignore") == c["token"] for c in content)
+    assert math.isclose(content[0]["logprob"], content[0]["top_logprobs"][0]["logprob"], abs_tol=1e-6)
+    assert client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "logprobs": True,
+                                                     "stream": True}).status_code == 400
+    assert client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}],
+                                                     "top_logprobs": 2}).status_code == 400
