@@ -148,6 +148,7 @@ class BatchTokenIDOutput:
     timing: List[Optional[Dict[str, float]]] = field(default_factory=list)
     # per request: None, or {"token_logprobs": [lp per generated token], "top_logprobs": [[(id, lp), ...] per token]}
     logprobs: List[Optional[Dict[str, Any]]] = field(default_factory=list)
+    stop_strs: List[Optional[List[str]]] = field(default_factory=list)   # the text is cut at the first of these
 
 
 @dataclass

@@ -27,6 +27,16 @@ class DetokenizerWorker:
             finished = batch.finished_reasons[i]
             if finished is None and text.endswith("�"):
                 text = text.rstrip("�")  # an incomplete multi-byte character: wait for the rest
+            stops = batch.stop_strs[i] if batch.stop_strs else None
+            if stops:
+                # cut at the earliest stop string; while the request runs, hold back a tail that could
+                # still turn into one, so that no part of a stop string is ever streamed
+                cut = min((p for p in (text.find(s) for s in stops) if p >= 0), default=-1)
+                if cut >= 0:
+                    text = text[:cut]
+                elif finished is None:
+                    keep = len(text) - (max(len(s) for s in stops) - 1)
+                    text = text[: max(len(self.sent.get(rid, "")), keep, 0)]
             prev = self.sent.get(rid, "")
             delta = text[len(prev):] if text.startswith(prev) else text
             if finished is None:

@@ -43,6 +43,7 @@ class Req:
     mm_inputs: Optional[Dict[str, Any]] = None
     extra_key: Optional[str] = None
     stop_token_ids: set = field(default_factory=set)
+    stop_strs: List[str] = field(default_factory=list)   # generation ends when the text contains one of these
     created_time: float = 0.0
     # generation state
     output_ids: List[int] = field(default_factory=list)

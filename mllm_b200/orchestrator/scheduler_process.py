@@ -63,6 +63,7 @@ class Scheduler:
         self.stream_interval = server_config.stream_interval
         self.context_len = mrp.runner.context_len
         self._decode_steps = 0
+        self._stop_tokenizer = None       # built on the first request with stop strings
 
     # ------------------------------------------------------------------ intake
     def add_request(self, t: TokenizedGenerateReqInput) -> Optional[str]:
@@ -87,7 +88,7 @@ class Scheduler:
         req = Req(rid=t.rid, input_ids=ids, sampling=sp, stream=t.stream, input_text=t.input_text,
                   mm_inputs=t.mm_inputs, extra_key=extra_key, stop_token_ids=stop_ids,
                   created_time=t.created_time or time.time(), return_logprob=bool(t.return_logprob),
-                  top_logprobs_num=int(t.top_logprobs_num or 0))
+                  top_logprobs_num=int(t.top_logprobs_num or 0), stop_strs=[s for s in (sp.stop or []) if s])
         if t.mm_inputs and "mrope_position_delta" in t.mm_inputs:
             req.mrope_delta = int(t.mm_inputs["mrope_position_delta"])
         self.waiting.append(req)
@@ -213,9 +214,25 @@ class Scheduler:
         self.prefilling = still
         return self._collect_output(reqs)
 
+    def _hits_stop_string(self, req: Req) -> bool:
+        """Decodes the tail of the generated ids (long enough to hold the longest stop string that could
+        have been completed by the newest token) and looks for the stop strings in it.  The detokenizer
+        cuts the text at the match; here the request only has to stop."""
+        if self._stop_tokenizer is None:
+            from ..utils.tokenizer import get_tokenizer
+
+            sc = self.cfg
+            self._stop_tokenizer = get_tokenizer(sc.tokenizer_path, self.mrp.runner.vocab_size, sc.tokenizer_mode,
+                                                 sc.trust_remote_code)
+        window = max(len(s) for s in req.stop_strs) + 8      # a token holds at least one byte of text
+        tail = self._stop_tokenizer.decode(req.output_ids[-window:], skip_special_tokens=req.sampling.skip_special_tokens)
+        return any(s in tail for s in req.stop_strs)
+
     def _check_finished(self, req: Req, now: float) -> None:
         tok = req.output_ids[-1]
         if tok in req.stop_token_ids:
+            req.finished_reason = "stop"
+        elif req.stop_strs and self._hits_stop_string(req):
             req.finished_reason = "stop"
         elif len(req.output_ids) >= req.sampling.max_new_tokens:
             req.finished_reason = "length"
@@ -270,6 +287,7 @@ class Scheduler:
             out.finished_reasons.append(q.finished_reason)
             out.output_ids.append(prior + list(q.output_ids))
             out.skip_special_tokens.append(q.sampling.skip_special_tokens)
+            out.stop_strs.append(list(q.stop_strs) or None)
             out.prompt_tokens.append(len(q.input_ids) - len(prior))
             out.completion_tokens.append(len(prior) + len(q.output_ids))
             out.cached_tokens.append(q.cached_tokens)

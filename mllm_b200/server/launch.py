@@ -168,6 +168,19 @@ def messages_to_prompt(tokenizer, messages: List[ChatMessage], tools=None, templ
     return render_chatml(plain, add_generation_prompt=True)
 
 
+def _n_sampling(sp: Dict[str, Any], n: int, prompts: int) -> List[Dict[str, Any]]:
+    """``n`` samples per prompt: the same parameters, with distinct seeds when one was given (otherwise the
+    sampler draws a fresh seed per request anyway)."""
+    out = []
+    for _ in range(prompts):
+        for j in range(n):
+            d = dict(sp)
+            if d.get("seed") is not None:
+                d["seed"] = int(d["seed"]) + j
+            out.append(d)
+    return out
+
+
 def _usage(meta: Dict[str, Any]) -> Dict[str, Any]:
     p, c = meta.get("prompt_tokens", 0), meta.get("completion_tokens", 0)
     return {"prompt_tokens": p, "completion_tokens": c, "total_tokens": p + c,
@@ -365,22 +378,27 @@ def create_app(engine: Engine, cfg: Optional[GlobalConfig] = None) -> FastAPI:
     # ---------------------------------------------------------------- /v1/completions
     @app.post("/v1/completions")
     async def completions(body: CompletionRequest, request: Request):
-        if body.n != 1:
-            return _error(400, "n > 1 is not supported")
+        n = int(body.n or 1)
+        if not 1 <= n <= 16 or (n > 1 and body.stream):
+            return _error(400, "n must be between 1 and 16, and 1 when streaming")
         want_lp = body.logprobs is not None
         if want_lp and body.stream:
             return _error(400, "logprobs are not supported together with stream")
         if want_lp and not 0 <= int(body.logprobs) <= 20:
             return _error(400, "logprobs must be between 0 and 20")
-        if body.echo:
-            return _error(400, "echo is not supported")
+        if body.echo and body.stream:
+            return _error(400, "echo is not supported together with stream")
         sp = _sampling(body, 16)
         kw: Dict[str, Any] = {}
+        prompts: List[Any]
         if isinstance(body.prompt, list) and body.prompt and isinstance(body.prompt[0], int):
-            kw["input_ids"] = body.prompt
+            prompts = [body.prompt]
+            kw["input_ids"] = prompts[0] if n == 1 else [p for p in prompts for _ in range(n)]
         else:
-            kw["text"] = body.prompt
-        obj = GenerateReqInput(sampling_params=sp, stream=body.stream, return_logprob=True if want_lp else None,
+            prompts = body.prompt if isinstance(body.prompt, list) else [body.prompt]
+            kw["text"] = body.prompt if n == 1 else [p for p in prompts for _ in range(n)]
+        sps: Any = sp if n == 1 else _n_sampling(sp, n, len(prompts))
+        obj = GenerateReqInput(sampling_params=sps, stream=body.stream, return_logprob=True if want_lp else None,
                                top_logprobs_num=int(body.logprobs) if want_lp and body.logprobs else None, **kw)
         cid = f"cmpl-{uuid.uuid4().hex}"
         if body.stream:
@@ -412,7 +430,11 @@ def create_app(engine: Engine, cfg: Optional[GlobalConfig] = None) -> FastAPI:
         for i, o in enumerate(outs):
             for k in total:
                 total[k] += o["meta_info"].get(k, 0)
-            choices.append({"index": i, "text": o["text"], "finish_reason": o["meta_info"]["finish_reason"],
+            text = o["text"]
+            if body.echo:   # choices come prompt-major: n per prompt
+                p = prompts[i // n]
+                text = (p if isinstance(p, str) else tokenizer().decode(p)) + text
+            choices.append({"index": i, "text": text, "finish_reason": o["meta_info"]["finish_reason"],
                             "logprobs": _completion_logprobs(o["meta_info"].get("output_token_logprobs"))})
         resp = {"id": cid, "object": "text_completion", "created": int(time.time()), "model": model_name,
                 "choices": choices, "usage": _usage(total)}
@@ -423,8 +445,9 @@ def create_app(engine: Engine, cfg: Optional[GlobalConfig] = None) -> FastAPI:
     # ---------------------------------------------------------------- /v1/chat/completions
     @app.post("/v1/chat/completions")
     async def chat_completions(body: ChatCompletionRequest, request: Request):
-        if body.n != 1:
-            return _error(400, "n > 1 is not supported")
+        n = int(body.n or 1)
+        if not 1 <= n <= 16 or (n > 1 and body.stream):
+            return _error(400, "n must be between 1 and 16, and 1 when streaming")
         if body.logprobs and body.stream:
             return _error(400, "logprobs are not supported together with stream")
         if body.top_logprobs is not None and not (body.logprobs and 0 <= body.top_logprobs <= 20):
@@ -434,9 +457,10 @@ def create_app(engine: Engine, cfg: Optional[GlobalConfig] = None) -> FastAPI:
         except Exception as exc:
             return _error(400, f"could not render the chat template: {exc}")
         images = _extract_images(body.messages)
-        obj = GenerateReqInput(text=prompt, sampling_params=_sampling(body, 128), stream=body.stream,
-                               image_data=images or None, return_logprob=True if body.logprobs else None,
-                               top_logprobs_num=body.top_logprobs or None)
+        sp = _sampling(body, 128)
+        obj = GenerateReqInput(text=prompt if n == 1 else [prompt] * n, sampling_params=sp if n == 1 else _n_sampling(sp, n, 1),
+                               stream=body.stream, image_data=(images or None) if n == 1 else ([images] * n if images else None),
+                               return_logprob=True if body.logprobs else None, top_logprobs_num=body.top_logprobs or None)
         cid = f"chatcmpl-{uuid.uuid4().hex}"
         use_reasoning = bool(sc.reasoning_parser) and body.separate_reasoning
         use_tools = bool(sc.tool_call_parser) and bool(body.tools)
@@ -489,24 +513,29 @@ def create_app(engine: Engine, cfg: Optional[GlobalConfig] = None) -> FastAPI:
             outs = await _collect(obj)
         except Exception as exc:
             return _map_exc(exc)
-        o = outs[0]
-        text = o["text"]
-        message: Dict[str, Any] = {"role": "assistant"}
-        if use_reasoning:
-            reasoning, text = ReasoningParser(sc.reasoning_parser).parse_non_stream(text)
-            message["reasoning_content"] = reasoning
-        finish = o["meta_info"]["finish_reason"]
-        if use_tools:
-            text, calls = ToolCallParser(sc.tool_call_parser, body.tools).parse_non_stream(text)
-            if calls:
-                message["tool_calls"] = [c.to_openai_dict(streaming=False) for c in calls]
-                if finish == "stop":
-                    finish = "tool_calls"
-        message["content"] = text
+        choices = []
+        total = {"prompt_tokens": 0, "completion_tokens": 0, "cached_tokens": 0}
+        for i, o in enumerate(outs):
+            for k in total:
+                total[k] += o["meta_info"].get(k, 0)
+            text = o["text"]
+            message: Dict[str, Any] = {"role": "assistant"}
+            if use_reasoning:
+                reasoning, text = ReasoningParser(sc.reasoning_parser).parse_non_stream(text)
+                message["reasoning_content"] = reasoning
+            finish = o["meta_info"]["finish_reason"]
+            if use_tools:
+                text, calls = ToolCallParser(sc.tool_call_parser, body.tools).parse_non_stream(text)
+                if calls:
+                    message["tool_calls"] = [c.to_openai_dict(streaming=False) for c in calls]
+                    if finish == "stop":
+                        finish = "tool_calls"
+            message["content"] = text
+            choices.append({"index": i, "message": message, "finish_reason": finish,
+                            "logprobs": _chat_logprobs(o["meta_info"].get("output_token_logprobs"))})
+        o = outs[-1]
         resp = {"id": cid, "object": "chat.completion", "created": int(time.time()), "model": model_name,
-                "choices": [{"index": 0, "message": message, "finish_reason": finish,
-                             "logprobs": _chat_logprobs(o["meta_info"].get("output_token_logprobs"))}],
-                "usage": _usage(o["meta_info"])}
+                "choices": choices, "usage": _usage(total if n > 1 else o["meta_info"])}
         if sc.enable_debug_timing:
             resp["debug_timing"] = _debug_timing(o["meta_info"])
         return resp

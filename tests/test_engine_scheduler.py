@@ -328,3 +328,26 @@ def test_logprobs_match_the_models_distribution():
             seq.append(tok)
     finally:
         eng.shutdown()
+
+
+def test_stop_strings_end_generation_and_never_reach_the_client():
+    """A stop string taken from the middle of what the model would otherwise generate: generation ends with
+    reason "stop", the text is cut right before it, streamed deltas never show any part of it, and the
+    request without stop strings is untouched."""
+    eng = Engine(_cfg(), mode="inproc", device="cpu").launch()
+    try:
+        sp = {"max_new_tokens": 24, "temperature": 0.0}
+        full = eng.generate("hello world", sp)
+        text = full["text"]
+        assert len(text) >= 12
+        stop = text[7:10]
+        first = text.find(stop)
+        out = eng.generate("hello world", dict(sp, stop=[stop, "\\x00never"]))
+        assert out["meta_info"]["finish_reason"] == "stop" and out["text"] == text[:first]
+        assert out["meta_info"]["completion_tokens"] < full["meta_info"]["completion_tokens"]
+        chunks = list(eng.generate("hello world", dict(sp, stop=stop), stream=True))
+        assert "".join(c["delta"] for c in chunks) == text[:first] and chunks[-1]["meta_info"]["finish_reason"] == "stop"
+        assert all(stop not in c["text"] for c in chunks)
+        assert eng.generate("hello world", sp)["text"] == text
+    finally:
+        eng.shutdown()

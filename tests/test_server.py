@@ -48,7 +48,7 @@ def test_generate_and_completions(client):
     body = r.json()
     assert body["object"] == "text_completion" and body["usage"]["completion_tokens"] == 5
     assert body["usage"]["total_tokens"] == body["usage"]["prompt_tokens"] + 5 and "debug_timing" in body
-    assert client.post("/v1/completions", json={"prompt": "x", "n": 2}).status_code == 400
+    assert client.post("/v1/completions", json={"prompt": "x", "n": 2, "stream": True}).status_code == 400
     assert client.post("/v1/completions", json={"prompt": "x", "top_p": 7}).status_code == 400
     s = _sse(client.post("/v1/completions", json={"prompt": "hello", "max_tokens": 5, "temperature": 0, "stream": True,
                                                   "stream_options": {"include_usage": True}}))
@@ -104,3 +104,25 @@ def test_logprobs_in_all_three_endpoints(client):
                                                      "stream": True}).status_code == 400
     assert client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}],
                                                      "top_logprobs": 2}).status_code == 400
+
+
+def test_n_samples_echo_and_stop(client):
+    body = client.post("/v1/completions", json={"prompt": "hello", "max_tokens": 5, "temperature": 0.9, "n": 3, "seed": 11}).json()
+    assert [c["index"] for c in body["choices"]] == [0, 1, 2] and body["usage"]["completion_tokens"] == 15
+    again = client.post("/v1/completions", json={"prompt": "hello", "max_tokens": 5, "temperature": 0.9, "n": 3, "seed": 11}).json()
+    assert [c["text"] for c in again["choices"]] == [c["text"] for c in body["choices"]]     # seeds are seed, seed+1, seed+2
+    assert len({c["text"] for c in body["choices"]}) > 1
+    echo = client.post("/v1/completions", json={"prompt": "hello", "max_tokens": 3, "temperature": 0, "echo": True}).json()
+    plain = client.post("/v1/completions", json={"prompt": "hello", "max_tokens": 3, "temperature": 0}).json()
+    assert echo["choices"][0]["text"] == "hello" + plain["choices"][0]["text"]
+    assert client.post("/v1/completions", json={"prompt": "x", "n": 2, "stream": True}).status_code == 400
+    assert client.post("/v1/completions", json={"prompt": "x", "n": 99}).status_code == 400
+    chat = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4,
+                                                     "temperature": 0, "n": 2}).json()
+    assert len(chat["choices"]) == 2 and chat["choices"][0]["message"]["content"] == chat["choices"][1]["message"]["content"]
+    assert chat["usage"]["completion_tokens"] == 8
+    # stop strings through the HTTP layer
+    long = client.post("/v1/completions", json={"prompt": "hello world", "max_tokens": 24, "temperature": 0}).json()["choices"][0]["text"]
+    stop = long[6:9]
+    cut = client.post("/v1/completions", json={"prompt": "hello world", "max_tokens": 24, "temperature": 0, "stop": stop}).json()
+    assert cut["choices"][0]["text"] == long[: long.find(stop)] and cut["choices"][0]["finish_reason"] == "stop"
