@@ -160,8 +160,8 @@ class ModelRunner:
         self._extract_model_metadata()
         self._init_tp_comm()
         self._configure_kv_cache_dtype()
+        self._init_state_pool()      # before the KV pool is sized: its memory is then seen as taken
         self.init_memory_pool()
-        self._init_state_pool()
         # the warm-up runs before graph capture use kernels that wait on peer flags with a bound of
         # a few seconds: the ranks enter them together, and leave initialisation together
         self._tp_rendezvous()
@@ -184,7 +184,12 @@ class ModelRunner:
             track = getattr(sc, "mamba_cache_slots", None)
             if track is None:
                 track = max(16, min(256, 4 * int(sc.max_running_requests or 1)))
-        self.gdn_pool = self.model.make_gdn_pool(self.req_to_token_pool.size, int(track))
+        self.gdn_pool = self.model.make_gdn_pool(self._num_req_slots(), int(track))
+
+    def _num_req_slots(self) -> int:
+        """Rows of the request table: the running batch plus a few spare rows for requests being prefilled
+        while it is full."""
+        return max(int(self.server_config.max_running_requests or 1), 1) + 8
 
     def _tp_rendezvous(self) -> None:
         if pstate.get_tensor_model_parallel_world_size() > 1:
@@ -430,11 +435,8 @@ class ModelRunner:
         page = self.server_config.radix_cache_page_size
         tokens = tokens // page * page
         self.max_total_num_tokens = tokens
-        max_reqs = self.server_config.max_running_requests or 1
-        max_reqs = max(max_reqs, 1)
-        self.max_running_requests = max_reqs
-        # a few spare rows: requests being prefilled while the running batch is full
-        self.req_to_token_pool = ReqToTokenPool(max_reqs + 8, self.context_len + 4, self.device)
+        self.max_running_requests = max(int(self.server_config.max_running_requests or 1), 1)
+        self.req_to_token_pool = ReqToTokenPool(self._num_req_slots(), self.context_len + 4, self.device)
         self.token_to_kv_pool = KVPool(tokens, self.num_hidden_layers, self.num_kv_heads, self.head_dim,
                                        self.kv_cache_dtype, self.device, page_size=page)
         self.token_to_kv_pool_allocator = TokenToKVPoolAllocator(tokens, page_size=page, device=self.device)

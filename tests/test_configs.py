@@ -63,3 +63,46 @@ def test_page_size_alias():
 def test_revalidation_on_cli():
     with pytest.raises(ValueError):
         read_args(["--server.port", "70000"])
+
+
+def test_kv_pool_capacity_from_the_memory_profile(monkeypatch):
+    """Token capacity = (free after load - (1 - mem_fraction_static) x free before load) / bytes per token,
+    capped by max_total_tokens; too little memory raises with the knob named in the message."""
+    import pytest
+    import torch
+
+    from mllm_b200.configs import ServerConfig
+    from mllm_b200.executor import model_runner as mrmod
+    from mllm_b200.executor import ModelRunner
+
+    mr = ModelRunner(ServerConfig(model_path="preset:qwen3-tiny", dtype="float32", max_running_requests=2,
+                                  max_total_tokens=None, mem_fraction_static=0.8), device="cpu")
+    mr.initialize()
+    cell = mr.cell_bytes()
+    assert cell == 2 * mr.num_hidden_layers * mr.num_kv_heads * mr.head_dim * 4          # K and V, fp32
+    mr._pre_load_avail_gib = 100.0
+    monkeypatch.setattr(mrmod, "get_available_gpu_memory", lambda *_a, **_k: 80.0)
+    prof = mr._profile_max_num_tokens()
+    assert prof.rest_gib == pytest.approx(80.0 - 100.0 * 0.2)
+    assert prof.max_total_num_tokens == int(60.0 * (1 << 30) // cell) and prof.cell_bytes == cell
+    mr.server_config.max_total_tokens = 4096
+    mr.init_memory_pool()
+    assert mr.max_total_num_tokens == 4096 and mr.req_to_token_pool.size == 2 + 8
+    monkeypatch.setattr(mrmod, "get_available_gpu_memory", lambda *_a, **_k: 10.0)
+    with pytest.raises(RuntimeError, match="mem_fraction_static"):
+        mr.init_memory_pool()
+
+
+def test_hybrid_state_pool_is_allocated_before_the_kv_pool_is_sized():
+    from mllm_b200.configs import ServerConfig
+    from mllm_b200.executor import ModelRunner
+
+    order = []
+    mr = ModelRunner(ServerConfig(model_path="preset:qwen3.5-tiny", dtype="float32", max_running_requests=3,
+                                  max_total_tokens=512, enable_mamba_cache=True, mamba_cache_slots=5), device="cpu")
+    for name in ("_init_state_pool", "init_memory_pool"):
+        orig = getattr(mr, name)
+        setattr(mr, name, (lambda o, n: lambda: (order.append(n), o())[1])(orig, name))
+    mr.initialize()
+    assert order == ["_init_state_pool", "init_memory_pool"]
+    assert mr.gdn_pool.slots == mr.req_to_token_pool.size == 3 + 8 and mr.gdn_pool.track_slots == 5
