@@ -129,3 +129,129 @@ def test_awq_config_keys():
     with pytest.raises(ValueError):
         cls.from_config({"bits": 8, "group_size": 128})
     assert cls.get_config_filenames() == ["quant_config.json", "quantize_config.json"]
+
+
+def test_gptq_layout_linear_and_tensor_parallel_shards():
+    """GPTQ tensors (qweight packed along K, qzeros packed along N and stored minus one) -> the K-major
+    4-bit layout; the linear equals the dequantised matmul; column- and row-parallel shards of the packed
+    tensors give the matching slices of the full result."""
+    from mllm_b200.layers.linear import ColumnParallelLinear, RowParallelLinear
+    from mllm_b200.quantization.methods.gptq import pack_words, unpack_words
+
+    torch.manual_seed(5)
+    vals = torch.randint(0, 16, (16, 24), dtype=torch.uint8)
+    assert torch.equal(unpack_words(pack_words(vals, 0), 0), vals) and torch.equal(unpack_words(pack_words(vals, 1), 1), vals)
+    col = torch.zeros(8, 1, dtype=torch.uint8)
+    col[1, 0] = 0xF                                       # input channel 1 sits in the second nibble of the word
+    assert int(pack_words(col, 0)[0, 0]) == 0xF << 4
+
+    K, N, g = 128, 64, 32
+    cfg = get_quantization_config("gptq").from_config({"bits": 4, "group_size": g, "sym": False, "desc_act": False})
+    q = torch.randint(0, 16, (K, N), dtype=torch.uint8)
+    z = torch.randint(1, 16, (K // g, N), dtype=torch.uint8)
+    s = torch.rand(K // g, N) * 0.1
+    w = (q.float() - z.float().repeat_interleave(g, 0)) * s.repeat_interleave(g, 0)       # [K, N]
+    tensors = {"qweight": pack_words(q, 0), "qzeros": pack_words(z - 1, 1), "scales": s, "g_idx": torch.arange(K, dtype=torch.int32) // g}
+
+    def build(cls, *a, **kw):
+        lin = cls(*a, quant_method=cfg.get_quant_method(None, "l"), params_dtype=torch.float32, **kw)
+        for name, t in tensors.items():
+            p = getattr(lin, name)
+            p.weight_loader(p, t)
+        lin.quant_method.process_weights_after_loading(lin)
+        return lin
+
+    lin = build(Linear, K, N)
+    assert lin.weight_packed.shape == (N, K // 8) and lin.weight_zeros.shape == (N, K // g) and not hasattr(lin, "g_idx")
+    x = torch.randn(3, K)
+    torch.testing.assert_close(lin(x), x @ w, atol=1e-4, rtol=1e-4)
+    # the classic format's "zero - 1" against the v2 format's plain zero
+    v2 = get_quantization_config("gptq").from_config({"bits": 4, "group_size": g, "checkpoint_format": "gptq_v2"})
+    assert v2.get_quant_method(None, "l").zero_offset == 0 and cfg.get_quant_method(None, "l").zero_offset == 1
+    with pytest.raises(ValueError):
+        get_quantization_config("gptq").from_config({"bits": 4, "group_size": g, "desc_act": True})
+    with pytest.raises(ValueError):
+        get_quantization_config("gptq").from_config({"bits": 8, "group_size": g})
+
+    # shards as a 2-rank job would load them
+    import mllm_b200.parallel.state as pstate
+
+    class FakeTP:
+        def __init__(self, r):
+            self.world_size, self.rank_in_group = 2, r
+
+    saved = pstate._TP
+    try:
+        for r in range(2):
+            pstate._TP = FakeTP(r)
+            colp = build(ColumnParallelLinear, K, N)
+            torch.testing.assert_close(colp(x), (x @ w)[:, r * N // 2:(r + 1) * N // 2], atol=1e-4, rtol=1e-4)
+            rowp = build(RowParallelLinear, K, N, reduce_results=False)
+            xs = x[:, r * K // 2:(r + 1) * K // 2]
+            torch.testing.assert_close(rowp.quant_method.apply(rowp, xs), xs @ w[r * K // 2:(r + 1) * K // 2], atol=1e-4, rtol=1e-4)
+    finally:
+        pstate._TP = saved
+
+
+def test_gptq_checkpoint_directory_end_to_end(tmp_path):
+    """A GPTQ checkpoint directory (config.json with quantization_config + safetensors with qweight / qzeros /
+    scales / g_idx per projection) served by the model runner gives the logits of the dense model built from
+    the dequantised weights."""
+    import json
+
+    from safetensors.torch import save_file
+
+    from mllm_b200.configs import ServerConfig
+    from mllm_b200.executor import ModelRunner
+    from mllm_b200.models.presets import get_preset, preset_to_config_json
+    from mllm_b200.quantization.methods.gptq import pack_words
+
+    cfg_json = dict(preset_to_config_json("qwen3-tiny"), tie_word_embeddings=False,
+                    quantization_config={"quant_method": "gptq", "bits": 4, "group_size": 32, "sym": True, "desc_act": False})
+    cfg = get_preset("qwen3-tiny", tie_word_embeddings=False)
+    g = torch.Generator().manual_seed(0)
+    sd_q, sd_d = {}, {}
+    H, D, I, V = cfg.hidden_size, cfg.head_dim, cfg.intermediate_size, cfg.vocab_size
+
+    def dense(name, t):
+        sd_q[name] = sd_d[name] = t
+
+    def quant(prefix, n, k):
+        q = torch.randint(0, 16, (k, n), generator=g, dtype=torch.uint8)
+        s = torch.rand(k // 32, n, generator=g) * 0.02
+        z = torch.randint(1, 16, (k // 32, n), generator=g, dtype=torch.uint8)
+        sd_q[prefix + ".qweight"], sd_q[prefix + ".qzeros"], sd_q[prefix + ".scales"] = pack_words(q, 0), pack_words(z - 1, 1), s
+        sd_q[prefix + ".g_idx"] = torch.arange(k, dtype=torch.int32) // 32
+        sd_d[prefix + ".weight"] = ((q.float() - z.float().repeat_interleave(32, 0)) * s.repeat_interleave(32, 0)).t().contiguous()
+
+    dense("model.embed_tokens.weight", torch.randn(V, H, generator=g) * 0.05)
+    dense("lm_head.weight", torch.randn(V, H, generator=g) * 0.05)
+    dense("model.norm.weight", torch.ones(H))
+    hq, hkv = cfg.num_attention_heads, cfg.num_key_value_heads
+    for i in range(cfg.num_hidden_layers):
+        p = f"model.layers.{i}."
+        for nm, n, k in (("self_attn.q_proj", hq * D, H), ("self_attn.k_proj", hkv * D, H), ("self_attn.v_proj", hkv * D, H),
+                         ("self_attn.o_proj", H, hq * D), ("mlp.gate_proj", I, H), ("mlp.up_proj", I, H), ("mlp.down_proj", H, I)):
+            quant(p + nm, n, k)
+        for nm, d in (("self_attn.q_norm.weight", D), ("self_attn.k_norm.weight", D), ("input_layernorm.weight", H),
+                      ("post_attention_layernorm.weight", H)):
+            dense(p + nm, torch.ones(d) + torch.randn(d, generator=g) * 0.05)
+    logits = []
+    for name, sd, extra in (("gptq", sd_q, cfg_json), ("dense", sd_d, {k: v for k, v in cfg_json.items() if k != "quantization_config"})):
+        d = tmp_path / name
+        d.mkdir()
+        (d / "config.json").write_text(json.dumps(extra))
+        save_file({k: v.contiguous() for k, v in sd.items()}, str(d / "model.safetensors"))
+        mr = ModelRunner(ServerConfig(model_path=str(d), dtype="float32", max_running_requests=2, max_total_tokens=256), device="cpu")
+        mr.initialize()
+        if name == "gptq":
+            assert type(mr.quant_config).__name__ == "GPTQConfig"
+            assert mr.model.model.layers[0].self_attn.qkv_proj.weight_packed.shape == ((hq + 2 * hkv) * D, H // 8)
+        ids = torch.arange(9) * 7 % V
+        slots = mr.req_to_token_pool.alloc(1)
+        loc = mr.token_to_kv_pool_allocator.alloc(9)
+        mr.req_to_token_pool.req_to_token[slots[0], :9] = loc.int()
+        lens = torch.tensor([9])
+        fb = mr.prepare_forward_batch_extend(ids, torch.tensor(slots), lens, lens, torch.zeros_like(lens), loc)
+        logits.append(mr.forward(fb).next_token_logits)
+    torch.testing.assert_close(logits[0], logits[1], atol=2e-4, rtol=2e-4)
