@@ -1,1 +1,1 @@
-from . import awq, compressed_tensors, gptq  # noqa: F401  (importing registers the schemes)
+from . import awq, compressed_tensors, fp8, gptq  # noqa: F401  (importing registers the schemes)

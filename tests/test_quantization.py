@@ -255,3 +255,43 @@ def test_gptq_checkpoint_directory_end_to_end(tmp_path):
         fb = mr.prepare_forward_batch_extend(ids, torch.tensor(slots), lens, lens, torch.zeros_like(lens), loc)
         logits.append(mr.forward(fb).next_token_logits)
     torch.testing.assert_close(logits[0], logits[1], atol=2e-4, rtol=2e-4)
+
+
+def test_fp8_block_and_per_tensor_weights_expand_to_the_dequantised_model():
+    from mllm_b200.layers.linear import MergedLinear
+
+    torch.manual_seed(9)
+    K, N, b = 256, 384, 128
+    cfg = get_quantization_config("fp8").from_config({"quant_method": "fp8", "fmt": "e4m3", "weight_block_size": [b, b]})
+    lin = Linear(K, N, quant_method=cfg.get_quant_method(None, "l"), params_dtype=torch.float32)
+    w8 = (torch.randn(N, K) * 2).to(torch.float8_e4m3fn)
+    sc = torch.rand(N // b, K // b) * 0.1 + 0.01
+    lin.weight.weight_loader(lin.weight, w8)
+    lin.weight_scale_inv.weight_loader(lin.weight_scale_inv, sc)
+    lin.quant_method.process_weights_after_loading(lin)
+    want = w8.float() * sc.repeat_interleave(b, 0).repeat_interleave(b, 1)
+    assert lin.weight.dtype == torch.float32 and not hasattr(lin, "weight_scale_inv")
+    x = torch.randn(3, K)
+    torch.testing.assert_close(lin(x), x @ want.t(), atol=1e-4, rtol=1e-4)
+    # fused q/k/v with block scales: every shard lands at its block offset
+    m = MergedLinear(K, [256, 128, 128], quant_method=cfg.get_quant_method(None, "qkv"), params_dtype=torch.float32,
+                     shard_names=["q", "k", "v"])
+    parts = []
+    for sid, n in (("q", 256), ("k", 128), ("v", 128)):
+        w = (torch.randn(n, K) * 2).to(torch.float8_e4m3fn)
+        s = torch.rand(n // b, K // b) * 0.1 + 0.01
+        m.weight.weight_loader(m.weight, w, sid)
+        m.weight_scale_inv.weight_loader(m.weight_scale_inv, s, sid)
+        parts.append(w.float() * s.repeat_interleave(b, 0).repeat_interleave(b, 1))
+    m.quant_method.process_weights_after_loading(m)
+    torch.testing.assert_close(m(x), x @ torch.cat(parts, 0).t(), atol=1e-4, rtol=1e-4)
+    # per-tensor scales
+    cfg_t = get_quantization_config("fp8").from_config({"quant_method": "fp8"})
+    lin_t = Linear(K, N, quant_method=cfg_t.get_quant_method(None, "l"), params_dtype=torch.float32)
+    lin_t.weight.weight_loader(lin_t.weight, w8)
+    lin_t.weight_scale.weight_loader(lin_t.weight_scale, torch.tensor(0.25))
+    lin_t.quant_method.process_weights_after_loading(lin_t)
+    torch.testing.assert_close(lin_t(x), x @ (w8.float() * 0.25).t(), atol=1e-4, rtol=1e-4)
+    assert type(cfg.get_quant_method(None, "lm_head")).__name__ == "UnquantizedLinearMethod"
+    with pytest.raises(ValueError):
+        get_quantization_config("fp8").from_config({"fmt": "e5m2"})
