@@ -9,6 +9,7 @@ _REGISTRY: Dict[str, Tuple[str, str]] = {
     "Qwen3ForCausalLM": ("mllm_b200.models.qwen3", "Qwen3ForCausalLM"),
     "Qwen3MoeForCausalLM": ("mllm_b200.models.qwen3_moe", "Qwen3MoeForCausalLM"),
     "Qwen3VLForConditionalGeneration": ("mllm_b200.models.qwen3_vl", "Qwen3VLForConditionalGeneration"),
+    "Qwen3VLMoeForConditionalGeneration": ("mllm_b200.models.qwen3_vl_moe", "Qwen3VLMoeForConditionalGeneration"),
     "Qwen3_5ForCausalLM": ("mllm_b200.models.qwen3_5", "Qwen3_5ForCausalLM"),
     "Qwen3_5ForConditionalGeneration": ("mllm_b200.models.qwen3_5", "Qwen3_5ForConditionalGeneration"),
     "LlamaForCausalLM": ("mllm_b200.models.llama", "LlamaForCausalLM"),

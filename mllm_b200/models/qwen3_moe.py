@@ -21,6 +21,8 @@ from ..parallel import state as pstate
 from .qwen3 import Qwen3DecoderLayer, Qwen3ForCausalLM, Qwen3Model
 
 _EXPERT_RE = re.compile(r"^(.*\.mlp)\.experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.weight$")
+# newer checkpoints keep all experts of a layer in two 3-D tensors
+_FUSED_EXPERT_RE = re.compile(r"^(.*\.mlp)\.experts\.(gate_up_proj|down_proj)$")
 
 
 def is_sparse_layer(config, layer_id: int) -> bool:
@@ -67,7 +69,7 @@ class Qwen3MoeForCausalLM(Qwen3ForCausalLM):
         params = dict(self.named_parameters())
         rest = []
         loaded = set()
-        for name, tensor in weights:
+        for name, tensor in self._split_fused_experts(weights):
             canon = self._canonical_name(name)
             m = _EXPERT_RE.match(canon) if canon else None
             if m is None:
@@ -93,6 +95,28 @@ class Qwen3MoeForCausalLM(Qwen3ForCausalLM):
                     loaded.add(f"{prefix}.block.w13")
         loaded |= super().load_weights(rest)
         return loaded
+
+    def _split_fused_experts(self, weights: Iterable[Tuple[str, torch.Tensor]]):
+        """Yields per-expert ``gate_proj`` / ``up_proj`` / ``down_proj`` matrices for checkpoints that store
+        ``experts.gate_up_proj`` ``[E, 2I, H]`` (or ``[E, H, 2I]``) and ``experts.down_proj`` ``[E, H, I]``
+        (or ``[E, I, H]``); everything else passes through."""
+        tc = self.config
+        inter, hidden = int(getattr(tc, "moe_intermediate_size", 0)), int(tc.hidden_size)
+        for name, tensor in weights:
+            m = _FUSED_EXPERT_RE.match(self._canonical_name(name) or "")
+            if m is None or tensor.dim() != 3:
+                yield name, tensor
+                continue
+            base = name[: name.rindex(".experts.") + len(".experts.")]
+            t = tensor.materialize() if hasattr(tensor, "materialize") else tensor
+            for e in range(t.shape[0]):
+                w = t[e]
+                if m.group(2) == "gate_up_proj":
+                    w = w if w.shape[0] == 2 * inter else w.t()
+                    yield f"{base}{e}.gate_proj.weight", w[:inter]
+                    yield f"{base}{e}.up_proj.weight", w[inter:]
+                else:
+                    yield f"{base}{e}.down_proj.weight", (w if w.shape[0] == hidden else w.t())
 
     def post_load(self) -> None:
         for m in self.modules():

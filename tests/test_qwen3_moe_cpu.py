@@ -57,24 +57,7 @@ def test_matches_hf_qwen3_moe():
                      hf_config=ns, device="cpu")
     mr.initialize()
     sd = hf.state_dict()
-    if not any(".experts.0.gate_proj" in k for k in sd):  # fused expert tensors in newer transformers
-        ex = {}
-        for k, v in list(sd.items()):
-            if k.endswith("mlp.experts.gate_up_proj"):
-                base = k[: -len("gate_up_proj")]
-                Iw = v.shape[1] // 2 if v.shape[1] == 2 * cfgd["moe_intermediate_size"] else None
-                for e in range(v.shape[0]):
-                    w = v[e] if Iw is not None else v[e].t()
-                    ex[f"{base}{e}.gate_proj.weight"] = w[: cfgd["moe_intermediate_size"]]
-                    ex[f"{base}{e}.up_proj.weight"] = w[cfgd["moe_intermediate_size"]:]
-                del sd[k]
-            elif k.endswith("mlp.experts.down_proj"):
-                base = k[: -len("down_proj")]
-                for e in range(v.shape[0]):
-                    w = v[e]
-                    ex[f"{base}{e}.down_proj.weight"] = w if w.shape[0] == cfgd["hidden_size"] else w.t()
-                del sd[k]
-        sd.update(ex)
+    # newer transformers keep the experts fused in two 3-D tensors: the loader splits them
     mr.model.load_weights(sd.items())
     ids = torch.randint(0, 300, (1, 10))
     slots = mr.req_to_token_pool.alloc(1)

@@ -105,3 +105,58 @@ def test_matches_hf_qwen3_vl():
         ids2 = torch.cat([ids, nxt[:, None]], 1)
         want2 = hf(input_ids=ids2, pixel_values=pixels, image_grid_thw=grid, mm_token_type_ids=(ids2 == IMG).int()).logits[:, -1]
     torch.testing.assert_close(got2, want2, atol=5e-4, rtol=5e-4)
+
+
+def test_matches_hf_qwen3_vl_moe():
+    """Vision tower + deepstack + 3-D rope on the mixture-of-experts text model; the checkpoint keeps the
+    experts of a layer fused in two 3-D tensors, which the loader splits."""
+    tr = pytest.importorskip("transformers")
+    text, vision = _tiny_cfg()
+    text = dict(text, moe_intermediate_size=32, num_experts=4, num_experts_per_tok=2, norm_topk_prob=True,
+                decoder_sparse_step=1, mlp_only_layers=[])
+    try:
+        hf_cfg = tr.Qwen3VLMoeConfig(text_config=dict(text), vision_config=dict(vision), image_token_id=IMG, video_token_id=1002,
+                                     vision_start_token_id=VSTART, vision_end_token_id=1004, tie_word_embeddings=False)
+        hf = tr.Qwen3VLMoeForConditionalGeneration(hf_cfg).float().eval()
+    except Exception as e:  # pragma: no cover
+        pytest.skip(f"transformers Qwen3-VL-MoE unavailable: {e}")
+    with torch.no_grad():   # spread the router so that different tokens pick different experts
+        for n, p in hf.named_parameters():
+            if n.endswith("mlp.gate.weight"):
+                p.copy_(torch.randn_like(p))
+            if "experts" in n:
+                p.copy_(torch.randn_like(p) * 0.05)
+    ns = types.SimpleNamespace(architectures=["Qwen3VLMoeForConditionalGeneration"], model_type="qwen3_vl_moe",
+                               tie_word_embeddings=False, image_token_id=IMG, video_token_id=1002,
+                               vision_start_token_id=VSTART, vision_end_token_id=1004,
+                               text_config=types.SimpleNamespace(tie_word_embeddings=False, **text),
+                               vision_config=types.SimpleNamespace(**vision))
+    mr = ModelRunner(ServerConfig(model_path="preset:x", dtype="float32", max_running_requests=2, max_total_tokens=512),
+                     hf_config=ns, device="cpu")
+    mr.initialize()
+    assert type(mr.model).__name__ == "Qwen3VLMoeForConditionalGeneration"
+    loaded = mr.model.load_weights(hf.state_dict().items())
+    missing = set(dict(mr.model.named_parameters())) - loaded
+    assert not missing, missing
+    for m in mr.model.modules():
+        if hasattr(m, "quant_method"):
+            m._gate_up_interleaved = False
+            m.quant_method.process_weights_after_loading(m)
+        if hasattr(m, "swiglu_block") and hasattr(m, "w13"):
+            m.swiglu_block = 0
+    mr.model.post_load()
+    torch.manual_seed(0)
+    grid = torch.tensor([[1, 4, 6]])
+    pixels = torch.randn(24, 3 * 2 * 16 * 16)
+    ids = torch.tensor([[11, 12, VSTART] + [IMG] * 6 + [1004, 13, 14, 15]])
+    L = ids.shape[1]
+    slots = mr.req_to_token_pool.alloc(1)
+    loc = mr.token_to_kv_pool_allocator.alloc(L)
+    mr.req_to_token_pool.req_to_token[slots[0], :L] = loc.int()
+    lens = torch.tensor([L])
+    fb = mr.prepare_forward_batch_extend(ids.reshape(-1), torch.tensor(slots), lens, lens, torch.zeros_like(lens), loc,
+                                         pixel_values=pixels, image_grid_thw=grid)
+    got = mr.forward(fb).next_token_logits
+    with torch.no_grad():
+        want = hf(input_ids=ids, pixel_values=pixels, image_grid_thw=grid, mm_token_type_ids=(ids == IMG).int()).logits[:, -1]
+    torch.testing.assert_close(got, want, atol=1e-3, rtol=1e-3)
