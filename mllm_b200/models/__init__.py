@@ -12,6 +12,8 @@ _REGISTRY: Dict[str, Tuple[str, str]] = {
     "Qwen3VLMoeForConditionalGeneration": ("mllm_b200.models.qwen3_vl_moe", "Qwen3VLMoeForConditionalGeneration"),
     "Qwen3_5ForCausalLM": ("mllm_b200.models.qwen3_5", "Qwen3_5ForCausalLM"),
     "Qwen3_5ForConditionalGeneration": ("mllm_b200.models.qwen3_5", "Qwen3_5ForConditionalGeneration"),
+    "Qwen3_5MoeForCausalLM": ("mllm_b200.models.qwen3_5_moe", "Qwen3_5MoeForCausalLM"),
+    "Qwen3_5MoeForConditionalGeneration": ("mllm_b200.models.qwen3_5_moe", "Qwen3_5MoeForConditionalGeneration"),
     "LlamaForCausalLM": ("mllm_b200.models.llama", "LlamaForCausalLM"),
     "MistralForCausalLM": ("mllm_b200.models.llama", "MistralForCausalLM"),
     "Qwen2ForCausalLM": ("mllm_b200.models.llama", "Qwen2ForCausalLM"),

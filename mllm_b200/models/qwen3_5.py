@@ -133,10 +133,13 @@ class Qwen3_5DecoderLayer(nn.Module):
             self.linear_attn = GatedDeltaNet(config, layer_id, gdn_index, params_dtype)
         else:
             self.self_attn = Qwen3_5Attention(config, attn_index, params_dtype)
-        self.mlp = MLP(config.hidden_size, config.intermediate_size, quant_config, f"model.layers.{layer_id}.mlp",
-                       params_dtype, reduce_results=True)
+        self.mlp = self._make_mlp(config, layer_id, quant_config, params_dtype)
         self.input_layernorm = GemmaRMSNorm(config.hidden_size, eps, params_dtype)
         self.post_attention_layernorm = GemmaRMSNorm(config.hidden_size, eps, params_dtype)
+
+    def _make_mlp(self, config, layer_id, quant_config, params_dtype):
+        return MLP(config.hidden_size, config.intermediate_size, quant_config, f"model.layers.{layer_id}.mlp",
+                   params_dtype, reduce_results=True)
 
     def forward(self, hidden, residual, fb):
         if residual is None:
@@ -150,12 +153,14 @@ class Qwen3_5DecoderLayer(nn.Module):
 
 
 class Qwen3_5Model(nn.Module):
+    layer_cls = Qwen3_5DecoderLayer
+
     def __init__(self, config, quant_config=None, params_dtype=None) -> None:
         super().__init__()
         self.embed_tokens = VocabParallelEmbedding(config.vocab_size, config.hidden_size, params_dtype, shard=False)
         layers, a, g = [], 0, 0
         for i in range(config.num_hidden_layers):
-            layers.append(Qwen3_5DecoderLayer(config, i, a, g, quant_config, params_dtype))
+            layers.append(self.layer_cls(config, i, a, g, quant_config, params_dtype))
             if config.layer_types[i] == "linear_attention":
                 g += 1
             else:
@@ -177,6 +182,8 @@ class Qwen3_5ForCausalLM(nn.Module):
     """Text model.  ``kv_layers`` tells the runner to size the KV pool for the full-attention layers only;
     the gated-delta-net state pool is created on first use, one row per request slot."""
 
+    model_cls = Qwen3_5Model
+
     def __init__(self, config, quant_config=None, params_dtype: Optional[torch.dtype] = None) -> None:
         super().__init__()
         config = getattr(config, "text_config", config)
@@ -185,7 +192,7 @@ class Qwen3_5ForCausalLM(nn.Module):
             config.layer_types = ["full_attention" if (i + 1) % interval == 0 else "linear_attention"
                                   for i in range(config.num_hidden_layers)]
         self.config = config
-        self.model = Qwen3_5Model(config, quant_config, params_dtype)
+        self.model = self.model_cls(config, quant_config, params_dtype)
         self.tie = bool(getattr(config, "tie_word_embeddings", False))
         if not self.tie:
             self.lm_head = VocabParallelEmbedding(config.vocab_size, config.hidden_size, params_dtype, shard=False)
@@ -244,10 +251,9 @@ class Qwen3_5ForCausalLM(nn.Module):
             if name.startswith("lm_head.") and self.tie:
                 continue
             target = name
-            if ".mlp.gate_proj." in name or ".mlp.up_proj." in name:
-                is_gate = ".mlp.gate_proj." in name
-                target = name.replace(".mlp.gate_proj.", ".mlp.gate_up_proj.") if is_gate else \
-                    name.replace(".mlp.up_proj.", ".mlp.gate_up_proj.")
+            if (".gate_proj." in name or ".up_proj." in name) and ".experts." not in name:
+                is_gate = ".gate_proj." in name
+                target = name.replace(".gate_proj.", ".gate_up_proj.") if is_gate else name.replace(".up_proj.", ".gate_up_proj.")
                 p = params.get(target)
                 if p is None:
                     continue
