@@ -14,6 +14,7 @@ _REGISTRY: Dict[str, Tuple[str, str]] = {
     "Qwen3_5ForConditionalGeneration": ("mllm_b200.models.qwen3_5", "Qwen3_5ForConditionalGeneration"),
     "Qwen3_5MoeForCausalLM": ("mllm_b200.models.qwen3_5_moe", "Qwen3_5MoeForCausalLM"),
     "Qwen3_5MoeForConditionalGeneration": ("mllm_b200.models.qwen3_5_moe", "Qwen3_5MoeForConditionalGeneration"),
+    "Qwen3NextForCausalLM": ("mllm_b200.models.qwen3_next", "Qwen3NextForCausalLM"),
     "LlamaForCausalLM": ("mllm_b200.models.llama", "LlamaForCausalLM"),
     "MistralForCausalLM": ("mllm_b200.models.llama", "MistralForCausalLM"),
     "Qwen2ForCausalLM": ("mllm_b200.models.llama", "Qwen2ForCausalLM"),

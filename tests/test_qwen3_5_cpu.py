@@ -262,3 +262,70 @@ def test_moe_variant_matches_hf():
     with torch.no_grad():
         want = hf(torch.cat([ids, nxt[:, None]], 1)).logits[:, -1]
     torch.testing.assert_close(got, want, atol=1e-3, rtol=1e-3)
+
+
+def test_qwen3_next_matches_hf():
+    """Qwen3-Next: fused per-key-head delta-net projections regrouped by the loader, one dense-MLP layer
+    among the expert layers, 1-D rope."""
+    import types
+
+    import pytest
+    import torch
+
+    from mllm_b200.configs import ServerConfig
+    from mllm_b200.executor import ModelRunner
+
+    tr = pytest.importorskip("transformers")
+    cfgd = dict(vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=4, num_attention_heads=2,
+                num_key_value_heads=1, head_dim=32, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=256,
+                attention_bias=False, linear_conv_kernel_dim=4, linear_key_head_dim=16, linear_value_head_dim=16,
+                linear_num_key_heads=2, linear_num_value_heads=4, hidden_act="silu", moe_intermediate_size=32,
+                shared_expert_intermediate_size=48, num_experts=4, num_experts_per_tok=2, norm_topk_prob=True,
+                decoder_sparse_step=1, mlp_only_layers=[1],
+                layer_types=["linear_attention", "linear_attention", "linear_attention", "full_attention"],
+                rope_parameters=dict(rope_theta=10000.0, partial_rotary_factor=0.25, rope_type="default"))
+    try:
+        hf = tr.Qwen3NextForCausalLM(tr.Qwen3NextConfig(**cfgd)).float().eval()
+    except Exception as e:  # pragma: no cover
+        pytest.skip(f"transformers Qwen3-Next unavailable: {e}")
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith(("layernorm.weight", "q_norm.weight", "k_norm.weight", "model.norm.weight")):
+                p.copy_(torch.randn_like(p) * 0.1)
+            if n.endswith("mlp.gate.weight") or n.endswith("shared_expert_gate.weight"):
+                p.copy_(torch.randn_like(p))
+            if "experts" in n:
+                p.copy_(torch.randn_like(p) * 0.05)
+    ns = types.SimpleNamespace(architectures=["Qwen3NextForCausalLM"], **cfgd)
+    mr = ModelRunner(ServerConfig(model_path="preset:x", dtype="float32", max_running_requests=2, max_total_tokens=256),
+                     hf_config=ns, device="cpu")
+    mr.initialize()
+    assert type(mr.model.model.layers[1].mlp).__name__ == "MLP" and type(mr.model.model.layers[0].mlp).__name__ == "SharedExpertMoE"
+    loaded = mr.model.load_weights(hf.state_dict().items())
+    missing = set(dict(mr.model.named_parameters())) - loaded
+    assert not missing, missing
+    for m in mr.model.modules():
+        if hasattr(m, "quant_method"):
+            m._gate_up_interleaved = False
+            m.quant_method.process_weights_after_loading(m)
+        if hasattr(m, "swiglu_block") and hasattr(m, "w13"):
+            m.swiglu_block = 0
+    mr.model.post_load()
+    torch.manual_seed(0)
+    ids = torch.randint(0, 320, (1, 12))
+    slots = mr.req_to_token_pool.alloc(1)
+    sl = torch.tensor(slots)
+    loc = mr.token_to_kv_pool_allocator.alloc(12)
+    mr.req_to_token_pool.req_to_token[slots[0], :12] = loc.int()
+    lens = torch.tensor([12])
+    got = mr.forward(mr.prepare_forward_batch_extend(ids[0], sl, lens, lens, torch.zeros_like(lens), loc)).next_token_logits
+    with torch.no_grad():
+        want = hf(ids).logits[:, -1]
+    torch.testing.assert_close(got, want, atol=1e-3, rtol=1e-3)
+    nxt = got.argmax(-1)
+    loc1 = mr.token_to_kv_pool_allocator.alloc(1)
+    mr.req_to_token_pool.req_to_token[slots[0], 12] = loc1.int()
+    got = mr.forward(mr.prepare_forward_batch_decode(nxt, sl, torch.tensor([13]), loc1)).next_token_logits
+    with torch.no_grad():
+        want = hf(torch.cat([ids, nxt[:, None]], 1)).logits[:, -1]
+    torch.testing.assert_close(got, want, atol=1e-3, rtol=1e-3)
