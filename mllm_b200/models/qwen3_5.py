@@ -110,6 +110,8 @@ class Qwen3_5Attention(nn.Module):
         if fb.forward_mode.is_decode():
             if fast:
                 o = ops.attention_decode(q, kc, vc, rtt, fb.req_pool_indices, fb.seq_lens, self.scale, max_seq_len=fb.max_seq_len)
+            elif q.is_cuda and fb.max_seq_len:   # no kernel for this head size: one batched pass, no device read-back
+                o = ref.attention_decode_batched(q, kc, vc, rtt, fb.req_pool_indices, fb.seq_lens, self.scale, fb.max_seq_len)
             else:
                 o = ref.attention_decode(q, kc, vc, rtt, fb.req_pool_indices, fb.seq_lens, self.scale)
         else:

@@ -304,6 +304,31 @@ def attention_decode(
     return out
 
 
+def attention_decode_batched(
+    q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, req_to_token: torch.Tensor,
+    req_pool_indices: torch.Tensor, seq_lens: torch.Tensor, scale: float, max_seq_len: int,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """:func:`attention_decode` for the whole batch at once: keys are gathered up to ``max_seq_len`` (a host
+    bound on ``seq_lens``) and the tail of every request is masked, so nothing is read back from the device.
+    Used on GPUs for head sizes the decode kernel does not cover."""
+    B, Hq, D = q.shape
+    Hkv = k_cache.shape[1]
+    S = int(max_seq_len)
+    slots = req_to_token[req_pool_indices.long(), :S].long()                  # [B, S]
+    k = _f32(k_cache[slots])                                                  # [B, S, Hkv, D]
+    v = _f32(v_cache[slots])
+    qg = _f32(q).view(B, Hkv, Hq // Hkv, D)
+    s = torch.einsum("bhgd,bshd->bhgs", qg, k) * scale
+    valid = torch.arange(S, device=q.device).unsqueeze(0) < seq_lens.view(-1, 1)
+    s = s.masked_fill(~valid.view(B, 1, 1, S), float("-inf"))
+    o = torch.einsum("bhgs,bshd->bhgd", torch.softmax(s, dim=-1), v).reshape(B, Hq, D)
+    if out is None:
+        return o.to(q.dtype)
+    out.copy_(o)
+    return out
+
+
 def attention_varlen_bidirectional(q, k, v, cu_seqlens, scale) -> torch.Tensor:
     """Full (non-causal) attention inside each segment ``cu_seqlens[i]..cu_seqlens[i+1]``; q,k,v [T,H,D]."""
     out = torch.empty_like(q)

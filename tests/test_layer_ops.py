@@ -90,3 +90,28 @@ def test_chain_speculative_sampling():
     bad[:, :, 0] = 1
     out, acc, emitted = sampling.chain_speculative_sampling(bad, torch.zeros(B, n, dtype=torch.long), tgt0, seed=1)
     assert (emitted == 0).all() and (out[:, 0] > 0).all() and (out[:, 1:] == -1).all()
+
+
+def test_batched_decode_attention_equals_the_per_request_statement():
+    import torch
+
+    from mllm_b200.ops import reference as ref
+
+    torch.manual_seed(0)
+    B, Hq, Hkv, D, slots_n = 3, 4, 2, 24, 64
+    kc, vc = torch.randn(slots_n, Hkv, D), torch.randn(slots_n, Hkv, D)
+    rtt = torch.zeros(5, 20, dtype=torch.int32)
+    seq = torch.tensor([7, 1, 13], dtype=torch.int32)
+    req = torch.tensor([4, 0, 2], dtype=torch.int32)
+    perm = torch.randperm(slots_n)[: int(seq.sum())].int()
+    off = 0
+    for b in range(B):
+        rtt[req[b], : seq[b]] = perm[off: off + int(seq[b])]
+        off += int(seq[b])
+    q = torch.randn(B, Hq, D)
+    want = ref.attention_decode(q, kc, vc, rtt, req, seq, D ** -0.5)
+    got = ref.attention_decode_batched(q, kc, vc, rtt, req, seq, D ** -0.5, max_seq_len=16)
+    torch.testing.assert_close(got, want, atol=1e-5, rtol=1e-5)
+    out = torch.empty_like(q)
+    ref.attention_decode_batched(q, kc, vc, rtt, req, seq, D ** -0.5, max_seq_len=13, out=out)
+    torch.testing.assert_close(out, want, atol=1e-5, rtol=1e-5)
