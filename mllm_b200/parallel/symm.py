@@ -64,6 +64,13 @@ class SymmetricHeap:
     @classmethod
     def create(cls, nbytes: int, device: torch.device, group) -> "SymmetricHeap":
         """Collective over ``group``: allocates, zeroes and exchanges the mappings once."""
+        import os
+
+        # The kernels of this build reach peers with plain loads / stores / reductions only.  Ask the
+        # symmetric-memory layer not to bind the heap to an NVLink multicast object as well: nothing here
+        # would use it, it is one more collective set-up step per rank, and memory bound to such an
+        # object makes a rank's abnormal exit visible as NVLink faults on its peers.
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
 
         buf = symm.empty((int(nbytes),), dtype=torch.uint8, device=device)
