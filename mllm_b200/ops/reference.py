@@ -270,6 +270,26 @@ def _attend(q, k, v, scale, causal_offset: Optional[int]):
     return torch.einsum("hqk,khd->qhd", p, vv)
 
 
+def _attend_sdpa(q, k, v, scale, causal_offset: Optional[int]):
+    """:func:`_attend` through ``scaled_dot_product_attention`` in the tensors' own dtype (no fp32 score
+    matrix): the fallback used on GPUs for head sizes without a kernel.  q [Tq,Hq,D], k / v [Tk,Hkv,D]."""
+    import torch.nn.functional as F
+
+    Tq, Tk = q.shape[0], k.shape[0]
+    qh, kh, vh = q.transpose(0, 1).unsqueeze(0), k.transpose(0, 1).unsqueeze(0), v.transpose(0, 1).unsqueeze(0)
+    mask, causal = None, False
+    if causal_offset is not None:
+        if causal_offset == 0 and Tq == Tk:
+            causal = True
+        else:
+            i = torch.arange(Tq, device=q.device).unsqueeze(-1)
+            j = torch.arange(Tk, device=q.device).unsqueeze(0)
+            mask = j <= i + causal_offset
+    o = F.scaled_dot_product_attention(qh, kh, vh, attn_mask=mask, is_causal=causal, scale=scale,
+                                       enable_gqa=q.shape[1] != k.shape[1])
+    return o.squeeze(0).transpose(0, 1)
+
+
 def attention_prefill(
     q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, req_to_token: torch.Tensor,
     req_pool_indices: torch.Tensor, seq_lens: torch.Tensor, prefix_lens: torch.Tensor,
@@ -285,7 +305,10 @@ def attention_prefill(
         sl, pl, qs = int(seq_lens[b]), int(prefix_lens[b]), int(q_start_loc[b])
         n = sl - pl
         slots = req_to_token[int(req_pool_indices[b]), :sl].long()
-        o = _attend(_f32(q[qs : qs + n]), _f32(k_cache[slots]), _f32(v_cache[slots]), scale, pl)
+        if q.is_cuda:
+            o = _attend_sdpa(q[qs : qs + n], k_cache[slots].to(q.dtype), v_cache[slots].to(q.dtype), scale, pl)
+        else:
+            o = _attend(_f32(q[qs : qs + n]), _f32(k_cache[slots]), _f32(v_cache[slots]), scale, pl)
         out[qs : qs + n] = o.to(out.dtype)
     return out
 

@@ -115,3 +115,17 @@ def test_batched_decode_attention_equals_the_per_request_statement():
     out = torch.empty_like(q)
     ref.attention_decode_batched(q, kc, vc, rtt, req, seq, D ** -0.5, max_seq_len=13, out=out)
     torch.testing.assert_close(out, want, atol=1e-5, rtol=1e-5)
+
+
+def test_sdpa_fallback_equals_the_softmax_statement():
+    """Rectangular causal (queries after a cached prefix), square causal and unmasked cases, grouped heads."""
+    import torch
+
+    from mllm_b200.ops import reference as ref
+
+    torch.manual_seed(1)
+    for Tq, Tk, off in ((5, 12, 7), (9, 9, 0), (1, 6, None), (4, 4, None)):
+        q, k, v = torch.randn(Tq, 4, 16), torch.randn(Tk, 2, 16), torch.randn(Tk, 2, 16)
+        want = ref._attend(q, k, v, 0.25, off)
+        got = ref._attend_sdpa(q, k, v, 0.25, off)
+        torch.testing.assert_close(got, want, atol=1e-5, rtol=1e-5)
