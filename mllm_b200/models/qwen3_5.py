@@ -118,6 +118,11 @@ class Qwen3_5Attention(nn.Module):
             if fast:
                 o = ops.attention_prefill(q, kc, vc, rtt, fb.req_pool_indices, fb.seq_lens, fb.extend_prefix_lens,
                                           fb.extend_start_loc, self.scale, max_q_len=fb.max_extend_len)
+            elif q.is_cuda:                      # no kernel for this head size: library attention per request
+                ext_cpu, pre_cpu = getattr(fb, "extend_seq_lens_cpu", None), getattr(fb, "extend_prefix_lens_cpu", None)
+                seq_cpu = [a + b for a, b in zip(ext_cpu, pre_cpu)] if ext_cpu is not None and pre_cpu is not None else None
+                o = ref.attention_prefill_sdpa(q, kc, vc, rtt, fb.req_pool_indices, fb.seq_lens, fb.extend_prefix_lens,
+                                               fb.extend_start_loc, self.scale, seq_cpu, pre_cpu)
             else:
                 o = ref.attention_prefill(q, kc, vc, rtt, fb.req_pool_indices, fb.seq_lens, fb.extend_prefix_lens,
                                           fb.extend_start_loc, self.scale)

@@ -305,11 +305,26 @@ def attention_prefill(
         sl, pl, qs = int(seq_lens[b]), int(prefix_lens[b]), int(q_start_loc[b])
         n = sl - pl
         slots = req_to_token[int(req_pool_indices[b]), :sl].long()
-        if q.is_cuda:
-            o = _attend_sdpa(q[qs : qs + n], k_cache[slots].to(q.dtype), v_cache[slots].to(q.dtype), scale, pl)
-        else:
-            o = _attend(_f32(q[qs : qs + n]), _f32(k_cache[slots]), _f32(v_cache[slots]), scale, pl)
+        o = _attend(_f32(q[qs : qs + n]), _f32(k_cache[slots]), _f32(v_cache[slots]), scale, pl)
         out[qs : qs + n] = o.to(out.dtype)
+    return out
+
+
+def attention_prefill_sdpa(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, prefix_lens, q_start_loc,
+                           scale: float, seq_lens_cpu=None, prefix_lens_cpu=None) -> torch.Tensor:
+    """:func:`attention_prefill` with ``scaled_dot_product_attention`` per request in the activation dtype —
+    not a numerical reference but the serving fallback on GPUs for head sizes without a kernel.  The host
+    copies of the lengths avoid device read-backs."""
+    out = torch.empty_like(q)
+    sls = seq_lens_cpu if seq_lens_cpu is not None else seq_lens.tolist()
+    pls = prefix_lens_cpu if prefix_lens_cpu is not None else prefix_lens.tolist()
+    qs = 0
+    pools = req_pool_indices.long()
+    for b, (sl, pl) in enumerate(zip(sls, pls)):
+        n = int(sl) - int(pl)
+        slots = req_to_token[pools[b], : int(sl)].long()
+        out[qs : qs + n] = _attend_sdpa(q[qs : qs + n], k_cache[slots].to(q.dtype), v_cache[slots].to(q.dtype), scale, int(pl))
+        qs += n
     return out
 
 

@@ -129,3 +129,25 @@ def test_sdpa_fallback_equals_the_softmax_statement():
         want = ref._attend(q, k, v, 0.25, off)
         got = ref._attend_sdpa(q, k, v, 0.25, off)
         torch.testing.assert_close(got, want, atol=1e-5, rtol=1e-5)
+
+
+def test_sdpa_prefill_fallback_equals_the_reference_prefill():
+    import torch
+
+    from mllm_b200.ops import reference as ref
+
+    torch.manual_seed(2)
+    Hq, Hkv, D = 4, 2, 16
+    kc, vc = torch.randn(80, Hkv, D), torch.randn(80, Hkv, D)
+    rtt = torch.zeros(4, 32, dtype=torch.int32)
+    seq, pre = torch.tensor([9, 14], dtype=torch.int32), torch.tensor([0, 6], dtype=torch.int32)
+    req = torch.tensor([3, 1], dtype=torch.int32)
+    perm = torch.randperm(80).int()
+    rtt[3, :9], rtt[1, :14] = perm[:9], perm[9:23]
+    q = torch.randn(9 + 8, Hq, D)
+    qs = torch.tensor([0, 9], dtype=torch.int32)
+    want = ref.attention_prefill(q, kc, vc, rtt, req, seq, pre, qs, D ** -0.5)
+    got = ref.attention_prefill_sdpa(q, kc, vc, rtt, req, seq, pre, qs, D ** -0.5)
+    torch.testing.assert_close(got, want, atol=1e-5, rtol=1e-5)
+    got = ref.attention_prefill_sdpa(q, kc, vc, rtt, req, seq, pre, qs, D ** -0.5, [9, 14], [0, 6])
+    torch.testing.assert_close(got, want, atol=1e-5, rtol=1e-5)
