@@ -7,7 +7,13 @@ the classic format stores ``zero - 1``), ``scales`` fp16 ``[K/g, N]`` and ``g_id
 ``w[k, n] = (q[k, n] - zero[k // g, n]) * scale[k // g, n]``.  After loading the tensors are unpacked
 once and laid out K-major like every other 4-bit scheme here — ``weight_packed`` int32 ``[N, K/8]``,
 ``weight_zeros`` uint8 ``[N, K/g]``, ``weight_scale`` ``[N, K/g]`` — and served by the tcgen05 W4A16
-kernel.  ``desc_act`` (activation-order permutation, a non-trivial ``g_idx``) is refused.
+kernel.
+
+``desc_act`` checkpoints (activation order: input channel ``k`` belongs to group ``g_idx[k]``, groups are
+not contiguous) are served by sorting the input channels by group once at load — the weight rows are
+permuted so that groups become contiguous again — and permuting the activation columns the same way before
+every GEMM (the role of the reference's ``permute_cols`` kernel).  Not combined with an input-dimension
+split across tensor-parallel ranks.
 """
 
 from __future__ import annotations
@@ -43,8 +49,8 @@ def pack_words(values: torch.Tensor, dim: int) -> torch.Tensor:
 
 
 class GPTQLinearMethod(LinearMethodBase):
-    def __init__(self, group_size: int, sym: bool, zero_offset: int = 1) -> None:
-        self.group_size, self.sym, self.zero_offset = group_size, sym, zero_offset
+    def __init__(self, group_size: int, sym: bool, zero_offset: int = 1, desc_act: bool = False) -> None:
+        self.group_size, self.sym, self.zero_offset, self.desc_act = group_size, sym, zero_offset, desc_act
 
     def create_weights(self, layer, input_size_per_partition, output_partition_sizes, input_size, output_size,
                        params_dtype, **extra) -> None:
@@ -54,6 +60,9 @@ class GPTQLinearMethod(LinearMethodBase):
             raise ValueError(f"GPTQ: N={n} and K={k} must be divisible by 8, K by the group size {g}")
         if self.group_size == -1 and input_size != input_size_per_partition:
             raise ValueError("GPTQ: per-channel groups (group_size -1) cannot be split along the input dimension")
+        if self.desc_act and input_size != input_size_per_partition:
+            raise ValueError("GPTQ: activation-order checkpoints cannot be split along the input dimension "
+                             "(row-parallel layers under tensor parallelism)")
         qweight = nn.Parameter(torch.zeros(k // 8, n, dtype=torch.int32), requires_grad=False)
         qzeros = nn.Parameter(torch.zeros(k // g, n // 8, dtype=torch.int32), requires_grad=False)
         scales = nn.Parameter(torch.zeros(k // g, n, dtype=params_dtype), requires_grad=False)
@@ -75,6 +84,16 @@ class GPTQLinearMethod(LinearMethodBase):
             return
         q = unpack_words(layer.qweight.data, 0)                      # [K, N]
         z = unpack_words(layer.qzeros.data, 1)                       # [K/g, N]
+        perm_buf = None
+        g_idx = layer.g_idx.data.long()
+        contiguous = torch.arange(g_idx.numel(), device=g_idx.device) // layer.w4_group
+        if self.desc_act and not torch.equal(g_idx, contiguous):
+            perm = torch.argsort(g_idx, stable=True)                 # input channels grouped by their scale group
+            if not torch.equal(g_idx[perm], contiguous):
+                raise ValueError("GPTQ: g_idx does not assign exactly group_size channels to every group")
+            q = q[perm]
+            perm_buf = perm.to(torch.int64)
+        layer.register_buffer("act_perm", perm_buf, persistent=False)
         z = ((z.to(torch.int16) + self.zero_offset) & 0xF).to(torch.uint8)
         packed = pack_rows_natural(q.t().contiguous())               # [N, K/8]
         zeros = z.t().contiguous()                                   # [N, K/g]
@@ -86,6 +105,9 @@ class GPTQLinearMethod(LinearMethodBase):
         layer.register_parameter("weight_scale", nn.Parameter(scale, requires_grad=False))
 
     def apply(self, layer, x, bias=None, residual=None):
+        perm = getattr(layer, "act_perm", None)
+        if perm is not None:
+            x = x.index_select(-1, perm)
         y = ops.w4a16_gemm(x, layer.weight_packed, layer.weight_scale, layer.weight_zeros, layer.w4_group, bias)
         return y if residual is None else y + residual
 
@@ -98,9 +120,9 @@ class GPTQConfig(QuantizationConfig):
             raise ValueError(f"GPTQ: only 4-bit weights are supported, got {weight_bits}")
         if group_size not in (-1, 32, 64, 128):
             raise ValueError(f"GPTQ: unsupported group size {group_size}")
-        if desc_act:
-            raise ValueError("GPTQ: desc_act (activation-order) checkpoints are not supported")
-        self.weight_bits, self.group_size, self.sym = weight_bits, group_size, sym
+        if desc_act and group_size == -1:
+            desc_act = False      # one group: the order of the input channels does not matter
+        self.weight_bits, self.group_size, self.sym, self.desc_act = weight_bits, group_size, sym, bool(desc_act)
         # "gptq_v2" files store the zero point itself, the classic format stores zero - 1
         self.zero_offset = 0 if checkpoint_format == "gptq_v2" else 1
         self.modules_to_not_convert = modules_to_not_convert or []
@@ -121,7 +143,7 @@ class GPTQConfig(QuantizationConfig):
     def get_quant_method(self, layer: Any, prefix: str = "") -> Optional[LinearMethodBase]:
         if any(m and m in prefix for m in self.modules_to_not_convert) or "lm_head" in prefix:
             return UnquantizedLinearMethod()
-        return GPTQLinearMethod(self.group_size, self.sym, self.zero_offset)
+        return GPTQLinearMethod(self.group_size, self.sym, self.zero_offset, self.desc_act)
 
 
 register_quantization("gptq_marlin")(GPTQConfig)

@@ -169,9 +169,18 @@ def test_gptq_layout_linear_and_tensor_parallel_shards():
     v2 = get_quantization_config("gptq").from_config({"bits": 4, "group_size": g, "checkpoint_format": "gptq_v2"})
     assert v2.get_quant_method(None, "l").zero_offset == 0 and cfg.get_quant_method(None, "l").zero_offset == 1
     with pytest.raises(ValueError):
-        get_quantization_config("gptq").from_config({"bits": 4, "group_size": g, "desc_act": True})
-    with pytest.raises(ValueError):
         get_quantization_config("gptq").from_config({"bits": 8, "group_size": g})
+    # activation order: channel k belongs to group g_idx[k]; rows sorted by group at load, x permuted at run time
+    act = get_quantization_config("gptq").from_config({"bits": 4, "group_size": g, "sym": False, "desc_act": True})
+    gi = (torch.arange(K) // g)[torch.randperm(K)].to(torch.int32)
+    w_act = (q.float() - z.float()[gi.long()]) * s[gi.long()]                            # [K, N]
+    lin_a = Linear(K, N, quant_method=act.get_quant_method(None, "l"), params_dtype=torch.float32)
+    for name, t in dict(tensors, g_idx=gi).items():
+        p = getattr(lin_a, name)
+        p.weight_loader(p, t)
+    lin_a.quant_method.process_weights_after_loading(lin_a)
+    assert lin_a.act_perm is not None
+    torch.testing.assert_close(lin_a(x), x @ w_act, atol=1e-4, rtol=1e-4)
 
     # shards as a 2-rank job would load them
     import mllm_b200.parallel.state as pstate
