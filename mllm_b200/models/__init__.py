@@ -18,6 +18,7 @@ _REGISTRY: Dict[str, Tuple[str, str]] = {
     "LlamaForCausalLM": ("mllm_b200.models.llama", "LlamaForCausalLM"),
     "MistralForCausalLM": ("mllm_b200.models.llama", "MistralForCausalLM"),
     "Qwen2ForCausalLM": ("mllm_b200.models.llama", "Qwen2ForCausalLM"),
+    "Qwen2VLForConditionalGeneration": ("mllm_b200.models.qwen2_vl", "Qwen2VLForConditionalGeneration"),
     "SmolLM3ForCausalLM": ("mllm_b200.models.llama", "SmolLM3ForCausalLM"),
 }
 

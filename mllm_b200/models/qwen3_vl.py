@@ -63,9 +63,11 @@ class VisionMLP(nn.Module):
         super().__init__()
         self.linear_fc1 = _Linear(dim, inter, dtype)
         self.linear_fc2 = _Linear(inter, dim, dtype)
-        self.act = ops.gelu_tanh if act == "gelu_pytorch_tanh" else (ops.gelu_erf if act == "gelu" else None)
-        if self.act is None:
+        acts = {"gelu_pytorch_tanh": ops.gelu_tanh, "gelu": ops.gelu_erf,
+                "quick_gelu": lambda x: x * torch.sigmoid(1.702 * x)}
+        if act not in acts:
             raise ValueError(f"unsupported vision activation {act!r}")
+        self.act = acts[act]
 
     def forward(self, x):
         return self.linear_fc2(self.act(self.linear_fc1(x)))
@@ -132,15 +134,17 @@ class Qwen3VLVisionModel(nn.Module):
         self.spatial_merge_size = getattr(vc, "spatial_merge_size", 2)
         self.in_channels = getattr(vc, "in_channels", 3)
         self.deepstack_visual_indexes = list(getattr(vc, "deepstack_visual_indexes", None) or [])
-        self.num_position_embeddings = vc.num_position_embeddings
-        self.side = int(vc.num_position_embeddings ** 0.5)
+        # towers without a learned position table (Qwen2-VL) rely on the 2-D rotary embedding alone
+        self.num_position_embeddings = int(getattr(vc, "num_position_embeddings", 0) or 0)
+        self.side = int(self.num_position_embeddings ** 0.5)
         eps = getattr(vc, "norm_eps", 1e-6)
         patch_dim = self.in_channels * self.temporal_patch_size * self.patch_size * self.patch_size
         self.patch_embed = nn.Module()
         self.patch_embed.proj = _Linear(patch_dim, vc.hidden_size, dtype)  # Conv3d with kernel == stride
-        self.pos_embed = nn.Module()
-        self.pos_embed.weight = nn.Parameter(torch.empty(vc.num_position_embeddings, vc.hidden_size, dtype=dtype),
-                                             requires_grad=False)
+        if self.num_position_embeddings:
+            self.pos_embed = nn.Module()
+            self.pos_embed.weight = nn.Parameter(torch.empty(self.num_position_embeddings, vc.hidden_size, dtype=dtype),
+                                                 requires_grad=False)
         self.blocks = nn.ModuleList(
             VisionBlock(vc.hidden_size, vc.num_heads, vc.intermediate_size, getattr(vc, "hidden_act", "gelu_pytorch_tanh"),
                         eps, dtype) for _ in range(vc.depth))
@@ -182,8 +186,9 @@ class Qwen3VLVisionModel(nn.Module):
         grids = grid_thw.tolist() if isinstance(grid_thw, torch.Tensor) else [list(g) for g in grid_thw]
         w = self.patch_embed.proj.weight
         x = self.patch_embed.proj(pixel_values.to(device=w.device, dtype=w.dtype).reshape(pixel_values.shape[0], -1))
-        idx, wts = self.pos_embed_indices(grids, w.device)
-        x = ops.vision_pos_embed_add(x, self.pos_embed.weight, idx, wts)
+        if self.num_position_embeddings:
+            idx, wts = self.pos_embed_indices(grids, w.device)
+            x = ops.vision_pos_embed_add(x, self.pos_embed.weight, idx, wts)
         cos, sin = self.rotary_cos_sin(grids, w.device)
         lens = np.repeat([g[1] * g[2] for g in grids], [g[0] for g in grids])
         cu = torch.from_numpy(np.concatenate([[0], np.cumsum(lens)]).astype(np.int32))
