@@ -19,6 +19,7 @@ _REGISTRY: Dict[str, Tuple[str, str]] = {
     "MistralForCausalLM": ("mllm_b200.models.llama", "MistralForCausalLM"),
     "Qwen2ForCausalLM": ("mllm_b200.models.llama", "Qwen2ForCausalLM"),
     "Qwen2VLForConditionalGeneration": ("mllm_b200.models.qwen2_vl", "Qwen2VLForConditionalGeneration"),
+    "Qwen2_5_VLForConditionalGeneration": ("mllm_b200.models.qwen2_5_vl", "Qwen2_5_VLForConditionalGeneration"),
     "SmolLM3ForCausalLM": ("mllm_b200.models.llama", "SmolLM3ForCausalLM"),
 }
 

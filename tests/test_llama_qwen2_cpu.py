@@ -175,3 +175,66 @@ def test_qwen2_vl_matches_hf():
         except TypeError:
             want2 = hf(input_ids=ids2, pixel_values=pixels, image_grid_thw=grid).logits[:, -1]
     torch.testing.assert_close(got2, want2, atol=5e-4, rtol=5e-4)
+
+
+def test_qwen2_5_vl_matches_hf():
+    """Qwen2.5-VL: windowed vision attention (an image larger than one window, with ragged edge windows),
+    one full-attention block, RMSNorm + SwiGLU tower, window order undone after the merger."""
+    tr = pytest.importorskip("transformers")
+    IMG, VSTART, VEND = 301, 302, 303
+    text = dict(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=2, rms_norm_eps=1e-6, max_position_embeddings=256, hidden_act="silu", rope_theta=10000.0,
+                rope_scaling=dict(type="mrope", mrope_section=[2, 3, 3]), tie_word_embeddings=False)
+    vision = dict(depth=3, hidden_size=32, hidden_act="silu", intermediate_size=48, num_heads=2, in_channels=3, patch_size=14,
+                  spatial_merge_size=2, temporal_patch_size=2, window_size=56, out_hidden_size=64, fullatt_block_indexes=[1],
+                  # An image is one temporal step, so its temporal position is the position where the image starts,
+                  # as in the model's original definition.  The transformers version at hand multiplies that start
+                  # position by tokens_per_second for images; 1 makes the two definitions coincide.
+                  tokens_per_second=1)
+    try:
+        hf_cfg = tr.Qwen2_5_VLConfig(text_config=dict(text), vision_config=dict(vision), image_token_id=IMG, video_token_id=304,
+                                     vision_start_token_id=VSTART, vision_end_token_id=VEND, tie_word_embeddings=False)
+        hf = tr.Qwen2_5_VLForConditionalGeneration(hf_cfg).float().eval()
+    except Exception as e:  # pragma: no cover
+        pytest.skip(f"transformers Qwen2.5-VL unavailable: {e}")
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith(".bias"):
+                p.copy_(torch.randn_like(p) * 0.05)
+            if "visual" in n and n.endswith(("norm1.weight", "norm2.weight", "ln_q.weight")):
+                p.copy_(1 + torch.randn_like(p) * 0.1)
+    ns = types.SimpleNamespace(architectures=["Qwen2_5_VLForConditionalGeneration"], model_type="qwen2_5_vl",
+                               tie_word_embeddings=False, image_token_id=IMG, video_token_id=304, vision_start_token_id=VSTART,
+                               vision_end_token_id=VEND, text_config=types.SimpleNamespace(head_dim=16, **text),
+                               vision_config=types.SimpleNamespace(**vision))
+    mr = ModelRunner(ServerConfig(model_path="preset:x", dtype="float32", max_running_requests=2, max_total_tokens=256),
+                     hf_config=ns, device="cpu")
+    mr.initialize()
+    loaded = mr.model.load_weights(hf.state_dict().items())
+    missing = {n for n in set(dict(mr.model.named_parameters())) - loaded if not n.endswith("patch_embed.proj.bias")}
+    assert not missing, missing
+    for m in mr.model.modules():
+        if hasattr(m, "quant_method"):
+            m._gate_up_interleaved = False
+            m.quant_method.process_weights_after_loading(m)
+    torch.manual_seed(0)
+    grid = torch.tensor([[1, 6, 10]])                    # 3 x 5 merged tokens, windows of 2 x 2 merged tokens
+    n_img = 15
+    pixels = torch.randn(60, 3 * 2 * 14 * 14)
+    ids = torch.tensor([[11, 12, VSTART] + [IMG] * n_img + [VEND, 13, 14, 15]])
+    L = ids.shape[1]
+    slots = mr.req_to_token_pool.alloc(1)
+    loc = mr.token_to_kv_pool_allocator.alloc(L)
+    mr.req_to_token_pool.req_to_token[slots[0], :L] = loc.int()
+    lens = torch.tensor([L])
+    fb = mr.prepare_forward_batch_extend(ids.reshape(-1), torch.tensor(slots), lens, lens, torch.zeros_like(lens), loc,
+                                         pixel_values=pixels, image_grid_thw=grid)
+    got = mr.forward(fb).next_token_logits
+    with torch.no_grad():
+        feats = hf.model.visual(pixels, grid_thw=grid).pooler_output
+        try:
+            want = hf(input_ids=ids, pixel_values=pixels, image_grid_thw=grid, mm_token_type_ids=(ids == IMG).int()).logits[:, -1]
+        except TypeError:
+            want = hf(input_ids=ids, pixel_values=pixels, image_grid_thw=grid).logits[:, -1]
+    torch.testing.assert_close(mr.model.visual(pixels, grid), feats, atol=5e-4, rtol=5e-4)
+    torch.testing.assert_close(got, want, atol=5e-4, rtol=5e-4)
