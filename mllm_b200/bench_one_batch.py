@@ -236,7 +236,7 @@ class BenchRunner:
         if sc.world_size > 1:
             pstate.init_distributed()
             if not pstate.model_parallel_is_initialized():
-                pstate.initialize_model_parallel(tp_size=sc.tp_size, ep_size=sc.ep_size)
+                pstate.initialize_model_parallel(tp_size=sc.tp_size, ep_size=sc.ep_size, pp_size=sc.pp_size)
         import os
 
         gpu = sc.base_gpu_id + int(os.environ.get("LOCAL_RANK", "0"))

@@ -55,6 +55,7 @@ class ServerConfig:
     tp_size: int = 1
     ep_size: int = 1
     dp_size: int = 1
+    pp_size: int = 1
     # "fused": GEMMs push/pull their collective over NVLink peer memory from
     # inside the kernel; "nccl": plain NCCL collectives after each GEMM.
     comm_backend: Literal["fused", "nccl"] = "fused"
@@ -147,11 +148,11 @@ class ServerConfig:
             self.schedule_conservativeness > 0,
             "`schedule_conservativeness` must be > 0.",
         )
-        for name in ("tp_size", "ep_size", "dp_size"):
+        for name in ("tp_size", "ep_size", "dp_size", "pp_size"):
             v = getattr(self, name)
             need(v >= 1 and (v & (v - 1)) == 0, f"`{name}` must be a power of two >= 1.")
 
     @property
     def world_size(self) -> int:
-        """GPU processes of one engine replica (EP reuses the TP ranks)."""
-        return max(self.tp_size, self.ep_size)
+        """GPU processes of one engine replica (EP reuses the TP ranks; pipeline stages multiply them)."""
+        return max(self.tp_size, self.ep_size) * self.pp_size

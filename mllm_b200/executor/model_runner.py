@@ -269,6 +269,17 @@ class ModelRunner:
         tc = text_config_of(self.hf_config)
         tp = pstate.get_tensor_model_parallel_world_size()
         self.num_hidden_layers = tc.num_hidden_layers
+        # layers that keep K/V on this rank: the full-attention layers of a hybrid model, this stage's run of
+        # layers under pipeline parallelism
+        self.kv_layer_offset = 0
+        self.num_kv_layers = int(getattr(self.model, "kv_layers", 0) or tc.num_hidden_layers)
+        if pstate.get_pipeline_parallel_world_size() > 1:
+            if hasattr(self.model, "kv_layers") or not hasattr(getattr(self.model, "model", None), "pp_layers"):
+                raise NotImplementedError(f"{type(self.model).__name__} does not support pipeline parallelism")
+            if pstate.get_tensor_model_parallel_world_size() > 1 and self.server_config.comm_backend == "fused":
+                raise NotImplementedError("pipeline stages hand over plain tensors: use --server.comm_backend nccl with tp_size > 1")
+            stage = self.model.model.pp_layers
+            self.kv_layer_offset, self.num_kv_layers = stage.start, len(stage)
         self.head_dim = getattr(tc, "head_dim", None) or tc.hidden_size // tc.num_attention_heads
         self.num_kv_heads_total = tc.num_key_value_heads
         self.num_kv_heads = max(1, tc.num_key_value_heads // tp)
@@ -409,7 +420,7 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ memory
     def cell_bytes(self) -> int:
-        return KVPool.cell_bytes(self.num_hidden_layers, self.num_kv_heads, self.head_dim, self.kv_cache_dtype)
+        return KVPool.cell_bytes(self.num_kv_layers, self.num_kv_heads, self.head_dim, self.kv_cache_dtype)
 
     def _profile_max_num_tokens(self) -> MemoryProfileResult:
         frac = self.server_config.mem_fraction_static or 0.85
@@ -437,8 +448,8 @@ class ModelRunner:
         self.max_total_num_tokens = tokens
         self.max_running_requests = max(int(self.server_config.max_running_requests or 1), 1)
         self.req_to_token_pool = ReqToTokenPool(self._num_req_slots(), self.context_len + 4, self.device)
-        self.token_to_kv_pool = KVPool(tokens, self.num_hidden_layers, self.num_kv_heads, self.head_dim,
-                                       self.kv_cache_dtype, self.device, page_size=page)
+        self.token_to_kv_pool = KVPool(tokens, self.num_kv_layers, self.num_kv_heads, self.head_dim,
+                                       self.kv_cache_dtype, self.device, page_size=page, layer_offset=self.kv_layer_offset)
         self.token_to_kv_pool_allocator = TokenToKVPoolAllocator(tokens, page_size=page, device=self.device)
         logger.info("KV pool: %d tokens, %.2f GiB (%d B/token)", tokens, tokens * prof.cell_bytes / (1 << 30),
                     prof.cell_bytes)
@@ -446,6 +457,8 @@ class ModelRunner:
     def init_cuda_graphs(self) -> None:
         if self.device.type != "cuda" or self.server_config.disable_cuda_graph:
             return
+        if pstate.get_pipeline_parallel_world_size() > 1:
+            return      # stages exchange activations with point-to-point calls between the layers: eager only
         from .cuda_graph_runner import CudaGraphRunner
 
         self.cuda_graph_runner = CudaGraphRunner(self)
@@ -512,7 +525,18 @@ class ModelRunner:
     @torch.no_grad()
     def sample(self, logits_output: LogitsProcessorOutput, info: Optional[SamplingBatchInfo] = None) -> torch.Tensor:
         """penalties -> greedy argmax when every temperature is ~0 -> temperature softmax + top-k/top-p/min-p."""
+        pp = pstate.get_pp_group()
+        if pp.world_size == 1:
+            return self._sample_local(logits_output.next_token_logits, info)
+        # pipeline parallelism: the last stage has the logits and samples; every stage gets the ids
         logits = logits_output.next_token_logits
+        if getattr(logits_output, "pp_placeholder", False):
+            ids = torch.zeros(logits.shape[0], dtype=torch.int64, device=logits.device)
+        else:
+            ids = self._sample_local(logits, info).to(torch.int64)
+        return pp.broadcast(ids, src=pp.world_size - 1)
+
+    def _sample_local(self, logits: torch.Tensor, info: Optional[SamplingBatchInfo] = None) -> torch.Tensor:
         if info is None or (info.all_greedy and not info.has_penalties):
             return ops.argmax(logits)
         if info.has_penalties:

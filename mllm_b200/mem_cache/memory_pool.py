@@ -39,7 +39,11 @@ class KVPool:
         device: torch.device | str,
         page_size: int = 1,
         v_head_dim: Optional[int] = None,
+        layer_offset: int = 0,
     ) -> None:
+        # ``layer_offset``: global index of the first layer held here (a pipeline stage keeps K/V only for its
+        # own layers, which address the pool by their global index)
+        self.layer_offset = int(layer_offset)
         if v_head_dim is not None and v_head_dim != head_dim:
             raise ValueError("K and V head widths must match in this pool")
         self.page_size = int(page_size)
@@ -63,13 +67,13 @@ class KVPool:
         return 2 * layer_num * kv_heads * head_dim * torch.empty((), dtype=dtype).element_size()
 
     def get_key_buffer(self, layer_id: int) -> torch.Tensor:
-        return self.k_buffer[layer_id]
+        return self.k_buffer[layer_id - self.layer_offset]
 
     def get_value_buffer(self, layer_id: int) -> torch.Tensor:
-        return self.v_buffer[layer_id]
+        return self.v_buffer[layer_id - self.layer_offset]
 
     def get_kv_buffer(self, layer_id: int) -> Tuple[torch.Tensor, torch.Tensor]:
-        return self.k_buffer[layer_id], self.v_buffer[layer_id]
+        return self.k_buffer[layer_id - self.layer_offset], self.v_buffer[layer_id - self.layer_offset]
 
     def set_kv_buffer(self, layer_id: int, loc: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
         """Scatter rows ``k[i]``/``v[i]`` to slot ``loc[i]``.
@@ -84,8 +88,8 @@ class KVPool:
             k.view(-1, self.kv_heads, self.head_dim),
             v.view(-1, self.kv_heads, self.head_dim),
             loc,
-            self.k_buffer[layer_id],
-            self.v_buffer[layer_id],
+            self.k_buffer[layer_id - self.layer_offset],
+            self.v_buffer[layer_id - self.layer_offset],
         )
 
     def clear(self) -> None:

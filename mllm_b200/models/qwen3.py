@@ -32,6 +32,9 @@ from ..parallel.symm import get_tp_comm
 class LogitsProcessorOutput:
     next_token_logits: torch.Tensor
     hidden_states: Optional[torch.Tensor] = None
+    # pipeline parallelism: on every stage but the last the logits are a [rows, 1] stand-in and the sampled
+    # ids arrive from the last stage
+    pp_placeholder: bool = False
 
 
 def _quant_method(quant_config, prefix: str):
@@ -160,26 +163,41 @@ class Qwen3Model(nn.Module):
         # and the decode step can be captured in a CUDA graph without library collectives inside.
         tied = bool(getattr(config, "tie_word_embeddings", False))
         self.embed_tokens = VocabParallelEmbedding(config.vocab_size, config.hidden_size, params_dtype, shard=tied)
+        # pipeline parallelism: a stage builds (and loads) only its own run of layers; the others are empty
+        # placeholders so that layer indices in parameter names stay global
+        self.pp_layers = pstate.pp_layer_range(config.num_hidden_layers)
         self.layers = nn.ModuleList(
             self.layer_cls(config, i, quant_config, f"{prefix}.layers.{i}", params_dtype, **attn_kw)
+            if i in self.pp_layers else nn.Identity()
             for i in range(config.num_hidden_layers)
         )
         self.norm = RMSNorm(config.hidden_size, getattr(config, "rms_norm_eps", 1e-6), params_dtype)
 
     def forward(self, input_ids: torch.Tensor, positions: torch.Tensor, forward_batch: ForwardBatch,
                 input_embeds: Optional[torch.Tensor] = None, deepstack_embeds=None) -> torch.Tensor:
-        hidden = self.embed_tokens(input_ids) if input_embeds is None else input_embeds
-        residual = None
+        staged = pstate.get_pipeline_parallel_world_size() > 1
+        if not staged or pstate.pp_is_first_stage():
+            hidden = self.embed_tokens(input_ids) if input_embeds is None else input_embeds
+            residual = None
+        else:
+            # the block output of the previous stage (partial sums under TP) and its residual stream
+            w = self.norm.weight
+            hidden = pstate.pp_recv_prev(torch.empty((input_ids.shape[0], w.shape[0]), dtype=w.dtype, device=w.device))
+            residual = pstate.pp_recv_prev(torch.empty_like(hidden))
         comm = get_tp_comm()
         if comm is not None:
             # deepstack injection adds to the block output, which the fused prefill step never materialises
             comm.prefill_fusion = deepstack_embeds is None
-        for i, layer in enumerate(self.layers):
-            hidden, residual = layer(hidden, residual, forward_batch)
+        for i in self.pp_layers:
+            hidden, residual = self.layers[i](hidden, residual, forward_batch)
             if deepstack_embeds is not None and i < len(deepstack_embeds):
                 # the MLP output is a partial sum under TP: inject on one rank only so it is counted once
                 if pstate.get_tensor_model_parallel_rank() == 0:
                     hidden = hidden + deepstack_embeds[i]
+        if staged and not pstate.pp_is_last_stage():
+            pstate.pp_send_next(hidden)
+            pstate.pp_send_next(residual)
+            return None
         if residual is None:
             return self.norm(hidden)
         tp = pstate.get_tensor_model_parallel_world_size() > 1
@@ -233,6 +251,9 @@ class Qwen3ForCausalLM(nn.Module):
                 input_embeds: Optional[torch.Tensor] = None) -> LogitsProcessorOutput:
         t0 = time.perf_counter()
         hidden = self.model(input_ids, positions, forward_batch, input_embeds)
+        if hidden is None:   # not the last pipeline stage: the sampled ids will come from there
+            rows = forward_batch.batch_size
+            return LogitsProcessorOutput(next_token_logits=torch.zeros((rows, 1), device=input_ids.device), pp_placeholder=True)
         out = LogitsProcessorOutput(next_token_logits=self.compute_logits(hidden, forward_batch))
         ms = (time.perf_counter() - t0) * 1e3
         if forward_batch.forward_mode.is_decode():

@@ -79,6 +79,8 @@ class Scheduler:
             return f"prompt of {len(ids)} tokens exceeds the KV pool ({self.mrp.runner.max_total_num_tokens} tokens)"
         if self.cfg.max_queued_requests is not None and len(self.waiting) >= self.cfg.max_queued_requests:
             return "queue full"
+        if t.return_logprob and getattr(self.cfg, "pp_size", 1) > 1:
+            return "log-probabilities are not available with pipeline parallelism (the logits live on the last stage)"
         stop_ids = set(sp.stop_token_ids or [])
         if not sp.ignore_eos:
             stop_ids |= self.eos_token_ids
@@ -325,7 +327,8 @@ def build_scheduler(server_config: ServerConfig, hf_config=None, quantization_me
     if server_config.world_size > 1:
         pstate.init_distributed()
         if not pstate.model_parallel_is_initialized():
-            pstate.initialize_model_parallel(tp_size=server_config.tp_size, ep_size=server_config.ep_size)
+            pstate.initialize_model_parallel(tp_size=server_config.tp_size, ep_size=server_config.ep_size,
+                                              pp_size=server_config.pp_size)
     gpu = server_config.base_gpu_id + int(os.environ.get("LOCAL_RANK", "0"))
     runner = ModelRunner(server_config, hf_config=hf_config, gpu_id=gpu, quantization_method=quantization_method,
                          kv_cache_dtype=kv_cache_dtype, device=device)

@@ -120,10 +120,12 @@ def initialize_model_parallel(tp_size: int = 1, dp_size: int = 1, pp_size: int =
         assert mine is not None
         return mine
 
+    # Rank layout inside one replica: tensor-parallel ranks are adjacent, pipeline stages are tp_size apart
+    # (rank = stage * tp_size + tp_rank); data-parallel replicas are tp_size * pp_size apart.
     _TP = make([list(range(i * tp_size, (i + 1) * tp_size)) for i in range(world // tp_size)])
-    n_dp_groups = world // dp_size
-    _DP = make([list(range(i, world, n_dp_groups)) for i in range(n_dp_groups)])
-    _PP = make([list(range(i * pp_size, (i + 1) * pp_size)) for i in range(world // pp_size)])
+    block = tp_size * pp_size
+    _PP = make([[rep * block + t + s * tp_size for s in range(pp_size)] for rep in range(world // block) for t in range(tp_size)])
+    _DP = make([[r + rep * block for rep in range(dp_size)] for r in range(block)])
     _EP = _TP if ep_size == tp_size else _SOLO
     _INITIALISED = True
 
@@ -152,6 +154,40 @@ def get_pp_group() -> GroupCoordinator:
 
 def get_ep_group() -> GroupCoordinator:
     return _EP
+
+
+def get_pipeline_parallel_rank() -> int:
+    return _PP.rank_in_group
+
+
+def get_pipeline_parallel_world_size() -> int:
+    return _PP.world_size
+
+
+def pp_is_first_stage() -> bool:
+    return _PP.rank_in_group == 0
+
+
+def pp_is_last_stage() -> bool:
+    return _PP.rank_in_group == _PP.world_size - 1
+
+
+def pp_send_next(t: torch.Tensor) -> None:
+    """Point-to-point send of ``t`` to the same tensor-parallel rank of the next pipeline stage."""
+    dist.send(t.contiguous(), dst=_PP.ranks[_PP.rank_in_group + 1], group=_PP.group)
+
+
+def pp_recv_prev(t: torch.Tensor) -> torch.Tensor:
+    dist.recv(t, src=_PP.ranks[_PP.rank_in_group - 1], group=_PP.group)
+    return t
+
+
+def pp_layer_range(num_layers: int) -> range:
+    """The layers this pipeline stage owns: contiguous, the first ``num_layers % stages`` stages get one more."""
+    n, r = _PP.world_size, _PP.rank_in_group
+    base, extra = divmod(num_layers, n)
+    lo = r * base + min(r, extra)
+    return range(lo, lo + base + (1 if r < extra else 0))
 
 
 def get_tensor_model_parallel_rank() -> int:

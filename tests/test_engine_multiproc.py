@@ -191,3 +191,24 @@ def test_router_sends_tensor_requests_through_the_shared_queue():
     back = _take_from_shared_queue(q, sink.got[1])
     assert back.rid == "img" and back.mm_inputs == {"pixel_values": [1.0, 2.0]} and back.input_ids == [1, 2, 3]
     assert "error" in _take_from_shared_queue(None, sink.got[1])
+
+
+def test_two_pipeline_stages_engine_on_cpu():
+    """Two scheduler / model-runner ranks as pipeline stages behind one tokenizer / detokenizer pair:
+    requests complete, batches of several requests work, repeated prompts reproduce their tokens, and a
+    request for log-probabilities is refused with a clear message (the logits live on the last stage)."""
+    cfg = _cfg()
+    cfg.pp_size = 2
+    eng = Engine(cfg, mode="multiproc", device="cpu").launch()
+    try:
+        assert len(eng._procs) == 4      # tokenizer, two stages, detokenizer
+        sp = {"max_new_tokens": 6, "temperature": 0.0}
+        first = eng.generate(["hello", "the quick brown fox", "a"], sp, timeout=180)
+        assert all(len(r["output_ids"]) == 6 and r["meta_info"]["finish_reason"] == "length" for r in first)
+        again = eng.generate(["hello", "the quick brown fox", "a"], sp, timeout=180)
+        assert [r["output_ids"] for r in again] == [r["output_ids"] for r in first]
+        with pytest.raises(ValueError, match="pipeline"):
+            eng.generate("hello", sp, timeout=60, return_logprob=True)
+        assert eng.is_healthy
+    finally:
+        eng.shutdown()

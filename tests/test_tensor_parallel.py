@@ -58,6 +58,24 @@ def test_tp2_fused_prefill_matches_nccl_on_gpu(tmp_path):
     assert (fused.argmax(-1) == ref.argmax(-1)).float().mean().item() > 0.8
 
 
+@pytest.mark.parametrize("preset", ["qwen3-tiny", "qwen3-moe-tiny"])
+def test_pp2_matches_single_rank_on_cpu(tmp_path, preset):
+    """Two pipeline stages (gloo ranks): each builds and loads its own layers, hidden state and residual go
+    from stage to stage, the last stage computes logits and shares the sampled ids; prefill and decode logits
+    equal the single-rank model's."""
+    env = {"TP_TEST_PRESET": preset}
+    one = _launch(1, str(tmp_path / "pp1.pt"), "cpu", "float32", 29651, env)
+    two = _launch(2, str(tmp_path / "pp2.pt"), "cpu", "float32", 29652, dict(env, TP_TEST_PP="2"))
+    torch.testing.assert_close(two, one, atol=2e-4, rtol=2e-4)
+
+
+def test_tp2_pp2_matches_single_rank_on_cpu(tmp_path):
+    """Four ranks: two pipeline stages of two tensor-parallel ranks each (collective-library path)."""
+    one = _launch(1, str(tmp_path / "a.pt"), "cpu", "float32", 29655)
+    four = _launch(4, str(tmp_path / "b.pt"), "cpu", "float32", 29656, {"TP_TEST_PP": "2", "TP_TEST_COMM": "nccl"})
+    torch.testing.assert_close(four, one, atol=3e-4, rtol=3e-4)
+
+
 def test_tp2_loads_only_its_slices_from_safetensors(tmp_path):
     """Two ranks loading one safetensors file through slice handles: logits equal the single-rank model
     loaded from the same tensors, and each rank reads clearly less than the whole file (the sharded

@@ -86,8 +86,10 @@ def run(out_path: str, device: str, dtype_name: str) -> None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     pstate.init_distributed(backend="gloo" if device == "cpu" else "nccl", timeout_s=120)
+    pp = int(os.environ.get("TP_TEST_PP", "1"))
     if world > 1:
-        pstate.initialize_model_parallel(tp_size=world, ep_size=world if os.environ.get("TP_TEST_EP") == "1" else 1)
+        pstate.initialize_model_parallel(tp_size=world // pp, pp_size=pp,
+                                         ep_size=world if os.environ.get("TP_TEST_EP") == "1" else 1)
     dev = device if device == "cpu" else f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}"
     preset = os.environ.get("TP_TEST_PRESET", "qwen3-tiny")
     hybrid = preset.startswith("qwen3.5")
@@ -99,7 +101,7 @@ def run(out_path: str, device: str, dtype_name: str) -> None:
     L = int(os.environ.get("TP_TEST_PREFILL_LEN", "9"))
     sc = ServerConfig(model_path=f"preset:{preset}", dtype=dtype_name, max_running_requests=4,
                       max_total_tokens=max(1024, 4 * L), chunked_prefill_size=max(2048, 2 * L),
-                      tp_size=world, ep_size=world if os.environ.get("TP_TEST_EP") == "1" else 1, disable_cuda_graph=os.environ.get("TP_TEST_GRAPH", "0") != "1",
+                      tp_size=world // pp, pp_size=pp, ep_size=world if os.environ.get("TP_TEST_EP") == "1" else 1, disable_cuda_graph=os.environ.get("TP_TEST_GRAPH", "0") != "1",
                       comm_backend=os.environ.get("TP_TEST_COMM", "fused"))
     mr = ModelRunner(sc, hf_config=cfg, device=dev)
     mr.initialize()
@@ -145,16 +147,18 @@ def run(out_path: str, device: str, dtype_name: str) -> None:
     lens = torch.full((B,), L, device=dev)
     fb = mr.prepare_forward_batch_extend(ids.reshape(-1).to(dev), sl, lens, lens, torch.zeros_like(lens), loc,
                                          extend_seq_lens_cpu=[L] * B, extend_prefix_lens_cpu=[0] * B)
-    outs = [mr.forward(fb).next_token_logits.float().cpu()]
-    nxt = outs[-1].argmax(-1).to(dev)
+    out = mr.forward(fb)
+    outs = [out.next_token_logits.float().cpu()]
+    nxt = mr.sample(out).to(dev)          # greedy; under pipeline parallelism the ids come from the last stage
     cur = L
     for _ in range(2):
         loc1 = mr.token_to_kv_pool_allocator.alloc(B)
         mr.req_to_token_pool.req_to_token[sl.long(), cur] = loc1.int()
         cur += 1
         fb = mr.prepare_forward_batch_decode(nxt, sl, torch.full((B,), cur, device=dev), loc1, max_seq_len=cur)
-        outs.append(mr.forward(fb).next_token_logits.float().cpu())
-        nxt = outs[-1].argmax(-1).to(dev)
+        out = mr.forward(fb)
+        outs.append(out.next_token_logits.float().cpu())
+        nxt = mr.sample(out).to(dev)
     if device != "cpu":
         from mllm_b200 import ops
 
@@ -169,7 +173,7 @@ def run(out_path: str, device: str, dtype_name: str) -> None:
         from mllm_b200.parallel.symm import get_tp_comm
 
         assert get_tp_comm() is not None and get_tp_comm().epoch > 0, "fused prefill path was not taken"
-    if rank == 0:
+    if rank == (world - 1 if pp > 1 else 0):      # under pipeline parallelism the last stage holds the logits
         torch.save(torch.stack(outs), out_path)
     if world > 1:
         import torch.distributed as dist
