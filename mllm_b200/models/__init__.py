@@ -20,6 +20,8 @@ _REGISTRY: Dict[str, Tuple[str, str]] = {
     "Qwen2ForCausalLM": ("mllm_b200.models.llama", "Qwen2ForCausalLM"),
     "Qwen2VLForConditionalGeneration": ("mllm_b200.models.qwen2_vl", "Qwen2VLForConditionalGeneration"),
     "Qwen2_5_VLForConditionalGeneration": ("mllm_b200.models.qwen2_5_vl", "Qwen2_5_VLForConditionalGeneration"),
+    "Qwen2MoeForCausalLM": ("mllm_b200.models.moe_families", "Qwen2MoeForCausalLM"),
+    "MixtralForCausalLM": ("mllm_b200.models.moe_families", "MixtralForCausalLM"),
     "SmolLM3ForCausalLM": ("mllm_b200.models.llama", "SmolLM3ForCausalLM"),
 }
 

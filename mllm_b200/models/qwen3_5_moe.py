@@ -29,8 +29,12 @@ _PREFIXES = (("model.language_model.", "model."), ("language_model.model.", "mod
 
 
 class SharedExpertMoE(nn.Module):
-    def __init__(self, config, layer_id: int, quant_config=None, params_dtype=None) -> None:
+    """``reduce_results=False`` leaves this rank's partial sums for the caller (decoder stacks whose next
+    norm performs the tensor-parallel reduction)."""
+
+    def __init__(self, config, layer_id: int, quant_config=None, params_dtype=None, reduce_results: bool = True) -> None:
         super().__init__()
+        self.reduce_results = reduce_results
         prefix = f"model.layers.{layer_id}.mlp"
         dt = params_dtype or torch.get_default_dtype()
         self.block = SparseMoeBlock(config.hidden_size, config.moe_intermediate_size, config.num_experts,
@@ -49,7 +53,7 @@ class SharedExpertMoE(nn.Module):
         shared = self.shared_expert(x)                   # a partial sum under tensor parallelism
         g = torch.sigmoid(torch.nn.functional.linear(x.float(), self.shared_expert_gate.weight.float())).to(x.dtype)
         y = routed + g * shared
-        return pstate.tensor_model_parallel_all_reduce(y) if self.tp > 1 else y
+        return pstate.tensor_model_parallel_all_reduce(y) if self.tp > 1 and self.reduce_results else y
 
 
 class Qwen3_5MoeDecoderLayer(Qwen3_5DecoderLayer):

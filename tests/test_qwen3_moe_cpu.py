@@ -77,3 +77,90 @@ def test_moe_preset_runs():
     mr.initialize()
     assert type(mr.model).__name__ == "Qwen3MoeForCausalLM"
     assert sum(1 for n, _ in mr.model.named_parameters() if n.endswith("block.w13")) == 2
+
+
+def _compare_moe_family(arch, hf, cfgd, rename=None):
+    ns = types.SimpleNamespace(architectures=[arch], head_dim=16, **cfgd)
+    mr = ModelRunner(ServerConfig(model_path="preset:x", dtype="float32", max_running_requests=2, max_total_tokens=256),
+                     hf_config=ns, device="cpu")
+    mr.initialize()
+    sd = hf.state_dict()
+    if rename is not None:
+        sd = rename(sd)
+    loaded = mr.model.load_weights(sd.items())
+    missing = set(dict(mr.model.named_parameters())) - loaded
+    assert not missing, missing
+    for m in mr.model.modules():
+        if hasattr(m, "quant_method"):
+            m._gate_up_interleaved = False
+            m.quant_method.process_weights_after_loading(m)
+        if hasattr(m, "swiglu_block") and hasattr(m, "w13"):
+            m.swiglu_block = 0
+    mr.model.post_load()
+    torch.manual_seed(0)
+    ids = torch.randint(0, cfgd["vocab_size"], (1, 11))
+    slots = mr.req_to_token_pool.alloc(1)
+    loc = mr.token_to_kv_pool_allocator.alloc(11)
+    mr.req_to_token_pool.req_to_token[slots[0], :11] = loc.int()
+    lens = torch.tensor([11])
+    fb = mr.prepare_forward_batch_extend(ids.reshape(-1), torch.tensor(slots), lens, lens, torch.zeros_like(lens), loc)
+    got = mr.forward(fb).next_token_logits
+    with torch.no_grad():
+        want = hf(ids).logits[:, -1]
+    torch.testing.assert_close(got, want, atol=1e-3, rtol=1e-3)
+
+
+def _spread(hf):
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith("mlp.gate.weight") or n.endswith("shared_expert_gate.weight"):
+                p.copy_(torch.randn_like(p))
+            if "experts" in n:
+                p.copy_(torch.randn_like(p) * 0.05)
+            if n.endswith(".bias"):
+                p.copy_(torch.randn_like(p) * 0.05)
+
+
+def test_qwen2_moe_matches_hf():
+    tr = pytest.importorskip("transformers")
+    cfgd = dict(vocab_size=320, hidden_size=64, intermediate_size=96, moe_intermediate_size=32, shared_expert_intermediate_size=48,
+                num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, num_experts=4, num_experts_per_tok=2,
+                norm_topk_prob=False, decoder_sparse_step=1, mlp_only_layers=[1], rms_norm_eps=1e-6, rope_theta=10000.0,
+                tie_word_embeddings=False, max_position_embeddings=256, use_sliding_window=False)
+    try:
+        hf = tr.Qwen2MoeForCausalLM(tr.Qwen2MoeConfig(**cfgd)).float().eval()
+    except Exception as e:  # pragma: no cover
+        pytest.skip(f"transformers Qwen2-MoE unavailable: {e}")
+    _spread(hf)
+    _compare_moe_family("Qwen2MoeForCausalLM", hf, cfgd)
+
+
+def test_mixtral_matches_hf_with_hub_style_names():
+    tr = pytest.importorskip("transformers")
+    cfgd = dict(vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=2, num_local_experts=4, num_experts_per_tok=2, rms_norm_eps=1e-5, rope_theta=10000.0,
+                tie_word_embeddings=False, max_position_embeddings=256, sliding_window=None)
+    try:
+        hf = tr.MixtralForCausalLM(tr.MixtralConfig(**cfgd)).float().eval()
+    except Exception as e:  # pragma: no cover
+        pytest.skip(f"transformers Mixtral unavailable: {e}")
+    _spread(hf)
+
+    def hub_names(sd):
+        """The layout of the published checkpoints: block_sparse_moe.gate / experts.N.w1 (gate), w3 (up), w2 (down)."""
+        out = {}
+        for k, v in sd.items():
+            if k.endswith("mlp.experts.gate_up_proj"):
+                base = k[: -len("mlp.experts.gate_up_proj")] + "block_sparse_moe.experts."
+                for e in range(v.shape[0]):
+                    out[f"{base}{e}.w1.weight"], out[f"{base}{e}.w3.weight"] = v[e, :96], v[e, 96:]
+            elif k.endswith("mlp.experts.down_proj"):
+                base = k[: -len("mlp.experts.down_proj")] + "block_sparse_moe.experts."
+                for e in range(v.shape[0]):
+                    out[f"{base}{e}.w2.weight"] = v[e]
+            else:
+                out[k.replace(".mlp.gate.", ".block_sparse_moe.gate.")] = v
+        return out
+
+    _compare_moe_family("MixtralForCausalLM", hf, cfgd, rename=hub_names)
+    _compare_moe_family("MixtralForCausalLM", hf, cfgd)          # and the fused in-memory layout
