@@ -290,10 +290,8 @@ class Qwen3ForCausalLM(nn.Module):
                     if cand in params:
                         target, shard = cand, sid
                         break
-            if target not in params:
-                alt = target.replace(".q_norm.", ".self_attn.q_norm.") if False else target
-                if alt not in params:
-                    continue
+            if target not in params:     # not kept on this rank / stage, or not part of this architecture
+                continue
             p = params[target]
             if shard in ("k", "v"):
                 attn = self._attn_of(target)
