@@ -44,7 +44,7 @@ class ServerConfig:
     max_total_tokens: Optional[int] = None
     chunked_prefill_size: Optional[int] = None
     max_prefill_tokens: Optional[int] = None
-    schedule_policy: Literal["auto", "fcfs"] = "fcfs"
+    schedule_policy: Literal["auto", "fcfs", "lpm"] = "fcfs"  # lpm: longest cached prefix first
     schedule_conservativeness: float = 1.0
     sleep_on_idle: bool = False
     stream_interval: int = 1

@@ -114,8 +114,31 @@ class Scheduler:
         return bool(self.waiting or self.prefilling or self.running)
 
     # ------------------------------------------------------------------ batch selection
+    LPM_WINDOW = 64   # requests at the head of the queue that the prefix-aware policy looks at
+
+    def _order_by_cached_prefix(self) -> None:
+        """``schedule_policy == "lpm"``: among the first requests of the queue, those with the longest
+        prefix already in the cache go first (they need the least new work and keep that prefix hot);
+        ties keep their arrival order."""
+        if len(self.waiting) < 2:
+            return
+        from ..mem_cache import RadixKey
+
+        head = [self.waiting.popleft() for _ in range(min(self.LPM_WINDOW, len(self.waiting)))]
+        cache = self.mrp.prefix_cache
+        hit = {}
+        for q in head:
+            if q.mm_inputs and q.mm_inputs.get("pixel_values") is not None:
+                hit[id(q)] = 0
+            else:
+                hit[id(q)] = cache.match_prefix(RadixKey(q.input_ids[: max(0, len(q.input_ids) - 1)], q.extra_key)).prefix_len
+        head.sort(key=lambda q: -hit[id(q)])           # stable: arrival order among equals
+        self.waiting.extendleft(reversed(head))
+
     def _admit_waiting(self) -> None:
         """Move requests from the queue into `prefilling` while the budgets allow."""
+        if self.cfg.schedule_policy == "lpm" and len(self.running) + len(self.prefilling) < self.max_running:
+            self._order_by_cached_prefix()
         while self.waiting:
             if len(self.running) + len(self.prefilling) >= self.max_running:
                 break

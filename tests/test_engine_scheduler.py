@@ -351,3 +351,35 @@ def test_stop_strings_end_generation_and_never_reach_the_client():
         assert eng.generate("hello world", sp)["text"] == text
     finally:
         eng.shutdown()
+
+
+def test_longest_prefix_first_policy():
+    """With one running slot, the queued request whose prompt is already cached is admitted before an older
+    request with a cold prompt; under fcfs the arrival order is kept.  Tokens are the same either way."""
+    warm = [7, 3, 9, 1, 4, 4, 2, 8, 6, 5, 1, 2, 3]
+
+    def run(policy):
+        sched = build_scheduler(_cfg(schedule_policy=policy, max_running_requests=1), device="cpu")
+        sched.add_request(_req("seed", warm, n=2))
+        _drain(sched)                                        # the warm prompt is now in the prefix cache
+        sched.add_request(_req("blocker", [50, 51, 52], n=3))
+        sched.step()                                         # occupies the only slot
+        sched.add_request(_req("cold", [90, 91, 92, 93, 94, 95], n=2))
+        sched.add_request(_req("hot", warm + [77], n=2))
+        order, done = [], {}
+        for _ in range(200):
+            out = sched.step()
+            if out is not None:
+                for i, rid in enumerate(out.rids):
+                    if out.finished_reasons[i] is not None:
+                        order.append(rid)
+                        done[rid] = (out.output_ids[i], out.cached_tokens[i])
+            if not sched.has_work():
+                break
+        return order, done
+
+    o_f, d_f = run("fcfs")
+    o_l, d_l = run("lpm")
+    assert o_f == ["blocker", "cold", "hot"] and o_l == ["blocker", "hot", "cold"]
+    assert {k: v[0] for k, v in d_f.items()} == {k: v[0] for k, v in d_l.items()}
+    assert d_l["hot"][1] >= len(warm) - 1 and d_l["cold"][1] == 0
