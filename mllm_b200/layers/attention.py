@@ -19,9 +19,13 @@ from .. import ops
 class RadixAttention(nn.Module):
     def __init__(self, num_heads: int, head_dim: int, scaling: float, num_kv_heads: int, layer_id: int,
                  rope_theta: float = 1e6, rms_eps: float = 1e-6, mrope_sections=None,
-                 mrope_interleaved: bool = False, rope_scaling: Optional[dict] = None) -> None:
+                 mrope_interleaved: bool = False, rope_scaling: Optional[dict] = None,
+                 sliding_window: Optional[int] = None, logit_cap: float = 0.0) -> None:
         super().__init__()
         self.rope_scaling = rope_scaling
+        # each query attends to its last `sliding_window` keys (itself included); scores soft-capped at logit_cap
+        self.sliding_window = int(sliding_window) if sliding_window else None
+        self.logit_cap = float(logit_cap or 0.0)
         self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
         self.scaling, self.layer_id = scaling, layer_id
         self.rope_theta, self.rms_eps = rope_theta, rms_eps
@@ -55,9 +59,10 @@ class RadixAttention(nn.Module):
         out = torch.empty((T, self.num_heads, self.head_dim), dtype=qkv.dtype, device=qkv.device)
         if fb.forward_mode.is_decode():
             ops.attention_decode(q, k_cache, v_cache, fb.req_to_token_pool.req_to_token, fb.req_pool_indices,
-                                 fb.seq_lens, self.scaling, out=out, max_seq_len=fb.max_seq_len)
+                                 fb.seq_lens, self.scaling, out=out, max_seq_len=fb.max_seq_len,
+                                 window=self.sliding_window, logit_cap=self.logit_cap)
         else:
             ops.attention_prefill(q, k_cache, v_cache, fb.req_to_token_pool.req_to_token, fb.req_pool_indices,
                                   fb.seq_lens, fb.extend_prefix_lens, fb.extend_start_loc, self.scaling, out=out,
-                                  max_q_len=fb.max_extend_len)
+                                  max_q_len=fb.max_extend_len, window=self.sliding_window, logit_cap=self.logit_cap)
         return out.view(T, self.num_heads * self.head_dim)

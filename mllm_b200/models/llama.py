@@ -3,7 +3,8 @@ Qwen3: ``mllm/models/llama``, ``mllm/models/qwen2``-style configs).  Both are th
 without the per-head q/k RMSNorm: same fused QKV + RoPE + KV-write prologue (norm weights absent), same
 attention and SwiGLU kernels, same tensor-parallel sharding and quantised linears.
 
-* ``LlamaForCausalLM`` (also Mistral-style configs without a sliding window): no attention bias unless
+* ``LlamaForCausalLM`` (also Mistral-style configs; a ``sliding_window`` is honoured, on fallback attention
+  paths): no attention bias unless
   ``attention_bias``; ``rope_scaling`` of type ``llama3`` / ``linear`` is applied to the rotary
   frequencies.
 * ``Qwen2ForCausalLM`` (Qwen2 / Qwen2.5): bias on the q, k and v projections.
@@ -32,7 +33,6 @@ class LlamaForCausalLM(Qwen3ForCausalLM):
         if getattr(config, "attention_bias", None) is None:
             config.attention_bias = False
         _unsupported(config, "mlp_bias", lambda v: not v)
-        _unsupported(config, "sliding_window", lambda v: not v)
         super().__init__(config, quant_config, params_dtype, **model_kw)
 
 
@@ -40,15 +40,11 @@ class Qwen2ForCausalLM(Qwen3ForCausalLM):
     def __init__(self, config, quant_config=None, params_dtype: Optional[torch.dtype] = None, **model_kw) -> None:
         config.use_qk_norm = False
         config.attention_bias = True          # Qwen2 always has q/k/v biases; the config does not say so
-        if getattr(config, "use_sliding_window", False):
-            raise NotImplementedError("Qwen2 sliding-window attention is not supported")
         super().__init__(config, quant_config, params_dtype, **model_kw)
 
 
 class SmolLM3ForCausalLM(LlamaForCausalLM):
     def __init__(self, config, quant_config=None, params_dtype: Optional[torch.dtype] = None, **model_kw) -> None:
-        if getattr(config, "use_sliding_window", False):
-            raise NotImplementedError("SmolLM3 sliding-window attention is not supported")
         if getattr(config, "no_rope_layers", None) is None:
             n = int(getattr(config, "no_rope_layer_interval", 4))
             config.no_rope_layers = [int((i + 1) % n != 0) for i in range(config.num_hidden_layers)]

@@ -43,8 +43,6 @@ class Qwen2MoeForCausalLM(Qwen3MoeForCausalLM):
         config.attention_bias = True
         if getattr(config, "norm_topk_prob", None) is None:
             config.norm_topk_prob = False
-        if getattr(config, "use_sliding_window", False):
-            raise NotImplementedError("sliding-window attention is not supported")
         super().__init__(config, quant_config, params_dtype, **model_kw)
 
 
@@ -55,8 +53,6 @@ class MixtralForCausalLM(Qwen3MoeForCausalLM):
         config.use_qk_norm = False
         if getattr(config, "attention_bias", None) is None:
             config.attention_bias = False
-        if getattr(config, "sliding_window", None):
-            raise NotImplementedError("sliding-window attention is not supported")
         config.num_experts = int(getattr(config, "num_local_experts", getattr(config, "num_experts", 8)))
         config.moe_intermediate_size = int(config.intermediate_size)
         config.norm_topk_prob, config.decoder_sparse_step, config.mlp_only_layers = True, 1, []

@@ -77,7 +77,9 @@ class Qwen3Attention(nn.Module):
         rope_theta = _rope_theta(config)
         self.attn = RadixAttention(self.num_heads, self.head_dim, self.head_dim ** -0.5, self.num_kv_heads, layer_id,
                                    rope_theta=rope_theta, rms_eps=eps, mrope_sections=mrope_sections,
-                                   mrope_interleaved=mrope_interleaved, rope_scaling=_rope_scaling(config, layer_id))
+                                   mrope_interleaved=mrope_interleaved, rope_scaling=_rope_scaling(config, layer_id),
+                                   sliding_window=_sliding_window(config, layer_id),
+                                   logit_cap=float(getattr(config, "attn_logit_softcapping", 0.0) or 0.0))
 
     def kv_shard_for_rank(self, loaded: torch.Tensor) -> torch.Tensor:
         """With fewer KV heads than ranks, rank r keeps head ``r * Hkv // tp``."""
@@ -116,6 +118,23 @@ def _rope_scaling(config, layer_id: int = 0) -> Optional[dict]:
     rs = rs if isinstance(rs, dict) else vars(rs)
     kind = rs.get("rope_type", rs.get("type", "default"))
     return dict(rs) if kind in ("linear", "llama3", "yarn", "dynamic", "longrope") else None
+
+
+def _sliding_window(config, layer_id: int) -> Optional[int]:
+    """The layer's attention window, if the checkpoint uses sliding-window attention: ``layer_types`` when
+    given, else every layer (Mistral) or the layers from ``max_window_layers`` on (Qwen2 with
+    ``use_sliding_window``)."""
+    w = getattr(config, "sliding_window", None)
+    if not w:
+        return None
+    types = getattr(config, "layer_types", None)
+    if types:
+        return int(w) if types[layer_id] == "sliding_attention" else None
+    if hasattr(config, "use_sliding_window"):
+        if not config.use_sliding_window:
+            return None
+        return int(w) if layer_id >= int(getattr(config, "max_window_layers", 0)) else None
+    return int(w)
 
 
 class Qwen3DecoderLayer(nn.Module):

@@ -428,26 +428,46 @@ def tp_reduce_add_rmsnorm(partial: torch.Tensor, residual: Optional[torch.Tensor
 # --------------------------------------------------------------------------
 # attention
 # --------------------------------------------------------------------------
+def _attention_kernel_ok(q: torch.Tensor, window, logit_cap) -> bool:
+    """The tcgen05 attention kernels cover head size 128 with plain causal masking."""
+    return use_kernels(q) and q.shape[-1] == 128 and not window and not logit_cap
+
+
 def attention_prefill(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, prefix_lens,
-                      q_start_loc, scale: float, out=None, max_q_len: int = 0) -> torch.Tensor:
-    if use_kernels(q) and hasattr(ext(), "attention_prefill"):
+                      q_start_loc, scale: float, out=None, max_q_len: int = 0, window: Optional[int] = None,
+                      logit_cap: float = 0.0, seq_lens_cpu=None, prefix_lens_cpu=None) -> torch.Tensor:
+    """Causal attention of new tokens over cached prefix + themselves.  ``window``: sliding-window attention
+    (each query sees its last ``window`` keys); ``logit_cap``: soft-capping of the scores.  Head sizes other
+    than 128, windows and caps take library / PyTorch fallbacks."""
+    if _attention_kernel_ok(q, window, logit_cap) and hasattr(ext(), "attention_prefill"):
         if out is None:
             out = torch.empty((q.shape[0], q.shape[1], q.shape[2]), dtype=q.dtype, device=q.device)
         ext().attention_prefill(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, prefix_lens,
                                 q_start_loc, scale, out, max_q_len, True)
         return out
+    if q.is_cuda and not logit_cap:
+        o = ref.attention_prefill_sdpa(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, prefix_lens,
+                                       q_start_loc, scale, seq_lens_cpu, prefix_lens_cpu, window)
+        if out is None:
+            return o
+        out.copy_(o)
+        return out
     return ref.attention_prefill(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, prefix_lens,
-                                 q_start_loc, scale, out)
+                                 q_start_loc, scale, out, window=window, logit_cap=logit_cap)
 
 
 def attention_decode(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, scale: float,
-                     out=None, max_seq_len: int = 0) -> torch.Tensor:
-    if use_kernels(q) and hasattr(ext(), "attention_decode"):
+                     out=None, max_seq_len: int = 0, window: Optional[int] = None, logit_cap: float = 0.0) -> torch.Tensor:
+    if _attention_kernel_ok(q, window, logit_cap) and hasattr(ext(), "attention_decode"):
         if out is None:
             out = torch.empty((q.shape[0], q.shape[1], q.shape[2]), dtype=q.dtype, device=q.device)
         ext().attention_decode(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, scale, out, max_seq_len)
         return out
-    return ref.attention_decode(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, scale, out)
+    if q.is_cuda and max_seq_len:
+        return ref.attention_decode_batched(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, scale,
+                                            max_seq_len, out, window, logit_cap)
+    return ref.attention_decode(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, scale, out,
+                                window=window, logit_cap=logit_cap)
 
 
 def attention_varlen_bidirectional(q, k, v, cu_seqlens, scale: float) -> torch.Tensor:

@@ -255,22 +255,30 @@ def kv_write(k, v, loc, k_cache, v_cache) -> None:
 # --------------------------------------------------------------------------
 # attention over the slot-indexed KV pool
 # --------------------------------------------------------------------------
-def _attend(q, k, v, scale, causal_offset: Optional[int]):
-    """q [Tq,Hq,D] k,v [Tk,Hkv,D] fp32 -> [Tq,Hq,D]; key j visible to query i iff j <= i + causal_offset."""
+def _attend(q, k, v, scale, causal_offset: Optional[int], window: Optional[int] = None, logit_cap: float = 0.0):
+    """q [Tq,Hq,D] k,v [Tk,Hkv,D] fp32 -> [Tq,Hq,D]; key j visible to query i iff j <= i + causal_offset and,
+    with a sliding ``window``, j > i + causal_offset - window (the last ``window`` keys, the query's own
+    included).  ``logit_cap`` > 0 soft-caps the scaled scores: ``cap * tanh(s / cap)``."""
     Hq, Hkv = q.shape[1], k.shape[1]
     g = Hq // Hkv
     kk = k.repeat_interleave(g, dim=1)
     vv = v.repeat_interleave(g, dim=1)
     s = torch.einsum("qhd,khd->hqk", q, kk) * scale
-    if causal_offset is not None:
+    if logit_cap and logit_cap > 0:
+        s = logit_cap * torch.tanh(s / logit_cap)
+    if causal_offset is not None or window:
+        off = causal_offset if causal_offset is not None else k.shape[0] - q.shape[0]
         i = torch.arange(q.shape[0], device=q.device).unsqueeze(-1)
         j = torch.arange(k.shape[0], device=q.device).unsqueeze(0)
-        s = s.masked_fill(j > i + causal_offset, float("-inf"))
+        hidden = j > i + off if causal_offset is not None else torch.zeros_like(j > i)
+        if window:
+            hidden = hidden | (j <= i + off - int(window))
+        s = s.masked_fill(hidden, float("-inf"))
     p = torch.softmax(s, dim=-1)
     return torch.einsum("hqk,khd->qhd", p, vv)
 
 
-def _attend_sdpa(q, k, v, scale, causal_offset: Optional[int]):
+def _attend_sdpa(q, k, v, scale, causal_offset: Optional[int], window: Optional[int] = None):
     """:func:`_attend` through ``scaled_dot_product_attention`` in the tensors' own dtype (no fp32 score
     matrix): the fallback used on GPUs for head sizes without a kernel.  q [Tq,Hq,D], k / v [Tk,Hkv,D]."""
     import torch.nn.functional as F
@@ -279,12 +287,14 @@ def _attend_sdpa(q, k, v, scale, causal_offset: Optional[int]):
     qh, kh, vh = q.transpose(0, 1).unsqueeze(0), k.transpose(0, 1).unsqueeze(0), v.transpose(0, 1).unsqueeze(0)
     mask, causal = None, False
     if causal_offset is not None:
-        if causal_offset == 0 and Tq == Tk:
+        if causal_offset == 0 and Tq == Tk and not window:
             causal = True
         else:
             i = torch.arange(Tq, device=q.device).unsqueeze(-1)
             j = torch.arange(Tk, device=q.device).unsqueeze(0)
             mask = j <= i + causal_offset
+            if window:
+                mask = mask & (j > i + causal_offset - int(window))
     o = F.scaled_dot_product_attention(qh, kh, vh, attn_mask=mask, is_causal=causal, scale=scale,
                                        enable_gqa=q.shape[1] != k.shape[1])
     return o.squeeze(0).transpose(0, 1)
@@ -294,6 +304,7 @@ def attention_prefill(
     q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, req_to_token: torch.Tensor,
     req_pool_indices: torch.Tensor, seq_lens: torch.Tensor, prefix_lens: torch.Tensor,
     q_start_loc: torch.Tensor, scale: float, out: Optional[torch.Tensor] = None, max_q_len: int = 0,
+    window: Optional[int] = None, logit_cap: float = 0.0,
 ) -> torch.Tensor:
     """Causal attention of each request's new tokens over its cached prefix plus itself.
 
@@ -305,13 +316,13 @@ def attention_prefill(
         sl, pl, qs = int(seq_lens[b]), int(prefix_lens[b]), int(q_start_loc[b])
         n = sl - pl
         slots = req_to_token[int(req_pool_indices[b]), :sl].long()
-        o = _attend(_f32(q[qs : qs + n]), _f32(k_cache[slots]), _f32(v_cache[slots]), scale, pl)
+        o = _attend(_f32(q[qs : qs + n]), _f32(k_cache[slots]), _f32(v_cache[slots]), scale, pl, window, logit_cap)
         out[qs : qs + n] = o.to(out.dtype)
     return out
 
 
 def attention_prefill_sdpa(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, prefix_lens, q_start_loc,
-                           scale: float, seq_lens_cpu=None, prefix_lens_cpu=None) -> torch.Tensor:
+                           scale: float, seq_lens_cpu=None, prefix_lens_cpu=None, window: Optional[int] = None) -> torch.Tensor:
     """:func:`attention_prefill` with ``scaled_dot_product_attention`` per request in the activation dtype —
     not a numerical reference but the serving fallback on GPUs for head sizes without a kernel.  The host
     copies of the lengths avoid device read-backs."""
@@ -323,7 +334,7 @@ def attention_prefill_sdpa(q, k_cache, v_cache, req_to_token, req_pool_indices, 
     for b, (sl, pl) in enumerate(zip(sls, pls)):
         n = int(sl) - int(pl)
         slots = req_to_token[pools[b], : int(sl)].long()
-        out[qs : qs + n] = _attend_sdpa(q[qs : qs + n], k_cache[slots].to(q.dtype), v_cache[slots].to(q.dtype), scale, int(pl))
+        out[qs : qs + n] = _attend_sdpa(q[qs : qs + n], k_cache[slots].to(q.dtype), v_cache[slots].to(q.dtype), scale, int(pl), window)
         qs += n
     return out
 
@@ -331,13 +342,14 @@ def attention_prefill_sdpa(q, k_cache, v_cache, req_to_token, req_pool_indices, 
 def attention_decode(
     q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, req_to_token: torch.Tensor,
     req_pool_indices: torch.Tensor, seq_lens: torch.Tensor, scale: float, out: Optional[torch.Tensor] = None,
+    window: Optional[int] = None, logit_cap: float = 0.0,
 ) -> torch.Tensor:
     """One query token per request over ``req_to_token[req, :seq_len]`` (the new token's K/V included)."""
     out = torch.empty_like(q) if out is None else out
     for b in range(req_pool_indices.numel()):
         sl = int(seq_lens[b])
         slots = req_to_token[int(req_pool_indices[b]), :sl].long()
-        o = _attend(_f32(q[b : b + 1]), _f32(k_cache[slots]), _f32(v_cache[slots]), scale, None)
+        o = _attend(_f32(q[b : b + 1]), _f32(k_cache[slots]), _f32(v_cache[slots]), scale, None, window, logit_cap)
         out[b] = o[0].to(out.dtype)
     return out
 
@@ -345,7 +357,7 @@ def attention_decode(
 def attention_decode_batched(
     q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, req_to_token: torch.Tensor,
     req_pool_indices: torch.Tensor, seq_lens: torch.Tensor, scale: float, max_seq_len: int,
-    out: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None, window: Optional[int] = None, logit_cap: float = 0.0,
 ) -> torch.Tensor:
     """:func:`attention_decode` for the whole batch at once: keys are gathered up to ``max_seq_len`` (a host
     bound on ``seq_lens``) and the tail of every request is masked, so nothing is read back from the device.
@@ -358,7 +370,12 @@ def attention_decode_batched(
     v = _f32(v_cache[slots])
     qg = _f32(q).view(B, Hkv, Hq // Hkv, D)
     s = torch.einsum("bhgd,bshd->bhgs", qg, k) * scale
-    valid = torch.arange(S, device=q.device).unsqueeze(0) < seq_lens.view(-1, 1)
+    if logit_cap and logit_cap > 0:
+        s = logit_cap * torch.tanh(s / logit_cap)
+    pos = torch.arange(S, device=q.device).unsqueeze(0)
+    valid = pos < seq_lens.view(-1, 1)
+    if window:
+        valid = valid & (pos >= seq_lens.view(-1, 1) - int(window))
     s = s.masked_fill(~valid.view(B, 1, 1, S), float("-inf"))
     o = torch.einsum("bhgs,bshd->bhgd", torch.softmax(s, dim=-1), v).reshape(B, Hq, D)
     if out is None:

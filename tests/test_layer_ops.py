@@ -151,3 +151,35 @@ def test_sdpa_prefill_fallback_equals_the_reference_prefill():
     torch.testing.assert_close(got, want, atol=1e-5, rtol=1e-5)
     got = ref.attention_prefill_sdpa(q, kc, vc, rtt, req, seq, pre, qs, D ** -0.5, [9, 14], [0, 6])
     torch.testing.assert_close(got, want, atol=1e-5, rtol=1e-5)
+
+
+def test_window_and_logit_cap_agree_across_attention_paths():
+    """Sliding window and soft-capping: the per-request statement, the batched decode form and the SDPA
+    prefill form agree with a direct softmax evaluation."""
+    import torch
+
+    from mllm_b200.ops import reference as ref
+
+    torch.manual_seed(3)
+    Hq, Hkv, D, W, cap = 4, 2, 16, 5, 3.0
+    kc, vc = torch.randn(64, Hkv, D), torch.randn(64, Hkv, D)
+    rtt = torch.zeros(2, 32, dtype=torch.int32)
+    rtt[0, :12], rtt[1, :20] = torch.arange(12).int(), torch.arange(20, 40).int()
+    req, seq, pre = torch.tensor([0, 1], dtype=torch.int32), torch.tensor([12, 20], dtype=torch.int32), torch.tensor([0, 9], dtype=torch.int32)
+    q = torch.randn(12 + 11, Hq, D)
+    qs = torch.tensor([0, 12], dtype=torch.int32)
+    scale = D ** -0.5
+    # direct evaluation for request 1, query row 3 (absolute position 12): keys 8..12 visible
+    want = ref.attention_prefill(q, kc, vc, rtt, req, seq, pre, qs, scale, window=W, logit_cap=cap)
+    k1, v1 = kc[20:40].repeat_interleave(2, 1), vc[20:40].repeat_interleave(2, 1)
+    s = torch.einsum("hd,khd->hk", q[12 + 3], k1) * scale
+    s = cap * torch.tanh(s / cap)
+    s[:, :8], s[:, 13:] = float("-inf"), float("-inf")
+    torch.testing.assert_close(want[12 + 3], torch.einsum("hk,khd->hd", torch.softmax(s, -1), v1), atol=1e-5, rtol=1e-5)
+    got = ref.attention_prefill_sdpa(q, kc, vc, rtt, req, seq, pre, qs, scale, window=W)
+    torch.testing.assert_close(got, ref.attention_prefill(q, kc, vc, rtt, req, seq, pre, qs, scale, window=W), atol=1e-5, rtol=1e-5)
+    qd = torch.randn(2, Hq, D)
+    a = ref.attention_decode(qd, kc, vc, rtt, req, seq, scale, window=W, logit_cap=cap)
+    b = ref.attention_decode_batched(qd, kc, vc, rtt, req, seq, scale, 24, window=W, logit_cap=cap)
+    torch.testing.assert_close(a, b, atol=1e-5, rtol=1e-5)
+    assert not torch.allclose(a, ref.attention_decode(qd, kc, vc, rtt, req, seq, scale), atol=1e-3)

@@ -103,13 +103,43 @@ def test_unsupported_variants_are_refused():
     from mllm_b200.models import get_model_class
 
     cfg = types.SimpleNamespace(vocab_size=32, hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=2,
-                                num_key_value_heads=2, rms_norm_eps=1e-6, tie_word_embeddings=True, sliding_window=128)
+                                num_key_value_heads=2, rms_norm_eps=1e-6, tie_word_embeddings=True, mlp_bias=True)
     with pytest.raises(NotImplementedError):
-        get_model_class("MistralForCausalLM")(cfg)
-    cfg2 = types.SimpleNamespace(**{**vars(cfg), "sliding_window": None, "rope_scaling": dict(rope_type="yarn", factor=4.0)})
+        get_model_class("LlamaForCausalLM")(cfg)
+    cfg2 = types.SimpleNamespace(**{**vars(cfg), "mlp_bias": False, "rope_scaling": dict(rope_type="yarn", factor=4.0)})
     with pytest.raises(NotImplementedError):
         m = get_model_class("LlamaForCausalLM")(cfg2)
         m.model.layers[0].self_attn.attn._tables(torch.device("cpu"))
+
+
+def test_mistral_sliding_window_matches_hf():
+    """A window (8) much shorter than the prompt (40 tokens, prefilled in two chunks) and the decode steps."""
+    tr = pytest.importorskip("transformers")
+    cfgd = dict(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=2, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=256,
+                hidden_act="silu", rope_theta=10000.0, sliding_window=8)
+    try:
+        hf = tr.MistralForCausalLM(tr.MistralConfig(**cfgd, attn_implementation="eager")).float().eval()
+    except Exception as e:  # pragma: no cover
+        pytest.skip(f"transformers Mistral unavailable: {e}")
+    ns = types.SimpleNamespace(architectures=["MistralForCausalLM"], head_dim=16, **cfgd)
+    _run_and_compare(hf, ns, 320)
+    # the window matters: the same weights without it give other logits
+    ns2 = types.SimpleNamespace(architectures=["MistralForCausalLM"], head_dim=16, **{**cfgd, "sliding_window": None})
+    with pytest.raises(AssertionError):
+        _run_and_compare(hf, ns2, 320)
+
+
+def test_qwen2_window_layers_follow_max_window_layers():
+    from mllm_b200.models.qwen3 import _sliding_window
+
+    c = types.SimpleNamespace(sliding_window=16, use_sliding_window=True, max_window_layers=2)
+    assert [_sliding_window(c, i) for i in range(4)] == [None, None, 16, 16]
+    c.use_sliding_window = False
+    assert _sliding_window(c, 3) is None
+    c2 = types.SimpleNamespace(sliding_window=16, layer_types=["full_attention", "sliding_attention"])
+    assert [_sliding_window(c2, i) for i in range(2)] == [None, 16]
+    assert _sliding_window(types.SimpleNamespace(sliding_window=None), 0) is None
 
 
 def test_qwen2_vl_matches_hf():
