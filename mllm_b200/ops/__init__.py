@@ -372,7 +372,7 @@ def qk_norm_rope_kv_write(
     mrope_sections=None, mrope_interleaved: bool = False,
     inv_freq: Optional[torch.Tensor] = None, axis_map: Optional[torch.Tensor] = None,
 ) -> None:
-    if not use_kernels(qkv) or head_dim != 128:
+    if not use_kernels(qkv) or head_dim != 128 or k_cache.dtype != qkv.dtype:
         return ref.qk_norm_rope_kv_write(
             qkv, q_weight, k_weight, positions, cache_loc, k_cache, v_cache, num_q_heads, num_kv_heads,
             head_dim, theta, eps, mrope_sections, mrope_interleaved, inv_freq=inv_freq,
@@ -388,7 +388,7 @@ def qk_norm_rope_kv_write(
 
 
 def kv_write(k, v, loc, k_cache, v_cache) -> None:
-    if not use_kernels(k):
+    if not use_kernels(k) or k_cache.dtype != k.dtype:
         return ref.kv_write(k, v, loc, k_cache, v_cache)
     ext().kv_write(k, v, loc.to(torch.int64).contiguous(), k_cache, v_cache)
 
@@ -428,9 +428,9 @@ def tp_reduce_add_rmsnorm(partial: torch.Tensor, residual: Optional[torch.Tensor
 # --------------------------------------------------------------------------
 # attention
 # --------------------------------------------------------------------------
-def _attention_kernel_ok(q: torch.Tensor, window, logit_cap) -> bool:
-    """The tcgen05 attention kernels cover head size 128 with plain causal masking."""
-    return use_kernels(q) and q.shape[-1] == 128 and not window and not logit_cap
+def _attention_kernel_ok(q: torch.Tensor, k_cache: torch.Tensor, window, logit_cap) -> bool:
+    """The tcgen05 attention kernels cover head size 128, plain causal masking and a cache of the activation dtype."""
+    return use_kernels(q) and q.shape[-1] == 128 and not window and not logit_cap and k_cache.dtype == q.dtype
 
 
 def attention_prefill(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, prefix_lens,
@@ -439,7 +439,7 @@ def attention_prefill(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_l
     """Causal attention of new tokens over cached prefix + themselves.  ``window``: sliding-window attention
     (each query sees its last ``window`` keys); ``logit_cap``: soft-capping of the scores.  Head sizes other
     than 128, windows and caps take library / PyTorch fallbacks."""
-    if _attention_kernel_ok(q, window, logit_cap) and hasattr(ext(), "attention_prefill"):
+    if _attention_kernel_ok(q, k_cache, window, logit_cap) and hasattr(ext(), "attention_prefill"):
         if out is None:
             out = torch.empty((q.shape[0], q.shape[1], q.shape[2]), dtype=q.dtype, device=q.device)
         ext().attention_prefill(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, prefix_lens,
@@ -458,7 +458,7 @@ def attention_prefill(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_l
 
 def attention_decode(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, scale: float,
                      out=None, max_seq_len: int = 0, window: Optional[int] = None, logit_cap: float = 0.0) -> torch.Tensor:
-    if _attention_kernel_ok(q, window, logit_cap) and hasattr(ext(), "attention_decode"):
+    if _attention_kernel_ok(q, k_cache, window, logit_cap) and hasattr(ext(), "attention_decode"):
         if out is None:
             out = torch.empty((q.shape[0], q.shape[1], q.shape[2]), dtype=q.dtype, device=q.device)
         ext().attention_decode(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, scale, out, max_seq_len)

@@ -106,3 +106,37 @@ def test_hybrid_state_pool_is_allocated_before_the_kv_pool_is_sized():
     mr.initialize()
     assert order == ["_init_state_pool", "init_memory_pool"]
     assert mr.gdn_pool.slots == mr.req_to_token_pool.size == 3 + 8 and mr.gdn_pool.track_slots == 5
+
+
+def test_fp8_kv_cache_halves_the_cache_and_stays_close():
+    """``kv_cache_dtype fp8_e4m3``: one byte per cached value, logits close to the 16-/32-bit cache run
+    (prefill in two chunks so that cached keys are really read back, then a decode step)."""
+    import torch
+
+    from mllm_b200.configs import ServerConfig
+    from mllm_b200.executor import ModelRunner
+
+    def run(kv):
+        mr = ModelRunner(ServerConfig(model_path="preset:qwen3-tiny", dtype="float32", max_running_requests=2,
+                                      max_total_tokens=256), kv_cache_dtype=kv, device="cpu")
+        mr.initialize()
+        ids = (torch.arange(20) * 13) % 1000
+        slots = mr.req_to_token_pool.alloc(1)
+        sl = torch.tensor(slots)
+        loc = mr.token_to_kv_pool_allocator.alloc(20)
+        mr.req_to_token_pool.req_to_token[slots[0], :20] = loc.int()
+        mr.forward(mr.prepare_forward_batch_extend(ids[:12], sl, torch.tensor([12]), torch.tensor([12]), torch.tensor([0]), loc[:12]))
+        out = mr.forward(mr.prepare_forward_batch_extend(ids[12:], sl, torch.tensor([20]), torch.tensor([8]), torch.tensor([12]), loc[12:]))
+        logits = [out.next_token_logits]
+        loc1 = mr.token_to_kv_pool_allocator.alloc(1)
+        mr.req_to_token_pool.req_to_token[slots[0], 20] = loc1.int()
+        logits.append(mr.forward(mr.prepare_forward_batch_decode(logits[0].argmax(-1), sl, torch.tensor([21]), loc1)).next_token_logits)
+        return torch.cat(logits), mr
+
+    ref_logits, mr_ref = run("auto")
+    fp8_logits, mr_fp8 = run("fp8_e4m3")
+    assert mr_fp8.token_to_kv_pool.store.dtype == torch.float8_e4m3fn
+    assert mr_fp8.cell_bytes() * 4 == mr_ref.cell_bytes()                 # fp32 reference run vs one byte
+    err = (fp8_logits - ref_logits).abs().max().item()
+    assert 0 < err < 0.05 * ref_logits.abs().max().item() + 0.02
+    assert torch.equal(fp8_logits.argmax(-1), ref_logits.argmax(-1))
