@@ -326,7 +326,7 @@ def create_app(engine: Engine, cfg: Optional[GlobalConfig] = None) -> FastAPI:
             metrics.sample_scheduler(sched)
         return PlainTextResponse(metrics.render(), media_type="text/plain; version=0.0.4")
 
-    @app.post("/flush_cache")
+    @app.api_route("/flush_cache", methods=["GET", "POST"])
     async def flush_cache():
         engine.flush_cache()
         return {"status": "requested"}
@@ -355,7 +355,7 @@ def create_app(engine: Engine, cfg: Optional[GlobalConfig] = None) -> FastAPI:
         return _error(500, f"{type(exc).__name__}: {exc}", "internal_error")
 
     # ---------------------------------------------------------------- /generate
-    @app.post("/generate")
+    @app.api_route("/generate", methods=["POST", "PUT"])
     async def generate(body: GenerateRequest, request: Request):
         obj = GenerateReqInput(rid=body.rid, text=body.text, input_ids=body.input_ids, sampling_params=body.sampling_params,
                                image_data=body.image_data, stream=body.stream, return_logprob=body.return_logprob or None,

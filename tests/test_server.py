@@ -126,3 +126,9 @@ def test_n_samples_echo_and_stop(client):
     stop = long[6:9]
     cut = client.post("/v1/completions", json={"prompt": "hello world", "max_tokens": 24, "temperature": 0, "stop": stop}).json()
     assert cut["choices"][0]["text"] == long[: long.find(stop)] and cut["choices"][0]["finish_reason"] == "stop"
+
+
+def test_method_variants_of_generate_and_flush(client):
+    r = client.put("/generate", json={"text": "hello", "sampling_params": {"max_new_tokens": 2, "temperature": 0}})
+    assert r.status_code == 200 and r.json()["meta_info"]["completion_tokens"] == 2
+    assert client.get("/flush_cache").status_code == client.post("/flush_cache").status_code == 200
