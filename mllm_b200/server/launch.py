@@ -49,10 +49,17 @@ class GenerateRequest(BaseModel):
     rid: Optional[Union[str, List[str]]] = None
     return_logprob: Optional[bool] = None
     top_logprobs_num: Optional[int] = None
+    # carried for request-format compatibility; not acted on
+    logprob_start_len: Optional[int] = None
+    video_data: Optional[Any] = None
+    audio_data: Optional[Any] = None
+    lora_path: Optional[str] = None
+    session_params: Optional[Dict[str, Any]] = None
 
 
 class StreamOptions(BaseModel):
     include_usage: bool = False
+    continuous_usage_stats: Optional[bool] = False   # usage so far in every streamed chunk
 
 
 class CompletionRequest(BaseModel):
@@ -72,6 +79,7 @@ class CompletionRequest(BaseModel):
     presence_penalty: float = 0.0
     repetition_penalty: float = 1.0
     seed: Optional[int] = None
+    user: Optional[str] = None
     logprobs: Optional[int] = None
     echo: bool = False
     ignore_eos: bool = False
@@ -108,6 +116,8 @@ class ChatCompletionRequest(BaseModel):
     tools: Optional[List[Dict[str, Any]]] = None
     tool_choice: Optional[Any] = None
     separate_reasoning: bool = True
+    stream_reasoning: bool = True     # False: reasoning text is delivered in one piece when the thinking block ends
+    user: Optional[str] = None
     chat_template_kwargs: Optional[Dict[str, Any]] = None
     ignore_eos: bool = False
 
@@ -468,15 +478,18 @@ def create_app(engine: Engine, cfg: Optional[GlobalConfig] = None) -> FastAPI:
             include_usage = bool(body.stream_options and body.stream_options.include_usage)
 
             async def sse():
-                rp = ReasoningParser(sc.reasoning_parser) if use_reasoning else None
+                rp = ReasoningParser(sc.reasoning_parser, stream_reasoning=body.stream_reasoning) if use_reasoning else None
+                every = bool(body.stream_options and body.stream_options.continuous_usage_stats)
                 tp = ToolCallParser(sc.tool_call_parser, body.tools) if use_tools else None
                 meta: Dict[str, Any] = {}
                 saw_tool = False
 
                 def chunk(delta: Dict[str, Any], finish=None) -> str:
-                    return "data: " + json.dumps({"id": cid, "object": "chat.completion.chunk", "created": int(time.time()),
-                                                  "model": model_name,
-                                                  "choices": [{"index": 0, "delta": delta, "finish_reason": finish}]}) + "\n\n"
+                    d = {"id": cid, "object": "chat.completion.chunk", "created": int(time.time()), "model": model_name,
+                         "choices": [{"index": 0, "delta": delta, "finish_reason": finish}]}
+                    if every and meta:
+                        d["usage"] = _usage(meta)
+                    return "data: " + json.dumps(d) + "\n\n"
                 try:
                     yield chunk({"role": "assistant", "content": ""})
                     async for o in _watch_disconnect(request, engine.generate_async(obj)):

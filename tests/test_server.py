@@ -132,3 +132,17 @@ def test_method_variants_of_generate_and_flush(client):
     r = client.put("/generate", json={"text": "hello", "sampling_params": {"max_new_tokens": 2, "temperature": 0}})
     assert r.status_code == 200 and r.json()["meta_info"]["completion_tokens"] == 2
     assert client.get("/flush_cache").status_code == client.post("/flush_cache").status_code == 200
+
+
+def test_compat_fields_and_continuous_usage(client):
+    msgs = [{"role": "user", "content": "hi"}]
+    s = _sse(client.post("/v1/chat/completions", json={"messages": msgs, "max_tokens": 4, "temperature": 0, "stream": True,
+                                                      "user": "u1", "stream_reasoning": False,
+                                                      "stream_options": {"include_usage": True, "continuous_usage_stats": True}}))
+    with_usage = [c for c in s if c.get("choices") and "usage" in c]
+    assert with_usage and with_usage[-1]["usage"]["completion_tokens"] >= with_usage[0]["usage"]["completion_tokens"]
+    assert s[-1]["usage"]["completion_tokens"] == 4
+    r = client.post("/generate", json={"text": "hello", "sampling_params": {"max_new_tokens": 2, "temperature": 0},
+                                       "logprob_start_len": -1, "lora_path": None, "session_params": None})
+    assert r.status_code == 200
+    assert client.post("/v1/completions", json={"prompt": "x", "max_tokens": 2, "user": "u"}).status_code == 200
