@@ -192,13 +192,17 @@ async def run_poisson(work, arrivals, engine=None, base_url=None, api_key=None) 
     return summarize(list(results), time.perf_counter() - t0)
 
 
-async def run_sequential(prompt_sizes, out_len, repeat, vocab, seed, engine=None, base_url=None, api_key=None):
+async def run_sequential(prompt_sizes, out_len, repeat, vocab, seed, engine=None, base_url=None, api_key=None,
+                         warmup: int = 0):
     rows = []
     session = None
     if engine is None:
         import aiohttp
 
         session = aiohttp.ClientSession(timeout=aiohttp.ClientTimeout(total=None))
+    for w in range(max(0, warmup)):      # untimed requests: first-use costs (graphs, allocator, caches) stay out
+        ids = make_workload(1, (prompt_sizes[0], prompt_sizes[0]), (8, 8), 0.0, 0, vocab, seed - 1 - w)[0][0]
+        await (_one_engine(engine, ids, 8) if engine is not None else _one_http(session, base_url, ids, 8, api_key))
     for n_in in prompt_sizes:
         res = []
         for rep in range(repeat):
@@ -235,7 +239,16 @@ def main(argv=None) -> None:
     ap = argparse.ArgumentParser(prog="python -m mllm_b200.bench_serve")
     make_args(ap)
     ap.add_argument("--mode", choices=["sequential", "poisson"], default="sequential")
-    ap.add_argument("--base-url", default=None)
+    ap.add_argument("--base-url", "--url", dest="base_url", default=None)
+    # spelled as in the reference's bench_serve (llama-bench style pp / tg run against a live server)
+    ap.add_argument("--prefill-sizes", dest="prompt_sizes", type=lambda v: [int(x) for x in str(v).split(",") if x],
+                    help="comma-separated prompt sizes (same as --prompt-sizes)")
+    ap.add_argument("--decode-tokens", dest="output_len", type=int, help="same as --output-len")
+    ap.add_argument("--warmup", type=int, default=2, help="untimed requests before the sequential measurement")
+    ap.add_argument("--temperature", type=float, default=0.0, help="accepted for compatibility; requests are greedy")
+    ap.add_argument("--model", default=None, help="accepted for compatibility; the server serves one model")
+    ap.add_argument("--client-timing", action="store_true",
+                    help="accepted for compatibility: timings are always taken at the client from the token stream")
     ap.add_argument("--api-key", default=None)
     ap.add_argument("--engine", action="store_true", help="drive an in-process engine instead of HTTP")
     ap.add_argument("--prompt-sizes", type=int, nargs="+", default=[128, 512, 2048])
@@ -263,7 +276,7 @@ def main(argv=None) -> None:
     try:
         if ns.mode == "sequential":
             rows = asyncio.run(run_sequential(ns.prompt_sizes, ns.output_len, ns.repeat, vocab, ns.seed, engine,
-                                              ns.base_url, ns.api_key))
+                                              ns.base_url, ns.api_key, warmup=ns.warmup))
             print_report(rows)
             result: Any = rows
         else:
