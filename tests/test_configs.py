@@ -140,3 +140,16 @@ def test_fp8_kv_cache_halves_the_cache_and_stays_close():
     err = (fp8_logits - ref_logits).abs().max().item()
     assert 0 < err < 0.05 * ref_logits.abs().max().item() + 0.02
     assert torch.equal(fp8_logits.argmax(-1), ref_logits.argmax(-1))
+
+
+def test_helper_command_lists_architectures_and_extensions(capsys):
+    import json
+
+    from mllm_b200.__main__ import main
+
+    main(["show-config"])
+    info = json.loads(capsys.readouterr().out)
+    assert "Qwen3ForCausalLM" in info["architectures"] and "compressed-tensors" in info["quantization"]
+    assert set(info["extensions"]) == {"mllm_b200_C", "mllm_b200_host"}
+    main(["models"])
+    assert "Qwen3VLForConditionalGeneration" in capsys.readouterr().out.split()
