@@ -387,6 +387,11 @@ def qk_norm_rope_kv_write(
     )
 
 
+def create_kv_indices(req_to_token, req_pool_indices, seq_lens, kv_start=None, max_len=None):
+    """``(kv_indptr, kv_indices)`` of a batch for callers that want a flat index list (device-side, no loop)."""
+    return ref.create_kv_indices(req_to_token, req_pool_indices, seq_lens, kv_start, max_len)
+
+
 def kv_write(k, v, loc, k_cache, v_cache) -> None:
     if not use_kernels(k) or k_cache.dtype != k.dtype:
         return ref.kv_write(k, v, loc, k_cache, v_cache)

@@ -252,6 +252,24 @@ def kv_write(k, v, loc, k_cache, v_cache) -> None:
     v_cache[loc.long()] = v.reshape(v.shape[0], *v_cache.shape[1:]).to(v_cache.dtype)
 
 
+def create_kv_indices(req_to_token: torch.Tensor, req_pool_indices: torch.Tensor, seq_lens: torch.Tensor,
+                      kv_start: Optional[torch.Tensor] = None, max_len: Optional[int] = None):
+    """Flat KV index list of a batch, as paged-attention libraries want it (role of mllm-kernel's
+    ``create_kv_indices``): ``kv_indices[kv_indptr[b] + j] = req_to_token[req_pool_indices[b], kv_start[b] + j]``
+    for ``j < seq_lens[b]``.  Returns ``(kv_indptr int32 [B + 1], kv_indices int32 [sum(seq_lens)])``.  The
+    attention kernels of this package read ``req_to_token`` directly and do not need it."""
+    lens = seq_lens.to(torch.int64)
+    B = lens.numel()
+    indptr = torch.zeros(B + 1, dtype=torch.int32, device=lens.device)
+    indptr[1:] = torch.cumsum(lens, 0).to(torch.int32)
+    width = int(max_len if max_len is not None else (int(lens.max()) if B else 0))
+    j = torch.arange(width, device=lens.device).unsqueeze(0)
+    start = kv_start.to(torch.int64).view(-1, 1) if kv_start is not None else 0
+    cols = (j + start).clamp_(max=req_to_token.shape[1] - 1)
+    rows = req_to_token[req_pool_indices.long().view(-1, 1), cols]
+    return indptr, rows[j < lens.view(-1, 1)].to(torch.int32)
+
+
 # --------------------------------------------------------------------------
 # attention over the slot-indexed KV pool
 # --------------------------------------------------------------------------

@@ -183,3 +183,22 @@ def test_window_and_logit_cap_agree_across_attention_paths():
     b = ref.attention_decode_batched(qd, kc, vc, rtt, req, seq, scale, 24, window=W, logit_cap=cap)
     torch.testing.assert_close(a, b, atol=1e-5, rtol=1e-5)
     assert not torch.allclose(a, ref.attention_decode(qd, kc, vc, rtt, req, seq, scale), atol=1e-3)
+
+
+def test_create_kv_indices_matches_a_python_loop():
+    import torch
+
+    from mllm_b200 import ops
+
+    torch.manual_seed(4)
+    rtt = torch.randint(0, 1000, (6, 40), dtype=torch.int32)
+    req = torch.tensor([4, 0, 5], dtype=torch.int32)
+    lens = torch.tensor([7, 0, 19], dtype=torch.int32)
+    start = torch.tensor([2, 0, 11], dtype=torch.int32)
+    indptr, idx = ops.create_kv_indices(rtt, req, lens, start)
+    want = []
+    for b in range(3):
+        want += rtt[req[b], start[b]: start[b] + lens[b]].tolist()
+    assert indptr.tolist() == [0, 7, 7, 26] and idx.tolist() == want and idx.dtype == torch.int32
+    indptr2, idx2 = ops.create_kv_indices(rtt, req, lens, max_len=32)
+    assert idx2.tolist() == rtt[4, :7].tolist() + rtt[5, :19].tolist()
