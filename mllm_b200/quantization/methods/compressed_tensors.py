@@ -1,4 +1,5 @@
-"""compressed-tensors checkpoints (llm-compressor): W4A16 ``pack-quantized`` and W8A8 ``int-quantized``.
+"""compressed-tensors checkpoints (llm-compressor): W4A16 ``pack-quantized``, W8A8 ``int-quantized`` and W8A16
+(expanded to 16 bits at load).
 
 Config parsing, the ``ignore`` matching rules (exact prefix, path component, ``re:`` regex, with
 ``model.`` / ``model.language_model.`` prefixes stripped) and the checkpoint tensor contracts
@@ -95,6 +96,60 @@ class CompressedTensorsW8A8Method(LinearMethodBase):
         return y if residual is None else y + residual
 
 
+class CompressedTensorsW8A16Method(UnquantizedLinearMethod):
+    """8-bit symmetric weights (per channel or per group), 16-bit activations.  There is no 8-bit-weight GEMM
+    here (the reference serves this scheme with Marlin): the weights are expanded to the serving dtype once,
+    after loading, and the ordinary tcgen05 GEMM runs — same outputs as the dequantised model, no memory
+    saving.  ``weight`` int8 ``[N, K]`` (``int-quantized``) or ``weight_packed`` int32 ``[N, K/4]``
+    (``pack-quantized``: byte i of word j = element 4j+i, stored +128), ``weight_scale`` ``[N, K/g]``."""
+
+    def __init__(self, group_size: int, packed: bool) -> None:
+        self.group_size, self.packed = group_size, packed
+
+    def create_weights(self, layer, input_size_per_partition, output_partition_sizes, input_size, output_size,
+                       params_dtype, **extra) -> None:
+        n, k = sum(output_partition_sizes), input_size_per_partition
+        g = k if self.group_size in (-1, None) else self.group_size
+        if k % g or (self.packed and k % 4):
+            raise ValueError(f"W8A16: input size {k} must be divisible by the group size {g}")
+        if self.packed:
+            w = nn.Parameter(torch.zeros(n, k // 4, dtype=torch.int32), requires_grad=False)
+            set_weight_attrs(w, {"input_dim": 1, "output_dim": 0, "packed_dim": 1, "pack_factor": 4})
+            shape = nn.Parameter(torch.zeros(2, dtype=torch.int64), requires_grad=False)
+            set_weight_attrs(shape, {"ignore_shard": True})
+            set_weight_attrs(shape, extra)
+            layer.register_parameter("weight_shape", shape)
+        else:
+            w = nn.Parameter(torch.zeros(n, k, dtype=torch.int8), requires_grad=False)
+            set_weight_attrs(w, {"input_dim": 1, "output_dim": 0})
+        sc = nn.Parameter(torch.zeros(n, k // g, dtype=params_dtype), requires_grad=False)
+        set_weight_attrs(sc, {"input_dim": 1, "output_dim": 0})
+        for p in (w, sc):
+            set_weight_attrs(p, extra)
+        layer.register_parameter("weight_packed" if self.packed else "weight", w)
+        layer.register_parameter("weight_scale", sc)
+        layer._w8_dtype, layer._w8_group = params_dtype, g
+
+    def process_weights_after_loading(self, layer) -> None:
+        if hasattr(layer, "weight_scale"):
+            if self.packed:
+                words = layer.weight_packed.data
+                shifts = torch.arange(0, 32, 8, device=words.device, dtype=torch.int32)
+                q = (((words.unsqueeze(-1) >> shifts) & 0xFF).to(torch.int16) - 128).reshape(words.shape[0], -1)
+                delattr(layer, "weight_packed")
+                if hasattr(layer, "weight_shape"):
+                    delattr(layer, "weight_shape")
+            else:
+                q = layer.weight.data.to(torch.int16)
+                delattr(layer, "weight")
+            scale = layer.weight_scale.data.float().repeat_interleave(layer._w8_group, dim=1)
+            delattr(layer, "weight_scale")
+            w = nn.Parameter((q.float() * scale).to(layer._w8_dtype), requires_grad=False)
+            set_weight_attrs(w, {"input_dim": 1, "output_dim": 0})
+            layer.register_parameter("weight", w)
+        super().process_weights_after_loading(layer)
+
+
 def _signature(cfg: "CompressedTensorsConfig") -> str:
     """Which kernel family serves this config, or a clear error."""
     if cfg.weight_type not in (None, "int"):
@@ -105,6 +160,10 @@ def _signature(cfg: "CompressedTensorsConfig") -> str:
         if cfg.actorder not in (None, "static", False):
             raise ValueError("compressed-tensors W4A16: activation reordering is not supported")
         return "w4a16"
+    if cfg.weight_bits == 8 and cfg.input_bits is None and cfg.quant_format in ("int-quantized", "naive-quantized", "pack-quantized"):
+        if not cfg.symmetric or cfg.weight_strategy not in ("channel", "group"):
+            raise ValueError("compressed-tensors W8A16: weights must be symmetric, per channel or per group")
+        return "w8a16"
     if cfg.quant_format in ("int-quantized", "naive-quantized") and cfg.weight_bits == 8 and cfg.input_bits == 8:
         if cfg.weight_strategy != "channel" or not cfg.symmetric:
             raise ValueError("compressed-tensors W8A8: weights must be per-channel symmetric")
@@ -186,4 +245,7 @@ class CompressedTensorsConfig(QuantizationConfig):
             return UnquantizedLinearMethod()
         if kind == "w4a16":
             return CompressedTensorsW4A16Method(self.group_size if self.group_size is not None else -1)
+        if kind == "w8a16":
+            return CompressedTensorsW8A16Method(self.group_size if self.weight_strategy == "group" else -1,
+                                                packed=self.quant_format == "pack-quantized")
         return CompressedTensorsW8A8Method()

@@ -304,3 +304,31 @@ def test_fp8_block_and_per_tensor_weights_expand_to_the_dequantised_model():
     assert type(cfg.get_quant_method(None, "lm_head")).__name__ == "UnquantizedLinearMethod"
     with pytest.raises(ValueError):
         get_quantization_config("fp8").from_config({"fmt": "e5m2"})
+
+
+def test_ct_w8a16_channel_group_and_packed_expand_to_the_dequantised_weights():
+    torch.manual_seed(11)
+    K, N = 128, 48
+    x = torch.randn(3, K)
+    q = torch.randint(-127, 128, (N, K), dtype=torch.int8)
+    # per channel, int-quantized
+    cfg = get_quantization_config("compressed-tensors").from_config(_ct(fmt="int-quantized", bits=8, group=None, strategy="channel"))
+    lin = Linear(K, N, quant_method=cfg.get_quant_method(None, "l"), params_dtype=torch.float32)
+    assert type(lin.quant_method).__name__ == "CompressedTensorsW8A16Method"
+    s = torch.rand(N, 1) * 0.01 + 0.001
+    lin.weight.weight_loader(lin.weight, q)
+    lin.weight_scale.weight_loader(lin.weight_scale, s)
+    lin.quant_method.process_weights_after_loading(lin)
+    torch.testing.assert_close(lin(x), x @ (q.float() * s).t(), atol=1e-4, rtol=1e-4)
+    # per group of 32, pack-quantized (four offset-binary bytes per word)
+    cfg_g = get_quantization_config("compressed-tensors").from_config(_ct(fmt="pack-quantized", bits=8, group=32))
+    lin_g = Linear(K, N, quant_method=cfg_g.get_quant_method(None, "l"), params_dtype=torch.float32)
+    sg = torch.rand(N, K // 32) * 0.01 + 0.001
+    u = (q.to(torch.int64) + 128).reshape(N, K // 4, 4)
+    words = (u[..., 0] | (u[..., 1] << 8) | (u[..., 2] << 16) | (u[..., 3] << 24))
+    words = torch.where(words >= 2 ** 31, words - 2 ** 32, words).to(torch.int32)
+    lin_g.weight_packed.weight_loader(lin_g.weight_packed, words)
+    lin_g.weight_scale.weight_loader(lin_g.weight_scale, sg)
+    lin_g.quant_method.process_weights_after_loading(lin_g)
+    assert not hasattr(lin_g, "weight_packed") and lin_g.weight.shape == (N, K)
+    torch.testing.assert_close(lin_g(x), x @ (q.float() * sg.repeat_interleave(32, 1)).t(), atol=1e-4, rtol=1e-4)
