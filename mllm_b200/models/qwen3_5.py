@@ -199,6 +199,7 @@ class Qwen3_5ForCausalLM(nn.Module):
             config.layer_types = ["full_attention" if (i + 1) % interval == 0 else "linear_attention"
                                   for i in range(config.num_hidden_layers)]
         self.config = config
+        self.quant_config = quant_config
         self.model = self.model_cls(config, quant_config, params_dtype)
         self.tie = bool(getattr(config, "tie_word_embeddings", False))
         if not self.tie:

@@ -86,7 +86,9 @@ class _MoeLoading:
                     p.weight_loader(p, w, expert, "gate" if which == "gate_proj" else "up")
                     loaded.add(f"{prefix}.block.w13")
 
-        for name, t in weights:
+        from ..quantization.expert_dequant import dequantized_experts
+
+        for name, t in dequantized_experts(weights, getattr(self, "quant_config", None), self.model.embed_tokens.weight.dtype):
             canon = name
             for old, new in _PREFIXES:
                 if canon.startswith(old):

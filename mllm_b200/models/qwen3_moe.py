@@ -69,7 +69,7 @@ class Qwen3MoeForCausalLM(Qwen3ForCausalLM):
         params = dict(self.named_parameters())
         rest = []
         loaded = set()
-        for name, tensor in self._split_fused_experts(weights):
+        for name, tensor in self._split_fused_experts(self._dequantized_experts(weights)):
             canon = self._canonical_name(name)
             m = _EXPERT_RE.match(canon) if canon else None
             if m is None:
@@ -95,6 +95,11 @@ class Qwen3MoeForCausalLM(Qwen3ForCausalLM):
                     loaded.add(f"{prefix}.block.w13")
         loaded |= super().load_weights(rest)
         return loaded
+
+    def _dequantized_experts(self, weights: Iterable[Tuple[str, torch.Tensor]]):
+        from ..quantization.expert_dequant import dequantized_experts
+
+        return dequantized_experts(weights, self.quant_config, self.model.embed_tokens.weight.dtype)
 
     def _split_fused_experts(self, weights: Iterable[Tuple[str, torch.Tensor]]):
         """Yields per-expert ``gate_proj`` / ``up_proj`` / ``down_proj`` matrices for checkpoints that store

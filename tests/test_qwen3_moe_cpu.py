@@ -164,3 +164,67 @@ def test_mixtral_matches_hf_with_hub_style_names():
 
     _compare_moe_family("MixtralForCausalLM", hf, cfgd, rename=hub_names)
     _compare_moe_family("MixtralForCausalLM", hf, cfgd)          # and the fused in-memory layout
+
+
+def test_gptq_quantised_moe_checkpoint_loads_like_its_dequantised_twin(tmp_path):
+    """A GPTQ checkpoint of the tiny MoE model — attention projections served by the 4-bit linear method,
+    expert projections dequantised at load — gives the logits of the dense model built from the same
+    dequantised weights."""
+    import json
+
+    from safetensors.torch import save_file
+
+    from mllm_b200.models.presets import get_preset, preset_to_config_json
+    from mllm_b200.quantization.methods.gptq import pack_words
+
+    cfg = get_preset("qwen3-moe-tiny", tie_word_embeddings=False)
+    cfg_json = dict(preset_to_config_json("qwen3-moe-tiny"), tie_word_embeddings=False,
+                    quantization_config={"quant_method": "gptq", "bits": 4, "group_size": 32, "sym": True, "desc_act": False})
+    g = torch.Generator().manual_seed(1)
+    H, D, V, E, Im = cfg.hidden_size, cfg.head_dim, cfg.vocab_size, cfg.num_experts, cfg.moe_intermediate_size
+    hq, hkv = cfg.num_attention_heads, cfg.num_key_value_heads
+    sd_q, sd_d = {}, {}
+
+    def dense(name, t):
+        sd_q[name] = sd_d[name] = t
+
+    def quant(prefix, n, k):
+        q = torch.randint(0, 16, (k, n), generator=g, dtype=torch.uint8)
+        s = torch.rand(k // 32, n, generator=g) * 0.02
+        z = torch.full((k // 32, n), 8, dtype=torch.uint8)
+        sd_q[prefix + ".qweight"], sd_q[prefix + ".qzeros"], sd_q[prefix + ".scales"] = pack_words(q, 0), pack_words(z - 1, 1), s
+        sd_q[prefix + ".g_idx"] = torch.arange(k, dtype=torch.int32) // 32
+        sd_d[prefix + ".weight"] = ((q.float() - 8) * s.repeat_interleave(32, 0)).t().contiguous()
+
+    dense("model.embed_tokens.weight", torch.randn(V, H, generator=g) * 0.05)
+    dense("lm_head.weight", torch.randn(V, H, generator=g) * 0.05)
+    dense("model.norm.weight", torch.ones(H))
+    for i in range(cfg.num_hidden_layers):
+        p = f"model.layers.{i}."
+        for nm, n, k in (("self_attn.q_proj", hq * D, H), ("self_attn.k_proj", hkv * D, H), ("self_attn.v_proj", hkv * D, H),
+                         ("self_attn.o_proj", H, hq * D)):
+            quant(p + nm, n, k)
+        dense(p + "mlp.gate.weight", torch.randn(E, H, generator=g))
+        for e in range(E):
+            quant(p + f"mlp.experts.{e}.gate_proj", Im, H)
+            quant(p + f"mlp.experts.{e}.up_proj", Im, H)
+            quant(p + f"mlp.experts.{e}.down_proj", H, Im)
+        for nm, d in (("self_attn.q_norm.weight", D), ("self_attn.k_norm.weight", D), ("input_layernorm.weight", H),
+                      ("post_attention_layernorm.weight", H)):
+            dense(p + nm, torch.ones(d))
+    logits = []
+    for name, sd, cj in (("gptq", sd_q, cfg_json), ("dense", sd_d, {k: v for k, v in cfg_json.items() if k != "quantization_config"})):
+        d = tmp_path / name
+        d.mkdir()
+        (d / "config.json").write_text(json.dumps(cj))
+        save_file({k: v.contiguous() for k, v in sd.items()}, str(d / "model.safetensors"))
+        mr = ModelRunner(ServerConfig(model_path=str(d), dtype="float32", max_running_requests=2, max_total_tokens=256), device="cpu")
+        mr.initialize()
+        ids = torch.arange(10) * 11 % V
+        slots = mr.req_to_token_pool.alloc(1)
+        loc = mr.token_to_kv_pool_allocator.alloc(10)
+        mr.req_to_token_pool.req_to_token[slots[0], :10] = loc.int()
+        lens = torch.tensor([10])
+        fb = mr.prepare_forward_batch_extend(ids, torch.tensor(slots), lens, lens, torch.zeros_like(lens), loc)
+        logits.append(mr.forward(fb).next_token_logits)
+    torch.testing.assert_close(logits[0], logits[1], atol=3e-4, rtol=3e-4)
