@@ -1,0 +1,78 @@
+"""Model configurations that leave the tcgen05 attention kernels (head size other than 128, sliding window,
+8-bit KV cache) on a GPU: GEMMs, norms and the rest still run on the package's kernels, attention on the
+library / batched PyTorch fallbacks.  Each case compares the GPU model (bf16) with the CPU model (fp32) holding
+the same weights: prefill in two chunks, then decode."""
+import pytest
+import torch
+
+from mllm_b200 import ops
+
+pytestmark = pytest.mark.gpu
+
+
+def _pair(preset, kv="auto", **overrides):
+    from mllm_b200.configs import ServerConfig
+    from mllm_b200.executor import ModelRunner
+    from mllm_b200.models.presets import get_preset
+
+    def build(device, dtype, kv_dtype):
+        sc = ServerConfig(model_path=f"preset:{preset}", dtype=dtype, max_running_requests=2, max_total_tokens=1024,
+                          disable_cuda_graph=True)
+        mr = ModelRunner(sc, hf_config=get_preset(preset, **overrides), kv_cache_dtype=kv_dtype, device=device)
+        mr.initialize()
+        return mr
+
+    gpu, cpu = build("cuda:0", "bfloat16", kv), build("cpu", "float32", "auto")
+    cpu.model.load_state_dict({k: v.detach().float().cpu() for k, v in gpu.model.state_dict().items()}, strict=False)
+    return gpu, cpu
+
+
+def _run(mr, ids):
+    dev = mr.device
+    B, L = ids.shape
+    half = L // 2
+    slots = mr.req_to_token_pool.alloc(B)
+    loc = mr.token_to_kv_pool_allocator.alloc(B * L).view(B, L)
+    sl = torch.tensor(slots, device=dev)
+    mr.req_to_token_pool.req_to_token[sl.long(), :L] = loc.int()
+    full = lambda n: torch.full((B,), n, device=dev, dtype=torch.int32)  # noqa: E731
+    fb = mr.prepare_forward_batch_extend(ids[:, :half].reshape(-1).to(dev).long(), sl, full(half), full(half), full(0),
+                                         loc[:, :half].reshape(-1), extend_seq_lens_cpu=[half] * B, extend_prefix_lens_cpu=[0] * B)
+    mr.forward(fb)
+    fb = mr.prepare_forward_batch_extend(ids[:, half:].reshape(-1).to(dev).long(), sl, full(L), full(L - half), full(half),
+                                         loc[:, half:].reshape(-1), extend_seq_lens_cpu=[L - half] * B,
+                                         extend_prefix_lens_cpu=[half] * B)
+    outs = [mr.forward(fb).next_token_logits.float().cpu()]
+    nxt = outs[-1].argmax(-1).to(dev)
+    loc1 = mr.token_to_kv_pool_allocator.alloc(B)
+    mr.req_to_token_pool.req_to_token[sl.long(), L] = loc1.int()
+    fbd = mr.prepare_forward_batch_decode(nxt, sl, full(L + 1), loc1, max_seq_len=L + 1)
+    outs.append(mr.forward(fbd).next_token_logits.float().cpu())
+    return torch.stack(outs)
+
+
+def _close(got, want, floor=0.985):
+    cos = torch.nn.functional.cosine_similarity(got.flatten(0, 1), want.flatten(0, 1), dim=-1)
+    assert cos.min().item() > floor, cos
+
+
+@pytest.mark.parametrize("preset,overrides", [
+    ("llama-tiny", dict(head_dim=64, num_attention_heads=4, num_key_value_heads=2)),       # head size 64
+    ("llama-tiny", dict(sliding_window=8, architectures=["MistralForCausalLM"])),          # sliding window
+    ("qwen2-tiny", dict(head_dim=64)),                                                     # q/k/v biases + head size 64
+])
+def test_gpu_model_on_fallback_attention_matches_cpu(preset, overrides):
+    gpu, cpu = _pair(preset, **overrides)
+    ids = torch.randint(0, 1000, (2, 24), generator=torch.Generator().manual_seed(0))
+    got, want = _run(gpu, ids), _run(cpu, ids)
+    ops.check_status()
+    _close(got, want)
+
+
+def test_fp8_kv_cache_on_gpu_stays_close_to_the_cpu_model():
+    gpu, cpu = _pair("qwen3-tiny", kv="fp8_e4m3")
+    assert gpu.token_to_kv_pool.store.dtype == torch.float8_e4m3fn and gpu.cuda_graph_runner is None
+    ids = torch.randint(0, 1000, (2, 24), generator=torch.Generator().manual_seed(1))
+    got, want = _run(gpu, ids), _run(cpu, ids)
+    ops.check_status()
+    _close(got, want, floor=0.97)
