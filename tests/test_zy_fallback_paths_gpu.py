@@ -24,6 +24,8 @@ def _pair(preset, kv="auto", **overrides):
 
     gpu, cpu = build("cuda:0", "bfloat16", kv), build("cpu", "float32", "auto")
     cpu.model.load_state_dict({k: v.detach().float().cpu() for k, v in gpu.model.state_dict().items()}, strict=False)
+    if hasattr(cpu.model, "post_load"):
+        cpu.model.post_load()
     return gpu, cpu
 
 
@@ -60,6 +62,7 @@ def _close(got, want, floor=0.985):
     ("llama-tiny", dict(head_dim=64, num_attention_heads=4, num_key_value_heads=2)),       # head size 64
     ("llama-tiny", dict(sliding_window=8, architectures=["MistralForCausalLM"])),          # sliding window
     ("qwen2-tiny", dict(head_dim=64)),                                                     # q/k/v biases + head size 64
+    ("qwen3.5-tiny", dict(head_dim=256)),                                                  # hybrid model, published head size
 ])
 def test_gpu_model_on_fallback_attention_matches_cpu(preset, overrides):
     gpu, cpu = _pair(preset, **overrides)
