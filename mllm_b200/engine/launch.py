@@ -290,6 +290,11 @@ class Engine:
             from ..orchestrator.ipc_utils import cleanup_ipc
 
             cleanup_ipc(self._addrs)
+            for q in getattr(self, "_tensor_queues", None) or []:
+                try:
+                    q.close()
+                except Exception:
+                    pass
         self._launched = self._healthy = False
 
     # ------------------------------------------------------------------ requests
