@@ -76,7 +76,9 @@ class CudaGraphRunner:
         fb = self._batch(bs)
         out = self.mr.model(fb.input_ids, fb.positions, fb)
         if self.tp_sharded_logits:
-            return out.next_token_logits, None  # vocabulary slice; gathered and sampled after the replay
+            # vocabulary slice: this rank's best candidate per row is found inside the graph; the ranks'
+            # candidates are compared after the replay (full logits are gathered only if someone needs them)
+            return out.next_token_logits, self.mr.model.local_greedy(out.next_token_logits)
         return out.next_token_logits, ops.argmax(out.next_token_logits)
 
     @torch.no_grad()
@@ -127,7 +129,10 @@ class CudaGraphRunner:
         self.replays += 1
         self.replayed_kernels += self.kernels_per_graph.get(bs, 0)
         if self.tp_sharded_logits:
-            return LogitsProcessorOutput(next_token_logits=self.mr.model.gather_logits(self.logits[bs][:raw]))
+            out = LogitsProcessorOutput(local_logits=self.logits[bs][:raw], gather=self.mr.model.gather_logits)
+            vals, ids = self.next_ids[bs]
+            out.next_token_ids = self.mr.model.pick_greedy(vals[:raw], ids[:raw])
+            return out
         out = LogitsProcessorOutput(next_token_logits=self.logits[bs][:raw])
         out.next_token_ids = self.next_ids[bs][:raw]
         return out

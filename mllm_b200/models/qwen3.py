@@ -28,13 +28,30 @@ from ..parallel import state as pstate
 from ..parallel.symm import get_tp_comm
 
 
-@dataclass
 class LogitsProcessorOutput:
-    next_token_logits: torch.Tensor
-    hidden_states: Optional[torch.Tensor] = None
-    # pipeline parallelism: on every stage but the last the logits are a [rows, 1] stand-in and the sampled
-    # ids arrive from the last stage
-    pp_placeholder: bool = False
+    """Result of a forward pass.  ``next_token_logits`` are the full-vocabulary logits of the rows that
+    produce a token; under tensor parallelism a pass may hand over only this rank's vocabulary slice
+    (``local_logits`` + ``gather``), and the full logits are then assembled the first time they are asked for —
+    greedy decoding never asks (``next_token_ids`` come from per-rank maxima and one tiny all-gather)."""
+
+    def __init__(self, next_token_logits: Optional[torch.Tensor] = None, hidden_states: Optional[torch.Tensor] = None,
+                 pp_placeholder: bool = False, local_logits: Optional[torch.Tensor] = None, gather=None) -> None:
+        self._full = next_token_logits
+        self.hidden_states = hidden_states
+        # pipeline parallelism: on every stage but the last the logits are a [rows, 1] stand-in and the sampled
+        # ids arrive from the last stage
+        self.pp_placeholder = pp_placeholder
+        self.local_logits, self._gather = local_logits, gather
+
+    @property
+    def next_token_logits(self) -> Optional[torch.Tensor]:
+        if self._full is None and self.local_logits is not None:
+            self._full = self._gather(self.local_logits)
+        return self._full
+
+    @next_token_logits.setter
+    def next_token_logits(self, value: Optional[torch.Tensor]) -> None:
+        self._full, self.local_logits = value, None
 
 
 def _quant_method(quant_config, prefix: str):
@@ -259,6 +276,29 @@ class Qwen3ForCausalLM(nn.Module):
                 return logits  # this rank's vocabulary slice; gathered by the caller after the replay
             logits = pstate.tensor_model_parallel_all_gather(logits, dim=-1)
         return logits[:, : self.config.vocab_size]
+
+    def local_greedy(self, local_logits: torch.Tensor):
+        """This rank's best candidate per row: (logit value fp32 [rows], global token id int64 [rows]); columns
+        that only pad the vocabulary to a multiple of the rank count are left out."""
+        per_rank = local_logits.shape[-1]
+        start = pstate.get_tensor_model_parallel_rank() * per_rank if self.tp_size > 1 else 0
+        valid = min(per_rank, self.config.vocab_size - start)
+        if valid <= 0:      # this rank holds padding only
+            rows = local_logits.shape[0]
+            return (torch.full((rows,), float("-inf"), device=local_logits.device),
+                    torch.zeros(rows, dtype=torch.int64, device=local_logits.device))
+        vals, idx = local_logits[:, :valid].float().max(dim=-1)
+        return vals, idx.to(torch.int64) + start
+
+    def pick_greedy(self, vals: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        """Global argmax from every rank's :meth:`local_greedy` candidates: one all-gather of two numbers per
+        row; ties go to the lower token id, as a full-vocabulary argmax would decide."""
+        if self.tp_size == 1:
+            return ids
+        pair = torch.stack([vals, ids.to(torch.float32)], dim=-1)                    # ids < 2^24: exact in fp32
+        allp = pstate.tensor_model_parallel_all_gather(pair.unsqueeze(0), dim=0)     # [tp, rows, 2]
+        best = allp[..., 0].argmax(dim=0)                                            # first rank holding the max
+        return allp[..., 1].gather(0, best.unsqueeze(0)).squeeze(0).to(torch.int64)
 
     def gather_logits(self, local_logits: torch.Tensor) -> torch.Tensor:
         """Full-vocabulary logits from per-rank slices (used after a graph replay)."""

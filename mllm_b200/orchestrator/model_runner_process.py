@@ -247,7 +247,8 @@ class ModelRunnerProcess:
             nxt = pre
         else:
             nxt = r.sample(out, info)
-        self._record_logprobs(reqs, out.next_token_logits, nxt)
+        if any(q.return_logprob for q in reqs):      # touching the logits may trigger a cross-rank gather
+            self._record_logprobs(reqs, out.next_token_logits, nxt)
         return nxt, fb
 
     @staticmethod

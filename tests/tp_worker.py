@@ -159,6 +159,20 @@ def run(out_path: str, device: str, dtype_name: str) -> None:
         out = mr.forward(fb)
         outs.append(out.next_token_logits.float().cpu())
         nxt = mr.sample(out).to(dev)
+    if world > 1 and pp == 1 and hasattr(mr.model, "pick_greedy"):
+        # greedy decoding without gathering logits: per-rank best candidate + one tiny all-gather must agree with
+        # the argmax over the full vocabulary (columns that pad the vocabulary must never win)
+        full = out.next_token_logits.float()
+        V = full.shape[-1]
+        per = -(-(V + 3) // world)                      # pretend the vocabulary needed padding
+        padded = torch.full((full.shape[0], per * world), 1e4, device=full.device)
+        padded[:, :V] = full
+        saved_v = mr.model.config.vocab_size
+        mr.model.config.vocab_size = V
+        vals, ids_l = mr.model.local_greedy(padded[:, rank * per:(rank + 1) * per])
+        picked = mr.model.pick_greedy(vals, ids_l)
+        mr.model.config.vocab_size = saved_v
+        assert torch.equal(picked.cpu(), full.argmax(-1).cpu()), (picked, full.argmax(-1))
     if device != "cpu":
         from mllm_b200 import ops
 
