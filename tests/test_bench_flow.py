@@ -61,3 +61,14 @@ def test_watchdog_ends_a_run_that_never_finishes():
     out = _last_json(p.stdout)
     assert out["value"] is None and "stuck phase" in out["error"] and out["n_gpus"] == 4
     assert "time.sleep" in p.stderr or "File" in p.stderr   # the stack dump
+
+
+def test_two_tensor_parallel_ranks_share_one_batch():
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", "29548", str(ROOT / "bench.py"), "--gpus", "2", "--parallelism", "tp", *TINY]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=_env(), cwd=ROOT)
+    assert p.returncode == 0, p.stderr[-2000:]
+    out = _last_json(p.stdout)
+    assert out["n_gpus"] == 2 and out["scaling"] == "strong"
+    assert out["config"]["parallelism"] == "tp2" and out["config"]["global_batch"] == 2
+    assert out["e2e"]["h2d_bytes_per_step"] == 2 * 32 * 4
