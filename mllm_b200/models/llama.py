@@ -1,5 +1,5 @@
-"""Llama-family and Qwen2-family decoders (the architectures the reference's C++ runtime ships beside
-Qwen3: ``mllm/models/llama``, ``mllm/models/qwen2``-style configs).  Both are the Qwen3 decoder stack
+"""Llama-family and Qwen2-family decoders (architectures the reference's C++ runtime ships beside Qwen3:
+``mllm/models/llama``, ``mllm/models/qwen2_5``, ``mllm/models/smollm3_3B``).  Both are the Qwen3 decoder stack
 without the per-head q/k RMSNorm: same fused QKV + RoPE + KV-write prologue (norm weights absent), same
 attention and SwiGLU kernels, same tensor-parallel sharding and quantised linears.
 

@@ -1,4 +1,4 @@
-"""Qwen2.5-VL (``Qwen2_5_VLForConditionalGeneration``): Qwen2 decoder with sectioned 3-D rope, behind a
+"""Qwen2.5-VL (``Qwen2_5_VLForConditionalGeneration``; ``mllm/models/qwen2_5vl`` in the reference's C++ runtime): Qwen2 decoder with sectioned 3-D rope, behind a
 vision tower with RMSNorm blocks, SwiGLU MLPs and *windowed* attention: patches are reordered (in units of
 one merged 2 x 2 token) so that every ``window_size`` square is contiguous, most blocks attend inside a
 window, the blocks listed in ``fullatt_block_indexes`` attend over the whole image, and the merged tokens

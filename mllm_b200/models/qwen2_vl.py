@@ -1,4 +1,4 @@
-"""Qwen2-VL (``Qwen2VLForConditionalGeneration``): a Qwen2 decoder (q / k / v biases, no q/k norm) with
+"""Qwen2-VL (``Qwen2VLForConditionalGeneration``; the reference's C++ runtime has it as ``mllm/models/qwen2vl``): a Qwen2 decoder (q / k / v biases, no q/k norm) with
 sectioned — not interleaved — 3-D rotary positions, behind a vision tower that is the Qwen3-VL tower
 without the learned position table and without deepstack taps (LayerNorm blocks, QuickGELU MLP, 2 x 2
 merger).  The checkpoint's names and config fields are translated here; kernels and control flow are

@@ -1,5 +1,6 @@
-"""GPTQ / AutoGPTQ checkpoints (``quant_method: "gptq"``): 4-bit weights, group-wise scales, optional
-zero points, no activation reordering.
+"""GPTQ / AutoGPTQ checkpoints (``quant_method: "gptq"``): 4-bit weights, group-wise scales, optional zero
+points (the layout the reference repacks for Marlin in
+``mllm-kernel/mllm_kernel/cuda/csrc/gemm/marlin/gptq_marlin_repack.cuh``).
 
 Checkpoint tensors per linear: ``qweight`` int32 ``[K/8, N]`` (eight consecutive input channels per
 word, low nibble first), ``qzeros`` int32 ``[K/g, N/8]`` (eight consecutive output channels per word;
