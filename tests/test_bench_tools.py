@@ -70,3 +70,29 @@ def test_bench_serve_workload_and_poisson_run():
         assert [r["pp"] for r in rows] == [8, 16] and all(r["decode_tok_s"] > 0 for r in rows)
     finally:
         eng.shutdown()
+
+
+def test_random_checkpoint_directory_loads_here_and_in_transformers(tmp_path):
+    """The seeded random-init checkpoint the benchmark's reference arm serves: a plain HF directory
+    (config.json + safetensors + index) that our runner and transformers both load, with the same logits."""
+    import torch
+
+    from mllm_b200.configs import ServerConfig
+    from mllm_b200.executor import ModelRunner
+    from mllm_b200.io.random_checkpoint import write_random_checkpoint
+
+    tr = pytest.importorskip("transformers")
+    d = write_random_checkpoint("qwen3-tiny", tmp_path / "ck", seed=0, dtype=torch.float32, device="cpu")
+    assert (d / ".complete").exists() and write_random_checkpoint("qwen3-tiny", d) == d      # second call reuses it
+    mr = ModelRunner(ServerConfig(model_path=str(d), dtype="float32", max_running_requests=2, max_total_tokens=256), device="cpu")
+    mr.initialize()
+    ids = torch.arange(9).view(1, 9) * 5 % 1000
+    slots = mr.req_to_token_pool.alloc(1)
+    loc = mr.token_to_kv_pool_allocator.alloc(9)
+    mr.req_to_token_pool.req_to_token[slots[0], :9] = loc.int()
+    lens = torch.tensor([9])
+    got = mr.forward(mr.prepare_forward_batch_extend(ids[0], torch.tensor(slots), lens, lens, torch.zeros_like(lens), loc)).next_token_logits
+    hf = tr.AutoModelForCausalLM.from_pretrained(str(d), torch_dtype=torch.float32).eval()
+    with torch.no_grad():
+        want = hf(ids).logits[:, -1]
+    torch.testing.assert_close(got, want, atol=5e-4, rtol=5e-4)
