@@ -94,7 +94,11 @@ class Engine:
         vc = getattr(cfg, "vision_config", None)
         if vc is None or getattr(cfg, "image_token_id", None) is None:
             return None
-        return dict(image_token_id=int(cfg.image_token_id), vision_start_token_id=int(cfg.vision_start_token_id),
+        from ..utils.image_processor import CLIP_MEAN, CLIP_STD
+
+        clip = str(getattr(cfg, "model_type", "")) in ("qwen2_vl", "qwen2_5_vl")   # these normalise with CLIP statistics
+        return dict(image_mean=list(CLIP_MEAN) if clip else 0.5, image_std=list(CLIP_STD) if clip else 0.5,
+                    image_token_id=int(cfg.image_token_id), vision_start_token_id=int(cfg.vision_start_token_id),
                     vision_end_token_id=int(getattr(cfg, "vision_end_token_id", cfg.vision_start_token_id)),
                     patch_size=int(vc.patch_size), merge_size=int(getattr(vc, "spatial_merge_size", 2)),
                     temporal_patch_size=int(getattr(vc, "temporal_patch_size", 2)))

@@ -78,7 +78,8 @@ class TokenizerWorker:
             arr = item if isinstance(item, (np.ndarray, torch.Tensor)) else np.asarray(self.load_image(item))
             img = torch.as_tensor(np.asarray(arr)).to(torch.uint8)
             h.update(img.numpy().tobytes())
-            pv, g = preprocess_image(img, mc["patch_size"], mc["merge_size"], mc["temporal_patch_size"])
+            pv, g = preprocess_image(img, mc["patch_size"], mc["merge_size"], mc["temporal_patch_size"],
+                                     mean=mc.get("image_mean", 0.5), std=mc.get("image_std", 0.5))
             pix.append(pv)
             grids.append(g)
             block += [mc["vision_start_token_id"]] + [mc["image_token_id"]] * image_token_count(g, mc["merge_size"]) + \

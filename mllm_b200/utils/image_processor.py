@@ -16,6 +16,10 @@ import torch
 import torch.nn.functional as F
 
 
+CLIP_MEAN = (0.48145466, 0.4578275, 0.40821073)
+CLIP_STD = (0.26862954, 0.26130258, 0.27577711)
+
+
 def smart_resize(height: int, width: int, factor: int = 32, min_pixels: int = 64 * 32 * 32,
                  max_pixels: int = 16384 * 32 * 32) -> Tuple[int, int]:
     """Closest size with both sides divisible by ``factor`` and the area inside the pixel budget."""
@@ -34,8 +38,10 @@ def smart_resize(height: int, width: int, factor: int = 32, min_pixels: int = 64
 
 def preprocess_image(image: torch.Tensor, patch_size: int = 16, merge_size: int = 2, temporal_patch_size: int = 2,
                      min_pixels: int = 64 * 32 * 32, max_pixels: int = 16384 * 32 * 32,
-                     mean: float = 0.5, std: float = 0.5) -> Tuple[torch.Tensor, torch.Tensor]:
-    """``image``: uint8 ``[H, W, 3]``.  Returns ``(pixel_values [N, 3*T*P*P] float32, grid_thw [1, 3])``."""
+                     mean=0.5, std=0.5) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``image``: uint8 ``[H, W, 3]``.  ``mean`` / ``std``: one number or one per channel (Qwen3-VL normalises with
+    0.5 / 0.5, Qwen2-VL and Qwen2.5-VL with the CLIP statistics, :data:`CLIP_MEAN` / :data:`CLIP_STD`).
+    Returns ``(pixel_values [N, 3*T*P*P] float32, grid_thw [1, 3])``."""
     if image.dim() != 3 or image.shape[-1] != 3:
         raise ValueError("image must be [H, W, 3]")
     H, W = int(image.shape[0]), int(image.shape[1])
@@ -43,7 +49,9 @@ def preprocess_image(image: torch.Tensor, patch_size: int = 16, merge_size: int 
     x = image.permute(2, 0, 1).unsqueeze(0).float()
     if (h, w) != (H, W):
         x = F.interpolate(x, size=(h, w), mode="bicubic", align_corners=False, antialias=True).clamp_(0, 255)
-    x = (x / 255.0 - mean) / std                                           # [1, 3, h, w]
+    mean_t = torch.as_tensor(mean, dtype=torch.float32).reshape(1, -1, 1, 1)
+    std_t = torch.as_tensor(std, dtype=torch.float32).reshape(1, -1, 1, 1)
+    x = (x / 255.0 - mean_t) / std_t                                       # [1, 3, h, w]
     x = x.repeat(temporal_patch_size, 1, 1, 1)                             # [T, 3, h, w]  (one temporal group)
     gh, gw = h // patch_size, w // patch_size
     m, P, T = merge_size, patch_size, temporal_patch_size

@@ -160,3 +160,32 @@ def test_matches_hf_qwen3_vl_moe():
     with torch.no_grad():
         want = hf(input_ids=ids, pixel_values=pixels, image_grid_thw=grid, mm_token_type_ids=(ids == IMG).int()).logits[:, -1]
     torch.testing.assert_close(got, want, atol=1e-3, rtol=1e-3)
+
+
+def test_builtin_image_preprocessing_matches_the_hf_processor():
+    """Patch layout, grid and normalisation of the built-in image path against transformers' Qwen2-VL image
+    processor: exact for a size that needs no resizing (both normalisation conventions); same grid and close
+    pixels when a resize is involved (the resampling filters differ slightly)."""
+    import numpy as np
+
+    tr = pytest.importorskip("transformers")
+    from mllm_b200.utils.image_processor import CLIP_MEAN, CLIP_STD, image_token_count, preprocess_image
+
+    rng = np.random.default_rng(0)
+    img = rng.integers(0, 256, (320, 448, 3), dtype=np.uint8)
+    for patch, mean, std in ((16, [0.5] * 3, [0.5] * 3), (14, list(CLIP_MEAN), list(CLIP_STD))):
+        side = patch * 2
+        im = img[: 10 * side, : 14 * side]
+        hf = tr.Qwen2VLImageProcessor(patch_size=patch, merge_size=2, temporal_patch_size=2, image_mean=mean, image_std=std,
+                                      min_pixels=64 * side * side, max_pixels=16384 * side * side)
+        want = hf(images=[im], return_tensors="pt")
+        pv, grid = preprocess_image(torch.from_numpy(im), patch, 2, 2, 64 * side * side, 16384 * side * side, mean, std)
+        assert grid.tolist() == want["image_grid_thw"].tolist() and image_token_count(grid) == 10 * 14
+        torch.testing.assert_close(pv, want["pixel_values"], atol=1e-5, rtol=1e-5)
+    odd = rng.integers(0, 256, (211, 333, 3), dtype=np.uint8)
+    hf = tr.Qwen2VLImageProcessor(patch_size=16, merge_size=2, temporal_patch_size=2, image_mean=[0.5] * 3, image_std=[0.5] * 3,
+                                  min_pixels=64 * 32 * 32, max_pixels=16384 * 32 * 32)
+    want = hf(images=[odd], return_tensors="pt")
+    pv, grid = preprocess_image(torch.from_numpy(odd))
+    assert grid.tolist() == want["image_grid_thw"].tolist() and pv.shape == want["pixel_values"].shape
+    assert (pv - want["pixel_values"]).abs().mean().item() < 0.05
