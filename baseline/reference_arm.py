@@ -155,5 +155,9 @@ def _run(a, metric: str, ranks: "_Ranks") -> dict:
         out["prefill_tokens_per_s"] = statistics.median(r["prefill_throughput"] for r in rows)
         out["decode_tokens_per_s"] = statistics.median(r["median_decode_throughput"] for r in rows)
         out["reference_reported_overall_throughput"] = statistics.median(r["overall_throughput"] for r in rows)
+        if all("prefill_latency" in r for r in rows):
+            out["p50_ttft_ms"] = statistics.median(r["prefill_latency"] for r in rows) * 1e3
+        if all("median_decode_latency" in r for r in rows):
+            out["p50_tpot_ms"] = statistics.median(r["median_decode_latency"] for r in rows) * 1e3
     runner.shutdown()
     return out

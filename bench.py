@@ -317,6 +317,8 @@ def run_ours(a: argparse.Namespace) -> dict:
         "prefill_tokens_per_s": replicas * bs * L / (prefill_med / 1e3),
         "decode_tokens_per_s": replicas * bs * (out_len - 1) / (decode_med / 1e3),
         "prefill_ms": prefill_med, "decode_ms_per_token": decode_med / (out_len - 1),
+        # the batch's time to first token and time per output token, median over the timed steps (max over ranks)
+        "p50_ttft_ms": prefill_med, "p50_tpot_ms": decode_med / (out_len - 1),
         "gpu_launches": launches_all, "gpu_launches_per_rank": int(launches), "clocks": clocks, "e2e": e2e,
     }
     if world > 1:
