@@ -198,3 +198,54 @@ def test_hybrid_engine_with_state_cache_reproduces_uncached_tokens():
     # two snapshot rows only: snapshots are evicted all the time, tokens must not change
     tight, _, _ = run(True, slots=2)
     assert tight == plain
+
+
+def test_hybrid_model_batched_chunked_mixed_equals_one_at_a_time():
+    """Five requests with shared prefixes submitted together to a hybrid model with small prefill chunks (so
+    prefill chunks of some requests ride in the same pass as decode steps of others) and the state-aware
+    cache on: every request gets the tokens it gets alone, without any cache."""
+    from mllm_b200.configs import ServerConfig
+    from mllm_b200.engine.io_struct import TokenizedGenerateReqInput
+    from mllm_b200.orchestrator.scheduler_process import build_scheduler
+
+    base = [5, 9, 2, 7, 7, 3, 1, 8, 4, 6, 2, 2, 9, 9, 1]
+    prompts = [base, base + [40, 41, 42], base[:9] + [60, 61], [70, 71, 72, 73], base + [40, 41, 42, 43, 44, 45, 46]]
+
+    def cfg(**kw):
+        return ServerConfig(model_path="preset:qwen3.5-tiny", dtype="float32", max_total_tokens=2048, context_length=256,
+                            log_level="warning", **kw)
+
+    def drain(sched):
+        done = {}
+        for _ in range(800):
+            out = sched.step()
+            if out is not None:
+                for i, rid in enumerate(out.rids):
+                    if out.finished_reasons[i] is not None:
+                        done[rid] = out.output_ids[i]
+            if not sched.has_work():
+                break
+        return done
+
+    def req(rid, ids):
+        return TokenizedGenerateReqInput(rid=rid, input_ids=list(ids), sampling_params=dict(max_new_tokens=7, temperature=0.0))
+
+    alone = {}
+    for i, p in enumerate(prompts):
+        s = build_scheduler(cfg(max_running_requests=1, disable_radix_cache=True), device="cpu")
+        s.add_request(req(f"r{i}", p))
+        alone.update(drain(s))
+    sched = build_scheduler(cfg(max_running_requests=4, chunked_prefill_size=8, enable_mamba_cache=True, mamba_cache_slots=8),
+                            device="cpu")
+    for i, p in enumerate(prompts[:3]):
+        sched.add_request(req(f"r{i}", p))
+    for _ in range(3):
+        sched.step()
+    for i, p in enumerate(prompts[3:], start=3):
+        sched.add_request(req(f"r{i}", p))
+    together = drain(sched)
+    assert together == alone
+    assert sched.stats.num_mixed_batches > 0
+    sched._sweep_finished()
+    mrp = sched.mrp
+    assert mrp.prefix_cache.protected_size() == 0 and mrp.prefix_cache.mamba_protected_size() == 0
