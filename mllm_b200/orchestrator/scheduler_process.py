@@ -411,7 +411,17 @@ def run_scheduler_process(server_config: ServerConfig, recv_addr: Optional[str],
         poller.register(recv, zmq.POLLIN)
     if pipe_writer is not None:
         pipe_writer.send({"status": "ready", "max_total_num_tokens": sched.mrp.runner.max_total_num_tokens})
-    scheduler_event_loop(sched, recv, send, poller, rank, world_size, ctrl, tensor_queue if rank == 0 else None)
+    try:
+        scheduler_event_loop(sched, recv, send, poller, rank, world_size, ctrl, tensor_queue if rank == 0 else None)
+    finally:
+        if world_size > 1:   # leave the process groups in an orderly way: their worker threads must not outlive main
+            import torch.distributed as dist
+
+            try:
+                if dist.is_initialized():
+                    dist.destroy_process_group()
+            except Exception:
+                pass
 
 
 def _take_from_shared_queue(tensor_queue, notice):
