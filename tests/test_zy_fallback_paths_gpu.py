@@ -79,3 +79,28 @@ def test_fp8_kv_cache_on_gpu_stays_close_to_the_cpu_model():
     got, want = _run(gpu, ids), _run(cpu, ids)
     ops.check_status()
     _close(got, want, floor=0.97)
+
+
+def test_bounded_flag_wait_runs_out_into_a_status_and_the_context_stays_usable():
+    """Failure detection without a fault: a kernel waits (with its built-in bound) on a flag that nothing
+    sets; it gives up, records the status word, and returns.  The host reads the status as an error, the
+    word is cleared by the read, and the device keeps working."""
+    import time
+
+    from mllm_b200.ops import reference as ref
+
+    ops.check_status()
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    t0 = time.perf_counter()
+    assert ops.ext().tp_wait_flags(flags, 1, 1) == 0          # launches fine; nobody will ever write epoch 1
+    with pytest.raises(RuntimeError, match="peer flag wait timed out"):
+        ops.check_status()
+    assert time.perf_counter() - t0 < 30.0                    # bounded: seconds, not forever
+    ops.check_status()                                        # cleared by the read above
+    flags.fill_(3)
+    assert ops.ext().tp_wait_flags(flags, 8, 3) == 0          # a wait that is satisfied leaves no status
+    ops.check_status()
+    x = torch.randn(16, 256, device="cuda").bfloat16()
+    w = torch.ones(256, device="cuda").bfloat16()
+    got = ops.rmsnorm(x, w, 1e-6).float()
+    assert (got - ref.rmsnorm(x.float(), w.float(), 1e-6)).abs().max().item() < 0.05
