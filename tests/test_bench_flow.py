@@ -18,6 +18,14 @@ def _last_json(stdout: str) -> dict:
     return json.loads(lines[-1])
 
 
+def _free_port() -> str:
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return str(s.getsockname()[1])
+
+
 def _env() -> dict:
     env = dict(os.environ)
     for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
@@ -40,7 +48,7 @@ def test_single_rank_line_has_the_contract_keys():
 
 def test_two_data_parallel_ranks_count_both_batches():
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", "29547", str(ROOT / "bench.py"), "--gpus", "2", *TINY]
+           "127.0.0.1", "--master-port", _free_port(), str(ROOT / "bench.py"), "--gpus", "2", *TINY]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=_env(), cwd=ROOT)
     assert p.returncode == 0, p.stderr[-2000:]
     lines = [ln for ln in p.stdout.splitlines() if ln.startswith("{")]
@@ -65,7 +73,7 @@ def test_watchdog_ends_a_run_that_never_finishes():
 
 def test_two_tensor_parallel_ranks_share_one_batch():
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", "29548", str(ROOT / "bench.py"), "--gpus", "2", "--parallelism", "tp", *TINY]
+           "127.0.0.1", "--master-port", _free_port(), str(ROOT / "bench.py"), "--gpus", "2", "--parallelism", "tp", *TINY]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=_env(), cwd=ROOT)
     assert p.returncode == 0, p.stderr[-2000:]
     out = _last_json(p.stdout)

@@ -10,7 +10,16 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
+def _free_port() -> int:
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
 def _launch(world, out, device, dtype, port, extra_env=None):
+    port = _free_port()      # the number passed by the test only documents the order of the runs
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE=str(world),
                NCCL_NVLS_ENABLE="0", **(extra_env or {}))
     procs = []
