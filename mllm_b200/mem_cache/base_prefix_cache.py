@@ -72,6 +72,7 @@ class InsertResult:
     prefix_len: int = 0  # tokens that were already in the tree
     last_node: Any = None
     mamba_exist: bool = False
+    adopted: int = 0  # tokens whose slots the tree took over in place of older ones (revived tombstones)
 
 
 @dataclass
