@@ -27,7 +27,8 @@ class RadixAttention(nn.Module):
         self.sliding_window = int(sliding_window) if sliding_window else None
         self.logit_cap = float(logit_cap or 0.0)
         self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
-        self.scaling, self.layer_id = scaling, layer_id
+        # yarn / longrope checkpoints scale cos and sin by a constant: q.k grows by its square
+        self.scaling, self.layer_id = scaling * ops.rope_attention_factor(rope_scaling) ** 2, layer_id
         self.rope_theta, self.rms_eps = rope_theta, rms_eps
         self.mrope_sections, self.mrope_interleaved = mrope_sections, mrope_interleaved
         self._inv_freq: Optional[torch.Tensor] = None

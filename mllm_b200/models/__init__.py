@@ -23,6 +23,8 @@ _REGISTRY: Dict[str, Tuple[str, str]] = {
     "Qwen2MoeForCausalLM": ("mllm_b200.models.moe_families", "Qwen2MoeForCausalLM"),
     "MixtralForCausalLM": ("mllm_b200.models.moe_families", "MixtralForCausalLM"),
     "SmolLM3ForCausalLM": ("mllm_b200.models.llama", "SmolLM3ForCausalLM"),
+    "MiniCPMForCausalLM": ("mllm_b200.models.minicpm", "MiniCPMForCausalLM"),
+    "MiniCPM4ForCausalLM": ("mllm_b200.models.minicpm", "MiniCPMForCausalLM"),
 }
 
 

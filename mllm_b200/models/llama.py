@@ -5,8 +5,8 @@ attention and SwiGLU kernels, same tensor-parallel sharding and quantised linear
 
 * ``LlamaForCausalLM`` (also Mistral-style configs; a ``sliding_window`` is honoured, on fallback attention
   paths): no attention bias unless
-  ``attention_bias``; ``rope_scaling`` of type ``llama3`` / ``linear`` is applied to the rotary
-  frequencies.
+  ``attention_bias``; ``rope_scaling`` of type ``llama3`` / ``linear`` / ``yarn`` / ``longrope`` is applied to
+  the rotary frequencies (and, for the last two, to the softmax scale).
 * ``Qwen2ForCausalLM`` (Qwen2 / Qwen2.5): bias on the q, k and v projections.
 * ``SmolLM3ForCausalLM``: Llama with ``no_rope_layers`` — every n-th layer attends without positional
   rotation (the prologue kernel gets all-zero frequencies there).

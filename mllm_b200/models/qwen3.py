@@ -134,7 +134,16 @@ def _rope_scaling(config, layer_id: int = 0) -> Optional[dict]:
         return None
     rs = rs if isinstance(rs, dict) else vars(rs)
     kind = rs.get("rope_type", rs.get("type", "default"))
-    return dict(rs) if kind in ("linear", "llama3", "yarn", "dynamic", "longrope") else None
+    if kind in (None, "default", "mrope"):
+        return None
+    if kind not in ("linear", "llama3", "yarn", "dynamic", "longrope"):
+        raise NotImplementedError(f"rope scaling type {kind!r}")
+    rs = dict(rs)
+    # yarn / longrope also look at how far the context was stretched
+    rs.setdefault("max_position_embeddings", getattr(config, "max_position_embeddings", None))
+    if getattr(config, "original_max_position_embeddings", None):
+        rs.setdefault("original_max_position_embeddings", config.original_max_position_embeddings)
+    return rs
 
 
 def _sliding_window(config, layer_id: int) -> Optional[int]:

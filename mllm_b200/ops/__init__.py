@@ -328,28 +328,95 @@ def w4a16_gemm(x, qweight, scales, zeros, group: int, bias=None) -> torch.Tensor
 # --------------------------------------------------------------------------
 # rope / kv
 # --------------------------------------------------------------------------
+def _rope_kind(scaling: Optional[dict]) -> str:
+    return (scaling or {}).get("rope_type", (scaling or {}).get("type", "default")) or "default"
+
+
+def _rope_stretch(scaling: dict) -> float:
+    """How far the context was stretched: ``factor``, or max positions / original max positions."""
+    f = scaling.get("factor")
+    if f is None:
+        f = float(scaling.get("max_position_embeddings", 0) or 0) / float(scaling["original_max_position_embeddings"])
+    return float(f)
+
+
+def rope_attention_factor(scaling: Optional[dict]) -> float:
+    """Magnitude that ``yarn`` / ``longrope`` checkpoints put on cos and sin (so on rotated q *and* k).  The
+    attention layer folds its square into the softmax scale instead of touching the rotation."""
+    import math
+
+    kind = _rope_kind(scaling)
+    if kind not in ("yarn", "longrope"):
+        return 1.0
+    if scaling.get("attention_factor") is not None:
+        return float(scaling["attention_factor"])
+    factor = _rope_stretch(scaling)
+    if kind == "longrope":
+        return 1.0 if factor <= 1.0 else math.sqrt(1.0 + math.log(factor) / math.log(float(scaling["original_max_position_embeddings"])))
+
+    def mscale(scale: float, m: float = 1.0) -> float:
+        return 1.0 if scale <= 1.0 else 0.1 * m * math.log(scale) + 1.0
+
+    m, m_all = scaling.get("mscale"), scaling.get("mscale_all_dim")
+    return mscale(factor, m) / mscale(factor, m_all) if (m and m_all) else mscale(factor)
+
+
 def rope_inv_freq(head_dim: int, theta: float, device, scaling: Optional[dict] = None) -> torch.Tensor:
-    """Rotary frequencies ``theta^(-2i/D)``, optionally rescaled the way the checkpoint's ``rope_scaling``
-    asks: ``linear`` (all frequencies divided by ``factor``) or ``llama3`` (long wavelengths divided by
-    ``factor``, short ones kept, a smooth blend between ``original_max_position_embeddings /
-    low_freq_factor`` and ``/ high_freq_factor``)."""
+    """Rotary frequencies ``theta^(-2i/D)``, optionally rescaled the way the checkpoint's ``rope_scaling`` asks:
+
+    * ``linear``: all frequencies divided by ``factor``;
+    * ``llama3``: long wavelengths divided by ``factor``, short ones kept, a smooth blend between
+      ``original_max_position_embeddings / low_freq_factor`` and ``/ high_freq_factor``;
+    * ``yarn``: frequencies that turn fewer than ``beta_slow`` times over the original context are divided by
+      ``factor``, those turning more than ``beta_fast`` times are kept, a linear ramp in between;
+    * ``longrope``: every frequency divided by its own learned factor — ``long_factor`` when the served context
+      (``max_position_embeddings``) exceeds the original one, else ``short_factor`` (chosen once: a cache written
+      with one set must not be read with the other);
+    * ``dynamic`` (NTK): only changes the base beyond the trained context, which a server that caps requests at
+      ``max_position_embeddings`` never reaches: plain frequencies.
+
+    ``yarn`` and ``longrope`` also scale the attention scores: see :func:`rope_attention_factor`."""
+    import math
+
     inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
-    kind = (scaling or {}).get("rope_type", (scaling or {}).get("type", "default"))
+    kind = _rope_kind(scaling)
     if kind == "none":          # a layer without positional rotation: angle 0 everywhere
         return torch.zeros_like(inv)
-    if not scaling or kind in (None, "default", "mrope"):
+    if not scaling or kind in (None, "default", "mrope", "dynamic"):
         return inv
     if kind == "linear":
         return inv / float(scaling["factor"])
     if kind == "llama3":
-        import math
-
         factor, lo, hi = float(scaling["factor"]), float(scaling["low_freq_factor"]), float(scaling["high_freq_factor"])
         old_len = float(scaling["original_max_position_embeddings"])
         wavelen = 2 * math.pi / inv
         smooth = ((old_len / wavelen - lo) / (hi - lo)).clamp(0.0, 1.0)
         blended = (1 - smooth) * inv / factor + smooth * inv
         return torch.where(wavelen > old_len / lo, inv / factor, torch.where(wavelen < old_len / hi, inv, blended))
+    if kind == "yarn":
+        factor = _rope_stretch(scaling)
+        old_len = float(scaling.get("original_max_position_embeddings") or scaling["max_position_embeddings"])
+        fast, slow = float(scaling.get("beta_fast") or 32), float(scaling.get("beta_slow") or 1)
+
+        def turn_dim(turns: float) -> float:      # index of the frequency that makes `turns` rotations over old_len
+            return head_dim * math.log(old_len / (turns * 2 * math.pi)) / (2 * math.log(theta))
+
+        low, high = turn_dim(fast), turn_dim(slow)
+        if scaling.get("truncate", True):
+            low, high = math.floor(low), math.ceil(high)
+        low, high = max(low, 0), min(high, head_dim - 1)
+        if low == high:
+            high += 0.001
+        ramp = ((torch.arange(head_dim // 2, device=device, dtype=torch.float32) - low) / (high - low)).clamp(0.0, 1.0)
+        return (inv / factor) * ramp + inv * (1.0 - ramp)
+    if kind == "longrope":
+        old_len = float(scaling["original_max_position_embeddings"])
+        served = float(scaling.get("max_position_embeddings", 0) or 0)
+        ext = scaling["long_factor"] if served > old_len else scaling["short_factor"]
+        ext = torch.tensor(ext, dtype=torch.float32, device=device)
+        if ext.numel() != inv.numel():
+            raise ValueError(f"longrope: {ext.numel()} factors for {inv.numel()} frequencies")
+        return inv / ext
     raise NotImplementedError(f"rope scaling type {kind!r}")
 
 

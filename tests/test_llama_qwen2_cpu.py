@@ -50,7 +50,13 @@ def _run_and_compare(hf, ns, vocab):
 @pytest.mark.parametrize("scaling", [None,
                                      dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
                                           original_max_position_embeddings=16),
-                                     dict(rope_type="linear", factor=2.0)])
+                                     dict(rope_type="linear", factor=2.0),
+                                     dict(rope_type="yarn", factor=4.0, original_max_position_embeddings=16),
+                                     dict(rope_type="yarn", factor=8.0, original_max_position_embeddings=32,
+                                          beta_fast=16, beta_slow=2, mscale=1.0, mscale_all_dim=0.5),
+                                     dict(rope_type="longrope", original_max_position_embeddings=16,
+                                          short_factor=[1.0, 1.0, 1.1, 1.2, 1.3, 1.5, 1.8, 2.0],
+                                          long_factor=[1.0, 1.2, 1.7, 2.5, 4.0, 7.0, 11.0, 16.0])])
 def test_llama_matches_hf(scaling):
     tr = pytest.importorskip("transformers")
     cfgd = dict(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
@@ -106,10 +112,9 @@ def test_unsupported_variants_are_refused():
                                 num_key_value_heads=2, rms_norm_eps=1e-6, tie_word_embeddings=True, mlp_bias=True)
     with pytest.raises(NotImplementedError):
         get_model_class("LlamaForCausalLM")(cfg)
-    cfg2 = types.SimpleNamespace(**{**vars(cfg), "mlp_bias": False, "rope_scaling": dict(rope_type="yarn", factor=4.0)})
+    cfg2 = types.SimpleNamespace(**{**vars(cfg), "mlp_bias": False, "rope_scaling": dict(rope_type="proportional", factor=4.0)})
     with pytest.raises(NotImplementedError):
-        m = get_model_class("LlamaForCausalLM")(cfg2)
-        m.model.layers[0].self_attn.attn._tables(torch.device("cpu"))
+        get_model_class("LlamaForCausalLM")(cfg2)
 
 
 def test_mistral_sliding_window_matches_hf():
