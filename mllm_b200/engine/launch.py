@@ -97,7 +97,10 @@ class Engine:
         from ..utils.image_processor import CLIP_MEAN, CLIP_STD
 
         clip = str(getattr(cfg, "model_type", "")) in ("qwen2_vl", "qwen2_5_vl")   # these normalise with CLIP statistics
-        return dict(image_mean=list(CLIP_MEAN) if clip else 0.5, image_std=list(CLIP_STD) if clip else 0.5,
+        # videos are served for the families whose prompt has one timestamped block per temporal patch
+        video = None if clip or getattr(cfg, "video_token_id", None) is None else int(cfg.video_token_id)
+        return dict(video_token_id=video,
+                    image_mean=list(CLIP_MEAN) if clip else 0.5, image_std=list(CLIP_STD) if clip else 0.5,
                     image_token_id=int(cfg.image_token_id), vision_start_token_id=int(cfg.vision_start_token_id),
                     vision_end_token_id=int(getattr(cfg, "vision_end_token_id", cfg.vision_start_token_id)),
                     patch_size=int(vc.patch_size), merge_size=int(getattr(vc, "spatial_merge_size", 2)),
@@ -330,13 +333,15 @@ class Engine:
 
     def generate(self, prompt: Optional[Union[str, List[str]]] = None, sampling_params=None, input_ids=None,
                  image_data=None, stream: bool = False, rid=None, timeout: Optional[float] = None,
-                 return_logprob: bool = False, top_logprobs_num: int = 0):
+                 return_logprob: bool = False, top_logprobs_num: int = 0, video_data=None):
         """Blocking generation. One prompt -> dict, a list -> list of dicts; ``stream=True`` (single
         prompt) returns an iterator of incremental dicts with a ``delta`` field.  With ``return_logprob``
         ``meta_info["output_token_logprobs"]`` holds the log-probability (and text) of every generated token
-        and, per token, the ``top_logprobs_num`` most likely alternatives."""
+        and, per token, the ``top_logprobs_num`` most likely alternatives.  ``video_data``: frames of a clip (array
+        ``[F, H, W, 3]``, list of images, ``.npy`` file, or ``{"frames": ..., "fps": f}``) for the model families with
+        video tokens."""
         obj = GenerateReqInput(rid=rid, text=prompt, input_ids=input_ids, sampling_params=sampling_params,
-                               image_data=image_data, stream=stream, return_logprob=return_logprob or None,
+                               image_data=image_data, video_data=video_data, stream=stream, return_logprob=return_logprob or None,
                                top_logprobs_num=top_logprobs_num or None)
         subs = self._submit(obj)
         if stream:
@@ -376,7 +381,7 @@ class Engine:
         return tok
 
     def chat(self, messages: List[Dict[str, Any]], sampling_params=None, stream: bool = False, tools=None,
-             image_data=None, timeout: Optional[float] = None, **template_kwargs):
+             image_data=None, timeout: Optional[float] = None, video_data=None, **template_kwargs):
         """Renders ``messages`` (``[{"role": ..., "content": ...}, ...]``) with the tokenizer's chat template
         (ChatML when it has none) and generates the assistant turn; same return types as ``generate``."""
         from ..utils.tokenizer import render_chatml
@@ -391,7 +396,8 @@ class Engine:
                 logger.warning("chat template failed (%s); using ChatML", exc)
         if prompt is None:
             prompt = render_chatml(messages, add_generation_prompt=True)
-        return self.generate(prompt, sampling_params, image_data=image_data, stream=stream, timeout=timeout)
+        return self.generate(prompt, sampling_params, image_data=image_data, stream=stream, timeout=timeout,
+                             video_data=video_data)
 
     @staticmethod
     def perf_summary(result: Dict[str, Any]) -> Dict[str, float]:

@@ -25,7 +25,10 @@ def host_ext():
 
 
 def _extra(extra_key: Optional[str]) -> int:
-    return 0 if extra_key is None else hash_bytes(str(extra_key).encode())
+    if extra_key is None:
+        return 0
+    h = hash_bytes(str(extra_key).encode()) & 0xFFFFFFFFFFFFFFFF
+    return h - (1 << 64) if h >= (1 << 63) else h      # the tree takes a signed 64-bit key
 
 
 class NativeTokenToKVPoolAllocator:

@@ -243,11 +243,14 @@ class VisionLanguageMixin:
     ``spatial_merge_size``, ``hidden_size``, ``num_deepstack`` and ``model.embed_tokens``."""
 
     uses_mrope = True
+    # videos: every temporal patch arrives as one more "image" of grid [1, h, w] whose rows carry this token
+    video_token_id: Optional[int] = None
 
     def _init_vision(self, config, dtype) -> None:
         self.full_config = config
         self.visual = Qwen3VLVisionModel(config.vision_config, dtype)
         self.image_token_id = config.image_token_id
+        self.video_token_id = getattr(config, "video_token_id", None)
         self.vision_start_token_id = config.vision_start_token_id
         self.spatial_merge_size = getattr(config.vision_config, "spatial_merge_size", 2)
         self.num_deepstack = len(self.visual.deepstack_visual_indexes)
@@ -273,6 +276,8 @@ class VisionLanguageMixin:
             torch.cuda.synchronize()
         fb.vit_prefill_ms = (time.perf_counter() - t0) * 1e3
         mask = input_ids == self.image_token_id
+        if self.video_token_id is not None:
+            mask = mask | (input_ids == self.video_token_id)
         n_tok = int(mask.sum())
         fb.vit_prefill_tokens = n_tok
         if n_tok != feats.shape[0]:

@@ -19,6 +19,20 @@ from ..utils.tokenizer import get_tokenizer
 logger = logging.getLogger(__name__)
 
 
+def _is_frame_list(v) -> bool:
+    """A list whose entries are single frames (one video given as its frames), not a list of videos."""
+    import numpy as np
+
+    if not isinstance(v, (list, tuple)) or not v:
+        return False
+    first = v[0]
+    if isinstance(first, (dict, list, tuple)):
+        return False
+    if isinstance(first, str):
+        return not first.endswith(".npy")
+    return not (hasattr(first, "ndim") and np.ndim(first) == 4)
+
+
 class TokenizerWorker:
     def __init__(self, tokenizer_path, context_length: Optional[int] = None, vocab_size: int = 1024,
                  tokenizer_mode: str = "auto", trust_remote_code: bool = False, mm_config: Optional[Dict[str, Any]] = None) -> None:
@@ -63,46 +77,193 @@ class TokenizerWorker:
 
         return Image.fromarray(np.asarray(item).astype("uint8")).convert("RGB")
 
-    def _builtin_image_inputs(self, images, text, ids):
-        """Built-in preprocessing: every image becomes ``<vision_start> <image_pad> * n <vision_end>`` in
-        front of the text tokens; pixels are patchified by :mod:`mllm_b200.utils.image_processor`."""
+    @classmethod
+    def load_video(cls, item: Any):
+        """-> (uint8 frames ``[F, H, W, 3]`` as a tensor, frames per second of that frame list or None).
+
+        Accepted: an array / tensor ``[F, H, W, 3]``; a list of frames (anything :meth:`load_image` takes, or
+        arrays); a ``.npy`` file holding such an array; a dict ``{"frames": <any of these>, "fps": f}``.  Container
+        formats (mp4, ...) need a decoder this package does not ship: decode to frames first."""
         import numpy as np
         import torch
 
-        from ..utils.image_processor import image_token_count, preprocess_image
+        fps = None
+        if isinstance(item, dict):
+            fps = item.get("fps")
+            item = item.get("frames")
+        if isinstance(item, str):
+            if not item.endswith(".npy"):
+                raise ValueError("video_data: pass frames (array, list of images or .npy file); container formats "
+                                 "such as mp4 are not decoded here")
+            item = np.load(item)
+        if isinstance(item, (list, tuple)):
+            frames = [np.asarray(f) if isinstance(f, (np.ndarray, torch.Tensor)) else np.asarray(cls.load_image(f)) for f in item]
+            if not frames or any(f.shape != frames[0].shape for f in frames):
+                raise ValueError("video_data: frames must be non-empty and share one size")
+            item = np.stack(frames)
+        arr = torch.as_tensor(np.asarray(item))
+        if arr.dim() != 4 or arr.shape[-1] != 3:
+            raise ValueError(f"video_data: expected frames [F, H, W, 3], got {tuple(arr.shape)}")
+        return arr.to(torch.uint8), (float(fps) if fps else None)
+
+    def _builtin_mm_inputs(self, images, videos, text, ids):
+        """Built-in preprocessing.  Every image becomes ``<vision_start> <image_pad> * n <vision_end>``; every
+        temporal patch of a video becomes ``"<t seconds>" <vision_start> <video_pad> * n <vision_end>`` (the
+        layout of the Qwen3-VL processor); the blocks go in front of the text tokens.  Pixels are patchified by
+        :mod:`mllm_b200.utils.image_processor`; a temporal patch is stored like an image of grid ``[1, h, w]``, so
+        the model sees one list of grids in order of appearance."""
+        import numpy as np
+        import torch
+
+        from ..utils.image_processor import (image_token_count, preprocess_image, preprocess_video,
+                                             sample_frame_indices, video_timestamps)
 
         mc = self.mm_config
         text_ids = list(ids) if ids is not None else self.tokenizer.encode(text or "")
-        pix, grids, block, h = [], [], [], hashlib.sha256()
-        for item in (images if isinstance(images, list) else [images]):
+        pix, grids, h = [], [], hashlib.sha256()
+        blocks = []                                   # (kind token, token ids of the block, pixel rows, grid rows)
+        norm = dict(mean=mc.get("image_mean", 0.5), std=mc.get("image_std", 0.5))
+        for item in ([] if images is None else images if isinstance(images, list) else [images]):
             arr = item if isinstance(item, (np.ndarray, torch.Tensor)) else np.asarray(self.load_image(item))
             img = torch.as_tensor(np.asarray(arr)).to(torch.uint8)
             h.update(img.numpy().tobytes())
-            pv, g = preprocess_image(img, mc["patch_size"], mc["merge_size"], mc["temporal_patch_size"],
-                                     mean=mc.get("image_mean", 0.5), std=mc.get("image_std", 0.5))
-            pix.append(pv)
-            grids.append(g)
-            block += [mc["vision_start_token_id"]] + [mc["image_token_id"]] * image_token_count(g, mc["merge_size"]) + \
-                [mc["vision_end_token_id"]]
+            pv, g = preprocess_image(img, mc["patch_size"], mc["merge_size"], mc["temporal_patch_size"], **norm)
+            blocks.append((mc["image_token_id"], [mc["vision_start_token_id"]] + [mc["image_token_id"]] *
+                           image_token_count(g, mc["merge_size"]) + [mc["vision_end_token_id"]], pv, g))
+        if videos is not None and mc.get("video_token_id") is None:
+            raise ValueError("this model has no video token: video_data is not supported")
+        for item in ([] if videos is None else videos if isinstance(videos, list) and not _is_frame_list(videos) else [videos]):
+            frames, fps = self.load_video(item)
+            src_fps = fps or 24.0
+            keep = sample_frame_indices(frames.shape[0], src_fps, float(mc.get("video_fps", 2.0)),
+                                        int(mc.get("video_min_frames", 4)), int(mc.get("video_max_frames", 768)))
+            frames = frames[keep]
+            h.update(frames.numpy().tobytes())
+            pv, g = preprocess_video(frames, mc["patch_size"], mc["merge_size"], mc["temporal_patch_size"], **norm)
+            T, gh, gw = (int(v) for v in g[0])
+            per = (gh // mc["merge_size"]) * (gw // mc["merge_size"])
+            block = []
+            for t in video_timestamps(keep, src_fps, mc["temporal_patch_size"]):
+                block += self.tokenizer.encode(f"<{t:.1f} seconds>") + [mc["vision_start_token_id"]] + \
+                    [mc["video_token_id"]] * per + [mc["vision_end_token_id"]]
+            blocks.append((mc["video_token_id"], block, pv, torch.tensor([[1, gh, gw]] * T, dtype=torch.int64)))
+        # a block replaces its placeholder  <vision_start> <pad> <vision_end>  in the text (chat templates write
+        # one per image / video part), in order of appearance; blocks without one go in front of the text
+        vs, ve = mc["vision_start_token_id"], mc["vision_end_token_id"]
+        out_ids, placed, i = [], [False] * len(blocks), 0
+        body = []                                     # (ids chunk, block index or None) in text order
+        while i < len(text_ids):
+            if text_ids[i] == vs and i + 2 < len(text_ids) and text_ids[i + 2] == ve:
+                j = next((b for b, blk in enumerate(blocks) if not placed[b] and blk[0] == text_ids[i + 1]), None)
+                if j is not None:
+                    placed[j] = True
+                    body.append((blocks[j][1], j))
+                    i += 3
+                    continue
+            body.append(([text_ids[i]], None))
+            i += 1
+        order = [b for b in range(len(blocks)) if not placed[b]] + [j for _, j in body if j is not None]
+        for b in range(len(blocks)):
+            if not placed[b]:
+                out_ids += blocks[b][1]
+        for chunk, _ in body:
+            out_ids += chunk
+        for b in order:
+            pix.append(blocks[b][2])
+            grids.append(blocks[b][3])
         mm = {"pixel_values": torch.cat(pix), "image_grid_thw": torch.cat(grids), "image_hash": h.hexdigest()[:16]}
-        return block + text_ids, mm
+        return out_ids, mm
+
+    @staticmethod
+    def merge_vision_inputs(ids, image_pixels, image_grids, video_pixels, video_grids, image_token_id: int,
+                            video_token_id: int, vision_start_token_id: int, merge_size: int):
+        """One ``(pixel_values, grid_thw)`` list in order of appearance from a processor's separate image and
+        video outputs.  Walks the vision-start tokens of ``ids``: an image block takes the next image grid; a
+        video block takes the next temporal patch of the current video as grid ``[1, h, w]`` (a video of grid
+        ``[T, h, w]`` whose prompt has one block per temporal patch), or the whole ``[T, h, w]`` grid when the
+        block holds all of its tokens."""
+        import torch
+
+        ig = [] if image_grids is None else image_grids.tolist()
+        vg = [] if video_grids is None else video_grids.tolist()
+        pix, grids = [], []
+        i_img = i_vid = t_in_vid = 0
+        img_row = vid_row = 0
+        n = len(ids)
+        for k, tok in enumerate(ids):
+            if tok != vision_start_token_id or k + 1 >= n:
+                continue
+            if ids[k + 1] == image_token_id and i_img < len(ig):
+                t, hh, ww = ig[i_img]
+                rows = t * hh * ww
+                pix.append(image_pixels[img_row:img_row + rows])
+                grids.append([t, hh, ww])
+                img_row += rows
+                i_img += 1
+            elif ids[k + 1] == video_token_id and i_vid < len(vg):
+                t, hh, ww = vg[i_vid]
+                per = (hh // merge_size) * (ww // merge_size)
+                run = 0
+                while k + 1 + run < n and ids[k + 1 + run] == video_token_id:
+                    run += 1
+                if run >= t * per and t_in_vid == 0:          # the whole video in one block
+                    take = t
+                else:
+                    take = 1
+                rows = take * hh * ww
+                pix.append(video_pixels[vid_row:vid_row + rows])
+                grids.append([take, hh, ww])
+                vid_row += rows
+                t_in_vid += take
+                if t_in_vid >= t:
+                    i_vid, t_in_vid = i_vid + 1, 0
+        if not pix:
+            return None, None
+        return torch.cat(pix), torch.tensor(grids, dtype=torch.int64)
+
+    def _processor_mm_inputs(self, images, videos, text):
+        """Through the checkpoint's own HF processor; its separate image / video outputs are merged into one list
+        in order of appearance (:meth:`merge_vision_inputs`)."""
+        h = hashlib.sha256()
+        kw = {}
+        if images is not None:
+            kw["images"] = [self.load_image(i) for i in (images if isinstance(images, list) else [images])]
+            for im in kw["images"]:
+                h.update(im.tobytes())
+        if videos is not None:
+            vids = videos if isinstance(videos, list) and not _is_frame_list(videos) else [videos]
+            loaded = [self.load_video(v) for v in vids]
+            kw["videos"] = [f.numpy() for f, _ in loaded]
+            for f, _ in loaded:
+                h.update(f.numpy().tobytes())
+            fps = [fp for _, fp in loaded]
+            if all(fp is not None for fp in fps):
+                kw["video_metadata"] = [dict(fps=fp, total_num_frames=int(f.shape[0]), frames_indices=list(range(int(f.shape[0]))))
+                                        for (f, _), fp in zip(loaded, fps)]
+                kw["do_sample_frames"] = False
+        out = self.processor(text=text or "", return_tensors="pt", **kw)
+        ids = out["input_ids"][0].tolist()
+        pv, grid = out.get("pixel_values"), out.get("image_grid_thw")
+        if out.get("pixel_values_videos") is not None:
+            mc = self.mm_config or {}
+            tok = self.processor
+            pv, grid = self.merge_vision_inputs(
+                ids, pv, grid, out["pixel_values_videos"], out["video_grid_thw"],
+                int(mc.get("image_token_id", getattr(tok, "image_token_id", -1))),
+                int(mc.get("video_token_id", getattr(tok, "video_token_id", -1))),
+                int(mc.get("vision_start_token_id", getattr(tok, "vision_start_token_id", -1))),
+                int(mc.get("merge_size", 2)))
+        return ids, {"pixel_values": pv, "image_grid_thw": grid, "image_hash": h.hexdigest()[:16]}
 
     def tokenize(self, req: Dict[str, Any]) -> TokenizedGenerateReqInput:
         text = req.get("text")
         ids = req.get("input_ids")
         mm_inputs = None
-        images = req.get("image_data")
-        if images is not None and self.processor is not None:
-            imgs = [self.load_image(i) for i in (images if isinstance(images, list) else [images])]
-            out = self.processor(images=imgs, text=text or "", return_tensors="pt")
-            ids = out["input_ids"][0].tolist()
-            h = hashlib.sha256()
-            for im in imgs:
-                h.update(im.tobytes())
-            mm_inputs = {"pixel_values": out.get("pixel_values"), "image_grid_thw": out.get("image_grid_thw"),
-                         "image_hash": h.hexdigest()[:16]}
-        elif images is not None and self.mm_config is not None:
-            ids, mm_inputs = self._builtin_image_inputs(images, text, ids)
+        images, videos = req.get("image_data"), req.get("video_data")
+        if (images is not None or videos is not None) and self.processor is not None:
+            ids, mm_inputs = self._processor_mm_inputs(images, videos, text)
+        elif (images is not None or videos is not None) and self.mm_config is not None:
+            ids, mm_inputs = self._builtin_mm_inputs(images, videos, text, ids)
         elif ids is None:
             ids = self.tokenizer.encode(text or "")
         ids = list(ids)

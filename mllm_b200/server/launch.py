@@ -154,6 +154,12 @@ def _extract_images(messages: List[ChatMessage]) -> List[Any]:
     return images
 
 
+def _extract_videos(messages: List[ChatMessage]) -> List[Any]:
+    """``{"type": "video", "video": <frames | .npy file | {"frames": ..., "fps": f}>}`` parts, in order."""
+    return [part.get("video") for m in messages if isinstance(m.content, list) for part in m.content
+            if part.get("type") == "video"]
+
+
 def messages_to_prompt(tokenizer, messages: List[ChatMessage], tools=None, template_kwargs=None) -> str:
     """Chat template of the tokenizer when it has one, else ChatML.  Image parts become the
     Qwen-VL placeholder ``<|vision_start|><|image_pad|><|vision_end|>``."""
@@ -167,6 +173,8 @@ def messages_to_prompt(tokenizer, messages: List[ChatMessage], tools=None, templ
                     text += part.get("text", "")
                 elif part.get("type") in ("image_url", "image"):
                     text += "<|vision_start|><|image_pad|><|vision_end|>"
+                elif part.get("type") == "video":
+                    text += "<|vision_start|><|video_pad|><|vision_end|>"
             d["content"] = text
         plain.append(d)
     if getattr(tokenizer, "chat_template", None):
@@ -368,8 +376,8 @@ def create_app(engine: Engine, cfg: Optional[GlobalConfig] = None) -> FastAPI:
     @app.api_route("/generate", methods=["POST", "PUT"])
     async def generate(body: GenerateRequest, request: Request):
         obj = GenerateReqInput(rid=body.rid, text=body.text, input_ids=body.input_ids, sampling_params=body.sampling_params,
-                               image_data=body.image_data, stream=body.stream, return_logprob=body.return_logprob or None,
-                               top_logprobs_num=body.top_logprobs_num or None)
+                               image_data=body.image_data, video_data=body.video_data, stream=body.stream,
+                               return_logprob=body.return_logprob or None, top_logprobs_num=body.top_logprobs_num or None)
         if body.stream:
             async def sse():
                 try:
@@ -467,9 +475,11 @@ def create_app(engine: Engine, cfg: Optional[GlobalConfig] = None) -> FastAPI:
         except Exception as exc:
             return _error(400, f"could not render the chat template: {exc}")
         images = _extract_images(body.messages)
+        videos = _extract_videos(body.messages)
         sp = _sampling(body, 128)
         obj = GenerateReqInput(text=prompt if n == 1 else [prompt] * n, sampling_params=sp if n == 1 else _n_sampling(sp, n, 1),
                                stream=body.stream, image_data=(images or None) if n == 1 else ([images] * n if images else None),
+                               video_data=(videos or None) if n == 1 else ([videos] * n if videos else None),
                                return_logprob=True if body.logprobs else None, top_logprobs_num=body.top_logprobs or None)
         cid = f"chatcmpl-{uuid.uuid4().hex}"
         use_reasoning = bool(sc.reasoning_parser) and body.separate_reasoning

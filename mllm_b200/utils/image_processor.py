@@ -64,3 +64,54 @@ def preprocess_image(image: torch.Tensor, patch_size: int = 16, merge_size: int 
 def image_token_count(grid_thw: torch.Tensor, merge_size: int = 2) -> int:
     g = grid_thw.reshape(-1, 3)
     return int((g[:, 0] * (g[:, 1] // merge_size) * (g[:, 2] // merge_size)).sum())
+
+
+def preprocess_video(frames: torch.Tensor, patch_size: int = 16, merge_size: int = 2, temporal_patch_size: int = 2,
+                     min_pixels: int = 64 * 32 * 32, max_pixels: int = 768 * 32 * 32,
+                     mean=0.5, std=0.5) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``frames``: uint8 ``[F, H, W, 3]`` (already sampled).  Consecutive groups of ``temporal_patch_size`` frames
+    form one temporal patch (the last frame is repeated when F does not divide); every frame is resized like an
+    image, with ``min_pixels`` / ``max_pixels`` bounding one frame.  Returns ``(pixel_values [T*gh*gw, 3*tp*P*P]
+    float32, grid_thw [[T, gh, gw]])``, rows ordered temporal patch by temporal patch and, inside one, like
+    :func:`preprocess_image` — so the rows of one temporal patch are exactly an image of grid ``[1, gh, gw]``."""
+    if frames.dim() != 4 or frames.shape[-1] != 3:
+        raise ValueError("frames must be [F, H, W, 3]")
+    n, H, W = int(frames.shape[0]), int(frames.shape[1]), int(frames.shape[2])
+    if n == 0:
+        raise ValueError("a video needs at least one frame")
+    tp, m, P = temporal_patch_size, merge_size, patch_size
+    if n % tp:
+        frames = torch.cat([frames, frames[-1:].expand(tp - n % tp, -1, -1, -1)])
+    h, w = smart_resize(H, W, P * m, min_pixels, max_pixels)
+    x = frames.permute(0, 3, 1, 2).float()
+    if (h, w) != (H, W):
+        x = F.interpolate(x, size=(h, w), mode="bicubic", align_corners=False, antialias=True).clamp_(0, 255)
+    mean_t = torch.as_tensor(mean, dtype=torch.float32).reshape(1, -1, 1, 1)
+    std_t = torch.as_tensor(std, dtype=torch.float32).reshape(1, -1, 1, 1)
+    x = (x / 255.0 - mean_t) / std_t                                       # [F', 3, h, w]
+    T, gh, gw = x.shape[0] // tp, h // P, w // P
+    x = x.reshape(T, tp, 3, gh // m, m, P, gw // m, m, P)
+    x = x.permute(0, 3, 6, 4, 7, 2, 1, 5, 8)                               # [T, gh/m, gw/m, m, m, C, tp, P, P]
+    return x.reshape(T * gh * gw, 3 * tp * P * P).contiguous(), torch.tensor([[T, gh, gw]], dtype=torch.int64)
+
+
+def sample_frame_indices(total_frames: int, source_fps: float, target_fps: float = 2.0, min_frames: int = 4,
+                         max_frames: int = 768) -> list:
+    """Evenly spaced frame numbers so that the clip is seen at about ``target_fps``, inside the frame budget."""
+    if total_frames <= 0:
+        return []
+    want = int(total_frames / max(source_fps, 1e-6) * target_fps)
+    want = max(min(want, max_frames, total_frames), min(min_frames, total_frames))
+    if want <= 1:
+        return [0]
+    return [int(round(i * (total_frames - 1) / (want - 1))) for i in range(want)]
+
+
+def video_timestamps(frame_indices, source_fps: float, temporal_patch_size: int = 2) -> list:
+    """Seconds shown in front of each temporal patch: the mean of the times of its first and last frame (the
+    frame list is padded with its last entry to a whole number of patches)."""
+    idx = list(frame_indices)
+    if len(idx) % temporal_patch_size:
+        idx += [idx[-1]] * (temporal_patch_size - len(idx) % temporal_patch_size)
+    t = [i / max(source_fps, 1e-6) for i in idx]
+    return [(t[i] + t[i + temporal_patch_size - 1]) / 2 for i in range(0, len(t), temporal_patch_size)]

@@ -87,6 +87,17 @@ def test_native_lru_order_and_lock_protection():
     assert sorted(freed) == [10, 11, 12, 13, 20, 21] and nat.total_size() == 0
 
 
+def test_native_namespaces_with_any_hash_value():
+    """Namespaces (image hashes, adapter ids) hash to unsigned 64-bit values; the tree's key is signed: both
+    halves of the range must work and stay distinct."""
+    nat = NativeRadixCache(None, 1)
+    for i in range(20):                                 # "img2", "img3", ... hash into the upper half
+        nat.insert(RadixKey([1, 2, 3], extra_key=f"img{i}"), np.array([100 * i, 100 * i + 1, 100 * i + 2]))
+    for i in range(20):
+        assert nat.match_prefix(RadixKey([1, 2, 3, 4], extra_key=f"img{i}")).indices.tolist() == [100 * i, 100 * i + 1, 100 * i + 2]
+    assert nat.match_prefix(RadixKey([1, 2, 3])).prefix_len == 0 and nat.total_size() == 60
+
+
 @pytest.mark.parametrize("page", [1, 8])
 def test_allocator_matches_python(page):
     rng = random.Random(0)
