@@ -125,7 +125,7 @@ class TokenizerWorker:
         norm = dict(mean=mc.get("image_mean", 0.5), std=mc.get("image_std", 0.5))
         for item in ([] if images is None else images if isinstance(images, list) else [images]):
             arr = item if isinstance(item, (np.ndarray, torch.Tensor)) else np.asarray(self.load_image(item))
-            img = torch.as_tensor(np.asarray(arr)).to(torch.uint8)
+            img = torch.as_tensor(np.array(arr)).to(torch.uint8)
             h.update(img.numpy().tobytes())
             pv, g = preprocess_image(img, mc["patch_size"], mc["merge_size"], mc["temporal_patch_size"], **norm)
             blocks.append((mc["image_token_id"], [mc["vision_start_token_id"]] + [mc["image_token_id"]] *

@@ -151,3 +151,36 @@ def test_video_request_through_the_engine():
         assert c["meta_info"]["prompt_tokens"] == a["meta_info"]["prompt_tokens"]
     finally:
         eng.shutdown()
+
+
+def test_video_and_image_parts_over_http():
+    testclient = pytest.importorskip("fastapi.testclient")
+    from mllm_b200.configs import GlobalConfig
+    from mllm_b200.engine.launch import Engine
+    from mllm_b200.server.launch import create_app
+
+    GlobalConfig.reset()
+    cfg = ServerConfig(model_path="preset:qwen3-vl-tiny", dtype="float32", max_running_requests=2, max_total_tokens=4096,
+                       context_length=2048, log_level="warning")
+    eng = Engine(cfg, mode="inproc", device="cpu").launch()
+    try:
+        rng = np.random.default_rng(0)
+        vid = rng.integers(0, 256, (4, 64, 64, 3), dtype=np.uint8)
+        img = rng.integers(0, 256, (64, 64, 3), dtype=np.uint8)
+        with testclient.TestClient(create_app(eng)) as c:
+            msgs = [{"role": "user", "content": [
+                {"type": "video", "video": {"frames": vid.tolist(), "fps": 2.0}},
+                {"type": "image", "image": img.tolist()},
+                {"type": "text", "text": "compare"}]}]
+            r = c.post("/v1/chat/completions", json={"messages": msgs, "max_tokens": 3, "temperature": 0})
+            assert r.status_code == 200, r.text
+            usage = r.json()["usage"]
+            tok = eng.tokenizer_worker.tokenize({"rid": "x", "text": "compare", "video_data": {"frames": vid, "fps": 2.0},
+                                                 "image_data": img})
+            n_vision = sum(1 for t in tok.input_ids if t in (IMG, VID))
+            assert usage["completion_tokens"] == 3 and usage["prompt_tokens"] > n_vision > 0
+            r = c.post("/generate", json={"text": "what", "video_data": {"frames": vid.tolist(), "fps": 2.0},
+                                          "sampling_params": {"max_new_tokens": 2, "temperature": 0}})
+            assert r.status_code == 200 and r.json()["meta_info"]["completion_tokens"] == 2
+    finally:
+        eng.shutdown()
