@@ -231,9 +231,10 @@ class Scheduler:
         # prompts that completed their prefill start generating
         still = []
         for q in self.prefilling:
-            if q.finished or q.num_computed >= len(q.input_ids):
-                if not q.finished:
-                    self.running.append(q)
+            if q.finished:
+                still.append(q)          # finished on its first token (or aborted): the next sweep releases it
+            elif q.num_computed >= len(q.input_ids):
+                self.running.append(q)
             else:
                 still.append(q)
         self.prefilling = still

@@ -70,6 +70,31 @@ def test_batched_equals_sequential_and_pool_is_returned():
     assert mrp.prefix_cache.protected_size() == 0 and mrp.free_req_slots() == mrp.runner.req_to_token_pool.size
 
 
+def test_requests_that_finish_on_their_first_token_give_everything_back():
+    """A request whose first sampled token already ends it (one new token asked for, or a stop token) never
+    joins the decode set; its row, its KV slots and its lock on the prefix tree must still be returned."""
+    torch.manual_seed(1)
+    sched = build_scheduler(_cfg(), device="cpu")
+    mrp = sched.mrp
+    free0 = mrp.runner.token_to_kv_pool_allocator.available_size()
+    for i in range(10):                                   # more than there are request rows
+        sched.add_request(_req(f"one{i}", torch.randint(0, 1000, (7 + i,)).tolist(), n=1))
+    done = _drain(sched)
+    assert len(done) == 10 and all(v[1] == "length" and len(v[0]) == 1 for v in done.values())
+    first = done["one0"][0][0]
+    sched.add_request(_req("stop", torch.randint(0, 1000, (7,), generator=torch.Generator().manual_seed(5)).tolist(), n=5))
+    # a stop token equal to whatever comes first: learn it from a dry run on a second scheduler
+    probe = build_scheduler(_cfg(), device="cpu")
+    ids = torch.randint(0, 1000, (9,), generator=torch.Generator().manual_seed(6)).tolist()
+    probe.add_request(_req("p", ids, n=1))
+    tok0 = _drain(probe)["p"][0][0]
+    sched.add_request(_req("stop2", ids, n=5, stop_token_ids=[tok0]))
+    done = _drain(sched)
+    assert done["stop2"][1] == "stop" and len(done["stop2"][0]) == 1 and first is not None
+    assert mrp.prefix_cache.protected_size() == 0 and mrp.free_req_slots() == mrp.runner.req_to_token_pool.size
+    assert mrp.runner.token_to_kv_pool_allocator.available_size() + mrp.prefix_cache.evictable_size() == free0
+
+
 def test_radix_reuse_gives_same_tokens_and_counts_cached():
     torch.manual_seed(1)
     shared = torch.randint(0, 1000, (40,)).tolist()
