@@ -54,6 +54,8 @@ class Req:
     cached_tokens: int = 0         # prefix hit at admission (reported to the client)
     num_computed: int = 0          # tokens whose KV is in the pool (prefix + prefilled chunks + decoded)
     last_node: Any = None
+    # page_size > 1: slots of the request's last page that are not used yet (pages are never shared)
+    spare_slots: Any = None
     # timing (seconds, host clock)
     first_token_time: float = 0.0
     finish_time: float = 0.0
@@ -125,10 +127,10 @@ class ModelRunnerProcess:
     def free_req_slots(self) -> int:
         return self.runner.req_to_token_pool.available_size()
 
-    def _alloc_kv_with_eviction(self, n: int) -> torch.Tensor:
+    def _alloc_kv_with_eviction(self, n: int, host: bool = False):
         alloc = self.runner.token_to_kv_pool_allocator
         for attempt in range(4):
-            out = alloc.alloc(n)
+            out = alloc.alloc_host(n) if host else alloc.alloc(n)
             if out is not None:
                 return out
             want = max(n, alloc.size // 10)
@@ -139,6 +141,32 @@ class ModelRunnerProcess:
         raise KVAllocationError(
             f"KV pool exhausted: need {n} slots, free {alloc.available_size()}, "
             f"evictable {self.prefix_cache.evictable_size()}, protected {self.prefix_cache.protected_size()}")
+
+    def _alloc_rows(self, needs: Sequence[Tuple[Req, int]]) -> torch.Tensor:
+        """KV slots for the next ``n`` tokens of each request, concatenated in order.
+
+        With one-slot pages this is a single allocation.  With larger pages every request owns whole pages —
+        the allocator frees a page as soon as one of its slots is freed, so a page shared by two requests
+        would be recycled while the other still reads it: a request first uses up what is left of its last
+        page (``spare_slots``) and then gets pages of its own."""
+        if self.page_size == 1:
+            return self._alloc_kv_with_eviction(sum(n for _, n in needs))
+        P = self.page_size
+        pages = []
+        for req, n in needs:
+            have = 0 if req.spare_slots is None else len(req.spare_slots)
+            pages.append(max(0, -(-(n - have) // P)))
+        fresh = self._alloc_kv_with_eviction(sum(pages) * P, host=True) if sum(pages) else np.empty(0, dtype=np.int64)
+        out, off = [], 0
+        for (req, n), k in zip(needs, pages):           # nothing above changed a request: a failed allocation leaves no trace
+            mine = fresh[off : off + k * P]
+            off += k * P
+            have = req.spare_slots if req.spare_slots is not None else mine[:0]
+            run = np.concatenate([have, mine]) if len(have) else mine
+            out.append(run[:n])
+            req.spare_slots = run[n:]
+        loc = torch.from_numpy(np.ascontiguousarray(np.concatenate(out)))
+        return loc if self.device.type == "cpu" else loc.pin_memory().to(self.device, non_blocking=True)
 
     # ------------------------------------------------------------------ admission
     def admit(self, req: Req) -> None:
@@ -176,7 +204,7 @@ class ModelRunnerProcess:
         ids: List[int] = []
         ext_lens, pre_lens, pool_idx = [], [], []
         total = sum(n for _, n in items)
-        loc = self._alloc_kv_with_eviction(total)
+        loc = self._alloc_rows(items)
         off = 0
         for req, n in items:
             seq = req.all_ids()
@@ -226,7 +254,7 @@ class ModelRunnerProcess:
         r = self.runner
         dev = self.device
         bs = len(reqs)
-        loc = self._alloc_kv_with_eviction(bs)
+        loc = self._alloc_rows([(q, 1) for q in reqs])
         pool = torch.tensor([q.req_pool_idx for q in reqs], dtype=torch.int32).to(dev, non_blocking=True)
         pos = torch.tensor([q.num_computed for q in reqs], dtype=torch.int64).to(dev, non_blocking=True)
         last = torch.tensor([q.last_id() for q in reqs], dtype=torch.int64).to(dev, non_blocking=True)
@@ -314,6 +342,12 @@ class ModelRunnerProcess:
         if cache and req.num_computed > req.prefix_len:
             self._insert(req, req.all_ids()[: req.num_computed])
         tail = self.runner.req_to_token_pool.req_to_token[req.req_pool_idx, req.prefix_len : req.num_computed]
+        if req.spare_slots is not None and len(req.spare_slots):
+            # the unused rest of the last page goes back in the same call as the tail: the allocator returns a
+            # page once per call in which one of its slots appears
+            spare = torch.from_numpy(np.ascontiguousarray(req.spare_slots)).to(tail.dtype)
+            tail = torch.cat([tail.to("cpu"), spare])
+        req.spare_slots = None
         if tail.numel():
             self.runner.token_to_kv_pool_allocator.free(tail)
         self.prefix_cache.dec_lock_ref(req.last_node)

@@ -95,6 +95,51 @@ def test_requests_that_finish_on_their_first_token_give_everything_back():
     assert mrp.runner.token_to_kv_pool_allocator.available_size() + mrp.prefix_cache.evictable_size() == free0
 
 
+@pytest.mark.parametrize("page", [4, 16])
+def test_paged_pool_never_shares_a_page_between_requests(page):
+    """With pages larger than one slot every request owns whole pages (the allocator recycles a page as soon as
+    one of its slots is freed): concurrent requests with odd lengths, prefix reuse and long generations give the
+    tokens of the one-slot-page run, no two live requests ever hold slots of one page, and every page comes back."""
+    torch.manual_seed(2)
+    shared = torch.randint(0, 1000, (37,)).tolist()
+    prompts = [torch.randint(0, 1000, (n,)).tolist() for n in (5, 17, 9, 33, 3)] + \
+        [shared + torch.randint(0, 1000, (n,)).tolist() for n in (4, 11, 2)]
+    news = [20, 3, 11, 1, 25, 7, 9, 13]
+
+    def run(page_size, check):
+        sched = build_scheduler(_cfg(page_size=page_size, max_total_tokens=1024), device="cpu")
+        mrp = sched.mrp
+        free0 = mrp.runner.token_to_kv_pool_allocator.available_size()
+        for i, (p, n) in enumerate(zip(prompts, news)):
+            sched.add_request(_req(f"r{i}", p, n=n))
+        done = {}
+        for _ in range(500):
+            out = sched.step()
+            if out is not None:
+                for i, rid in enumerate(out.rids):
+                    if out.finished_reasons[i] is not None:
+                        done[rid] = out.output_ids[i]
+            if check:
+                rtt = mrp.runner.req_to_token_pool.req_to_token
+                owner = {}
+                for q in sched.running + sched.prefilling:
+                    if q.req_pool_idx < 0 or q.finished:
+                        continue
+                    own = rtt[q.req_pool_idx, q.prefix_len:q.num_computed].tolist() + \
+                        ([] if q.spare_slots is None else list(map(int, q.spare_slots)))
+                    for pg in {s // page_size for s in own}:
+                        assert owner.setdefault(pg, q.rid) == q.rid, f"page {pg} held by {owner[pg]} and {q.rid}"
+            if not sched.has_work():
+                break
+        sched._sweep_finished()
+        assert mrp.prefix_cache.protected_size() == 0
+        assert mrp.runner.token_to_kv_pool_allocator.available_size() + mrp.prefix_cache.evictable_size() == free0
+        return done
+
+    want, got = run(1, False), run(page, True)
+    assert len(got) == len(prompts) and got == want
+
+
 def test_radix_reuse_gives_same_tokens_and_counts_cached():
     torch.manual_seed(1)
     shared = torch.randint(0, 1000, (40,)).tolist()
