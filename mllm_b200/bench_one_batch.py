@@ -250,6 +250,7 @@ class BenchRunner:
         r.req_to_token_pool.clear()
         r.token_to_kv_pool_allocator.clear()
         self.slots, self.seq_len, self.batch = [], 0, 0
+        self._spare = None
 
     def max_batch_size_for(self, input_len: int, output_len: int) -> int:
         return self.runner.max_total_num_tokens // max(1, input_len + output_len)
@@ -281,7 +282,18 @@ class BenchRunner:
     def decode(self, last_ids: torch.Tensor) -> torch.Tensor:
         r = self.runner
         bs = self.batch
-        loc = r.token_to_kv_pool_allocator.alloc(bs)
+        page = getattr(r.token_to_kv_pool_allocator, "page_size", 1)
+        if page == 1:
+            loc = r.token_to_kv_pool_allocator.alloc(bs)
+        else:
+            # whole pages are granted; what a step does not use serves the next ones (nothing is freed before
+            # clear(), so the batch may share pages)
+            spare = getattr(self, "_spare", None)
+            if spare is None or spare.numel() < bs:
+                got = r.token_to_kv_pool_allocator.alloc(-(-bs // page) * page)
+                spare = got if (spare is None or got is None) else torch.cat([spare, got])
+            loc = None if spare is None else spare[:bs]
+            self._spare = None if spare is None else spare[bs:]
         if loc is None:
             raise RuntimeError("KV pool exhausted during decode")
         r.req_to_token_pool.req_to_token[self._slots_dev.long(), self.seq_len] = loc.to(torch.int32)
