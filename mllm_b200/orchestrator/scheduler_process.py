@@ -72,6 +72,11 @@ class Scheduler:
         ids = list(t.input_ids)
         if not ids:
             return "empty prompt"
+        # an id outside the embedding table would be an out-of-bounds read on the device
+        vocab = int(self.mrp.runner.vocab_size)
+        lo, hi = min(ids), max(ids)
+        if lo < 0 or hi >= vocab:
+            return f"token id {lo if lo < 0 else hi} is outside the vocabulary (0..{vocab - 1})"
         if len(ids) >= self.context_len:
             ids = ids[: self.context_len - 1]
         sp.max_new_tokens = max(0, min(sp.max_new_tokens, self.context_len - len(ids)))
@@ -79,6 +84,9 @@ class Scheduler:
             return f"prompt of {len(ids)} tokens exceeds the KV pool ({self.mrp.runner.max_total_num_tokens} tokens)"
         if self.cfg.max_queued_requests is not None and len(self.waiting) >= self.cfg.max_queued_requests:
             return "queue full"
+        bad = self._vision_inputs_error(ids, t.mm_inputs, len(ids) < len(t.input_ids))
+        if bad:
+            return bad
         if t.return_logprob and getattr(self.cfg, "pp_size", 1) > 1:
             return "log-probabilities are not available with pipeline parallelism (the logits live on the last stage)"
         stop_ids = set(sp.stop_token_ids or [])
@@ -94,6 +102,29 @@ class Scheduler:
         if t.mm_inputs and "mrope_position_delta" in t.mm_inputs:
             req.mrope_delta = int(t.mm_inputs["mrope_position_delta"])
         self.waiting.append(req)
+        return None
+
+    def _vision_inputs_error(self, ids: List[int], mm: Optional[Dict[str, Any]], truncated: bool) -> Optional[str]:
+        """Pixels, grids and vision tokens of a request must agree before it reaches the model: the vision tower
+        writes one feature row per vision token, and a mismatch found there would end the serving loop."""
+        if not mm or mm.get("pixel_values") is None or mm.get("image_grid_thw") is None:
+            return None
+        cfg = self.mrp.runner.hf_config
+        image_id = getattr(cfg, "image_token_id", None)
+        if image_id is None:
+            return "this model takes no image or video inputs"
+        if truncated:
+            return "the prompt with its image / video tokens exceeds the context length"
+        merge = int(getattr(getattr(cfg, "vision_config", None), "spatial_merge_size", 2) or 2)
+        grids = mm["image_grid_thw"].reshape(-1, 3).tolist()
+        rows = sum(int(t) * int(h) * int(w) for t, h, w in grids)
+        want = sum(int(t) * (int(h) // merge) * (int(w) // merge) for t, h, w in grids)
+        if int(mm["pixel_values"].shape[0]) != rows:
+            return f"pixel_values has {int(mm['pixel_values'].shape[0])} rows, the grids describe {rows}"
+        vision_ids = {image_id, getattr(cfg, "video_token_id", None)} - {None}
+        have = sum(1 for tok in ids if tok in vision_ids)
+        if have != want:
+            return f"the prompt holds {have} image / video tokens, the grids describe {want}"
         return None
 
     def abort(self, rid: str) -> bool:

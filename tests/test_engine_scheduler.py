@@ -140,6 +140,30 @@ def test_paged_pool_never_shares_a_page_between_requests(page):
     assert len(got) == len(prompts) and got == want
 
 
+def test_requests_the_model_cannot_take_are_refused_at_intake():
+    """Token ids outside the vocabulary (an out-of-bounds read on a device) and vision inputs whose pixels, grids
+    and tokens disagree are answered with an error; the serving loop keeps running."""
+    import numpy as np
+
+    sched = build_scheduler(_cfg(), device="cpu")
+    assert "outside the vocabulary" in sched.add_request(_req("a", [5, 99999]))
+    assert "outside the vocabulary" in sched.add_request(_req("b", [5, -3]))
+    assert sched.add_request(_req("c", [5, 6])) is None and "c" in _drain(sched)
+
+    eng = Engine(_cfg(model_path="preset:qwen3-vl-tiny", context_length=256), mode="inproc", device="cpu").launch()
+    try:
+        img = np.random.default_rng(0).integers(0, 256, (64, 64, 3), dtype=np.uint8)
+        sp = {"max_new_tokens": 2, "temperature": 0.0}
+        with pytest.raises(ValueError, match="image / video tokens"):
+            eng.generate(input_ids=[5, 1001, 6], image_data=img, sampling_params=sp, timeout=60)     # a stray image token
+        big = np.random.default_rng(0).integers(0, 256, (640, 640, 3), dtype=np.uint8)
+        with pytest.raises(ValueError):
+            eng.generate("x", sp, image_data=big, timeout=60)                                      # image longer than the context
+        assert len(eng.generate("x", sp, image_data=img, timeout=60)["output_ids"]) == 2
+    finally:
+        eng.shutdown()
+
+
 def test_radix_reuse_gives_same_tokens_and_counts_cached():
     torch.manual_seed(1)
     shared = torch.randint(0, 1000, (40,)).tolist()
