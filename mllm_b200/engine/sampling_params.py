@@ -41,6 +41,12 @@ class SamplingParams:
             raise ValueError(f"top_p must be in (0, 1], got {self.top_p}")
         if self.top_k < -1 or self.top_k == 0:
             raise ValueError(f"top_k must be -1 (off) or >= 1, got {self.top_k}")
+        if self.top_k > (1 << 30):      # larger than any vocabulary: no filter (and keeps the value inside int32)
+            self.top_k = -1
+        for name in ("temperature", "top_p", "min_p", "repetition_penalty"):
+            v = getattr(self, name)
+            if v != v or v in (float("inf"), float("-inf")):
+                raise ValueError(f"{name} must be a finite number")
         if not 0 <= self.min_p <= 1:
             raise ValueError(f"min_p must be in [0, 1], got {self.min_p}")
         if self.max_new_tokens < 0:

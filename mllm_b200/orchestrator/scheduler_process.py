@@ -98,7 +98,7 @@ class Scheduler:
         req = Req(rid=t.rid, input_ids=ids, sampling=sp, stream=t.stream, input_text=t.input_text,
                   mm_inputs=t.mm_inputs, extra_key=extra_key, stop_token_ids=stop_ids,
                   created_time=t.created_time or time.time(), return_logprob=bool(t.return_logprob),
-                  top_logprobs_num=int(t.top_logprobs_num or 0), stop_strs=[s for s in (sp.stop or []) if s])
+                  top_logprobs_num=max(0, min(int(t.top_logprobs_num or 0), vocab)), stop_strs=[s for s in (sp.stop or []) if s])
         if t.mm_inputs and "mrope_position_delta" in t.mm_inputs:
             req.mrope_delta = int(t.mm_inputs["mrope_position_delta"])
         self.waiting.append(req)
