@@ -1,11 +1,11 @@
 """Flagship benchmark: Qwen3-8B-shaped decoder, bf16, one batch of `--batch-size` requests with
 input_len 2048 and output_len 128 (prefill + 127 greedy decode steps) — the reference's
-``bench_one_batch`` workload — on N GPUs of one node.  With N > 1 the default is data parallelism
-(``--parallelism dp``): one full replica of the model per GPU, each serving its own batch of
-`--batch-size` requests, so the global batch is N x batch and per-GPU work is fixed (weak scaling);
-this is the layout that serves the most tokens per second for a model that fits one GPU.
-``--parallelism tp`` shards the one batch over the N GPUs instead (tensor parallelism with the
-fused NVLink kernels; strong scaling, lower latency per batch).
+``bench_one_batch`` workload — on N GPUs of one node.  With N > 1 the default is tensor parallelism
+(``--parallelism tp``): the one batch is sharded over the N GPUs and every layer's partial sums cross
+NVLink inside the fused kernels (GEMM with reduce-scatter epilogue, reduce + add + RMSNorm + all-gather,
+flag-gated consumer GEMM; the peer-memory reduce in decode) — strong scaling, lower latency per batch.
+``--parallelism dp`` runs one full replica of the model per GPU instead, each serving its own batch of
+`--batch-size` requests (global batch N x batch, weak scaling, no collective in the timed region).
 
     python bench.py --gpus 1 --steps 5 --warmup 3
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
@@ -50,8 +50,10 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--input-len", type=int, default=2048)
     ap.add_argument("--output-len", type=int, default=128)
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--parallelism", choices=["dp", "tp"], default="dp",
-                    help="N > 1: dp = one replica and one batch per GPU (weak scaling), tp = one batch sharded over N GPUs")
+    ap.add_argument("--parallelism", choices=["dp", "tp"], default="tp",
+                    help="N > 1: tp = one batch sharded over N GPUs (fused NVLink kernels), dp = one replica and one batch per GPU")
+    ap.add_argument("--comm-backend", choices=["fused", "nccl"], default="fused",
+                    help="tp only: fused = peer-memory kernels of this package, nccl = library all-reduce after o_proj / down_proj")
     ap.add_argument("--device", choices=["cuda", "cpu"], default="cuda",
                     help="cpu runs the same control flow on the host reference ops (flow tests; not a measurement)")
     ap.add_argument("--watchdog-s", type=float, default=1500.0,
@@ -208,6 +210,8 @@ def run_ours(a: argparse.Namespace) -> dict:
     sc.model_path = f"preset:{a.model}"
     sc.dtype = "bfloat16"
     sc.tp_size = a.gpus if use_tp else 1
+    if use_tp:
+        sc.comm_backend = a.comm_backend
     sc.dp_size = replicas
     sc.max_running_requests = a.batch_size
     sc.max_total_tokens = a.batch_size * (a.input_len + a.output_len) + 4096
@@ -304,6 +308,14 @@ def run_ours(a: argparse.Namespace) -> dict:
         wd.log("end-to-end region done")
 
     layout = f"tp{a.gpus}" if use_tp else f"dp{a.gpus}"
+    comm_info = None
+    if use_tp:
+        from mllm_b200.parallel.symm import get_tp_comm
+
+        comm = get_tp_comm()
+        comm_info = {"path": "fused peer-memory kernels" if comm is not None else "nccl all-reduce",
+                     "fused_prefill_calls": int(comm.epoch) if comm is not None else 0,
+                     "prefill_rows_cap": int(comm.prefill.rows_cap) if comm is not None and comm.prefill is not None else 0}
     result = {
         "metric": METRIC, "value": tokens_per_step / (ms_per_step / 1e3), "unit": "tokens/s", "n_gpus": a.gpus,
         "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
@@ -320,6 +332,7 @@ def run_ours(a: argparse.Namespace) -> dict:
         # the batch's time to first token and time per output token, median over the timed steps (max over ranks)
         "p50_ttft_ms": prefill_med, "p50_tpot_ms": decode_med / (out_len - 1),
         "gpu_launches": launches_all, "gpu_launches_per_rank": int(launches), "clocks": clocks, "e2e": e2e,
+        "comm": comm_info,
     }
     if world > 1:
         barrier()

@@ -358,22 +358,48 @@ def run_single_setting(*, bench_runner: BenchRunner, args: BenchArgs, setting: B
                                        vocab_size=br.runner.vocab_size, seed=seed, device=dev)
     use_events = dev.type == "cuda"
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(setting.output_len + 1)] if use_events else []
+    # --profile: one trace for the prefill and one for a window of decode steps (separate files, like the
+    # stage switches of pymllm/bench_one_batch.py:668-758); NVTX ranges mark both stages for external tools
+    import contextlib
+
+    from .utils.profiling import nvtx_range, torch_profiler
+
+    traces: List[str] = []
+    tag = f"bs{setting.batch_size}_in{setting.input_len}_out{setting.output_len}"
+
+    def stage_profiler(stage: str):
+        on = bool(record_result and args.profile and args.profile_stage in ("all", stage))
+        return torch_profiler(on, args.profile_activities, args.profile_record_shapes,
+                              filename_prefix=args.profile_filename_prefix, tag=f"{tag}_{stage}", exported=traces)
+
     if use_events:
         _sync(dev)
         ev[0].record()
-    prefill_latency, nxt = _timed_call(dev, lambda: br.extend(ids, **mm))
+    with stage_profiler("prefill"), nvtx_range("bench_one_batch.prefill"):
+        prefill_latency, nxt = _timed_call(dev, lambda: br.extend(ids, **mm))
     if use_events:
         ev[1].record()
     decode_lat: List[float] = []
-    for step in range(setting.output_len - 1):
-        lat, nxt = _timed_call(dev, lambda: br.decode(nxt))
-        if use_events:
-            ev[step + 2].record()
-        decode_lat.append(lat)
-        if args.log_decode_step and (step + 1) % args.log_decode_step == 0:
-            logger.info("decode step %d: %.3f ms, %.1f tok/s", step + 1, lat * 1e3, setting.batch_size / lat)
+    n_decode = setting.output_len - 1
+    win_start = min(max(0, n_decode - 1), args.profile_start_step if args.profile_start_step is not None else n_decode // 2)
+    win_end = min(n_decode, win_start + max(1, args.profile_steps))
+    with contextlib.ExitStack() as window:
+        for step in range(n_decode):
+            if step == win_start:
+                window.enter_context(stage_profiler("decode"))
+            with nvtx_range("bench_one_batch.decode_step"):
+                lat, nxt = _timed_call(dev, lambda: br.decode(nxt))
+            if use_events:
+                ev[step + 2].record()
+            decode_lat.append(lat)
+            if step + 1 == win_end:
+                window.close()
+            if args.log_decode_step and (step + 1) % args.log_decode_step == 0:
+                logger.info("decode step %d: %.3f ms, %.1f tok/s", step + 1, lat * 1e3, setting.batch_size / lat)
     _sync(dev)
     extra: Dict[str, Any] = {"tp_size": pstate.get_tensor_model_parallel_world_size()}
+    if traces:
+        extra["profile_traces"] = list(traces)
     if mm:
         fb0 = br.last_forward_batch
         vit_ms, vit_tok = float(fb0.vit_prefill_ms or 0.0), int(fb0.vit_prefill_tokens or 0)
@@ -437,16 +463,7 @@ def run_benchmark(cfg: GlobalConfig, args: BenchArgs) -> List[Dict[str, Any]]:
         run_single_setting(bench_runner=br, args=args, setting=warm, seed=args.seed, record_result=False)
     rows = []
     for s in settings:
-        prof = None
-        if args.profile:
-            from .utils.profiling import torch_profiler
-
-            prof = torch_profiler(args, s)
-        if prof is not None:
-            with prof:
-                row = run_single_setting(bench_runner=br, args=args, setting=s, seed=args.seed, record_result=True)
-        else:
-            row = run_single_setting(bench_runner=br, args=args, setting=s, seed=args.seed, record_result=True)
+        row = run_single_setting(bench_runner=br, args=args, setting=s, seed=args.seed, record_result=True)
         if row is not None:
             rows.append(row)
             if rank0:

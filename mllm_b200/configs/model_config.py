@@ -18,7 +18,5 @@ class ModelConfig:
         hf = self.__dict__.get("hf_config")
         if hf is not None and hasattr(hf, name):
             return getattr(hf, name)
-        raise AttributeError(
-            f"'{type(self).__name__}' has no attribute '{name}' "
-            f"(also not found on hf_config)"
-        )
+        where = "no hf_config is loaded" if hf is None else f"{type(hf).__name__} does not define it either"
+        raise AttributeError(f"model config: unknown field {name!r} ({where})")

@@ -816,12 +816,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
 }
 
 bool set_attn_smem() {
-  static bool done = false, ok = false;
-  if (!done) {
-    ok = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) == cudaSuccess;
-    done = true;
-  }
-  return ok;
+  return ensure_dynamic_smem(reinterpret_cast<const void*>(attn_fwd_kernel), kAttnSmem) == cudaSuccess;
 }
 
 }  // namespace
@@ -837,16 +832,11 @@ int decode_num_splits(int batch, int hkv, int max_seq_len, int num_sms) {
 
 template <int NQ>
 int launch_decode_cfg(const AttnParams& p, dim3 grid, cudaStream_t s) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(attn_decode_kernel<NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             DecCfg<NQ>::kSmem) != cudaSuccess)
-      return -3;
-    attr_set = true;
-  }
-  launch_pdl(attn_decode_kernel<NQ>, grid, dim3(kDecThreads), DecCfg<NQ>::kSmem, s, p);
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(attn_decode_kernel<NQ>), DecCfg<NQ>::kSmem) != cudaSuccess)
+    return -3;
+  const cudaError_t err = launch_pdl(attn_decode_kernel<NQ>, grid, dim3(kDecThreads), DecCfg<NQ>::kSmem, s, p);
   note_launch();
-  return 0;
+  return err == cudaSuccess ? 0 : -4;
 }
 
 int launch_attention(const AttnArgs& a, cudaStream_t s) {

@@ -5,7 +5,7 @@
 // with cluster multicast), tcgen05 tensor-memory allocation / MMA / commit /
 // load, proxy fences, and system-scope flag accesses for peer memory.
 //
-// Every wait in this file is bounded: after a fixed number of polls it gives
+// Every wait in this file is bounded: after a fixed time it gives
 // up and returns false so the calling kernel can record an error status and
 // leave in an orderly way (free TMEM, let copies in flight land) instead of
 // spinning forever on a shared GPU.
@@ -29,10 +29,18 @@ enum KernelStatus : int {
   kStatusBadIndex = 3,         // a slot / page / expert index was out of range
 };
 
-// polls before giving up: fast polls first, then polls separated by nanosleep.
-// ~4M polls * (try_wait suspend + 32 ns) is on the order of a second.
+// Waits are bounded by elapsed time, not by a poll count (how long one poll takes is up to the
+// hardware): a few thousand polls without sleeping first, then polls separated by nanosleep until the
+// budget on the global nanosecond timer is spent.
 constexpr uint32_t kFastPolls = 2048;
-constexpr uint32_t kMaxPolls = 2u << 20;
+constexpr uint64_t kPipelineWaitNs = 2000000000ull;  // waits between roles of one CTA: 2 s
+constexpr uint64_t kPeerWaitNs = 8000000000ull;      // waits for another rank's flag: 8 s
+
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -82,23 +90,45 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return done != 0;
 }
 
-// Bounded wait. Returns false when the phase did not complete in time.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kMaxPolls; ++i) {
+// Same, with an upper bound (ns) on how long the hardware may keep the thread suspended in the call.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t suspend_ns) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(suspend_ns)
+      : "memory");
+  return done != 0;
+}
+
+// Bounded wait. Returns false when the phase did not complete within kPipelineWaitNs, or as soon as
+// *abort (a flag in shared memory that another role of the CTA sets when it gives up) is non-zero.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const volatile int* abort = nullptr) {
+  for (uint32_t i = 0; i < kFastPolls; ++i)
     if (mbar_try_wait(bar, parity)) return true;
-    if (i > kFastPolls) __nanosleep(32);
+  const uint64_t t0 = global_ns();
+  for (uint32_t i = 0;; ++i) {
+    if (mbar_try_wait_hint(bar, parity, 2000u)) return true;
+    if ((i & 7u) == 7u) {
+      if (abort != nullptr && *abort != 0) return false;
+      if (global_ns() - t0 > kPipelineWaitNs) return false;
+    }
+    __nanosleep(32);
   }
-  return false;
 }
 
 // Bounded wait for warps that share their scheduler with working warps: backs off from the first
 // failed poll so that the polling loop does not compete for issue slots.
 __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, uint32_t sleep_ns = 200) {
-  for (uint32_t i = 0; i < kMaxPolls; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
+  for (uint32_t i = 0;; ++i) {
     __nanosleep(sleep_ns);
+    if (mbar_try_wait_hint(bar, parity, 2000u)) return true;
+    if ((i & 7u) == 7u && global_ns() - t0 > kPipelineWaitNs) return false;
   }
-  return false;
 }
 
 // ---------------------------------------------------------------------------
@@ -290,19 +320,34 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 __device__ __forceinline__ void red_add_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-// Bounded spin until *p >= want. False on timeout.  When `status` is given the wait also gives up
-// as soon as that word is non-zero: once one wait of the process has run out (a peer is gone or
-// far behind) the later ones return after a few hundred polls instead of spending their full
-// bound each, so the host reaches its status check quickly.
-__device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t want, const int* status = nullptr) {
-  for (uint32_t i = 0; i < kMaxPolls; ++i) {
+// Bounded spin until *p >= want. False when kPeerWaitNs (or `budget_ns`) went by first.  When `status`
+// is given the wait also gives up as soon as that word is non-zero: once one wait of the process has
+// run out (a peer is gone or far behind) the later ones return after a few hundred polls instead of
+// spending their full budget each, so the host reaches its status check quickly.
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t want, const int* status = nullptr,
+                                             uint64_t budget_ns = kPeerWaitNs) {
+  for (uint32_t i = 0; i < 64; ++i)
     if (ld_acquire_sys(p) >= want) return true;
-    if (i > 64) {
-      __nanosleep(64);
-      if (status != nullptr && (i & 255u) == 128u && *reinterpret_cast<const volatile int*>(status) != 0) return false;
+  const uint64_t t0 = global_ns();
+  for (uint32_t i = 0;; ++i) {
+    if (ld_acquire_sys(p) >= want) return true;
+    __nanosleep(64);
+    if ((i & 63u) == 63u) {
+      if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return false;
+      if (global_ns() - t0 > budget_ns) return false;
     }
   }
-  return false;
+}
+
+// counters in shared memory that one role of a CTA bumps and another polls (cannot be lapped, unlike
+// an mbarrier phase)
+__device__ __forceinline__ void red_add_release_cta_smem(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.cta.shared::cta.add.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_cta_smem(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+  return v;
 }
 
 // ---------------------------------------------------------------------------
@@ -362,6 +407,11 @@ __device__ __forceinline__ float warp_max(float v) {
     using T = __half;                         \
     __VA_ARGS__;                              \
   }
+
+// Host side: raises `kernel`'s dynamic shared-memory limit to `bytes`, once per (kernel, device).
+// cudaFuncSetAttribute acts on the current device only, so the record of what was set is kept per
+// device; safe to call from several threads.
+cudaError_t ensure_dynamic_smem(const void* kernel, int bytes);
 
 // Host side: launch with the programmatic-stream-serialization attribute (MLLM_B200_PDL=0 turns
 // it off).  Works under stream capture: the dependency becomes a programmatic graph edge.

@@ -7,6 +7,9 @@
 // scaling pass), so their ceiling is HBM bandwidth.
 #include <atomic>
 #include <cstdlib>
+#include <map>
+#include <mutex>
+#include <utility>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -22,6 +25,20 @@ bool pdl_enabled() {
     return !(v != nullptr && v[0] == '0');
   }();
   return on;
+}
+
+cudaError_t ensure_dynamic_smem(const void* kernel, int bytes) {
+  static std::mutex mu;
+  static std::map<std::pair<const void*, int>, int> set_to;  // (kernel, device) -> bytes granted
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = set_to.find({kernel, dev});
+  if (it != set_to.end() && it->second >= bytes) return cudaSuccess;
+  err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (err == cudaSuccess) set_to[{kernel, dev}] = bytes;
+  return err;
 }
 
 namespace {

@@ -135,8 +135,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
   uint64_t* empty_bar = bars + n_stages;
   uint64_t* acc_full = bars + 2 * n_stages;
   uint64_t* acc_empty = acc_full + 2;
-  uint64_t* rs_done = acc_empty + 2;  // reduce-scatter: epilogue stores of an accumulator buffer issued
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(rs_done + 2);
+  // reduce-scatter: number of (epilogue warp, tile) store batches issued so far.  A counter, not an mbarrier:
+  // the publisher warp may fall several tiles behind the epilogue (its system-scope fence waits for peer
+  // stores in flight), and a phase bit that is lapped twice reads as "not yet" for ever.
+  uint32_t* rs_stored = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   int* ticket_slot = const_cast<int*>(abort_flag) + 1;
   uint8_t* epi_staging = reinterpret_cast<uint8_t*>(bars) + 512;  // normal tiling only
@@ -152,8 +155,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 128);
-      mbar_init(&rs_done[a], 128);
     }
+    *rs_stored = 0;
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_row);
@@ -242,7 +245,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
         }
       }
       for (int kb = kb0; kb < kb1; ++kb) {
-        if (*abort_flag || !mbar_wait(&empty_bar[stage], phase ^ 1)) {
+        if (*abort_flag || !mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
           ok = false;
           break;
         }
@@ -274,14 +277,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
     for (int idx = 0; ok && get_work(idx, tr, tc, kb0, kb1); ++idx) {
       const int acc = idx % C::kAccBufs;
       const uint32_t acc_phase = (idx / C::kAccBufs) & 1;
-      if (*abort_flag || !mbar_wait(&acc_empty[acc], acc_phase ^ 1)) {
+      if (*abort_flag || !mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) {
         ok = false;
         break;
       }
       tc_fence_after_sync();
       const uint32_t d_base = tmem_base + acc * C::kAccCols;
       for (int kb = kb0; kb < kb1; ++kb) {
-        if (*abort_flag || !mbar_wait(&full_bar[stage], phase)) {
+        if (*abort_flag || !mbar_wait(&full_bar[stage], phase, abort_flag)) {
           ok = false;
           break;
         }
@@ -321,14 +324,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
     }
   } else if (warp == 3 && lane == 0 && !SWAP && p.rs_tp > 0) {
     // ------------------------------ reduce-scatter publisher ------------------
-    // Waits until the epilogue threads have issued a tile's stores (mbarrier arrive / wait orders them
-    // before this thread), makes them visible system-wide with one fence, counts the tile in and, when the
-    // last column tile of a 128-row tile is done, raises the owner's flag.
+    // Waits until the four epilogue warps have issued a tile's stores (release increment / acquire load of
+    // the shared counter orders them before this thread), makes them visible system-wide with one fence,
+    // counts the tile in and, when the last column tile of a 128-row tile is done, raises the owner's flag.
     int tr, tc, kb0, kb1;
     for (int idx = 0; get_work(idx, tr, tc, kb0, kb1); ++idx) {
-      const int acc = idx % C::kAccBufs;
-      const uint32_t ph = (idx / C::kAccBufs) & 1;
-      if (*abort_flag || !mbar_wait(&rs_done[acc], ph)) {
+      const uint32_t want = 4u * static_cast<uint32_t>(idx + 1);
+      bool seen = false;
+      const uint64_t t0 = global_ns();
+      for (uint32_t i = 0;; ++i) {
+        if (ld_acquire_cta_smem(rs_stored) >= want) {
+          seen = true;
+          break;
+        }
+        __nanosleep(100);
+        if ((i & 31u) == 31u && (*abort_flag || global_ns() - t0 > kPipelineWaitNs)) break;
+      }
+      if (!seen) {
         *abort_flag = 1;
         if (p.status != nullptr) atomicExch(p.status, kStatusPipelineTimeout);
         break;
@@ -352,7 +364,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
     for (int idx = 0; ok && get_work(idx, tr, tc, kb0, kb1); ++idx) {
       const int acc = idx % C::kAccBufs;
       const uint32_t acc_phase = (idx / C::kAccBufs) & 1;
-      if (*abort_flag || !mbar_wait(&acc_full[acc], acc_phase)) {
+      if (*abort_flag || !mbar_wait(&acc_full[acc], acc_phase, abort_flag)) {
         ok = false;
         break;
       }
@@ -432,7 +444,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
             __syncwarp();
           }
           // hand the tile to the publisher warp, which fences and signals off the epilogue's critical path
-          mbar_arrive(&rs_done[acc]);
+          __syncwarp();
+          if (lane == 0) red_add_release_cta_smem(rs_stored, 1u);
         } else {
         // thread = one output row; columns in chunks of 32
         const int64_t row = static_cast<int64_t>(tr) * kBM + row_in_tile;
@@ -710,13 +723,10 @@ int launch_cfg(const CUtensorMap& tr, const CUtensorMap& tc, KParams p, int grid
   p.stages = C::kStages;
   if (SWAP && stage_cap >= 2 && stage_cap < p.stages) p.stages = stage_cap;
   auto kern = gemm_tcgen05_kernel<BN, SWAP, SWIGLU, RT, KD>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(static_cast<size_t>(C::kStages) * C::kStageBytes + 1024 + 512 + (SWAP ? 0 : kEpiStagingBytes))) !=
-        cudaSuccess)
-      return -3;
-    attr_set = true;
-  }
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern),
+                          static_cast<int>(static_cast<size_t>(C::kStages) * C::kStageBytes + 1024 + 512 +
+                                           (SWAP ? 0 : kEpiStagingBytes))) != cudaSuccess)
+    return -3;
   const size_t smem = static_cast<size_t>(p.stages) * C::kStageBytes + 1024 + 512 + (SWAP ? 0 : kEpiStagingBytes);
   const cudaError_t err = launch_pdl(kern, dim3(grid), dim3(kThreads), smem, s, tr, tc, p);
   note_launch();

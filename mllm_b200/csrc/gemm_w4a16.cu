@@ -389,12 +389,7 @@ int launch_w4_cfg(const CUtensorMap& tx, const CUtensorMap& tw, const W4Params& 
   using C = W4Cfg<BN>;
   auto kern = w4a16_gemm_kernel<T, BN>;
   const size_t smem = static_cast<size_t>(C::kStages) * C::kStageBytes + C::kRawStages * C::kRawBytes + 1024 + 512;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
-      return -3;
-    attr_set = true;
-  }
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), static_cast<int>(smem)) != cudaSuccess) return -3;
   const cudaError_t err = launch_pdl(kern, grid, dim3(kW4Threads), smem, s, tx, tw, p);
   note_launch();
   return err == cudaSuccess ? 0 : -4;

@@ -405,12 +405,7 @@ int launch_grouped_cfg(const CUtensorMap& tw, const CUtensorMap& tx, const Group
   using C = GCfg<BN, SWIGLU>;
   auto kern = moe_grouped_gemm_kernel<BN, SWIGLU>;
   const size_t smem = static_cast<size_t>(C::kStages) * C::kStageBytes + 1024 + 512;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
-      return -3;
-    attr_set = true;
-  }
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), static_cast<int>(smem)) != cudaSuccess) return -3;
   const cudaError_t err = launch_pdl(kern, dim3(grid), dim3(kThreads), smem, s, tw, tx, p);
   note_launch();
   return err == cudaSuccess ? 0 : -4;

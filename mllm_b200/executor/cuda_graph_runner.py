@@ -5,7 +5,8 @@ pymllm/executor/cuda_graph_runner.py:95-548: sizes
 ``[1, 2, 4, 8, 12, 16..256 step 8, 272..496 step 16, 512.. step 32]`` up to
 ``max_running_requests``; capture from the largest size down on a side stream, all graphs
 sharing one memory pool; replay pads the batch up to the next captured size with rows that
-point at request slot 0 / KV slot 0 (the padding sink) and slices the outputs.
+point at the request table's spare row (``ReqToTokenPool.pad_row``, owned by no request) and KV slot 0
+(the padding sink) and slices the outputs.
 
 The whole step — embedding, every layer, lm_head and the greedy argmax — sits inside the
 graph.  The attention kernels take sequence lengths and the request->slot table from
@@ -45,9 +46,10 @@ class CudaGraphRunner:
         self.batch_sizes = batch_sizes or capture_batch_sizes(self.max_bs)
         n = self.batch_sizes[-1]
         dev = self.device
-        # static inputs; padded rows read request slot 0 / write KV slot 0
+        # static inputs; padded rows use the request table's spare row / write KV slot 0
+        self.pad_row = int(getattr(model_runner.req_to_token_pool, "pad_row", 0))
         self.input_ids = torch.zeros(n, dtype=torch.int64, device=dev)
-        self.req_pool_indices = torch.zeros(n, dtype=torch.int32, device=dev)
+        self.req_pool_indices = torch.full((n,), self.pad_row, dtype=torch.int32, device=dev)
         self.seq_lens = torch.ones(n, dtype=torch.int32, device=dev)
         self.out_cache_loc = torch.zeros(n, dtype=torch.int64, device=dev)
         self.positions = torch.zeros(n, dtype=torch.int64, device=dev)
@@ -114,7 +116,7 @@ class CudaGraphRunner:
         raw = fb.batch_size
         bs = self.batch_sizes[bisect.bisect_left(self.batch_sizes, raw)]
         if bs != raw:  # reset the padded tail
-            self.req_pool_indices[raw:bs].zero_()
+            self.req_pool_indices[raw:bs].fill_(self.pad_row)
             self.seq_lens[raw:bs].fill_(1)
             self.out_cache_loc[raw:bs].zero_()
             self.positions[raw:bs].zero_()

@@ -184,7 +184,8 @@ class ModelRunner:
             track = getattr(sc, "mamba_cache_slots", None)
             if track is None:
                 track = max(16, min(256, 4 * int(sc.max_running_requests or 1)))
-        self.gdn_pool = self.model.make_gdn_pool(self._num_req_slots(), int(track))
+        # one state row per request-table row, the spare padding row included
+        self.gdn_pool = self.model.make_gdn_pool(self._num_req_slots() + 1, int(track))
 
     def _num_req_slots(self) -> int:
         """Rows of the request table: the running batch plus a few spare rows for requests being prefilled

@@ -224,14 +224,20 @@ class GDNPool:
 
 
 class ReqToTokenPool:
-    """Request slot -> KV slot table (device) plus a host free list of request slots."""
+    """Request slot -> KV slot table (device) plus a host free list of request slots.
+
+    The table has one row more than ``max_reqs``: row ``pad_row`` is never handed out.  Batches padded
+    up to a captured CUDA-graph size point their extra rows at it, so kernels that keep per-request
+    state by request row (recurrent / convolution state of hybrid models) read and write a row no
+    request owns; its KV entries stay 0, the reserved sink slot of the KV pool."""
 
     def __init__(self, max_reqs: int, max_context_len: int, device: torch.device | str) -> None:
         self.size = int(max_reqs)
         self.max_context_len = int(max_context_len)
         self.device = torch.device(device)
+        self.pad_row = self.size
         self.req_to_token = torch.zeros(
-            (self.size, self.max_context_len), dtype=torch.int32, device=self.device
+            (self.size + 1, self.max_context_len), dtype=torch.int32, device=self.device
         )
         self.free_slots: List[int] = list(range(self.size))
 

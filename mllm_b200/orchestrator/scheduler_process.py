@@ -68,7 +68,10 @@ class Scheduler:
     # ------------------------------------------------------------------ intake
     def add_request(self, t: TokenizedGenerateReqInput) -> Optional[str]:
         """Queue a request. Returns an error string when it cannot be served at all."""
-        sp = SamplingParams.from_dict(t.sampling_params)
+        try:
+            sp = SamplingParams.from_dict(t.sampling_params)
+        except (ValueError, TypeError) as exc:      # a malformed request must not end the serving loop
+            return f"invalid sampling parameters: {exc}"
         ids = list(t.input_ids)
         if not ids:
             return "empty prompt"
@@ -82,6 +85,11 @@ class Scheduler:
         sp.max_new_tokens = max(0, min(sp.max_new_tokens, self.context_len - len(ids)))
         if len(ids) + 1 > self.mrp.runner.max_total_num_tokens:
             return f"prompt of {len(ids)} tokens exceeds the KV pool ({self.mrp.runner.max_total_num_tokens} tokens)"
+        # a request alone in the pool must be able to finish: prompt + output may not exceed the pool
+        # (whole pages, one page kept back for the rounding of the last one)
+        page = max(1, int(getattr(self.cfg, "radix_cache_page_size", 1) or 1))
+        room = self.mrp.runner.max_total_num_tokens - (len(ids) + page - 1) // page * page - (page if page > 1 else 0)
+        sp.max_new_tokens = max(1, min(sp.max_new_tokens, room)) if sp.max_new_tokens > 0 else 0
         if self.cfg.max_queued_requests is not None and len(self.waiting) >= self.cfg.max_queued_requests:
             return "queue full"
         bad = self._vision_inputs_error(ids, t.mm_inputs, len(ids) < len(t.input_ids))
@@ -313,15 +321,28 @@ class Scheduler:
                     keep.append(q)
             setattr(self, group_name, keep)
 
-    def _shed_load(self, why: str) -> Optional[BatchTokenIDOutput]:
-        """The pool ran dry mid-flight: retract the youngest running request back to the queue."""
+    def _shed_load(self, why: str, requeue_lone: bool = False) -> Optional[BatchTokenIDOutput]:
+        """The pool ran dry mid-flight: retract the youngest running request back to the queue.  A request
+        that holds the pool alone is ended instead (``requeue_lone`` queues it again all the same)."""
         logger.warning("KV allocation failed (%s); retracting a request", why)
         victims = self.prefilling or self.running
         if not victims:
             raise RuntimeError(why)
         q = victims[-1]
+        alone = len(self.prefilling) + len(self.running) == 1
         (self.prefilling if q in self.prefilling else self.running).remove(q)
+        if alone and not requeue_lone:
+            # nobody else holds KV: queueing it again would meet the same full pool for ever
+            q.finished_reason = "length"
+            q.finish_time = time.time()
+            self.mrp.release(q, cache=True)
+            self.stats.finished += 1
+            return self._collect_output([q])
         self.mrp.release(q, cache=True)
+        if q.mm_inputs:
+            # the whole prompt is prefilled again: pixels are needed again and positions start over
+            q.mm_inputs.pop("_consumed", None)
+            q.mrope_delta = int(q.mm_inputs.get("mrope_position_delta", 0))
         q.input_ids = q.all_ids()
         q.sampling.max_new_tokens = max(0, q.sampling.max_new_tokens - len(q.output_ids))
         retained, q.output_ids = q.output_ids, []
@@ -500,7 +521,11 @@ def scheduler_event_loop(sched: "Scheduler", recv, send, poller, rank: int = 0, 
                     send.send_pyobj(None)  # lets the detokenizer count this replica out
                 return
             if isinstance(msg, TokenizedGenerateReqInput):
-                err = sched.add_request(msg)
+                try:
+                    err = sched.add_request(msg)
+                except Exception as exc:  # every rank sees the same message, so every rank refuses it alike
+                    logger.exception("request %s refused at intake", getattr(msg, "rid", "?"))
+                    err = f"request refused: {type(exc).__name__}: {exc}"
                 if err is not None and rank == 0:
                     send.send_pyobj({"error": err, "rid": msg.rid})
             elif isinstance(msg, AbortReq):

@@ -26,10 +26,12 @@ def nvtx_range(name: str) -> Iterator[None]:
 
 @contextlib.contextmanager
 def torch_profiler(enabled: bool, activities: Iterable[str] = ("CPU", "GPU"), record_shapes: bool = False,
-                   output_dir: Optional[str] = None, filename_prefix: str = "mllm_b200", tag: str = "") -> Iterator[Optional[object]]:
+                   output_dir: Optional[str] = None, filename_prefix: str = "mllm_b200", tag: str = "",
+                   exported: Optional[list] = None) -> Iterator[Optional[object]]:
     """``with torch_profiler(True, ...) as prof:`` profiles the block and exports
-    ``<output_dir>/<prefix>_<tag>_<time>.trace.json.gz``.  ``"CUDA_PROFILER"`` in ``activities`` brackets the block
-    with cudaProfilerStart/Stop instead (for external tools)."""
+    ``<output_dir>/<prefix>_<tag>_<time>.trace.json.gz`` (the path is appended to ``exported`` when given).
+    ``"CUDA_PROFILER"`` in ``activities`` brackets the block with cudaProfilerStart/Stop instead (for
+    external tools)."""
     if not enabled:
         yield None
         return
@@ -56,3 +58,5 @@ def torch_profiler(enabled: bool, activities: Iterable[str] = ("CPU", "GPU"), re
     path = os.path.join(out_dir, name + ".trace.json.gz")
     prof.export_chrome_trace(path)
     prof.exported_path = path
+    if exported is not None:
+        exported.append(path)

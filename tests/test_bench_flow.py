@@ -48,7 +48,7 @@ def test_single_rank_line_has_the_contract_keys():
 
 def test_two_data_parallel_ranks_count_both_batches():
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", _free_port(), str(ROOT / "bench.py"), "--gpus", "2", *TINY]
+           "127.0.0.1", "--master-port", _free_port(), str(ROOT / "bench.py"), "--gpus", "2", "--parallelism", "dp", *TINY]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=_env(), cwd=ROOT)
     assert p.returncode == 0, p.stderr[-2000:]
     lines = [ln for ln in p.stdout.splitlines() if ln.startswith("{")]
@@ -73,7 +73,7 @@ def test_watchdog_ends_a_run_that_never_finishes():
 
 def test_two_tensor_parallel_ranks_share_one_batch():
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", _free_port(), str(ROOT / "bench.py"), "--gpus", "2", "--parallelism", "tp", *TINY]
+           "127.0.0.1", "--master-port", _free_port(), str(ROOT / "bench.py"), "--gpus", "2", *TINY]       # tensor parallelism is the default layout at N > 1
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=_env(), cwd=ROOT)
     assert p.returncode == 0, p.stderr[-2000:]
     out = _last_json(p.stdout)

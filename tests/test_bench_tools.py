@@ -45,6 +45,27 @@ def test_bench_one_batch_jsonl_schema(tmp_path):
     assert cfg.server.max_running_requests >= 2  # raised to cover the batch
 
 
+def test_bench_one_batch_profile_writes_a_trace_per_stage(tmp_path, monkeypatch):
+    """``--profile`` with the CPU activity: one trace file for the prefill, one for the decode window."""
+    import os
+
+    monkeypatch.setenv("MLLM_B200_PROFILE_DIR", str(tmp_path / "traces"))
+    cfg, args = bob.parse_args(["--server.model_path", "preset:qwen3-tiny", "--server.dtype", "float32",
+                                "--server.max_total_tokens", "2048", "--batch-size", "2", "--input-len", "16",
+                                "--output-len", "6", "--skip-warmup", "--profile", "--profile-activities", "CPU",
+                                "--profile-start-step", "1", "--profile-steps", "2",
+                                "--result-filename", str(tmp_path / "r.jsonl")])
+    rows = bob.run_benchmark(cfg, args)
+    traces = rows[0]["profile_traces"]
+    assert len(traces) == 2 and "_prefill_" in traces[0] and "_decode_" in traces[1]
+    assert all(os.path.getsize(t) > 0 for t in traces)
+    cfg, args = bob.parse_args(["--server.model_path", "preset:qwen3-tiny", "--server.dtype", "float32",
+                                "--server.max_total_tokens", "2048", "--batch-size", "1", "--input-len", "8",
+                                "--output-len", "3", "--skip-warmup", "--profile", "--profile-activities", "CPU",
+                                "--profile-stage", "decode", "--result-filename", str(tmp_path / "r2.jsonl")])
+    assert len(bob.run_benchmark(cfg, args)[0]["profile_traces"]) == 1
+
+
 def test_bench_one_batch_skips_oversize(tmp_path):
     cfg, args = bob.parse_args(["--server.model_path", "preset:qwen3-tiny", "--server.dtype", "float32",
                                 "--server.max_total_tokens", "64", "--batch-size", "8", "--input-len", "64", "--output-len", "4",

@@ -105,7 +105,8 @@ def test_hybrid_state_pool_is_allocated_before_the_kv_pool_is_sized():
         setattr(mr, name, (lambda o, n: lambda: (order.append(n), o())[1])(orig, name))
     mr.initialize()
     assert order == ["_init_state_pool", "init_memory_pool"]
-    assert mr.gdn_pool.slots == mr.req_to_token_pool.size == 3 + 8 and mr.gdn_pool.track_slots == 5
+    # one state row per request-table row, the spare padding row included
+    assert mr.gdn_pool.slots == mr.req_to_token_pool.size + 1 == 3 + 8 + 1 and mr.gdn_pool.track_slots == 5
 
 
 def test_fp8_kv_cache_halves_the_cache_and_stays_close():

@@ -477,3 +477,62 @@ def test_longest_prefix_first_policy():
     assert o_f == ["blocker", "cold", "hot"] and o_l == ["blocker", "hot", "cold"]
     assert {k: v[0] for k, v in d_f.items()} == {k: v[0] for k, v in d_l.items()}
     assert d_l["hot"][1] >= len(warm) - 1 and d_l["cold"][1] == 0
+
+
+def test_malformed_sampling_parameters_are_refused_not_raised():
+    """A bad sampling value is answered with an error string (the multi-process serving loop has no other
+    guard in front of the scheduler) and the next request is served."""
+    sched = build_scheduler(_cfg(), device="cpu")
+    assert "invalid sampling parameters" in sched.add_request(_req("bad", [1, 2, 3], top_p=0.0))
+    assert "invalid sampling parameters" in sched.add_request(_req("bad2", [1, 2, 3], top_k="many"))
+    assert sched.add_request(_req("good", [1, 2, 3])) is None
+    assert "good" in _drain(sched)
+
+
+def test_request_longer_than_the_pool_finishes_instead_of_cycling():
+    """prompt + max_new_tokens beyond the KV pool: the output is cut to what the pool can hold, and a request
+    that is alone in the pool when it runs dry ends with reason ``length`` instead of being queued again."""
+    sched = build_scheduler(_cfg(max_total_tokens=64, context_length=256, max_running_requests=2), device="cpu")
+    assert sched.add_request(_req("long", list(range(1, 31)), n=200)) is None
+    done = _drain(sched, limit=400)
+    assert "long" in done and done["long"][1] == "length"
+    assert 0 < len(done["long"][0]) <= 64 - 30
+    assert not sched.has_work()
+    # direct check of the last resort: a lone request that cannot get KV ends, with its tokens delivered
+    sched.add_request(_req("again", list(range(1, 21)), n=8))
+    sched.step()
+    out = sched._shed_load("test")
+    assert out is not None and out.rids == ["again"] and out.finished_reasons == ["length"]
+    assert not sched.has_work()
+
+
+def test_retracted_image_request_is_prefilled_with_its_pixels_again():
+    """An image request that is retracted mid-decode is prefilled again from its first token: the pixels must
+    go through the vision tower again, so the tokens equal those of an undisturbed run."""
+    import numpy as np
+
+    img = np.random.default_rng(1).integers(0, 256, (64, 64, 3), dtype=np.uint8)
+    sp = {"max_new_tokens": 6, "temperature": 0.0}
+
+    def run(retract: bool):
+        eng = Engine(_cfg(model_path="preset:qwen3-vl-tiny", context_length=256, max_running_requests=2,
+                          disable_radix_cache=True), mode="inproc", device="cpu").launch()
+        try:
+            sched = eng.scheduler
+            real_step, state = sched.step, {"did": False}
+
+            def step():
+                if retract and not state["did"] and sched.running and len(sched.running[0].output_ids) >= 3:
+                    state["did"] = True
+                    return sched._shed_load("test", requeue_lone=True)
+                return real_step()
+
+            sched.step = step
+            out = eng.generate("describe", sp, image_data=img, timeout=120)["output_ids"]
+            return out, state["did"]
+        finally:
+            eng.shutdown()
+
+    want, _ = run(False)
+    got, did = run(True)
+    assert did and len(want) == 6 and got == want
