@@ -49,6 +49,7 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--batch-size", type=int, default=8)
     ap.add_argument("--input-len", type=int, default=2048)
     ap.add_argument("--output-len", type=int, default=128)
+    ap.add_argument("--page-size", type=int, default=16, help="slots per KV page of our engine")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--parallelism", choices=["dp", "tp"], default="tp",
                     help="N > 1: tp = one batch sharded over N GPUs (fused NVLink kernels), dp = one replica and one batch per GPU")
@@ -214,8 +215,11 @@ def run_ours(a: argparse.Namespace) -> dict:
         sc.comm_backend = a.comm_backend
     sc.dp_size = replicas
     sc.max_running_requests = a.batch_size
-    sc.max_total_tokens = a.batch_size * (a.input_len + a.output_len) + 4096
+    sc.max_total_tokens = a.batch_size * (a.input_len + a.output_len + a.page_size) + 4096
     sc.context_length = a.input_len + a.output_len + 64
+    # pages of 16 slots: a request's tokens lie in runs of consecutive slots, which the decode-attention kernel
+    # fetches as whole boxes from the head-major KV pool
+    sc.radix_cache_page_size = a.page_size
     br = BenchRunner.create(cfg, device=None if on_gpu else "cpu")
     wd.log("model runner ready")
     dev = br.device
@@ -324,7 +328,7 @@ def run_ours(a: argparse.Namespace) -> dict:
         "impl": "ours", **({} if on_gpu else {"device": "cpu", "note": "host flow run: not a measurement"}),
         "config": {"model": a.model, "global_batch": replicas * bs, "per_gpu_batch": bs if not use_tp else None,
                    "seq_len": L, "output_len": out_len,
-                   "parallelism": layout, "cuda_graph_decode": graphs is not None,
+                   "parallelism": layout, "cuda_graph_decode": graphs is not None, "kv_page_size": a.page_size,
                    "l2_policy": "inputs larger than L2: every step streams the full weight set (>= 16 GB per replica) and the KV pool"},
         "prefill_tokens_per_s": replicas * bs * L / (prefill_med / 1e3),
         "decode_tokens_per_s": replicas * bs * (out_len - 1) / (decode_med / 1e3),

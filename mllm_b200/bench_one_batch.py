@@ -250,7 +250,7 @@ class BenchRunner:
         r.req_to_token_pool.clear()
         r.token_to_kv_pool_allocator.clear()
         self.slots, self.seq_len, self.batch = [], 0, 0
-        self._spare = None
+        self._own, self._used = None, 0
 
     def max_batch_size_for(self, input_len: int, output_len: int) -> int:
         return self.runner.max_total_num_tokens // max(1, input_len + output_len)
@@ -261,9 +261,16 @@ class BenchRunner:
         r = self.runner
         bs, L = input_ids.shape
         slots = r.req_to_token_pool.alloc(bs)
-        loc = r.token_to_kv_pool_allocator.alloc(bs * L)
-        if slots is None or loc is None:
+        # every request owns whole pages: its prompt starts a run of consecutive slots and what is left of its
+        # last page serves its first decode steps (with page size 1 this is one plain allocation)
+        page = getattr(r.token_to_kv_pool_allocator, "page_size", 1)
+        per_req = -(-L // page) * page
+        got = r.token_to_kv_pool_allocator.alloc(bs * per_req)
+        if slots is None or got is None:
             raise RuntimeError("bench batch does not fit the KV pool")
+        self._own = got.view(bs, per_req)
+        self._used = L
+        loc = self._own[:, :L].reshape(-1)
         self.slots, self.batch, self.seq_len = slots, bs, L
         self._slots_dev = torch.tensor(slots, dtype=torch.int32).to(self.device, non_blocking=True)
         r.req_to_token_pool.req_to_token[self._slots_dev.long(), :L] = loc.view(bs, L).to(torch.int32)
@@ -283,19 +290,13 @@ class BenchRunner:
         r = self.runner
         bs = self.batch
         page = getattr(r.token_to_kv_pool_allocator, "page_size", 1)
-        if page == 1:
-            loc = r.token_to_kv_pool_allocator.alloc(bs)
-        else:
-            # whole pages are granted; what a step does not use serves the next ones (nothing is freed before
-            # clear(), so the batch may share pages)
-            spare = getattr(self, "_spare", None)
-            if spare is None or spare.numel() < bs:
-                got = r.token_to_kv_pool_allocator.alloc(-(-bs // page) * page)
-                spare = got if (spare is None or got is None) else torch.cat([spare, got])
-            loc = None if spare is None else spare[:bs]
-            self._spare = None if spare is None else spare[bs:]
-        if loc is None:
-            raise RuntimeError("KV pool exhausted during decode")
+        if self._used == self._own.shape[1]:       # every request's last page is full: one more page each
+            more = r.token_to_kv_pool_allocator.alloc(bs * page)
+            if more is None:
+                raise RuntimeError("KV pool exhausted during decode")
+            self._own = torch.cat([self._own, more.view(bs, page)], dim=1)
+        loc = self._own[:, self._used].contiguous()
+        self._used += 1
         r.req_to_token_pool.req_to_token[self._slots_dev.long(), self.seq_len] = loc.to(torch.int32)
         self.seq_len += 1
         self._seq_lens += 1

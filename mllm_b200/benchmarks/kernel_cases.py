@@ -47,8 +47,9 @@ def _time(fn, iters: int, warm: int = 3) -> float:
 
 def _kv(batch, seq, hkv, dev):
     slots = batch * seq + 16
-    kc = torch.randn(slots, hkv, 128, device=dev, dtype=torch.bfloat16)
-    vc = torch.randn(slots, hkv, 128, device=dev, dtype=torch.bfloat16)
+    # stored head-major like the KV pool, handed out as [slots, kv heads, 128] views
+    kc = torch.randn(hkv, slots, 128, device=dev, dtype=torch.bfloat16).transpose(0, 1)
+    vc = torch.randn(hkv, slots, 128, device=dev, dtype=torch.bfloat16).transpose(0, 1)
     rtt = torch.zeros(batch, seq + 8, dtype=torch.int32, device=dev)
     rtt[:, :seq] = (torch.arange(batch * seq, device=dev, dtype=torch.int32) + 1).view(batch, seq)
     req = torch.arange(batch, dtype=torch.int32, device=dev)
@@ -97,14 +98,19 @@ def gemm(a) -> dict:
         ws = [ref.interleave_gate_up(w, ops.SWIGLU_BLOCK).contiguous() for w in ws]
     state = {"i": 0}
 
+    if a.param:
+        ws = [torch.nn.Parameter(w, requires_grad=False) for w in ws]
+
     def run():
         w = ws[state["i"] % copies]
         state["i"] += 1
+        if a.library:
+            return torch.matmul(x, w.t())
         return ops.linear_swiglu(x, w) if a.swiglu else ops.linear(x, w)
 
     ms = _time(run, a.iters)
     byts = (a.n * a.k + a.m * a.k + a.m * a.n) * 2
-    return {"case": "gemm", "m": a.m, "n": a.n, "k": a.k, "swiglu": a.swiglu, "ms": ms,
+    return {"case": "gemm", "m": a.m, "n": a.n, "k": a.k, "swiglu": a.swiglu, "library": a.library, "param": a.param, "ms": ms,
             "tflops": 2 * a.m * a.n * a.k / ms / 1e9, "gbs": byts / ms / 1e6}
 
 
@@ -160,6 +166,9 @@ def main() -> None:
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--swiglu", action="store_true")
+    ap.add_argument("--library", action="store_true",
+                    help="gemm: time the vendor library's GEMM (torch.matmul) on the same operands instead, for comparison")
+    ap.add_argument("--param", action="store_true", help="gemm: hold the weights in an nn.Parameter (model-weight path)")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--kv-sets", type=int, default=4, help="attn_decode: KV caches used in turn (working set > L2)")
     a = ap.parse_args()

@@ -54,6 +54,10 @@ struct AttnParams {
   int64_t q_stride;
   int64_t rtt_stride;
   int64_t num_slots;
+  int64_t kv_tok_stride, kv_head_stride;  // elements: row of head h of slot s at s * tok + h * head
+  // the caches seen as matrices of 128-wide rows: row of (slot, head) = slot * kv_row_mul + head * kv_row_add;
+  // kv_runs = 1 when consecutive slots of one head are consecutive rows (head-major storage)
+  int kv_row_mul, kv_row_add, kv_runs;
   int hq, hkv, group;
   int tokens_per_tile;     // query tokens per CTA tile = 128 / group (rounded down)
   int num_splits;          // decode only
@@ -206,7 +210,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const AttnPar
       const int r = (tid >> 4) + 8 * i;
       const int s = slots_next[i];
       const bool ok = s >= 0;
-      const int64_t off = (static_cast<int64_t>(ok ? s : 0) * p.hkv + hk) * kD + ch * 8;
+      const int64_t off = static_cast<int64_t>(ok ? s : 0) * p.kv_tok_stride + hk * p.kv_head_stride + ch * 8;
       const uint32_t so = swz_off(r, ch, kHalfKV);
       cp_async16(sk + so, kbase + off, ok);
       cp_async16(sv + so, vbase + off, ok);
@@ -423,16 +427,19 @@ __device__ __forceinline__ float m_used_at(const float (&m)[N], int idx) {
 // row sums stay per-thread until the end) and one feature d of the output, so the final store is
 // coalesced.  The CTA is warp-specialised and coupled by mbarriers only:
 //   warps 0-3  softmax: tcgen05.ld S^T, running max, exponentials, P^T to shared memory
-//   warps 4-7  gather:  slot-table reads and cp.async of K and V tiles into two three-deep rings
-//                       (tile t+2 and t+1 in flight while t is consumed: >= 128 KB per SM)
-//   warp  8    one thread issues the MMAs: S^T of tile t is queued before P*V of tile t-1, so the
+//   warp  4    producer: reads the request's slot table and moves K and V rows with the TMA engine into
+//              two three-deep rings, in the 128-byte-swizzled operand layout.  Groups of 16 tokens whose
+//              slots are consecutive (paged allocation, or a prompt that was given one run of slots) are
+//              plain 2 KB boxes when the pool is stored head-major; other groups are gathered row by row
+//              (cp.async.bulk.tensor ... tile::gather4: four pool rows, given by index, per copy).
+//   warp  5    one thread issues the MMAs: S^T of tile t is queued before P*V of tile t-1, so the
 //              tensor-core and barrier latency of S^T hides behind the softmax of the tile before
 // ---------------------------------------------------------------------------------------------
 constexpr int kDT = 128;                       // tokens per decode tile
 constexpr int kDecHalf = kDT * 128;            // bytes of one 64-feature half of a K or V tile
 constexpr int kDecTileBytes = 2 * kDecHalf;    // 32 KB per tensor
 constexpr int kDecBufs = 3;
-constexpr int kDecThreads = 288;
+constexpr int kDecThreads = 192;
 
 template <int NQ>
 struct DecCfg {
@@ -441,15 +448,25 @@ struct DecCfg {
   static constexpr int kSmem = kDecBufs * 2 * kDecTileBytes + kQBytes + kPBytes + 1024 + 256 + 9 * NQ * 4;
 };
 
-__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
-  // the barrier gets one arrival once all cp.async issued so far by this thread have landed
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+// Four rows of a 2-D tensor (row indices r[0..3], 64 16-bit columns starting at column x: one 128-byte
+// swizzle span per row) to four consecutive 128-byte rows of shared memory.  The tensor map's box is
+// {64, 1}; the copy signals 512 bytes on `bar`.  x * 2 bytes must be a multiple of 16.
+__device__ __forceinline__ void tma_gather4(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x,
+                                            const int (&r)[4]) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(r[0]),
+      "r"(r[1]), "r"(r[2]), "r"(r[3])
+      : "memory");
 }
 
 template <int NQ>
-__global__ void __launch_bounds__(kDecThreads, 1) attn_decode_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kDecThreads, 1)
+attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                   const __grid_constant__ CUtensorMap tm_k_run, const __grid_constant__ CUtensorMap tm_v_run,
+                   const AttnParams p) {
   using C = DecCfg<NQ>;
-  pdl_wait();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;                                   // kDecBufs tiles
@@ -457,7 +474,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) attn_decode_kernel(const AttnP
   uint8_t* sQ = sV + kDecBufs * kDecTileBytes;
   uint8_t* sP = sQ + C::kQBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + C::kPBytes);
-  uint64_t* k_full = bars;            // [3] 128 gather threads
+  uint64_t* k_full = bars;            // [3] TMA transaction bytes
   uint64_t* k_empty = bars + 3;       // [3] tcgen05.commit
   uint64_t* v_full = bars + 6;        // [3]
   uint64_t* v_empty = bars + 9;       // [3]
@@ -465,8 +482,9 @@ __global__ void __launch_bounds__(kDecThreads, 1) attn_decode_kernel(const AttnP
   uint64_t* s_empty = bars + 14;      // [2] 128 softmax threads
   uint64_t* p_full = bars + 16;       // 128 softmax threads
   uint64_t* p_empty = bars + 17;      // tcgen05.commit (P*V of the tile finished)
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 18);
-  int* fail_flag = reinterpret_cast<int*>(bars + 19);
+  uint64_t* q_full = bars + 18;       // producer warp: Q^T operand written
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 19);
+  int* fail_flag = reinterpret_cast<int*>(tmem_holder + 1);
   float* red = reinterpret_cast<float*>(bars + 20);     // [2][4 warps][NQ] tile maxima, double buffered
   float* red2 = red + 8 * NQ;                           // [NQ] totals
 
@@ -477,30 +495,12 @@ __global__ void __launch_bounds__(kDecThreads, 1) attn_decode_kernel(const AttnP
   const int hk = blockIdx.y;
   const int split = blockIdx.x;
   const int g = p.group;
-  const int req = p.req_pool_indices[b];
-  const int seq_len = p.seq_lens[b];
-  const int tiles = (seq_len + kDT - 1) / kDT;
-  const int per = (tiles + p.num_splits - 1) / p.num_splits;
-  const int kv_begin = split * per * kDT;
-  const int kv_end = min(seq_len, kv_begin + per * kDT);
-
-  if (kv_begin >= kv_end) {
-    if (p.num_splits > 1) {
-      for (int i = tid; i < g * kD; i += kDecThreads) {
-        const int head = hk * g + i / kD;
-        p.part_o[((static_cast<int64_t>(b) * p.hq + head) * p.num_splits + split) * kD + (i % kD)] = 0.f;
-      }
-      if (tid < g) p.part_lse[(static_cast<int64_t>(b) * p.hq + hk * g + tid) * p.num_splits + split] = -INFINITY;
-    }
-    return;
-  }
-  const int n_tiles = (kv_end - kv_begin + kDT - 1) / kDT;
 
   if (tid == 0) {
     for (int i = 0; i < 3; ++i) {
-      mbar_init(&k_full[i], 128);
+      mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], 1);
-      mbar_init(&v_full[i], 128);
+      mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -509,14 +509,19 @@ __global__ void __launch_bounds__(kDecThreads, 1) attn_decode_kernel(const AttnP
     }
     mbar_init(p_full, 128);
     mbar_init(p_empty, 1);
+    mbar_init(q_full, 1);
     *fail_flag = 0;
     fence_barrier_init();
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+    tma_prefetch_desc(&tm_k_run);
+    tma_prefetch_desc(&tm_v_run);
   }
   // rows of P^T beyond the group are never written again: clear them once
   for (int i = tid; i < C::kPBytes / 16; i += kDecThreads) reinterpret_cast<uint4*>(sP)[i] = make_uint4(0, 0, 0, 0);
   fence_proxy_async_smem();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == 5) {
     tmem_alloc(tmem_holder, 128);
     tmem_relinquish();
   }
@@ -526,79 +531,125 @@ __global__ void __launch_bounds__(kDecThreads, 1) attn_decode_kernel(const AttnP
   const uint32_t tmem_base = *tmem_holder;
   const uint32_t tmem_s = tmem_base;            // two buffers of NQ columns
   const uint32_t tmem_o = tmem_base + 2 * NQ;   // NQ columns
+  // everything above touched no global memory; sequence lengths, slot table, Q and the KV pool are
+  // written by earlier kernels of the stream
+  pdl_wait();
 
-  if (warp >= 4 && warp < 8) {
-    // =============================== gather warps ===============================
-    const int pt = tid - 128;
-    const uint16_t* qbase = static_cast<const uint16_t*>(p.q);
-    const uint16_t* kbase = static_cast<const uint16_t*>(p.k_cache);
-    const uint16_t* vbase = static_cast<const uint16_t*>(p.v_cache);
-    const int* rtt = p.req_to_token + static_cast<int64_t>(req) * p.rtt_stride;
-    const int ch = pt & 15;
-    {  // Q^T operand: NQ rows (query heads, zero beyond the group) x 16 chunks; lands with K tile 0
-      const uint32_t sq = smem_u32(sQ);
-      for (int c = pt; c < NQ * 16; c += 128) {
-        const int r = c >> 4, qc = c & 15;
-        const bool ok = r < g;
-        const uint16_t* src = qbase + static_cast<int64_t>(b) * p.q_stride +
-                              static_cast<int64_t>(hk * g + (ok ? r : 0)) * kD + qc * 8;
-        cp_async16(sq + swz_off(r, qc, NQ * 128), src, ok);
+  const int req = p.req_pool_indices[b];
+  const int seq_len = p.seq_lens[b];
+  const int tiles = (seq_len + kDT - 1) / kDT;
+  const int per = (tiles + p.num_splits - 1) / p.num_splits;
+  const int kv_begin = split * per * kDT;
+  const int kv_end = min(seq_len, kv_begin + per * kDT);
+  const int n_tiles = kv_begin < kv_end ? (kv_end - kv_begin + kDT - 1) / kDT : 0;
+
+  if (n_tiles == 0) {
+    // nothing to attend to: a neutral partial for the merge, or an all-zero output row
+    if (p.num_splits > 1) {
+      for (int i = tid; i < g * kD; i += kDecThreads) {
+        const int head = hk * g + i / kD;
+        p.part_o[((static_cast<int64_t>(b) * p.hq + head) * p.num_splits + split) * kD + (i % kD)] = 0.f;
       }
+      if (tid < g) p.part_lse[(static_cast<int64_t>(b) * p.hq + hk * g + tid) * p.num_splits + split] = -INFINITY;
+    } else {
+      for (int i = tid; i < g * kD; i += kDecThreads)
+        static_cast<uint16_t*>(p.out)[(static_cast<int64_t>(b) * p.hq + hk * g) * kD + i] = 0;
     }
-    auto load_slots = [&](int tile, int (&slots)[16]) {
-      const int t0 = kv_begin + tile * kDT;
+  } else if (warp == 4) {
+    // =============================== producer warp ===============================
+    {  // Q^T operand: NQ rows (query heads, zero beyond the group) x 16 chunks of 16 bytes
+      const uint16_t* qbase = static_cast<const uint16_t*>(p.q);
+      for (int c = lane; c < NQ * 16; c += 32) {
+        const int r = c >> 4, qc = c & 15;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < g)
+          v = *reinterpret_cast<const uint4*>(qbase + static_cast<int64_t>(b) * p.q_stride +
+                                              static_cast<int64_t>(hk * g + r) * kD + qc * 8);
+        *reinterpret_cast<uint4*>(sQ + swz_off(r, qc, NQ * 128)) = v;
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(q_full);
+    }
+    const int* rtt = p.req_to_token + static_cast<int64_t>(req) * p.rtt_stride;
+    bool ok_all = true, bad = false;
+    // A lane owns four consecutive tokens of the tile; the four lanes of a quad own a group of 16.  When the
+    // 16 slots of a group are consecutive and the storage is head-major, the group's K and V rows are four
+    // plain 2 KB boxes (K low / high feature half, V low / high) and each lane of the quad issues one of them;
+    // otherwise every lane gathers its own four rows, four at a time by index.
+    const int grp = lane >> 2, sub = lane & 3;
+    auto load_slots = [&](int tile, int (&sl4)[4]) {
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const int t = t0 + (pt >> 4) + 8 * i;
-        slots[i] = (tile < n_tiles && t < kv_end) ? __ldg(rtt + t) : -1;
+      for (int j = 0; j < 4; ++j) {
+        const int tk = min(kv_begin + tile * kDT + grp * 16 + sub * 4 + j, kv_end - 1);
+        sl4[j] = tile < n_tiles ? __ldg(rtt + tk) : 0;
       }
     };
-    int slots[16], next[16];
-    load_slots(0, slots);
-    bool ok_all = true, bad = false;
+    int cur[4], nxt[4];
+    load_slots(0, cur);
     for (int t = 0; t < n_tiles && ok_all; ++t) {
       const int sl = t % kDecBufs;
       const uint32_t ph = (t / kDecBufs) & 1;
-      load_slots(t + 1, next);  // consumed one tile from now: never waited for
-      int64_t off[16];
-      uint32_t so[16];
-      bool okv[16];
+      load_slots(t + 1, nxt);   // used one tile from now
+      bool run = p.kv_runs != 0;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        int s_id = slots[i];
-        if (s_id < -1 || s_id >= p.num_slots) {
+      for (int j = 0; j < 4; ++j) {
+        if (cur[j] < 0 || cur[j] >= p.num_slots) {
           bad = true;
-          s_id = -1;
+          cur[j] = 0;
         }
-        okv[i] = s_id >= 0;
-        off[i] = (static_cast<int64_t>(okv[i] ? s_id : 0) * p.hkv + hk) * kD + ch * 8;
-        so[i] = swz_off((pt >> 4) + 8 * i, ch, kDecHalf);
       }
-      if (!mbar_wait(&k_empty[sl], ph ^ 1)) ok_all = false;
-      const uint32_t dk = smem_u32(sK + sl * kDecTileBytes);
+      const int first = __shfl_sync(0xffffffffu, cur[0], lane & ~3);   // slot of the group's first token
 #pragma unroll
-      for (int i = 0; i < 16; ++i) cp_async16(dk + so[i], kbase + off[i], okv[i]);
-      cp_async_arrive_noinc(&k_full[sl]);
-      if (!mbar_wait(&v_empty[sl], ph ^ 1)) ok_all = false;
-      const uint32_t dv = smem_u32(sV + sl * kDecTileBytes);
+      for (int j = 0; j < 4; ++j) {
+        const int tk = kv_begin + t * kDT + grp * 16 + sub * 4 + j;
+        // tokens past the end repeat the last slot and are masked: they do not break a run
+        run = run && (tk >= kv_end || cur[j] == first + sub * 4 + j);
+      }
+      const uint32_t votes = __ballot_sync(0xffffffffu, run);
+      run = ((votes >> (lane & ~3)) & 0xFu) == 0xFu && first + 16 <= p.num_slots;
+      if (!mbar_wait(&k_empty[sl], ph ^ 1, fail_flag)) ok_all = false;
+      if (!mbar_wait(&v_empty[sl], ph ^ 1, fail_flag)) ok_all = false;
+      if (!__all_sync(0xffffffffu, ok_all)) {
+        ok_all = false;
+        break;
+      }
+      if (lane == 0) {
+        mbar_arrive_expect_tx(&k_full[sl], kDecTileBytes);
+        mbar_arrive_expect_tx(&v_full[sl], kDecTileBytes);
+      }
+      __syncwarp();
+      uint8_t* tile_k = sK + sl * kDecTileBytes;
+      uint8_t* tile_v = sV + sl * kDecTileBytes;
+      if (run) {
+        const int row0 = first * p.kv_row_mul + hk * p.kv_row_add;
+        const int half = sub & 1;
+        uint8_t* dst = (sub < 2 ? tile_k : tile_v) + half * kDecHalf + grp * 16 * 128;
+        tma_load_2d(dst, sub < 2 ? &tm_k_run : &tm_v_run, sub < 2 ? &k_full[sl] : &v_full[sl], half * 64, row0);
+      } else {
+        int rows[4];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) cp_async16(dv + so[i], vbase + off[i], okv[i]);
-      cp_async_arrive_noinc(&v_full[sl]);
+        for (int j = 0; j < 4; ++j) rows[j] = cur[j] * p.kv_row_mul + hk * p.kv_row_add;
+        const int off = (grp * 16 + sub * 4) * 128;
+        tma_gather4(tile_k + off, &tm_k, &k_full[sl], 0, rows);
+        tma_gather4(tile_k + kDecHalf + off, &tm_k, &k_full[sl], 64, rows);
+        tma_gather4(tile_v + off, &tm_v, &v_full[sl], 0, rows);
+        tma_gather4(tile_v + kDecHalf + off, &tm_v, &v_full[sl], 64, rows);
+      }
 #pragma unroll
-      for (int i = 0; i < 16; ++i) slots[i] = next[i];
+      for (int j = 0; j < 4; ++j) cur[j] = nxt[j];
     }
-    cp_async_wait<0>();
     if (bad && p.status != nullptr) atomicExch(p.status, kStatusBadIndex);
     if (!ok_all) *fail_flag = 1;
-  } else if (warp == 8) {
+  } else if (warp == 5) {
     // =============================== MMA issuer ===============================
     if (lane == 0) {
-      bool ok_all = true;
+      bool ok_all = mbar_wait(q_full, 0, fail_flag);
       auto issue_pv = [&](int u) {
         const int sl = u % kDecBufs;
-        if (!mbar_wait(&v_full[sl], (u / kDecBufs) & 1)) ok_all = false;
-        if (!mbar_wait(p_full, u & 1)) ok_all = false;
-        fence_proxy_async_smem();
+        if (!mbar_wait(&v_full[sl], (u / kDecBufs) & 1, fail_flag)) ok_all = false;
+        if (!mbar_wait(p_full, u & 1, fail_flag)) ok_all = false;
+        if (!ok_all) return;
         tc_fence_after_sync();
         const uint32_t va = smem_u32(sV + sl * kDecTileBytes);
         const uint32_t pa = smem_u32(sP);
@@ -613,9 +664,9 @@ __global__ void __launch_bounds__(kDecThreads, 1) attn_decode_kernel(const AttnP
       };
       for (int t = 0; t < n_tiles && ok_all; ++t) {
         const int sl = t % kDecBufs;
-        if (!mbar_wait(&k_full[sl], (t / kDecBufs) & 1)) ok_all = false;
-        if (!mbar_wait(&s_empty[t & 1], ((t >> 1) & 1) ^ 1)) ok_all = false;
-        fence_proxy_async_smem();
+        if (!mbar_wait(&k_full[sl], (t / kDecBufs) & 1, fail_flag)) ok_all = false;
+        if (!mbar_wait(&s_empty[t & 1], ((t >> 1) & 1) ^ 1, fail_flag)) ok_all = false;
+        if (!ok_all) break;
         tc_fence_after_sync();
         const uint32_t ka = smem_u32(sK + sl * kDecTileBytes);
         const uint32_t qa = smem_u32(sQ);
@@ -627,7 +678,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) attn_decode_kernel(const AttnP
         }
         umma_commit(&k_empty[sl]);
         umma_commit(&s_full[t & 1]);
-        if (t > 0 && ok_all) issue_pv(t - 1);
+        if (t > 0) issue_pv(t - 1);
       }
       if (ok_all) issue_pv(n_tiles - 1);
       if (!ok_all) *fail_flag = 1;
@@ -644,7 +695,10 @@ __global__ void __launch_bounds__(kDecThreads, 1) attn_decode_kernel(const AttnP
     }
     bool ok_all = true;
     for (int t = 0; t < n_tiles; ++t) {
-      if (!mbar_wait(&s_full[t & 1], (t >> 1) & 1)) ok_all = false;
+      if (!mbar_wait(&s_full[t & 1], (t >> 1) & 1, fail_flag)) {
+        ok_all = false;
+        break;
+      }
       tc_fence_after_sync();
       float sc[NQ];
       {
@@ -689,7 +743,10 @@ __global__ void __launch_bounds__(kDecThreads, 1) attn_decode_kernel(const AttnP
       }
       // P*V of the previous tile must be finished before P^T and O^T are touched again
       if (t > 0) {
-        if (!mbar_wait(p_empty, (t - 1) & 1)) ok_all = false;
+        if (!mbar_wait(p_empty, (t - 1) & 1, fail_flag)) {
+          ok_all = false;
+          break;
+        }
         tc_fence_after_sync();
       }
       if (need) {  // uniform over the four warps: every thread sees the same maxima
@@ -732,7 +789,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) attn_decode_kernel(const AttnP
       tc_fence_before_sync();
       mbar_arrive(p_full);
     }
-    if (!mbar_wait(p_empty, (n_tiles - 1) & 1)) ok_all = false;
+    if (ok_all && !mbar_wait(p_empty, (n_tiles - 1) & 1, fail_flag)) ok_all = false;
     tc_fence_after_sync();
     if (!ok_all) *fail_flag = 1;
 
@@ -784,8 +841,13 @@ __global__ void __launch_bounds__(kDecThreads, 1) attn_decode_kernel(const AttnP
 
   tc_fence_before_sync();
   __syncthreads();
-  if (*fail_flag && tid == 0 && p.status != nullptr) atomicExch(p.status, kStatusPipelineTimeout);
-  if (warp == 8) {
+  if (*fail_flag) {
+    if (tid == 0 && p.status != nullptr) atomicExch(p.status, kStatusPipelineTimeout);
+    // copies of the producer may still be in flight: give them time to land before the CTA's memory is reused
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 5) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 128);
   }
@@ -831,10 +893,21 @@ int decode_num_splits(int batch, int hkv, int max_seq_len, int num_sms) {
 }
 
 template <int NQ>
-int launch_decode_cfg(const AttnParams& p, dim3 grid, cudaStream_t s) {
+int launch_decode_cfg(const AttnParams& p, const AttnArgs& a, dim3 grid, cudaStream_t s) {
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(attn_decode_kernel<NQ>), DecCfg<NQ>::kSmem) != cudaSuccess)
     return -3;
-  const cudaError_t err = launch_pdl(attn_decode_kernel<NQ>, grid, dim3(kDecThreads), DecCfg<NQ>::kSmem, s, p);
+  // the K and V pools as 2-D tensors [slots * kv heads, 128] with one 64-column row per box: the form
+  // the gather copies take
+  CUtensorMap tm_k, tm_v, tm_k_run, tm_v_run;
+  const int type = a.dt == kF16 ? 1 : 0;
+  const int64_t rows = a.num_slots * static_cast<int64_t>(a.hkv);
+  if (rows >= (int64_t(1) << 31)) return -1;
+  if (!make_tma_operand_map(&tm_k, a.k_cache, rows, kD, kD, 2, type, 1)) return -2;
+  if (!make_tma_operand_map(&tm_v, a.v_cache, rows, kD, kD, 2, type, 1)) return -2;
+  if (!make_tma_operand_map(&tm_k_run, a.k_cache, rows, kD, kD, 2, type, 16)) return -2;
+  if (!make_tma_operand_map(&tm_v_run, a.v_cache, rows, kD, kD, 2, type, 16)) return -2;
+  const cudaError_t err = launch_pdl(attn_decode_kernel<NQ>, grid, dim3(kDecThreads), DecCfg<NQ>::kSmem, s, tm_k, tm_v,
+                                     tm_k_run, tm_v_run, p);
   note_launch();
   return err == cudaSuccess ? 0 : -4;
 }
@@ -861,6 +934,19 @@ int launch_attention(const AttnArgs& a, cudaStream_t s) {
   p.q_stride = a.q_stride;
   p.rtt_stride = a.rtt_stride;
   p.num_slots = a.num_slots;
+  p.kv_tok_stride = a.kv_tok_stride;
+  p.kv_head_stride = a.kv_head_stride;
+  if (a.kv_tok_stride == static_cast<int64_t>(a.hkv) * kD && a.kv_head_stride == kD) {
+    p.kv_row_mul = a.hkv;        // slot-major: rows of one slot are adjacent
+    p.kv_row_add = 1;
+    p.kv_runs = a.hkv == 1 ? 1 : 0;
+  } else if (a.kv_tok_stride == kD && a.kv_head_stride == a.num_slots * kD) {
+    p.kv_row_mul = 1;            // head-major: consecutive slots of a head are consecutive rows
+    p.kv_row_add = static_cast<int>(a.num_slots);
+    p.kv_runs = 1;
+  } else if (a.is_decode) {
+    return -1;                   // the decode kernel reads the caches through 2-D tensor maps
+  }
   p.hq = a.hq;
   p.hkv = a.hkv;
   p.group = g;
@@ -879,7 +965,7 @@ int launch_attention(const AttnArgs& a, cudaStream_t s) {
     p.idesc_s = umma_idesc(kRows, nq, 1, fmt, fmt, 0, 0);
     p.idesc_o = umma_idesc(kRows, nq, 1, fmt, fmt, 1, 0);
     grid = dim3(p.num_splits, a.hkv, a.batch);
-    const int rc = nq == 16 ? launch_decode_cfg<16>(p, grid, s) : launch_decode_cfg<32>(p, grid, s);
+    const int rc = nq == 16 ? launch_decode_cfg<16>(p, a, grid, s) : launch_decode_cfg<32>(p, a, grid, s);
     if (rc != 0) return rc;
     if (p.num_splits > 1) {
       launch_pdl(attn_merge_kernel, dim3(a.hq, a.batch), dim3(kD), 0, s, a.part_o, a.part_lse, a.out, a.hq, p.num_splits, p.out_f16);

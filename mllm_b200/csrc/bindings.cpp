@@ -119,6 +119,16 @@ void embedding(const Tensor& ids, const Tensor& table, Tensor& out) {
                           table.size(0), dtype_of(table), st.status.data_ptr<int>(), stream_of(table));
 }
 
+// K and V caches: [slots, kv heads, head_dim] views with unit stride along head_dim, equal strides for K and V
+// and 16-byte aligned rows; slot-major and head-major storage both qualify.
+static void check_kv_cache(const Tensor& k_cache, const Tensor& v_cache, at::ScalarType dt, int64_t hkv, int64_t head_dim) {
+  TORCH_CHECK(k_cache.dim() == 3 && v_cache.dim() == 3 && k_cache.sizes() == v_cache.sizes() &&
+                  k_cache.strides() == v_cache.strides() && k_cache.stride(2) == 1 && k_cache.size(1) == hkv &&
+                  k_cache.size(2) == head_dim && k_cache.stride(0) % 8 == 0 && k_cache.stride(1) % 8 == 0 &&
+                  k_cache.scalar_type() == dt && v_cache.scalar_type() == dt,
+              "kv cache: [slots, kv_heads, head_dim] views of the activation dtype with unit inner stride");
+}
+
 void qk_norm_rope_kv_write(Tensor& qkv, const c10::optional<Tensor>& q_w, const c10::optional<Tensor>& k_w,
                            const Tensor& positions, const c10::optional<Tensor>& axis_map, const Tensor& inv_freq,
                            const Tensor& cache_loc, Tensor& k_cache, Tensor& v_cache, int64_t hq, int64_t hkv,
@@ -130,8 +140,7 @@ void qk_norm_rope_kv_write(Tensor& qkv, const c10::optional<Tensor>& q_w, const 
   TORCH_CHECK(positions.scalar_type() == at::kLong && positions.is_contiguous(), "positions int64 contiguous");
   TORCH_CHECK(cache_loc.scalar_type() == at::kLong && cache_loc.is_contiguous(), "cache_loc int64 contiguous");
   TORCH_CHECK(inv_freq.scalar_type() == at::kFloat && inv_freq.numel() == head_dim / 2, "inv_freq fp32 [D/2]");
-  TORCH_CHECK(k_cache.is_contiguous() && v_cache.is_contiguous() && k_cache.scalar_type() == qkv.scalar_type(),
-              "kv cache must be contiguous and of the activation dtype");
+  check_kv_cache(k_cache, v_cache, qkv.scalar_type(), hkv, head_dim);
   const int tokens = qkv.size(0);
   const int pos_rows = positions.dim() == 2 ? positions.size(0) : 1;
   TORCH_CHECK(positions.numel() == static_cast<int64_t>(pos_rows) * tokens, "positions size");
@@ -141,7 +150,8 @@ void qk_norm_rope_kv_write(Tensor& qkv, const c10::optional<Tensor>& q_w, const 
   mb200::launch_qk_norm_rope_kv_write(
       qkv.data_ptr(), q_w.has_value() ? q_w->data_ptr() : nullptr, k_w.has_value() ? k_w->data_ptr() : nullptr,
       positions.data_ptr<int64_t>(), pos_rows, axis_map.has_value() ? axis_map->data_ptr<int8_t>() : nullptr,
-      inv_freq.data_ptr<float>(), cache_loc.data_ptr<int64_t>(), k_cache.data_ptr(), v_cache.data_ptr(), tokens, hq,
+      inv_freq.data_ptr<float>(), cache_loc.data_ptr<int64_t>(), k_cache.data_ptr(), v_cache.data_ptr(),
+      k_cache.stride(0), k_cache.stride(1), tokens, hq,
       hkv, head_dim, qkv.stride(0), k_cache.size(0), static_cast<float>(eps), dtype_of(qkv),
       st.status.data_ptr<int>(), stream_of(qkv));
 }
@@ -150,15 +160,17 @@ void kv_write(const Tensor& k, const Tensor& v, const Tensor& loc, Tensor& k_cac
   check_half(k, "k");
   TORCH_CHECK(loc.scalar_type() == at::kLong && loc.is_contiguous(), "loc int64 contiguous");
   const int tokens = loc.numel();
-  const int64_t row = k_cache.numel() / k_cache.size(0);
-  TORCH_CHECK(row % 8 == 0 && k.numel() == tokens * row && v.numel() == tokens * row, "kv_write: row size");
+  check_kv_cache(k_cache, v_cache, k.scalar_type(), k_cache.size(1), k_cache.size(2));
+  const int64_t row = k_cache.size(1) * k_cache.size(2);
+  TORCH_CHECK(k_cache.size(2) % 8 == 0 && k.numel() == tokens * row && v.numel() == tokens * row, "kv_write: row size");
   auto k2 = k.reshape({tokens, row});
   auto v2 = v.reshape({tokens, row});
   TORCH_CHECK(k2.stride(1) == 1 && v2.stride(1) == 1 && k2.stride(0) % 8 == 0 && v2.stride(0) % 8 == 0, "kv strides");
   c10::cuda::CUDAGuard g(k.device());
   auto& st = device_state(k.get_device());
   mb200::launch_kv_write(k2.data_ptr(), v2.data_ptr(), loc.data_ptr<int64_t>(), k_cache.data_ptr(),
-                         v_cache.data_ptr(), tokens, row, k2.stride(0), v2.stride(0), k_cache.size(0), dtype_of(k),
+                         v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1), k_cache.size(2), tokens, row,
+                         k2.stride(0), v2.stride(0), k_cache.size(0), dtype_of(k),
                          st.status.data_ptr<int>(), stream_of(k));
 }
 
@@ -467,7 +479,7 @@ struct TpFusion {
 
 int64_t gemm_impl(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<Tensor>& bias,
                   const c10::optional<Tensor>& residual, bool swiglu, const c10::optional<Tensor>& a_scale,
-                  const c10::optional<Tensor>& b_scale, const TpFusion* tp) {
+                  const c10::optional<Tensor>& b_scale, const TpFusion* tp, bool b_static = false) {
   check_cuda(a, "a");
   check_cuda(b, "b");
   const bool is_int8 = a.scalar_type() == at::kChar;
@@ -519,6 +531,7 @@ int64_t gemm_impl(const Tensor& a, const Tensor& b, Tensor& out, const c10::opti
   args.num_counters = st.counters.numel();
   args.status = st.status.data_ptr<int>();
   args.num_sms = st.num_sms;
+  args.b_static = b_static ? 1 : 0;
   if (tp != nullptr) {
     args.gate_flags = tp->gate_flags;
     args.gate_epoch = tp->gate_epoch;
@@ -536,10 +549,12 @@ int64_t gemm_impl(const Tensor& a, const Tensor& b, Tensor& out, const c10::opti
   return mb200::launch_gemm(args, stream_of(a));
 }
 
+// b_static: b holds model weights, which no kernel of the stream writes; the small-batch tiling may then
+// start streaming them before the kernels in front of this launch have finished.
 int64_t gemm(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<Tensor>& bias,
              const c10::optional<Tensor>& residual, bool swiglu, const c10::optional<Tensor>& a_scale,
-             const c10::optional<Tensor>& b_scale) {
-  return gemm_impl(a, b, out, bias, residual, swiglu, a_scale, b_scale, nullptr);
+             const c10::optional<Tensor>& b_scale, bool b_static) {
+  return gemm_impl(a, b, out, bias, residual, swiglu, a_scale, b_scale, nullptr, b_static);
 }
 
 // Tensor-parallel prefill GEMM.  gate_flags (uint32 as int32 tensor, one per 128-row tile of a) delays
@@ -613,7 +628,8 @@ void attention_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_c
   check_half(q, "q");
   TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.stride(2) == 1 && q.stride(1) == 128, "q must be [T,Hq,128]");
   TORCH_CHECK(out.is_contiguous() && out.sizes() == q.sizes() && out.scalar_type() == q.scalar_type(), "out");
-  TORCH_CHECK(k_cache.is_contiguous() && v_cache.is_contiguous() && k_cache.dim() == 3 && k_cache.size(2) == 128 &&
+  check_kv_cache(k_cache, v_cache, q.scalar_type(), k_cache.size(1), 128);
+  TORCH_CHECK(k_cache.dim() == 3 && k_cache.size(2) == 128 &&
                   k_cache.scalar_type() == q.scalar_type(),
               "kv cache [slots,Hkv,128] of q's dtype");
   for (const Tensor* t : {&req_to_token, &req_pool_indices, &seq_lens, &prefix_lens, &q_start})
@@ -625,6 +641,8 @@ void attention_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_c
   a.q = q.data_ptr();
   a.k_cache = k_cache.data_ptr();
   a.v_cache = v_cache.data_ptr();
+  a.kv_tok_stride = k_cache.stride(0);
+  a.kv_head_stride = k_cache.stride(1);
   a.out = out.data_ptr();
   a.req_to_token = req_to_token.data_ptr<int>();
   a.req_pool_indices = req_pool_indices.data_ptr<int>();
@@ -655,7 +673,8 @@ void attention_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
   check_half(q, "q");
   TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.stride(2) == 1 && q.stride(1) == 128, "q must be [B,Hq,128]");
   TORCH_CHECK(out.is_contiguous() && out.sizes() == q.sizes() && out.scalar_type() == q.scalar_type(), "out");
-  TORCH_CHECK(k_cache.is_contiguous() && v_cache.is_contiguous() && k_cache.dim() == 3 && k_cache.size(2) == 128 &&
+  check_kv_cache(k_cache, v_cache, q.scalar_type(), k_cache.size(1), 128);
+  TORCH_CHECK(k_cache.dim() == 3 && k_cache.size(2) == 128 &&
                   k_cache.scalar_type() == q.scalar_type(),
               "kv cache [slots,Hkv,128] of q's dtype");
   for (const Tensor* t : {&req_to_token, &req_pool_indices, &seq_lens})
@@ -679,6 +698,8 @@ void attention_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
   a.q = q.data_ptr();
   a.k_cache = k_cache.data_ptr();
   a.v_cache = v_cache.data_ptr();
+  a.kv_tok_stride = k_cache.stride(0);
+  a.kv_head_stride = k_cache.stride(1);
   a.out = out.data_ptr();
   a.req_to_token = req_to_token.data_ptr<int>();
   a.req_pool_indices = req_pool_indices.data_ptr<int>();

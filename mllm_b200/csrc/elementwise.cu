@@ -290,7 +290,8 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const T* __res
                                              int pos_rows, const int8_t* __restrict__ axis_map,
                                              const float* __restrict__ inv_freq,
                                              const int64_t* __restrict__ cache_loc, T* __restrict__ k_cache,
-                                             T* __restrict__ v_cache, int tokens, int hq, int hkv,
+                                             T* __restrict__ v_cache, int64_t kv_tok_stride,
+                                             int64_t kv_head_stride, int tokens, int hq, int hkv,
                                              int64_t qkv_stride, int64_t num_slots, float eps, int* status) {
   pdl_launch_dependents();
   pdl_wait();
@@ -346,16 +347,18 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const T* __res
     *reinterpret_cast<uint2*>(src) = raw;
   }
   if (is_k) {
-    *reinterpret_cast<uint2*>(k_cache + (slot * hkv + (h - hq)) * D + lane * 4) = raw;
+    *reinterpret_cast<uint2*>(k_cache + slot * kv_tok_stride + (h - hq) * kv_head_stride + lane * 4) = raw;
   } else if (!is_q) {
-    *reinterpret_cast<uint2*>(v_cache + (slot * hkv + (h - hq - hkv)) * D + lane * 4) = raw;
+    *reinterpret_cast<uint2*>(v_cache + slot * kv_tok_stride + (h - hq - hkv) * kv_head_stride + lane * 4) = raw;
   }
 }
 
-// rows of `row_elems` elements (a multiple of 8) copied to slot rows of both caches
+// rows of `row_elems` = heads x head_elems elements (head_elems a multiple of 8) copied to the slot rows of both
+// caches; a cache row of head h of slot s starts at s * kv_tok_stride + h * kv_head_stride
 template <typename T>
 __global__ void kv_write_kernel(const T* __restrict__ k, const T* __restrict__ v, const int64_t* __restrict__ loc,
-                                T* __restrict__ k_cache, T* __restrict__ v_cache, int tokens, int row_elems,
+                                T* __restrict__ k_cache, T* __restrict__ v_cache, int64_t kv_tok_stride,
+                                int64_t kv_head_stride, int head_elems, int tokens, int row_elems,
                                 int64_t k_stride, int64_t v_stride, int64_t num_slots, int* status) {
   pdl_launch_dependents();
   pdl_wait();
@@ -370,8 +373,10 @@ __global__ void kv_write_kernel(const T* __restrict__ k, const T* __restrict__ v
       if (status != nullptr) atomicExch(status, kStatusBadIndex);
       continue;
     }
-    reinterpret_cast<uint4*>(k_cache + slot * row_elems)[c] = reinterpret_cast<const uint4*>(k + t * k_stride)[c];
-    reinterpret_cast<uint4*>(v_cache + slot * row_elems)[c] = reinterpret_cast<const uint4*>(v + t * v_stride)[c];
+    const int head = (c << 3) / head_elems;
+    const int64_t dst = slot * kv_tok_stride + head * kv_head_stride + ((c << 3) - head * head_elems);
+    *reinterpret_cast<uint4*>(k_cache + dst) = reinterpret_cast<const uint4*>(k + t * k_stride)[c];
+    *reinterpret_cast<uint4*>(v_cache + dst) = reinterpret_cast<const uint4*>(v + t * v_stride)[c];
   }
 }
 
@@ -633,7 +638,8 @@ void launch_embedding(const int64_t* ids, const void* table, void* out, int toke
 
 void launch_qk_norm_rope_kv_write(void* qkv, const void* q_w, const void* k_w, const int64_t* positions,
                                   int pos_rows, const int8_t* axis_map, const float* inv_freq,
-                                  const int64_t* cache_loc, void* k_cache, void* v_cache, int tokens,
+                                  const int64_t* cache_loc, void* k_cache, void* v_cache, int64_t kv_tok_stride,
+                                  int64_t kv_head_stride, int tokens,
                                   int num_q_heads, int num_kv_heads, int head_dim, int64_t qkv_stride,
                                   int64_t num_slots, float eps, DType dt, int* status, cudaStream_t s) {
   if (tokens == 0 || head_dim != 128) return;
@@ -643,12 +649,13 @@ void launch_qk_norm_rope_kv_write(void* qkv, const void* q_w, const void* k_w, c
   MB200_DISPATCH_HALF(dt, (launch_pdl(qk_norm_rope_kv_write_kernel<T>, dim3(blocks), dim3(threads), 0, s, 
                               static_cast<T*>(qkv), static_cast<const T*>(q_w), static_cast<const T*>(k_w),
                               positions, pos_rows, axis_map, inv_freq, cache_loc, static_cast<T*>(k_cache),
-                              static_cast<T*>(v_cache), tokens, num_q_heads, num_kv_heads, qkv_stride, num_slots,
-                              eps, status)));
+                              static_cast<T*>(v_cache), kv_tok_stride, kv_head_stride, tokens, num_q_heads,
+                              num_kv_heads, qkv_stride, num_slots, eps, status)));
   note_launch();
 }
 
-void launch_kv_write(const void* k, const void* v, const int64_t* loc, void* k_cache, void* v_cache, int tokens,
+void launch_kv_write(const void* k, const void* v, const int64_t* loc, void* k_cache, void* v_cache,
+                     int64_t kv_tok_stride, int64_t kv_head_stride, int head_elems, int tokens,
                      int row_elems, int64_t k_stride, int64_t v_stride, int64_t num_slots, DType dt, int* status,
                      cudaStream_t s) {
   if (tokens == 0) return;
@@ -657,7 +664,8 @@ void launch_kv_write(const void* k, const void* v, const int64_t* loc, void* k_c
   const int blocks = static_cast<int>(std::min<int64_t>((total + threads - 1) / threads, 148 * 16));
   MB200_DISPATCH_HALF(dt, (launch_pdl(kv_write_kernel<T>, dim3(blocks), dim3(threads), 0, s, 
                               static_cast<const T*>(k), static_cast<const T*>(v), loc, static_cast<T*>(k_cache),
-                              static_cast<T*>(v_cache), tokens, row_elems, k_stride, v_stride, num_slots, status)));
+                              static_cast<T*>(v_cache), kv_tok_stride, kv_head_stride, head_elems, tokens, row_elems,
+                              k_stride, v_stride, num_slots, status)));
   note_launch();
 }
 

@@ -24,6 +24,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 #include "common.cuh"
@@ -54,6 +55,7 @@ struct KParams {
   int stages;            // ring depth in use (<= Cfg::kStages)
   int out_f16;           // 0: bf16 output, 1: fp16 output
   int is_int8;
+  int row_static;        // swap tiling: the row operand (weights) is not written by earlier kernels of the stream
   uint32_t idesc;
   // ---- tensor-parallel fusion (normal tiling only) ----
   // all-gather -> GEMM: row tile t of the activations may be read once gate_flags[t] >= gate_epoch
@@ -171,8 +173,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
-  // set-up above touched no global memory; from here on inputs of earlier kernels are read
-  pdl_wait();
+  // set-up above touched no global memory; from here on inputs of earlier kernels are read.  In the
+  // small-batch tiling the producer thread may first fill the ring with weight tiles, which no earlier
+  // kernel of the stream writes, and waits for its predecessors only before it loads activations: the
+  // weight stream then starts while the previous kernel is still draining.
+  const bool early_weights = SWAP && p.row_static != 0;
+  if (!(early_weights && threadIdx.x == 0)) pdl_wait();
 
   const int total_tiles = p.tiles_r * p.tiles_c;
   // swap tiling: this CTA's contiguous range of the (tile, k-block) iteration space
@@ -231,8 +237,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
     uint32_t phase = 0;
     bool ok = true;
     int tr, tc, kb0, kb1;
+    const int k_elems_per_block = p.is_int8 ? kRowBytes : kRowBytes / 2;
+    int early = 0;  // iterations whose weight tiles were issued ahead of the dependency wait
+    if constexpr (SWAP) {
+      if (early_weights) {
+        for (int idx = 0; early < n_stages && get_work(idx, tr, tc, kb0, kb1); ++idx) {
+          for (int kb = kb0; kb < kb1 && early < n_stages; ++kb, ++early) {
+            uint8_t* stage_base = smem + static_cast<size_t>(early) * C::kStageBytes;
+            mbar_arrive_expect_tx(&full_bar[early], C::kStageBytes);
+#pragma unroll
+            for (int kd = 0; kd < KD; ++kd)
+              tma_load_2d(stage_base + kd * C::kAtomBytes, &tm_row, &full_bar[early],
+                          (kb * KD + kd) * k_elems_per_block, tr * kBM * C::R);
+          }
+        }
+        pdl_wait();
+      }
+    }
+    int seen = 0;   // iterations handled so far by the loop below
     for (int idx = 0; ok && get_work(idx, tr, tc, kb0, kb1); ++idx) {
-      const int k_elems_per_block = p.is_int8 ? kRowBytes : kRowBytes / 2;
       if constexpr (!SWAP) {
         if (p.gate_flags != nullptr) {
           // rows of this tile are written by peers (generic proxy); the TMA engine reads them
@@ -244,19 +267,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
           fence_proxy_async_all();
         }
       }
-      for (int kb = kb0; kb < kb1; ++kb) {
-        if (*abort_flag || !mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
-          ok = false;
-          break;
-        }
+      for (int kb = kb0; kb < kb1; ++kb, ++seen) {
         uint8_t* stage_base = smem + static_cast<size_t>(stage) * C::kStageBytes;
-        mbar_arrive_expect_tx(&full_bar[stage], C::kStageBytes);
+        if (seen < early) {
+          // first pass over the ring: the stage is free and its weight tiles are already on their way
 #pragma unroll
-        for (int kd = 0; kd < KD; ++kd) {
-          uint8_t* row_tile = stage_base + kd * C::kAtomBytes;
-          const int x = (kb * KD + kd) * k_elems_per_block;
-          tma_load_2d(row_tile, &tm_row, &full_bar[stage], x, tr * kBM * C::R);
-          tma_load_2d(row_tile + C::kRowTileBytes, &tm_col, &full_bar[stage], x, tc * BN);
+          for (int kd = 0; kd < KD; ++kd)
+            tma_load_2d(stage_base + kd * C::kAtomBytes + C::kRowTileBytes, &tm_col, &full_bar[stage],
+                        (kb * KD + kd) * k_elems_per_block, tc * BN);
+        } else {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&full_bar[stage], C::kStageBytes);
+#pragma unroll
+          for (int kd = 0; kd < KD; ++kd) {
+            uint8_t* row_tile = stage_base + kd * C::kAtomBytes;
+            const int x = (kb * KD + kd) * k_elems_per_block;
+            tma_load_2d(row_tile, &tm_row, &full_bar[stage], x, tr * kBM * C::R);
+            tma_load_2d(row_tile + C::kRowTileBytes, &tm_col, &full_bar[stage], x, tc * BN);
+          }
         }
         if (++stage == n_stages) {
           stage = 0;
@@ -274,48 +305,56 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
     uint32_t phase = 0;
     bool ok = true;
     int tr, tc, kb0, kb1;
+    const uint64_t desc_stage0 = umma_desc_k_sw128(smem_u32(smem));
+    const uint32_t idesc = p.idesc;
     for (int idx = 0; ok && get_work(idx, tr, tc, kb0, kb1); ++idx) {
       const int acc = idx % C::kAccBufs;
       const uint32_t acc_phase = (idx / C::kAccBufs) & 1;
-      if (*abort_flag || !mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) {
+      if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) {
         ok = false;
         break;
       }
       tc_fence_after_sync();
       const uint32_t d_base = tmem_base + acc * C::kAccCols;
-      for (int kb = kb0; kb < kb1; ++kb) {
-        if (*abort_flag || !mbar_wait(&full_bar[stage], phase, abort_flag)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after_sync();
-        const uint32_t stage_addr = smem_u32(smem + static_cast<size_t>(stage) * C::kStageBytes);
+      // The issuing thread is a serial chain of its own: it must get through a k-block in fewer cycles than
+      // the tensor core needs for it, so the loop body is kept to the wait, the MMAs and the commit.  The
+      // descriptor of a stage is the descriptor of stage 0 plus a multiple of 16 bytes in its low word.
+      auto issue = [&](auto int8_tag) {
+        constexpr bool kInt8 = decltype(int8_tag)::value;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint64_t a_stage = desc_stage0 + static_cast<uint32_t>(stage) * (C::kStageBytes >> 4);
 #pragma unroll
-        for (int kd = 0; kd < KD; ++kd) {
-          const uint32_t row_addr = stage_addr + kd * C::kAtomBytes;
-          const uint64_t a_base = umma_desc_k_sw128(row_addr);
-          const uint64_t b_base = umma_desc_k_sw128(row_addr + C::kRowTileBytes);
+          for (int kd = 0; kd < KD; ++kd) {
 #pragma unroll
-          for (int r = 0; r < C::R; ++r) {
+            for (int r = 0; r < C::R; ++r) {
 #pragma unroll
-            for (int kk = 0; kk < kRowBytes / kUmmaKBytes; ++kk) {
-              // descriptors advance in 16-byte units inside the low word
-              const uint64_t a_desc = a_base + ((r * (kBM * kRowBytes) + kk * kUmmaKBytes) >> 4);
-              const uint64_t b_desc = b_base + ((kk * kUmmaKBytes) >> 4);
-              const uint32_t accum = (kb > kb0 || kd > 0 || kk > 0) ? 1u : 0u;
-              if (p.is_int8)
-                umma_i8(d_base + r * BN, a_desc, b_desc, p.idesc, accum);
-              else
-                umma_f16(d_base + r * BN, a_desc, b_desc, p.idesc, accum);
+              for (int kk = 0; kk < kRowBytes / kUmmaKBytes; ++kk) {
+                const uint64_t a_desc = a_stage + ((kd * C::kAtomBytes + r * (kBM * kRowBytes) + kk * kUmmaKBytes) >> 4);
+                const uint64_t b_desc = a_stage + ((kd * C::kAtomBytes + C::kRowTileBytes + kk * kUmmaKBytes) >> 4);
+                const uint32_t accum = (kd > 0 || kk > 0) ? 1u : (kb > kb0 ? 1u : 0u);
+                if constexpr (kInt8)
+                  umma_i8(d_base + r * BN, a_desc, b_desc, idesc, accum);
+                else
+                  umma_f16(d_base + r * BN, a_desc, b_desc, idesc, accum);
+              }
             }
           }
+          umma_commit(&empty_bar[stage]);  // stage reusable once these MMAs have read it
+          if (++stage == n_stages) {
+            stage = 0;
+            phase ^= 1;
+          }
         }
-        umma_commit(&empty_bar[stage]);  // stage reusable once these MMAs have read it
-        if (++stage == n_stages) {
-          stage = 0;
-          phase ^= 1;
-        }
-      }
+      };
+      if (p.is_int8)
+        issue(std::true_type{});
+      else
+        issue(std::false_type{});
       if (ok) umma_commit(&acc_full[acc]);
     }
     if (!ok) {
@@ -667,6 +706,347 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
   }
 }
 
+
+// =========================================================================================
+// Two-CTA tiling (large m): a cluster of two CTAs on neighbouring SMs computes one 256 x 256 output
+// tile with tcgen05.mma.cta_group::2.  Each CTA stages 128 activation rows (its half of the tile's M)
+// and 128 weight rows (its half of the tile's N) per 64-element k-block: 32 KB per CTA and k-block
+// instead of the 48 KB a lone CTA needs for its 128 x 256 tile, i.e. a third less traffic from L2 into
+// shared memory per FLOP, which is what bounds the one-CTA tiling.  The leader CTA (cluster rank 0)
+// issues the MMAs for the pair; the hardware reads the A rows and the B half of each CTA from that CTA's
+// shared memory and writes each CTA's 128 accumulator rows into that CTA's tensor memory.
+//   * TMA loads of both CTAs signal the LEADER's full barrier (cp.async.bulk.tensor ... cta_group::2
+//     with the barrier address mapped into the leader; no cluster multicast anywhere).
+//   * tcgen05.commit (cta_group::2) arrives on the empty / accumulator-full barriers of BOTH CTAs
+//     (two commits, one per CTA, each addressed through mapa).
+//   * epilogue warps of both CTAs arrive on the leader's accumulator-empty barrier (remote arrive).
+// Roles per CTA as in the one-CTA kernel: warp 0 TMA producer, warp 1 MMA issuer (leader only), warp 2
+// tensor-memory allocator, warps 4-7 epilogue.  All waits are bounded; a CTA that gives up raises its own
+// and its partner's abort flag.
+// =========================================================================================
+constexpr int kPairBN = 256;
+constexpr int kPairStageBytes = 2 * kBM * kRowBytes;            // A half-tile + B half-tile: 32 KB
+constexpr int kPairStages = 6;
+constexpr int kPairSmem = kPairStages * kPairStageBytes + 1024 + 512;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `local` (an address in this CTA's shared memory) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_smem(uint32_t local, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// TMA load whose completion bytes are counted on a barrier that may live in the partner CTA
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_out, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_out)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// all pair MMAs issued so far by this thread arrive on the barrier at `bar_cluster_addr` when they finish
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
+               : "memory");
+}
+
+template <bool SWIGLU>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_constant__ CUtensorMap tm_col,
+                 const KParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(kPairStages) * kPairStageBytes);
+  uint64_t* full_bar = bars;                       // used in the leader: 1 arrival + bytes of both CTAs
+  uint64_t* empty_bar = bars + kPairStages;        // per CTA: tcgen05.commit
+  uint64_t* acc_full = bars + 2 * kPairStages;     // per CTA: tcgen05.commit
+  uint64_t* acc_empty = acc_full + 2;              // used in the leader: 256 epilogue threads of the pair
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 256);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_row);
+    tma_prefetch_desc(&tm_col);
+  }
+  __syncthreads();
+  if (warp == 2) {
+    tmem_alloc_pair(tmem_holder, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  cluster_sync_all();   // both CTAs' barriers are initialised before either signals the other's
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+  pdl_wait();
+
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int total_tiles = p.tiles_r * p.tiles_c;   // tiles of 256 x 256
+  auto get_tile = [&](int idx, int& tr, int& tc) -> bool {
+    const int tile = pair + idx * num_pairs;
+    if (tile >= total_tiles) return false;
+    constexpr int kGroup = 8;  // 256-row tiles per raster group
+    const int per_group = kGroup * p.tiles_c;
+    const int g = tile / per_group;
+    const int first = g * kGroup;
+    const int gsize = min(p.tiles_r - first, kGroup);
+    const int in = tile - g * per_group;
+    tr = first + in % gsize;
+    tc = in / gsize;
+    return true;
+  };
+  auto give_up = [&](int code) {
+    *abort_flag = 1;
+    st_cluster_u32(mapa_smem(smem_u32(const_cast<int*>(abort_flag)), rank ^ 1u), 1u);
+    if (p.status != nullptr) atomicExch(p.status, code);
+  };
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    const int k_elems_per_block = p.is_int8 ? kRowBytes : kRowBytes / 2;
+    const uint32_t full_leader0 = mapa_smem(smem_u32(&full_bar[0]), 0);   // barriers are 8 bytes apart
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    int tr, tc;
+    for (int idx = 0; ok && get_tile(idx, tr, tc); ++idx) {
+      const int row0 = tr * 2 * kBM + static_cast<int>(rank) * kBM;       // this CTA's 128 activation rows
+      const int col0 = tc * kPairBN + static_cast<int>(rank) * (kPairBN / 2);  // this CTA's 128 weight rows
+      if (p.gate_flags != nullptr && row0 < p.m) {
+        if (!wait_flag_ge(p.gate_flags + (row0 >> 7), p.gate_epoch, p.status)) {
+          give_up(kStatusPeerTimeout);
+          ok = false;
+          break;
+        }
+        fence_proxy_async_all();
+      }
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+          ok = false;
+          break;
+        }
+        uint8_t* stage_base = smem + static_cast<size_t>(stage) * kPairStageBytes;
+        const uint32_t full_leader = full_leader0 + static_cast<uint32_t>(stage) * 8u;
+        if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * kPairStageBytes);
+        const int x = kb * k_elems_per_block;
+        tma_load_2d_pair(stage_base, &tm_row, full_leader, x, row0);
+        tma_load_2d_pair(stage_base + kBM * kRowBytes, &tm_col, full_leader, x, col0);
+        if (++stage == kPairStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+    if (!ok) give_up(kStatusPipelineTimeout);
+  } else if (warp == 1 && lane == 0 && leader) {
+    // ------------------------------ MMA issuer (leader CTA) -------------------------------
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    int tr, tc;
+    const uint64_t desc_stage0 = umma_desc_k_sw128(smem_u32(smem));
+    const uint32_t idesc = p.idesc;
+    const uint32_t empty0 = mapa_smem(smem_u32(&empty_bar[0]), 0), empty1 = mapa_smem(smem_u32(&empty_bar[0]), 1);
+    for (int idx = 0; ok && get_tile(idx, tr, tc); ++idx) {
+      const int acc = idx & 1;
+      const uint32_t acc_phase = (idx >> 1) & 1;
+      if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t d_base = tmem_base + acc * kPairBN;
+      auto issue = [&](auto int8_tag) {
+        constexpr bool kInt8 = decltype(int8_tag)::value;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint64_t a_stage = desc_stage0 + static_cast<uint32_t>(stage) * (kPairStageBytes >> 4);
+#pragma unroll
+          for (int kk = 0; kk < kRowBytes / kUmmaKBytes; ++kk) {
+            const uint64_t a_desc = a_stage + ((kk * kUmmaKBytes) >> 4);
+            const uint64_t b_desc = a_stage + ((kBM * kRowBytes + kk * kUmmaKBytes) >> 4);
+            const uint32_t accum = kk > 0 ? 1u : (kb > 0 ? 1u : 0u);
+            if constexpr (kInt8)
+              umma_i8_pair(d_base, a_desc, b_desc, idesc, accum);
+            else
+              umma_f16_pair(d_base, a_desc, b_desc, idesc, accum);
+          }
+          // the stage is reusable, in both CTAs, once these MMAs have read it
+          umma_commit_pair(empty0 + static_cast<uint32_t>(stage) * 8u);
+          umma_commit_pair(empty1 + static_cast<uint32_t>(stage) * 8u);
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      };
+      if (p.is_int8)
+        issue(std::true_type{});
+      else
+        issue(std::false_type{});
+      if (ok) {
+        umma_commit_pair(mapa_smem(smem_u32(&acc_full[acc]), 0));
+        umma_commit_pair(mapa_smem(smem_u32(&acc_full[acc]), 1));
+      }
+    }
+    if (!ok) give_up(kStatusPipelineTimeout);
+  } else if (warp >= 4) {
+    // ------------------------------ epilogue (both CTAs) ----------------------------------
+    const int ew = warp - 4;
+    const int row_in_tile = ew * 32 + lane;
+    bool ok = true;
+    int tr, tc;
+    constexpr int kOutCols = SWIGLU ? kPairBN / 2 : kPairBN;
+    const int n_out = SWIGLU ? p.n / 2 : p.n;
+    for (int idx = 0; ok && get_tile(idx, tr, tc); ++idx) {
+      const int acc = idx & 1;
+      const uint32_t acc_phase = (idx >> 1) & 1;
+      if (*abort_flag || !mbar_wait(&acc_full[acc], acc_phase, abort_flag)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t t_base = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + acc * kPairBN;
+      const int64_t row = static_cast<int64_t>(tr) * 2 * kBM + static_cast<int64_t>(rank) * kBM + row_in_tile;
+      const bool row_ok = row < p.m;
+      const int64_t col0 = static_cast<int64_t>(tc) * kOutCols;
+      const float sa = (p.is_int8 && row_ok) ? p.a_scale[row] : 1.f;
+#pragma unroll 1
+      for (int c = 0; c < kOutCols; c += 32) {
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32(t_base + c, r0);
+        if constexpr (SWIGLU) tmem_ld_32x32(t_base + kPairBN / 2 + c, r1);
+        tmem_ld_wait();
+        if (!row_ok) continue;
+#pragma unroll
+        for (int v8 = 0; v8 < 4; ++v8) {
+          const int64_t col = col0 + c + v8 * 8;
+          if (col >= n_out) break;
+          float f[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float x = acc_to_float(r0[v8 * 8 + j], p.is_int8);
+            if constexpr (SWIGLU) {
+              float u = acc_to_float(r1[v8 * 8 + j], p.is_int8);
+              if (p.is_int8) {
+                x *= sa * p.b_scale[tc * kPairBN + c + v8 * 8 + j];
+                u *= sa * p.b_scale[tc * kPairBN + kPairBN / 2 + c + v8 * 8 + j];
+              }
+              x = silu_f(x) * u;
+            } else {
+              if (p.is_int8) x *= sa * p.b_scale[col + j];
+              if (p.bias != nullptr) x += load_out1(p.bias, col + j, p.out_f16);
+            }
+            f[j] = x;
+          }
+          if (!SWIGLU && p.residual != nullptr) {
+            const uint4 rv = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.residual) +
+                                                             row * p.ld_res + col);
+            const uint32_t* ru = reinterpret_cast<const uint32_t*>(&rv);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float2 q;
+              if (p.out_f16) {
+                q = __half22float2(*reinterpret_cast<const __half2*>(&ru[j]));
+              } else {
+                q = unpack_bf16x2(ru[j]);
+              }
+              f[2 * j] += q.x;
+              f[2 * j + 1] += q.y;
+            }
+          }
+          uint4 o;
+          o.x = pack_out2(f[0], f[1], p.out_f16);
+          o.y = pack_out2(f[2], f[3], p.out_f16);
+          o.z = pack_out2(f[4], f[5], p.out_f16);
+          o.w = pack_out2(f[6], f[7], p.out_f16);
+          *reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + row * p.ldc + col) = o;
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive_cluster(mapa_smem(smem_u32(&acc_empty[acc]), 0));
+    }
+    if (!ok) give_up(kStatusPipelineTimeout);
+  }
+
+  pdl_launch_dependents();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    // give copies that may still be in flight time to land before the CTAs' memory is reused
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  // neither CTA may leave while its partner can still read its shared memory or signal its barriers
+  cluster_sync_all();
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------
@@ -733,6 +1113,29 @@ int launch_cfg(const CUtensorMap& tr, const CUtensorMap& tc, KParams p, int grid
   return err == cudaSuccess ? 0 : -4;
 }
 
+template <bool SWIGLU>
+int launch_pair_cfg(const CUtensorMap& tr, const CUtensorMap& tc, const KParams& p, int pairs, cudaStream_t s) {
+  auto kern = gemm_pair_kernel<SWIGLU>;
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kPairSmem) != cudaSuccess) return -3;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kPairSmem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  const cudaError_t err = cudaLaunchKernelEx(&cfg, kern, tr, tc, p);
+  note_launch();
+  return err == cudaSuccess ? 0 : -4;
+}
+
 }  // namespace
 
 bool make_tma_operand_map(void* map, const void* base, int64_t rows, int64_t k, int64_t ld, int elem_bytes, int type,
@@ -771,6 +1174,7 @@ int launch_gemm(const GemmArgs& a, cudaStream_t s) {
   p.ld_res = a.ld_res;
   p.out_f16 = (a.dt == kF16) ? 1 : 0;
   p.is_int8 = a.is_int8;
+  p.row_static = a.b_static;
   p.max_contrib = 1;
 
   const CUtensorMapDataType type =
@@ -800,6 +1204,19 @@ int launch_gemm(const GemmArgs& a, cudaStream_t s) {
   p.gate_flags = a.gate_flags;
   p.gate_epoch = a.gate_epoch;
   if (a.m > 256) {
+    // ---- two-CTA tiling: 256 x 256 tiles per pair of SMs, when there are enough of them to fill the GPU ----
+    static const int pair_knob = env_int("MLLM_B200_GEMM_PAIR", 1);
+    const int64_t tiles_pair = static_cast<int64_t>((a.m + 2 * kBM - 1) / (2 * kBM)) * ((a.n + kPairBN - 1) / kPairBN);
+    if (pair_knob && a.rs_tp == 0 && a.n % 256 == 0 && tiles_pair >= num_sms / 2) {
+      p.tiles_r = (a.m + 2 * kBM - 1) / (2 * kBM);
+      p.tiles_c = (a.n + kPairBN - 1) / kPairBN;
+      p.idesc = umma_idesc(2 * kBM, kPairBN, c_fmt, ab_fmt, ab_fmt);
+      if (!make_operand_map(&tm_row, a.a, a.m, a.k, a.lda, eb, type, kBM)) return -2;
+      if (!make_operand_map(&tm_col, a.b, a.n, a.k, a.ldb, eb, type, kPairBN / 2)) return -2;
+      const int pairs = static_cast<int>(std::min<int64_t>(tiles_pair, num_sms / 2));
+      return a.swiglu ? launch_pair_cfg<true>(tm_row, tm_col, p, pairs, s)
+                      : launch_pair_cfg<false>(tm_row, tm_col, p, pairs, s);
+    }
     // ---- normal tiling: activations are the 128-row operand ----
     int bn = 256;
     if (!a.swiglu) {

@@ -33,12 +33,17 @@ void launch_embedding(const int64_t* ids, const void* table, void* out, int toke
 // in place inside the fused qkv activation. head_dim is 128 or 64.
 // positions: [pos_rows, tokens] int64 with pos_rows 1 (plain RoPE) or 3 (M-RoPE: t,h,w);
 // axis_map[head_dim/2] selects the position row per frequency (null -> row 0).
+// The caches are addressed by strides (in elements): the row of head h of slot s starts at
+// s * kv_tok_stride + h * kv_head_stride, which covers both the slot-major [slots, heads, D] and the head-major
+// [heads, slots, D] layout.
 void launch_qk_norm_rope_kv_write(void* qkv, const void* q_w, const void* k_w, const int64_t* positions,
                                   int pos_rows, const int8_t* axis_map, const float* inv_freq,
-                                  const int64_t* cache_loc, void* k_cache, void* v_cache, int tokens,
+                                  const int64_t* cache_loc, void* k_cache, void* v_cache, int64_t kv_tok_stride,
+                                  int64_t kv_head_stride, int tokens,
                                   int num_q_heads, int num_kv_heads, int head_dim, int64_t qkv_stride,
                                   int64_t num_slots, float eps, DType dt, int* status, cudaStream_t s);
-void launch_kv_write(const void* k, const void* v, const int64_t* loc, void* k_cache, void* v_cache, int tokens,
+void launch_kv_write(const void* k, const void* v, const int64_t* loc, void* k_cache, void* v_cache,
+                     int64_t kv_tok_stride, int64_t kv_head_stride, int head_elems, int tokens,
                      int row_elems, int64_t k_stride, int64_t v_stride, int64_t num_slots, DType dt, int* status,
                      cudaStream_t s);
 
@@ -80,6 +85,7 @@ struct GemmArgs {
   int num_counters;
   int* status;           // device int, set non-zero when a bounded wait ran out
   int num_sms;
+  int b_static;          // 1: b (the weights) is not written by kernels that precede this launch in its stream
   // ---- tensor-parallel fusion, large-m tiling only (all zero = off) ----
   // all-gather -> GEMM: 128-row tile t of `a` is read only once gate_flags[t] >= gate_epoch
   const uint32_t* gate_flags;
@@ -152,8 +158,10 @@ int launch_moe_grouped_gemm(const MoeGemmArgs& args, cudaStream_t s);
 // ----- attention over the slot-indexed KV pool (tcgen05, head_dim 128) -----------------
 struct AttnArgs {
   const void* q;            // [T, Hq, 128], token stride q_stride elements
-  const void* k_cache;      // [slots, Hkv, 128]
+  const void* k_cache;      // row of head h of slot s at s * kv_tok_stride + h * kv_head_stride (elements)
   const void* v_cache;
+  int64_t kv_tok_stride;    // slot-major [slots, Hkv, 128]: Hkv * 128 and 128; head-major [Hkv, slots, 128]:
+  int64_t kv_head_stride;   // 128 and slots * 128 (consecutive slots of a head are then contiguous)
   void* out;                // [T, Hq, 128] contiguous
   float* part_o;            // decode with num_splits > 1: [B, Hq, splits, 128]
   float* part_lse;          // decode with num_splits > 1: [B, Hq, splits]

@@ -86,6 +86,8 @@ extern "C" int mllm_b200_attention_decode_noalloc(const void* q, const void* k_c
   a.q = q;
   a.k_cache = k_cache;
   a.v_cache = v_cache;
+  a.kv_tok_stride = static_cast<int64_t>(hkv) * head_dim;   // the documented slot-major layout
+  a.kv_head_stride = head_dim;
   a.out = out;
   a.part_o = splits > 1 ? pd->scratch : nullptr;
   a.part_lse = splits > 1 ? pd->scratch + static_cast<size_t>(batch) * hq * splits * 128 : nullptr;

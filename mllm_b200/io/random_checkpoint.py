@@ -22,12 +22,29 @@ def _randn(shape, gen, device, dtype, std):
 
 
 def write_random_checkpoint(preset: str, out_dir, seed: int = 0, std: float = 0.02,
-                            dtype: torch.dtype = torch.bfloat16, device: Optional[str] = None) -> Path:
+                            dtype: torch.dtype = torch.bfloat16, device: Optional[str] = None,
+                            tp_shard: int = 1) -> Path:
+    """``tp_shard = N > 1`` writes the checkpoint of ONE tensor-parallel rank of an N-way split of the dense
+    model, for runners that have no sharded loading of their own: ``config.json`` names the per-rank head
+    counts and intermediate size, q / k / v / gate / up have per-rank shapes, and o_proj / down_proj keep
+    their full input width so that a row-parallel layer can cut out its own slice."""
     from safetensors.torch import save_file
 
     out = Path(out_dir)
     out.mkdir(parents=True, exist_ok=True)
     cfg = preset_to_config_json(preset)
+    full_q = full_inter = None
+    if tp_shard > 1:
+        tcfg = cfg.get("text_config", cfg)
+        if tcfg.get("num_experts", 0):
+            raise ValueError("tp_shard is for dense models")
+        if tcfg["num_attention_heads"] % tp_shard or tcfg["intermediate_size"] % tp_shard:
+            raise ValueError(f"heads / intermediate size not divisible by {tp_shard}")
+        full_q = tcfg["num_attention_heads"] * tcfg["head_dim"]
+        full_inter = tcfg["intermediate_size"]
+        tcfg["num_attention_heads"] //= tp_shard
+        tcfg["num_key_value_heads"] = max(1, tcfg["num_key_value_heads"] // tp_shard)
+        tcfg["intermediate_size"] //= tp_shard
     done_marker = out / ".complete"
     if done_marker.exists():
         return out
@@ -60,7 +77,7 @@ def write_random_checkpoint(preset: str, out_dir, seed: int = 0, std: float = 0.
             p + "self_attn.q_proj.weight": _randn((hq * D, H), gen, dev, dtype, std),
             p + "self_attn.k_proj.weight": _randn((hkv * D, H), gen, dev, dtype, std),
             p + "self_attn.v_proj.weight": _randn((hkv * D, H), gen, dev, dtype, std),
-            p + "self_attn.o_proj.weight": _randn((H, hq * D), gen, dev, dtype, std),
+            p + "self_attn.o_proj.weight": _randn((H, full_q or hq * D), gen, dev, dtype, std),
             p + "self_attn.q_norm.weight": torch.ones(D, dtype=dtype),
             p + "self_attn.k_norm.weight": torch.ones(D, dtype=dtype),
             p + "input_layernorm.weight": torch.ones(H, dtype=dtype),
@@ -75,7 +92,7 @@ def write_random_checkpoint(preset: str, out_dir, seed: int = 0, std: float = 0.
         else:
             t[p + "mlp.gate_proj.weight"] = _randn((inter, H), gen, dev, dtype, std)
             t[p + "mlp.up_proj.weight"] = _randn((inter, H), gen, dev, dtype, std)
-            t[p + "mlp.down_proj.weight"] = _randn((H, inter), gen, dev, dtype, std)
+            t[p + "mlp.down_proj.weight"] = _randn((H, full_inter or inter), gen, dev, dtype, std)
         dump(f"model-layer-{i:03d}.safetensors", t)
     with open(out / "model.safetensors.index.json", "w") as f:
         json.dump({"metadata": {}, "weight_map": index}, f)

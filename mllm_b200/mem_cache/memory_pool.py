@@ -16,8 +16,13 @@ Three objects, with the roles of pymllm/mem_cache/memory_pool.py:23-415:
   per step.
 
 All K/V rows of all layers sit in ONE allocation laid out
-``[layer, k|v, slot, kv_head, head_dim]`` so that a kernel gets a layer's
-buffers as base pointer + offset and 180 GB of HBM is carved exactly once.
+``[layer, k|v, kv_head, slot, head_dim]`` (head-major), so that a kernel gets a layer's
+buffers as base pointer + strides and 180 GB of HBM is carved exactly once.  Head-major
+means that consecutive slots of one KV head are consecutive 256-byte rows: a page, or any
+run of slots a request was given in one piece, is one contiguous block per head, which the
+attention kernels fetch as whole TMA boxes instead of row by row.  ``get_kv_buffer``
+hands out ``[slot, kv_head, head_dim]`` *views* of that storage, so code that indexes the
+cache by slot does not see the difference.
 """
 
 from __future__ import annotations
@@ -56,10 +61,10 @@ class KVPool:
         self.dtype = dtype
         self.device = torch.device(device)
         self.store = torch.zeros(
-            (layer_num, 2, self.num_slots, kv_heads, head_dim), dtype=dtype, device=self.device
+            (layer_num, 2, kv_heads, self.num_slots, head_dim), dtype=dtype, device=self.device
         )
-        self.k_buffer: List[torch.Tensor] = [self.store[l, 0] for l in range(layer_num)]
-        self.v_buffer: List[torch.Tensor] = [self.store[l, 1] for l in range(layer_num)]
+        self.k_buffer: List[torch.Tensor] = [self.store[l, 0].transpose(0, 1) for l in range(layer_num)]
+        self.v_buffer: List[torch.Tensor] = [self.store[l, 1].transpose(0, 1) for l in range(layer_num)]
 
     @staticmethod
     def cell_bytes(layer_num: int, kv_heads: int, head_dim: int, dtype: torch.dtype) -> int:

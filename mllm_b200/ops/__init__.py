@@ -134,7 +134,8 @@ def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
 # GEMMs
 # --------------------------------------------------------------------------
 def _gemm(a, b, out, bias, residual, swiglu, a_scale, b_scale) -> None:
-    rc = ext().gemm(a, b, out, bias, residual, swiglu, a_scale, b_scale)
+    # a Parameter is a model weight: nothing in the stream writes it, so the kernel may fetch it early
+    rc = ext().gemm(a, b, out, bias, residual, swiglu, a_scale, b_scale, isinstance(b, torch.nn.Parameter))
     if rc != 0:
         raise RuntimeError(f"mllm_b200 gemm: unsupported shape or launch failure (code {rc}) for "
                            f"M={a.shape[0]} N={b.shape[0]} K={a.shape[1]}")

@@ -99,3 +99,75 @@ def test_large_scores_rescale():
     want = ref.attention_prefill(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], s["pre"], s["q_start"], 1.0)
     ops.check_status()
     assert _err(got, want) < 5e-2
+
+
+def _head_major(s, pattern: str, seed=0):
+    """The caches of ``s`` re-stored head-major ([kv heads, slots, D] storage, handed out as [slots, kv heads, D]
+    views, as the KV pool does) and the request table rewritten so that the requests' slots are runs of
+    consecutive slots (``runs``), runs of 16 with scattered pages (``pages``), or a mix where every other group
+    of 16 is scattered (``mixed``)."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    seq = s["seq"].tolist()
+    hkv = s["kc"].shape[1]
+    total = sum(-(-n // 16) * 16 for n in seq) + 64
+    kc = torch.randn(hkv, total, D, device=DEV, dtype=s["kc"].dtype).transpose(0, 1)
+    vc = torch.randn(hkv, total, D, device=DEV, dtype=s["kc"].dtype).transpose(0, 1)
+    rtt = torch.zeros_like(s["rtt"])
+    pages = torch.randperm((total - 16) // 16, generator=g) + 1     # page 0 unused
+    nxt = 0
+    for b, n in enumerate(seq):
+        np_ = -(-n // 16)
+        mine = pages[nxt:nxt + np_]
+        nxt += np_
+        if pattern == "runs":      # one run of consecutive pages per request
+            mine = torch.arange(np_) + 1 + sum(-(-m // 16) for m in seq[:b])
+        slots = (mine.view(-1, 1) * 16 + torch.arange(16).view(1, -1)).reshape(-1)[:n].clone()
+        if pattern == "mixed":
+            for gi in range(1, np_, 2):
+                lo, hi = gi * 16, min(n, gi * 16 + 16)
+                slots[lo:hi] = slots[lo:hi][torch.randperm(hi - lo, generator=g)]
+        rtt[s["req"][b], :n] = slots.to(DEV).int()
+    return dict(s, kc=kc, vc=vc, rtt=rtt)
+
+
+@pytest.mark.parametrize("pattern", ["runs", "pages", "mixed"])
+@pytest.mark.parametrize("seq_lens", [[1], [15], [16], [17], [129], [500], [2048], [1, 700, 64, 129], [3000] * 3])
+@pytest.mark.parametrize("hq,hkv", [(32, 8), (8, 1)])
+def test_decode_head_major_pool(pattern, seq_lens, hq, hkv):
+    """Decode over head-major storage: groups of 16 consecutive slots arrive as whole boxes, scattered groups row
+    by row; both must give the fp32 statement's result."""
+    s = _head_major(_setup(seq_lens, [x - 1 for x in seq_lens], hq, hkv, seed=1), pattern, seed=len(seq_lens))
+    assert s["kc"].stride(0) == D and (hkv == 1 or not s["kc"].is_contiguous())
+    scale = D ** -0.5
+    got = ops.attention_decode(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], scale, max_seq_len=max(seq_lens))
+    ops.check_status()
+    want = ref.attention_decode(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], scale)
+    assert _err(got, want) < 3e-2
+
+
+@pytest.mark.parametrize("seq_lens,prefix_lens", [([300], [0]), ([200, 130], [64, 1]), ([1000], [873])])
+def test_prefill_head_major_pool(seq_lens, prefix_lens):
+    s = _head_major(_setup(seq_lens, prefix_lens, 16, 8), "pages", seed=2)
+    scale = D ** -0.5
+    got = ops.attention_prefill(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], s["pre"], s["q_start"], scale,
+                                max_q_len=s["max_q"])
+    ops.check_status()
+    want = ref.attention_prefill(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], s["pre"], s["q_start"], scale)
+    assert _err(got, want) < 3e-2
+
+
+def test_kv_write_kernels_on_head_major_pool():
+    """The stand-alone KV write and the fused norm + rotary + write kernel address the caches by strides."""
+    from mllm_b200.mem_cache import KVPool
+
+    pool = KVPool(256, 1, 4, D, torch.bfloat16, DEV)
+    kc, vc = pool.get_kv_buffer(0)
+    assert kc.stride(0) == D and kc.stride(1) == pool.num_slots * D
+    torch.manual_seed(0)
+    k = torch.randn(37, 4, D, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(37, 4, D, device=DEV, dtype=torch.bfloat16)
+    loc = torch.randperm(255, device=DEV)[:37] + 1
+    ops.kv_write(k, v, loc, kc, vc)
+    ops.check_status()
+    assert torch.equal(kc[loc], k) and torch.equal(vc[loc], v)
+    assert torch.equal(pool.store[0, 0, 2, loc], k[:, 2])

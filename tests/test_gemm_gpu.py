@@ -86,3 +86,44 @@ def test_gemm_repeatable_splitk():
     b = ops.linear(x, w)
     ops.check_status()
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("m,n,k,dtype", [(2500, 4096, 1024, torch.float16), (4096, 2048, 4096, torch.bfloat16),
+                                         (16384, 1024, 512, torch.bfloat16)])
+def test_gemm_two_cta_tiles_bias_residual_ragged_rows(m, n, k, dtype):
+    """Shapes with enough 256 x 256 tiles for the two-CTA tiling; m = 2500 leaves a partial last row tile."""
+    torch.manual_seed(m + n)
+    x = torch.randn(m, k, device=DEV, dtype=dtype)
+    w = torch.randn(n, k, device=DEV, dtype=dtype) * (k ** -0.5)
+    b = torch.randn(n, device=DEV, dtype=dtype)
+    r = torch.randn(m, n, device=DEV, dtype=dtype)
+    got = ops.linear(x, w, bias=b, residual=r)
+    ops.check_status()
+    want = ref.linear(x, w, b, r, out_dtype=torch.float32)
+    assert _rel_err(got, want) < (2e-3 if dtype == torch.float16 else 6e-3)
+    got2 = ops.linear(x, w)
+    ops.check_status()
+    assert _rel_err(got2, ref.linear(x, w, out_dtype=torch.float32)) < 6e-3
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1024, 1024), (8, 6144, 4096), (8, 4096, 12288), (40, 2048, 1024), (200, 4096, 4096)])
+def test_gemm_small_batch_with_parameter_weights(m, n, k):
+    """Weights held in an ``nn.Parameter`` take the path that starts the weight stream ahead of the
+    stream-order wait; several launches back to back (each waits on the one before) must all be right."""
+    torch.manual_seed(m + n + k)
+    w = torch.nn.Parameter(torch.randn(n, k, device=DEV, dtype=torch.bfloat16) * (k ** -0.5), requires_grad=False)
+    xs = [torch.randn(m, k, device=DEV, dtype=torch.bfloat16) for _ in range(4)]
+    outs = [ops.linear(x, w) for x in xs]
+    ops.check_status()
+    for x, got in zip(xs, outs):
+        assert _rel_err(got, ref.linear(x, w.data, out_dtype=torch.float32)) < 6e-3
+    # a chain: each GEMM consumes the previous one's output, so an early start must still see it
+    w2 = torch.nn.Parameter(torch.randn(k, n, device=DEV, dtype=torch.bfloat16) * (n ** -0.5), requires_grad=False)
+    y = xs[0]
+    want = xs[0].float()
+    for _ in range(3):
+        y = ops.linear(ops.linear(y, w), w2)
+        want = ref.linear(ref.linear(want.bfloat16(), w.data, out_dtype=torch.float32).bfloat16(), w2.data,
+                          out_dtype=torch.float32)
+    ops.check_status()
+    assert _rel_err(y, want) < 3e-2

@@ -154,3 +154,39 @@ def test_moe_ep2_matches_single_rank_on_gpu(tmp_path):
     two = _launch(2, str(tmp_path / "moe2.pt"), "cuda", "bfloat16", 29626, dict(env, TP_TEST_EP="1"))
     assert (two - one).abs().max().item() < 0.2
     assert (two.argmax(-1) == one.argmax(-1)).float().mean().item() > 0.8
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_kernels_match_fp32_sums_on_n_gpus(world):
+    """The fused decode reduce and the fused prefill step (GEMM with reduce-scatter epilogue -> reduce + add +
+    RMSNorm + all-gather -> flag-gated consumer GEMM, three steps in a row, several tiles per CTA) on
+    ``world`` GPUs against fp32 sums of the same partial products, within the rounding of the 16-bit
+    partials.  Every rank is a child process; NVLS is off and the kernels use plain peer loads / stores."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
+        env.pop(k, None)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), "-m", "mllm_b200.benchmarks.tp_selftest",
+           "--rows", "8192", "--k-per-rank", "512", "--steps", "3", "--deadline-s", "150"]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=200, env=env, cwd=os.path.dirname(HERE))
+    assert p.returncode == 0, (p.stdout[-1500:], p.stderr[-3000:])
+    done = [ln for ln in p.stdout.splitlines() if '"stage": "canaries"' in ln]
+    assert len(done) == world, p.stdout[-2000:]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [4, 8])
+def test_tp_n_matches_tp1_tokens_on_gpu(tmp_path, world):
+    """Token equality of the tensor-parallel model on 4 and 8 GPUs against one GPU, on a prefill long enough for
+    the fused sequence-sharded path (1024 rows) and the decode steps after it."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = {"TP_TEST_PREFILL_LEN": "512", "TP_TEST_HEADS": "8"}
+    one = _launch(1, str(tmp_path / "tp1.pt"), "cuda", "bfloat16", 0, env)
+    many = _launch(world, str(tmp_path / "tpn.pt"), "cuda", "bfloat16", 0,
+                   dict(env, TP_TEST_EXPECT_FUSED_PREFILL="1"))
+    assert (many - one).abs().max().item() < 0.1
+    assert torch.equal(many.argmax(-1), one.argmax(-1))

@@ -97,7 +97,8 @@ def run(out_path: str, device: str, dtype_name: str) -> None:
         cfg = get_preset(preset, num_attention_heads=4, num_key_value_heads=int(os.environ.get("TP_TEST_KV_HEADS", "2")),
                          linear_num_key_heads=2, linear_num_value_heads=4, tie_word_embeddings=False)
     else:
-        cfg = get_preset(preset, num_attention_heads=4, num_key_value_heads=2, tie_word_embeddings=False)
+        heads = int(os.environ.get("TP_TEST_HEADS", "4"))
+        cfg = get_preset(preset, num_attention_heads=heads, num_key_value_heads=2, tie_word_embeddings=False)
     L = int(os.environ.get("TP_TEST_PREFILL_LEN", "9"))
     sc = ServerConfig(model_path=f"preset:{preset}", dtype=dtype_name, max_running_requests=4,
                       max_total_tokens=max(1024, 4 * L), chunked_prefill_size=max(2048, 2 * L),
