@@ -295,6 +295,19 @@ class BenchRunner:
             if more is None:
                 raise RuntimeError("KV pool exhausted during decode")
             self._own = torch.cat([self._own, more.view(bs, page)], dim=1)
+        graphs = r.cuda_graph_runner
+        if (graphs is not None and self.device.type == "cuda" and not getattr(r.model, "uses_mrope", False)
+                and graphs.captured_size_for(bs) == bs and last_ids.is_cuda and last_ids.dtype == torch.int64):
+            # one kernel does the step's bookkeeping (slot, request table, lengths, positions) and writes the
+            # inputs where the captured graph reads them; then the graph is replayed
+            from . import ops
+
+            ops.ext().decode_prepare(last_ids.contiguous(), self._slots_dev, self._own, self._used, self._seq_lens,
+                                     r.req_to_token_pool.req_to_token, graphs.input_ids, graphs.req_pool_indices,
+                                     graphs.seq_lens, graphs.out_cache_loc, graphs.positions)
+            self._used += 1
+            self.seq_len += 1
+            return graphs.replay_static(bs).next_token_ids
         loc = self._own[:, self._used].contiguous()
         self._used += 1
         r.req_to_token_pool.req_to_token[self._slots_dev.long(), self.seq_len] = loc.to(torch.int32)

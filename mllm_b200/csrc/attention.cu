@@ -557,20 +557,6 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     }
   } else if (warp == 4) {
     // =============================== producer warp ===============================
-    {  // Q^T operand: NQ rows (query heads, zero beyond the group) x 16 chunks of 16 bytes
-      const uint16_t* qbase = static_cast<const uint16_t*>(p.q);
-      for (int c = lane; c < NQ * 16; c += 32) {
-        const int r = c >> 4, qc = c & 15;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < g)
-          v = *reinterpret_cast<const uint4*>(qbase + static_cast<int64_t>(b) * p.q_stride +
-                                              static_cast<int64_t>(hk * g + r) * kD + qc * 8);
-        *reinterpret_cast<uint4*>(sQ + swz_off(r, qc, NQ * 128)) = v;
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(q_full);
-    }
     const int* rtt = p.req_to_token + static_cast<int64_t>(req) * p.rtt_stride;
     bool ok_all = true, bad = false;
     // A lane owns four consecutive tokens of the tile; the four lanes of a quad own a group of 16.  When the
@@ -635,6 +621,22 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         tma_gather4(tile_k + kDecHalf + off, &tm_k, &k_full[sl], 64, rows);
         tma_gather4(tile_v + off, &tm_v, &v_full[sl], 0, rows);
         tma_gather4(tile_v + kDecHalf + off, &tm_v, &v_full[sl], 64, rows);
+      }
+      if (t == 0) {   // the first K and V tiles are on their way: stage the Q^T operand meanwhile
+      {  // Q^T operand: NQ rows (query heads, zero beyond the group) x 16 chunks of 16 bytes
+        const uint16_t* qbase = static_cast<const uint16_t*>(p.q);
+        for (int c = lane; c < NQ * 16; c += 32) {
+          const int r = c >> 4, qc = c & 15;
+          uint4 v = make_uint4(0, 0, 0, 0);
+          if (r < g)
+            v = *reinterpret_cast<const uint4*>(qbase + static_cast<int64_t>(b) * p.q_stride +
+                                                static_cast<int64_t>(hk * g + r) * kD + qc * 8);
+          *reinterpret_cast<uint4*>(sQ + swz_off(r, qc, NQ * 128)) = v;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(q_full);
+      }
       }
 #pragma unroll
       for (int j = 0; j < 4; ++j) cur[j] = nxt[j];

@@ -174,6 +174,34 @@ void kv_write(const Tensor& k, const Tensor& v, const Tensor& loc, Tensor& k_cac
                          st.status.data_ptr<int>(), stream_of(k));
 }
 
+void decode_prepare(const Tensor& last_ids, const Tensor& req_rows, const Tensor& own, int64_t used, Tensor& seq_lens,
+                    Tensor& req_to_token, Tensor& g_input_ids, Tensor& g_req_rows, Tensor& g_seq_lens, Tensor& g_out_loc,
+                    Tensor& g_positions) {
+  check_cuda(last_ids, "last_ids");
+  const int64_t bs = last_ids.numel();
+  TORCH_CHECK(last_ids.scalar_type() == at::kLong && last_ids.is_contiguous(), "last_ids int64 contiguous");
+  TORCH_CHECK(req_rows.scalar_type() == at::kInt && req_rows.numel() == bs && req_rows.is_contiguous(), "req_rows int32 [bs]");
+  TORCH_CHECK(own.scalar_type() == at::kLong && own.dim() == 2 && own.size(0) == bs && own.stride(1) == 1 && used >= 0 &&
+                  used < own.size(1),
+              "own int64 [bs, cap] and 0 <= used < cap");
+  TORCH_CHECK(seq_lens.scalar_type() == at::kInt && seq_lens.numel() == bs && seq_lens.is_contiguous(), "seq_lens int32 [bs]");
+  TORCH_CHECK(req_to_token.scalar_type() == at::kInt && req_to_token.dim() == 2 && req_to_token.stride(1) == 1, "req_to_token");
+  TORCH_CHECK(g_input_ids.scalar_type() == at::kLong && g_out_loc.scalar_type() == at::kLong &&
+                  g_positions.scalar_type() == at::kLong && g_req_rows.scalar_type() == at::kInt &&
+                  g_seq_lens.scalar_type() == at::kInt,
+              "graph input buffers: int64 ids / slots / positions, int32 rows / lengths");
+  TORCH_CHECK(g_input_ids.numel() >= bs && g_req_rows.numel() >= bs && g_seq_lens.numel() >= bs && g_out_loc.numel() >= bs &&
+                  g_positions.numel() >= bs && g_input_ids.is_contiguous() && g_req_rows.is_contiguous() &&
+                  g_seq_lens.is_contiguous() && g_out_loc.is_contiguous() && g_positions.is_contiguous(),
+              "graph input buffers too small");
+  c10::cuda::CUDAGuard g(last_ids.device());
+  mb200::launch_decode_prepare(last_ids.data_ptr<int64_t>(), req_rows.data_ptr<int32_t>(), own.data_ptr<int64_t>(),
+                               own.stride(0), static_cast<int>(used), seq_lens.data_ptr<int32_t>(),
+                               req_to_token.data_ptr<int32_t>(), req_to_token.stride(0), g_input_ids.data_ptr<int64_t>(),
+                               g_req_rows.data_ptr<int32_t>(), g_seq_lens.data_ptr<int32_t>(), g_out_loc.data_ptr<int64_t>(),
+                               g_positions.data_ptr<int64_t>(), static_cast<int>(bs), stream_of(last_ids));
+}
+
 std::vector<Tensor> per_token_quant_int8(const Tensor& x) {
   check_half(x, "x");
   TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && x.size(1) % 16 == 0 && x.size(1) <= 32768, "quant: [M,K], K%16");
@@ -598,20 +626,90 @@ int64_t tp_rs_add_rmsnorm_ag(const Tensor& inbox, const Tensor& tile_flags, Tens
                   inbox.size(2) == residual_shard.size(1) && inbox.size(1) >= residual_shard.size(0) &&
                   inbox.scalar_type() == residual_shard.scalar_type() && weight.scalar_type() == residual_shard.scalar_type(),
               "tp_rs_add_rmsnorm_ag: inbox [tp, rows_cap, hidden], residual shard [rows, hidden]");
-  TORCH_CHECK(peer_hidden.size() == peer_gather_flags.size() && static_cast<int64_t>(peer_hidden.size()) == inbox.size(0) &&
-                  peer_hidden.size() <= 8,
+  // inbox [tp, ...]: one partial sum per rank, tile_flags tell when they are in; inbox [1, ...] with an empty
+  // tile_flags tensor: the rows are already complete (e.g. the output of the expert-parallel exchange)
+  const bool complete_rows = inbox.size(0) == 1 && tile_flags.numel() == 0;
+  TORCH_CHECK(peer_hidden.size() == peer_gather_flags.size() && peer_hidden.size() <= 8 &&
+                  (complete_rows || static_cast<int64_t>(peer_hidden.size()) == inbox.size(0)),
               "tp_rs_add_rmsnorm_ag: peer lists");
   TORCH_CHECK(tile_flags.scalar_type() == at::kInt && ag_count.scalar_type() == at::kInt &&
-                  ag_count.numel() * 128 >= residual_shard.size(0) && tile_flags.numel() * 16 >= residual_shard.size(0),
+                  ag_count.numel() * 128 >= residual_shard.size(0) &&
+                  (complete_rows || tile_flags.numel() * 16 >= residual_shard.size(0)),
               "tp_rs_add_rmsnorm_ag: flag blocks");
   c10::cuda::CUDAGuard g(residual_shard.device());
   auto& st = device_state(residual_shard.get_device());
   std::vector<uint64_t> h(peer_hidden.begin(), peer_hidden.end()), f(peer_gather_flags.begin(), peer_gather_flags.end());
   return mb200::launch_tp_rs_add_rmsnorm_ag(
-      inbox.data_ptr(), inbox.size(1), reinterpret_cast<const uint32_t*>(tile_flags.data_ptr<int>()),
+      inbox.data_ptr(), inbox.size(1),
+      complete_rows ? nullptr : reinterpret_cast<const uint32_t*>(tile_flags.data_ptr<int>()),
       residual_shard.data_ptr(), weight.data_ptr(), h.data(), f.data(), ag_count.data_ptr<int>(), residual_shard.size(0),
-      residual_shard.size(1), static_cast<int>(h.size()), static_cast<int>(rank), static_cast<uint32_t>(epoch),
+      residual_shard.size(1), static_cast<int>(h.size()), static_cast<int>(inbox.size(0)), static_cast<int>(rank),
+      static_cast<uint32_t>(epoch),
       static_cast<float>(eps), dtype_of(residual_shard), st.status.data_ptr<int>(), stream_of(residual_shard));
+}
+
+// ---- expert-parallel token exchange: every list holds one address per rank (index = rank) ----
+static mb200::EpA2AArgs ep_args(const std::vector<std::vector<int64_t>>& ptrs, int64_t rank, int64_t experts, int64_t hidden,
+                                int64_t cap_rows, int64_t epoch) {
+  TORCH_CHECK(ptrs.size() == 7, "ep: seven address lists (cnt_all, cnt_flags, recv_x, recv_meta, disp_flags, ret_y, ret_flags)");
+  const size_t ep = ptrs[0].size();
+  TORCH_CHECK(ep >= 1 && ep <= 8, "ep: 1..8 ranks");
+  mb200::EpA2AArgs a{};
+  a.ep = static_cast<int>(ep);
+  a.rank = static_cast<int>(rank);
+  a.experts = static_cast<int>(experts);
+  a.hidden = static_cast<int>(hidden);
+  a.cap_rows = static_cast<int>(cap_rows);
+  a.epoch = static_cast<uint32_t>(epoch);
+  uint64_t* dst[7] = {a.cnt_all, a.cnt_flags, a.recv_x, a.recv_meta, a.disp_flags, a.ret_y, a.ret_flags};
+  for (int k = 0; k < 7; ++k) {
+    TORCH_CHECK(ptrs[k].size() == ep, "ep: address lists of equal length");
+    for (size_t r = 0; r < ep; ++r) dst[k][r] = static_cast<uint64_t>(ptrs[k][r]);
+  }
+  return a;
+}
+
+int64_t ep_plan(const Tensor& topk_ids, std::vector<std::vector<int64_t>> ptrs, int64_t rank, int64_t experts, int64_t hidden,
+                int64_t cap_rows, int64_t epoch, int64_t bn, Tensor& pair_dst_rank, Tensor& pair_dst_row,
+                Tensor& expert_offsets, Tensor& work, Tensor& n_work, Tensor& recv_rows) {
+  check_cuda(topk_ids, "topk_ids");
+  TORCH_CHECK(topk_ids.scalar_type() == at::kInt && topk_ids.is_contiguous() && topk_ids.dim() == 2, "ep_plan: int32 [T,k] ids");
+  const int pairs = topk_ids.numel();
+  for (const Tensor* t : {&pair_dst_rank, &pair_dst_row, &expert_offsets, &work, &n_work, &recv_rows})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kInt && t->is_contiguous(), "ep_plan: int32 outputs");
+  const auto a = ep_args(ptrs, rank, experts, hidden, cap_rows, epoch);
+  TORCH_CHECK(pair_dst_rank.numel() >= pairs && pair_dst_row.numel() >= pairs &&
+                  expert_offsets.numel() >= experts / a.ep + 1 && work.dim() == 2 && work.size(1) == 2,
+              "ep_plan: output sizes");
+  c10::cuda::CUDAGuard g(topk_ids.device());
+  auto& st = device_state(topk_ids.get_device());
+  return mb200::launch_ep_plan(a, topk_ids.data_ptr<int>(), pairs, static_cast<int>(bn), pair_dst_rank.data_ptr<int>(),
+                               pair_dst_row.data_ptr<int>(), expert_offsets.data_ptr<int>(), work.data_ptr<int>(),
+                               n_work.data_ptr<int>(), static_cast<int>(work.size(0)), recv_rows.data_ptr<int>(),
+                               st.status.data_ptr<int>(), stream_of(topk_ids));
+}
+
+int64_t ep_dispatch(const Tensor& x, int64_t top_k, const Tensor& pair_dst_rank, const Tensor& pair_dst_row,
+                    std::vector<std::vector<int64_t>> ptrs, int64_t rank, int64_t experts, int64_t cap_rows, int64_t epoch,
+                    Tensor& done_count) {
+  check_half(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && x.size(1) % 8 == 0 && x.stride(0) % 8 == 0, "ep_dispatch: x [T, hidden]");
+  const int pairs = x.size(0) * top_k;
+  TORCH_CHECK(pair_dst_rank.numel() >= pairs && pair_dst_row.numel() >= pairs && done_count.scalar_type() == at::kInt,
+              "ep_dispatch: plan tensors");
+  const auto a = ep_args(ptrs, rank, experts, x.size(1), cap_rows, epoch);
+  c10::cuda::CUDAGuard g(x.device());
+  return mb200::launch_ep_dispatch(a, x.data_ptr(), x.stride(0), pairs, static_cast<int>(top_k), pair_dst_rank.data_ptr<int>(),
+                                   pair_dst_row.data_ptr<int>(), done_count.data_ptr<int>(), stream_of(x));
+}
+
+int64_t ep_return(const Tensor& ys, const Tensor& recv_rows, std::vector<std::vector<int64_t>> ptrs, int64_t rank,
+                  int64_t experts, int64_t epoch, Tensor& done_count) {
+  check_half(ys, "ys");
+  TORCH_CHECK(ys.dim() == 2 && ys.is_contiguous() && ys.size(1) % 8 == 0, "ep_return: ys [slab rows, hidden]");
+  const auto a = ep_args(ptrs, rank, experts, ys.size(1), ys.size(0), epoch);
+  c10::cuda::CUDAGuard g(ys.device());
+  return mb200::launch_ep_return(a, ys.data_ptr(), recv_rows.data_ptr<int>(), done_count.data_ptr<int>(), stream_of(ys));
 }
 
 int64_t tp_wait_flags(const Tensor& flags, int64_t n, int64_t epoch) {
@@ -763,6 +861,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("argmax", &argmax);
   m.def("sample", &sample);
   m.def("apply_penalties", &apply_penalties);
+  m.def("decode_prepare", &decode_prepare);
+  m.def("ep_plan", &ep_plan);
+  m.def("ep_dispatch", &ep_dispatch);
+  m.def("ep_return", &ep_return);
   m.def("gemm", &gemm);
   m.def("gemm_tp", &gemm_tp);
   m.def("w4a16_gemm", &w4a16_gemm);

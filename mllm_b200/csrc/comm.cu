@@ -163,7 +163,7 @@ template <typename T, int VPT>
 __global__ void tp_rs_add_rmsnorm_ag_kernel(const T* __restrict__ inbox, int64_t inbox_rows_cap,
                                             const uint32_t* __restrict__ tile_flags, T* __restrict__ residual,
                                             const T* __restrict__ weight, GatherPtrs peers, int* __restrict__ ag_count,
-                                            int rows, int hidden, int tp, int rank, uint32_t epoch, float eps,
+                                            int rows, int hidden, int tp, int n_src, int rank, uint32_t epoch, float eps,
                                             int* status) {
   __shared__ float red[2][33];
   __shared__ int wait_ok;
@@ -172,7 +172,9 @@ __global__ void tp_rs_add_rmsnorm_ag_kernel(const T* __restrict__ inbox, int64_t
   const int tile = row0 >> 7;
   if (threadIdx.x == 0) wait_ok = 1;
   __syncthreads();
-  if (threadIdx.x < tp) {
+  // n_src partial sums per row (tp for the reduce-scatter inbox; 1 when the rows arrive complete, e.g. from the
+  // expert-parallel exchange, and tile_flags is then null)
+  if (tile_flags != nullptr && threadIdx.x < n_src) {
     if (!wait_flag_ge(tile_flags + tile * kMaxTp + threadIdx.x, epoch, status)) {
       wait_ok = 0;
       if (status != nullptr) atomicExch(status, kStatusPeerTimeout);
@@ -201,7 +203,7 @@ __global__ void tp_rs_add_rmsnorm_ag_kernel(const T* __restrict__ inbox, int64_t
         float acc[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-        for (int r = 0; r < tp; ++r) {
+        for (int r = 0; r < n_src; ++r) {
           const uint4 raw =
               __ldcg(reinterpret_cast<const uint4*>(inbox + (static_cast<int64_t>(r) * inbox_rows_cap + row) * hidden) + v);
           float f[8];
@@ -277,7 +279,7 @@ __global__ void tp_wait_flags_kernel(const uint32_t* __restrict__ flags, int n, 
 int launch_tp_rs_add_rmsnorm_ag(const void* inbox, int64_t inbox_rows_cap, const uint32_t* tile_flags,
                                 void* residual_shard, const void* weight, const uint64_t* peer_hidden,
                                 const uint64_t* peer_gather_flags, int* ag_count, int rows, int hidden, int tp,
-                                int rank, uint32_t epoch, float eps, DType dt, int* status, cudaStream_t s) {
+                                int n_src, int rank, uint32_t epoch, float eps, DType dt, int* status, cudaStream_t s) {
   if (rows == 0) return 0;
   if (tp < 1 || tp > kMaxTp || hidden % 8 != 0 || hidden > 8 * 1024 * kVecPerThread || rows % 128 != 0 ||
       residual_shard == nullptr || weight == nullptr)
@@ -296,7 +298,7 @@ int launch_tp_rs_add_rmsnorm_ag(const void* inbox, int64_t inbox_rows_cap, const
 #define MB200_RS_LAUNCH(TT, V)                                                                                      \
   err = launch_pdl(tp_rs_add_rmsnorm_ag_kernel<TT, V>, grid, block, 0, s, static_cast<const TT*>(inbox), inbox_rows_cap, \
                    tile_flags, static_cast<TT*>(residual_shard), static_cast<const TT*>(weight), gp, ag_count, rows,   \
-                   hidden, tp, rank, epoch, eps, status)
+                   hidden, tp, n_src, rank, epoch, eps, status)
   if (dt == kBF16) {
     if (vpt == 1) MB200_RS_LAUNCH(__nv_bfloat16, 1);
     else if (vpt == 2) MB200_RS_LAUNCH(__nv_bfloat16, 2);

@@ -636,6 +636,43 @@ void launch_embedding(const int64_t* ids, const void* table, void* out, int toke
   note_launch();
 }
 
+// One decode step's bookkeeping for a static batch in a single launch: request b takes KV slot
+// own[b, used] for its next token, the slot is entered into the request table at position seq_lens[b], the
+// length grows by one, and the step's inputs (token ids, request rows, lengths, slots, positions) are written
+// where the captured decode graph reads them.
+__global__ void decode_prepare_kernel(const int64_t* __restrict__ last_ids, const int32_t* __restrict__ req_rows,
+                                      const int64_t* __restrict__ own, int64_t own_stride, int used,
+                                      int32_t* __restrict__ seq_lens, int32_t* __restrict__ req_to_token,
+                                      int64_t rtt_stride, int64_t* __restrict__ g_input_ids,
+                                      int32_t* __restrict__ g_req_rows, int32_t* __restrict__ g_seq_lens,
+                                      int64_t* __restrict__ g_out_loc, int64_t* __restrict__ g_positions, int batch) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= batch) return;
+  const int64_t slot = own[b * own_stride + used];
+  const int32_t len = seq_lens[b];          // tokens so far; the new token's position
+  const int32_t row = req_rows[b];
+  req_to_token[row * rtt_stride + len] = static_cast<int32_t>(slot);
+  seq_lens[b] = len + 1;
+  g_input_ids[b] = last_ids[b];
+  g_req_rows[b] = row;
+  g_seq_lens[b] = len + 1;
+  g_out_loc[b] = slot;
+  g_positions[b] = len;
+}
+
+void launch_decode_prepare(const int64_t* last_ids, const int32_t* req_rows, const int64_t* own, int64_t own_stride,
+                           int used, int32_t* seq_lens, int32_t* req_to_token, int64_t rtt_stride,
+                           int64_t* g_input_ids, int32_t* g_req_rows, int32_t* g_seq_lens, int64_t* g_out_loc,
+                           int64_t* g_positions, int batch, cudaStream_t s) {
+  if (batch <= 0) return;
+  launch_pdl(decode_prepare_kernel, dim3((batch + 127) / 128), dim3(128), 0, s, last_ids, req_rows, own, own_stride,
+             used, seq_lens, req_to_token, rtt_stride, g_input_ids, g_req_rows, g_seq_lens, g_out_loc, g_positions,
+             batch);
+  note_launch();
+}
+
 void launch_qk_norm_rope_kv_write(void* qkv, const void* q_w, const void* k_w, const int64_t* positions,
                                   int pos_rows, const int8_t* axis_map, const float* inv_freq,
                                   const int64_t* cache_loc, void* k_cache, void* v_cache, int64_t kv_tok_stride,

@@ -56,6 +56,8 @@ struct KParams {
   int out_f16;           // 0: bf16 output, 1: fp16 output
   int is_int8;
   int row_static;        // swap tiling: the row operand (weights) is not written by earlier kernels of the stream
+  int cluster_k;         // swap tiling: > 1 = the k range of a tile is split over the CTAs of a cluster of this size
+  int early_trigger;     // swap tiling: let the kernels behind this one start their set-up as soon as this one runs
   uint32_t idesc;
   // ---- tensor-parallel fusion (normal tiling only) ----
   // all-gather -> GEMM: row tile t of the activations may be read once gate_flags[t] >= gate_epoch
@@ -101,6 +103,33 @@ struct Cfg {
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "invalid MMA N");
 };
 
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `local` (an address in this CTA's shared memory) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_smem(uint32_t local, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_cluster_v4f(uint32_t cluster_addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+__device__ __forceinline__ void fence_acq_rel_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
+
 __device__ __forceinline__ float silu_f(float v) { return v / (1.f + __expf(-v)); }
 
 __device__ __forceinline__ uint32_t pack_out2(float lo, float hi, int out_f16) {
@@ -145,6 +174,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   int* ticket_slot = const_cast<int*>(abort_flag) + 1;
   uint8_t* epi_staging = reinterpret_cast<uint8_t*>(bars) + 512;  // normal tiling only
+  // small-batch tiling with the k range split over a cluster: the leader's inbox for its partners' fp32
+  // partial sums, [partner][row of the tile][BN], and the barrier the partners arrive on
+  float* red_buf = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 512);
+  uint64_t* red_bar = acc_empty + 6;   // first free 8-byte slot behind tmem_holder / abort_flag / ticket_slot
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -160,6 +193,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
     }
     *rs_stored = 0;
     *abort_flag = 0;
+    if (SWAP && p.cluster_k > 1) mbar_init(red_bar, (p.cluster_k - 1) * 128);
     fence_barrier_init();
     tma_prefetch_desc(&tm_row);
     tma_prefetch_desc(&tm_col);
@@ -170,7 +204,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
     tmem_relinquish();
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if (SWAP && p.cluster_k > 1)
+    cluster_sync_all();   // the leader's inbox barrier exists before any partner can reach it
+  else
+    __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
   // set-up above touched no global memory; from here on inputs of earlier kernels are read.  In the
@@ -178,6 +215,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
   // kernel of the stream writes, and waits for its predecessors only before it loads activations: the
   // weight stream then starts while the previous kernel is still draining.
   const bool early_weights = SWAP && p.row_static != 0;
+  if (SWAP && p.early_trigger) pdl_launch_dependents();
   if (!(early_weights && threadIdx.x == 0)) pdl_wait();
 
   const int total_tiles = p.tiles_r * p.tiles_c;
@@ -195,6 +233,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
   // idx-th piece of work of this CTA -> (row tile, column tile, k-block range); false when done
   auto get_work = [&](int idx, int& tr, int& tc, int& kb0, int& kb1) -> bool {
     if constexpr (SWAP) {
+      if (p.cluster_k > 1) {
+        // one tile per cluster, one slice of its k range per CTA of the cluster
+        if (idx > 0) return false;
+        const int r = static_cast<int>(blockIdx.x) % p.cluster_k;
+        tr = static_cast<int>(blockIdx.x) / p.cluster_k;
+        tc = 0;
+        kb0 = p.k_blocks * r / p.cluster_k;
+        kb1 = p.k_blocks * (r + 1) / p.cluster_k;
+        return true;
+      }
       int64_t it = it_begin;
       for (int i = 0;; ++i) {
         if (it >= it_end) return false;
@@ -548,7 +596,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
         const int64_t nrow0 = static_cast<int64_t>(tr) * kBM * C::R;  // first weight row of the tile
         const int m_cols = min(p.m, BN);
         const bool whole_tile = (kb0 == 0 && kb1 == p.k_blocks);
-        if (!whole_tile) {
+        const int crank = p.cluster_k > 1 ? static_cast<int>(blockIdx.x) % p.cluster_k : 0;
+        if (p.cluster_k > 1 && crank != 0) {
+          // partner of a cluster: the fp32 partial sums go straight into the leader's shared memory
+          constexpr int kTileRows = kBM * C::R;
+          const uint32_t inbox = mapa_smem(smem_u32(red_buf), 0) +
+                                 static_cast<uint32_t>(crank - 1) * (kTileRows * BN * 4);
+#pragma unroll 1
+          for (int r = 0; r < C::R; ++r) {
+            const uint32_t row_addr = inbox + static_cast<uint32_t>(r * kBM + row_in_tile) * (BN * 4);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+              uint32_t v[16];
+              tmem_ld_32x16(t_base + r * BN + c, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 16; j += 4)
+                st_cluster_v4f(row_addr + (c + j) * 4, acc_to_float(v[j], p.is_int8), acc_to_float(v[j + 1], p.is_int8),
+                               acc_to_float(v[j + 2], p.is_int8), acc_to_float(v[j + 3], p.is_int8));
+            }
+          }
+          mbar_arrive_cluster(mapa_smem(smem_u32(red_bar), 0));   // release: orders the stores above
+        } else if (!whole_tile && p.cluster_k <= 1) {
           // contributors of this tile are consecutive CTAs; this CTA's position among them
           const int first_cta = cta_of(static_cast<int64_t>(tr) * p.k_blocks);
           const int n_contrib = cta_of(static_cast<int64_t>(tr + 1) * p.k_blocks - 1) - first_cta + 1;
@@ -647,6 +716,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
             }
           }
         } else {
+          constexpr int kTileRows = kBM * C::R;
+          if (p.cluster_k > 1) {
+            // leader of a cluster: wait for the partners' partial sums
+            if (!mbar_wait(red_bar, 0, abort_flag)) {
+              ok = false;
+              break;
+            }
+            fence_acq_rel_cluster();
+          }
 #pragma unroll 1
           for (int sub = 0; sub < C::kSub; ++sub) {
           const int64_t wrow = nrow0 + sub * kBM + row_in_tile;
@@ -662,9 +740,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
               const int mi = c + j;
               if (mi >= m_cols) break;
               float x = acc_to_float(v0[j], p.is_int8);
+              float u_extra = 0.f;
+              for (int s2 = 1; s2 < p.cluster_k; ++s2) {   // partners in rank order: the sum does not depend on timing
+                const float* part = red_buf + static_cast<size_t>(s2 - 1) * kTileRows * BN;
+                x += part[(sub * kBM + row_in_tile) * BN + mi];
+                if constexpr (SWIGLU) u_extra += part[(kBM + row_in_tile) * BN + mi];
+              }
               int64_t ocol;
               if constexpr (SWIGLU) {
-                float u = acc_to_float(v1[j], p.is_int8);
+                float u = acc_to_float(v1[j], p.is_int8) + u_extra;
                 if (p.is_int8) {
                   x *= p.a_scale[mi] * p.b_scale[wrow];
                   u *= p.a_scale[mi] * p.b_scale[wrow + kBM];
@@ -729,27 +813,6 @@ constexpr int kPairStageBytes = 2 * kBM * kRowBytes;            // A half-tile +
 constexpr int kPairStages = 6;
 constexpr int kPairSmem = kPairStages * kPairStageBytes + 1024 + 512;
 
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// shared::cluster address of `local` (an address in this CTA's shared memory) in CTA `rank` of the cluster
-__device__ __forceinline__ uint32_t mapa_smem(uint32_t local, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
-  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
-}
 // TMA load whose completion bytes are counted on a barrier that may live in the partner CTA
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
                                                  int x, int y) {
@@ -1103,12 +1166,35 @@ int launch_cfg(const CUtensorMap& tr, const CUtensorMap& tc, KParams p, int grid
   p.stages = C::kStages;
   if (SWAP && stage_cap >= 2 && stage_cap < p.stages) p.stages = stage_cap;
   auto kern = gemm_tcgen05_kernel<BN, SWAP, SWIGLU, RT, KD>;
+  const size_t tail = 1024 + 512 + (SWAP ? 0 : kEpiStagingBytes);
+  // cluster split of k: the leader's inbox for its partners' partial sums comes out of the ring's memory
+  const size_t inbox = (SWAP && p.cluster_k > 1) ? static_cast<size_t>(p.cluster_k - 1) * kBM * C::R * BN * sizeof(float) : 0;
+  while (p.stages > 2 && static_cast<size_t>(p.stages) * C::kStageBytes + tail + inbox > 232448) --p.stages;
+  if (static_cast<size_t>(p.stages) * C::kStageBytes + tail + inbox > 232448) return -1;
+  const size_t smem = static_cast<size_t>(p.stages) * C::kStageBytes + tail + inbox;
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern),
-                          static_cast<int>(static_cast<size_t>(C::kStages) * C::kStageBytes + 1024 + 512 +
-                                           (SWAP ? 0 : kEpiStagingBytes))) != cudaSuccess)
+                          static_cast<int>(std::max(smem, static_cast<size_t>(C::kStages) * C::kStageBytes + tail))) != cudaSuccess)
     return -3;
-  const size_t smem = static_cast<size_t>(p.stages) * C::kStageBytes + 1024 + 512 + (SWAP ? 0 : kEpiStagingBytes);
-  const cudaError_t err = launch_pdl(kern, dim3(grid), dim3(kThreads), smem, s, tr, tc, p);
+  cudaError_t err;
+  if (SWAP && p.cluster_k > 1) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(p.cluster_k);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    err = cudaLaunchKernelEx(&cfg, kern, tr, tc, p);
+  } else {
+    err = launch_pdl(kern, dim3(grid), dim3(kThreads), smem, s, tr, tc, p);
+  }
   note_launch();
   return err == cudaSuccess ? 0 : -4;
 }
@@ -1175,6 +1261,13 @@ int launch_gemm(const GemmArgs& a, cudaStream_t s) {
   p.out_f16 = (a.dt == kF16) ? 1 : 0;
   p.is_int8 = a.is_int8;
   p.row_static = a.b_static;
+  {
+    // The CTAs of a following small-batch GEMM fit beside ours when both keep their rings short: they are
+    // then launched while this kernel still streams, fetch their first weight tiles, and take over the memory
+    // pipe the moment our CTAs drain (tuning knobs; 0 / 0 = trigger at the end, ring as deep as memory allows).
+    static const int early_knob = env_int("MLLM_B200_GEMM_EARLY_TRIGGER", 0);
+    p.early_trigger = early_knob;
+  }
   p.max_contrib = 1;
 
   const CUtensorMapDataType type =
@@ -1274,7 +1367,24 @@ int launch_gemm(const GemmArgs& a, cudaStream_t s) {
     return static_cast<size_t>(p.tiles_r) * contributors(g) * kBM * r * bn * sizeof(float);
   };
   p.whole_tiles = 0;
-  if (!can_share || ws_need(grid) > a.workspace_bytes) {
+  // Tiles fewer than SMs and a small batch: split the k range of every tile over a cluster of CTAs instead, and
+  // sum the partial products through the leader's shared memory (no workspace round trip, no tickets).
+  static const int cluster_knob = env_int("MLLM_B200_GEMM_CLUSTER_K", 1);
+  p.cluster_k = 0;
+  if (cluster_knob && !a.swiglu && bn == 16 && p.tiles_r * 2 <= num_sms) {
+    // power-of-two cluster sizes only: clusters of 3 did not all fit one wave when measured (22.4 us against
+    // 15.9 us for the 6144 x 4096 projection), 4-CTA clusters gained 1.4-1.9 us on 4096-row projections
+    int split = std::min(8, num_sms / p.tiles_r);
+    while (split & (split - 1)) --split;
+    while (split > 1 && p.k_blocks < 4 * split) split >>= 1;
+    if (split > 1 && p.tiles_r * split * 8 >= num_sms * 6) {   // at least three quarters of the SMs busy
+      p.cluster_k = split;
+      grid = p.tiles_r * split;
+    }
+  }
+  if (p.cluster_k > 1) {
+    // nothing shared through global memory
+  } else if (!can_share || ws_need(grid) > a.workspace_bytes) {
     grid = std::min(grid, p.tiles_r);  // every CTA gets whole tiles: nothing is shared
     p.whole_tiles = 1;
   }

@@ -47,6 +47,13 @@ void launch_kv_write(const void* k, const void* v, const int64_t* loc, void* k_c
                      int row_elems, int64_t k_stride, int64_t v_stride, int64_t num_slots, DType dt, int* status,
                      cudaStream_t s);
 
+// Bookkeeping of one decode step of a static batch (see decode_prepare_kernel): one launch instead of a dozen
+// small framework kernels.
+void launch_decode_prepare(const int64_t* last_ids, const int32_t* req_rows, const int64_t* own, int64_t own_stride,
+                           int used, int32_t* seq_lens, int32_t* req_to_token, int64_t rtt_stride,
+                           int64_t* g_input_ids, int32_t* g_req_rows, int32_t* g_seq_lens, int64_t* g_out_loc,
+                           int64_t* g_positions, int batch, cudaStream_t s);
+
 // ----- quantisation -------------------------------------------------------------------
 void launch_per_token_quant_int8(const void* x, int8_t* q, float* scale, int rows, int k, DType dt,
                                  cudaStream_t s);
@@ -127,6 +134,26 @@ int launch_w4a16_gemm(const W4A16Args& args, cudaStream_t s);
 // map points at a CUtensorMap.  type: 0 bf16, 1 fp16, 2 uint8.
 bool make_tma_operand_map(void* map, const void* base, int64_t rows, int64_t k, int64_t ld, int elem_bytes, int type,
                           int box_rows);
+
+// ----- expert-parallel token exchange (ep_a2a.cu) -------------------------------------------
+// Addresses of every rank's copy of the shared buffers (index = rank), this rank's id and the call's epoch.
+struct EpA2AArgs {
+  int ep, rank, experts, hidden, cap_rows;
+  uint32_t epoch;
+  uint64_t cnt_all[8];     // int32 [ep][experts]
+  uint64_t cnt_flags[8];   // uint32 [ep]
+  uint64_t recv_x[8];      // 16-bit [cap_rows][hidden]
+  uint64_t recv_meta[8];   // int32 [cap_rows][2]
+  uint64_t disp_flags[8];  // uint32 [ep]
+  uint64_t ret_y[8];       // 16-bit [pairs capacity][hidden]
+  uint64_t ret_flags[8];   // uint32 [ep]
+};
+int launch_ep_plan(const EpA2AArgs& a, const int* topk_ids, int pairs, int bn, int* pair_dst_rank, int* pair_dst_row,
+                   int* expert_offsets, int* work, int* n_work, int max_work, int* recv_rows, int* status,
+                   cudaStream_t s);
+int launch_ep_dispatch(const EpA2AArgs& a, const void* x, int64_t x_stride, int pairs, int top_k, const int* pair_dst_rank,
+                       const int* pair_dst_row, int* done_count, cudaStream_t s);
+int launch_ep_return(const EpA2AArgs& a, const void* ys, const int* recv_rows, int* done_count, cudaStream_t s);
 
 // ----- mixture of experts ----------------------------------------------------------------
 // router: fp32 softmax over `experts` (<= 256) logits -> top_k (<= 32, sorted, lowest index wins ties)
@@ -223,10 +250,12 @@ int launch_tp_reduce_add_rmsnorm(const uint64_t* peer_data, const uint64_t* peer
 // store the row into every rank's gathered buffer (peer_hidden[r] + global_row * hidden).  When a
 // 128-row tile is complete, gather_flags[global tile] on every rank is set to `epoch`.
 // ag_count: local int[tiles], zero-initialised, self-resetting.  rows must be a multiple of 128.
+// n_src = partial sums per row in the inbox: tp for the reduce-scatter inbox; 1 with tile_flags == nullptr when
+// the rows of this rank are already complete (output of the expert-parallel exchange).
 int launch_tp_rs_add_rmsnorm_ag(const void* inbox, int64_t inbox_rows_cap, const uint32_t* tile_flags,
                                 void* residual_shard, const void* weight, const uint64_t* peer_hidden,
                                 const uint64_t* peer_gather_flags, int* ag_count, int rows, int hidden, int tp,
-                                int rank, uint32_t epoch, float eps, DType dt, int* status, cudaStream_t s);
+                                int n_src, int rank, uint32_t epoch, float eps, DType dt, int* status, cudaStream_t s);
 // Bounded wait until flags[i] >= epoch for all i < n (makes peers' deliveries visible to later kernels).
 int launch_tp_wait_flags(const uint32_t* flags, int n, uint32_t epoch, int* status, cudaStream_t s);
 

@@ -111,6 +111,33 @@ class CudaGraphRunner:
     def can_run(self, fb: ForwardBatch) -> bool:
         return fb.forward_mode.is_decode() and fb.batch_size <= self.batch_sizes[-1] and bool(self.graphs)
 
+    def captured_size_for(self, raw: int) -> Optional[int]:
+        """The captured batch size a batch of ``raw`` rows would replay, or None when none is large enough."""
+        if not self.graphs or raw > self.batch_sizes[-1]:
+            return None
+        return self.batch_sizes[bisect.bisect_left(self.batch_sizes, raw)]
+
+    @torch.no_grad()
+    def replay_static(self, raw: int) -> LogitsProcessorOutput:
+        """Replay for a batch whose inputs were already written into this runner's static buffers (``input_ids``,
+        ``req_pool_indices``, ``seq_lens``, ``out_cache_loc``, ``positions``) by a kernel of the caller; rows past
+        ``raw`` must hold the padding values (they do after construction and after any padded :meth:`replay`)."""
+        bs = self.batch_sizes[bisect.bisect_left(self.batch_sizes, raw)]
+        self.graphs[bs].replay()
+        self.replays += 1
+        self.replayed_kernels += self.kernels_per_graph.get(bs, 0)
+        return self._outputs(bs, raw)
+
+    def _outputs(self, bs: int, raw: int) -> LogitsProcessorOutput:
+        if self.tp_sharded_logits:
+            out = LogitsProcessorOutput(local_logits=self.logits[bs][:raw], gather=self.mr.model.gather_logits)
+            vals, ids = self.next_ids[bs]
+            out.next_token_ids = self.mr.model.pick_greedy(vals[:raw], ids[:raw])
+            return out
+        out = LogitsProcessorOutput(next_token_logits=self.logits[bs][:raw])
+        out.next_token_ids = self.next_ids[bs][:raw]
+        return out
+
     @torch.no_grad()
     def replay(self, fb: ForwardBatch) -> LogitsProcessorOutput:
         raw = fb.batch_size
@@ -130,11 +157,4 @@ class CudaGraphRunner:
         self.graphs[bs].replay()
         self.replays += 1
         self.replayed_kernels += self.kernels_per_graph.get(bs, 0)
-        if self.tp_sharded_logits:
-            out = LogitsProcessorOutput(local_logits=self.logits[bs][:raw], gather=self.mr.model.gather_logits)
-            vals, ids = self.next_ids[bs]
-            out.next_token_ids = self.mr.model.pick_greedy(vals[:raw], ids[:raw])
-            return out
-        out = LogitsProcessorOutput(next_token_logits=self.logits[bs][:raw])
-        out.next_token_ids = self.next_ids[bs][:raw]
-        return out
+        return self._outputs(bs, raw)
