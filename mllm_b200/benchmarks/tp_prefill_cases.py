@@ -66,6 +66,30 @@ def main() -> None:
         if it >= 3:
             for name, a, b, _ in recs:
                 acc[name] += a.elapsed_time(b)
+    # decode-sized pieces: the fused peer-memory reduce + add + RMSNorm of 8 rows against the process group's
+    # all-reduce followed by the local add + norm, 20 calls each inside one pair of events
+    names += ["decode_reduce_fused", "decode_reduce_library"]
+    rows_d = 8
+    resid = torch.zeros(rows_d, H, device=dev, dtype=torch.bfloat16)
+    yd = torch.randn(rows_d, H, device=dev, dtype=torch.bfloat16)
+    for name in names[-2:]:
+        for rep in range(2):                      # first repetition warms up
+            dist.barrier()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(20):
+                if name == "decode_reduce_fused":
+                    part = comm.partial_buffer(rows_d)
+                    part.copy_(yd)
+                    ops.tp_reduce_add_rmsnorm(part, resid, nw, 1e-6)
+                else:
+                    tmp = yd.clone()
+                    dist.all_reduce(tmp)
+                    ops.fused_add_rmsnorm(tmp, resid, nw, 1e-6)
+            b.record()
+            torch.cuda.synchronize()
+            acc[name] = a.elapsed_time(b) / 20 * args.iters    # per call; includes the 16 KB staging copy of both arms
     ops.check_status()
     t = torch.tensor([acc[n] / args.iters for n in names], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)

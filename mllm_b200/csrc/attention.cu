@@ -64,6 +64,9 @@ struct AttnParams {
   int is_decode;
   int out_f16;
   float scale_log2;        // softmax scale * log2(e)
+  int window;              // sliding window: a query at position i sees keys i - window + 1 .. i (0 = everything)
+  float logit_cap;         // soft cap: score = cap * tanh(score / cap) before the softmax (0 = off)
+  float scale;             // softmax scale (used with the soft cap)
   uint32_t idesc_s, idesc_o;
 };
 
@@ -110,16 +113,18 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const AttnPar
     q_len = 1;
     prefix = seq_len - 1;
     q_row0 = b;
-    const int tiles = (seq_len + kKV - 1) / kKV;
+    const int lo = p.window > 0 ? max(0, seq_len - p.window) / kKV * kKV : 0;   // first tile the window touches
+    const int tiles = (seq_len - lo + kKV - 1) / kKV;
     const int per = (tiles + p.num_splits - 1) / p.num_splits;
-    kv_begin = blockIdx.x * per * kKV;
+    kv_begin = lo + blockIdx.x * per * kKV;
     kv_end = min(seq_len, kv_begin + per * kKV);
   } else {
     prefix = p.prefix_lens[b];
     q_len = seq_len - prefix;
     q0 = blockIdx.x * p.tokens_per_tile;
     q_row0 = p.q_start[b];
-    kv_begin = 0;
+    // with a window the tile's first query row bounds the keys from below
+    kv_begin = (p.window > 0 && !p.non_causal) ? max(0, prefix + q0 - p.window + 1) / kKV * kKV : 0;
     kv_end = p.non_causal ? seq_len
                           : min(seq_len, prefix + min(q_len, q0 + p.tokens_per_tile));  // causal upper bound of the tile
     if (q0 >= q_len) return;
@@ -265,19 +270,23 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const AttnPar
     tmem_ld_wait();
     const int col0 = kv_begin + j * kKV;
     const int visible = min(kv_limit, kv_end - 1) - col0;  // columns 0..visible are allowed
+    const int first_vis = (p.window > 0 && !(p.non_causal && !p.is_decode)) ? kv_limit - p.window + 1 - col0 : -(1 << 30);
     float sc[64];
     float m_tile = -INFINITY;
 #pragma unroll
     for (int c = 0; c < 64; ++c) {
-      float v = __uint_as_float(sraw[c >> 5][c & 31]) * p.scale_log2;
-      v = (c <= visible) ? v : -INFINITY;
+      float v = __uint_as_float(sraw[c >> 5][c & 31]);
+      v = p.logit_cap > 0.f ? p.logit_cap * tanhf(v * p.scale / p.logit_cap) * kLog2e : v * p.scale_log2;
+      v = (c <= visible && c >= first_vis) ? v : -INFINITY;
       sc[c] = v;
       m_tile = fmaxf(m_tile, v);
     }
     float factor = 1.f;
     bool need = false;
-    if (j == 0) {
-      m_used = (m_tile == -INFINITY) ? 0.f : m_tile;
+    if (m_used == -INFINITY) {
+      // no visible key so far (first tile, or tiles in front of this row's window): the accumulator row is
+      // still all zero, so the first finite maximum is adopted without a rescale
+      m_used = m_tile;
     } else if (m_tile > m_used + kRescaleThreshold) {
       factor = exp2f(m_used - m_tile);
       m_used = m_tile;
@@ -298,6 +307,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const AttnPar
       tmem_st_wait();
     }
     float psum = 0.f;
+    const float m_exp = (m_used == -INFINITY) ? 0.f : m_used;   // a row without a visible key yet: all p = 0
     {
       const uint32_t sp = smem_u32(sP);
 #pragma unroll
@@ -305,8 +315,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const AttnPar
         uint32_t w[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float p0 = fast_exp2(sc[ch * 8 + 2 * i] - m_used);
-          const float p1 = fast_exp2(sc[ch * 8 + 2 * i + 1] - m_used);
+          const float p0 = fast_exp2(sc[ch * 8 + 2 * i] - m_exp);
+          const float p1 = fast_exp2(sc[ch * 8 + 2 * i + 1] - m_exp);
           // sum what the tensor core will actually see (bf16-rounded probabilities)
           const uint32_t pk = p.out_f16 ? 0u : pack_bf16x2(p0, p1);
           if (p.out_f16) {
@@ -537,9 +547,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 
   const int req = p.req_pool_indices[b];
   const int seq_len = p.seq_lens[b];
-  const int tiles = (seq_len + kDT - 1) / kDT;
+  const int kv_lo = p.window > 0 ? max(0, seq_len - p.window) : 0;   // first key the (single) query sees
+  const int lo_tile = kv_lo / kDT * kDT;
+  const int tiles = (seq_len - lo_tile + kDT - 1) / kDT;
   const int per = (tiles + p.num_splits - 1) / p.num_splits;
-  const int kv_begin = split * per * kDT;
+  const int kv_begin = lo_tile + split * per * kDT;
   const int kv_end = min(seq_len, kv_begin + per * kDT);
   const int n_tiles = kv_begin < kv_end ? (kv_end - kv_begin + kDT - 1) / kDT : 0;
 
@@ -715,12 +727,15 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       }
       tc_fence_before_sync();
       mbar_arrive(&s_empty[t & 1]);  // the S^T buffer may be overwritten by tile t+2
-      const bool tok_ok = (kv_begin + t * kDT + tid) < kv_end;
+      const int tok_pos = kv_begin + t * kDT + tid;
+      const bool tok_ok = tok_pos < kv_end && tok_pos >= kv_lo;
       float* redt = red + (t & 1) * 4 * NQ;
 #pragma unroll
       for (int c = 0; c < NQ; ++c) {
         if (c < g) {
-          sc[c] = tok_ok ? sc[c] * p.scale_log2 : -INFINITY;
+          const float capped = p.logit_cap > 0.f ? p.logit_cap * tanhf(sc[c] * p.scale / p.logit_cap) * kLog2e
+                                                 : sc[c] * p.scale_log2;
+          sc[c] = tok_ok ? capped : -INFINITY;
           const float wm = warp_max(sc[c]);
           if (lane == 0) redt[warp * NQ + c] = wm;
         }
@@ -957,6 +972,9 @@ int launch_attention(const AttnArgs& a, cudaStream_t s) {
   p.is_decode = a.is_decode;
   p.out_f16 = a.dt == kF16 ? 1 : 0;
   p.scale_log2 = a.scale * kLog2e;
+  p.scale = a.scale;
+  p.window = a.window > 0 ? a.window : 0;
+  p.logit_cap = a.logit_cap > 0.f ? a.logit_cap : 0.f;
   const uint32_t fmt = a.dt == kF16 ? 0u : 1u;
   p.idesc_s = umma_idesc(kRows, kKV, 1, fmt, fmt, 0, 0);
   p.idesc_o = umma_idesc(kRows, kD, 1, fmt, fmt, 0, 1);

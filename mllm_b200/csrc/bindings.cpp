@@ -273,7 +273,7 @@ void apply_penalties(Tensor& logits, const Tensor& counts, const c10::optional<T
 }
 
 int64_t w4a16_gemm(const Tensor& x, const Tensor& qweight, const Tensor& scales, const c10::optional<Tensor>& zeros,
-                   int64_t group, const c10::optional<Tensor>& bias, Tensor& out) {
+                   int64_t group, const c10::optional<Tensor>& bias, Tensor& out, bool interleaved) {
   check_half(x, "x");
   check_cuda(qweight, "qweight");
   TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && qweight.dim() == 2 && qweight.is_contiguous() &&
@@ -313,6 +313,7 @@ int64_t w4a16_gemm(const Tensor& x, const Tensor& qweight, const Tensor& scales,
   a.ldc = out.stride(0);
   a.dt = dtype_of(x);
   a.num_sms = st.num_sms;
+  a.interleaved = interleaved ? 1 : 0;
   return mb200::launch_w4a16_gemm(a, stream_of(x));
 }
 
@@ -722,7 +723,8 @@ int64_t tp_wait_flags(const Tensor& flags, int64_t n, int64_t epoch) {
 
 void attention_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& req_to_token,
                        const Tensor& req_pool_indices, const Tensor& seq_lens, const Tensor& prefix_lens,
-                       const Tensor& q_start, double scale, Tensor& out, int64_t max_q_len, bool causal) {
+                       const Tensor& q_start, double scale, Tensor& out, int64_t max_q_len, bool causal, int64_t window,
+                       double logit_cap) {
   check_half(q, "q");
   TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.stride(2) == 1 && q.stride(1) == 128, "q must be [T,Hq,128]");
   TORCH_CHECK(out.is_contiguous() && out.sizes() == q.sizes() && out.scalar_type() == q.scalar_type(), "out");
@@ -760,6 +762,8 @@ void attention_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_c
   a.is_decode = 0;
   a.non_causal = causal ? 0 : 1;
   a.scale = static_cast<float>(scale);
+  a.window = static_cast<int>(window);
+  a.logit_cap = static_cast<float>(logit_cap);
   a.dt = dtype_of(q);
   const int rc = mb200::launch_attention(a, stream_of(q));
   TORCH_CHECK(rc == 0, "mllm_b200 attention_prefill: unsupported configuration (code ", rc, ")");
@@ -767,7 +771,7 @@ void attention_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_c
 
 void attention_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& req_to_token,
                       const Tensor& req_pool_indices, const Tensor& seq_lens, double scale, Tensor& out,
-                      int64_t max_seq_len) {
+                      int64_t max_seq_len, int64_t window, double logit_cap) {
   check_half(q, "q");
   TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.stride(2) == 1 && q.stride(1) == 128, "q must be [B,Hq,128]");
   TORCH_CHECK(out.is_contiguous() && out.sizes() == q.sizes() && out.scalar_type() == q.scalar_type(), "out");
@@ -809,6 +813,8 @@ void attention_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
   a.head_dim = 128;
   a.is_decode = 1;
   a.scale = static_cast<float>(scale);
+  a.window = static_cast<int>(window);
+  a.logit_cap = static_cast<float>(logit_cap);
   a.dt = dtype_of(q);
   const int rc = mb200::launch_attention(a, stream_of(q));
   TORCH_CHECK(rc == 0, "mllm_b200 attention_decode: unsupported configuration (code ", rc, ")");

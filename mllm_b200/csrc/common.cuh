@@ -413,6 +413,11 @@ __device__ __forceinline__ float warp_max(float v) {
 // device; safe to call from several threads.
 cudaError_t ensure_dynamic_smem(const void* kernel, int bytes);
 
+// Host side, opt-in (MLLM_B200_MAX_CARVEOUT=1): asks, once per (kernel, device), for the largest shared-memory
+// carve-out for `kernel`, so that every kernel of this library runs with the same split of the SM's L1 /
+// shared-memory array.
+void ensure_max_carveout(const void* kernel);
+
 // Host side: launch with the programmatic-stream-serialization attribute (MLLM_B200_PDL=0 turns
 // it off).  Works under stream capture: the dependency becomes a programmatic graph edge.
 bool pdl_enabled();
@@ -420,6 +425,7 @@ bool pdl_enabled();
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                               Args&&... args) {
+  ensure_max_carveout(reinterpret_cast<const void*>(kernel));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;

@@ -41,6 +41,26 @@ cudaError_t ensure_dynamic_smem(const void* kernel, int bytes) {
   return err;
 }
 
+void ensure_max_carveout(const void* kernel) {
+  static const bool on = [] {
+    // opt-in: measured neutral on the decode step (5.38 ms with, 5.34 ms without), so the default leaves every
+    // kernel's carve-out to the driver
+    const char* v = std::getenv("MLLM_B200_MAX_CARVEOUT");
+    return v != nullptr && v[0] == '1';
+  }();
+  if (!on) return;
+  static std::mutex mu;
+  static std::map<std::pair<const void*, int>, bool> done;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return;
+  std::lock_guard<std::mutex> lock(mu);
+  auto& d = done[{kernel, dev}];
+  if (d) return;
+  d = true;
+  cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  cudaGetLastError();   // a kernel that cannot take the hint keeps its default
+}
+
 namespace {
 
 template <typename T>

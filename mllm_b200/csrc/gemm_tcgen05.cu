@@ -1177,6 +1177,7 @@ int launch_cfg(const CUtensorMap& tr, const CUtensorMap& tc, KParams p, int grid
     return -3;
   cudaError_t err;
   if (SWAP && p.cluster_k > 1) {
+    ensure_max_carveout(reinterpret_cast<const void*>(kern));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kThreads);
@@ -1203,6 +1204,7 @@ template <bool SWIGLU>
 int launch_pair_cfg(const CUtensorMap& tr, const CUtensorMap& tc, const KParams& p, int pairs, cudaStream_t s) {
   auto kern = gemm_pair_kernel<SWIGLU>;
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kPairSmem) != cudaSuccess) return -3;
+  ensure_max_carveout(reinterpret_cast<const void*>(kern));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);
   cfg.blockDim = dim3(kThreads);

@@ -14,7 +14,13 @@
 // (two buffers); epilogue warps write out[token][row].  Small problems are split along K into fp32
 // partials that a second kernel sums in split order (deterministic).
 //
-// Warp roles (384 threads): 0 TMA producer, 1 MMA issuer, 2 TMEM allocator, 4-7 dequant, 8-11 epilogue.
+// Warp roles (512 threads): 0 TMA producer, 1 MMA issuer, 2 TMEM allocator, 4-11 dequant (two threads per
+// weight row: each expands half of the row's 64-element k-block), 12-15 epilogue.
+//
+// Nibble order inside a 32-bit word.  "natural": nibble i = element 8j + i.  "interleaved" (what the loaders
+// produce for this kernel): element 8j + 2p + h sits in nibble p + 4h, so that ((word >> 4p) & 0x000F000F) holds
+// the ADJACENT elements 2p and 2p + 1 in the low bits of its two 16-bit halves: one shift and one logic
+// operation per pair instead of five.
 // Every barrier wait is bounded (kStatusPipelineTimeout on expiry).
 #include <algorithm>
 
@@ -27,7 +33,7 @@ namespace {
 constexpr int kBM = 128;
 constexpr int kRowBytes = 128;
 constexpr int kUmmaKBytes = 32;
-constexpr int kW4Threads = 384;
+constexpr int kW4Threads = 512;
 
 struct W4Params {
   const uint32_t* qweight;
@@ -42,6 +48,7 @@ struct W4Params {
   int tiles_n, tiles_m;
   int64_t ldc;
   int out_f16;
+  int interleaved;   // nibble order of qweight (see the head of this file)
   uint32_t idesc;
 };
 
@@ -92,6 +99,26 @@ __device__ __forceinline__ uint32_t dequant_pair<__half>(uint32_t t, uint32_t of
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// interleaved nibble order: t = word >> 4p holds elements 2p (bits 0-3) and 2p + 1 (bits 16-19)
+template <typename T>
+__device__ __forceinline__ uint32_t dequant_pair_il(uint32_t t, uint32_t off2, uint32_t scale2);
+template <>
+__device__ __forceinline__ uint32_t dequant_pair_il<__nv_bfloat16>(uint32_t t, uint32_t off2, uint32_t scale2) {
+  const uint32_t p = (t & 0x000F000Fu) | W4Magic<__nv_bfloat16>::kOr;
+  __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&p);
+  v = __hsub2(v, *reinterpret_cast<const __nv_bfloat162*>(&off2));
+  v = __hmul2(v, *reinterpret_cast<const __nv_bfloat162*>(&scale2));
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <>
+__device__ __forceinline__ uint32_t dequant_pair_il<__half>(uint32_t t, uint32_t off2, uint32_t scale2) {
+  const uint32_t p = (t & 0x000F000Fu) | W4Magic<__half>::kOr;
+  __half2 v = *reinterpret_cast<const __half2*>(&p);
+  v = __hsub2(v, *reinterpret_cast<const __half2*>(&off2));
+  v = __hmul2(v, *reinterpret_cast<const __half2*>(&scale2));
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
 template <typename T>
 __device__ __forceinline__ uint32_t splat2(float v);
 template <>
@@ -128,7 +155,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(&full_x[s], 1);
-      mbar_init(&full_w[s], 4);  // one arrival per expansion warp
+      mbar_init(&full_w[s], 8);  // one arrival per expansion warp
       mbar_init(&empty_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -137,7 +164,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     }
     for (int s = 0; s < C::kRawStages; ++s) {
       mbar_init(&raw_full[s], 1);
-      mbar_init(&raw_empty[s], 4);
+      mbar_init(&raw_empty[s], 8);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -235,12 +262,13 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       if (ok) umma_commit(&acc_full[acc]);
     }
     if (!ok) fail();
-  } else if (warp >= 4 && warp < 8) {
-    // ---------------- weight expansion: thread = weight row of the tile ----------------
+  } else if (warp >= 4 && warp < 12) {
+    // ---------------- weight expansion: two threads per weight row of the tile ----------------
     // The packed rows arrive by TMA, 128 bytes (four k-blocks) per row at a time, so DRAM sees whole
-    // 128-byte lines; a thread copies its row out of the (128-byte swizzled) staging tile, releases it,
-    // and expands one k-block per operand stage.
-    const int r = threadIdx.x - 128;
+    // 128-byte lines; a thread copies its half of the row out of the (128-byte swizzled) staging tile,
+    // releases it, and expands its 32 elements of one k-block per operand stage.
+    const int r = (threadIdx.x - 128) & 127;
+    const int hf = (threadIdx.x - 128) >> 7;   // which 16 bytes of a k-block's 32 packed bytes
     int stage = 0, rstage = 0;
     uint32_t phase = 0, rphase = 0;
     bool ok = true;
@@ -264,11 +292,11 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           ok = false;
           break;
         }
-        uint4 raw[8];
+        uint4 raw[4];   // this thread's 16 bytes of each of the four k-blocks
         {
           const uint8_t* src = raw_ring + rstage * C::kRawBytes + r * kRowBytes;
 #pragma unroll
-          for (int c = 0; c < 8; ++c) raw[c] = *reinterpret_cast<const uint4*>(src + ((c ^ (r & 7)) << 4));
+          for (int u = 0; u < 4; ++u) raw[u] = *reinterpret_cast<const uint4*>(src + (((2 * u + hf) ^ (r & 7)) << 4));
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&raw_empty[rstage]);  // arrivals on one barrier serialise: one per warp
@@ -286,21 +314,27 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             break;
           }
           uint8_t* dst = smem + static_cast<size_t>(stage) * C::kStageBytes + r * kRowBytes;
-          const uint32_t words[8] = {raw[2 * u].x, raw[2 * u].y, raw[2 * u].z, raw[2 * u].w,
-                                     raw[2 * u + 1].x, raw[2 * u + 1].y, raw[2 * u + 1].z, raw[2 * u + 1].w};
+          const uint32_t words[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
 #pragma unroll
-          for (int jj = 0; jj < 8; ++jj) {
+          for (int jj = 0; jj < 4; ++jj) {
             uint4 o4;
             if (row_ok) {
               const uint32_t w = words[jj];
-              o4.x = dequant_pair<T>(w, off2, scale2);
-              o4.y = dequant_pair<T>(w >> 8, off2, scale2);
-              o4.z = dequant_pair<T>(w >> 16, off2, scale2);
-              o4.w = dequant_pair<T>(w >> 24, off2, scale2);
+              if (p.interleaved) {
+                o4.x = dequant_pair_il<T>(w, off2, scale2);
+                o4.y = dequant_pair_il<T>(w >> 4, off2, scale2);
+                o4.z = dequant_pair_il<T>(w >> 8, off2, scale2);
+                o4.w = dequant_pair_il<T>(w >> 12, off2, scale2);
+              } else {
+                o4.x = dequant_pair<T>(w, off2, scale2);
+                o4.y = dequant_pair<T>(w >> 8, off2, scale2);
+                o4.z = dequant_pair<T>(w >> 16, off2, scale2);
+                o4.w = dequant_pair<T>(w >> 24, off2, scale2);
+              }
             } else {
               o4 = make_uint4(0, 0, 0, 0);
             }
-            *reinterpret_cast<uint4*>(dst + ((jj ^ (r & 7)) << 4)) = o4;
+            *reinterpret_cast<uint4*>(dst + (((4 * hf + jj) ^ (r & 7)) << 4)) = o4;
           }
           fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
           __syncwarp();
@@ -313,9 +347,9 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       }
     }
     if (!ok) fail();
-  } else if (warp >= 8) {
+  } else if (warp >= 12) {
     // ---------------- epilogue: thread = weight row (output column) ----------------
-    const int ew = warp - 8;
+    const int ew = warp - 12;
     const int row_in_tile = ew * 32 + lane;
     bool ok = true;
     int idx = 0;
@@ -426,6 +460,7 @@ int launch_w4a16_gemm(const W4A16Args& a, cudaStream_t s) {
   p.tiles_m = (a.m + bn - 1) / bn;
   p.ldc = a.ldc;
   p.out_f16 = a.dt == kF16 ? 1 : 0;
+  p.interleaved = a.interleaved;
   const uint32_t fmt = a.dt == kF16 ? 0u : 1u;
   p.idesc = umma_idesc(kBM, bn, 1u, fmt, fmt);
   const int num_sms = a.num_sms > 0 ? a.num_sms : 148;

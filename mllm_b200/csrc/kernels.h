@@ -115,7 +115,8 @@ size_t gemm_workspace_bytes(int m, int n, int k, int num_sms);
 // ----- W4A16 GEMM (4-bit weights expanded in shared memory, tcgen05) ----------------------------
 struct W4A16Args {
   const void* x;        // [m, k] activations (bf16 / fp16), row stride ldx
-  const void* qweight;  // int32 [n, k/8], nibble i of word j = element 8j + i
+  const void* qweight;  // int32 [n, k/8]; nibble i of word j = element 8j + i, or (interleaved = 1) element
+                        // 8j + 2p + h in nibble p + 4h
   const void* scales;   // [n, k/group] in the activation type
   const uint8_t* zeros; // [n, k/group] or null (zero point 8)
   const void* bias;     // [n] or null
@@ -127,6 +128,7 @@ struct W4A16Args {
   int64_t ldx, ldc;
   DType dt;
   int num_sms;
+  int interleaved;
 };
 int launch_w4a16_gemm(const W4A16Args& args, cudaStream_t s);
 
@@ -205,6 +207,8 @@ struct AttnArgs {
   int is_decode;
   int non_causal;           // prefill only: bidirectional attention inside each sequence
   float scale;
+  int window;               // > 0: a query at position i sees keys i - window + 1 .. i only (causal attention)
+  float logit_cap;          // > 0: scores pass through cap * tanh(score / cap) before the softmax
   DType dt;
 };
 int launch_attention(const AttnArgs& args, cudaStream_t s);

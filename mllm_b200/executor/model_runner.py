@@ -214,6 +214,36 @@ class ModelRunner:
                 logger.warning("fused tensor-parallel kernels failed their start-up check on this system; "
                                "tensor-parallel layers use NCCL collectives")
                 set_tp_comm(None)
+                comm = None
+            self._init_ep_comm(comm, min(prefill_rows, 65536))
+
+    def _init_ep_comm(self, tp_comm, prefill_rows: int) -> None:
+        """Buffers of the expert-parallel token exchange, when experts are sharded over the same ranks as the
+        tensor-parallel group and the fused prefill step (row-sharded residual) is available."""
+        from ..layers.moe import SparseMoeBlock
+        from ..parallel.symm import EPComm, SymmetricHeap, set_ep_comm
+
+        set_ep_comm(None)
+        ep = pstate.get_ep_group()
+        tp = pstate.get_tp_group()
+        blocks = [m for m in self.model.modules() if isinstance(m, SparseMoeBlock)]
+        if (tp_comm is None or tp_comm.prefill is None or not blocks or ep.world_size <= 1
+                or ep.world_size != tp.world_size or ep.world_size > 8):
+            return
+        b = blocks[0]
+        tc = text_config_of(self.hf_config)
+        top_k = int(getattr(tc, "num_experts_per_tok", 0) or b.gate.top_k)
+        tokens_cap = tp_comm.prefill.rows_cap // ep.world_size
+        try:
+            nbytes = EPComm.heap_bytes(self.hidden_size, self.dtype, ep.world_size, b.num_experts, top_k, tokens_cap)
+            heap = SymmetricHeap.create(nbytes, self.device, tp.group)
+            comm = EPComm(heap, ep.rank_in_group, ep.world_size, self.hidden_size, self.dtype, b.num_experts, top_k,
+                          tokens_cap)
+            torch.cuda.synchronize(self.device)
+            tp.barrier()
+            set_ep_comm(comm)
+        except Exception as exc:  # no peer-mapped memory for it: sparse blocks keep the replicated layout
+            logger.warning("expert-parallel exchange unavailable (%s); experts run on replicated activations", exc)
 
     def _tp_comm_self_test(self, comm) -> bool:
         """One fused reduce over the peer-mapped buffers with a known answer (rank r contributes r + 1

@@ -90,11 +90,40 @@ class SparseMoeBlock(nn.Module):
                 w[e] = ops.ref.interleave_gate_up(w[e].clone(), ops.SWIGLU_BLOCK)
             self.swiglu_block = ops.SWIGLU_BLOCK
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        """Returns this rank's contribution (a partial sum when ``ep_size`` or ``tp_size`` > 1)."""
+    def forward(self, x: torch.Tensor):
+        """Returns this rank's contribution (a partial sum when ``ep_size`` or ``tp_size`` > 1).
+
+        Inside the fused tensor-parallel prefill step (``x`` is the gathered buffer, the residual stream is
+        sharded by rows) with the expert-parallel exchange set up, the rank routes only the rows it owns, the
+        rows travel to their experts' ranks and back (``ops.ep_moe_exchange``), and the result is a
+        ``PrefillShard``: this rank's rows, complete, for the following norm."""
+        shard = self._exchange(x)
+        if shard is not None:
+            return shard
         topk_w, topk_ids = self.gate(x)
         return ops.moe_experts(x, self.w13, self.w2, topk_w, topk_ids, self.expert_offset, self.swiglu_block,
                                self.num_experts)
+
+    def can_exchange(self, rows: int) -> bool:
+        """Whether a batch of ``rows`` tokens can go through the expert-parallel exchange on this block."""
+        from ..parallel.symm import get_ep_comm, get_tp_comm
+
+        ep, tp = get_ep_comm(), get_tp_comm()
+        return (ep is not None and tp is not None and tp.prefill is not None and self.ep_size == ep.world
+                and self.swiglu_block == ops.SWIGLU_BLOCK and self.w13.is_cuda and ep.eligible(rows))
+
+    def _exchange(self, x: torch.Tensor):
+        from ..parallel.symm import PrefillShard, get_ep_comm, get_tp_comm
+
+        ep, tp = get_ep_comm(), get_tp_comm()
+        if (x.dim() != 2 or not x.is_cuda or not self.can_exchange(x.shape[0])
+                or x.data_ptr() != tp.prefill.hidden_full.data_ptr()):
+            return None
+        own = x.shape[0] // ep.world
+        mine = x[ep.rank * own:(ep.rank + 1) * own]
+        topk_w, topk_ids = self.gate(mine)
+        out = ops.ep_moe_exchange(mine, self.w13, self.w2, topk_w, topk_ids, self.swiglu_block, ep)
+        return PrefillShard(x.shape[0], tp.next_epoch(), out)
 
     @property
     def is_partial(self) -> bool:

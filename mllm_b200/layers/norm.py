@@ -28,9 +28,9 @@ class RMSNorm(nn.Module):
         the step is reduce-scatter + add + norm + all-gather; the returned residual is then this rank's
         row shard, and ``gated=True`` promises that the consumer of the normed rows is a GEMM that waits
         per row tile (otherwise the stream waits for the whole gather here)."""
-        from ..parallel.symm import PrefillPartial, get_tp_comm
+        from ..parallel.symm import PrefillPartial, PrefillShard, get_tp_comm
 
-        if isinstance(x, PrefillPartial):
+        if isinstance(x, (PrefillPartial, PrefillShard)):
             assert residual is not None
             return ops.tp_rs_add_rmsnorm_ag(x, residual, self.weight, self.eps, get_tp_comm(), gated)
         if partial:

@@ -218,6 +218,13 @@ class Qwen3Model(nn.Module):
         )
         self.norm = RMSNorm(config.hidden_size, getattr(config, "rms_norm_eps", 1e-6), params_dtype)
 
+    def _sparse_blocks_can_shard(self, rows: int) -> bool:
+        if not hasattr(self, "_sparse"):
+            from ..layers.moe import SparseMoeBlock
+
+            self._sparse = [m for m in self.modules() if isinstance(m, SparseMoeBlock)]
+        return all(b.can_exchange(rows) for b in self._sparse)
+
     def forward(self, input_ids: torch.Tensor, positions: torch.Tensor, forward_batch: ForwardBatch,
                 input_embeds: Optional[torch.Tensor] = None, deepstack_embeds=None) -> torch.Tensor:
         staged = pstate.get_pipeline_parallel_world_size() > 1
@@ -231,8 +238,9 @@ class Qwen3Model(nn.Module):
             residual = pstate.pp_recv_prev(torch.empty_like(hidden))
         comm = get_tp_comm()
         if comm is not None:
-            # deepstack injection adds to the block output, which the fused prefill step never materialises
-            comm.prefill_fusion = deepstack_embeds is None
+            # deepstack injection adds to the block output, which the fused prefill step never materialises; a
+            # sparse block can follow the row-sharded residual only through the expert-parallel exchange
+            comm.prefill_fusion = deepstack_embeds is None and self._sparse_blocks_can_shard(input_ids.shape[0])
         for i in self.pp_layers:
             hidden, residual = self.layers[i](hidden, residual, forward_batch)
             if deepstack_embeds is not None and i < len(deepstack_embeds):

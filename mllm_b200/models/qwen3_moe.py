@@ -41,6 +41,8 @@ class _MoEMlp(torch.nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         y = self.block(x)
+        if not isinstance(y, torch.Tensor):
+            return y            # this rank's rows, complete (expert-parallel exchange): the next norm takes it as is
         tp = pstate.get_tensor_model_parallel_world_size()
         if tp > 1 and not self.block.is_partial:
             # every rank computed the full output: keep one copy in the sum that the next norm reduces

@@ -212,14 +212,21 @@ def tp_rs_add_rmsnorm_ag(partial, residual: torch.Tensor, weight: torch.Tensor, 
     off), normalises and stores the rows into every rank's gathered buffer.  Returns
     ``(hidden_full[:M], residual_shard)``.  With ``gated`` the next GEMM waits per row tile; otherwise the
     stream waits here for the whole gather."""
+    from ..parallel.symm import PrefillShard
+
     p = comm.prefill
     rows = partial.rows
     own = rows // comm.world
     if residual.shape[0] == rows and comm.world > 1:
         residual = residual[comm.rank * own:(comm.rank + 1) * own].clone()
     assert residual.shape[0] == own and residual.is_contiguous()
-    inbox_view = p.inbox
-    rc = ext().tp_rs_add_rmsnorm_ag(inbox_view, p.tile_flags, residual, weight, p.hidden_ptrs, p.gather_flag_ptrs,
+    if isinstance(partial, PrefillShard):
+        # this rank's rows arrive complete: one "partial" per row, nothing to wait for
+        inbox_view = partial.shard.contiguous().view(1, own, -1)
+        tile_flags = p.tile_flags[:0]
+    else:
+        inbox_view, tile_flags = p.inbox, p.tile_flags
+    rc = ext().tp_rs_add_rmsnorm_ag(inbox_view, tile_flags, residual, weight, p.hidden_ptrs, p.gather_flag_ptrs,
                                     p.ag_count, comm.rank, partial.epoch, eps)
     if rc != 0:
         raise RuntimeError(f"mllm_b200 tp_rs_add_rmsnorm_ag failed (code {rc})")
@@ -304,22 +311,47 @@ def int8_scaled_mm(a_q, w_q, a_scale, w_scale, out_dtype, bias=None) -> torch.Te
     return out.view(*a_q.shape[:-1], w_q.shape[0])
 
 
-def w4a16_gemm(x, qweight, scales, zeros, group: int, bias=None) -> torch.Tensor:
+_W4_ORDER = (0, 2, 4, 6, 1, 3, 5, 7)   # nibble position -> element of the word, interleaved layout
+
+
+def w4a16_interleave(qweight: torch.Tensor) -> torch.Tensor:
+    """Re-orders the eight nibbles of every 32-bit word from natural order (nibble i = element i) to the order the
+    GEMM kernel expands fastest: element ``2p + h`` in nibble ``p + 4h``, so that adjacent elements come out of one
+    mask.  Done once when weights are loaded."""
+    w = qweight.to(torch.int64) & 0xFFFFFFFF
+    out = torch.zeros_like(w)
+    for pos, elem in enumerate(_W4_ORDER):
+        out |= ((w >> (4 * elem)) & 0xF) << (4 * pos)
+    out = torch.where(out >= 2 ** 31, out - 2 ** 32, out)
+    return out.to(torch.int32)
+
+
+def w4a16_deinterleave(qweight: torch.Tensor) -> torch.Tensor:
+    w = qweight.to(torch.int64) & 0xFFFFFFFF
+    out = torch.zeros_like(w)
+    for pos, elem in enumerate(_W4_ORDER):
+        out |= ((w >> (4 * pos)) & 0xF) << (4 * elem)
+    out = torch.where(out >= 2 ** 31, out - 2 ** 32, out)
+    return out.to(torch.int32)
+
+
+def w4a16_gemm(x, qweight, scales, zeros, group: int, bias=None, interleaved: bool = False) -> torch.Tensor:
     """``x @ dequant(qweight).T (+bias)``: 4-bit weights with group-wise scales (and optional zero points).
     On the GPU the nibbles are expanded inside the tcgen05 GEMM kernel; the weights are never
-    materialised in 16 bits in device memory."""
+    materialised in 16 bits in device memory.  ``interleaved`` says that ``qweight`` went through
+    :func:`w4a16_interleave`."""
     x2 = _2d(x)
     K = x2.shape[1]
     ok = (use_kernels(x) and x.dtype in (torch.bfloat16, torch.float16) and K % 64 == 0 and group % 64 == 0
           and K % group == 0 and qweight.dtype == torch.int32)
     if not ok:
-        return ref.w4a16_gemm(x, qweight, scales, zeros, group, bias)
+        return ref.w4a16_gemm(x, w4a16_deinterleave(qweight) if interleaved else qweight, scales, zeros, group, bias)
     if x2.stride(-1) != 1 or (x2.stride(0) * x2.element_size()) % 16:
         x2 = x2.contiguous()
     out = torch.empty((x2.shape[0], qweight.shape[0]), dtype=x.dtype, device=x.device)
     z = None if zeros is None else zeros.to(torch.uint8).contiguous()
     rc = ext().w4a16_gemm(x2, qweight.contiguous(), scales.to(x.dtype).contiguous(), z, int(group),
-                          None if bias is None else bias.to(x.dtype).contiguous(), out)
+                          None if bias is None else bias.to(x.dtype).contiguous(), out, bool(interleaved))
     if rc != 0:
         raise RuntimeError(f"mllm_b200 w4a16_gemm: unsupported shape or launch failure (code {rc}) for "
                            f"M={x2.shape[0]} N={qweight.shape[0]} K={K} group={group}")
@@ -502,21 +534,23 @@ def tp_reduce_add_rmsnorm(partial: torch.Tensor, residual: Optional[torch.Tensor
 # attention
 # --------------------------------------------------------------------------
 def _attention_kernel_ok(q: torch.Tensor, k_cache: torch.Tensor, window, logit_cap) -> bool:
-    """The tcgen05 attention kernels cover head size 128, plain causal masking and a cache of the activation dtype."""
-    return use_kernels(q) and q.shape[-1] == 128 and not window and not logit_cap and k_cache.dtype == q.dtype
+    """The tcgen05 attention kernels cover head size 128 (causal, optionally with a sliding window and a soft cap
+    on the scores) and a cache of the activation dtype."""
+    return use_kernels(q) and q.shape[-1] == 128 and k_cache.dtype == q.dtype
 
 
 def attention_prefill(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, prefix_lens,
                       q_start_loc, scale: float, out=None, max_q_len: int = 0, window: Optional[int] = None,
                       logit_cap: float = 0.0, seq_lens_cpu=None, prefix_lens_cpu=None) -> torch.Tensor:
     """Causal attention of new tokens over cached prefix + themselves.  ``window``: sliding-window attention
-    (each query sees its last ``window`` keys); ``logit_cap``: soft-capping of the scores.  Head sizes other
-    than 128, windows and caps take library / PyTorch fallbacks."""
+    (each query sees its last ``window`` keys); ``logit_cap``: soft-capping of the scores; both are mask /
+    score options of the tcgen05 kernels.  Head sizes other than 128 and caches of another dtype take
+    library / PyTorch fallbacks."""
     if _attention_kernel_ok(q, k_cache, window, logit_cap) and hasattr(ext(), "attention_prefill"):
         if out is None:
             out = torch.empty((q.shape[0], q.shape[1], q.shape[2]), dtype=q.dtype, device=q.device)
         ext().attention_prefill(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, prefix_lens,
-                                q_start_loc, scale, out, max_q_len, True)
+                                q_start_loc, scale, out, max_q_len, True, int(window or 0), float(logit_cap or 0.0))
         return out
     if q.is_cuda and not logit_cap:
         o = ref.attention_prefill_sdpa(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, prefix_lens,
@@ -534,7 +568,8 @@ def attention_decode(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_le
     if _attention_kernel_ok(q, k_cache, window, logit_cap) and hasattr(ext(), "attention_decode"):
         if out is None:
             out = torch.empty((q.shape[0], q.shape[1], q.shape[2]), dtype=q.dtype, device=q.device)
-        ext().attention_decode(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, scale, out, max_seq_len)
+        ext().attention_decode(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, scale, out, max_seq_len,
+                               int(window or 0), float(logit_cap or 0.0))
         return out
     if q.is_cuda and max_seq_len:
         return ref.attention_decode_batched(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, scale,
@@ -567,7 +602,7 @@ def _varlen_bidirectional_padded(q, k, v, cu_seqlens, scale: float) -> torch.Ten
     out = torch.empty_like(q)
     ext().attention_prefill(q, k, v, rtt, torch.arange(n, device=q.device, dtype=torch.int32), lens.contiguous(),
                             torch.zeros(n, device=q.device, dtype=torch.int32), cu[:-1].contiguous(), scale, out, max_len,
-                            False)
+                            False, 0, 0.0)
     return out
 
 
@@ -742,6 +777,43 @@ def moe_experts(x, w13, w2, topk_w, topk_ids, expert_offset: int = 0, swiglu_blo
     _moe_gemm(h, w2, ys, offsets, work, n_work, bn, False)
     out = torch.empty((T, H), dtype=x.dtype, device=dev)
     e.moe_combine(ys, sorted_pos, topk_w.contiguous(), out)
+    return out
+
+
+def ep_moe_exchange(x_own, w13, w2, topk_w, topk_ids, swiglu_block: int, comm) -> torch.Tensor:
+    """Expert-parallel MoE for the token rows this rank owns (``x_own [T/ep, H]``, routed here: ``topk_ids`` are
+    global expert ids): the rows travel to the ranks that own their experts, run through the grouped expert GEMMs
+    there, come back and are summed with the router weights.  Everything stays on the device; the flags that
+    order the exchange are epochs in peer-mapped memory, waited for with a bound."""
+    if swiglu_block != SWIGLU_BLOCK:
+        raise ValueError("the expert-parallel exchange needs w13 in 128-row gate / up blocks")
+    T, H = x_own.shape
+    k = topk_ids.shape[1]
+    E_local, N13, _ = w13.shape
+    inter = N13 // 2
+    e = ext()
+    epoch = comm.next_epoch()
+    bn = moe_chunk_rows(T * comm.world, k, comm.experts)
+    ids = (topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)).contiguous()
+    x2 = x_own if x_own.stride(-1) == 1 and (x_own.stride(0) * x_own.element_size()) % 16 == 0 else x_own.contiguous()
+
+    def check(rc, what):
+        if rc != 0:
+            raise RuntimeError(f"mllm_b200 {what} failed (code {rc})")
+
+    check(e.ep_plan(ids, comm.ptrs, comm.rank, comm.experts, H, comm.cap_rows, epoch, bn, comm.pair_dst_rank,
+                    comm.pair_dst_row, comm.expert_offsets, comm.work, comm.n_work, comm.recv_rows), "ep_plan")
+    check(e.ep_dispatch(x2, k, comm.pair_dst_rank, comm.pair_dst_row, comm.ptrs, comm.rank, comm.experts, comm.cap_rows,
+                        epoch, comm.done[0:1]), "ep_dispatch")
+    check(e.tp_wait_flags(comm.disp_flags, comm.world, epoch), "ep dispatch wait")
+    h = torch.empty((comm.cap_rows, inter), dtype=x_own.dtype, device=x_own.device)
+    _moe_gemm(comm.recv_x, w13, h, comm.expert_offsets, comm.work, comm.n_work, bn, True)
+    ys = torch.empty((comm.cap_rows, H), dtype=x_own.dtype, device=x_own.device)
+    _moe_gemm(h, w2, ys, comm.expert_offsets, comm.work, comm.n_work, bn, False)
+    check(e.ep_return(ys, comm.recv_rows, comm.ptrs, comm.rank, comm.experts, epoch, comm.done[1:2]), "ep_return")
+    check(e.tp_wait_flags(comm.ret_flags, comm.world, epoch), "ep return wait")
+    out = torch.empty((T, H), dtype=x_own.dtype, device=x_own.device)
+    e.moe_combine(comm.ret_y[: T * k], comm.pair_index[: T * k], topk_w.contiguous(), out)
     return out
 
 

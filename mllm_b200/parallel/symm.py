@@ -158,6 +158,73 @@ class PrefillPartial:
         self.rows, self.epoch, self.dtype, self.device = rows, epoch, dtype, device
 
 
+class PrefillShard:
+    """The rows this rank owns of a block's output, already complete (no partial sums left to add): what the
+    expert-parallel exchange returns.  Only the following norm (add + RMSNorm + all-gather) can consume it."""
+
+    def __init__(self, rows: int, epoch: int, shard: torch.Tensor) -> None:
+        self.rows, self.epoch, self.shard = rows, epoch, shard
+        self.dtype, self.device = shard.dtype, shard.device
+
+
+class EPComm:
+    """Peer-mapped buffers of the expert-parallel token exchange (``csrc/ep_a2a.cu``): every rank's per-expert
+    pair counts, the receive slab for routed token rows (grouped by local expert, then by source rank), the
+    (source rank, pair) note beside each row, the return buffer for the experts' output rows, and three flag
+    blocks (counts, dispatch, return) holding the epoch of the last completed exchange per source rank."""
+
+    def __init__(self, heap: "SymmetricHeap", rank: int, world: int, hidden: int, dtype: torch.dtype, experts: int,
+                 top_k: int, tokens_cap: int, slab_factor: float = 2.0) -> None:
+        i32 = torch.int32
+        self.rank, self.world, self.hidden, self.dtype = rank, world, hidden, dtype
+        self.experts, self.top_k = experts, top_k
+        self.tokens_cap = int(tokens_cap)                 # tokens of ONE rank per call
+        self.pairs_cap = self.tokens_cap * top_k
+        # rows a rank receives: pairs of all ranks / ranks on average; the factor is head-room for skewed routing
+        self.cap_rows = int(min(self.pairs_cap * world, max(256, slab_factor * self.pairs_cap)))
+        self.cap_rows = (self.cap_rows + 127) // 128 * 128
+        dev = heap.buf.device
+        cut = {}
+        for name, shape, dt in (("cnt_all", (world * experts,), i32), ("cnt_flags", (8,), i32),
+                                ("recv_x", (self.cap_rows, hidden), dtype), ("recv_meta", (self.cap_rows, 2), i32),
+                                ("disp_flags", (8,), i32), ("ret_y", (self.pairs_cap, hidden), dtype),
+                                ("ret_flags", (8,), i32)):
+            cut[name] = heap.tensor(shape, dt)
+        self.recv_x, self.ret_y = cut["recv_x"][0], cut["ret_y"][0]
+        self.disp_flags, self.ret_flags = cut["disp_flags"][0], cut["ret_flags"][0]
+        self.ptrs = [cut[n][1] for n in ("cnt_all", "cnt_flags", "recv_x", "recv_meta", "disp_flags", "ret_y", "ret_flags")]
+        self.heap = heap
+        self.epoch = 0
+        # local scratch of the plan
+        el = experts // world
+        self.pair_dst_rank = torch.empty(self.pairs_cap, dtype=i32, device=dev)
+        self.pair_dst_row = torch.empty(self.pairs_cap, dtype=i32, device=dev)
+        self.expert_offsets = torch.zeros(el + 1, dtype=i32, device=dev)
+        self.work = torch.zeros((el + self.cap_rows // 16 + 1, 2), dtype=i32, device=dev)
+        self.n_work = torch.zeros(1, dtype=i32, device=dev)
+        self.recv_rows = torch.zeros(1, dtype=i32, device=dev)
+        self.done = torch.zeros(2, dtype=i32, device=dev)
+        self.pair_index = torch.arange(self.pairs_cap, dtype=i32, device=dev)
+
+    @staticmethod
+    def heap_bytes(hidden: int, dtype: torch.dtype, world: int, experts: int, top_k: int, tokens_cap: int,
+                   slab_factor: float = 2.0) -> int:
+        pairs = tokens_cap * top_k
+        cap = int(min(pairs * world, max(256, slab_factor * pairs)))
+        cap = (cap + 127) // 128 * 128
+        i32 = torch.int32
+        return SymmetricHeap.bytes_for([((world * experts,), i32), ((8,), i32), ((cap, hidden), dtype), ((cap, 2), i32),
+                                        ((8,), i32), ((pairs, hidden), dtype), ((8,), i32)])
+
+    def eligible(self, tokens_total: int) -> bool:
+        """Prefill-sized batches whose rows split evenly into whole 128-row tiles per rank."""
+        return (tokens_total % (128 * self.world) == 0 and 0 < tokens_total // self.world <= self.tokens_cap)
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+
 class TPComm:
     def __init__(self, slots: List[_Slot], max_rows: int, hidden: int, dtype: torch.dtype, rank: int, world: int,
                  prefill: Optional[PrefillBuffers] = None) -> None:
@@ -252,6 +319,16 @@ class TPComm:
 
 
 _COMM: Optional[TPComm] = None
+_EP_COMM: Optional[EPComm] = None
+
+
+def get_ep_comm() -> Optional[EPComm]:
+    return _EP_COMM
+
+
+def set_ep_comm(comm: Optional[EPComm]) -> None:
+    global _EP_COMM
+    _EP_COMM = comm
 
 
 def get_tp_comm() -> Optional[TPComm]:

@@ -87,12 +87,16 @@ class AWQLinearMethod(LinearMethodBase):
         scale = layer.scales.data.t().contiguous()      # [N, K/g]
         for name in ("qweight", "qzeros", "scales"):
             delattr(layer, name)
+        layer.w4_interleaved = packed.is_cuda     # GPU: nibble order the GEMM kernel expands fastest
+        if layer.w4_interleaved:
+            packed = ops.w4a16_interleave(packed)
         layer.register_parameter("weight_packed", nn.Parameter(packed, requires_grad=False))
         layer.register_parameter("weight_zeros", nn.Parameter(zeros, requires_grad=False))
         layer.register_parameter("weight_scale", nn.Parameter(scale, requires_grad=False))
 
     def apply(self, layer, x, bias=None, residual=None):
-        y = ops.w4a16_gemm(x, layer.weight_packed, layer.weight_scale, layer.weight_zeros, layer.w4_group, bias)
+        y = ops.w4a16_gemm(x, layer.weight_packed, layer.weight_scale, layer.weight_zeros, layer.w4_group, bias,
+                            interleaved=getattr(layer, "w4_interleaved", False))
         return y if residual is None else y + residual
 
 

@@ -60,6 +60,10 @@ class CompressedTensorsW4A16Method(LinearMethodBase):
 
     def process_weights_after_loading(self, layer) -> None:
         layer.weight_packed.data = layer.weight_packed.data.contiguous()
+        if layer.weight_packed.is_cuda and not getattr(layer, "w4_interleaved", False):
+            # GPU: nibble order the GEMM kernel expands fastest
+            layer.weight_packed.data = ops.w4a16_interleave(layer.weight_packed.data)
+            layer.w4_interleaved = True
         layer.weight_scale.data = layer.weight_scale.data.contiguous()
         # the fused projections were assembled shard by shard; record the true local shape
         layer.weight_shape.data = torch.tensor(
@@ -67,7 +71,8 @@ class CompressedTensorsW4A16Method(LinearMethodBase):
             device=layer.weight_shape.device)
 
     def apply(self, layer, x, bias=None, residual=None):
-        y = ops.w4a16_gemm(x, layer.weight_packed, layer.weight_scale, None, layer.w4_group, bias)
+        y = ops.w4a16_gemm(x, layer.weight_packed, layer.weight_scale, None, layer.w4_group, bias,
+                           interleaved=getattr(layer, "w4_interleaved", False))
         return y if residual is None else y + residual
 
 

@@ -101,6 +101,9 @@ class GPTQLinearMethod(LinearMethodBase):
         scale = layer.scales.data.t().contiguous()                   # [N, K/g]
         for name in ("qweight", "qzeros", "scales", "g_idx"):
             delattr(layer, name)
+        layer.w4_interleaved = packed.is_cuda     # GPU: nibble order the GEMM kernel expands fastest
+        if layer.w4_interleaved:
+            packed = ops.w4a16_interleave(packed)
         layer.register_parameter("weight_packed", nn.Parameter(packed, requires_grad=False))
         layer.register_parameter("weight_zeros", nn.Parameter(zeros, requires_grad=False))
         layer.register_parameter("weight_scale", nn.Parameter(scale, requires_grad=False))
@@ -109,7 +112,8 @@ class GPTQLinearMethod(LinearMethodBase):
         perm = getattr(layer, "act_perm", None)
         if perm is not None:
             x = x.index_select(-1, perm)
-        y = ops.w4a16_gemm(x, layer.weight_packed, layer.weight_scale, layer.weight_zeros, layer.w4_group, bias)
+        y = ops.w4a16_gemm(x, layer.weight_packed, layer.weight_scale, layer.weight_zeros, layer.w4_group, bias,
+                            interleaved=getattr(layer, "w4_interleaved", False))
         return y if residual is None else y + residual
 
 

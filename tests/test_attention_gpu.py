@@ -171,3 +171,31 @@ def test_kv_write_kernels_on_head_major_pool():
     ops.check_status()
     assert torch.equal(kc[loc], k) and torch.equal(vc[loc], v)
     assert torch.equal(pool.store[0, 0, 2, loc], k[:, 2])
+
+
+@pytest.mark.parametrize("window,cap", [(64, 0.0), (100, 0.0), (1, 0.0), (4096, 0.0), (0, 30.0), (150, 20.0)])
+@pytest.mark.parametrize("seq_lens,prefix_lens", [([300], [0]), ([700, 33], [0, 0]), ([200, 130], [64, 1]), ([1000], [873])])
+def test_prefill_sliding_window_and_soft_cap(window, cap, seq_lens, prefix_lens):
+    """Sliding window (each query sees its last ``window`` keys) and soft-capped scores as options of the
+    tcgen05 prefill kernel, against the fp32 statement."""
+    s = _setup(seq_lens, prefix_lens, 16, 8, seed=window + int(cap))
+    scale = D ** -0.5 * (3.0 if cap else 1.0)      # larger scores so that the cap bites
+    got = ops.attention_prefill(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], s["pre"], s["q_start"], scale,
+                                max_q_len=s["max_q"], window=window or None, logit_cap=cap)
+    ops.check_status()
+    want = ref.attention_prefill(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], s["pre"], s["q_start"], scale,
+                                 window=window or None, logit_cap=cap)
+    assert _err(got, want) < 3e-2
+
+
+@pytest.mark.parametrize("window,cap", [(64, 0.0), (129, 0.0), (1, 0.0), (5000, 0.0), (0, 30.0), (700, 20.0)])
+@pytest.mark.parametrize("seq_lens", [[1], [65], [500], [2048], [1, 700, 64, 129]])
+def test_decode_sliding_window_and_soft_cap(window, cap, seq_lens):
+    s = _head_major(_setup(seq_lens, [x - 1 for x in seq_lens], 32, 8, seed=1), "pages", seed=3)
+    scale = D ** -0.5 * (3.0 if cap else 1.0)
+    got = ops.attention_decode(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], scale, max_seq_len=max(seq_lens),
+                               window=window or None, logit_cap=cap)
+    ops.check_status()
+    want = ref.attention_decode(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], scale, window=window or None,
+                                logit_cap=cap)
+    assert _err(got, want) < 3e-2

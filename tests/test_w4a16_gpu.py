@@ -53,3 +53,17 @@ def test_w4a16_expansion_is_exact():
     w = ref.dequant_w4(qw, sc.float(), None, group)
     want = w.to(torch.bfloat16)[:, cols].t()
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("M,N,K,group,zeros,dtype", [(8, 512, 1024, 128, False, torch.bfloat16), (8, 4096, 4096, 128, True, torch.bfloat16),
+                                                     (300, 384, 2048, 64, True, torch.float16), (1, 256, 256, 128, False, torch.bfloat16)])
+def test_w4a16_interleaved_nibbles_give_the_same_bits(M, N, K, group, zeros, dtype):
+    """The loaders re-order the nibbles of every word for the kernel's fast expansion; the product must be
+    bit-identical to the natural-order path on the same weights."""
+    x, qw, sc, z, b = _case(M, N, K, group, zeros=zeros, bias=True, dtype=dtype, seed=M + K)
+    natural = ops.w4a16_gemm(x, qw, sc, z, group, b)
+    il = ops.w4a16_interleave(qw)
+    assert torch.equal(ops.w4a16_deinterleave(il), qw)
+    fast = ops.w4a16_gemm(x, il, sc, z, group, b, interleaved=True)
+    ops.check_status()
+    assert torch.equal(natural, fast)

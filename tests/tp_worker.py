@@ -184,6 +184,11 @@ def run(out_path: str, device: str, dtype_name: str) -> None:
         if device != "cpu":
             torch.cuda.synchronize()
         assert _comm().heap.check_guards() == [], "a kernel wrote outside a symmetric buffer"
+    if os.environ.get("TP_TEST_EXPECT_EP_EXCHANGE") == "1":
+        from mllm_b200.parallel.symm import get_ep_comm
+
+        assert get_ep_comm() is not None and get_ep_comm().epoch > 0, "the expert-parallel exchange was not used"
+        assert get_ep_comm().heap.check_guards() == [], "a kernel wrote outside an exchange buffer"
     if os.environ.get("TP_TEST_EXPECT_FUSED_PREFILL") == "1":
         from mllm_b200.parallel.symm import get_tp_comm
 
