@@ -67,6 +67,11 @@ struct KParams {
   // that rank's inbox (rs_out[owner], this rank's slot) and, once all column tiles of the row tile
   // have been stored, rs_flags[owner][local tile * 8 + rs_rank] is set to rs_epoch
   int rs_tp, rs_rank, rs_tiles_per_rank;
+  // Row tiles are visited starting rs_shift tiles (of this kernel's row-tile size) further on, modulo the tile
+  // count: rank r begins with the rows of owner r + 1 and ends with its own, so that at any moment the ranks
+  // store into DIFFERENT owners' inboxes.  In the same order everywhere they would all push to owner 0 first
+  // and share that one GPU's NVLink ingress while the others' links idle.
+  int rs_shift;
   uint32_t rs_epoch;
   int64_t rs_ld;
   void* rs_out[8];
@@ -268,6 +273,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
       const int gsize = min(p.tiles_r - first, kGroup);
       const int in = tile - g * per_group;
       tr = first + in % gsize;
+      if (p.rs_shift > 0) tr = (tr + p.rs_shift) % p.tiles_r;
       tc = in / gsize;
       kb0 = 0;
       kb1 = p.k_blocks;
@@ -811,7 +817,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_con
 constexpr int kPairBN = 256;
 constexpr int kPairStageBytes = 2 * kBM * kRowBytes;            // A half-tile + B half-tile: 32 KB
 constexpr int kPairStages = 6;
-constexpr int kPairSmem = kPairStages * kPairStageBytes + 1024 + 512;
+constexpr int kPairSmem = kPairStages * kPairStageBytes + 1024 + 512 + kEpiStagingBytes;
 
 // TMA load whose completion bytes are counted on a barrier that may live in the partner CTA
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
@@ -870,6 +876,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_consta
   uint64_t* acc_empty = acc_full + 2;              // used in the leader: 256 epilogue threads of the pair
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  uint32_t* rs_stored = tmem_holder + 2;   // reduce-scatter: (epilogue warp, tile) store batches issued so far
+  uint8_t* epi_staging = reinterpret_cast<uint8_t*>(bars) + 512;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -886,6 +894,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_consta
       mbar_init(&acc_empty[a], 256);
     }
     *abort_flag = 0;
+    *rs_stored = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_row);
     tma_prefetch_desc(&tm_col);
@@ -914,6 +923,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_consta
     const int gsize = min(p.tiles_r - first, kGroup);
     const int in = tile - g * per_group;
     tr = first + in % gsize;
+    if (p.rs_shift > 0) tr = (tr + p.rs_shift) % p.tiles_r;
     tc = in / gsize;
     return true;
   };
@@ -1016,6 +1026,38 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_consta
       }
     }
     if (!ok) give_up(kStatusPipelineTimeout);
+  } else if (warp == 3 && lane == 0 && p.rs_tp > 0) {
+    // ------------------------------ reduce-scatter publisher (both CTAs) ------------------
+    // as in the one-CTA kernel: fence once per tile after the four epilogue warps have issued its stores,
+    // count the tile in, and raise the owner's flag when the last column tile of a 128-row tile is done
+    int tr, tc;
+    for (int idx = 0; get_tile(idx, tr, tc); ++idx) {
+      const uint32_t want = 4u * static_cast<uint32_t>(idx + 1);
+      bool seen = false;
+      const uint64_t t0 = global_ns();
+      for (uint32_t i = 0;; ++i) {
+        if (ld_acquire_cta_smem(rs_stored) >= want) {
+          seen = true;
+          break;
+        }
+        __nanosleep(100);
+        if ((i & 31u) == 31u && (*abort_flag || global_ns() - t0 > kPipelineWaitNs)) break;
+      }
+      if (!seen) {
+        give_up(kStatusPipelineTimeout);
+        break;
+      }
+      __threadfence_system();
+      const int tr128 = tr * 2 + static_cast<int>(rank);
+      const int owner = tr128 / p.rs_tiles_per_rank;
+      const int local_tile = tr128 - owner * p.rs_tiles_per_rank;
+      const int old = atomicAdd(&p.rs_count[tr128], 1);
+      if (old == p.tiles_c - 1) {
+        p.rs_count[tr128] = 0;  // self-reset for the next launch
+        __threadfence_system();
+        st_release_sys(p.rs_flags[owner] + local_tile * 8 + p.rs_rank, p.rs_epoch);
+      }
+    }
   } else if (warp >= 4) {
     // ------------------------------ epilogue (both CTAs) ----------------------------------
     const int ew = warp - 4;
@@ -1037,6 +1079,63 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_row, const __grid_consta
       const bool row_ok = row < p.m;
       const int64_t col0 = static_cast<int64_t>(tc) * kOutCols;
       const float sa = (p.is_int8 && row_ok) ? p.a_scale[row] : 1.f;
+      if constexpr (!SWIGLU) {
+        if (p.rs_tp > 0) {
+          // reduce-scatter: 64 output columns at a time are rounded, parked in shared memory and written so that
+          // eight lanes cover 128 contiguous bytes of one row of the owner's inbox (full-line peer stores)
+          uint8_t* stage_buf = epi_staging + ew * (32 * kStageRowBytes);
+          const int tr128 = tr * 2 + static_cast<int>(rank);
+          const int owner = tr128 / p.rs_tiles_per_rank;
+          const int local_tile = tr128 - owner * p.rs_tiles_per_rank;
+          uint16_t* dst_base = static_cast<uint16_t*>(p.rs_out[owner]);
+          const int64_t dst_row0 = static_cast<int64_t>(local_tile) * kBM + ew * 32;
+          const int64_t tile_row0 = static_cast<int64_t>(tr128) * kBM + ew * 32;
+#pragma unroll 1
+          for (int c = 0; c < kOutCols; c += 64) {
+            uint32_t packed[32];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t r0[32];
+              tmem_ld_32x32(t_base + c + h * 32, r0);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; j += 2) {
+                float f[2];
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                  const int64_t col = col0 + c + h * 32 + j + q;
+                  float x = acc_to_float(r0[j + q], p.is_int8);
+                  if (p.is_int8 && col < n_out) x *= sa * p.b_scale[col];
+                  if (p.bias != nullptr && col < n_out) x += load_out1(p.bias, col, p.out_f16);
+                  f[q] = x;
+                }
+                packed[h * 16 + j / 2] = pack_out2(f[0], f[1], p.out_f16);
+              }
+            }
+            uint4* my_row = reinterpret_cast<uint4*>(stage_buf + lane * kStageRowBytes);
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              my_row[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = i * 4 + (lane >> 3);
+              const int piece = lane & 7;
+              const int64_t col = col0 + c + piece * 8;
+              if (tile_row0 + r < p.m && col < n_out) {
+                const uint4 v = *reinterpret_cast<const uint4*>(stage_buf + r * kStageRowBytes + piece * 16);
+                *reinterpret_cast<uint4*>(dst_base + (dst_row0 + r) * p.rs_ld + col) = v;
+              }
+            }
+            __syncwarp();
+          }
+          __syncwarp();
+          if (lane == 0) red_add_release_cta_smem(rs_stored, 1u);
+          tc_fence_before_sync();
+          mbar_arrive_cluster(mapa_smem(smem_u32(&acc_empty[acc]), 0));
+          continue;
+        }
+      }
 #pragma unroll 1
       for (int c = 0; c < kOutCols; c += 32) {
         uint32_t r0[32], r1[32];
@@ -1302,7 +1401,10 @@ int launch_gemm(const GemmArgs& a, cudaStream_t s) {
     // ---- two-CTA tiling: 256 x 256 tiles per pair of SMs, when there are enough of them to fill the GPU ----
     static const int pair_knob = env_int("MLLM_B200_GEMM_PAIR", 1);
     const int64_t tiles_pair = static_cast<int64_t>((a.m + 2 * kBM - 1) / (2 * kBM)) * ((a.n + kPairBN - 1) / kPairBN);
-    if (pair_knob && a.rs_tp == 0 && a.n % 256 == 0 && tiles_pair >= num_sms / 2) {
+    const bool pair_rs_ok = a.rs_tp == 0 || (!a.swiglu && (a.m / kBM / a.rs_tp) % 2 == 0);
+    const int rs_first_owner = a.rs_tp > 0 ? (a.rs_rank + 1) % a.rs_tp : 0;
+    if (pair_knob && a.n % 256 == 0 && tiles_pair >= num_sms / 2 && pair_rs_ok) {
+      if (a.rs_tp > 0) p.rs_shift = rs_first_owner * (p.rs_tiles_per_rank / 2);
       p.tiles_r = (a.m + 2 * kBM - 1) / (2 * kBM);
       p.tiles_c = (a.n + kPairBN - 1) / kPairBN;
       p.idesc = umma_idesc(2 * kBM, kPairBN, c_fmt, ab_fmt, ab_fmt);
@@ -1320,6 +1422,7 @@ int launch_gemm(const GemmArgs& a, cudaStream_t s) {
     }
     p.tiles_r = (a.m + kBM - 1) / kBM;
     p.tiles_c = (a.n + bn - 1) / bn;
+    if (a.rs_tp > 0) p.rs_shift = rs_first_owner * p.rs_tiles_per_rank;
     p.idesc = umma_idesc(kBM, bn, c_fmt, ab_fmt, ab_fmt);
     if (!make_operand_map(&tm_row, a.a, a.m, a.k, a.lda, eb, type, kBM)) return -2;
     if (!make_operand_map(&tm_col, a.b, a.n, a.k, a.ldb, eb, type, bn)) return -2;

@@ -150,16 +150,22 @@ def run(out_path: str, device: str, dtype_name: str) -> None:
                                          extend_seq_lens_cpu=[L] * B, extend_prefix_lens_cpu=[0] * B)
     out = mr.forward(fb)
     outs = [out.next_token_logits.float().cpu()]
-    nxt = mr.sample(out).to(dev)          # greedy; under pipeline parallelism the ids come from the last stage
+    # The decode inputs are fixed ids, not the sampled ones: with random weights the two best logits of a row
+    # can lie closer than the 16-bit rounding differences between two layouts, and one flipped token would
+    # make every later step incomparable.  The sampler still runs (under pipeline parallelism the ids come
+    # from the last stage).
+    forced = torch.randint(0, cfg.vocab_size, (2, B))
+    mr.sample(out)
     cur = L
-    for _ in range(2):
+    for step in range(2):
+        nxt = forced[step].to(dev)
         loc1 = mr.token_to_kv_pool_allocator.alloc(B)
         mr.req_to_token_pool.req_to_token[sl.long(), cur] = loc1.int()
         cur += 1
         fb = mr.prepare_forward_batch_decode(nxt, sl, torch.full((B,), cur, device=dev), loc1, max_seq_len=cur)
         out = mr.forward(fb)
         outs.append(out.next_token_logits.float().cpu())
-        nxt = mr.sample(out).to(dev)
+        mr.sample(out)
     if world > 1 and pp == 1 and hasattr(mr.model, "pick_greedy"):
         # greedy decoding without gathering logits: per-rank best candidate + one tiny all-gather must agree with
         # the argmax over the full vocabulary (columns that pad the vocabulary must never win)
