@@ -17,6 +17,7 @@
 #include <algorithm>
 
 #include <cstdlib>
+#include <string>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -67,6 +68,12 @@ struct AttnParams {
   int window;              // sliding window: a query at position i sees keys i - window + 1 .. i (0 = everything)
   float logit_cap;         // soft cap: score = cap * tanh(score / cap) before the softmax (0 = off)
   float scale;             // softmax scale (used with the soft cap)
+  float cap_pre, cap_post; // soft cap: score in the log2 domain = cap_post * tanh(raw * cap_pre)
+  int n_prefetch;          // decode: matrices whose rows are requested into L2 (see AttnArgs)
+  const uint8_t* pf_base[2];
+  int64_t pf_pitch[2];
+  int pf_row_bytes[2];
+  int pf_rows[2];
   uint32_t idesc_s, idesc_o;
 };
 
@@ -273,11 +280,17 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const AttnPar
     const int first_vis = (p.window > 0 && !(p.non_causal && !p.is_decode)) ? kv_limit - p.window + 1 - col0 : -(1 << 30);
     float sc[64];
     float m_tile = -INFINITY;
+    if (p.logit_cap > 0.f) {   // uniform branch, kept outside the loop: the tanh must not be paid by plain scores
+#pragma unroll
+      for (int c = 0; c < 64; ++c)
+        sc[c] = p.cap_post * tanhf(__uint_as_float(sraw[c >> 5][c & 31]) * p.cap_pre);
+    } else {
+#pragma unroll
+      for (int c = 0; c < 64; ++c) sc[c] = __uint_as_float(sraw[c >> 5][c & 31]) * p.scale_log2;
+    }
 #pragma unroll
     for (int c = 0; c < 64; ++c) {
-      float v = __uint_as_float(sraw[c >> 5][c & 31]);
-      v = p.logit_cap > 0.f ? p.logit_cap * tanhf(v * p.scale / p.logit_cap) * kLog2e : v * p.scale_log2;
-      v = (c <= visible && c >= first_vis) ? v : -INFINITY;
+      const float v = (c <= visible && c >= first_vis) ? sc[c] : -INFINITY;
       sc[c] = v;
       m_tile = fmaxf(m_tile, v);
     }
@@ -541,7 +554,21 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   const uint32_t tmem_base = *tmem_holder;
   const uint32_t tmem_s = tmem_base;            // two buffers of NQ columns
   const uint32_t tmem_o = tmem_base + 2 * NQ;   // NQ columns
-  // everything above touched no global memory; sequence lengths, slot table, Q and the KV pool are
+  // Requests to the L2 for the rows of the layer's next weight matrices: nothing in the stream writes model
+  // weights, so they go out before the stream-order wait.  The MMA warp has 31 idle lanes (and its first lane
+  // nothing to do until the first tile has landed); the CTAs of the grid share the rows.
+  if (warp == 5 && p.n_prefetch > 0) {
+    const int n_cta = gridDim.x * gridDim.y * gridDim.z;
+    const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    for (int i = 0; i < p.n_prefetch; ++i) {
+      for (int r = cta * 32 + lane; r < p.pf_rows[i]; r += n_cta * 32) {
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.pf_base[i] + r * p.pf_pitch[i]),
+                     "r"(p.pf_row_bytes[i])
+                     : "memory");
+      }
+    }
+  }
+  // everything above touched no activation; sequence lengths, slot table, Q and the KV pool are
   // written by earlier kernels of the stream
   pdl_wait();
 
@@ -730,12 +757,17 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       const int tok_pos = kv_begin + t * kDT + tid;
       const bool tok_ok = tok_pos < kv_end && tok_pos >= kv_lo;
       float* redt = red + (t & 1) * 4 * NQ;
+      if (p.logit_cap > 0.f) {   // uniform branch outside the loop: plain scores pay one multiply
+#pragma unroll
+        for (int c = 0; c < NQ; ++c) sc[c] = p.cap_post * tanhf(sc[c] * p.cap_pre);
+      } else {
+#pragma unroll
+        for (int c = 0; c < NQ; ++c) sc[c] *= p.scale_log2;
+      }
 #pragma unroll
       for (int c = 0; c < NQ; ++c) {
         if (c < g) {
-          const float capped = p.logit_cap > 0.f ? p.logit_cap * tanhf(sc[c] * p.scale / p.logit_cap) * kLog2e
-                                                 : sc[c] * p.scale_log2;
-          sc[c] = tok_ok ? capped : -INFINITY;
+          sc[c] = tok_ok ? sc[c] : -INFINITY;
           const float wm = warp_max(sc[c]);
           if (lane == 0) redt[warp * NQ + c] = wm;
         }
@@ -870,6 +902,408 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Prefill kernel, warp-specialised.  A CTA owns one request, one KV head and TWO tiles of 128 rows (a row is a
+// (query token, query head of the GQA group) pair, as above), so every K/V tile that reaches shared memory
+// serves both; KV tiles hold 128 tokens.  The CTA's roles meet only at mbarriers:
+//   warps 0-3  softmax of row tile A      warps 4-7  softmax of row tile B
+//   warp  8    producer: the decode kernel's TMA path (2 KB boxes over runs of 16 consecutive slots, else
+//              gather4 by row index) into a two-slot K ring and a single V slot
+//   warp  9    one thread issues the MMAs.  Tensor memory holds S_A, S_B (128 columns each) and O_A, O_B.
+// A softmax thread pulls its whole S row (128 scores) into registers with four tcgen05.ld and releases the S
+// buffer at once, so the scores of tile t+1 are computed while the exponentials of tile t are; P*V of tile t
+// runs under the softmax of tile t+1.  K is fetched two tiles ahead, V one.  The running maximum and the row
+// sum are kept in several independent chains (a single chain of 128 dependent operations would cost more than
+// the exponentials).  Tiles that need no causal / window mask and no soft cap take one FMA and one exponential
+// per score.
+// ---------------------------------------------------------------------------------------------
+constexpr int kPfThreads = 320;
+constexpr int kPfTile = 128;                    // KV tokens per tile
+constexpr int kPfHalf = 128 * 128;              // 16 KB: 128 rows of one 128-byte swizzle span
+constexpr int kPfTileBytes = 2 * kPfHalf;       // 32 KB: a Q tile, a K or V tile, or one group's P tile
+constexpr int kPfSmem = (2 + 2 + 3) * kPfTileBytes + 1024 + 256;
+
+__global__ void __launch_bounds__(kPfThreads, 1)
+attn_prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                       const __grid_constant__ CUtensorMap tm_k_run, const __grid_constant__ CUtensorMap tm_v_run,
+                       const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;                             // two row tiles
+  uint8_t* sP = sQ + 2 * kPfTileBytes;            // two row tiles of probabilities
+  uint8_t* sK = sP + 2 * kPfTileBytes;            // two K tiles
+  uint8_t* sV = sK + 2 * kPfTileBytes;            // one V tile
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + kPfTileBytes);
+  uint64_t* k_full = bars;             // [2] TMA transaction bytes
+  uint64_t* k_empty = bars + 2;        // [2] tcgen05.commit
+  uint64_t* v_full = bars + 4;         // TMA transaction bytes
+  uint64_t* v_empty = bars + 5;        // tcgen05.commit
+  uint64_t* s_full = bars + 6;         // [2] tcgen05.commit: scores of a group are in tensor memory
+  uint64_t* s_free = bars + 8;         // [2] 128 threads: the group holds its scores in registers
+  uint64_t* p_full = bars + 10;        // [2] 128 threads: the group has written P (and rescaled O)
+  uint64_t* o_done = bars + 12;        // [2] tcgen05.commit: the group's P*V has finished
+  uint64_t* q_full = bars + 14;        // 256 threads: both Q tiles are in shared memory
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 15);
+  int* fail_flag = reinterpret_cast<int*>(tmem_holder + 1);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int b = blockIdx.z;
+  const int hk = blockIdx.y;
+  const int g = p.group;
+  const int tpt = p.tokens_per_tile;             // query tokens per row tile
+  pdl_wait();
+
+  const int req = p.req_pool_indices[b];
+  const int seq_len = p.seq_lens[b];
+  const int prefix = p.prefix_lens[b];
+  const int q_len = seq_len - prefix;
+  const int q0 = (static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)) * 2 * tpt;   // long rows first
+  if (q0 >= q_len) return;
+  const int q_row0 = p.q_start[b];
+  const int kv_begin = (p.window > 0 && !p.non_causal) ? max(0, prefix + q0 - p.window + 1) / kPfTile * kPfTile : 0;
+  const int kv_end = p.non_causal ? seq_len : min(seq_len, prefix + min(q_len, q0 + 2 * tpt));
+  const int n_tiles = (kv_end - kv_begin + kPfTile - 1) / kPfTile;   // >= 1: the tile's first row sees itself
+
+  if (tid == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_free[i], 128);
+      mbar_init(&p_full[i], 128);
+      mbar_init(&o_done[i], 1);
+    }
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
+    mbar_init(q_full, 256);
+    *fail_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+    tma_prefetch_desc(&tm_k_run);
+    tma_prefetch_desc(&tm_v_run);
+  }
+  __syncthreads();
+  if (warp == 9) {
+    tmem_alloc(tmem_holder, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 8) {
+    // =============================== producer warp ===============================
+    // Order of the copies: K0, K1, V0, K2, V1, K3, V2, ...  (K two tiles ahead of the tile being multiplied, V one)
+    const int* rtt = p.req_to_token + static_cast<int64_t>(req) * p.rtt_stride;
+    bool ok_all = true, bad = false;
+    // lane = four consecutive tokens; a quad = 16 tokens, one 2 KB box per 64-feature half when their slots
+    // are consecutive
+    const int grp = lane >> 2, sub = lane & 3;
+    auto load_tile = [&](int t, bool is_v) {
+      int cur[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int tk = min(kv_begin + t * kPfTile + grp * 16 + sub * 4 + j, kv_end - 1);
+        cur[j] = __ldg(rtt + tk);
+        if (cur[j] < 0 || cur[j] >= p.num_slots) {
+          bad = true;
+          cur[j] = 0;
+        }
+      }
+      bool run = p.kv_runs != 0;
+      const int first = __shfl_sync(0xffffffffu, cur[0], lane & ~3);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int tk = kv_begin + t * kPfTile + grp * 16 + sub * 4 + j;
+        run = run && (tk >= kv_end || cur[j] == first + sub * 4 + j);   // tokens past the end are masked
+      }
+      const uint32_t votes = __ballot_sync(0xffffffffu, run);
+      run = ((votes >> (lane & ~3)) & 0xFu) == 0xFu && first + 16 <= p.num_slots;
+      uint64_t* full = is_v ? v_full : &k_full[t & 1];
+      uint64_t* empty = is_v ? v_empty : &k_empty[t & 1];
+      const uint32_t ph = is_v ? (t & 1) : ((t >> 1) & 1);
+      if (!mbar_wait(empty, ph ^ 1, fail_flag)) ok_all = false;
+      if (!__all_sync(0xffffffffu, ok_all)) {
+        ok_all = false;
+        return;
+      }
+      if (lane == 0) mbar_arrive_expect_tx(full, kPfTileBytes);
+      __syncwarp();
+      uint8_t* tile = is_v ? sV : sK + (t & 1) * kPfTileBytes;
+      if (run) {
+        const int row0 = first * p.kv_row_mul + hk * p.kv_row_add;
+        if (sub < 2)
+          tma_load_2d(tile + sub * kPfHalf + grp * 16 * 128, is_v ? &tm_v_run : &tm_k_run, full, sub * 64, row0);
+      } else {
+        int rows[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) rows[j] = cur[j] * p.kv_row_mul + hk * p.kv_row_add;
+        const int off = (grp * 16 + sub * 4) * 128;
+        tma_gather4(tile + off, is_v ? &tm_v : &tm_k, full, 0, rows);
+        tma_gather4(tile + kPfHalf + off, is_v ? &tm_v : &tm_k, full, 64, rows);
+      }
+    };
+    load_tile(0, false);
+    if (ok_all && n_tiles > 1) load_tile(1, false);
+    for (int t = 0; t < n_tiles && ok_all; ++t) {
+      load_tile(t, true);
+      if (ok_all && t + 2 < n_tiles) load_tile(t + 2, false);
+    }
+    if (bad && p.status != nullptr) atomicExch(p.status, kStatusBadIndex);
+    if (!ok_all) *fail_flag = 1;
+  } else if (warp == 9) {
+    // =============================== MMA issuer ===============================
+    if (lane == 0) {
+      bool ok_all = mbar_wait(q_full, 0, fail_flag);
+      auto wait_on = [&](uint64_t* bar, uint32_t parity) {
+        if (ok_all && !mbar_wait(bar, parity, fail_flag)) ok_all = false;
+        if (ok_all) tc_fence_after_sync();
+      };
+      auto issue_s = [&](int grp_i, int t) {        // S = Q K^T of group grp_i and KV tile t
+        const uint32_t qa = smem_u32(sQ + grp_i * kPfTileBytes);
+        const uint32_t ka = smem_u32(sK + (t & 1) * kPfTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t a_desc = umma_desc_k_sw128(qa + (kk >> 2) * kPfHalf + (kk & 3) * 32);
+          const uint64_t b_desc = umma_desc_k_sw128(ka + (kk >> 2) * kPfHalf + (kk & 3) * 32);
+          umma_f16(tmem_base + grp_i * 128, a_desc, b_desc, p.idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[grp_i]);
+      };
+      auto issue_pv = [&](int grp_i, int t) {       // O += P V
+        const uint32_t pa = smem_u32(sP + grp_i * kPfTileBytes);
+        const uint32_t va = smem_u32(sV);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t a_desc = umma_desc_k_sw128(pa + (kk >> 2) * kPfHalf + (kk & 3) * 32);
+          const uint64_t b_desc = umma_desc_mn_sw128(va + kk * 2048, kPfHalf, 1024);
+          umma_f16(tmem_base + 256 + grp_i * 128, a_desc, b_desc, p.idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&o_done[grp_i]);
+      };
+      wait_on(&k_full[0], 0);
+      if (ok_all) {
+        issue_s(0, 0);
+        issue_s(1, 0);
+        umma_commit(&k_empty[0]);
+      }
+      for (int t = 0; t < n_tiles && ok_all; ++t) {
+        if (t + 1 < n_tiles) {
+          // scores of the next tile, as soon as the groups hold the current ones in registers
+          wait_on(&k_full[(t + 1) & 1], ((t + 1) >> 1) & 1);
+          wait_on(&s_free[0], t & 1);
+          if (ok_all) issue_s(0, t + 1);
+          wait_on(&s_free[1], t & 1);
+          if (ok_all) {
+            issue_s(1, t + 1);
+            umma_commit(&k_empty[(t + 1) & 1]);
+          }
+        }
+        wait_on(v_full, t & 1);
+        wait_on(&p_full[0], t & 1);
+        if (ok_all) issue_pv(0, t);
+        wait_on(&p_full[1], t & 1);
+        if (ok_all) {
+          issue_pv(1, t);
+          umma_commit(v_empty);
+        }
+      }
+      if (!ok_all) *fail_flag = 1;
+    }
+  } else {
+    // =============================== softmax groups ===============================
+    const int grp_i = warp >> 2;                    // 0 = row tile A, 1 = row tile B
+    const int row = tid & 127;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tmem_s = tmem_base + grp_i * 128 + lane_base;
+    const uint32_t tmem_o = tmem_base + 256 + grp_i * 128 + lane_base;
+    const int tile_q0 = q0 + grp_i * tpt;           // first query token of this group's row tile
+    const int row_tok = row / g;
+    const int row_head = hk * g + row % g;
+    const bool row_valid = (row_tok < tpt) && (tile_q0 + row_tok < q_len);
+    const int kv_limit = p.non_causal ? seq_len - 1 : (row_valid ? prefix + tile_q0 + row_tok : prefix + q0);
+
+    // ---- Q tile of this group: 128 rows x 256 B ----
+    {
+      const uint16_t* qbase = static_cast<const uint16_t*>(p.q);
+      const uint32_t sq = smem_u32(sQ + grp_i * kPfTileBytes);
+      for (int c = row; c < kRows * 16; c += 128) {
+        const int r = c >> 4, ch = c & 15;
+        const int tok = r / g;
+        const bool ok = (tok < tpt) && (tile_q0 + tok < q_len);
+        const int head = hk * g + r % g;
+        const uint16_t* src = qbase + static_cast<int64_t>(q_row0 + (ok ? tile_q0 + tok : 0)) * p.q_stride +
+                              static_cast<int64_t>(head) * kD + ch * 8;
+        cp_async16(sq + swz_off(r, ch, kPfHalf), src, ok);
+      }
+      cp_async_commit();
+      cp_async_wait<0>();
+      fence_proxy_async_smem();
+      mbar_arrive(q_full);
+    }
+
+    float m_used = -INFINITY;   // running maximum in use for the exponent (log2 domain)
+    float l_sum = 0.f;
+    bool ok_all = true;
+    const uint32_t sp = smem_u32(sP + grp_i * kPfTileBytes) + row * 128;
+    const bool plain_scores = p.logit_cap <= 0.f;
+
+    for (int t = 0; t < n_tiles; ++t) {
+      if (!mbar_wait(&s_full[grp_i], t & 1, fail_flag)) {
+        ok_all = false;
+        break;
+      }
+      tc_fence_after_sync();
+      uint32_t raw[kPfTile];
+#pragma unroll
+      for (int c0 = 0; c0 < kPfTile; c0 += 32)
+        tmem_ld_32x32(tmem_s + c0, *reinterpret_cast<uint32_t(*)[32]>(&raw[c0]));
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&s_free[grp_i]);   // the scores of the next tile may overwrite the buffer
+
+      const int col0 = kv_begin + t * kPfTile;
+      const int visible = min(kv_limit, kv_end - 1) - col0;      // columns 0..visible are allowed
+      const int first_vis = (p.window > 0 && !p.non_causal) ? kv_limit - p.window + 1 - col0 : -(1 << 30);
+      const bool fast = __all_sync(0xffffffffu, plain_scores && visible >= kPfTile - 1 && first_vis <= 0);
+      float mul = p.scale_log2;
+      if (!fast) {
+        // masked / capped tile: turn the raw products into final scores in place
+        if (plain_scores) {
+#pragma unroll
+          for (int c = 0; c < kPfTile; ++c) raw[c] = __float_as_uint(__uint_as_float(raw[c]) * p.scale_log2);
+        } else {
+#pragma unroll 8
+          for (int c = 0; c < kPfTile; ++c)
+            raw[c] = __float_as_uint(p.cap_post * tanhf(__uint_as_float(raw[c]) * p.cap_pre));
+        }
+#pragma unroll
+        for (int c = 0; c < kPfTile; ++c)
+          raw[c] = (c <= visible && c >= first_vis) ? raw[c] : __float_as_uint(-INFINITY);
+        mul = 1.f;
+      }
+      float mx[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mx[i] = __uint_as_float(raw[i]);
+#pragma unroll
+      for (int c = 8; c < kPfTile; c += 8) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mx[i] = fmaxf(mx[i], __uint_as_float(raw[c + i]));
+      }
+      const float m_tile = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
+                                 fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7]))) * mul;   // mul > 0
+      float factor = 1.f;
+      bool need = false;
+      if (m_used == -INFINITY) {
+        m_used = m_tile;   // no visible key so far: the accumulator row is all zero, adopt without a rescale
+      } else if (m_tile > m_used + kRescaleThreshold) {
+        factor = exp2f(m_used - m_tile);
+        m_used = m_tile;
+        need = true;
+      }
+      const float m_exp = (m_used == -INFINITY) ? 0.f : m_used;
+      // exponentials, packed to 16 bits, kept in registers until the P buffer is free
+      uint32_t w[kPfTile / 2];
+      float ps[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < kPfTile / 2; ++i) {
+        const float p0 = fast_exp2(fmaf(__uint_as_float(raw[2 * i]), mul, -m_exp));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(raw[2 * i + 1]), mul, -m_exp));
+        ps[i & 3] += p0 + p1;
+        if (p.out_f16) {
+          __half2 h = __floats2half2_rn(p0, p1);
+          w[i] = *reinterpret_cast<uint32_t*>(&h);
+        } else {
+          w[i] = pack_bf16x2(p0, p1);
+        }
+      }
+      // the group's previous P*V must have finished before P is overwritten and O is rescaled
+      if (t > 0) {
+        if (!mbar_wait(&o_done[grp_i], (t - 1) & 1, fail_flag)) {
+          ok_all = false;
+          break;
+        }
+        tc_fence_after_sync();
+      }
+      if (__any_sync(0xffffffffu, need)) {
+        l_sum *= factor;
+#pragma unroll 1
+        for (int c = 0; c < kD; c += 32) {
+          uint32_t o[32];
+          tmem_ld_32x32(tmem_o + c, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+          tmem_st_32x32(tmem_o + c, o);
+        }
+        tmem_st_wait();
+      }
+      l_sum += (ps[0] + ps[1]) + (ps[2] + ps[3]);
+      // P in the operand layout: two 64-token halves of 128-byte rows, 16-byte chunks swizzled by the row
+#pragma unroll
+      for (int q16 = 0; q16 < 16; ++q16) {
+        const uint32_t dst = sp + (q16 >> 3) * kPfHalf + (((q16 & 7) ^ (row & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[4 * q16]), "r"(w[4 * q16 + 1]),
+                     "r"(w[4 * q16 + 2]), "r"(w[4 * q16 + 3])
+                     : "memory");
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(&p_full[grp_i]);
+    }
+    if (ok_all && !mbar_wait(&o_done[grp_i], (n_tiles - 1) & 1, fail_flag)) ok_all = false;
+    tc_fence_after_sync();
+    if (!ok_all) *fail_flag = 1;
+
+    // ---- epilogue: normalise and store this thread's output row ----
+    const float inv_l = l_sum > 0.f ? 1.f / l_sum : 0.f;
+    uint16_t* orow = static_cast<uint16_t*>(p.out) +
+                     (static_cast<int64_t>(q_row0 + (row_valid ? tile_q0 + row_tok : 0)) * p.hq + row_head) * kD;
+#pragma unroll 1
+    for (int c = 0; c < kD; c += 32) {
+      uint32_t o[32];
+      tmem_ld_32x32(tmem_o + c, o);
+      tmem_ld_wait();
+      if (row_valid && ok_all) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          uint4 v;
+          uint32_t* vv = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+          for (int k2 = 0; k2 < 4; ++k2) {
+            const float a = __uint_as_float(o[i + 2 * k2]) * inv_l;
+            const float bb = __uint_as_float(o[i + 2 * k2 + 1]) * inv_l;
+            if (p.out_f16) {
+              __half2 h = __floats2half2_rn(a, bb);
+              vv[k2] = *reinterpret_cast<uint32_t*>(&h);
+            } else {
+              vv[k2] = pack_bf16x2(a, bb);
+            }
+          }
+          *reinterpret_cast<uint4*>(orow + c + i) = v;
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*fail_flag) {
+    if (tid == 0 && p.status != nullptr) atomicExch(p.status, kStatusPipelineTimeout);
+    // copies of the producer may still be in flight: give them time to land before the CTA's memory is reused
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 9) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 // combine decode partials: out[b, h, :] = sum_s w_s * O_s with w_s = 2^(lse_s - max) / sum
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                   void* __restrict__ out, int hq, int splits, int out_f16) {
@@ -907,6 +1341,32 @@ int decode_num_splits(int batch, int hkv, int max_seq_len, int num_sms) {
   int splits = num_sms / ctas;
   splits = std::min(splits, std::max(1, tiles / 2));
   return std::max(1, std::min(splits, 64));
+}
+
+// Prefill through the warp-specialised kernel; returns 1 when this launch is not for it (storage that is neither
+// head-major nor slot-major, or MLLM_B200_ATTN_PREFILL=legacy) and the single-role kernel should run instead.
+int launch_prefill_ws(AttnParams p, const AttnArgs& a, cudaStream_t s) {
+  const char* knob = std::getenv("MLLM_B200_ATTN_PREFILL");   // read per call: tests switch it
+  const bool legacy = knob != nullptr && std::string(knob) == "legacy";
+  if (legacy || p.kv_row_mul == 0) return 1;
+  const int64_t rows = a.num_slots * static_cast<int64_t>(a.hkv);
+  if (rows >= (int64_t(1) << 31)) return 1;
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(attn_prefill_ws_kernel), kPfSmem) != cudaSuccess) return -3;
+  CUtensorMap tm_k, tm_v, tm_k_run, tm_v_run;
+  const int type = a.dt == kF16 ? 1 : 0;
+  if (!make_tma_operand_map(&tm_k, a.k_cache, rows, kD, kD, 2, type, 1)) return -2;
+  if (!make_tma_operand_map(&tm_v, a.v_cache, rows, kD, kD, 2, type, 1)) return -2;
+  if (!make_tma_operand_map(&tm_k_run, a.k_cache, rows, kD, kD, 2, type, 16)) return -2;
+  if (!make_tma_operand_map(&tm_v_run, a.v_cache, rows, kD, kD, 2, type, 16)) return -2;
+  const uint32_t fmt = a.dt == kF16 ? 0u : 1u;
+  p.idesc_s = umma_idesc(kRows, kPfTile, 1, fmt, fmt, 0, 0);
+  p.idesc_o = umma_idesc(kRows, kD, 1, fmt, fmt, 0, 1);
+  const int q_tiles = (a.max_q_len + 2 * p.tokens_per_tile - 1) / (2 * p.tokens_per_tile);
+  if (q_tiles <= 0) return 0;
+  const cudaError_t err = launch_pdl(attn_prefill_ws_kernel, dim3(q_tiles, a.hkv, a.batch), dim3(kPfThreads), kPfSmem, s,
+                                     tm_k, tm_v, tm_k_run, tm_v_run, p);
+  note_launch();
+  return err == cudaSuccess ? 0 : -4;
 }
 
 template <int NQ>
@@ -975,6 +1435,21 @@ int launch_attention(const AttnArgs& a, cudaStream_t s) {
   p.scale = a.scale;
   p.window = a.window > 0 ? a.window : 0;
   p.logit_cap = a.logit_cap > 0.f ? a.logit_cap : 0.f;
+  p.cap_pre = p.logit_cap > 0.f ? a.scale / p.logit_cap : 0.f;
+  p.cap_post = p.logit_cap * kLog2e;
+  p.n_prefetch = 0;
+  if (a.is_decode) {
+    for (int i = 0; i < a.n_prefetch && i < 2; ++i) {
+      const bool aligned = (reinterpret_cast<uintptr_t>(a.pf_base[i]) & 15) == 0 && (a.pf_pitch[i] & 15) == 0 &&
+                           (a.pf_row_bytes[i] & 15) == 0;
+      if (a.pf_base[i] == nullptr || a.pf_rows[i] <= 0 || a.pf_row_bytes[i] <= 0 || !aligned) continue;
+      p.pf_base[p.n_prefetch] = static_cast<const uint8_t*>(a.pf_base[i]);
+      p.pf_pitch[p.n_prefetch] = a.pf_pitch[i];
+      p.pf_row_bytes[p.n_prefetch] = a.pf_row_bytes[i];
+      p.pf_rows[p.n_prefetch] = a.pf_rows[i];
+      ++p.n_prefetch;
+    }
+  }
   const uint32_t fmt = a.dt == kF16 ? 0u : 1u;
   p.idesc_s = umma_idesc(kRows, kKV, 1, fmt, fmt, 0, 0);
   p.idesc_o = umma_idesc(kRows, kD, 1, fmt, fmt, 0, 1);
@@ -992,6 +1467,10 @@ int launch_attention(const AttnArgs& a, cudaStream_t s) {
       note_launch();
     }
     return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  }
+  if (!a.is_decode) {
+    const int rc = launch_prefill_ws(p, a, s);
+    if (rc <= 0) return rc;
   }
   if (a.is_decode) {
     grid = dim3(p.num_splits, a.hkv, a.batch);

@@ -156,6 +156,35 @@ def test_prefill_head_major_pool(seq_lens, prefix_lens):
     assert _err(got, want) < 3e-2
 
 
+@pytest.mark.parametrize("pattern", ["pages", "scattered"])
+def test_prefill_long_sequences_many_tiles(pattern):
+    """Benchmark-like shape: enough 128-token tiles that every ring slot and barrier phase of the warp-specialised
+    kernel wraps several times, with slots in pages of 16 (boxes) and scattered (row gathers)."""
+    s = _setup([2048, 1500], [0, 300], 32, 8, seed=5)
+    if pattern == "pages":
+        s = _head_major(s, "pages", seed=4)
+    scale = D ** -0.5
+    got = ops.attention_prefill(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], s["pre"], s["q_start"], scale,
+                                max_q_len=s["max_q"])
+    ops.check_status()
+    want = ref.attention_prefill(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], s["pre"], s["q_start"], scale)
+    assert _err(got, want) < 3e-2
+
+
+@pytest.mark.parametrize("seq_lens,prefix_lens", [([3], [0]), ([700, 33], [0, 0]), ([200, 130], [64, 1])])
+def test_prefill_single_role_kernel(monkeypatch, seq_lens, prefix_lens):
+    """The older kernel (every warp gathers, computes the softmax and issues in turn) still serves storage that
+    is neither head-major nor slot-major; the switch selects it for any storage."""
+    monkeypatch.setenv("MLLM_B200_ATTN_PREFILL", "legacy")
+    s = _setup(seq_lens, prefix_lens, 8, 2, seed=7)
+    scale = D ** -0.5
+    got = ops.attention_prefill(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], s["pre"], s["q_start"], scale,
+                                max_q_len=s["max_q"])
+    ops.check_status()
+    want = ref.attention_prefill(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], s["pre"], s["q_start"], scale)
+    assert _err(got, want) < 3e-2
+
+
 def test_kv_write_kernels_on_head_major_pool():
     """The stand-alone KV write and the fused norm + rotary + write kernel address the caches by strides."""
     from mllm_b200.mem_cache import KVPool
@@ -199,3 +228,19 @@ def test_decode_sliding_window_and_soft_cap(window, cap, seq_lens):
     want = ref.attention_decode(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], scale, window=window or None,
                                 logit_cap=cap)
     assert _err(got, want) < 3e-2
+
+
+def test_decode_with_weight_prefetch_hints_gives_the_same_output():
+    """The rows requested into the L2 for the layer's next GEMMs are a hint only: the output does not change
+    and the matrices are left as they were."""
+    s = _head_major(_setup([700, 64, 129], [699, 63, 128], 32, 8, seed=1), "pages", seed=3)
+    scale = D ** -0.5
+    w1 = torch.randn(512, 1024, device=DEV, dtype=torch.bfloat16)
+    w2 = torch.randn(300, 4096, device=DEV, dtype=torch.bfloat16)[:, :2048]      # pitch larger than the row
+    keep1, keep2 = w1.clone(), w2.clone()
+    plain = ops.attention_decode(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], scale, max_seq_len=700)
+    hinted = ops.attention_decode(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], scale, max_seq_len=700,
+                                  prefetch=[(w1, 1.0), (w2, 0.4)])
+    ops.check_status()
+    assert torch.equal(plain, hinted)
+    assert torch.equal(w1, keep1) and torch.equal(w2, keep2)

@@ -59,7 +59,8 @@ def test_embedding():
     assert torch.equal(ops.embedding(ids, table), table[ids])
 
 
-@pytest.mark.parametrize("tokens", [1, 2, 3, 17, 127, 128, 129])
+# long batches: a warp then owns several heads of its token (every 10th, every 2nd, all of them)
+@pytest.mark.parametrize("tokens", [1, 2, 3, 17, 127, 128, 129, 3000, 16384, 40000])
 @pytest.mark.parametrize("hq,hkv", [(16, 8), (32, 8), (4, 1)])
 def test_qk_norm_rope_kv_write(tokens, hq, hkv):
     torch.manual_seed(5)
@@ -68,7 +69,7 @@ def test_qk_norm_rope_kv_write(tokens, hq, hkv):
     qw = (1 + 0.1 * torch.randn(D, device=DEV)).bfloat16()
     kw = (1 + 0.1 * torch.randn(D, device=DEV)).bfloat16()
     pos = torch.randint(0, 4096, (tokens,), device=DEV)
-    slots = 300
+    slots = max(300, tokens + 8)
     loc = torch.randperm(slots - 1, device=DEV)[:tokens] + 1
     kc = torch.zeros(slots, hkv, D, device=DEV, dtype=torch.bfloat16)
     vc = torch.zeros_like(kc)
