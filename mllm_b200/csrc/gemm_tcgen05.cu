@@ -1432,6 +1432,12 @@ int launch_gemm(const GemmArgs& a, cudaStream_t s) {
     return launch_cfg<128, false, false>(tm_row, tm_col, p, grid, s);
   }
 
+  // ---- a handful of rows: stream the weights through registers (gemm_smallm.cu) ----
+  if (a.m <= 8) {
+    const int rc = launch_gemm_smallm(a, s);
+    if (rc <= 0) return rc;
+  }
+
   // ---- swap tiling: weights are the 128-row operand, the batch is MMA N ----
   int bn = 16;
   while (bn < a.m) bn <<= 1;

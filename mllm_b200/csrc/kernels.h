@@ -111,6 +111,9 @@ struct GemmArgs {
 // Returns 0 on success, a negative code when the shape is unsupported (caller falls back / raises).
 int launch_gemm(const GemmArgs& args, cudaStream_t s);
 size_t gemm_workspace_bytes(int m, int n, int k, int num_sms);
+// m <= 8, 16-bit operands: the weight matrix streamed through registers and warp-level MMAs (no tensor memory, no
+// shared-memory ring, no split of k between CTAs).  Returns 0 when launched, 1 when the shape is not for it.
+int launch_gemm_smallm(const GemmArgs& args, cudaStream_t s);
 
 // ----- W4A16 GEMM (4-bit weights expanded in shared memory, tcgen05) ----------------------------
 struct W4A16Args {

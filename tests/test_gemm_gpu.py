@@ -127,3 +127,36 @@ def test_gemm_small_batch_with_parameter_weights(m, n, k):
                           out_dtype=torch.float32)
     ops.check_status()
     assert _rel_err(y, want) < 3e-2
+
+
+@pytest.mark.parametrize("m", [1, 2, 5, 8])
+@pytest.mark.parametrize("n,k", [(4096, 4096), (6144, 4096), (4096, 12288), (1024, 256), (8, 512), (151936, 1024)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_streaming_gemm_for_a_handful_of_rows(m, n, k, dtype):
+    """Up to 8 rows and k a multiple of 256 take the register-streaming kernel (weights through warp-level MMAs,
+    no tensor memory); with a Parameter its weight loads go out before the stream-order wait."""
+    torch.manual_seed(m + n + k)
+    x = torch.randn(m, k, device=DEV, dtype=dtype)
+    w = torch.nn.Parameter(torch.randn(n, k, device=DEV, dtype=dtype) * (k ** -0.5), requires_grad=False)
+    b = torch.randn(n, device=DEV, dtype=dtype)
+    r = torch.randn(m, n, device=DEV, dtype=dtype)
+    want = ref.linear(x, w.data, out_dtype=torch.float32)
+    assert _rel_err(ops.linear(x, w), want) < 6e-3
+    assert _rel_err(ops.linear(x, w, bias=b, residual=r), ref.linear(x, w.data, b, r, out_dtype=torch.float32)) < 6e-3
+    # activations as a view with a larger row stride, plain-tensor weights
+    wide = torch.randn(m, k + 64, device=DEV, dtype=dtype)
+    assert _rel_err(ops.linear(wide[:, :k], w.data), ref.linear(wide[:, :k], w.data, out_dtype=torch.float32)) < 6e-3
+    ops.check_status()
+
+
+@pytest.mark.parametrize("m", [1, 3, 8])
+@pytest.mark.parametrize("inter,k", [(12288, 4096), (768, 2048), (128, 256)])
+def test_streaming_gemm_swiglu(m, inter, k):
+    torch.manual_seed(m + inter)
+    x = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(2 * inter, k, device=DEV, dtype=torch.bfloat16) * (k ** -0.5)  # [gate ; up]
+    wi = torch.nn.Parameter(ref.interleave_gate_up(w, ops.SWIGLU_BLOCK).contiguous(), requires_grad=False)
+    got = ops.linear_swiglu(x, wi)
+    ops.check_status()
+    want = ref.linear_swiglu(x.float(), w.float(), 0)
+    assert _rel_err(got, want) < 8e-3
