@@ -29,6 +29,7 @@ from ..engine.io_struct import AbortReq, BatchTokenIDOutput, FlushCacheReq, Shar
 from ..engine.sampling_params import SamplingParams
 from .model_runner_process import KVAllocationError, ModelRunnerProcess, Req
 
+from ..utils.profiling import nvtx_range
 logger = logging.getLogger(__name__)
 
 
@@ -229,15 +230,18 @@ class Scheduler:
             return None
         t0 = time.perf_counter()
         try:
-            if kind == "extend":
-                next_ids, produced, _ = self.mrp.extend(rows)
-                reqs = [rows[i][0] for i in produced]
-            else:
-                reqs = [q for q, _ in rows]
-                next_ids, _ = self.mrp.decode(reqs)
+            # one named range per pass (visible in timeline tools next to the kernels it launched)
+            with nvtx_range(f"scheduler.{kind}[{len(rows)}]"):
+                if kind == "extend":
+                    next_ids, produced, _ = self.mrp.extend(rows)
+                    reqs = [rows[i][0] for i in produced]
+                else:
+                    reqs = [q for q, _ in rows]
+                    next_ids, _ = self.mrp.decode(reqs)
         except KVAllocationError as exc:
             return self._shed_load(str(exc))
-        ids = next_ids.tolist() if next_ids is not None and len(reqs) else []  # the step's one device->host sync
+        with nvtx_range("scheduler.read_tokens"):
+            ids = next_ids.tolist() if next_ids is not None and len(reqs) else []  # the step's one device->host sync
         dt = time.perf_counter() - t0
         now = time.time()
         n_prefill = sum(n for q, n in rows if q in self.prefilling) if kind == "extend" else 0

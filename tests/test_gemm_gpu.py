@@ -130,7 +130,8 @@ def test_gemm_small_batch_with_parameter_weights(m, n, k):
 
 
 @pytest.mark.parametrize("m", [1, 2, 5, 8])
-@pytest.mark.parametrize("n,k", [(4096, 4096), (6144, 4096), (4096, 12288), (1024, 256), (8, 512), (151936, 1024)])
+@pytest.mark.parametrize("n,k", [(4096, 4096), (6144, 4096), (4096, 12288), (1024, 6144), (6144, 8192), (1024, 256), (8, 512),
+                                 (151936, 1024)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_streaming_gemm_for_a_handful_of_rows(m, n, k, dtype):
     """Up to 8 rows and k a multiple of 256 take the register-streaming kernel (weights through warp-level MMAs,
