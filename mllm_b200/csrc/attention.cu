@@ -69,11 +69,6 @@ struct AttnParams {
   float logit_cap;         // soft cap: score = cap * tanh(score / cap) before the softmax (0 = off)
   float scale;             // softmax scale (used with the soft cap)
   float cap_pre, cap_post; // soft cap: score in the log2 domain = cap_post * tanh(raw * cap_pre)
-  int n_prefetch;          // decode: matrices whose rows are requested into L2 (see AttnArgs)
-  const uint8_t* pf_base[2];
-  int64_t pf_pitch[2];
-  int pf_row_bytes[2];
-  int pf_rows[2];
   uint32_t idesc_s, idesc_o;
 };
 
@@ -554,21 +549,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   const uint32_t tmem_base = *tmem_holder;
   const uint32_t tmem_s = tmem_base;            // two buffers of NQ columns
   const uint32_t tmem_o = tmem_base + 2 * NQ;   // NQ columns
-  // Requests to the L2 for the rows of the layer's next weight matrices: nothing in the stream writes model
-  // weights, so they go out before the stream-order wait.  The MMA warp has 31 idle lanes (and its first lane
-  // nothing to do until the first tile has landed); the CTAs of the grid share the rows.
-  if (warp == 5 && p.n_prefetch > 0) {
-    const int n_cta = gridDim.x * gridDim.y * gridDim.z;
-    const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
-    for (int i = 0; i < p.n_prefetch; ++i) {
-      for (int r = cta * 32 + lane; r < p.pf_rows[i]; r += n_cta * 32) {
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.pf_base[i] + r * p.pf_pitch[i]),
-                     "r"(p.pf_row_bytes[i])
-                     : "memory");
-      }
-    }
-  }
-  // everything above touched no activation; sequence lengths, slot table, Q and the KV pool are
+  // everything above touched no global memory; sequence lengths, slot table, Q and the KV pool are
   // written by earlier kernels of the stream
   pdl_wait();
 
@@ -1437,19 +1418,6 @@ int launch_attention(const AttnArgs& a, cudaStream_t s) {
   p.logit_cap = a.logit_cap > 0.f ? a.logit_cap : 0.f;
   p.cap_pre = p.logit_cap > 0.f ? a.scale / p.logit_cap : 0.f;
   p.cap_post = p.logit_cap * kLog2e;
-  p.n_prefetch = 0;
-  if (a.is_decode) {
-    for (int i = 0; i < a.n_prefetch && i < 2; ++i) {
-      const bool aligned = (reinterpret_cast<uintptr_t>(a.pf_base[i]) & 15) == 0 && (a.pf_pitch[i] & 15) == 0 &&
-                           (a.pf_row_bytes[i] & 15) == 0;
-      if (a.pf_base[i] == nullptr || a.pf_rows[i] <= 0 || a.pf_row_bytes[i] <= 0 || !aligned) continue;
-      p.pf_base[p.n_prefetch] = static_cast<const uint8_t*>(a.pf_base[i]);
-      p.pf_pitch[p.n_prefetch] = a.pf_pitch[i];
-      p.pf_row_bytes[p.n_prefetch] = a.pf_row_bytes[i];
-      p.pf_rows[p.n_prefetch] = a.pf_rows[i];
-      ++p.n_prefetch;
-    }
-  }
   const uint32_t fmt = a.dt == kF16 ? 0u : 1u;
   p.idesc_s = umma_idesc(kRows, kKV, 1, fmt, fmt, 0, 0);
   p.idesc_o = umma_idesc(kRows, kD, 1, fmt, fmt, 0, 1);

@@ -771,8 +771,7 @@ void attention_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_c
 
 void attention_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& req_to_token,
                       const Tensor& req_pool_indices, const Tensor& seq_lens, double scale, Tensor& out,
-                      int64_t max_seq_len, int64_t window, double logit_cap, std::vector<Tensor> prefetch,
-                      std::vector<double> prefetch_fraction) {
+                      int64_t max_seq_len, int64_t window, double logit_cap) {
   check_half(q, "q");
   TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.stride(2) == 1 && q.stride(1) == 128, "q must be [B,Hq,128]");
   TORCH_CHECK(out.is_contiguous() && out.sizes() == q.sizes() && out.scalar_type() == q.scalar_type(), "out");
@@ -817,20 +816,6 @@ void attention_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
   a.window = static_cast<int>(window);
   a.logit_cap = static_cast<float>(logit_cap);
   a.dt = dtype_of(q);
-  // matrices (weights of the layer's next GEMMs) whose leading row bytes the kernel requests into the L2
-  TORCH_CHECK(prefetch.size() <= 2 && prefetch.size() == prefetch_fraction.size(), "prefetch: at most two matrices");
-  for (size_t i = 0; i < prefetch.size(); ++i) {
-    const Tensor& w = prefetch[i];
-    if (!w.defined() || !w.is_cuda() || w.dim() != 2 || w.stride(1) != 1 || w.get_device() != q.get_device()) continue;
-    const int64_t row_bytes = w.size(1) * w.element_size();
-    int64_t take = static_cast<int64_t>(row_bytes * std::min(1.0, std::max(0.0, prefetch_fraction[i]))) & ~int64_t(127);
-    if (take <= 0) continue;
-    a.pf_base[a.n_prefetch] = w.data_ptr();
-    a.pf_pitch[a.n_prefetch] = w.stride(0) * w.element_size();
-    a.pf_row_bytes[a.n_prefetch] = static_cast<int>(take);
-    a.pf_rows[a.n_prefetch] = static_cast<int>(w.size(0));
-    ++a.n_prefetch;
-  }
   const int rc = mb200::launch_attention(a, stream_of(q));
   TORCH_CHECK(rc == 0, "mllm_b200 attention_decode: unsupported configuration (code ", rc, ")");
 }

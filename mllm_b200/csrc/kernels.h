@@ -213,14 +213,6 @@ struct AttnArgs {
   int window;               // > 0: a query at position i sees keys i - window + 1 .. i only (causal attention)
   float logit_cap;          // > 0: scores pass through cap * tanh(score / cap) before the softmax
   DType dt;
-  // decode only: up to two read-only matrices (the weights the next kernels of the layer will stream) whose rows'
-  // first pf_row_bytes bytes the kernel asks the L2 to fetch while it works; the decode kernel is bound by
-  // latency, not bandwidth.  Pointers and pitches are multiples of 16 bytes.
-  int n_prefetch;
-  const void* pf_base[2];
-  int64_t pf_pitch[2];      // bytes between rows
-  int pf_row_bytes[2];      // bytes fetched per row (multiple of 16)
-  int pf_rows[2];
 };
 int launch_attention(const AttnArgs& args, cudaStream_t s);
 int decode_num_splits(int batch, int hkv, int max_seq_len, int num_sms);

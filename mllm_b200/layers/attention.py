@@ -33,9 +33,6 @@ class RadixAttention(nn.Module):
         self.mrope_sections, self.mrope_interleaved = mrope_sections, mrope_interleaved
         self._inv_freq: Optional[torch.Tensor] = None
         self._axis_map: Optional[torch.Tensor] = None
-        # set by the decoder layer: a callable giving the (weight matrix, fraction of each row) pairs that the decode
-        # kernel should request into the L2 for the GEMMs that follow it in the layer
-        self.decode_prefetch = None
 
     def _tables(self, device):
         if self._inv_freq is None or self._inv_freq.device != device:
@@ -64,8 +61,7 @@ class RadixAttention(nn.Module):
         if fb.forward_mode.is_decode():
             ops.attention_decode(q, k_cache, v_cache, fb.req_to_token_pool.req_to_token, fb.req_pool_indices,
                                  fb.seq_lens, self.scaling, out=out, max_seq_len=fb.max_seq_len,
-                                 window=self.sliding_window, logit_cap=self.logit_cap,
-                                 prefetch=self.decode_prefetch() if (self.decode_prefetch is not None and T <= 64) else None)
+                                 window=self.sliding_window, logit_cap=self.logit_cap)
         else:
             ops.attention_prefill(q, k_cache, v_cache, fb.req_to_token_pool.req_to_token, fb.req_pool_indices,
                                   fb.seq_lens, fb.extend_prefix_lens, fb.extend_start_loc, self.scaling, out=out,

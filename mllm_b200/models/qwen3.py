@@ -14,7 +14,6 @@ row-parallel.
 
 from __future__ import annotations
 
-import os
 import time
 from dataclasses import dataclass
 from typing import Iterable, Optional, Tuple
@@ -164,10 +163,6 @@ def _sliding_window(config, layer_id: int) -> Optional[int]:
     return int(w)
 
 
-# share of each row of the MLP's first weight matrix that the decode attention kernel requests into the L2
-_PREFETCH_MLP_FRACTION = float(os.environ.get("MLLM_B200_DECODE_PREFETCH_MLP", "0.4"))
-
-
 class Qwen3DecoderLayer(nn.Module):
     def __init__(self, config, layer_id: int, quant_config=None, prefix: str = "", params_dtype=None, **attn_kw):
         super().__init__()
@@ -182,22 +177,6 @@ class Qwen3DecoderLayer(nn.Module):
         self._gated_qkv = isinstance(self.self_attn.qkv_proj.quant_method, UnquantizedLinearMethod) and \
             self.self_attn.qkv_proj.bias is None
         self._gated_mlp = isinstance(self.mlp, MLP) and isinstance(self.mlp.gate_up_proj.quant_method, UnquantizedLinearMethod)
-        if hasattr(self.self_attn, "attn") and os.environ.get("MLLM_B200_DECODE_PREFETCH", "0") == "1":
-            self.self_attn.attn.decode_prefetch = self._decode_prefetch
-
-    def _decode_prefetch(self):
-        """What the decode attention kernel should request into the L2 while it runs: all of ``o_proj`` (the next
-        GEMM) and the leading part of every row of the MLP's first matrix (the one after); 16-bit weights only."""
-        from ..layers.quantize_base import UnquantizedLinearMethod
-
-        out = []
-        o = self.self_attn.o_proj
-        if isinstance(o.quant_method, UnquantizedLinearMethod):
-            out.append((o.weight, 1.0))
-        up = getattr(self.mlp, "gate_up_proj", None)
-        if up is not None and isinstance(up.quant_method, UnquantizedLinearMethod):
-            out.append((up.weight, _PREFETCH_MLP_FRACTION))
-        return out
 
     def _make_mlp(self, config, layer_id, quant_config, prefix, params_dtype):
         return MLP(config.hidden_size, config.intermediate_size, quant_config, prefix, params_dtype)

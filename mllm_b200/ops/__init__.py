@@ -564,18 +564,12 @@ def attention_prefill(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_l
 
 
 def attention_decode(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, scale: float,
-                     out=None, max_seq_len: int = 0, window: Optional[int] = None, logit_cap: float = 0.0,
-                     prefetch=None) -> torch.Tensor:
-    """``prefetch``: up to two ``(matrix, fraction)`` pairs, the weights that the next GEMMs of the layer will
-    stream.  The decode kernel is bound by latency and leaves most of the memory bandwidth idle, so its spare
-    lanes ask the L2 for the leading ``fraction`` of every row of those matrices while it runs; the GEMMs then
-    find that part on chip.  Ignored by the fallback paths."""
+                     out=None, max_seq_len: int = 0, window: Optional[int] = None, logit_cap: float = 0.0) -> torch.Tensor:
     if _attention_kernel_ok(q, k_cache, window, logit_cap) and hasattr(ext(), "attention_decode"):
         if out is None:
             out = torch.empty((q.shape[0], q.shape[1], q.shape[2]), dtype=q.dtype, device=q.device)
-        pf = [(w, f) for w, f in (prefetch or []) if isinstance(w, torch.Tensor) and w.is_cuda and w.dim() == 2][:2]
         ext().attention_decode(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, scale, out, max_seq_len,
-                               int(window or 0), float(logit_cap or 0.0), [w for w, _ in pf], [float(f) for _, f in pf])
+                               int(window or 0), float(logit_cap or 0.0))
         return out
     if q.is_cuda and max_seq_len:
         return ref.attention_decode_batched(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, scale,

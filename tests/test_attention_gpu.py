@@ -228,19 +228,3 @@ def test_decode_sliding_window_and_soft_cap(window, cap, seq_lens):
     want = ref.attention_decode(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], scale, window=window or None,
                                 logit_cap=cap)
     assert _err(got, want) < 3e-2
-
-
-def test_decode_with_weight_prefetch_hints_gives_the_same_output():
-    """The rows requested into the L2 for the layer's next GEMMs are a hint only: the output does not change
-    and the matrices are left as they were."""
-    s = _head_major(_setup([700, 64, 129], [699, 63, 128], 32, 8, seed=1), "pages", seed=3)
-    scale = D ** -0.5
-    w1 = torch.randn(512, 1024, device=DEV, dtype=torch.bfloat16)
-    w2 = torch.randn(300, 4096, device=DEV, dtype=torch.bfloat16)[:, :2048]      # pitch larger than the row
-    keep1, keep2 = w1.clone(), w2.clone()
-    plain = ops.attention_decode(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], scale, max_seq_len=700)
-    hinted = ops.attention_decode(s["q"], s["kc"], s["vc"], s["rtt"], s["req"], s["seq"], scale, max_seq_len=700,
-                                  prefetch=[(w1, 1.0), (w2, 0.4)])
-    ops.check_status()
-    assert torch.equal(plain, hinted)
-    assert torch.equal(w1, keep1) and torch.equal(w2, keep2)
