@@ -76,6 +76,13 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool v
   const int sz = valid ? 16 : 0;
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
 }
+// hardware tanh (one special-function instruction, relative error about 2^-11): enough for a soft cap whose
+// result is rounded to 16 bits two instructions later
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
@@ -1158,9 +1165,9 @@ attn_prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
 #pragma unroll
           for (int c = 0; c < kPfTile; ++c) raw[c] = __float_as_uint(__uint_as_float(raw[c]) * p.scale_log2);
         } else {
-#pragma unroll 8
+#pragma unroll   // full: a partly unrolled loop would index raw[] dynamically and push it out of the registers
           for (int c = 0; c < kPfTile; ++c)
-            raw[c] = __float_as_uint(p.cap_post * tanhf(__uint_as_float(raw[c]) * p.cap_pre));
+            raw[c] = __float_as_uint(p.cap_post * tanh_approx(__uint_as_float(raw[c]) * p.cap_pre));
         }
 #pragma unroll
         for (int c = 0; c < kPfTile; ++c)
@@ -1187,22 +1194,9 @@ attn_prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
         need = true;
       }
       const float m_exp = (m_used == -INFINITY) ? 0.f : m_used;
-      // exponentials, packed to 16 bits, kept in registers until the P buffer is free
-      uint32_t w[kPfTile / 2];
-      float ps[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int i = 0; i < kPfTile / 2; ++i) {
-        const float p0 = fast_exp2(fmaf(__uint_as_float(raw[2 * i]), mul, -m_exp));
-        const float p1 = fast_exp2(fmaf(__uint_as_float(raw[2 * i + 1]), mul, -m_exp));
-        ps[i & 3] += p0 + p1;
-        if (p.out_f16) {
-          __half2 h = __floats2half2_rn(p0, p1);
-          w[i] = *reinterpret_cast<uint32_t*>(&h);
-        } else {
-          w[i] = pack_bf16x2(p0, p1);
-        }
-      }
-      // the group's previous P*V must have finished before P is overwritten and O is rescaled
+      // The group's previous P*V must have finished before P is overwritten and O is rescaled.  It was queued a
+      // whole softmax ago, so this wait is short; taking it here lets the exponentials go to shared memory as
+      // they are computed instead of waiting in 64 registers.
       if (t > 0) {
         if (!mbar_wait(&o_done[grp_i], (t - 1) & 1, fail_flag)) {
           ok_all = false;
@@ -1223,15 +1217,30 @@ attn_prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
         }
         tmem_st_wait();
       }
-      l_sum += (ps[0] + ps[1]) + (ps[2] + ps[3]);
-      // P in the operand layout: two 64-token halves of 128-byte rows, 16-byte chunks swizzled by the row
+      // exponentials -> P in the operand layout: two 64-token halves of 128-byte rows, 16-byte chunks swizzled
+      // by the row
+      float ps[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int q16 = 0; q16 < 16; ++q16) {
+        uint32_t w4[4];
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4) {
+          const int i = q16 * 4 + k4;
+          const float p0 = fast_exp2(fmaf(__uint_as_float(raw[2 * i]), mul, -m_exp));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(raw[2 * i + 1]), mul, -m_exp));
+          ps[k4] += p0 + p1;
+          if (p.out_f16) {
+            __half2 h = __floats2half2_rn(p0, p1);
+            w4[k4] = *reinterpret_cast<uint32_t*>(&h);
+          } else {
+            w4[k4] = pack_bf16x2(p0, p1);
+          }
+        }
         const uint32_t dst = sp + (q16 >> 3) * kPfHalf + (((q16 & 7) ^ (row & 7)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[4 * q16]), "r"(w[4 * q16 + 1]),
-                     "r"(w[4 * q16 + 2]), "r"(w[4 * q16 + 3])
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w4[0]), "r"(w4[1]), "r"(w4[2]), "r"(w4[3])
                      : "memory");
       }
+      l_sum += (ps[0] + ps[1]) + (ps[2] + ps[3]);
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(&p_full[grp_i]);
@@ -1240,32 +1249,50 @@ attn_prefill_ws_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
     tc_fence_after_sync();
     if (!ok_all) *fail_flag = 1;
 
-    // ---- epilogue: normalise and store this thread's output row ----
+    // ---- epilogue: normalise, park the group's 128 rows x 256 B in its P buffer (free now), then store them
+    // row by row: 16 lanes cover one output row, and the g rows of a token are adjacent in memory ----
     const float inv_l = l_sum > 0.f ? 1.f / l_sum : 0.f;
-    uint16_t* orow = static_cast<uint16_t*>(p.out) +
-                     (static_cast<int64_t>(q_row0 + (row_valid ? tile_q0 + row_tok : 0)) * p.hq + row_head) * kD;
 #pragma unroll 1
     for (int c = 0; c < kD; c += 32) {
       uint32_t o[32];
       tmem_ld_32x32(tmem_o + c, o);
       tmem_ld_wait();
-      if (row_valid && ok_all) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          uint4 v;
-          uint32_t* vv = reinterpret_cast<uint32_t*>(&v);
+      for (int i = 0; i < 32; i += 8) {
+        uint32_t vv[4];
 #pragma unroll
-          for (int k2 = 0; k2 < 4; ++k2) {
-            const float a = __uint_as_float(o[i + 2 * k2]) * inv_l;
-            const float bb = __uint_as_float(o[i + 2 * k2 + 1]) * inv_l;
-            if (p.out_f16) {
-              __half2 h = __floats2half2_rn(a, bb);
-              vv[k2] = *reinterpret_cast<uint32_t*>(&h);
-            } else {
-              vv[k2] = pack_bf16x2(a, bb);
-            }
+        for (int k2 = 0; k2 < 4; ++k2) {
+          const float a = __uint_as_float(o[i + 2 * k2]) * inv_l;
+          const float bb = __uint_as_float(o[i + 2 * k2 + 1]) * inv_l;
+          if (p.out_f16) {
+            __half2 h = __floats2half2_rn(a, bb);
+            vv[k2] = *reinterpret_cast<uint32_t*>(&h);
+          } else {
+            vv[k2] = pack_bf16x2(a, bb);
           }
-          *reinterpret_cast<uint4*>(orow + c + i) = v;
+        }
+        const int chunk = (c + i) >> 3;   // 16-byte chunk of the 256-byte row
+        const uint32_t dst = smem_u32(sP + grp_i * kPfTileBytes) + row * 256 + ((chunk ^ (row & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(vv[0]), "r"(vv[1]), "r"(vv[2]), "r"(vv[3])
+                     : "memory");
+      }
+    }
+    if (grp_i == 0)
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    else
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+    if (ok_all) {
+      const int w4 = warp & 3;
+      const int chunk = lane & 15;
+#pragma unroll 4
+      for (int it = 0; it < 16; ++it) {
+        const int r = it * 8 + w4 * 2 + (lane >> 4);
+        const int tok = r / g;
+        if (tok < tpt && tile_q0 + tok < q_len) {
+          const uint4 v = *reinterpret_cast<const uint4*>(sP + grp_i * kPfTileBytes + r * 256 + ((chunk ^ (r & 7)) << 4));
+          uint16_t* dst = static_cast<uint16_t*>(p.out) +
+                          (static_cast<int64_t>(q_row0 + tile_q0 + tok) * p.hq + hk * g + r % g) * kD + chunk * 8;
+          *reinterpret_cast<uint4*>(dst) = v;
         }
       }
     }
