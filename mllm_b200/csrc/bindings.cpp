@@ -506,9 +506,18 @@ struct TpFusion {
   int* rs_count = nullptr;
 };
 
+// fused add + RMSNorm in front of a small-batch product (see GemmArgs)
+struct NormFusion {
+  const Tensor* weight = nullptr;
+  const Tensor* residual = nullptr;      // may stay null
+  Tensor* residual_out = nullptr;        // may stay null
+  double eps = 1e-6;
+};
+
 int64_t gemm_impl(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<Tensor>& bias,
                   const c10::optional<Tensor>& residual, bool swiglu, const c10::optional<Tensor>& a_scale,
-                  const c10::optional<Tensor>& b_scale, const TpFusion* tp, bool b_static = false) {
+                  const c10::optional<Tensor>& b_scale, const TpFusion* tp, bool b_static = false,
+                  const NormFusion* norm = nullptr) {
   check_cuda(a, "a");
   check_cuda(b, "b");
   const bool is_int8 = a.scalar_type() == at::kChar;
@@ -574,6 +583,27 @@ int64_t gemm_impl(const Tensor& a, const Tensor& b, Tensor& out, const c10::opti
       args.rs_flags[r] = tp->rs_flags[r];
     }
   }
+  if (norm != nullptr) {
+    const Tensor& w = *norm->weight;
+    TORCH_CHECK(w.is_cuda() && w.dim() == 1 && w.is_contiguous() && w.numel() == a.size(1) && w.scalar_type() == a.scalar_type(),
+                "gemm: norm weight [k] of the activations' dtype");
+    args.norm_weight = w.data_ptr();
+    args.norm_eps = static_cast<float>(norm->eps);
+    for (const Tensor* t : {norm->residual, static_cast<const Tensor*>(norm->residual_out)}) {
+      if (t == nullptr) continue;
+      TORCH_CHECK(t->is_cuda() && t->dim() == 2 && t->stride(1) == 1 && t->sizes() == a.sizes() &&
+                      t->scalar_type() == a.scalar_type(),
+                  "gemm: residual tensors of the fused norm must match the activations");
+    }
+    if (norm->residual != nullptr) {
+      args.norm_residual = norm->residual->data_ptr();
+      args.norm_residual_ld = norm->residual->stride(0);
+    }
+    if (norm->residual_out != nullptr) {
+      args.norm_residual_out = norm->residual_out->data_ptr();
+      args.norm_residual_out_ld = norm->residual_out->stride(0);
+    }
+  }
   // 0 on success; a negative code (unsupported shape / launch failure) is raised by the Python caller
   return mb200::launch_gemm(args, stream_of(a));
 }
@@ -584,6 +614,20 @@ int64_t gemm(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<
              const c10::optional<Tensor>& residual, bool swiglu, const c10::optional<Tensor>& a_scale,
              const c10::optional<Tensor>& b_scale, bool b_static) {
   return gemm_impl(a, b, out, bias, residual, swiglu, a_scale, b_scale, nullptr, b_static);
+}
+
+// out = (rmsnorm(a + residual) * norm_weight) b^T [+ bias | SwiGLU] for up to 8 rows, with a + residual (rounded to
+// the activations' type) written to residual_out.  Returns 0 when launched; a negative code when the shape is not
+// served by the fused kernel (the caller then runs the norm and the product separately).
+int64_t gemm_norm(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<Tensor>& bias, bool swiglu,
+                  const Tensor& norm_weight, const c10::optional<Tensor>& residual, c10::optional<Tensor> residual_out,
+                  double eps, bool b_static) {
+  NormFusion nf;
+  nf.weight = &norm_weight;
+  nf.eps = eps;
+  if (residual.has_value()) nf.residual = &*residual;
+  if (residual_out.has_value()) nf.residual_out = &*residual_out;
+  return gemm_impl(a, b, out, bias, c10::nullopt, swiglu, c10::nullopt, c10::nullopt, nullptr, b_static, &nf);
 }
 
 // Tensor-parallel prefill GEMM.  gate_flags (uint32 as int32 tensor, one per 128-row tile of a) delays
@@ -872,6 +916,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ep_dispatch", &ep_dispatch);
   m.def("ep_return", &ep_return);
   m.def("gemm", &gemm);
+  m.def("gemm_norm", &gemm_norm);
   m.def("gemm_tp", &gemm_tp);
   m.def("w4a16_gemm", &w4a16_gemm);
   m.def("tp_rs_add_rmsnorm_ag", &tp_rs_add_rmsnorm_ag);

@@ -55,6 +55,13 @@ struct SmallMParams {
   int swiglu;
   int b_static;
   int early_trigger;     // let the kernels behind this one start their set-up as soon as this one runs
+  // fused prologue (norm_w != null): the rows fed to the product are rmsnorm(a + norm_res) * norm_w, with the sum
+  // rounded to 16 bits first (it is the new residual stream, which CTA 0 also writes to norm_res_out)
+  const void* norm_w;
+  const uint8_t* norm_res;     // may be null: the rows of `a` are the residual stream already
+  uint8_t* norm_res_out;       // may be null
+  int64_t norm_res_ld_bytes, norm_res_out_ld_bytes;
+  float norm_eps;
 };
 
 template <bool F16>
@@ -146,16 +153,86 @@ __global__ void __launch_bounds__(kSmThreads, 1) gemm_smallm_kernel(const SmallM
   }
   if (p.b_static) pdl_wait();
   // the batch's rows into shared memory (rows past m are zero); every warp reads all of them again and again
-  {
-    const int vec_per_row = p.k >> 3;
+  const int vec_per_row = p.k >> 3;
+  if (p.norm_w == nullptr) {
     for (int v = threadIdx.x; v < 8 * vec_per_row; v += kSmThreads) {
       const int r = v / vec_per_row, q = v - r * vec_per_row;
       uint4 val = make_uint4(0, 0, 0, 0);
       if (r < p.m) val = __ldg(reinterpret_cast<const uint4*>(p.a + static_cast<int64_t>(r) * p.lda_bytes) + q);
       *reinterpret_cast<uint4*>(x_rows + r * x_pitch + q * 16) = val;
     }
+    __syncthreads();
+  } else {
+    // Fused add + RMSNorm: every CTA normalises the same 8 rows for itself (a few tens of KB from L2, while
+    // its weight copies are already in flight); CTA 0 also stores the new residual stream.
+    float ss[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) ss[r] = 0.f;
+    for (int q = threadIdx.x; q < vec_per_row; q += kSmThreads) {
+      // all sixteen loads of this column of vectors first: one round trip to L2, not sixteen
+      uint4 val[8], res[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        val[r] = make_uint4(0, 0, 0, 0);
+        if (r < p.m) val[r] = __ldg(reinterpret_cast<const uint4*>(p.a + static_cast<int64_t>(r) * p.lda_bytes) + q);
+      }
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        res[r] = make_uint4(0, 0, 0, 0);
+        if (r < p.m && p.norm_res != nullptr)
+          res[r] = __ldg(reinterpret_cast<const uint4*>(p.norm_res + static_cast<int64_t>(r) * p.norm_res_ld_bytes) + q);
+      }
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (r < p.m) {
+          uint16_t* e = reinterpret_cast<uint16_t*>(&val[r]);
+          if (p.norm_res != nullptr) {
+            const uint16_t* f = reinterpret_cast<const uint16_t*>(&res[r]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) e[i] = f_to_half<F16>(half_to_f<F16>(e[i]) + half_to_f<F16>(f[i]));
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float x = half_to_f<F16>(e[i]);
+            ss[r] += x * x;
+          }
+          if (blockIdx.x == 0 && p.norm_res_out != nullptr)
+            *(reinterpret_cast<uint4*>(p.norm_res_out + static_cast<int64_t>(r) * p.norm_res_out_ld_bytes) + q) = val[r];
+        }
+        *reinterpret_cast<uint4*>(x_rows + r * x_pitch + q * 16) = val[r];
+      }
+    }
+    float* red = &partial[0][0][0];     // [warp][8] sums of squares, then [8] reciprocal root mean squares
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const float w = warp_sum(ss[r]);
+      if (lane == 0) red[warp * 8 + r] = w;
+    }
+    __syncthreads();
+    if (threadIdx.x < 8) {
+      float tot = 0.f;
+#pragma unroll
+      for (int w = 0; w < kSmWarps; ++w) tot += red[w * 8 + threadIdx.x];
+      red[kSmWarps * 8 + threadIdx.x] = rsqrtf(tot / static_cast<float>(p.k) + p.norm_eps);
+    }
+    __syncthreads();
+    for (int q = threadIdx.x; q < vec_per_row; q += kSmThreads) {
+      const uint4 wv = __ldg(reinterpret_cast<const uint4*>(p.norm_w) + q);
+      const uint16_t* f = reinterpret_cast<const uint16_t*>(&wv);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (r < p.m) {
+          const float rstd = red[kSmWarps * 8 + r];
+          uint4 val = *reinterpret_cast<const uint4*>(x_rows + r * x_pitch + q * 16);
+          uint16_t* e = reinterpret_cast<uint16_t*>(&val);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) e[i] = f_to_half<F16>(half_to_f<F16>(e[i]) * rstd * half_to_f<F16>(f[i]));
+          *reinterpret_cast<uint4*>(x_rows + r * x_pitch + q * 16) = val;
+        }
+      }
+    }
+    __syncthreads();
   }
-  __syncthreads();
   const uint32_t x_lane = smem_u32(x_rows) + g * x_pitch + static_cast<uint32_t>(k_off0);
   int xj = 0;
 
@@ -241,6 +318,12 @@ int launch_gemm_smallm(const GemmArgs& a, cudaStream_t s) {
   if (static_cast<int64_t>(a.n) * a.k * 2 > (int64_t(384) << 20)) return 1;
   if (a.swiglu && (a.n % 256 != 0 || a.bias != nullptr || a.residual != nullptr)) return 1;
   if ((a.lda * 2) % 16 != 0 || (a.ldb * 2) % 16 != 0) return 1;
+  if (a.norm_weight != nullptr &&
+      ((a.norm_residual_ld * 2) % 16 != 0 || (a.norm_residual_out_ld * 2) % 16 != 0 ||
+       ((reinterpret_cast<uintptr_t>(a.norm_weight) | reinterpret_cast<uintptr_t>(a.norm_residual) |
+         reinterpret_cast<uintptr_t>(a.norm_residual_out)) & 15) != 0 ||
+       (a.norm_residual != nullptr && a.norm_residual == a.norm_residual_out)))
+    return 1;
   SmallMParams p{};
   p.a = static_cast<const uint8_t*>(a.a);
   p.b = static_cast<const uint8_t*>(a.b);
@@ -258,6 +341,12 @@ int launch_gemm_smallm(const GemmArgs& a, cudaStream_t s) {
   p.steps_per_warp = a.k / (32 * kSmWarps);
   p.swiglu = a.swiglu;
   p.b_static = a.b_static;
+  p.norm_w = a.norm_weight;
+  p.norm_res = static_cast<const uint8_t*>(a.norm_residual);
+  p.norm_res_out = static_cast<uint8_t*>(a.norm_residual_out);
+  p.norm_res_ld_bytes = a.norm_residual_ld * 2;
+  p.norm_res_out_ld_bytes = a.norm_residual_out_ld * 2;
+  p.norm_eps = a.norm_eps;
   static const int trigger_knob = [] {
     // measured on the decode step of an 8B model: 5.22 ms per step with the trigger at the start, 4.95 ms without
     const char* e = std::getenv("MLLM_B200_GEMM_SMALLM_TRIGGER");

@@ -1336,6 +1336,7 @@ size_t gemm_workspace_bytes(int, int, int, int) { return size_t(64) << 20; }
 
 int launch_gemm(const GemmArgs& a, cudaStream_t s) {
   if (a.m <= 0 || a.n <= 0) return 0;
+  if (a.norm_weight != nullptr && a.m > 8) return -1;
   const int eb = a.is_int8 ? 1 : 2;
   const int k_per_block = kRowBytes / eb;
   if (a.k % (16 / eb) != 0 || a.lda % (16 / eb) != 0 || a.ldb % (16 / eb) != 0) return -1;
@@ -1437,6 +1438,7 @@ int launch_gemm(const GemmArgs& a, cudaStream_t s) {
     const int rc = launch_gemm_smallm(a, s);
     if (rc <= 0) return rc;
   }
+  if (a.norm_weight != nullptr) return -1;   // the fused norm prologue exists in that kernel only
 
   // ---- swap tiling: weights are the 128-row operand, the batch is MMA N ----
   int bn = 16;

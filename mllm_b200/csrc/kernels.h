@@ -93,6 +93,14 @@ struct GemmArgs {
   int* status;           // device int, set non-zero when a bounded wait ran out
   int num_sms;
   int b_static;          // 1: b (the weights) is not written by kernels that precede this launch in its stream
+  // ---- fused add + RMSNorm prologue, batches of up to 8 rows only (norm_weight null = off) ----
+  // the product is taken of rmsnorm(a + norm_residual) * norm_weight; the 16-bit sum a + norm_residual (the new
+  // residual stream) is written to norm_residual_out, which must not alias norm_residual (other CTAs still read it)
+  const void* norm_weight;        // [k]
+  const void* norm_residual;      // [m, k] or null
+  void* norm_residual_out;        // [m, k] or null
+  int64_t norm_residual_ld, norm_residual_out_ld;   // elements
+  float norm_eps;
   // ---- tensor-parallel fusion, large-m tiling only (all zero = off) ----
   // all-gather -> GEMM: 128-row tile t of `a` is read only once gate_flags[t] >= gate_epoch
   const uint32_t* gate_flags;

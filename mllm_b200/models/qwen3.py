@@ -177,12 +177,35 @@ class Qwen3DecoderLayer(nn.Module):
         self._gated_qkv = isinstance(self.self_attn.qkv_proj.quant_method, UnquantizedLinearMethod) and \
             self.self_attn.qkv_proj.bias is None
         self._gated_mlp = isinstance(self.mlp, MLP) and isinstance(self.mlp.gate_up_proj.quant_method, UnquantizedLinearMethod)
+        self._plain_qkv = isinstance(self.self_attn.qkv_proj.quant_method, UnquantizedLinearMethod)
 
     def _make_mlp(self, config, layer_id, quant_config, prefix, params_dtype):
         return MLP(config.hidden_size, config.intermediate_size, quant_config, prefix, params_dtype)
 
+    def _small_batch_fusable(self, hidden) -> bool:
+        """A handful of rows on one GPU with 16-bit weights: both norms of the layer run inside the GEMMs that
+        consume them (``ops.add_rmsnorm_linear``)."""
+        if not (isinstance(hidden, torch.Tensor) and hidden.is_cuda and hidden.dim() == 2 and hidden.shape[0] <= 8):
+            return False
+        attn = self.self_attn
+        return (type(attn).forward is Qwen3Attention.forward and attn.o_proj.tp_size == 1 and type(self.mlp) is MLP
+                and self._plain_qkv and self._gated_mlp and getattr(self.mlp.gate_up_proj, "_gate_up_interleaved", False)
+                and type(self.input_layernorm) is RMSNorm and type(self.post_attention_layernorm) is RMSNorm)
+
+    def _forward_small_batch(self, hidden, residual, forward_batch):
+        attn = self.self_attn
+        qkv, residual = ops.add_rmsnorm_linear(hidden, residual, self.input_layernorm.weight, self.input_layernorm.eps,
+                                               attn.qkv_proj.weight, bias=attn.qkv_proj.bias)
+        qw, kw = (attn.q_norm.weight, attn.k_norm.weight) if attn.use_qk_norm else (None, None)
+        a = attn.o_proj(attn.attn(qkv, qw, kw, forward_batch))
+        h, residual = ops.add_rmsnorm_linear(a, residual, self.post_attention_layernorm.weight,
+                                             self.post_attention_layernorm.eps, self.mlp.gate_up_proj.weight, swiglu=True)
+        return self.mlp.down_proj(h), residual
+
     def forward(self, hidden: torch.Tensor, residual: Optional[torch.Tensor], forward_batch: ForwardBatch
                 ) -> Tuple[torch.Tensor, torch.Tensor]:
+        if self._small_batch_fusable(hidden):
+            return self._forward_small_batch(hidden, residual, forward_batch)
         # residual-carry: the add of the previous block's output happens inside the next norm
         if residual is None:
             residual = hidden

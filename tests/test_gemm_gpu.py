@@ -161,3 +161,38 @@ def test_streaming_gemm_swiglu(m, inter, k):
     ops.check_status()
     want = ref.linear_swiglu(x.float(), w.float(), 0)
     assert _rel_err(got, want) < 8e-3
+
+
+@pytest.mark.parametrize("m", [1, 3, 8])
+@pytest.mark.parametrize("n,k,swiglu", [(6144, 4096, False), (24576, 4096, True), (1024, 1024, False), (512, 2048, True)])
+@pytest.mark.parametrize("with_residual", [True, False])
+def test_add_rmsnorm_fused_into_the_streaming_gemm(monkeypatch, m, n, k, swiglu, with_residual):
+    """residual add + RMSNorm as the prologue of the small-batch GEMM: one launch gives the product of the normed
+    rows and the new residual stream; checked against the fp32 statement of the three steps."""
+    monkeypatch.setattr(ops, "_FUSE_NORM_GEMM", True)
+    torch.manual_seed(m + n + k)
+    dt = torch.bfloat16
+    x = torch.randn(m, k, device=DEV, dtype=dt)
+    res = torch.randn(m, k, device=DEV, dtype=dt) if with_residual else None
+    nw = (1 + 0.1 * torch.randn(k, device=DEV)).to(dt)
+    w = torch.randn(n, k, device=DEV, dtype=dt) * (k ** -0.5)
+    wk = torch.nn.Parameter(ref.interleave_gate_up(w, ops.SWIGLU_BLOCK).contiguous() if swiglu else w, requires_grad=False)
+    res_before = None if res is None else res.clone()
+    y, s = ops.add_rmsnorm_linear(x, res, nw, 1e-6, wk, swiglu=swiglu)
+    ops.check_status()
+    if res is not None:
+        assert torch.equal(res, res_before), "the fused path must not touch the incoming residual"
+    s_want = (x.float() + (res.float() if res is not None else 0)).to(dt)
+    assert torch.equal(s, s_want)
+    h = (s_want.float() * torch.rsqrt(s_want.float().pow(2).mean(-1, keepdim=True) + 1e-6) * nw.float()).to(dt)
+    want = ref.linear_swiglu(h.float(), w.float(), 0) if swiglu else ref.linear(h, w, out_dtype=torch.float32)
+    assert _rel_err(y, want) < 8e-3
+    # an input the fused kernel does not take (9 rows) goes through the separate kernels with the same result
+    x9 = torch.randn(9, k, device=DEV, dtype=dt)
+    r9 = torch.randn(9, k, device=DEV, dtype=dt)
+    s9_want = (x9.float() + r9.float()).to(dt)
+    y9, s9 = ops.add_rmsnorm_linear(x9.clone(), r9, nw, 1e-6, wk, swiglu=swiglu)
+    assert torch.equal(s9, s9_want)
+    h9 = (s9_want.float() * torch.rsqrt(s9_want.float().pow(2).mean(-1, keepdim=True) + 1e-6) * nw.float()).to(dt)
+    want9 = ref.linear_swiglu(h9.float(), w.float(), 0) if swiglu else ref.linear(h9, w, out_dtype=torch.float32)
+    assert _rel_err(y9, want9) < 8e-3
