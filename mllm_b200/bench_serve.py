@@ -102,6 +102,7 @@ def summarize(results: List[RequestResult], wall: float) -> Dict[str, Any]:
     cached = sum(r.cached_tokens for r in ok)
     return {
         "completed": len(ok), "failed": len(results) - len(ok), "duration_s": wall,
+        "first_error": next((r.error for r in results if r.error), None),
         "request_throughput": len(ok) / wall if wall else 0.0,
         "input_token_throughput": tot_in / wall if wall else 0.0,
         "output_token_throughput": tot_out / wall if wall else 0.0,
@@ -155,7 +156,9 @@ async def _one_http(session, base_url: str, ids: List[int], n_out: int, api_key:
                     continue
                 ev = json.loads(line[6:])
                 now = time.perf_counter()
-                if ev.get("usage"):
+                if ev.get("error"):
+                    r.error = str(ev["error"])[:200]
+                elif ev.get("usage"):
                     r.output_tokens = max(r.output_tokens, ev["usage"]["completion_tokens"])
                     r.cached_tokens = ev["usage"].get("prompt_tokens_details", {}).get("cached_tokens", 0)
                 elif ev.get("choices") and ev["choices"][0].get("text") is not None:
@@ -262,10 +265,12 @@ def main(argv=None) -> None:
     ap.add_argument("--shared-prefix-len", type=int, default=1024)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--output-file", default=None)
+    ap.add_argument("--vocab-size", type=int, default=10000,
+                    help="HTTP mode: synthetic prompt ids are drawn below this (the served model's vocabulary must hold them)")
     ns = ap.parse_args(argv)
     cfg = read_args(argv, ap)
     engine = None
-    vocab = 10000
+    vocab = ns.vocab_size
     if ns.engine:
         from .engine.launch import Engine
 
