@@ -439,6 +439,10 @@ size_t w4a16_workspace_bytes(int m, int n, int k, int num_sms) {
 
 int launch_w4a16_gemm(const W4A16Args& a, cudaStream_t s) {
   if (a.m <= 0 || a.n <= 0) return 0;
+  if (a.m <= 8) {   // a handful of rows: stream and expand in registers
+    const int rc = launch_w4a16_smallm(a, s);
+    if (rc <= 0) return rc;
+  }
   if (a.k % 64 != 0 || a.group % 64 != 0 || a.k % a.group != 0 || a.ldx % 8 != 0 || (a.k / 2) % 16 != 0) return -1;
   if ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.qweight)) & 15) return -1;
   int bn = 16;

@@ -142,6 +142,8 @@ struct W4A16Args {
   int interleaved;
 };
 int launch_w4a16_gemm(const W4A16Args& args, cudaStream_t s);
+// m <= 8, k <= 4096: packed weights streamed and expanded in registers (gemm_smallm_w4.cu).  0 launched, 1 not for it.
+int launch_w4a16_smallm(const W4A16Args& args, cudaStream_t s);
 
 // 128-byte-swizzled 2-D tensor map over a row-major [rows, k] matrix (box = 128 bytes of k x box_rows);
 // map points at a CUtensorMap.  type: 0 bf16, 1 fp16, 2 uint8.

@@ -67,3 +67,21 @@ def test_w4a16_interleaved_nibbles_give_the_same_bits(M, N, K, group, zeros, dty
     fast = ops.w4a16_gemm(x, il, sc, z, group, b, interleaved=True)
     ops.check_status()
     assert torch.equal(natural, fast)
+
+
+@pytest.mark.parametrize("M", [1, 5, 8])
+@pytest.mark.parametrize("N,K,group", [(4096, 4096, 128), (6144, 4096, 128), (1024, 1024, 32), (512, 2048, 64), (24576, 4096, 128),
+                                       (4096, 12288, 128), (1024, 6144, 64), (256, 8192, 128)])
+@pytest.mark.parametrize("zeros,interleaved,dtype", [(False, True, torch.bfloat16), (True, False, torch.bfloat16),
+                                                     (True, True, torch.float16)])
+def test_w4a16_streaming_kernel_for_a_handful_of_rows(M, N, K, group, zeros, interleaved, dtype):
+    """Up to 8 rows; k a multiple of 1024 up to 4096 (two CTAs per SM), or a multiple of 2048 up to 12288 (one CTA
+    whose shared memory is mostly the activation rows): weights, scales and zero points stream through a per-lane
+    copy queue and are expanded in registers (no tensor memory); against the fp32 statement."""
+    x, qw, sc, z, b = _case(M, N, K, group, zeros=zeros, bias=True, dtype=dtype, seed=M + N + K)
+    w = ref.dequant_w4(qw, sc, z, group).to(dtype).float()
+    want = x.float() @ w.t() + b.float()
+    q_in = ops.w4a16_interleave(qw) if interleaved else qw
+    got = ops.w4a16_gemm(x, q_in, sc, z, group, b, interleaved=interleaved).float()
+    ops.check_status()
+    assert (got - want).abs().max().item() <= 0.02 * want.abs().max().item() + 0.02
