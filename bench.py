@@ -17,8 +17,10 @@ One *step* is one complete batch: prefill of batch x 2048 seeded random token id
 ``batch * (2048 + 128) / seconds_per_step``, with the step timed on the device by CUDA events
 (maximum over ranks).  ``e2e`` repeats the measurement through the public
 ``BenchRunner.extend`` / ``decode`` API with the prompt ids copied from pinned host memory
-and every step's sampled ids read back to the host, timed by the host clock around device
-synchronisation.  Weights are random-init (seeded N(0, 0.02)); data are synthetic.
+and every step's sampled ids read back into pinned host memory (the copy of a step is queued behind
+it, the next step is queued, then the host waits for the copy: the host reads every step, one step
+behind the launches), timed by the host clock around device synchronisation.  Weights are random-init
+(seeded N(0, 0.02)); data are synthetic.
 """
 
 from __future__ import annotations
@@ -141,6 +143,9 @@ class _HostEvent:
     def elapsed_time(self, other: "_HostEvent") -> float:
         return (other.t - self.t) * 1e3
 
+    def synchronize(self) -> None:
+        pass
+
 
 class Watchdog:
     """Bounds the whole run: past the deadline every thread's Python stack goes to stderr, rank 0
@@ -242,15 +247,32 @@ def run_ours(a: argparse.Namespace) -> dict:
         if world > 1:
             reduce_host(0.0, dist.ReduceOp.SUM)
 
+    # end-to-end passes read every step's token ids back into pinned host memory
+    host_ids = torch.empty((out_len, bs), dtype=torch.int64, pin_memory=on_gpu)
+
     def one_pass(ids, readback: bool):
+        """One batch through the public API.  With ``readback`` every step's sampled ids are copied to the host:
+        the copy of step t is queued behind step t, step t + 1 is queued next, and only then does the host wait
+        for the copy of step t - so the device never idles while the host reads (the ids a step needs are on the
+        device already).  Returns the last ids and the host buffer."""
         br.clear()
         nxt = br.extend(ids)
-        host = [nxt.cpu()] if readback else None
-        for _ in range(out_len - 1):
-            nxt = br.decode(nxt)
-            if readback:
-                host.append(nxt.cpu())
-        return nxt, host
+        if not readback:
+            for _ in range(out_len - 1):
+                nxt = br.decode(nxt)
+            return nxt, None
+        pending = None
+        for t in range(out_len):
+            host_ids[t].copy_(nxt.reshape(-1), non_blocking=True)
+            done = Event(enable_timing=False)
+            done.record()
+            if t + 1 < out_len:
+                nxt = br.decode(nxt)
+            if pending is not None:
+                pending.synchronize()      # step t - 1's ids are in host memory now
+            pending = done
+        pending.synchronize()
+        return nxt, host_ids
 
     for i in range(max(a.warmup, 3)):
         one_pass(ids_dev, False)
@@ -308,6 +330,7 @@ def run_ours(a: argparse.Namespace) -> dict:
             "d2h_bytes_per_step": int(replicas * out_len * bs * 8),
             "ms_per_step": e2e_s * 1e3 / a.steps,
             "api": "mllm_b200.bench_one_batch.BenchRunner.extend/decode",
+            "readback": "each step's ids to pinned host memory, awaited after the next step is queued",
         }
         wd.log("end-to-end region done")
 
