@@ -22,7 +22,8 @@
 //     leaves L1 too small, and every step then paid an L2 round trip), rows 64 bytes apart modulo 128 so
 //     that a warp's read of 8 rows x 64 bytes has no bank conflict; hence k <= 4096.  (Walking a longer k in
 //     pieces, with the activations of a piece staged at a time, was tried and was slower than the tcgen05
-//     path: 32-43 us against 23 us for a 4096 x 12288 projection.)
+//     path: 32-43 us against 23 us for a 4096 x 12288 projection; so was a cluster of four CTAs sharing the k range
+//     with one exchange of partial sums at the end: 37 clusters of four 200 KB CTAs do not fit one wave, 42.6 us.)
 //   * at the end of a unit the warps' 8 x 8 partial sums meet in shared memory (double-buffered, one
 //     __syncthreads per unit) and 64 threads add bias / residual or apply SwiGLU and store.
 #include <algorithm>
