@@ -619,7 +619,8 @@ def attention_varlen_bidirectional(q, k, v, cu_seqlens, scale: float) -> torch.T
     zero-padded to 128 and the tcgen05 prefill kernel runs without its causal mask, every segment being
     one "request" whose keys sit at rows ``cu[i]..cu[i+1]`` of k / v."""
     if not use_kernels(q) or q.shape[-1] > 128:
-        return ref.attention_varlen_bidirectional(q, k, v, cu_seqlens, scale)
+        return ref.attention_varlen_bidirectional(q, k, v, cu_seqlens.cu_host if isinstance(cu_seqlens, VarlenPlan) else cu_seqlens,
+                                                  scale)
     D = q.shape[-1]
     if D != 128:
         pad = (0, 128 - D)
@@ -627,17 +628,33 @@ def attention_varlen_bidirectional(q, k, v, cu_seqlens, scale: float) -> torch.T
     return _varlen_bidirectional_padded(q.contiguous(), k.contiguous(), v.contiguous(), cu_seqlens, scale)[..., :D]
 
 
+class VarlenPlan:
+    """Everything the bidirectional variable-length attention needs besides q, k, v, built once for a set of
+    segment boundaries and reused by every block of a vision tower (and captured with it in a CUDA graph): the
+    device copies of the boundaries and lengths, the row table that lets the prefill kernel see every segment as
+    one request, and the host-side maximum length."""
+
+    def __init__(self, cu_seqlens: torch.Tensor, total_rows: int, device) -> None:
+        self.cu_host = cu_seqlens.cpu()
+        lens_host = (self.cu_host[1:] - self.cu_host[:-1]).tolist()
+        self.max_len = int(max(lens_host)) if lens_host else 0
+        self.n = len(lens_host)
+        dev = torch.device(device)
+        if dev.type != "cuda":
+            return
+        cu = self.cu_host.to(device=dev, dtype=torch.int32)
+        self.lens = (cu[1:] - cu[:-1]).contiguous()
+        self.starts = cu[:-1].contiguous()
+        rtt = self.starts.unsqueeze(1) + torch.arange(self.max_len, device=dev, dtype=torch.int32).unsqueeze(0)
+        self.rtt = rtt.clamp_(max=max(0, total_rows - 1)).contiguous()
+        self.req = torch.arange(self.n, device=dev, dtype=torch.int32)
+        self.zeros = torch.zeros(self.n, device=dev, dtype=torch.int32)
+
+
 def _varlen_bidirectional_padded(q, k, v, cu_seqlens, scale: float) -> torch.Tensor:
-    cu = cu_seqlens.to(device=q.device, dtype=torch.int32)
-    lens = cu[1:] - cu[:-1]
-    lens_host = (cu_seqlens[1:] - cu_seqlens[:-1]).tolist() if not cu_seqlens.is_cuda else lens.tolist()
-    max_len = int(max(lens_host)) if lens_host else 0
-    n = len(lens_host)
-    rtt = (cu[:-1].unsqueeze(1) + torch.arange(max_len, device=q.device, dtype=torch.int32).unsqueeze(0)).contiguous()
-    rtt.clamp_(max=q.shape[0] - 1)
+    plan = cu_seqlens if isinstance(cu_seqlens, VarlenPlan) else VarlenPlan(cu_seqlens, q.shape[0], q.device)
     out = torch.empty_like(q)
-    ext().attention_prefill(q, k, v, rtt, torch.arange(n, device=q.device, dtype=torch.int32), lens.contiguous(),
-                            torch.zeros(n, device=q.device, dtype=torch.int32), cu[:-1].contiguous(), scale, out, max_len,
+    ext().attention_prefill(q, k, v, plan.rtt, plan.req, plan.lens, plan.zeros, plan.starts, scale, out, plan.max_len,
                             False, 0, 0.0)
     return out
 
@@ -652,9 +669,13 @@ def vision_attention(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, cu
     if use_kernels(qkv) and D <= 128 and D % 2 == 0:
         q = torch.empty((T, num_heads, 128), dtype=qkv.dtype, device=qkv.device)
         k, v = torch.empty_like(q), torch.empty_like(q)
-        ext().vision_rope_split_pad(q4.contiguous(), cos.float().contiguous(), sin.float().contiguous(), q, k, v)
+        cos32 = cos if (cos.dtype == torch.float32 and cos.is_contiguous()) else cos.float().contiguous()
+        sin32 = sin if (sin.dtype == torch.float32 and sin.is_contiguous()) else sin.float().contiguous()
+        ext().vision_rope_split_pad(q4.contiguous(), cos32, sin32, q, k, v)
         o = _varlen_bidirectional_padded(q, k, v, cu_seqlens, scale)
         return o[..., :D].reshape(T, num_heads * D)
+    if isinstance(cu_seqlens, VarlenPlan):
+        cu_seqlens = cu_seqlens.cu_host
     q, k, v = q4.unbind(1)
     q, k = ref.vision_rope(q, cos, sin), ref.vision_rope(k, cos, sin)
     return ref.attention_varlen_bidirectional(q, k, v, cu_seqlens, scale).reshape(T, num_heads * D)

@@ -91,3 +91,34 @@ def test_qwen3_vl_tiny_gpu_matches_cpu_oracle():
     ops.check_status()
     assert (got - want).abs().max().item() < 0.1 * max(1.0, want.abs().max().item())
     assert torch.nn.functional.cosine_similarity(got, want, dim=-1).min().item() > 0.99
+
+
+def test_vision_tower_graph_replay_equals_eager(monkeypatch):
+    """The captured tower (one graph per set of image grids) gives the eager tower's features, for new pixels at
+    every replay, for two grids alternating, and after the cache has evicted and re-captured an entry."""
+    from mllm_b200.models.presets import get_preset
+    from mllm_b200.models.qwen3_vl import Qwen3VLVisionModel
+
+    cfg = get_preset("qwen3-vl-tiny")
+    torch.manual_seed(0)
+    with torch.device("cuda"):
+        vis = Qwen3VLVisionModel(cfg.vision_config, torch.bfloat16)
+    for prm in vis.parameters():
+        prm.data.normal_(0, 0.05)
+    patch_dim = vis.in_channels * vis.temporal_patch_size * vis.patch_size ** 2
+    grids = [[[1, 8, 12]], [[1, 4, 4], [1, 8, 8]]]
+
+    def pixels(g, seed):
+        n = sum(t * h * w for t, h, w in g)
+        return torch.randn(n, patch_dim, device="cuda", generator=torch.Generator(device="cuda").manual_seed(seed)).bfloat16()
+
+    monkeypatch.setenv("MLLM_B200_VIT_GRAPH", "0")
+    want = {(gi, s): vis(pixels(g, s), g) for gi, g in enumerate(grids) for s in (1, 2)}
+    monkeypatch.setenv("MLLM_B200_VIT_GRAPH", "1")
+    monkeypatch.setattr(Qwen3VLVisionModel, "_GRAPH_CACHE_ENTRIES", 1)     # every change of grids evicts and re-captures
+    for s in (1, 2):
+        for gi, g in enumerate(grids):
+            got = vis(pixels(g, s), g)
+            assert torch.equal(got, want[(gi, s)]), (gi, s)
+    assert len(vis.__dict__["_graphs"]) == 1
+    ops.check_status()
