@@ -209,3 +209,32 @@ def test_moe_expert_parallel_exchange_matches_single_rank_on_gpu(tmp_path, world
     rows = (many - one).abs().amax(-1).flatten()
     assert (rows < 0.15).float().mean().item() >= 0.8 and rows.max().item() < 1.0, rows
     assert (many.argmax(-1) == one.argmax(-1)).float().mean().item() >= 0.8
+
+
+def _rows_close(many, one, tol=0.15):
+    """Per (step, request) row; with random weights a near-tie may fall the other way in one row."""
+    rows = (many - one).abs().amax(-1).flatten()
+    return (rows < tol).float().mean().item() >= 0.8 and rows.max().item() < 1.0
+
+
+@pytest.mark.gpu
+def test_pp2_matches_single_rank_on_gpu(tmp_path):
+    """Two pipeline stages on two GPUs: hidden state and residual travel by NCCL send / recv, the last stage's
+    sampled ids go back to the first; logits of the prefill and of the decode steps equal the single-GPU model's."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    one = _launch(1, str(tmp_path / "pp1.pt"), "cuda", "bfloat16", 0)
+    two = _launch(2, str(tmp_path / "pp2.pt"), "cuda", "bfloat16", 0, {"TP_TEST_PP": "2"})
+    assert _rows_close(two, one), (two - one).abs().amax(-1)
+
+
+@pytest.mark.gpu
+def test_hybrid_tp2_matches_single_rank_on_gpu(tmp_path):
+    """The Qwen3.5-style hybrid model (gated delta net + gated attention) on two GPUs: heads of both kinds split
+    over the ranks, partial sums through the NCCL all-reduce; logits equal the single-GPU model's."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = {"TP_TEST_PRESET": "qwen3.5-tiny", "TP_TEST_KV_HEADS": "2", "TP_TEST_PREFILL_LEN": "21"}
+    one = _launch(1, str(tmp_path / "h1.pt"), "cuda", "bfloat16", 0, env)
+    two = _launch(2, str(tmp_path / "h2.pt"), "cuda", "bfloat16", 0, env)
+    assert _rows_close(two, one), (two - one).abs().amax(-1)
