@@ -89,12 +89,20 @@ __global__ void tp_reduce_add_rmsnorm_kernel(PeerPtrs peers, uint32_t* __restric
       float acc[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-      for (int r = 0; r < tp; ++r) {
-        const uint4 raw = *(reinterpret_cast<const uint4*>(static_cast<const T*>(peers.data[r]) + row * row_stride) + v);
-        float f[8];
-        unpack8v<T>(raw, f);
+      // every rank's vector first, then the sum in rank order: the loads are independent and cross NVLink together
+      // (issued one after the other, each behind the previous one's use, they cost one link round trip per rank)
+      uint4 raw[kMaxTp];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] += f[i];
+      for (int r = 0; r < kMaxTp; ++r)
+        if (r < tp) raw[r] = *(reinterpret_cast<const uint4*>(static_cast<const T*>(peers.data[r]) + row * row_stride) + v);
+#pragma unroll
+      for (int r = 0; r < kMaxTp; ++r) {
+        if (r < tp) {
+          float f[8];
+          unpack8v<T>(raw[r], f);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] += f[i];
+        }
       }
       if (residual != nullptr) {
         uint4* rp = reinterpret_cast<uint4*>(residual + static_cast<int64_t>(row) * hidden) + v;
