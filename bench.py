@@ -249,6 +249,7 @@ def run_ours(a: argparse.Namespace) -> dict:
 
     # end-to-end passes read every step's token ids back into pinned host memory
     host_ids = torch.empty((out_len, bs), dtype=torch.int64, pin_memory=on_gpu)
+    copied = [Event(enable_timing=False), Event(enable_timing=False)]   # step t records copied[t & 1]
 
     def one_pass(ids, readback: bool):
         """One batch through the public API.  With ``readback`` every step's sampled ids are copied to the host:
@@ -261,17 +262,14 @@ def run_ours(a: argparse.Namespace) -> dict:
             for _ in range(out_len - 1):
                 nxt = br.decode(nxt)
             return nxt, None
-        pending = None
         for t in range(out_len):
             host_ids[t].copy_(nxt.reshape(-1), non_blocking=True)
-            done = Event(enable_timing=False)
-            done.record()
+            copied[t & 1].record()
             if t + 1 < out_len:
                 nxt = br.decode(nxt)
-            if pending is not None:
-                pending.synchronize()      # step t - 1's ids are in host memory now
-            pending = done
-        pending.synchronize()
+            if t > 0:
+                copied[(t - 1) & 1].synchronize()      # step t - 1's ids are in host memory now
+        copied[(out_len - 1) & 1].synchronize()
         return nxt, host_ids
 
     for i in range(max(a.warmup, 3)):
