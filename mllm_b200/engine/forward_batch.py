@@ -53,6 +53,7 @@ class ForwardBatch:
     mrope_position_deltas: Optional[torch.Tensor] = None
     pixel_values: Optional[torch.Tensor] = None
     image_grid_thw: Optional[torch.Tensor] = None
+    mrope_t_scale: Optional[torch.Tensor] = None        # [grids] temporal position step per grid (None: 1 everywhere)
     # pools
     req_to_token_pool: Any = None
     token_to_kv_pool: Any = None

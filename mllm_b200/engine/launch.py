@@ -96,10 +96,14 @@ class Engine:
             return None
         from ..utils.image_processor import CLIP_MEAN, CLIP_STD
 
-        clip = str(getattr(cfg, "model_type", "")) in ("qwen2_vl", "qwen2_5_vl")   # these normalise with CLIP statistics
-        # videos are served for the families whose prompt has one timestamped block per temporal patch
-        video = None if clip or getattr(cfg, "video_token_id", None) is None else int(cfg.video_token_id)
-        return dict(video_token_id=video,
+        family = str(getattr(cfg, "model_type", ""))
+        clip = family in ("qwen2_vl", "qwen2_5_vl")                 # these normalise with CLIP statistics
+        video = None if getattr(cfg, "video_token_id", None) is None else int(cfg.video_token_id)
+        # Qwen3-VL prompts hold one timestamped block per temporal patch; Qwen2-VL / Qwen2.5-VL prompts hold one
+        # block per clip, and Qwen2.5-VL advances the temporal position by seconds x tokens_per_second
+        layout = "clip" if clip else "frames"
+        tps = float(getattr(vc, "tokens_per_second", 2)) if family == "qwen2_5_vl" else None
+        return dict(video_token_id=video, video_layout=layout, tokens_per_second=tps,
                     image_mean=list(CLIP_MEAN) if clip else 0.5, image_std=list(CLIP_STD) if clip else 0.5,
                     image_token_id=int(cfg.image_token_id), vision_start_token_id=int(cfg.vision_start_token_id),
                     vision_end_token_id=int(getattr(cfg, "vision_end_token_id", cfg.vision_start_token_id)),

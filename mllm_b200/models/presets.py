@@ -2,7 +2,8 @@
 
 Each preset is a plain attribute bag with the HF ``config.json`` field names the
 models read.  Shapes: Qwen3 dense (0.6B / 1.7B / 4B / 8B / 14B / 32B), Qwen3-30B-A3B
-(MoE) and the Qwen3-VL-2B vision+language pair.
+(MoE), Llama / Qwen2 decoders, the Qwen3.5 hybrids, and the vision+language pairs Qwen3-VL-2B, Qwen2-VL-2B
+and Qwen2.5-VL-3B (each with a ``-tiny`` shape for tests).
 """
 
 from __future__ import annotations
@@ -95,6 +96,49 @@ PRESETS["qwen3-vl-tiny"] = dict(
                        temporal_patch_size=2, spatial_merge_size=2, in_channels=3, out_hidden_size=256,
                        num_position_embeddings=64, deepstack_visual_indexes=[0, 1],
                        hidden_act="gelu_pytorch_tanh"),
+    torch_dtype="bfloat16", eos_token_id=1,
+)
+
+# Qwen2-VL / Qwen2.5-VL: Qwen2 decoder (biased q / k / v, sectioned 3-D rope) behind their own vision towers
+_Q2VL_IDS = dict(image_token_id=151655, video_token_id=151656, vision_start_token_id=151652, vision_end_token_id=151653)
+_Q2VL_TINY_IDS = dict(image_token_id=1001, video_token_id=1002, vision_start_token_id=1003, vision_end_token_id=1004)
+
+
+def _qwen2_text(hidden, layers, heads, kv, inter, tie, vocab=151936, sections=(16, 24, 24)) -> Dict[str, Any]:
+    d = _dense(hidden, layers, heads, kv, inter, tie, vocab=vocab, theta=1e6)
+    d.update(architectures=["Qwen2ForCausalLM"], model_type="qwen2", head_dim=hidden // heads, max_position_embeddings=32768,
+             rope_scaling=dict(type="mrope", mrope_section=list(sections)))
+    return d
+
+
+PRESETS["qwen2-vl-2b"] = dict(
+    architectures=["Qwen2VLForConditionalGeneration"], model_type="qwen2_vl", tie_word_embeddings=True, **_Q2VL_IDS,
+    text_config=_qwen2_text(1536, 28, 12, 2, 8960, True),
+    vision_config=dict(depth=32, embed_dim=1280, hidden_size=1536, num_heads=16, mlp_ratio=4, patch_size=14,
+                       spatial_merge_size=2, temporal_patch_size=2, in_channels=3, hidden_act="quick_gelu"),
+    torch_dtype="bfloat16", eos_token_id=151645,
+)
+PRESETS["qwen2-vl-tiny"] = dict(
+    architectures=["Qwen2VLForConditionalGeneration"], model_type="qwen2_vl", tie_word_embeddings=True, **_Q2VL_TINY_IDS,
+    text_config=_qwen2_text(256, 2, 4, 2, 512, True, vocab=1024, sections=(8, 12, 12)),
+    vision_config=dict(depth=2, embed_dim=64, hidden_size=256, num_heads=2, mlp_ratio=2, patch_size=14,
+                       spatial_merge_size=2, temporal_patch_size=2, in_channels=3, hidden_act="quick_gelu"),
+    torch_dtype="bfloat16", eos_token_id=1,
+)
+PRESETS["qwen2.5-vl-3b"] = dict(
+    architectures=["Qwen2_5_VLForConditionalGeneration"], model_type="qwen2_5_vl", tie_word_embeddings=True, **_Q2VL_IDS,
+    text_config=_qwen2_text(2048, 36, 16, 2, 11008, True),
+    vision_config=dict(depth=32, hidden_size=1280, hidden_act="silu", intermediate_size=3420, num_heads=16, in_channels=3,
+                       patch_size=14, spatial_merge_size=2, temporal_patch_size=2, window_size=112, out_hidden_size=2048,
+                       fullatt_block_indexes=[7, 15, 23, 31], tokens_per_second=2),
+    torch_dtype="bfloat16", eos_token_id=151645,
+)
+PRESETS["qwen2.5-vl-tiny"] = dict(
+    architectures=["Qwen2_5_VLForConditionalGeneration"], model_type="qwen2_5_vl", tie_word_embeddings=True, **_Q2VL_TINY_IDS,
+    text_config=_qwen2_text(256, 2, 4, 2, 512, True, vocab=1024, sections=(8, 12, 12)),
+    vision_config=dict(depth=3, hidden_size=64, hidden_act="silu", intermediate_size=96, num_heads=2, in_channels=3,
+                       patch_size=14, spatial_merge_size=2, temporal_patch_size=2, window_size=56, out_hidden_size=256,
+                       fullatt_block_indexes=[1], tokens_per_second=2),
     torch_dtype="bfloat16", eos_token_id=1,
 )
 

@@ -126,6 +126,7 @@ class Qwen2_5_VLForConditionalGeneration(VisionLanguageMixin, Qwen2ForCausalLM):
         self.full_config = config
         self.visual = Qwen2_5VisionModel(config.vision_config, dt)
         self.image_token_id = config.image_token_id
+        self.video_token_id = getattr(config, "video_token_id", None)
         self.vision_start_token_id = config.vision_start_token_id
         self.spatial_merge_size = self.visual.spatial_merge_size
         self.num_deepstack = 0

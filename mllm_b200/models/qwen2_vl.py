@@ -39,6 +39,7 @@ class Qwen2VLForConditionalGeneration(VisionLanguageMixin, Qwen2ForCausalLM):
         Qwen2ForCausalLM.__init__(self, tc, quant_config, params_dtype, mrope_sections=rs.get("mrope_section", [16, 24, 24]),
                                   mrope_interleaved=False)
         shim = SimpleNamespace(vision_config=_tower_config(config.vision_config), image_token_id=config.image_token_id,
+                               video_token_id=getattr(config, "video_token_id", None),
                                vision_start_token_id=config.vision_start_token_id)
         self._init_vision(shim, params_dtype or torch.get_default_dtype())
         self.full_config = config

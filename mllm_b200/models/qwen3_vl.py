@@ -250,12 +250,15 @@ class Qwen3VLVisionModel(nn.Module):
 
 
 def get_rope_index(input_ids: torch.Tensor, image_grid_thw, image_token_id: int, vision_start_token_id: int,
-                   spatial_merge_size: int, start: int = 0) -> Tuple[torch.Tensor, int]:
+                   spatial_merge_size: int, start: int = 0, t_scales=None) -> Tuple[torch.Tensor, int]:
     """3-D (t, h, w) position ids of one sequence and ``delta = next_position - len``.
 
     Text tokens advance all three axes together; the tokens of an image that follows a vision-start
-    token take ``base + (t, h, w)`` of the merged grid and the counter then jumps by
-    ``max(t, h, w)``.  ``start`` is the first position (a cached prefix of text)."""
+    token take ``base + (t, h, w)`` of the merged grid and the counter then jumps to one past the
+    largest position used (``max(t, h, w)`` when time is not scaled).  ``start`` is the first position
+    (a cached prefix of text).  ``t_scales`` holds one factor per grid for the temporal axis: a video clip
+    of Qwen2.5-VL advances ``seconds per temporal patch x tokens per second`` positions per temporal patch
+    (truncated to an integer per patch); 1 everywhere else."""
     ids = input_ids.tolist()
     T = len(ids)
     grids = [] if image_grid_thw is None else (image_grid_thw.tolist() if isinstance(image_grid_thw, torch.Tensor)
@@ -269,11 +272,14 @@ def get_rope_index(input_ids: torch.Tensor, image_grid_thw, image_token_id: int,
             i += 1
             t, h, w = int(grids[img][0]), int(grids[img][1]) // spatial_merge_size, int(grids[img][2]) // spatial_merge_size
             n = min(t * h * w, T - i)
-            tt, hh, ww = np.meshgrid(np.arange(t), np.arange(h), np.arange(w), indexing="ij")
+            steps = np.arange(t)
+            if t_scales is not None and float(t_scales[img]) != 1.0:
+                steps = (steps * float(t_scales[img])).astype(np.int64)
+            tt, hh, ww = np.meshgrid(steps, np.arange(h), np.arange(w), indexing="ij")
             pos[0, i:i + n] = tt.flatten()[:n] + cur
             pos[1, i:i + n] = hh.flatten()[:n] + cur
             pos[2, i:i + n] = ww.flatten()[:n] + cur
-            cur += max(t, h, w)
+            cur += max(int(steps[-1]) + 1, h, w)
             i += n
             img += 1
         else:
@@ -290,7 +296,8 @@ class VisionLanguageMixin:
     ``spatial_merge_size``, ``hidden_size``, ``num_deepstack`` and ``model.embed_tokens``."""
 
     uses_mrope = True
-    # videos: every temporal patch arrives as one more "image" of grid [1, h, w] whose rows carry this token
+    # videos: rows that carry this token take features like image rows.  Qwen3-VL prompts hold one block per
+    # temporal patch (grid [1, h, w] each); Qwen2-VL / Qwen2.5-VL prompts hold one block per clip (grid [T, h, w])
     video_token_id: Optional[int] = None
 
     def _init_vision(self, config, dtype) -> None:
@@ -372,15 +379,17 @@ class VisionLanguageMixin:
             fb.extend_prefix_lens.tolist() if fb.extend_prefix_lens is not None else [0] * len(lens))
         known = fb.mrope_position_deltas.tolist() if fb.mrope_position_deltas is not None else [0] * len(lens)
         grids = None if fb.image_grid_thw is None else fb.image_grid_thw.tolist()
+        scales = None if getattr(fb, "mrope_t_scale", None) is None else fb.mrope_t_scale.tolist()
         ids_cpu = input_ids.cpu()
         out, deltas, off, img = [], [], 0, 0
         for i, n in enumerate(lens):
             seq = ids_cpu[off:off + n]
             n_img = int((seq == self.vision_start_token_id).sum())
             thw = grids[img:img + n_img] if (grids is not None and n_img) else None
+            ts = scales[img:img + n_img] if (scales is not None and thw is not None) else None
             img += n_img if thw is not None else 0
             p, d = get_rope_index(seq, thw, self.image_token_id, self.vision_start_token_id, self.spatial_merge_size,
-                                  start=int(prefix[i]) + int(known[i]))
+                                  start=int(prefix[i]) + int(known[i]), t_scales=ts)
             out.append(p)
             deltas.append(int(known[i]) + d)
             off += n

@@ -397,13 +397,21 @@ class ModelRunnerProcess:
 
     def _mm_kwargs(self, items) -> Dict[str, Any]:
         """Pixel inputs of requests whose image tokens fall inside this pass."""
-        pixel, grids = [], []
+        pixel, grids, scales, scaled = [], [], [], False
         for req, _ in items:
             mm = req.mm_inputs
             if mm and mm.get("pixel_values") is not None and not mm.get("_consumed"):
                 pixel.append(torch.as_tensor(mm["pixel_values"]))
                 grids.append(torch.as_tensor(mm["image_grid_thw"]).reshape(-1, 3))
+                if mm.get("mrope_t_scale") is not None:
+                    scales.append(torch.as_tensor(mm["mrope_t_scale"], dtype=torch.float64).reshape(-1))
+                    scaled = True
+                else:
+                    scales.append(torch.ones(grids[-1].shape[0], dtype=torch.float64))
                 mm["_consumed"] = True
         if not pixel:
             return {}
-        return {"pixel_values": torch.cat(pixel).to(self.device), "image_grid_thw": torch.cat(grids).to(self.device)}
+        out = {"pixel_values": torch.cat(pixel).to(self.device), "image_grid_thw": torch.cat(grids).to(self.device)}
+        if scaled:
+            out["mrope_t_scale"] = torch.cat(scales)          # read on the host when positions are built
+        return out

@@ -107,21 +107,24 @@ class TokenizerWorker:
         return arr.to(torch.uint8), (float(fps) if fps else None)
 
     def _builtin_mm_inputs(self, images, videos, text, ids):
-        """Built-in preprocessing.  Every image becomes ``<vision_start> <image_pad> * n <vision_end>``; every
-        temporal patch of a video becomes ``"<t seconds>" <vision_start> <video_pad> * n <vision_end>`` (the
-        layout of the Qwen3-VL processor); the blocks go in front of the text tokens.  Pixels are patchified by
-        :mod:`mllm_b200.utils.image_processor`; a temporal patch is stored like an image of grid ``[1, h, w]``, so
-        the model sees one list of grids in order of appearance."""
+        """Built-in preprocessing.  Every image becomes ``<vision_start> <image_pad> * n <vision_end>``.  A video
+        depends on the family (``video_layout``): ``"frames"`` writes ``"<t seconds>" <vision_start> <video_pad> * n
+        <vision_end>`` per temporal patch (the layout of the Qwen3-VL processor), each stored like an image of grid
+        ``[1, h, w]``; ``"clip"`` writes one ``<vision_start> <video_pad> * (T n) <vision_end>`` block of grid
+        ``[T, h, w]`` (Qwen2-VL, Qwen2.5-VL), and with ``tokens_per_second`` set the temporal position advances by
+        ``seconds per temporal patch x tokens_per_second`` per patch (``mrope_t_scale``).  The blocks go in front of
+        the text tokens unless the text holds placeholders.  Pixels are patchified by
+        :mod:`mllm_b200.utils.image_processor`; the model sees one list of grids in order of appearance."""
         import numpy as np
         import torch
 
-        from ..utils.image_processor import (image_token_count, preprocess_image, preprocess_video,
-                                             sample_frame_indices, video_timestamps)
+        from ..utils.image_processor import (image_token_count, preprocess_image, preprocess_video, sample_frame_indices,
+                                             sample_frame_indices_strided, video_timestamps)
 
         mc = self.mm_config
         text_ids = list(ids) if ids is not None else self.tokenizer.encode(text or "")
         pix, grids, h = [], [], hashlib.sha256()
-        blocks = []                                   # (kind token, token ids of the block, pixel rows, grid rows)
+        blocks = []                     # (kind token, token ids of the block, pixel rows, grid rows, temporal step)
         norm = dict(mean=mc.get("image_mean", 0.5), std=mc.get("image_std", 0.5))
         for item in ([] if images is None else images if isinstance(images, list) else [images]):
             arr = item if isinstance(item, (np.ndarray, torch.Tensor)) else np.asarray(self.load_image(item))
@@ -129,14 +132,31 @@ class TokenizerWorker:
             h.update(img.numpy().tobytes())
             pv, g = preprocess_image(img, mc["patch_size"], mc["merge_size"], mc["temporal_patch_size"], **norm)
             blocks.append((mc["image_token_id"], [mc["vision_start_token_id"]] + [mc["image_token_id"]] *
-                           image_token_count(g, mc["merge_size"]) + [mc["vision_end_token_id"]], pv, g))
+                           image_token_count(g, mc["merge_size"]) + [mc["vision_end_token_id"]], pv, g, [1.0]))
         if videos is not None and mc.get("video_token_id") is None:
             raise ValueError("this model has no video token: video_data is not supported")
         for item in ([] if videos is None else videos if isinstance(videos, list) and not _is_frame_list(videos) else [videos]):
             frames, fps = self.load_video(item)
             src_fps = fps or 24.0
-            keep = sample_frame_indices(frames.shape[0], src_fps, float(mc.get("video_fps", 2.0)),
-                                        int(mc.get("video_min_frames", 4)), int(mc.get("video_max_frames", 768)))
+            target, lo, hi = float(mc.get("video_fps", 2.0)), int(mc.get("video_min_frames", 4)), int(mc.get("video_max_frames", 768))
+            if mc.get("video_layout", "frames") == "clip":
+                total = int(frames.shape[0])
+                keep = sample_frame_indices_strided(total, src_fps, target, lo, hi, mc["temporal_patch_size"])
+                frames = frames[keep]
+                h.update(frames.numpy().tobytes())
+                unit = (mc["patch_size"] * mc["merge_size"]) ** 2
+                pv, g = preprocess_video(frames, mc["patch_size"], mc["merge_size"], mc["temporal_patch_size"],
+                                         min_pixels=128 * unit, max_pixels=768 * unit, **norm)
+                T, gh, gw = (int(v) for v in g[0])
+                per = (gh // mc["merge_size"]) * (gw // mc["merge_size"])
+                block = [mc["vision_start_token_id"]] + [mc["video_token_id"]] * (T * per) + [mc["vision_end_token_id"]]
+                step = 1.0
+                if mc.get("tokens_per_second"):
+                    sampled_fps = len(keep) / max(total, 1) * src_fps
+                    step = mc["temporal_patch_size"] / max(sampled_fps, 1e-6) * float(mc["tokens_per_second"])
+                blocks.append((mc["video_token_id"], block, pv, g, [step]))
+                continue
+            keep = sample_frame_indices(frames.shape[0], src_fps, target, lo, hi)
             frames = frames[keep]
             h.update(frames.numpy().tobytes())
             pv, g = preprocess_video(frames, mc["patch_size"], mc["merge_size"], mc["temporal_patch_size"], **norm)
@@ -146,7 +166,7 @@ class TokenizerWorker:
             for t in video_timestamps(keep, src_fps, mc["temporal_patch_size"]):
                 block += self.tokenizer.encode(f"<{t:.1f} seconds>") + [mc["vision_start_token_id"]] + \
                     [mc["video_token_id"]] * per + [mc["vision_end_token_id"]]
-            blocks.append((mc["video_token_id"], block, pv, torch.tensor([[1, gh, gw]] * T, dtype=torch.int64)))
+            blocks.append((mc["video_token_id"], block, pv, torch.tensor([[1, gh, gw]] * T, dtype=torch.int64), [1.0] * T))
         # a block replaces its placeholder  <vision_start> <pad> <vision_end>  in the text (chat templates write
         # one per image / video part), in order of appearance; blocks without one go in front of the text
         vs, ve = mc["vision_start_token_id"], mc["vision_end_token_id"]
@@ -168,25 +188,30 @@ class TokenizerWorker:
                 out_ids += blocks[b][1]
         for chunk, _ in body:
             out_ids += chunk
+        steps = []
         for b in order:
             pix.append(blocks[b][2])
             grids.append(blocks[b][3])
+            steps += blocks[b][4]
         mm = {"pixel_values": torch.cat(pix), "image_grid_thw": torch.cat(grids), "image_hash": h.hexdigest()[:16]}
+        if any(v != 1.0 for v in steps):
+            mm["mrope_t_scale"] = torch.tensor(steps, dtype=torch.float64)
         return out_ids, mm
 
     @staticmethod
     def merge_vision_inputs(ids, image_pixels, image_grids, video_pixels, video_grids, image_token_id: int,
-                            video_token_id: int, vision_start_token_id: int, merge_size: int):
+                            video_token_id: int, vision_start_token_id: int, merge_size: int, video_steps=None):
         """One ``(pixel_values, grid_thw)`` list in order of appearance from a processor's separate image and
         video outputs.  Walks the vision-start tokens of ``ids``: an image block takes the next image grid; a
         video block takes the next temporal patch of the current video as grid ``[1, h, w]`` (a video of grid
         ``[T, h, w]`` whose prompt has one block per temporal patch), or the whole ``[T, h, w]`` grid when the
-        block holds all of its tokens."""
+        block holds all of its tokens.  With ``video_steps`` (one temporal position step per video) a third value
+        is returned: the step of every merged grid, 1 for images."""
         import torch
 
         ig = [] if image_grids is None else image_grids.tolist()
         vg = [] if video_grids is None else video_grids.tolist()
-        pix, grids = [], []
+        pix, grids, steps = [], [], []
         i_img = i_vid = t_in_vid = 0
         img_row = vid_row = 0
         n = len(ids)
@@ -198,6 +223,7 @@ class TokenizerWorker:
                 rows = t * hh * ww
                 pix.append(image_pixels[img_row:img_row + rows])
                 grids.append([t, hh, ww])
+                steps.append(1.0)
                 img_row += rows
                 i_img += 1
             elif ids[k + 1] == video_token_id and i_vid < len(vg):
@@ -213,13 +239,15 @@ class TokenizerWorker:
                 rows = take * hh * ww
                 pix.append(video_pixels[vid_row:vid_row + rows])
                 grids.append([take, hh, ww])
+                steps.append(float(video_steps[i_vid]) if video_steps is not None else 1.0)
                 vid_row += rows
                 t_in_vid += take
                 if t_in_vid >= t:
                     i_vid, t_in_vid = i_vid + 1, 0
         if not pix:
-            return None, None
-        return torch.cat(pix), torch.tensor(grids, dtype=torch.int64)
+            return (None, None) if video_steps is None else (None, None, None)
+        out = torch.cat(pix), torch.tensor(grids, dtype=torch.int64)
+        return out if video_steps is None else out + (torch.tensor(steps, dtype=torch.float64),)
 
     def _processor_mm_inputs(self, images, videos, text):
         """Through the checkpoint's own HF processor; its separate image / video outputs are merged into one list
@@ -244,16 +272,24 @@ class TokenizerWorker:
         out = self.processor(text=text or "", return_tensors="pt", **kw)
         ids = out["input_ids"][0].tolist()
         pv, grid = out.get("pixel_values"), out.get("image_grid_thw")
+        steps = None
         if out.get("pixel_values_videos") is not None:
             mc = self.mm_config or {}
             tok = self.processor
-            pv, grid = self.merge_vision_inputs(
+            if mc.get("tokens_per_second") and out.get("second_per_grid_ts") is not None:
+                steps = [float(v) * float(mc["tokens_per_second"]) for v in out["second_per_grid_ts"]]
+            merged = self.merge_vision_inputs(
                 ids, pv, grid, out["pixel_values_videos"], out["video_grid_thw"],
                 int(mc.get("image_token_id", getattr(tok, "image_token_id", -1))),
                 int(mc.get("video_token_id", getattr(tok, "video_token_id", -1))),
                 int(mc.get("vision_start_token_id", getattr(tok, "vision_start_token_id", -1))),
-                int(mc.get("merge_size", 2)))
-        return ids, {"pixel_values": pv, "image_grid_thw": grid, "image_hash": h.hexdigest()[:16]}
+                int(mc.get("merge_size", 2)), video_steps=steps)
+            pv, grid = merged[0], merged[1]
+            steps = merged[2] if steps is not None else None
+        mm = {"pixel_values": pv, "image_grid_thw": grid, "image_hash": h.hexdigest()[:16]}
+        if steps is not None and bool((steps != 1.0).any()):
+            mm["mrope_t_scale"] = steps
+        return ids, mm
 
     def tokenize(self, req: Dict[str, Any]) -> TokenizedGenerateReqInput:
         text = req.get("text")

@@ -107,6 +107,22 @@ def sample_frame_indices(total_frames: int, source_fps: float, target_fps: float
     return [int(round(i * (total_frames - 1) / (want - 1))) for i in range(want)]
 
 
+def sample_frame_indices_strided(total_frames: int, source_fps: float, target_fps: float = 2.0, min_frames: int = 4,
+                                 max_frames: int = 768, temporal_patch_size: int = 2) -> list:
+    """Frame numbers at a constant stride from frame 0 (the sampling of the Qwen2-VL / Qwen2.5-VL video processor):
+    about ``target_fps`` frames per second inside the frame budget, a whole number of temporal patches."""
+    if total_frames <= 0:
+        return []
+    tp = max(1, temporal_patch_size)
+    cap = (min(max_frames, total_frames) // tp) * tp
+    want = total_frames / max(source_fps, 1e-6) * target_fps
+    want = int(min(max(want, min_frames), cap, total_frames) // tp) * tp
+    if want <= 0:                                    # fewer frames than one temporal patch: keep them all
+        return list(range(total_frames))
+    step = total_frames / want
+    return [int(i * step) for i in range(want)]
+
+
 def video_timestamps(frame_indices, source_fps: float, temporal_patch_size: int = 2) -> list:
     """Seconds shown in front of each temporal patch: the mean of the times of its first and last frame (the
     frame list is padded with its last entry to a whole number of patches)."""
