@@ -1,4 +1,6 @@
-// Attention over the slot-indexed KV pool on tcgen05 tensor cores (head_dim 128).
+// Attention over the slot-indexed KV pool on tcgen05 tensor cores.  The single-role kernel described first is
+// instantiated for head sizes 64, 128 and 256 (one, two or four 64-feature halves per row; the figures below
+// are those of 128); the warp-specialised prefill and decode kernels further down are for head size 128.
 //
 // One kernel serves prefill (ragged new tokens after an optional cached prefix, causal) and
 // decode (one token per request, split over the KV length): a CTA owns one request, one KV
@@ -25,16 +27,13 @@
 namespace mb200 {
 namespace {
 
-constexpr int kD = 128;        // head dim
+constexpr int kD = 128;        // head dim of the specialised kernels (the single-role kernel also takes 64 and 256)
 constexpr int kRows = 128;     // MMA M
 constexpr int kKV = 64;        // KV tokens per tile
 constexpr int kAttnThreads = 128;
 constexpr int kHalfQ = kRows * 128;  // bytes of one 64-feature half of the Q tile
 constexpr int kHalfKV = kKV * 128;   // bytes of one 64-feature half of a K or V tile
-constexpr int kSmemQ = 2 * kHalfQ;                 // 32 KB
-constexpr int kSmemKVBuf = 2 * kHalfKV;            // 16 KB per tensor per buffer
 constexpr int kSmemP = kRows * 128;                // 16 KB
-constexpr int kAttnSmem = kSmemQ + 4 * kSmemKVBuf + kSmemP + 1024 + 64;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;
 
@@ -95,7 +94,26 @@ __device__ __forceinline__ uint32_t swz_off(int row, int chunk, int half_bytes) 
   return (chunk >> 3) * half_bytes + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
 }
 
-__global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const AttnParams p) {
+// NH = number of 64-feature halves of a head: head sizes 64, 128 and 256
+template <int NH>
+struct FwdCfg {
+  static constexpr int kD = 64 * NH;                   // head dim
+  static constexpr int kChunks = 8 * NH;               // 16-byte chunks per row
+  static constexpr int kTokPerPass = kAttnThreads / kChunks;   // KV tokens one pass of the CTA's threads covers
+  static constexpr int kPasses = kKV / kTokPerPass;
+  static constexpr int kSmemQ = NH * kHalfQ;
+  static constexpr int kSmemKVBuf = NH * kHalfKV;      // per tensor per buffer
+  static constexpr int kSmem = kSmemQ + 4 * kSmemKVBuf + kSmemP + 1024 + 64;
+  static constexpr int kTmemCols = NH == 1 ? 128 : (NH == 2 ? 256 : 512);   // 64 (S) + kD (O), a power of two
+  static constexpr int kCtasPerSm = NH == 4 ? 1 : 2;
+};
+
+template <int NH>
+__global__ void __launch_bounds__(kAttnThreads, FwdCfg<NH>::kCtasPerSm) attn_fwd_kernel(const AttnParams p) {
+  using C = FwdCfg<NH>;
+  constexpr int kD = C::kD;
+  constexpr int kSmemQ = C::kSmemQ;
+  constexpr int kSmemKVBuf = C::kSmemKVBuf;
   pdl_wait();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -158,7 +176,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const AttnPar
   }
   __syncthreads();
   if (warp == 0) {
-    tmem_alloc(tmem_holder, 256);
+    tmem_alloc(tmem_holder, C::kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before_sync();
@@ -166,7 +184,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const AttnPar
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
   const uint32_t tmem_s = tmem_base;         // 64 columns
-  const uint32_t tmem_o = tmem_base + 64;    // 128 columns
+  const uint32_t tmem_o = tmem_base + 64;    // kD columns
   const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
 
   // ---- this thread's row ------------------------------------------------------------------
@@ -182,11 +200,11 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const AttnPar
   const uint16_t* vbase = static_cast<const uint16_t*>(p.v_cache);
   const int* rtt = p.req_to_token + static_cast<int64_t>(req) * p.rtt_stride;
 
-  // ---- Q tile: 128 rows x 256 B, 16 chunks per row -------------------------------------------
+  // ---- Q tile: 128 rows x (2 kD) B, kChunks chunks per row ----------------------------------
   {
     const uint32_t sq = smem_u32(sQ);
-    for (int c = tid; c < kRows * 16; c += kAttnThreads) {
-      const int r = c >> 4, ch = c & 15;
+    for (int c = tid; c < kRows * C::kChunks; c += kAttnThreads) {
+      const int r = c / C::kChunks, ch = c % C::kChunks;
       const int tok = r / g;
       const bool ok = (tok < p.tokens_per_tile) && (q0 + tok < q_len);
       const int head = hk * g + r % g;
@@ -196,18 +214,19 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const AttnPar
     }
   }
 
-  // gather of one KV tile: 64 tokens x 16 chunks for K and V; thread handles token (tid>>4)+8*i
-  int slots_next[8];
+  // gather of one KV tile: 64 tokens x kChunks chunks for K and V; thread handles token
+  // tid / kChunks + kTokPerPass * i
+  int slots_next[C::kPasses];
   auto fetch_slots = [&](int tile) {
     const int t0 = kv_begin + tile * kKV;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int t = t0 + (tid >> 4) + 8 * i;
+    for (int i = 0; i < C::kPasses; ++i) {
+      const int t = t0 + tid / C::kChunks + C::kTokPerPass * i;
       slots_next[i] = (tile < n_tiles && t < kv_end) ? __ldg(rtt + t) : -1;
     }
     bool bad = false;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < C::kPasses; ++i) {
       if (slots_next[i] < -1 || slots_next[i] >= p.num_slots) {
         bad = true;
         slots_next[i] = -1;
@@ -218,10 +237,10 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const AttnPar
   auto gather = [&](int buf) {
     const uint32_t sk = smem_u32(sK + buf * kSmemKVBuf);
     const uint32_t sv = smem_u32(sV + buf * kSmemKVBuf);
-    const int ch = tid & 15;
+    const int ch = tid % C::kChunks;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int r = (tid >> 4) + 8 * i;
+    for (int i = 0; i < C::kPasses; ++i) {
+      const int r = tid / C::kChunks + C::kTokPerPass * i;
       const int s = slots_next[i];
       const bool ok = s >= 0;
       const int64_t off = static_cast<int64_t>(ok ? s : 0) * p.kv_tok_stride + hk * p.kv_head_stride + ch * 8;
@@ -252,7 +271,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const AttnPar
       const uint32_t qa = smem_u32(sQ);
       const uint32_t ka = smem_u32(sK + buf * kSmemKVBuf);
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {
+      for (int kk = 0; kk < 4 * NH; ++kk) {
         const uint64_t a_desc = umma_desc_k_sw128(qa + (kk >> 2) * kHalfQ + (kk & 3) * 32);
         const uint64_t b_desc = umma_desc_k_sw128(ka + (kk >> 2) * kHalfKV + (kk & 3) * 32);
         umma_f16(tmem_s, a_desc, b_desc, p.idesc_s, kk > 0 ? 1u : 0u);
@@ -429,7 +448,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const AttnPar
   __syncthreads();
   if (warp == 0) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 256);
+    tmem_dealloc(tmem_base, C::kTmemCols);
   }
 }
 
@@ -1318,6 +1337,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
   pdl_launch_dependents();
   pdl_wait();
   const int b = blockIdx.y, h = blockIdx.x, d = threadIdx.x;
+  const int hd = blockDim.x;                       // one thread per feature of the head
   const int64_t base = (static_cast<int64_t>(b) * hq + h) * splits;
   float m = -INFINITY;
   for (int s = 0; s < splits; ++s) m = fmaxf(m, part_lse[base + s]);
@@ -1326,18 +1346,22 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
     const float l = part_lse[base + s];
     const float w = (l == -INFINITY) ? 0.f : exp2f(l - m);
     den += w;
-    acc += w * part_o[(base + s) * kD + d];
+    acc += w * part_o[(base + s) * hd + d];
   }
   const float v = den > 0.f ? acc / den : 0.f;
-  const int64_t o = (static_cast<int64_t>(b) * hq + h) * kD + d;
+  const int64_t o = (static_cast<int64_t>(b) * hq + h) * hd + d;
   if (out_f16)
     static_cast<__half*>(out)[o] = __float2half_rn(v);
   else
     static_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(v);
 }
 
-bool set_attn_smem() {
-  return ensure_dynamic_smem(reinterpret_cast<const void*>(attn_fwd_kernel), kAttnSmem) == cudaSuccess;
+template <int NH>
+int launch_fwd_cfg(const AttnParams& p, dim3 grid, cudaStream_t s) {
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(attn_fwd_kernel<NH>), FwdCfg<NH>::kSmem) != cudaSuccess) return -3;
+  const cudaError_t err = launch_pdl(attn_fwd_kernel<NH>, grid, dim3(kAttnThreads), FwdCfg<NH>::kSmem, s, p);
+  note_launch();
+  return err == cudaSuccess ? 0 : -4;
 }
 
 }  // namespace
@@ -1398,10 +1422,12 @@ int launch_decode_cfg(const AttnParams& p, const AttnArgs& a, dim3 grid, cudaStr
 }
 
 int launch_attention(const AttnArgs& a, cudaStream_t s) {
-  if (a.head_dim != kD || a.hq % a.hkv != 0) return -1;
+  // head size 128 has the specialised prefill and decode kernels; 64 and 256 run on the single-role kernel
+  const int hd = a.head_dim;
+  if ((hd != 64 && hd != 128 && hd != 256) || a.hq % a.hkv != 0) return -1;
+  const bool specialised = hd == kD;
   const int g = a.hq / a.hkv;
   if (g > kRows) return -1;
-  if (!set_attn_smem()) return -3;
   AttnParams p{};
   p.q = a.q;
   p.k_cache = a.k_cache;
@@ -1421,15 +1447,15 @@ int launch_attention(const AttnArgs& a, cudaStream_t s) {
   p.num_slots = a.num_slots;
   p.kv_tok_stride = a.kv_tok_stride;
   p.kv_head_stride = a.kv_head_stride;
-  if (a.kv_tok_stride == static_cast<int64_t>(a.hkv) * kD && a.kv_head_stride == kD) {
+  if (a.kv_tok_stride == static_cast<int64_t>(a.hkv) * hd && a.kv_head_stride == hd) {
     p.kv_row_mul = a.hkv;        // slot-major: rows of one slot are adjacent
     p.kv_row_add = 1;
     p.kv_runs = a.hkv == 1 ? 1 : 0;
-  } else if (a.kv_tok_stride == kD && a.kv_head_stride == a.num_slots * kD) {
+  } else if (a.kv_tok_stride == hd && a.kv_head_stride == a.num_slots * hd) {
     p.kv_row_mul = 1;            // head-major: consecutive slots of a head are consecutive rows
     p.kv_row_add = static_cast<int>(a.num_slots);
     p.kv_runs = 1;
-  } else if (a.is_decode) {
+  } else if (a.is_decode && specialised && g <= 32) {
     return -1;                   // the decode kernel reads the caches through 2-D tensor maps
   }
   p.hq = a.hq;
@@ -1447,10 +1473,10 @@ int launch_attention(const AttnArgs& a, cudaStream_t s) {
   p.cap_post = p.logit_cap * kLog2e;
   const uint32_t fmt = a.dt == kF16 ? 0u : 1u;
   p.idesc_s = umma_idesc(kRows, kKV, 1, fmt, fmt, 0, 0);
-  p.idesc_o = umma_idesc(kRows, kD, 1, fmt, fmt, 0, 1);
+  p.idesc_o = umma_idesc(kRows, hd, 1, fmt, fmt, 0, 1);
   if (a.batch <= 0) return 0;
   dim3 grid;
-  if (a.is_decode && g <= 32) {
+  if (specialised && a.is_decode && g <= 32) {
     const int nq = g <= 16 ? 16 : 32;
     p.idesc_s = umma_idesc(kRows, nq, 1, fmt, fmt, 0, 0);
     p.idesc_o = umma_idesc(kRows, nq, 1, fmt, fmt, 1, 0);
@@ -1463,7 +1489,7 @@ int launch_attention(const AttnArgs& a, cudaStream_t s) {
     }
     return cudaGetLastError() == cudaSuccess ? 0 : -4;
   }
-  if (!a.is_decode) {
+  if (specialised && !a.is_decode) {
     const int rc = launch_prefill_ws(p, a, s);
     if (rc <= 0) return rc;
   }
@@ -1474,10 +1500,10 @@ int launch_attention(const AttnArgs& a, cudaStream_t s) {
     if (q_tiles <= 0) return 0;
     grid = dim3(q_tiles, a.hkv, a.batch);
   }
-  launch_pdl(attn_fwd_kernel, grid, dim3(kAttnThreads), kAttnSmem, s, p);
-  note_launch();
+  const int rc = hd == 64 ? launch_fwd_cfg<1>(p, grid, s) : hd == 128 ? launch_fwd_cfg<2>(p, grid, s) : launch_fwd_cfg<4>(p, grid, s);
+  if (rc != 0) return rc;
   if (a.is_decode && p.num_splits > 1) {
-    launch_pdl(attn_merge_kernel, dim3(a.hq, a.batch), dim3(kD), 0, s, a.part_o, a.part_lse, a.out, a.hq, p.num_splits, p.out_f16);
+    launch_pdl(attn_merge_kernel, dim3(a.hq, a.batch), dim3(hd), 0, s, a.part_o, a.part_lse, a.out, a.hq, p.num_splits, p.out_f16);
     note_launch();
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;

@@ -380,13 +380,14 @@ void vision_rope_split_pad(const Tensor& qkv, const Tensor& cos, const Tensor& s
   TORCH_CHECK(cos.is_cuda() && cos.scalar_type() == at::kFloat && cos.is_contiguous() && cos.size(0) == T &&
                   cos.size(1) == D / 2 && sin.sizes() == cos.sizes() && sin.scalar_type() == at::kFloat && sin.is_contiguous(),
               "vision_rope_split_pad: fp32 cos / sin [T, D/2]");
+  const int64_t W = q.dim() == 3 ? q.size(2) : 0;
   for (Tensor* t : {&q, &k, &v})
-    TORCH_CHECK(t->is_contiguous() && t->dim() == 3 && t->size(0) == T && t->size(1) == H && t->size(2) == 128 &&
-                    t->scalar_type() == qkv.scalar_type(),
-                "vision_rope_split_pad: outputs [T, H, 128]");
+    TORCH_CHECK(t->is_contiguous() && t->dim() == 3 && t->size(0) == T && t->size(1) == H && t->size(2) == W && W >= D &&
+                    W <= 128 && t->scalar_type() == qkv.scalar_type(),
+                "vision_rope_split_pad: outputs [T, H, W] with D <= W <= 128");
   c10::cuda::CUDAGuard g(qkv.device());
   mb200::launch_vision_rope_split_pad(qkv.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(), q.data_ptr(),
-                                      k.data_ptr(), v.data_ptr(), T, H, D, dtype_of(qkv), stream_of(qkv));
+                                      k.data_ptr(), v.data_ptr(), T, H, D, W, dtype_of(qkv), stream_of(qkv));
 }
 
 void vision_pos_embed_add(Tensor& x, const Tensor& table, const Tensor& idx, const Tensor& w) {
@@ -770,12 +771,11 @@ void attention_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_c
                        const Tensor& q_start, double scale, Tensor& out, int64_t max_q_len, bool causal, int64_t window,
                        double logit_cap) {
   check_half(q, "q");
-  TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.stride(2) == 1 && q.stride(1) == 128, "q must be [T,Hq,128]");
+  TORCH_CHECK(q.dim() == 3, "q must be [T,Hq,D]");
+  const int64_t hd = q.size(2);
+  TORCH_CHECK((hd == 64 || hd == 128 || hd == 256) && q.stride(2) == 1 && q.stride(1) == hd, "q must be [T,Hq,D], D 64, 128 or 256");
   TORCH_CHECK(out.is_contiguous() && out.sizes() == q.sizes() && out.scalar_type() == q.scalar_type(), "out");
-  check_kv_cache(k_cache, v_cache, q.scalar_type(), k_cache.size(1), 128);
-  TORCH_CHECK(k_cache.dim() == 3 && k_cache.size(2) == 128 &&
-                  k_cache.scalar_type() == q.scalar_type(),
-              "kv cache [slots,Hkv,128] of q's dtype");
+  check_kv_cache(k_cache, v_cache, q.scalar_type(), k_cache.size(1), hd);
   for (const Tensor* t : {&req_to_token, &req_pool_indices, &seq_lens, &prefix_lens, &q_start})
     TORCH_CHECK(t->scalar_type() == at::kInt && t->is_cuda(), "index tensors must be int32 CUDA tensors");
   TORCH_CHECK(req_to_token.dim() == 2 && req_to_token.stride(1) == 1, "req_to_token layout");
@@ -800,7 +800,7 @@ void attention_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_c
   a.batch = req_pool_indices.numel();
   a.hq = q.size(1);
   a.hkv = k_cache.size(1);
-  a.head_dim = 128;
+  a.head_dim = static_cast<int>(hd);
   a.max_q_len = max_q_len > 0 ? max_q_len : q.size(0);
   a.num_splits = 1;
   a.is_decode = 0;
@@ -817,12 +817,11 @@ void attention_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
                       const Tensor& req_pool_indices, const Tensor& seq_lens, double scale, Tensor& out,
                       int64_t max_seq_len, int64_t window, double logit_cap) {
   check_half(q, "q");
-  TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.stride(2) == 1 && q.stride(1) == 128, "q must be [B,Hq,128]");
+  TORCH_CHECK(q.dim() == 3, "q must be [B,Hq,D]");
+  const int64_t hd = q.size(2);
+  TORCH_CHECK((hd == 64 || hd == 128 || hd == 256) && q.stride(2) == 1 && q.stride(1) == hd, "q must be [B,Hq,D], D 64, 128 or 256");
   TORCH_CHECK(out.is_contiguous() && out.sizes() == q.sizes() && out.scalar_type() == q.scalar_type(), "out");
-  check_kv_cache(k_cache, v_cache, q.scalar_type(), k_cache.size(1), 128);
-  TORCH_CHECK(k_cache.dim() == 3 && k_cache.size(2) == 128 &&
-                  k_cache.scalar_type() == q.scalar_type(),
-              "kv cache [slots,Hkv,128] of q's dtype");
+  check_kv_cache(k_cache, v_cache, q.scalar_type(), k_cache.size(1), hd);
   for (const Tensor* t : {&req_to_token, &req_pool_indices, &seq_lens})
     TORCH_CHECK(t->scalar_type() == at::kInt && t->is_cuda(), "index tensors must be int32 CUDA tensors");
   c10::cuda::CUDAGuard g(q.device());
@@ -836,7 +835,7 @@ void attention_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
                                            st.num_sms);
   Tensor part_o, part_lse;
   if (a.num_splits > 1) {
-    part_o = torch::empty({a.batch, a.hq, a.num_splits, 128}, q.options().dtype(torch::kFloat32));
+    part_o = torch::empty({a.batch, a.hq, a.num_splits, hd}, q.options().dtype(torch::kFloat32));
     part_lse = torch::empty({a.batch, a.hq, a.num_splits}, q.options().dtype(torch::kFloat32));
     a.part_o = part_o.data_ptr<float>();
     a.part_lse = part_lse.data_ptr<float>();
@@ -854,7 +853,7 @@ void attention_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
   a.q_stride = q.stride(0);
   a.rtt_stride = req_to_token.stride(0);
   a.num_slots = k_cache.size(0);
-  a.head_dim = 128;
+  a.head_dim = static_cast<int>(hd);
   a.is_decode = 1;
   a.scale = static_cast<float>(scale);
   a.window = static_cast<int>(window);

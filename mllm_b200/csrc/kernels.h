@@ -243,7 +243,7 @@ void launch_rmsnorm_gated(const void* x, const void* gate, const void* w, void* 
 // qkv [T, 3, H, D] (D <= 128, D % 8 == 0) -> q, k, v [T, H, 128] zero-padded; q and k get the 2-D rotary
 // embedding: out[i] = x[i] c[i] - x[i + D/2] s[i], out[i + D/2] = x[i + D/2] c[i] + x[i] s[i], cos/sin fp32 [T, D/2].
 void launch_vision_rope_split_pad(const void* qkv, const float* cos, const float* sin, void* q, void* k, void* v,
-                                  int tokens, int heads, int head_dim, DType dt, cudaStream_t s);
+                                  int tokens, int heads, int head_dim, int out_dim, DType dt, cudaStream_t s);
 // x[t, :] += sum_i w[i, t] * table[idx[i, t], :]  (i < 4: bilinear corners); idx int64 [4, T], w fp32 [4, T]
 void launch_vision_pos_embed_add(void* x, const void* table, const int64_t* idx, const float* w, int tokens, int hidden,
                                  DType dt, cudaStream_t s);

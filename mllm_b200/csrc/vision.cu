@@ -9,11 +9,12 @@
 namespace mb200 {
 namespace {
 
-// one warp per (token, head); lane handles elements lane, lane + 32, ... of the padded 128-wide row
+// one warp per (token, head); lane handles elements lane, lane + 32, ... of the output row, which is out_dim wide
+// (the head size itself, or a wider row whose tail is zero)
 template <typename T>
 __global__ void vision_rope_split_pad_kernel(const T* __restrict__ qkv, const float* __restrict__ cos,
                                              const float* __restrict__ sin, T* __restrict__ q, T* __restrict__ k,
-                                             T* __restrict__ v, int tokens, int heads, int head_dim) {
+                                             T* __restrict__ v, int tokens, int heads, int head_dim, int out_dim) {
   pdl_wait();
   const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (w >= tokens * heads) return;
@@ -22,8 +23,8 @@ __global__ void vision_rope_split_pad_kernel(const T* __restrict__ qkv, const fl
   const int half = head_dim >> 1;
   const T* src = qkv + (static_cast<int64_t>(t) * 3 * heads + h) * head_dim;
   const int64_t plane = static_cast<int64_t>(heads) * head_dim;
-  const int64_t dst = (static_cast<int64_t>(t) * heads + h) * 128;
-  for (int i = lane; i < 128; i += 32) {
+  const int64_t dst = (static_cast<int64_t>(t) * heads + h) * out_dim;
+  for (int i = lane; i < out_dim; i += 32) {
     float oq = 0.f, ok = 0.f, ov = 0.f;
     if (i < head_dim) {
       const int f = i < half ? i : i - half;
@@ -73,12 +74,13 @@ __global__ void gelu_erf_kernel(const T* __restrict__ x, T* __restrict__ out, in
 }  // namespace
 
 void launch_vision_rope_split_pad(const void* qkv, const float* cos, const float* sin, void* q, void* k, void* v,
-                                  int tokens, int heads, int head_dim, DType dt, cudaStream_t s) {
+                                  int tokens, int heads, int head_dim, int out_dim, DType dt, cudaStream_t s) {
   if (tokens == 0) return;
   const int warps = 8;
   const dim3 grid((tokens * heads + warps - 1) / warps), block(warps * 32);
   MB200_DISPATCH_HALF(dt, (launch_pdl(vision_rope_split_pad_kernel<T>, grid, block, 0, s, static_cast<const T*>(qkv), cos, sin,
-                                      static_cast<T*>(q), static_cast<T*>(k), static_cast<T*>(v), tokens, heads, head_dim)));
+                                      static_cast<T*>(q), static_cast<T*>(k), static_cast<T*>(v), tokens, heads, head_dim,
+                                      out_dim)));
   note_launch();
 }
 

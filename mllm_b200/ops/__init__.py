@@ -569,10 +569,16 @@ def tp_reduce_add_rmsnorm(partial: torch.Tensor, residual: Optional[torch.Tensor
 # --------------------------------------------------------------------------
 # attention
 # --------------------------------------------------------------------------
+# Head sizes the tcgen05 attention kernels take: 128 through the specialised prefill and decode kernels, 64 and 256
+# through the single-role kernel.  MLLM_B200_ATTN_HEAD_SIZES=128 sends the other two back to the library / PyTorch
+# paths (and the vision towers back to zero-padding their 64-wide heads to 128).
+_ATTN_HEAD_SIZES = tuple(int(v) for v in os.environ.get("MLLM_B200_ATTN_HEAD_SIZES", "64,128,256").split(",") if v.strip())
+
+
 def _attention_kernel_ok(q: torch.Tensor, k_cache: torch.Tensor, window, logit_cap) -> bool:
-    """The tcgen05 attention kernels cover head size 128 (causal, optionally with a sliding window and a soft cap
-    on the scores) and a cache of the activation dtype."""
-    return use_kernels(q) and q.shape[-1] == 128 and k_cache.dtype == q.dtype
+    """The tcgen05 attention kernels cover head sizes 64, 128 and 256 (causal, optionally with a sliding window and a
+    soft cap on the scores) and a cache of the activation dtype."""
+    return use_kernels(q) and q.shape[-1] in _ATTN_HEAD_SIZES and k_cache.dtype == q.dtype
 
 
 def attention_prefill(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, prefix_lens,
@@ -580,7 +586,7 @@ def attention_prefill(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_l
                       logit_cap: float = 0.0, seq_lens_cpu=None, prefix_lens_cpu=None) -> torch.Tensor:
     """Causal attention of new tokens over cached prefix + themselves.  ``window``: sliding-window attention
     (each query sees its last ``window`` keys); ``logit_cap``: soft-capping of the scores; both are mask /
-    score options of the tcgen05 kernels.  Head sizes other than 128 and caches of another dtype take
+    score options of the tcgen05 kernels.  Head sizes other than 64 / 128 / 256 and caches of another dtype take
     library / PyTorch fallbacks."""
     if _attention_kernel_ok(q, k_cache, window, logit_cap) and hasattr(ext(), "attention_prefill"):
         if out is None:
@@ -615,14 +621,14 @@ def attention_decode(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_le
 
 
 def attention_varlen_bidirectional(q, k, v, cu_seqlens, scale: float) -> torch.Tensor:
-    """Bidirectional attention inside each segment; q, k, v [T, H, D].  On the GPU the head dimension is
-    zero-padded to 128 and the tcgen05 prefill kernel runs without its causal mask, every segment being
-    one "request" whose keys sit at rows ``cu[i]..cu[i+1]`` of k / v."""
-    if not use_kernels(q) or q.shape[-1] > 128:
+    """Bidirectional attention inside each segment; q, k, v [T, H, D].  On the GPU the tcgen05 prefill kernel runs
+    without its causal mask, every segment being one "request" whose keys sit at rows ``cu[i]..cu[i+1]`` of k / v;
+    a head size the kernel has no instantiation for is zero-padded to 128."""
+    if not use_kernels(q) or (q.shape[-1] > 128 and q.shape[-1] not in _ATTN_HEAD_SIZES):
         return ref.attention_varlen_bidirectional(q, k, v, cu_seqlens.cu_host if isinstance(cu_seqlens, VarlenPlan) else cu_seqlens,
                                                   scale)
     D = q.shape[-1]
-    if D != 128:
+    if D not in _ATTN_HEAD_SIZES:
         pad = (0, 128 - D)
         q, k, v = (torch.nn.functional.pad(t, pad) for t in (q, k, v))
     return _varlen_bidirectional_padded(q.contiguous(), k.contiguous(), v.contiguous(), cu_seqlens, scale)[..., :D]
@@ -667,7 +673,8 @@ def vision_attention(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, cu
     D = qkv.shape[1] // (3 * num_heads)
     q4 = qkv.view(T, 3, num_heads, D)
     if use_kernels(qkv) and D <= 128 and D % 2 == 0:
-        q = torch.empty((T, num_heads, 128), dtype=qkv.dtype, device=qkv.device)
+        width = D if D in _ATTN_HEAD_SIZES else 128              # 64-wide heads run unpadded
+        q = torch.empty((T, num_heads, width), dtype=qkv.dtype, device=qkv.device)
         k, v = torch.empty_like(q), torch.empty_like(q)
         cos32 = cos if (cos.dtype == torch.float32 and cos.is_contiguous()) else cos.float().contiguous()
         sin32 = sin if (sin.dtype == torch.float32 and sin.is_contiguous()) else sin.float().contiguous()

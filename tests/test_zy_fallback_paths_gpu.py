@@ -1,7 +1,8 @@
-"""Model configurations that leave the tcgen05 attention kernels (head size other than 128, sliding window,
-8-bit KV cache) on a GPU: GEMMs, norms and the rest still run on the package's kernels, attention on the
-library / batched PyTorch fallbacks.  Each case compares the GPU model (bf16) with the CPU model (fp32) holding
-the same weights: prefill in two chunks, then decode."""
+"""Model configurations off the main path of the attention kernels on a GPU: head sizes 64 and 256 (the
+single-role tcgen05 kernel; the fused q/k prologue is written for head size 128, so norms, rotation and the cache
+write run as separate steps), a sliding window, and an 8-bit KV cache (attention on the library / batched PyTorch
+fallbacks).  Each case compares the GPU model (bf16) with the CPU model (fp32) holding the same weights: prefill
+in two chunks, then decode."""
 import pytest
 import torch
 
@@ -64,7 +65,7 @@ def _close(got, want, floor=0.985):
     ("qwen2-tiny", dict(head_dim=64)),                                                     # q/k/v biases + head size 64
     ("qwen3.5-tiny", dict(head_dim=256)),                                                  # hybrid model, published head size
 ])
-def test_gpu_model_on_fallback_attention_matches_cpu(preset, overrides):
+def test_gpu_model_off_the_main_attention_path_matches_cpu(preset, overrides):
     gpu, cpu = _pair(preset, **overrides)
     ids = torch.randint(0, 1000, (2, 24), generator=torch.Generator().manual_seed(0))
     got, want = _run(gpu, ids), _run(cpu, ids)
