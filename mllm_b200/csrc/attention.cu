@@ -68,6 +68,7 @@ struct AttnParams {
   float logit_cap;         // soft cap: score = cap * tanh(score / cap) before the softmax (0 = off)
   float scale;             // softmax scale (used with the soft cap)
   float cap_pre, cap_post; // soft cap: score in the log2 domain = cap_post * tanh(raw * cap_pre)
+  int kv_fmt;              // single-role kernel only: 1 / 2 = the caches hold unscaled e4m3 / e5m2 bytes
   uint32_t idesc_s, idesc_o;
 };
 
@@ -108,7 +109,9 @@ struct FwdCfg {
   static constexpr int kCtasPerSm = NH == 4 ? 1 : 2;
 };
 
-template <int NH>
+// KV8: the caches hold 8-bit floats; a tile is then read with plain loads, widened to the activation dtype in
+// registers and stored into the same swizzled operand layout (the tensor core sees 16-bit operands either way)
+template <int NH, bool KV8>
 __global__ void __launch_bounds__(kAttnThreads, FwdCfg<NH>::kCtasPerSm) attn_fwd_kernel(const AttnParams p) {
   using C = FwdCfg<NH>;
   constexpr int kD = C::kD;
@@ -238,15 +241,51 @@ __global__ void __launch_bounds__(kAttnThreads, FwdCfg<NH>::kCtasPerSm) attn_fwd
     const uint32_t sk = smem_u32(sK + buf * kSmemKVBuf);
     const uint32_t sv = smem_u32(sV + buf * kSmemKVBuf);
     const int ch = tid % C::kChunks;
+    if constexpr (KV8) {
+      // all loads of the tile first (they are independent), then widen and store
+      const uint8_t* k8 = static_cast<const uint8_t*>(p.k_cache);
+      const uint8_t* v8 = static_cast<const uint8_t*>(p.v_cache);
+      uint2 kr[C::kPasses], vr[C::kPasses];
 #pragma unroll
-    for (int i = 0; i < C::kPasses; ++i) {
-      const int r = tid / C::kChunks + C::kTokPerPass * i;
-      const int s = slots_next[i];
-      const bool ok = s >= 0;
-      const int64_t off = static_cast<int64_t>(ok ? s : 0) * p.kv_tok_stride + hk * p.kv_head_stride + ch * 8;
-      const uint32_t so = swz_off(r, ch, kHalfKV);
-      cp_async16(sk + so, kbase + off, ok);
-      cp_async16(sv + so, vbase + off, ok);
+      for (int i = 0; i < C::kPasses; ++i) {
+        const int s = slots_next[i];
+        kr[i] = vr[i] = make_uint2(0u, 0u);
+        if (s >= 0) {
+          const int64_t off = static_cast<int64_t>(s) * p.kv_tok_stride + hk * p.kv_head_stride + ch * 8;
+          kr[i] = __ldg(reinterpret_cast<const uint2*>(k8 + off));
+          vr[i] = __ldg(reinterpret_cast<const uint2*>(v8 + off));
+        }
+      }
+      auto widen = [&](uint32_t two) -> uint32_t {   // two fp8 bytes -> two 16-bit values of the activation dtype
+        const float2 f = unpack_fp8x2(two, p.kv_fmt);
+        if (p.out_f16) {
+          __half2 h = __floats2half2_rn(f.x, f.y);
+          return *reinterpret_cast<uint32_t*>(&h);
+        }
+        return pack_bf16x2(f.x, f.y);
+      };
+#pragma unroll
+      for (int i = 0; i < C::kPasses; ++i) {
+        const int r = tid / C::kChunks + C::kTokPerPass * i;
+        const uint32_t so = swz_off(r, ch, kHalfKV);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sk + so), "r"(widen(kr[i].x)), "r"(widen(kr[i].x >> 16)),
+                     "r"(widen(kr[i].y)), "r"(widen(kr[i].y >> 16))
+                     : "memory");
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sv + so), "r"(widen(vr[i].x)), "r"(widen(vr[i].x >> 16)),
+                     "r"(widen(vr[i].y)), "r"(widen(vr[i].y >> 16))
+                     : "memory");
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < C::kPasses; ++i) {
+        const int r = tid / C::kChunks + C::kTokPerPass * i;
+        const int s = slots_next[i];
+        const bool ok = s >= 0;
+        const int64_t off = static_cast<int64_t>(ok ? s : 0) * p.kv_tok_stride + hk * p.kv_head_stride + ch * 8;
+        const uint32_t so = swz_off(r, ch, kHalfKV);
+        cp_async16(sk + so, kbase + off, ok);
+        cp_async16(sv + so, vbase + off, ok);
+      }
     }
   };
 
@@ -1356,12 +1395,16 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
     static_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(v);
 }
 
-template <int NH>
-int launch_fwd_cfg(const AttnParams& p, dim3 grid, cudaStream_t s) {
-  if (ensure_dynamic_smem(reinterpret_cast<const void*>(attn_fwd_kernel<NH>), FwdCfg<NH>::kSmem) != cudaSuccess) return -3;
-  const cudaError_t err = launch_pdl(attn_fwd_kernel<NH>, grid, dim3(kAttnThreads), FwdCfg<NH>::kSmem, s, p);
+template <int NH, bool KV8>
+int launch_fwd_one(const AttnParams& p, dim3 grid, cudaStream_t s) {
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(attn_fwd_kernel<NH, KV8>), FwdCfg<NH>::kSmem) != cudaSuccess) return -3;
+  const cudaError_t err = launch_pdl(attn_fwd_kernel<NH, KV8>, grid, dim3(kAttnThreads), FwdCfg<NH>::kSmem, s, p);
   note_launch();
   return err == cudaSuccess ? 0 : -4;
+}
+template <int NH>
+int launch_fwd_cfg(const AttnParams& p, dim3 grid, cudaStream_t s) {
+  return p.kv_fmt != 0 ? launch_fwd_one<NH, true>(p, grid, s) : launch_fwd_one<NH, false>(p, grid, s);
 }
 
 }  // namespace
@@ -1425,7 +1468,8 @@ int launch_attention(const AttnArgs& a, cudaStream_t s) {
   // head size 128 has the specialised prefill and decode kernels; 64 and 256 run on the single-role kernel
   const int hd = a.head_dim;
   if ((hd != 64 && hd != 128 && hd != 256) || a.hq % a.hkv != 0) return -1;
-  const bool specialised = hd == kD;
+  // the specialised kernels move K and V with the TMA engine as they are stored: a cache of the activation dtype
+  const bool specialised = hd == kD && a.kv_fmt == 0;
   const int g = a.hq / a.hkv;
   if (g > kRows) return -1;
   AttnParams p{};
@@ -1471,6 +1515,7 @@ int launch_attention(const AttnArgs& a, cudaStream_t s) {
   p.logit_cap = a.logit_cap > 0.f ? a.logit_cap : 0.f;
   p.cap_pre = p.logit_cap > 0.f ? a.scale / p.logit_cap : 0.f;
   p.cap_post = p.logit_cap * kLog2e;
+  p.kv_fmt = a.kv_fmt;
   const uint32_t fmt = a.dt == kF16 ? 0u : 1u;
   p.idesc_s = umma_idesc(kRows, kKV, 1, fmt, fmt, 0, 0);
   p.idesc_o = umma_idesc(kRows, hd, 1, fmt, fmt, 0, 1);

@@ -120,13 +120,18 @@ void embedding(const Tensor& ids, const Tensor& table, Tensor& out) {
 }
 
 // K and V caches: [slots, kv heads, head_dim] views with unit stride along head_dim, equal strides for K and V
-// and 16-byte aligned rows; slot-major and head-major storage both qualify.
-static void check_kv_cache(const Tensor& k_cache, const Tensor& v_cache, at::ScalarType dt, int64_t hkv, int64_t head_dim) {
+// and rows aligned to 8 elements; slot-major and head-major storage both qualify.  The element type is the
+// activation dtype (returns 0) or an unscaled 8-bit float (returns 1 for e4m3, 2 for e5m2).
+static int check_kv_cache(const Tensor& k_cache, const Tensor& v_cache, at::ScalarType dt, int64_t hkv, int64_t head_dim) {
+  const auto ct = k_cache.scalar_type();
+  const int fmt = ct == dt ? 0 : ct == at::kFloat8_e4m3fn ? 1 : ct == at::kFloat8_e5m2 ? 2 : -1;
   TORCH_CHECK(k_cache.dim() == 3 && v_cache.dim() == 3 && k_cache.sizes() == v_cache.sizes() &&
                   k_cache.strides() == v_cache.strides() && k_cache.stride(2) == 1 && k_cache.size(1) == hkv &&
                   k_cache.size(2) == head_dim && k_cache.stride(0) % 8 == 0 && k_cache.stride(1) % 8 == 0 &&
-                  k_cache.scalar_type() == dt && v_cache.scalar_type() == dt,
-              "kv cache: [slots, kv_heads, head_dim] views of the activation dtype with unit inner stride");
+                  fmt >= 0 && v_cache.scalar_type() == ct && k_cache.is_cuda() && v_cache.is_cuda(),
+              "kv cache: [slots, kv_heads, head_dim] views of the activation dtype, float8_e4m3fn or float8_e5m2, "
+              "with unit inner stride");
+  return fmt;
 }
 
 void qk_norm_rope_kv_write(Tensor& qkv, const c10::optional<Tensor>& q_w, const c10::optional<Tensor>& k_w,
@@ -140,7 +145,7 @@ void qk_norm_rope_kv_write(Tensor& qkv, const c10::optional<Tensor>& q_w, const 
   TORCH_CHECK(positions.scalar_type() == at::kLong && positions.is_contiguous(), "positions int64 contiguous");
   TORCH_CHECK(cache_loc.scalar_type() == at::kLong && cache_loc.is_contiguous(), "cache_loc int64 contiguous");
   TORCH_CHECK(inv_freq.scalar_type() == at::kFloat && inv_freq.numel() == head_dim / 2, "inv_freq fp32 [D/2]");
-  check_kv_cache(k_cache, v_cache, qkv.scalar_type(), hkv, head_dim);
+  const int kv_fmt = check_kv_cache(k_cache, v_cache, qkv.scalar_type(), hkv, head_dim);
   const int tokens = qkv.size(0);
   const int pos_rows = positions.dim() == 2 ? positions.size(0) : 1;
   TORCH_CHECK(positions.numel() == static_cast<int64_t>(pos_rows) * tokens, "positions size");
@@ -152,7 +157,7 @@ void qk_norm_rope_kv_write(Tensor& qkv, const c10::optional<Tensor>& q_w, const 
       positions.data_ptr<int64_t>(), pos_rows, axis_map.has_value() ? axis_map->data_ptr<int8_t>() : nullptr,
       inv_freq.data_ptr<float>(), cache_loc.data_ptr<int64_t>(), k_cache.data_ptr(), v_cache.data_ptr(),
       k_cache.stride(0), k_cache.stride(1), tokens, hq,
-      hkv, head_dim, qkv.stride(0), k_cache.size(0), static_cast<float>(eps), dtype_of(qkv),
+      hkv, head_dim, qkv.stride(0), k_cache.size(0), static_cast<float>(eps), dtype_of(qkv), kv_fmt,
       st.status.data_ptr<int>(), stream_of(qkv));
 }
 
@@ -160,7 +165,7 @@ void kv_write(const Tensor& k, const Tensor& v, const Tensor& loc, Tensor& k_cac
   check_half(k, "k");
   TORCH_CHECK(loc.scalar_type() == at::kLong && loc.is_contiguous(), "loc int64 contiguous");
   const int tokens = loc.numel();
-  check_kv_cache(k_cache, v_cache, k.scalar_type(), k_cache.size(1), k_cache.size(2));
+  const int kv_fmt = check_kv_cache(k_cache, v_cache, k.scalar_type(), k_cache.size(1), k_cache.size(2));
   const int64_t row = k_cache.size(1) * k_cache.size(2);
   TORCH_CHECK(k_cache.size(2) % 8 == 0 && k.numel() == tokens * row && v.numel() == tokens * row, "kv_write: row size");
   auto k2 = k.reshape({tokens, row});
@@ -170,7 +175,7 @@ void kv_write(const Tensor& k, const Tensor& v, const Tensor& loc, Tensor& k_cac
   auto& st = device_state(k.get_device());
   mb200::launch_kv_write(k2.data_ptr(), v2.data_ptr(), loc.data_ptr<int64_t>(), k_cache.data_ptr(),
                          v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1), k_cache.size(2), tokens, row,
-                         k2.stride(0), v2.stride(0), k_cache.size(0), dtype_of(k),
+                         k2.stride(0), v2.stride(0), k_cache.size(0), dtype_of(k), kv_fmt,
                          st.status.data_ptr<int>(), stream_of(k));
 }
 
@@ -775,7 +780,7 @@ void attention_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_c
   const int64_t hd = q.size(2);
   TORCH_CHECK((hd == 64 || hd == 128 || hd == 256) && q.stride(2) == 1 && q.stride(1) == hd, "q must be [T,Hq,D], D 64, 128 or 256");
   TORCH_CHECK(out.is_contiguous() && out.sizes() == q.sizes() && out.scalar_type() == q.scalar_type(), "out");
-  check_kv_cache(k_cache, v_cache, q.scalar_type(), k_cache.size(1), hd);
+  const int kv_fmt = check_kv_cache(k_cache, v_cache, q.scalar_type(), k_cache.size(1), hd);
   for (const Tensor* t : {&req_to_token, &req_pool_indices, &seq_lens, &prefix_lens, &q_start})
     TORCH_CHECK(t->scalar_type() == at::kInt && t->is_cuda(), "index tensors must be int32 CUDA tensors");
   TORCH_CHECK(req_to_token.dim() == 2 && req_to_token.stride(1) == 1, "req_to_token layout");
@@ -801,6 +806,7 @@ void attention_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_c
   a.hq = q.size(1);
   a.hkv = k_cache.size(1);
   a.head_dim = static_cast<int>(hd);
+  a.kv_fmt = kv_fmt;
   a.max_q_len = max_q_len > 0 ? max_q_len : q.size(0);
   a.num_splits = 1;
   a.is_decode = 0;
@@ -821,7 +827,7 @@ void attention_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
   const int64_t hd = q.size(2);
   TORCH_CHECK((hd == 64 || hd == 128 || hd == 256) && q.stride(2) == 1 && q.stride(1) == hd, "q must be [B,Hq,D], D 64, 128 or 256");
   TORCH_CHECK(out.is_contiguous() && out.sizes() == q.sizes() && out.scalar_type() == q.scalar_type(), "out");
-  check_kv_cache(k_cache, v_cache, q.scalar_type(), k_cache.size(1), hd);
+  const int kv_fmt = check_kv_cache(k_cache, v_cache, q.scalar_type(), k_cache.size(1), hd);
   for (const Tensor* t : {&req_to_token, &req_pool_indices, &seq_lens})
     TORCH_CHECK(t->scalar_type() == at::kInt && t->is_cuda(), "index tensors must be int32 CUDA tensors");
   c10::cuda::CUDAGuard g(q.device());
@@ -854,6 +860,7 @@ void attention_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
   a.rtt_stride = req_to_token.stride(0);
   a.num_slots = k_cache.size(0);
   a.head_dim = static_cast<int>(hd);
+  a.kv_fmt = kv_fmt;
   a.is_decode = 1;
   a.scale = static_cast<float>(scale);
   a.window = static_cast<int>(window);

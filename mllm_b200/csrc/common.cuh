@@ -14,6 +14,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -368,6 +369,18 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// 8-bit KV cache formats (no scaling factors): 0 = the cache holds the activation dtype
+constexpr int kKvSame = 0, kKvE4M3 = 1, kKvE5M2 = 2;
+// two floats -> two fp8 bytes (lo in the low byte), round to nearest even, saturating at the format's largest value
+__device__ __forceinline__ uint32_t pack_fp8x2(float lo, float hi, int fmt) {
+  return static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, fmt == kKvE5M2 ? __NV_E5M2 : __NV_E4M3));
+}
+// two fp8 bytes (low 16 bits of `u`) -> two floats; every fp8 value is exact in fp16, bf16 and fp32
+__device__ __forceinline__ float2 unpack_fp8x2(uint32_t u, int fmt) {
+  const __half2_raw r = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(u & 0xffffu), fmt == kKvE5M2 ? __NV_E5M2 : __NV_E4M3);
+  return __half22float2(*reinterpret_cast<const __half2*>(&r));
+}
+
 __device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
   __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&u);
   return __bfloat1622float2(v);

@@ -313,8 +313,8 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const T* __res
                                              const T* __restrict__ k_w, const int64_t* __restrict__ positions,
                                              int pos_rows, const int8_t* __restrict__ axis_map,
                                              const float* __restrict__ inv_freq,
-                                             const int64_t* __restrict__ cache_loc, T* __restrict__ k_cache,
-                                             T* __restrict__ v_cache, int64_t kv_tok_stride,
+                                             const int64_t* __restrict__ cache_loc, void* __restrict__ k_cache,
+                                             void* __restrict__ v_cache, int kv_fmt, int64_t kv_tok_stride,
                                              int64_t kv_head_stride, int tokens, int hq, int hkv, int hsplit,
                                              int64_t qkv_stride, int64_t num_slots, float eps, int* status) {
   pdl_launch_dependents();
@@ -386,9 +386,16 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const T* __res
       *reinterpret_cast<uint2*>(src) = raw;
     }
     if (!is_q && slot_ok) {
-      T* cache = is_k ? k_cache : v_cache;
+      void* cache = is_k ? k_cache : v_cache;
       const int kvh = is_k ? h - hq : h - hq - hkv;
-      *reinterpret_cast<uint2*>(cache + slot * kv_tok_stride + kvh * kv_head_stride + lane * 4) = raw;
+      const int64_t at = slot * kv_tok_stride + kvh * kv_head_stride + lane * 4;
+      if (kv_fmt == kKvSame) {
+        *reinterpret_cast<uint2*>(static_cast<T*>(cache) + at) = raw;
+      } else {   // 8-bit cache: the 16-bit values that attention would have read, rounded once more
+        const T* e = reinterpret_cast<const T*>(&raw);
+        const uint32_t packed = pack_fp8x2(to_f32(e[0]), to_f32(e[1]), kv_fmt) | (pack_fp8x2(to_f32(e[2]), to_f32(e[3]), kv_fmt) << 16);
+        *reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(cache) + at) = packed;
+      }
     }
   }
 }
@@ -397,7 +404,7 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const T* __res
 // caches; a cache row of head h of slot s starts at s * kv_tok_stride + h * kv_head_stride
 template <typename T>
 __global__ void kv_write_kernel(const T* __restrict__ k, const T* __restrict__ v, const int64_t* __restrict__ loc,
-                                T* __restrict__ k_cache, T* __restrict__ v_cache, int64_t kv_tok_stride,
+                                void* __restrict__ k_cache, void* __restrict__ v_cache, int kv_fmt, int64_t kv_tok_stride,
                                 int64_t kv_head_stride, int head_elems, int tokens, int row_elems,
                                 int64_t k_stride, int64_t v_stride, int64_t num_slots, int* status) {
   pdl_launch_dependents();
@@ -415,8 +422,22 @@ __global__ void kv_write_kernel(const T* __restrict__ k, const T* __restrict__ v
     }
     const int head = (c << 3) / head_elems;
     const int64_t dst = slot * kv_tok_stride + head * kv_head_stride + ((c << 3) - head * head_elems);
-    *reinterpret_cast<uint4*>(k_cache + dst) = reinterpret_cast<const uint4*>(k + t * k_stride)[c];
-    *reinterpret_cast<uint4*>(v_cache + dst) = reinterpret_cast<const uint4*>(v + t * v_stride)[c];
+    const uint4 kr = reinterpret_cast<const uint4*>(k + t * k_stride)[c];
+    const uint4 vr = reinterpret_cast<const uint4*>(v + t * v_stride)[c];
+    if (kv_fmt == kKvSame) {
+      *reinterpret_cast<uint4*>(static_cast<T*>(k_cache) + dst) = kr;
+      *reinterpret_cast<uint4*>(static_cast<T*>(v_cache) + dst) = vr;
+    } else {
+      const T* ke = reinterpret_cast<const T*>(&kr);
+      const T* ve = reinterpret_cast<const T*>(&vr);
+      uint2 ko, vo;
+      ko.x = pack_fp8x2(to_f32(ke[0]), to_f32(ke[1]), kv_fmt) | (pack_fp8x2(to_f32(ke[2]), to_f32(ke[3]), kv_fmt) << 16);
+      ko.y = pack_fp8x2(to_f32(ke[4]), to_f32(ke[5]), kv_fmt) | (pack_fp8x2(to_f32(ke[6]), to_f32(ke[7]), kv_fmt) << 16);
+      vo.x = pack_fp8x2(to_f32(ve[0]), to_f32(ve[1]), kv_fmt) | (pack_fp8x2(to_f32(ve[2]), to_f32(ve[3]), kv_fmt) << 16);
+      vo.y = pack_fp8x2(to_f32(ve[4]), to_f32(ve[5]), kv_fmt) | (pack_fp8x2(to_f32(ve[6]), to_f32(ve[7]), kv_fmt) << 16);
+      *reinterpret_cast<uint2*>(static_cast<uint8_t*>(k_cache) + dst) = ko;
+      *reinterpret_cast<uint2*>(static_cast<uint8_t*>(v_cache) + dst) = vo;
+    }
   }
 }
 
@@ -718,7 +739,7 @@ void launch_qk_norm_rope_kv_write(void* qkv, const void* q_w, const void* k_w, c
                                   const int64_t* cache_loc, void* k_cache, void* v_cache, int64_t kv_tok_stride,
                                   int64_t kv_head_stride, int tokens,
                                   int num_q_heads, int num_kv_heads, int head_dim, int64_t qkv_stride,
-                                  int64_t num_slots, float eps, DType dt, int* status, cudaStream_t s) {
+                                  int64_t num_slots, float eps, DType dt, int kv_fmt, int* status, cudaStream_t s) {
   if (tokens == 0 || head_dim != 128) return;
   // warps per token: every head its own warp for a few tokens, a handful of warps per token for long prefills
   // (each then amortises its sines and cosines over heads / hsplit heads)
@@ -729,23 +750,23 @@ void launch_qk_norm_rope_kv_write(void* qkv, const void* q_w, const void* k_w, c
   const int blocks = static_cast<int>((warps * 32 + threads - 1) / threads);
   MB200_DISPATCH_HALF(dt, (launch_pdl(qk_norm_rope_kv_write_kernel<T>, dim3(blocks), dim3(threads), 0, s, 
                               static_cast<T*>(qkv), static_cast<const T*>(q_w), static_cast<const T*>(k_w),
-                              positions, pos_rows, axis_map, inv_freq, cache_loc, static_cast<T*>(k_cache),
-                              static_cast<T*>(v_cache), kv_tok_stride, kv_head_stride, tokens, num_q_heads,
+                              positions, pos_rows, axis_map, inv_freq, cache_loc, k_cache,
+                              v_cache, kv_fmt, kv_tok_stride, kv_head_stride, tokens, num_q_heads,
                               num_kv_heads, hsplit, qkv_stride, num_slots, eps, status)));
   note_launch();
 }
 
 void launch_kv_write(const void* k, const void* v, const int64_t* loc, void* k_cache, void* v_cache,
                      int64_t kv_tok_stride, int64_t kv_head_stride, int head_elems, int tokens,
-                     int row_elems, int64_t k_stride, int64_t v_stride, int64_t num_slots, DType dt, int* status,
+                     int row_elems, int64_t k_stride, int64_t v_stride, int64_t num_slots, DType dt, int kv_fmt, int* status,
                      cudaStream_t s) {
   if (tokens == 0) return;
   const int64_t total = static_cast<int64_t>(tokens) * (row_elems >> 3);
   const int threads = 256;
   const int blocks = static_cast<int>(std::min<int64_t>((total + threads - 1) / threads, 148 * 16));
   MB200_DISPATCH_HALF(dt, (launch_pdl(kv_write_kernel<T>, dim3(blocks), dim3(threads), 0, s, 
-                              static_cast<const T*>(k), static_cast<const T*>(v), loc, static_cast<T*>(k_cache),
-                              static_cast<T*>(v_cache), kv_tok_stride, kv_head_stride, head_elems, tokens, row_elems,
+                              static_cast<const T*>(k), static_cast<const T*>(v), loc, k_cache,
+                              v_cache, kv_fmt, kv_tok_stride, kv_head_stride, head_elems, tokens, row_elems,
                               k_stride, v_stride, num_slots, status)));
   note_launch();
 }

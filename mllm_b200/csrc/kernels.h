@@ -30,7 +30,8 @@ void launch_embedding(const int64_t* ids, const void* table, void* out, int toke
 
 // Per-head RMSNorm of q and k (weights may be null), NeoX rotary embedding and the
 // write of K (normed, rotated) and V into the slot-indexed cache; q and k are updated
-// in place inside the fused qkv activation. head_dim is 128 or 64.
+// in place inside the fused qkv activation. head_dim is 128.  kv_fmt 1 / 2: the caches hold unscaled e4m3 / e5m2
+// bytes and K and V are rounded to that format on the way in.
 // positions: [pos_rows, tokens] int64 with pos_rows 1 (plain RoPE) or 3 (M-RoPE: t,h,w);
 // axis_map[head_dim/2] selects the position row per frequency (null -> row 0).
 // The caches are addressed by strides (in elements): the row of head h of slot s starts at
@@ -41,10 +42,10 @@ void launch_qk_norm_rope_kv_write(void* qkv, const void* q_w, const void* k_w, c
                                   const int64_t* cache_loc, void* k_cache, void* v_cache, int64_t kv_tok_stride,
                                   int64_t kv_head_stride, int tokens,
                                   int num_q_heads, int num_kv_heads, int head_dim, int64_t qkv_stride,
-                                  int64_t num_slots, float eps, DType dt, int* status, cudaStream_t s);
+                                  int64_t num_slots, float eps, DType dt, int kv_fmt, int* status, cudaStream_t s);
 void launch_kv_write(const void* k, const void* v, const int64_t* loc, void* k_cache, void* v_cache,
                      int64_t kv_tok_stride, int64_t kv_head_stride, int head_elems, int tokens,
-                     int row_elems, int64_t k_stride, int64_t v_stride, int64_t num_slots, DType dt, int* status,
+                     int row_elems, int64_t k_stride, int64_t v_stride, int64_t num_slots, DType dt, int kv_fmt, int* status,
                      cudaStream_t s);
 
 // Bookkeeping of one decode step of a static batch (see decode_prepare_kernel): one launch instead of a dozen
@@ -223,6 +224,7 @@ struct AttnArgs {
   int window;               // > 0: a query at position i sees keys i - window + 1 .. i only (causal attention)
   float logit_cap;          // > 0: scores pass through cap * tanh(score / cap) before the softmax
   DType dt;
+  int kv_fmt;               // 0: the caches hold dt; 1 / 2: unscaled e4m3 / e5m2 bytes (strides then count bytes)
 };
 int launch_attention(const AttnArgs& args, cudaStream_t s);
 int decode_num_splits(int batch, int hkv, int max_seq_len, int num_sms);

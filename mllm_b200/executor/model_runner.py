@@ -292,10 +292,10 @@ class ModelRunner:
         elif name in ("float16", "bfloat16"):
             self.kv_cache_dtype = _DTYPES[name]
         elif name in ("fp8_e4m3", "fp8_e5m2"):
-            # 8-bit cache without scaling factors: halves the KV memory; the tcgen05 attention kernels read a
-            # cache of the activation dtype only, so attention then runs on the fallback paths
+            # 8-bit cache without scaling factors: halves the KV memory.  K and V are rounded on the way in; the
+            # single-role attention kernel widens a tile on its way into shared memory (the specialised prefill
+            # and decode kernels read a cache of the activation dtype only)
             self.kv_cache_dtype = torch.float8_e4m3fn if name == "fp8_e4m3" else torch.float8_e5m2
-            logger.warning("kv_cache_dtype %s: attention runs on the library / PyTorch fallback paths", name)
         else:
             raise ValueError(f"unknown kv_cache_dtype {name!r}")
 
@@ -493,8 +493,8 @@ class ModelRunner:
             return
         if pstate.get_pipeline_parallel_world_size() > 1:
             return      # stages exchange activations with point-to-point calls between the layers: eager only
-        if self.kv_cache_dtype != self.dtype:
-            return      # 8-bit cache: attention runs on the fallback paths, which are not captured
+        if self.kv_cache_dtype != self.dtype and not ops.attention_kernels_cover(self.head_dim, self.kv_cache_dtype, self.dtype):
+            return      # 8-bit cache off the kernels: attention runs on paths that are not captured
         from .cuda_graph_runner import CudaGraphRunner
 
         self.cuda_graph_runner = CudaGraphRunner(self)

@@ -508,7 +508,7 @@ def qk_norm_rope_kv_write(
     mrope_sections=None, mrope_interleaved: bool = False,
     inv_freq: Optional[torch.Tensor] = None, axis_map: Optional[torch.Tensor] = None,
 ) -> None:
-    if not use_kernels(qkv) or head_dim != 128 or k_cache.dtype != qkv.dtype:
+    if not use_kernels(qkv) or head_dim != 128 or not _cache_dtype_ok(k_cache, qkv):
         return ref.qk_norm_rope_kv_write(
             qkv, q_weight, k_weight, positions, cache_loc, k_cache, v_cache, num_q_heads, num_kv_heads,
             head_dim, theta, eps, mrope_sections, mrope_interleaved, inv_freq=inv_freq,
@@ -529,7 +529,7 @@ def create_kv_indices(req_to_token, req_pool_indices, seq_lens, kv_start=None, m
 
 
 def kv_write(k, v, loc, k_cache, v_cache) -> None:
-    if not use_kernels(k) or k_cache.dtype != k.dtype:
+    if not use_kernels(k) or not _cache_dtype_ok(k_cache, k):
         return ref.kv_write(k, v, loc, k_cache, v_cache)
     ext().kv_write(k, v, loc.to(torch.int64).contiguous(), k_cache, v_cache)
 
@@ -573,12 +573,26 @@ def tp_reduce_add_rmsnorm(partial: torch.Tensor, residual: Optional[torch.Tensor
 # through the single-role kernel.  MLLM_B200_ATTN_HEAD_SIZES=128 sends the other two back to the library / PyTorch
 # paths (and the vision towers back to zero-padding their 64-wide heads to 128).
 _ATTN_HEAD_SIZES = tuple(int(v) for v in os.environ.get("MLLM_B200_ATTN_HEAD_SIZES", "64,128,256").split(",") if v.strip())
+# An 8-bit KV cache (unscaled e4m3 / e5m2) is written by the fused q/k prologue and the cache-write kernel and read
+# by the single-role attention kernel, which widens a tile on its way into shared memory.  MLLM_B200_KV8_KERNELS=0
+# sends such a cache back to the library / PyTorch paths.
+_KV8_KERNELS = os.environ.get("MLLM_B200_KV8_KERNELS", "1") != "0"
+_KV8_DTYPES = (torch.float8_e4m3fn, torch.float8_e5m2)
+
+
+def _cache_dtype_ok(cache: torch.Tensor, act: torch.Tensor) -> bool:
+    return cache.dtype == act.dtype or (_KV8_KERNELS and cache.dtype in _KV8_DTYPES)
+
+
+def attention_kernels_cover(head_dim: int, cache_dtype, act_dtype) -> bool:
+    """Whether attention of this head size over a cache of this dtype runs on the package's kernels."""
+    return head_dim in _ATTN_HEAD_SIZES and (cache_dtype == act_dtype or (_KV8_KERNELS and cache_dtype in _KV8_DTYPES))
 
 
 def _attention_kernel_ok(q: torch.Tensor, k_cache: torch.Tensor, window, logit_cap) -> bool:
     """The tcgen05 attention kernels cover head sizes 64, 128 and 256 (causal, optionally with a sliding window and a
-    soft cap on the scores) and a cache of the activation dtype."""
-    return use_kernels(q) and q.shape[-1] in _ATTN_HEAD_SIZES and k_cache.dtype == q.dtype
+    soft cap on the scores) and a cache of the activation dtype or of an unscaled 8-bit float."""
+    return use_kernels(q) and q.shape[-1] in _ATTN_HEAD_SIZES and _cache_dtype_ok(k_cache, q)
 
 
 def attention_prefill(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_lens, prefix_lens,
@@ -586,8 +600,8 @@ def attention_prefill(q, k_cache, v_cache, req_to_token, req_pool_indices, seq_l
                       logit_cap: float = 0.0, seq_lens_cpu=None, prefix_lens_cpu=None) -> torch.Tensor:
     """Causal attention of new tokens over cached prefix + themselves.  ``window``: sliding-window attention
     (each query sees its last ``window`` keys); ``logit_cap``: soft-capping of the scores; both are mask /
-    score options of the tcgen05 kernels.  Head sizes other than 64 / 128 / 256 and caches of another dtype take
-    library / PyTorch fallbacks."""
+    score options of the tcgen05 kernels.  Head sizes other than 64 / 128 / 256 and caches that hold neither the
+    activation dtype nor an 8-bit float take library / PyTorch fallbacks."""
     if _attention_kernel_ok(q, k_cache, window, logit_cap) and hasattr(ext(), "attention_prefill"):
         if out is None:
             out = torch.empty((q.shape[0], q.shape[1], q.shape[2]), dtype=q.dtype, device=q.device)
