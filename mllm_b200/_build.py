@@ -36,7 +36,7 @@ CXX_FLAGS = ["-O3", "-std=c++17"]
 EXTENSIONS: Dict[str, Dict[str, List[str]]] = {
     "mllm_b200_C": {
         "sources": ["bindings.cpp", "elementwise.cu", "gemm_tcgen05.cu", "attention.cu", "sampling.cu", "moe.cu",
-                    "comm.cu", "gemm_w4a16.cu", "vision.cu", "gdn.cu", "no_alloc.cu", "ep_a2a.cu", "gemm_smallm.cu", "gemm_smallm_w4.cu"],
+                    "comm.cu", "gemm_w4a16.cu", "vision.cu", "gdn.cu", "gdn_chunk.cu", "no_alloc.cu", "ep_a2a.cu", "gemm_smallm.cu", "gemm_smallm_w4.cu"],
         "headers": ["common.cuh", "kernels.h", "no_alloc.h"],
         "cuda": True,
     },

@@ -376,6 +376,27 @@ void gdn_recurrent(const Tensor& q, const Tensor& k, const Tensor& v, const Tens
   TORCH_CHECK(rc == 0, "gdn_recurrent: head dims must be 128");
 }
 
+void gdn_chunk(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& g, const Tensor& beta, Tensor& state,
+               const Tensor& slots, const Tensor& lens, const Tensor& has, const Tensor& q_start, Tensor& out) {
+  check_half(q, "q");
+  check_ragged(slots, lens, has, q_start);
+  TORCH_CHECK(q.dim() == 3 && q.is_contiguous() && k.is_contiguous() && v.is_contiguous() && k.sizes() == q.sizes() &&
+                  v.size(0) == q.size(0) && v.size(1) == q.size(1) && out.is_contiguous() && out.sizes() == v.sizes() &&
+                  k.scalar_type() == q.scalar_type() && v.scalar_type() == q.scalar_type() && out.scalar_type() == q.scalar_type() &&
+                  g.scalar_type() == at::kFloat && beta.scalar_type() == at::kFloat && g.is_contiguous() && beta.is_contiguous() &&
+                  g.numel() == q.size(0) * q.size(1) && beta.numel() == g.numel() && state.scalar_type() == at::kFloat &&
+                  state.is_contiguous() && state.dim() == 4 && state.size(1) == q.size(1) && state.size(2) == q.size(2) &&
+                  state.size(3) == v.size(2),
+              "gdn_chunk: q, k [T, H, Dk], v [T, H, Dv], g / beta fp32 [T, H], state fp32 [slots, H, Dk, Dv]");
+  c10::cuda::CUDAGuard gd(q.device());
+  auto& st = device_state(q.get_device());
+  const int rc = mb200::launch_gdn_chunk(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr<float>(), beta.data_ptr<float>(),
+                                         state.data_ptr<float>(), slots.data_ptr<int>(), lens.data_ptr<int>(),
+                                         has.data_ptr<int>(), q_start.data_ptr<int>(), out.data_ptr(), slots.numel(),
+                                         q.size(1), q.size(2), v.size(2), st.num_sms, dtype_of(q), stream_of(q));
+  TORCH_CHECK(rc == 0, "gdn_chunk: head dims must be 128 (code ", rc, ")");
+}
+
 // ---- vision tower ----
 void vision_rope_split_pad(const Tensor& qkv, const Tensor& cos, const Tensor& sin, Tensor& q, Tensor& k, Tensor& v) {
   check_half(qkv, "qkv");
@@ -930,6 +951,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_gated", &rmsnorm_gated);
   m.def("gdn_conv1d_silu", &gdn_conv1d_silu);
   m.def("gdn_recurrent", &gdn_recurrent);
+  m.def("gdn_chunk", &gdn_chunk);
   m.def("vision_rope_split_pad", &vision_rope_split_pad);
   m.def("vision_pos_embed_add", &vision_pos_embed_add);
   m.def("gelu_erf", &gelu_erf);

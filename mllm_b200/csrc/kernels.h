@@ -238,6 +238,10 @@ int launch_gdn_conv1d_silu(const void* x, const void* w, void* conv_state, const
 int launch_gdn_recurrent(const void* q, const void* k, const void* v, const float* g, const float* beta, float* state,
                          const int* slots, const int* lens, const int* has_state, const int* q_start, void* out, int batch,
                          int heads, int dk, int dv, DType dt, cudaStream_t s);
+// The same rule evaluated 64 tokens at a time with tensor-core products (prefill); same arguments and state layout.
+int launch_gdn_chunk(const void* q, const void* k, const void* v, const float* g, const float* beta, float* state,
+                     const int* slots, const int* lens, const int* has_state, const int* q_start, void* out, int batch,
+                     int heads, int dk, int dv, int num_sms, DType dt, cudaStream_t s);
 void launch_rmsnorm_gated(const void* x, const void* gate, const void* w, void* out, int rows, int width, float eps, DType dt,
                           cudaStream_t s);
 

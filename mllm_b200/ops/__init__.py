@@ -754,8 +754,10 @@ _GDN_EXTEND_BACKEND = "auto"
 
 
 def set_gdn_extend_backend(name: str) -> None:
-    """``pytorch``: the chunk-parallel PyTorch form on every device; anything else: the CUDA kernel where
-    it applies (``--server.gdn_extend_backend``)."""
+    """How the gated delta rule runs on new tokens (``--server.gdn_extend_backend``).  ``pytorch``: the chunk-parallel
+    PyTorch form on every device; ``cuda_chunkwise``: the chunk-parallel CUDA kernel for every batch; ``mllm_kernel``:
+    the token-sequential CUDA kernel for every batch; anything else: the chunk-parallel kernel for batches that
+    average 32 new tokens per request or more (prefill), the sequential one otherwise (decode, short extends)."""
     global _GDN_EXTEND_BACKEND
     _GDN_EXTEND_BACKEND = str(name)
 
@@ -771,9 +773,11 @@ def gated_delta_rule(q, k, v, g, beta, state, state_indices, seq_lens, has_state
         if q_start is None:
             q_start = torch.cumsum(lens, 0, dtype=torch.int32) - lens
         out = torch.empty_like(v)
-        ext().gdn_recurrent(q.contiguous(), k.contiguous(), v.contiguous(), g.float().contiguous(), beta.float().contiguous(),
-                            state, state_indices.to(torch.int32), lens.to(torch.int32), has.to(torch.int32),
-                            q_start.to(torch.int32), out)
+        chunked = _GDN_EXTEND_BACKEND == "cuda_chunkwise" or (
+            _GDN_EXTEND_BACKEND != "mllm_kernel" and q.shape[0] >= 32 * max(1, lens.numel()))
+        rule = ext().gdn_chunk if chunked and hasattr(ext(), "gdn_chunk") else ext().gdn_recurrent
+        rule(q.contiguous(), k.contiguous(), v.contiguous(), g.float().contiguous(), beta.float().contiguous(),
+             state, state_indices.to(torch.int32), lens.to(torch.int32), has.to(torch.int32), q_start.to(torch.int32), out)
         return out
     lens = seq_lens.tolist() if isinstance(seq_lens, torch.Tensor) else seq_lens
     has = has_state.tolist() if isinstance(has_state, torch.Tensor) else has_state

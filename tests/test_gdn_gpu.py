@@ -53,6 +53,58 @@ def test_gated_delta_rule(lens, has):
     assert (st.cpu() - st_ref).abs().max().item() < 0.02 * st_ref.abs().max().item() + 0.02
 
 
+@pytest.mark.parametrize("lens,has", [([64], [0]), ([1, 63, 65], [1, 0, 1]), ([130, 7], [1, 0]), ([700, 300, 1024], [0, 1, 0]),
+                                      ([200] * 5, [1] * 5)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gated_delta_rule_chunk_kernel(lens, has, dtype):
+    """The chunk-parallel kernel (64 tokens at a time, tensor-core products) against the fp32 token loop: whole
+    chunks, ragged tails, several chunks with the state carried between them, resumed states, both block widths."""
+    torch.manual_seed(3)
+    H, D, B = 4, 128, len(lens)
+    T = sum(lens)
+    q, k, v = (torch.randn(T, H, D, device="cuda").to(dtype) for _ in range(3))
+    g = -torch.rand(T, H, device="cuda") * 0.5
+    beta = torch.rand(T, H, device="cuda")
+    st = (torch.randn(B + 1, H, D, D, device="cuda") * 0.1).contiguous()
+    slots = torch.arange(1, B + 1, device="cuda", dtype=torch.int32)
+    st_ref = st.clone().cpu()
+    want = ref.gated_delta_rule(q.float().cpu(), k.float().cpu(), v.float().cpu(), g.cpu(), beta.cpu(), st_ref, slots.cpu(), lens, has)
+    ops.set_gdn_extend_backend("cuda_chunkwise")
+    try:
+        n0 = ops.launch_count()
+        got = ops.gated_delta_rule(q, k, v, g, beta, st, slots, lens, has)
+        ops.check_status()
+        assert ops.launch_count() == n0 + 1
+    finally:
+        ops.set_gdn_extend_backend("auto")
+    scale = want.abs().max().item()
+    assert (got.float().cpu() - want).abs().max().item() < 0.02 * scale + 0.02
+    assert (st.cpu() - st_ref).abs().max().item() < 0.02 * st_ref.abs().max().item() + 0.02
+    assert torch.equal(st[0].cpu(), st_ref[0])            # a state row of no request is left alone
+
+
+def test_chunk_and_sequential_kernels_agree_on_a_long_prefill():
+    torch.manual_seed(4)
+    H, D, lens = 16, 128, [2048, 1500]
+    T = sum(lens)
+    q, k, v = (torch.randn(T, H, D, device="cuda").bfloat16() for _ in range(3))
+    g = -torch.rand(T, H, device="cuda") * 0.3
+    beta = torch.rand(T, H, device="cuda")
+    slots = torch.tensor([0, 1], device="cuda", dtype=torch.int32)
+    outs, states = [], []
+    for name in ("cuda_chunkwise", "mllm_kernel"):
+        st = torch.zeros(2, H, D, D, device="cuda")
+        ops.set_gdn_extend_backend(name)
+        try:
+            outs.append(ops.gated_delta_rule(q, k, v, g, beta, st, slots, lens, [0, 0]).float())
+        finally:
+            ops.set_gdn_extend_backend("auto")
+        states.append(st)
+    ops.check_status()
+    assert (outs[0] - outs[1]).abs().max().item() < 0.02 * outs[1].abs().max().item() + 0.02
+    assert (states[0] - states[1]).abs().max().item() < 0.02 * states[1].abs().max().item() + 0.02
+
+
 def test_qwen3_5_tiny_gpu_matches_cpu_oracle():
     from mllm_b200.configs import ServerConfig
     from mllm_b200.executor import ModelRunner
