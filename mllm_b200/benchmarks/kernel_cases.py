@@ -3,6 +3,7 @@
     python -m mllm_b200.benchmarks.kernel_cases attn_decode --batch 16 --seq 2050
     python -m mllm_b200.benchmarks.kernel_cases gemm --m 8 --n 4096 --k 12288
     python -m mllm_b200.benchmarks.kernel_cases attn_prefill --batch 2 --seq 2048
+    python -m mllm_b200.benchmarks.kernel_cases gdn --batch 1 --seq 2048 --gdn-backend cuda_chunkwise
 
 Each case allocates inputs larger than the 126 MB L2 where the kernel is memory bound, runs a
 few warm-up launches, then times `--iters` launches with CUDA events and prints one JSON line
@@ -154,9 +155,31 @@ def w4a16(a) -> dict:
             "weight_gbs": a.n * a.k / 2 / ms / 1e6}
 
 
+def gdn(a) -> dict:
+    """Prefill of the gated delta rule: `--batch` requests of `--seq` new tokens, `--hq` heads of 128 x 128."""
+    dev = "cuda"
+    B, L, H, D = a.batch, a.seq, a.hq, 128
+    T = B * L
+    q, k, v = (torch.randn(T, H, D, device=dev).bfloat16() for _ in range(3))
+    g = -torch.rand(T, H, device=dev) * 0.3
+    beta = torch.rand(T, H, device=dev)
+    slots = torch.arange(B, device=dev, dtype=torch.int32)
+    lens = torch.full((B,), L, device=dev, dtype=torch.int32)
+    has = torch.zeros(B, device=dev, dtype=torch.int32)
+    st = torch.zeros(B, H, D, D, device=dev)
+    ops.set_gdn_extend_backend(a.gdn_backend)
+    ms = _time(lambda: ops.gated_delta_rule(q, k, v, g, beta, st, slots, lens, has), a.iters)
+    ops.set_gdn_extend_backend("auto")
+    # per token and head: S^T k, the rank-one update and S^T q touch the 128 x 128 state three times
+    return {"case": "gdn", "backend": a.gdn_backend, "batch": B, "seq": L, "heads": H, "ms": ms,
+            "us_per_64_tokens": ms * 1e3 / (L / 64), "state_tflops": 6 * T * H * D * D / ms / 1e9}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["attn_decode", "attn_prefill", "gemm", "moe", "w4a16"])
+    ap.add_argument("case", choices=["attn_decode", "attn_prefill", "gemm", "moe", "w4a16", "gdn"])
+    ap.add_argument("--gdn-backend", default="auto", choices=["auto", "cuda_chunkwise", "mllm_kernel"],
+                    help="gdn: chunk-parallel kernel, token-sequential kernel, or the default choice between them")
     ap.add_argument("--experts", type=int, default=16, help="moe: local experts")
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--seq", type=int, default=2050)
@@ -172,7 +195,7 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--kv-sets", type=int, default=4, help="attn_decode: KV caches used in turn (working set > L2)")
     a = ap.parse_args()
-    out = {"attn_decode": attn_decode, "attn_prefill": attn_prefill, "gemm": gemm, "moe": moe, "w4a16": w4a16}[a.case](a)
+    out = {"attn_decode": attn_decode, "attn_prefill": attn_prefill, "gemm": gemm, "moe": moe, "w4a16": w4a16, "gdn": gdn}[a.case](a)
     ops.check_status()
     print(json.dumps(out))
 

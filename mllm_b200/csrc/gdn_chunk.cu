@@ -12,8 +12,10 @@
 // (request, head) and a block of BV value features: grid (128 / BV, heads, batch), 256 threads.  The products
 // K K^T, Q K^T, K S0, Q S0, P U and K^T U' run on the tensor cores through warp-level MMA on tf32 operands with
 // fp32 accumulation (tiles of 16 x 16 x 8 read from shared memory); the state stays in fp32 in shared memory for
-// the whole sequence and is rounded to tf32 only as an MMA operand.  The substitution is the one sequential step:
-// one thread per value feature keeps its 64 unknowns in registers, rows of A are broadcast from shared memory.
+// the whole sequence and is rounded to tf32 only as an MMA operand.  The substitution is the one sequential step;
+// it runs 16 rows at a time (one thread per value feature inside a block, a tensor-core product to carry a solved
+// block into the rows below): one thread walking all 64 rows kept the other warps at a barrier for a quarter of
+// the kernel's issue slots.
 // The 64 x 64 x BV tiles and the chunk-to-chunk dependency are too small and too serial for a tcgen05 pipeline
 // (tensor-memory round trips between the six dependent products would dominate), hence the warp-level path.
 #include <mma.h>
@@ -30,14 +32,14 @@ constexpr int kGC = 64;             // tokens per chunk
 constexpr int kGD = 128;            // key / value head size
 constexpr int kGLd = kGD + 4;       // row stride (floats) of the K and Q tiles
 constexpr int kGLdC = kGC + 4;      // row stride of the chunk x chunk matrices
-constexpr int kGThreads = 256;
+constexpr int kGThreads = 512;
 constexpr int kGWarps = kGThreads / 32;
 
 template <int BV>
 struct GdnChunkCfg {
   static constexpr int kLdV = BV + 4;   // row stride of everything that is BV wide
-  static constexpr int kFloats = 2 * kGC * kGLd + kGD * kLdV + 2 * kGC * kGLdC + 3 * kGC * kLdV + 4 * kGC;
-  static constexpr int kSmem = kFloats * 4 + 128;
+  static constexpr int kFloats = 2 * kGC * kGLd + kGD * kLdV + 2 * kGC * kGLdC + 3 * kGC * kLdV + 6 * kGC;
+  static constexpr int kSmem = kFloats * 4 + kGC * BV * 2 + 128;    // + the staged 16-bit V block of the next chunk
 };
 
 using FragA = wmma::fragment<wmma::matrix_a, 16, 16, 8, wmma::precision::tf32, wmma::row_major>;
@@ -45,6 +47,16 @@ using FragAT = wmma::fragment<wmma::matrix_a, 16, 16, 8, wmma::precision::tf32, 
 using FragB = wmma::fragment<wmma::matrix_b, 16, 16, 8, wmma::precision::tf32, wmma::row_major>;
 using FragBT = wmma::fragment<wmma::matrix_b, 16, 16, 8, wmma::precision::tf32, wmma::col_major>;
 using FragC = wmma::fragment<wmma::accumulator, 16, 16, 8, float>;
+
+// asynchronous global -> shared copies; with `valid` false nothing is read and the destination is zero-filled
+__device__ __forceinline__ void stage16(void* dst, const void* src, bool valid) {
+  const int sz = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void stage4(void* dst, const void* src, bool valid) {
+  const int sz = valid ? 4 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(sz) : "memory");
+}
 
 template <typename F>
 __device__ __forceinline__ void to_tf32(F& f) {
@@ -76,6 +88,13 @@ gdn_chunk_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __re
   float* sB = sG + kGC;                  // [64] beta
   float* sE = sB + kGC;                  // [64] exp(G)
   float* sT = sE + kGC;                  // [64] exp(G_C - G)
+  float* sGn = sT + kGC;                 // [64] staged g of the next chunk
+  float* sBn = sGn + kGC;                // [64] staged beta of the next chunk
+  T* sVn = reinterpret_cast<T*>(sBn + kGC);   // [64][BV] staged V block of the next chunk
+  // The 16-bit K and Q rows of the next chunk are staged in the bytes of sQ, which nothing reads once Q K^T and
+  // Q S0 of the current chunk are done: K rows at byte 0, Q rows at byte 16384, 256 bytes per row.
+  T* sKn = reinterpret_cast<T*>(sQ);
+  T* sQn = sKn + kGC * kGD;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int vb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -90,33 +109,72 @@ gdn_chunk_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __re
   }
   const float qscale = rsqrtf(static_cast<float>(kGD));
 
-  for (int c0 = 0; c0 < n; c0 += kGC) {
+  // every copy of one chunk: 64 rows x 16 pieces of K and of Q, 64 x BV / 8 pieces of V, 64 scalars of g and beta
+  auto stage_chunk = [&](int c0) {
     const int nv = min(kGC, n - c0);
-    // ---- load: K and Q rows normalised (a warp per row), the V block, g and beta; rows past the end are zero ----
-    for (int r = warp; r < kGC; r += kGWarps) {
+    for (int idx = tid; idx < kGC * 16; idx += kGThreads) {
+      const int r = idx >> 4, piece = idx & 15;
       const bool valid = r < nv;
-      const int64_t base = ((row0 + c0 + (valid ? r : 0)) * heads + h) * kGD + lane * 4;
-      float kk[4], qq[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        kk[i] = valid ? to_f32(k[base + i]) : 0.f;
-        qq[i] = valid ? to_f32(q[base + i]) : 0.f;
-      }
-      const float ks = warp_sum(kk[0] * kk[0] + kk[1] * kk[1] + kk[2] * kk[2] + kk[3] * kk[3]);
-      const float qs = warp_sum(qq[0] * qq[0] + qq[1] * qq[1] + qq[2] * qq[2] + qq[3] * qq[3]);
-      const float kn = rsqrtf(ks + 1e-6f), qn = rsqrtf(qs + 1e-6f) * qscale;
-      *reinterpret_cast<float4*>(sK + r * kGLd + lane * 4) = make_float4(kk[0] * kn, kk[1] * kn, kk[2] * kn, kk[3] * kn);
-      *reinterpret_cast<float4*>(sQ + r * kGLd + lane * 4) = make_float4(qq[0] * qn, qq[1] * qn, qq[2] * qn, qq[3] * qn);
+      const int64_t at = ((row0 + c0 + (valid ? r : 0)) * heads + h) * kGD + piece * 8;
+      stage16(sKn + r * kGD + piece * 8, k + at, valid);
+      stage16(sQn + r * kGD + piece * 8, q + at, valid);
     }
-    for (int idx = tid; idx < kGC * BV; idx += kGThreads) {
-      const int r = idx / BV, c = idx % BV;
-      sU[r * kLdV + c] = r < nv ? to_f32(v[((row0 + c0 + r) * heads + h) * kGD + vb * BV + c]) : 0.f;
+    for (int idx = tid; idx < kGC * (BV / 8); idx += kGThreads) {
+      const int r = idx / (BV / 8), piece = idx % (BV / 8);
+      const bool valid = r < nv;
+      stage16(sVn + r * BV + piece * 8, v + ((row0 + c0 + (valid ? r : 0)) * heads + h) * kGD + vb * BV + piece * 8, valid);
     }
     if (tid < kGC) {
       const bool valid = tid < nv;
       const int64_t at = (row0 + c0 + (valid ? tid : 0)) * heads + h;
-      sG[tid] = valid ? g[at] : 0.f;
-      sB[tid] = valid ? beta[at] : 0.f;
+      stage4(sGn + tid, g + at, valid);
+      stage4(sBn + tid, beta + at, valid);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  stage_chunk(0);
+
+  for (int c0 = 0; c0 < n; c0 += kGC) {
+    const int nv = min(kGC, n - c0);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();      // the staged rows of this chunk are visible to every thread
+    // ---- K and Q rows normalised (a warp per row; all rows are read before any is written: the staged rows
+    // share their bytes with sQ), the V block widened, g and beta moved; rows past the end are zero ----
+    {
+      float kk[kGC / kGWarps][4], qq[kGC / kGWarps][4];
+#pragma unroll
+      for (int it = 0; it < kGC / kGWarps; ++it) {
+        const int r = warp + it * kGWarps;
+        const uint2 kr = *reinterpret_cast<const uint2*>(sKn + r * kGD + lane * 4);
+        const uint2 qr = *reinterpret_cast<const uint2*>(sQn + r * kGD + lane * 4);
+        const T* ke = reinterpret_cast<const T*>(&kr);
+        const T* qe = reinterpret_cast<const T*>(&qr);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          kk[it][i] = to_f32(ke[i]);
+          qq[it][i] = to_f32(qe[i]);
+        }
+      }
+      for (int idx = tid; idx < kGC * BV; idx += kGThreads) {
+        const int r = idx / BV, c = idx % BV;
+        sU[r * kLdV + c] = to_f32(sVn[r * BV + c]);
+      }
+      if (tid < kGC) {
+        sG[tid] = sGn[tid];
+        sB[tid] = sBn[tid];
+      }
+      __syncthreads();    // every staged row has been read
+#pragma unroll
+      for (int it = 0; it < kGC / kGWarps; ++it) {
+        const int r = warp + it * kGWarps;
+        const float ks = warp_sum(kk[it][0] * kk[it][0] + kk[it][1] * kk[it][1] + kk[it][2] * kk[it][2] + kk[it][3] * kk[it][3]);
+        const float qs = warp_sum(qq[it][0] * qq[it][0] + qq[it][1] * qq[it][1] + qq[it][2] * qq[it][2] + qq[it][3] * qq[it][3]);
+        const float kn = rsqrtf(ks + 1e-6f), qn = rsqrtf(qs + 1e-6f) * qscale;
+        *reinterpret_cast<float4*>(sK + r * kGLd + lane * 4) =
+            make_float4(kk[it][0] * kn, kk[it][1] * kn, kk[it][2] * kn, kk[it][3] * kn);
+        *reinterpret_cast<float4*>(sQ + r * kGLd + lane * 4) =
+            make_float4(qq[it][0] * qn, qq[it][1] * qn, qq[it][2] * qn, qq[it][3] * qn);
+      }
     }
     __syncthreads();
 
@@ -140,49 +198,51 @@ gdn_chunk_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __re
       sT[2 * lane + 1] = expf(total - g1);
     }
 
-    // ---- products that need no decay: K K^T -> sA, Q K^T -> sP (tiles on or below the diagonal), K S0 -> sX, Q S0 -> sY ----
-    for (int t = warp; t < 32; t += kGWarps) {
-      const int which = t >> 4, ti = (t & 15) >> 2, tj = t & 3;
-      if (tj > ti) continue;
+    // ---- products that need no decay: K K^T -> sA, Q K^T -> sP (tiles on or below the diagonal), K S0 -> sX,
+    // Q S0 -> sY; one list of tiles dealt round-robin to the warps ----
+    for (int t = warp; t < 20 + 8 * kVT; t += kGWarps) {
       FragC acc;
       wmma::fill_fragment(acc, 0.f);
-      const float* left = (which ? sQ : sK) + ti * 16 * kGLd;
-      const float* right = sK + tj * 16 * kGLd;
+      if (t < 20) {       // the ten tiles on or below the diagonal of K K^T, then those of Q K^T
+        const int which = t / 10, idx = t % 10;
+        const int ti = idx >= 6 ? 3 : idx >= 3 ? 2 : idx >= 1 ? 1 : 0, tj = idx - ti * (ti + 1) / 2;
+        const float* left = (which ? sQ : sK) + ti * 16 * kGLd;
+        const float* right = sK + tj * 16 * kGLd;
 #pragma unroll 4
-      for (int k0 = 0; k0 < kGD; k0 += 8) {
-        FragA fa;
-        FragBT fb;
-        wmma::load_matrix_sync(fa, left + k0, kGLd);
-        wmma::load_matrix_sync(fb, right + k0, kGLd);     // B[k][j] = K[j][k]
-        to_tf32(fa);
-        to_tf32(fb);
-        wmma::mma_sync(acc, fa, fb, acc);
-      }
-      wmma::store_matrix_sync((which ? sP : sA) + ti * 16 * kGLdC + tj * 16, acc, kGLdC, wmma::mem_row_major);
-    }
-    for (int t = warp; t < 2 * 4 * kVT; t += kGWarps) {
-      const int which = t / (4 * kVT), rem = t % (4 * kVT), ti = rem / kVT, tc = rem % kVT;
-      FragC acc;
-      wmma::fill_fragment(acc, 0.f);
-      const float* left = (which ? sQ : sK) + ti * 16 * kGLd;
+        for (int k0 = 0; k0 < kGD; k0 += 8) {
+          FragA fa;
+          FragBT fb;
+          wmma::load_matrix_sync(fa, left + k0, kGLd);
+          wmma::load_matrix_sync(fb, right + k0, kGLd);     // B[k][j] = K[j][k]
+          to_tf32(fa);
+          to_tf32(fb);
+          wmma::mma_sync(acc, fa, fb, acc);
+        }
+        wmma::store_matrix_sync((which ? sP : sA) + ti * 16 * kGLdC + tj * 16, acc, kGLdC, wmma::mem_row_major);
+      } else {
+        const int s2 = t - 20, which = s2 / (4 * kVT), rem = s2 % (4 * kVT), ti = rem / kVT, tc = rem % kVT;
+        const float* left = (which ? sQ : sK) + ti * 16 * kGLd;
 #pragma unroll 4
-      for (int k0 = 0; k0 < kGD; k0 += 8) {
-        FragA fa;
-        FragB fb;
-        wmma::load_matrix_sync(fa, left + k0, kGLd);
-        wmma::load_matrix_sync(fb, sS + k0 * kLdV + tc * 16, kLdV);
-        to_tf32(fa);
-        to_tf32(fb);
-        wmma::mma_sync(acc, fa, fb, acc);
+        for (int k0 = 0; k0 < kGD; k0 += 8) {
+          FragA fa;
+          FragB fb;
+          wmma::load_matrix_sync(fa, left + k0, kGLd);
+          wmma::load_matrix_sync(fb, sS + k0 * kLdV + tc * 16, kLdV);
+          to_tf32(fa);
+          to_tf32(fb);
+          wmma::mma_sync(acc, fa, fb, acc);
+        }
+        wmma::store_matrix_sync((which ? sY : sX) + ti * 16 * kLdV + tc * 16, acc, kLdV, wmma::mem_row_major);
       }
-      wmma::store_matrix_sync((which ? sY : sX) + ti * 16 * kLdV + tc * 16, acc, kLdV, wmma::mem_row_major);
     }
     __syncthreads();
+    // sQ is free from here on: the next chunk's rows travel while this chunk is finished
+    if (c0 + kGC < n) stage_chunk(c0 + kGC);
 
     // ---- decay masks, right-hand side ----
     for (int idx = tid; idx < kGC * kGC; idx += kGThreads) {
       const int i = idx >> 6, j = idx & 63;
-      const float d = j <= i ? expf(sG[i] - sG[j]) : 0.f;
+      const float d = j <= i ? __expf(sG[i] - sG[j]) : 0.f;
       const float ka = sA[i * kGLdC + j], qa = sP[i * kGLdC + j];
       sA[i * kGLdC + j] = j < i ? sB[i] * d * ka : 0.f;
       sP[i * kGLdC + j] = j <= i ? d * qa : 0.f;
@@ -195,29 +255,56 @@ gdn_chunk_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __re
     }
     __syncthreads();
 
-    // ---- forward substitution (I + A) U = rhs: one thread per value feature, unknowns in registers ----
-    if (tid < BV) {
-      float u[kGC];
+    // ---- forward substitution (I + A) U = rhs, 16 rows at a time: the rows of a block are solved by one thread
+    // per value feature (the block's unknowns in registers), then the block's contribution leaves the right-hand
+    // sides of all rows below it as one small tensor-core product ----
+    for (int blk = 0; blk < kGC / 16; ++blk) {
+      if (tid < BV) {
+        float u[16];
 #pragma unroll
-      for (int i = 0; i < kGC; ++i) {
-        float a0 = sU[i * kLdV + tid], a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        for (int i = 0; i < 16; ++i) {
+          const int row = blk * 16 + i;
+          float a0 = sU[row * kLdV + tid], a1 = 0.f;
 #pragma unroll
-        for (int j4 = 0; j4 < (i + 3) / 4; ++j4) {
-          const float4 ar = *reinterpret_cast<const float4*>(sA + i * kGLdC + j4 * 4);   // entries at j >= i are zero
-          if (j4 * 4 + 0 < i) a0 = fmaf(-ar.x, u[j4 * 4 + 0], a0);
-          if (j4 * 4 + 1 < i) a1 = fmaf(-ar.y, u[j4 * 4 + 1], a1);
-          if (j4 * 4 + 2 < i) a2 = fmaf(-ar.z, u[j4 * 4 + 2], a2);
-          if (j4 * 4 + 3 < i) a3 = fmaf(-ar.w, u[j4 * 4 + 3], a3);
+          for (int j4 = 0; j4 < (i + 3) / 4; ++j4) {
+            const float4 ar = *reinterpret_cast<const float4*>(sA + row * kGLdC + blk * 16 + j4 * 4);   // zero at j >= i
+            if (j4 * 4 + 0 < i) a0 = fmaf(-ar.x, u[j4 * 4 + 0], a0);
+            if (j4 * 4 + 1 < i) a1 = fmaf(-ar.y, u[j4 * 4 + 1], a1);
+            if (j4 * 4 + 2 < i) a0 = fmaf(-ar.z, u[j4 * 4 + 2], a0);
+            if (j4 * 4 + 3 < i) a1 = fmaf(-ar.w, u[j4 * 4 + 3], a1);
+          }
+          u[i] = a0 + a1;
         }
-        u[i] = (a0 + a1) + (a2 + a3);
-      }
 #pragma unroll
-      for (int i = 0; i < kGC; ++i) {
-        sU[i * kLdV + tid] = u[i];
-        sX[i * kLdV + tid] = sT[i] * u[i];
+        for (int i = 0; i < 16; ++i) {
+          const int row = blk * 16 + i;
+          sU[row * kLdV + tid] = u[i];
+          sX[row * kLdV + tid] = sT[row] * u[i];
+        }
+      }
+      __syncthreads();
+      if (blk + 1 < kGC / 16) {
+        for (int t = warp; t < (kGC / 16 - 1 - blk) * kVT; t += kGWarps) {
+          const int ti = blk + 1 + t / kVT, tc = t % kVT;
+          float* tile = sU + ti * 16 * kLdV + tc * 16;
+          FragC acc;
+          wmma::load_matrix_sync(acc, tile, kLdV, wmma::mem_row_major);
+#pragma unroll
+          for (int k0 = 0; k0 < 16; k0 += 8) {
+            FragA fa;
+            FragB fb;
+            wmma::load_matrix_sync(fa, sA + ti * 16 * kGLdC + blk * 16 + k0, kGLdC);
+            wmma::load_matrix_sync(fb, sU + (blk * 16 + k0) * kLdV + tc * 16, kLdV);
+#pragma unroll
+            for (int i = 0; i < fa.num_elements; ++i) fa.x[i] = wmma::__float_to_tf32(-fa.x[i]);
+            to_tf32(fb);
+            wmma::mma_sync(acc, fa, fb, acc);
+          }
+          wmma::store_matrix_sync(tile, acc, kLdV, wmma::mem_row_major);
+        }
+        __syncthreads();
       }
     }
-    __syncthreads();
 
     // ---- O = exp(G) (Q S0) + P U  and  S = exp(G_C) S0 + K^T U' ----
     const float carry = sE[kGC - 1];
@@ -263,8 +350,7 @@ gdn_chunk_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __re
       const int i = idx / BV, c = idx % BV;
       out[((row0 + c0 + i) * heads + h) * kGD + vb * BV + c] = from_f32<T>(sY[i * kLdV + c]);
     }
-    // the next chunk's loads overwrite tiles whose last readers finished before the barrier above; sY is
-    // rewritten only after the barrier that follows those loads
+    // the next iteration starts with a barrier, so sY is rewritten only after these reads
   }
   for (int idx = tid; idx < kGD * BV; idx += kGThreads) {
     const int i = idx / BV, c = idx % BV;
