@@ -106,26 +106,15 @@ class Qwen3_5Attention(nn.Module):
         kc, vc = fb.token_to_kv_pool.get_kv_buffer(self.layer_id)
         ops.kv_write(k.reshape(T, -1), v.reshape(T, -1), fb.out_cache_loc, kc, vc)
         rtt = fb.req_to_token_pool.req_to_token
-        fast = D == 128
+        # head sizes 64 / 128 / 256 run on the attention kernels; ops falls back to library / PyTorch paths otherwise
         if fb.forward_mode.is_decode():
-            if fast:
-                o = ops.attention_decode(q, kc, vc, rtt, fb.req_pool_indices, fb.seq_lens, self.scale, max_seq_len=fb.max_seq_len)
-            elif q.is_cuda and fb.max_seq_len:   # no kernel for this head size: one batched pass, no device read-back
-                o = ref.attention_decode_batched(q, kc, vc, rtt, fb.req_pool_indices, fb.seq_lens, self.scale, fb.max_seq_len)
-            else:
-                o = ref.attention_decode(q, kc, vc, rtt, fb.req_pool_indices, fb.seq_lens, self.scale)
+            o = ops.attention_decode(q, kc, vc, rtt, fb.req_pool_indices, fb.seq_lens, self.scale, max_seq_len=fb.max_seq_len)
         else:
-            if fast:
-                o = ops.attention_prefill(q, kc, vc, rtt, fb.req_pool_indices, fb.seq_lens, fb.extend_prefix_lens,
-                                          fb.extend_start_loc, self.scale, max_q_len=fb.max_extend_len)
-            elif q.is_cuda:                      # no kernel for this head size: library attention per request
-                ext_cpu, pre_cpu = getattr(fb, "extend_seq_lens_cpu", None), getattr(fb, "extend_prefix_lens_cpu", None)
-                seq_cpu = [a + b for a, b in zip(ext_cpu, pre_cpu)] if ext_cpu is not None and pre_cpu is not None else None
-                o = ref.attention_prefill_sdpa(q, kc, vc, rtt, fb.req_pool_indices, fb.seq_lens, fb.extend_prefix_lens,
-                                               fb.extend_start_loc, self.scale, seq_cpu, pre_cpu)
-            else:
-                o = ref.attention_prefill(q, kc, vc, rtt, fb.req_pool_indices, fb.seq_lens, fb.extend_prefix_lens,
-                                          fb.extend_start_loc, self.scale)
+            ext_cpu, pre_cpu = getattr(fb, "extend_seq_lens_cpu", None), getattr(fb, "extend_prefix_lens_cpu", None)
+            seq_cpu = [a + b for a, b in zip(ext_cpu, pre_cpu)] if ext_cpu is not None and pre_cpu is not None else None
+            o = ops.attention_prefill(q, kc, vc, rtt, fb.req_pool_indices, fb.seq_lens, fb.extend_prefix_lens,
+                                      fb.extend_start_loc, self.scale, max_q_len=fb.max_extend_len,
+                                      seq_lens_cpu=seq_cpu, prefix_lens_cpu=pre_cpu)
         o = o.reshape(T, self.num_heads * D) * torch.sigmoid(gate.float()).to(x.dtype)
         y = ops.linear(o, self.o_proj.weight)
         return pstate.tensor_model_parallel_all_reduce(y) if self.tp > 1 else y
