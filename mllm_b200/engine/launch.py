@@ -55,6 +55,7 @@ class Engine:
             self.quant_method, self.kv_cache_dtype = None, "auto"
         if mode not in ("inproc", "multiproc"):
             raise ValueError("mode must be 'inproc' or 'multiproc'")
+        self._resolve_paths()
         self.mode = mode
         self.hf_config = hf_config
         self.device = device
@@ -66,6 +67,23 @@ class Engine:
         self.rr: Optional[RequestResponseProcess] = None
         self.scheduler = None
         self._addrs: List[str] = []
+
+    def _resolve_paths(self) -> None:
+        """A model path that is neither a directory nor a preset names a hub repository: fetch it once, before any
+        process is started, and point the model and tokenizer paths at the local snapshot."""
+        from ..utils.hub import resolve_model_path
+
+        sc = self.server_config
+        if sc.model_path is None:
+            return
+        same_tokenizer = sc.tokenizer_path is None or str(sc.tokenizer_path) == str(sc.model_path)
+        local = resolve_model_path(sc.model_path, sc.download_dir)
+        if str(local) != str(sc.model_path):
+            sc.model_path = local
+        if same_tokenizer:
+            sc.tokenizer_path = sc.model_path
+        else:
+            sc.tokenizer_path = resolve_model_path(sc.tokenizer_path, sc.download_dir)
 
     # ------------------------------------------------------------------ lifecycle
     def launch(self) -> "Engine":
