@@ -130,6 +130,9 @@ class Scheduler:
         want = sum(int(t) * (int(h) // merge) * (int(w) // merge) for t, h, w in grids)
         if int(mm["pixel_values"].shape[0]) != rows:
             return f"pixel_values has {int(mm['pixel_values'].shape[0])} rows, the grids describe {rows}"
+        steps = mm.get("mrope_t_scale")
+        if steps is not None and int(steps.numel()) != len(grids):
+            return f"mrope_t_scale has {int(steps.numel())} entries for {len(grids)} grids"
         vision_ids = {image_id, getattr(cfg, "video_token_id", None)} - {None}
         have = sum(1 for tok in ids if tok in vision_ids)
         if have != want:

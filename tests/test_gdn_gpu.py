@@ -83,6 +83,28 @@ def test_gated_delta_rule_chunk_kernel(lens, has, dtype):
     assert torch.equal(st[0].cpu(), st_ref[0])            # a state row of no request is left alone
 
 
+def test_chunk_kernel_wide_value_blocks():
+    """Enough (request, head) pairs to fill the GPU: the kernel then takes value blocks of 64 features."""
+    torch.manual_seed(5)
+    H, D, lens, has = 16, 128, [70, 130, 64, 1, 200], [1, 0, 1, 1, 0]
+    B, T = len(lens), sum(lens)
+    q, k, v = (torch.randn(T, H, D, device="cuda").bfloat16() for _ in range(3))
+    g = -torch.rand(T, H, device="cuda") * 0.5
+    beta = torch.rand(T, H, device="cuda")
+    st = (torch.randn(B, H, D, D, device="cuda") * 0.1).contiguous()
+    slots = torch.arange(B, device="cuda", dtype=torch.int32)
+    st_ref = st.clone().cpu()
+    want = ref.gated_delta_rule(q.float().cpu(), k.float().cpu(), v.float().cpu(), g.cpu(), beta.cpu(), st_ref, slots.cpu(), lens, has)
+    ops.set_gdn_extend_backend("cuda_chunkwise")
+    try:
+        got = ops.gated_delta_rule(q, k, v, g, beta, st, slots, lens, has)
+        ops.check_status()
+    finally:
+        ops.set_gdn_extend_backend("auto")
+    assert (got.float().cpu() - want).abs().max().item() < 0.02 * want.abs().max().item() + 0.02
+    assert (st.cpu() - st_ref).abs().max().item() < 0.02 * st_ref.abs().max().item() + 0.02
+
+
 def test_chunk_and_sequential_kernels_agree_on_a_long_prefill():
     torch.manual_seed(4)
     H, D, lens = 16, 128, [2048, 1500]
