@@ -248,3 +248,22 @@ def test_clip_request_through_the_engine(preset):
         assert ("mrope_t_scale" in tok.mm_inputs) == (preset == "qwen2.5-vl-tiny")
     finally:
         eng.shutdown()
+
+
+def test_temporal_steps_stay_aligned_with_the_grids_of_a_mixed_batch():
+    """An image request (no step list) and a clip request (steps) prefilled in one pass: one step per grid, in order."""
+    from mllm_b200.orchestrator.model_runner_process import ModelRunnerProcess
+
+    me = types.SimpleNamespace(device=torch.device("cpu"))
+    img = types.SimpleNamespace(mm_inputs={"pixel_values": torch.zeros(16, 4), "image_grid_thw": torch.tensor([[1, 4, 4]])})
+    clip = types.SimpleNamespace(mm_inputs={"pixel_values": torch.zeros(48 + 16, 4),
+                                            "image_grid_thw": torch.tensor([[3, 4, 4], [1, 4, 4]]),
+                                            "mrope_t_scale": torch.tensor([2.0, 1.0], dtype=torch.float64)})
+    text = types.SimpleNamespace(mm_inputs=None)
+    out = ModelRunnerProcess._mm_kwargs(me, [(img, 0), (text, 0), (clip, 0)])
+    assert out["image_grid_thw"].tolist() == [[1, 4, 4], [3, 4, 4], [1, 4, 4]] and out["pixel_values"].shape[0] == 80
+    assert out["mrope_t_scale"].tolist() == [1.0, 2.0, 1.0]
+    # consumed once: a second pass over the same requests carries no pixels
+    assert ModelRunnerProcess._mm_kwargs(me, [(img, 0), (clip, 0)]) == {}
+    only_images = types.SimpleNamespace(mm_inputs={"pixel_values": torch.zeros(16, 4), "image_grid_thw": torch.tensor([[1, 4, 4]])})
+    assert "mrope_t_scale" not in ModelRunnerProcess._mm_kwargs(me, [(only_images, 0)])
