@@ -9,6 +9,7 @@ from __future__ import annotations
 import hashlib
 import io
 import logging
+import os
 import time
 from collections import OrderedDict
 from typing import Any, Dict, List, Optional, Sequence, Union
@@ -28,8 +29,9 @@ def _is_frame_list(v) -> bool:
     first = v[0]
     if isinstance(first, (dict, list, tuple)):
         return False
-    if isinstance(first, str):
-        return not first.endswith(".npy")
+    if isinstance(first, str):      # image files are frames; array files, containers and video data URIs are whole videos
+        return not (first.endswith(".npy") or first.startswith("data:video/")
+                    or first.lower().endswith(TokenizerWorker._CONTAINER_EXT))
     return not (hasattr(first, "ndim") and np.ndim(first) == 4)
 
 
@@ -82,19 +84,27 @@ class TokenizerWorker:
         """-> (uint8 frames ``[F, H, W, 3]`` as a tensor, frames per second of that frame list or None).
 
         Accepted: an array / tensor ``[F, H, W, 3]``; a list of frames (anything :meth:`load_image` takes, or
-        arrays); a ``.npy`` file holding such an array; a dict ``{"frames": <any of these>, "fps": f}``.  Container
-        formats (mp4, ...) need a decoder this package does not ship: decode to frames first."""
+        arrays); a ``.npy`` file holding such an array; a container file (mp4, avi, mov, mkv, webm, ...: decoded with
+        OpenCV when it is installed), its bytes or a ``data:video/...;base64,`` URI; a dict
+        ``{"frames": <any of these>, "fps": f}`` (``f`` overrides the container's own rate)."""
         import numpy as np
         import torch
 
+        src = cls._container_source(item)
+        if src is not None:
+            path, fps, cleanup = src
+            try:
+                total, own_fps = cls._probe_container(path)
+                return cls._decode_container(path, None), float(fps or own_fps or 0.0) or None
+            finally:
+                cleanup()
         fps = None
         if isinstance(item, dict):
             fps = item.get("fps")
             item = item.get("frames")
         if isinstance(item, str):
             if not item.endswith(".npy"):
-                raise ValueError("video_data: pass frames (array, list of images or .npy file); container formats "
-                                 "such as mp4 are not decoded here")
+                raise ValueError(f"video_data: {item!r} is neither a .npy file nor a video container this build can open")
             item = np.load(item)
         if isinstance(item, (list, tuple)):
             frames = [np.asarray(f) if isinstance(f, (np.ndarray, torch.Tensor)) else np.asarray(cls.load_image(f)) for f in item]
@@ -105,6 +115,119 @@ class TokenizerWorker:
         if arr.dim() != 4 or arr.shape[-1] != 3:
             raise ValueError(f"video_data: expected frames [F, H, W, 3], got {tuple(arr.shape)}")
         return arr.to(torch.uint8), (float(fps) if fps else None)
+
+    # ---- container files (mp4, ...) through OpenCV's FFmpeg reader ----
+    _CONTAINER_EXT = (".mp4", ".m4v", ".mov", ".avi", ".mkv", ".webm", ".mpg", ".mpeg", ".wmv", ".flv", ".gif")
+
+    @classmethod
+    def _container_source(cls, item: Any):
+        """``(path, fps override, cleanup)`` when ``item`` names or holds a container file, else None.  Bytes and
+        data URIs are written to a temporary file (the reader wants a path); ``cleanup()`` removes it."""
+        fps = None
+        if isinstance(item, dict):
+            fps = item.get("fps")
+            item = item.get("frames", item.get("path"))
+        nothing = lambda: None  # noqa: E731
+        if isinstance(item, os.PathLike):
+            item = os.fspath(item)
+        if isinstance(item, str) and item.lower().endswith(cls._CONTAINER_EXT):
+            return item, fps, nothing
+        data = None
+        if isinstance(item, str) and item.startswith("data:video/"):
+            import base64
+
+            data = base64.b64decode(item.split(",", 1)[1])
+        elif isinstance(item, (bytes, bytearray)):
+            data = bytes(item)
+        if data is None:
+            return None
+        import tempfile
+
+        f = tempfile.NamedTemporaryFile(suffix=".mp4", delete=False)
+        f.write(data)
+        f.close()
+        return f.name, fps, lambda: os.path.exists(f.name) and os.unlink(f.name)
+
+    @staticmethod
+    def _cv2():
+        try:
+            import cv2
+        except ImportError as e:
+            raise ValueError("video_data: container formats need OpenCV (cv2) to be decoded; pass frames instead") from e
+        return cv2
+
+    @classmethod
+    def _probe_container(cls, path: str):
+        """(frame count the container declares, its frames per second)."""
+        cv2 = cls._cv2()
+        cap = cv2.VideoCapture(path)
+        try:
+            if not cap.isOpened():
+                raise ValueError(f"video_data: cannot open {path!r} as a video")
+            return int(cap.get(cv2.CAP_PROP_FRAME_COUNT) or 0), float(cap.get(cv2.CAP_PROP_FPS) or 0.0)
+        finally:
+            cap.release()
+
+    @classmethod
+    def _decode_container(cls, path: str, keep: Optional[Sequence[int]]):
+        """uint8 RGB frames ``[F, H, W, 3]``: all of them, or the frame numbers ``keep`` (ascending; frames in
+        between are skipped without being converted).  A file that ends before its declared length gives fewer."""
+        import numpy as np
+        import torch
+
+        cv2 = cls._cv2()
+        cap = cv2.VideoCapture(path)
+        if not cap.isOpened():
+            raise ValueError(f"video_data: cannot open {path!r} as a video")
+        want = None if keep is None else list(keep)
+        out, i, k = [], 0, 0
+        try:
+            while want is None or k < len(want):
+                if not cap.grab():
+                    break
+                while want is not None and k < len(want) and want[k] < i:
+                    k += 1                                   # repeated or unsorted entries: take what still lies ahead
+                if want is None or (k < len(want) and want[k] == i):
+                    ok, frame = cap.retrieve()
+                    if not ok:
+                        break
+                    rgb = np.ascontiguousarray(frame[..., ::-1])
+                    reps = 1
+                    if want is not None:
+                        reps = 0
+                        while k < len(want) and want[k] == i:
+                            reps, k = reps + 1, k + 1
+                    out.extend([rgb] * reps)
+                i += 1
+        finally:
+            cap.release()
+        if not out:
+            raise ValueError(f"video_data: no frame could be decoded from {path!r}")
+        return torch.from_numpy(np.stack(out)).to(torch.uint8)
+
+    @classmethod
+    def load_video_sampled(cls, item: Any, sampler):
+        """``(kept frames, their frame numbers, frames per second of the source, frame count of the source)``;
+        ``sampler(total, fps)`` picks the frame numbers.  A container is decoded only at those frames."""
+        src = cls._container_source(item)
+        if src is None:
+            frames, fps = cls.load_video(item)
+            src_fps = fps or 24.0
+            keep = list(sampler(int(frames.shape[0]), src_fps))
+            return frames[keep], keep, src_fps, int(frames.shape[0])
+        path, fps, cleanup = src
+        try:
+            total, own_fps = cls._probe_container(path)
+            src_fps = float(fps or own_fps or 24.0)
+            if total <= 0:                                   # no declared length: decode, then sample
+                frames = cls._decode_container(path, None)
+                keep = list(sampler(int(frames.shape[0]), src_fps))
+                return frames[keep], keep, src_fps, int(frames.shape[0])
+            keep = list(sampler(total, src_fps))
+            frames = cls._decode_container(path, keep)
+            return frames, keep[: int(frames.shape[0])], src_fps, total
+        finally:
+            cleanup()
 
     def _builtin_mm_inputs(self, images, videos, text, ids):
         """Built-in preprocessing.  Every image becomes ``<vision_start> <image_pad> * n <vision_end>``.  A video
@@ -136,13 +259,10 @@ class TokenizerWorker:
         if videos is not None and mc.get("video_token_id") is None:
             raise ValueError("this model has no video token: video_data is not supported")
         for item in ([] if videos is None else videos if isinstance(videos, list) and not _is_frame_list(videos) else [videos]):
-            frames, fps = self.load_video(item)
-            src_fps = fps or 24.0
             target, lo, hi = float(mc.get("video_fps", 2.0)), int(mc.get("video_min_frames", 4)), int(mc.get("video_max_frames", 768))
             if mc.get("video_layout", "frames") == "clip":
-                total = int(frames.shape[0])
-                keep = sample_frame_indices_strided(total, src_fps, target, lo, hi, mc["temporal_patch_size"])
-                frames = frames[keep]
+                frames, keep, src_fps, total = self.load_video_sampled(
+                    item, lambda n, f: sample_frame_indices_strided(n, f, target, lo, hi, mc["temporal_patch_size"]))
                 h.update(frames.numpy().tobytes())
                 unit = (mc["patch_size"] * mc["merge_size"]) ** 2
                 pv, g = preprocess_video(frames, mc["patch_size"], mc["merge_size"], mc["temporal_patch_size"],
@@ -156,8 +276,7 @@ class TokenizerWorker:
                     step = mc["temporal_patch_size"] / max(sampled_fps, 1e-6) * float(mc["tokens_per_second"])
                 blocks.append((mc["video_token_id"], block, pv, g, [step]))
                 continue
-            keep = sample_frame_indices(frames.shape[0], src_fps, target, lo, hi)
-            frames = frames[keep]
+            frames, keep, src_fps, _ = self.load_video_sampled(item, lambda n, f: sample_frame_indices(n, f, target, lo, hi))
             h.update(frames.numpy().tobytes())
             pv, g = preprocess_video(frames, mc["patch_size"], mc["merge_size"], mc["temporal_patch_size"], **norm)
             T, gh, gw = (int(v) for v in g[0])

@@ -155,9 +155,19 @@ def _extract_images(messages: List[ChatMessage]) -> List[Any]:
 
 
 def _extract_videos(messages: List[ChatMessage]) -> List[Any]:
-    """``{"type": "video", "video": <frames | .npy file | {"frames": ..., "fps": f}>}`` parts, in order."""
-    return [part.get("video") for m in messages if isinstance(m.content, list) for part in m.content
-            if part.get("type") == "video"]
+    """Video parts in order: ``{"type": "video", "video": <frames | .npy file | container file | {"frames": ...,
+    "fps": f}>}`` or ``{"type": "video_url", "video_url": {"url": <container file | data:video/...;base64,...>}}``."""
+    videos = []
+    for m in messages:
+        if isinstance(m.content, list):
+            for part in m.content:
+                if part.get("type") == "video":
+                    videos.append(part.get("video"))
+                elif part.get("type") == "video_url":
+                    url = part.get("video_url")
+                    url = url.get("url") if isinstance(url, dict) else url
+                    videos.append(url[len("file://"):] if isinstance(url, str) and url.startswith("file://") else url)
+    return videos
 
 
 def messages_to_prompt(tokenizer, messages: List[ChatMessage], tools=None, template_kwargs=None) -> str:
@@ -173,7 +183,7 @@ def messages_to_prompt(tokenizer, messages: List[ChatMessage], tools=None, templ
                     text += part.get("text", "")
                 elif part.get("type") in ("image_url", "image"):
                     text += "<|vision_start|><|image_pad|><|vision_end|>"
-                elif part.get("type") == "video":
+                elif part.get("type") in ("video", "video_url"):
                     text += "<|vision_start|><|video_pad|><|vision_end|>"
             d["content"] = text
         plain.append(d)

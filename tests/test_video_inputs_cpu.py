@@ -153,7 +153,7 @@ def test_video_request_through_the_engine():
         eng.shutdown()
 
 
-def test_video_and_image_parts_over_http():
+def test_video_and_image_parts_over_http(tmp_path):
     testclient = pytest.importorskip("fastapi.testclient")
     from mllm_b200.configs import GlobalConfig
     from mllm_b200.engine.launch import Engine
@@ -179,8 +179,62 @@ def test_video_and_image_parts_over_http():
                                                  "image_data": img})
             n_vision = sum(1 for t in tok.input_ids if t in (IMG, VID))
             assert usage["completion_tokens"] == 3 and usage["prompt_tokens"] > n_vision > 0
+            clip = _write_clip(tmp_path / "clip.mp4")
+            import base64
+            uri = "data:video/mp4;base64," + base64.b64encode(clip.read_bytes()).decode()
+            for url in (uri, "file://" + str(clip)):
+                msgs = [{"role": "user", "content": [{"type": "video_url", "video_url": {"url": url}}, {"type": "text", "text": "go"}]}]
+                r = c.post("/v1/chat/completions", json={"messages": msgs, "max_tokens": 2, "temperature": 0})
+                assert r.status_code == 200, r.text
+                assert r.json()["usage"]["prompt_tokens"] > 20
             r = c.post("/generate", json={"text": "what", "video_data": {"frames": vid.tolist(), "fps": 2.0},
                                           "sampling_params": {"max_new_tokens": 2, "temperature": 0}})
             assert r.status_code == 200 and r.json()["meta_info"]["completion_tokens"] == 2
     finally:
         eng.shutdown()
+
+
+def _write_clip(path, n=12, fps=10.0, size=(96, 64), step=20):
+    cv2 = pytest.importorskip("cv2")
+    w = cv2.VideoWriter(str(path), cv2.VideoWriter_fourcc(*"mp4v"), fps, size)
+    if not w.isOpened():
+        pytest.skip("this OpenCV build cannot write mp4")
+    for i in range(n):
+        w.write(np.full((size[1], size[0], 3), i * step, dtype=np.uint8))     # frame i is a flat grey of value step x i
+    w.release()
+    return path
+
+
+def test_container_files_are_decoded_and_only_the_sampled_frames_are_converted(tmp_path):
+    """An mp4 written here is read back through the OpenCV reader: all frames, or just the sampled frame numbers."""
+    clip = _write_clip(tmp_path / "clip.mp4")
+    frames, fps = TokenizerWorker.load_video(str(clip))
+    assert tuple(frames.shape) == (12, 64, 96, 3) and fps == 10.0
+    level = frames.float().mean(dim=(1, 2, 3))
+    assert (level - torch.arange(12) * 20.0).abs().max() < 6                     # lossy codec: close, in order
+    kept, keep, src_fps, total = TokenizerWorker.load_video_sampled(str(clip), lambda n, f: [0, 5, 5, 11])
+    assert keep == [0, 5, 5, 11] and total == 12 and src_fps == 10.0 and kept.shape[0] == 4
+    assert (kept.float().mean(dim=(1, 2, 3)) - torch.tensor([0.0, 100.0, 100.0, 220.0])).abs().max() < 6
+    # the same file as bytes, as a data URI, and with a rate that overrides the container's
+    raw = clip.read_bytes()
+    import base64
+    for item in (raw, "data:video/mp4;base64," + base64.b64encode(raw).decode(), {"frames": str(clip), "fps": 5.0}):
+        f2, fps2 = TokenizerWorker.load_video(item)
+        assert f2.shape == frames.shape and fps2 == (5.0 if isinstance(item, dict) else 10.0)
+    with pytest.raises(ValueError, match="neither"):
+        TokenizerWorker.load_video("clip.txt")
+    with pytest.raises(ValueError, match="cannot open"):
+        TokenizerWorker.load_video(str(tmp_path / "missing.mp4"))
+
+
+def test_container_request_matches_the_same_frames_given_as_an_array(tmp_path):
+    clip = _write_clip(tmp_path / "clip.mp4", n=20, fps=10.0, step=12)
+    w = _worker()
+    frames, fps = TokenizerWorker.load_video(str(clip))
+    a = w.tokenize({"rid": "a", "input_ids": [5], "video_data": str(clip)})
+    b = w.tokenize({"rid": "b", "input_ids": [5], "video_data": {"frames": frames.numpy(), "fps": fps}})
+    assert a.input_ids == b.input_ids
+    assert torch.equal(a.mm_inputs["pixel_values"], b.mm_inputs["pixel_values"])
+    assert a.mm_inputs["image_grid_thw"].tolist() == b.mm_inputs["image_grid_thw"].tolist()
+    two = w.tokenize({"rid": "c", "input_ids": [5], "video_data": [str(clip), str(clip)]})      # a list of containers = two videos
+    assert two.mm_inputs["pixel_values"].shape[0] == 2 * a.mm_inputs["pixel_values"].shape[0]
