@@ -60,9 +60,29 @@ class TokenizerWorker:
             logger.warning("no multimodal processor: %s", exc)
             return None
 
-    @staticmethod
-    def load_image(item: Any):
-        """path / URL-less data URI / bytes / PIL image / array -> PIL image."""
+    # remote media: fetched with a time limit and a size cap; MLLM_B200_FETCH_URLS=0 refuses every remote URL
+    _FETCH_TIMEOUT_S = 10.0
+    _FETCH_MAX_BYTES = 256 << 20
+
+    @classmethod
+    def fetch_url(cls, url: str) -> bytes:
+        """The bytes behind an ``http(s)://`` URL of an image or video part."""
+        if os.environ.get("MLLM_B200_FETCH_URLS", "1") == "0":
+            raise ValueError("remote media URLs are disabled on this server (MLLM_B200_FETCH_URLS=0): send the data inline")
+        import urllib.request
+
+        try:
+            with urllib.request.urlopen(url, timeout=cls._FETCH_TIMEOUT_S) as r:
+                data = r.read(cls._FETCH_MAX_BYTES + 1)
+        except Exception as e:
+            raise ValueError(f"could not fetch {url!r}: {type(e).__name__}: {e}") from e
+        if len(data) > cls._FETCH_MAX_BYTES:
+            raise ValueError(f"{url!r} is larger than {cls._FETCH_MAX_BYTES >> 20} MiB")
+        return data
+
+    @classmethod
+    def load_image(cls, item: Any):
+        """path / http(s) URL / data URI / bytes / PIL image / array -> PIL image."""
         from PIL import Image
 
         if isinstance(item, Image.Image):
@@ -74,6 +94,10 @@ class TokenizerWorker:
                 import base64
 
                 return Image.open(io.BytesIO(base64.b64decode(item.split(",", 1)[1]))).convert("RGB")
+            if item.startswith(("http://", "https://")):
+                return Image.open(io.BytesIO(cls.fetch_url(item))).convert("RGB")
+            if item.startswith("file://"):
+                item = item[len("file://"):]
             return Image.open(item).convert("RGB")
         import numpy as np
 
@@ -130,6 +154,10 @@ class TokenizerWorker:
         nothing = lambda: None  # noqa: E731
         if isinstance(item, os.PathLike):
             item = os.fspath(item)
+        if isinstance(item, str) and item.startswith("file://"):
+            item = item[len("file://"):]
+        if isinstance(item, str) and item.startswith(("http://", "https://")):
+            item = cls.fetch_url(item)
         if isinstance(item, str) and item.lower().endswith(cls._CONTAINER_EXT):
             return item, fps, nothing
         data = None

@@ -238,3 +238,37 @@ def test_container_request_matches_the_same_frames_given_as_an_array(tmp_path):
     assert a.mm_inputs["image_grid_thw"].tolist() == b.mm_inputs["image_grid_thw"].tolist()
     two = w.tokenize({"rid": "c", "input_ids": [5], "video_data": [str(clip), str(clip)]})      # a list of containers = two videos
     assert two.mm_inputs["pixel_values"].shape[0] == 2 * a.mm_inputs["pixel_values"].shape[0]
+
+
+def test_remote_image_and_clip_urls_are_fetched_with_limits(tmp_path, monkeypatch):
+    """A local HTTP server stands in for the remote host."""
+    import functools
+    import http.server
+    import threading
+
+    from PIL import Image
+
+    img = np.random.default_rng(3).integers(0, 256, (40, 48, 3), dtype=np.uint8)
+    Image.fromarray(img).save(tmp_path / "pic.png")
+    clip = _write_clip(tmp_path / "clip.mp4")
+    handler = functools.partial(http.server.SimpleHTTPRequestHandler, directory=str(tmp_path))
+    handler.log_message = lambda *a, **k: None
+    srv = http.server.ThreadingHTTPServer(("127.0.0.1", 0), handler)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    base = f"http://127.0.0.1:{srv.server_address[1]}"
+    try:
+        got = np.asarray(TokenizerWorker.load_image(base + "/pic.png"))
+        assert np.array_equal(got, img)
+        assert np.array_equal(np.asarray(TokenizerWorker.load_image("file://" + str(tmp_path / "pic.png"))), img)
+        frames, fps = TokenizerWorker.load_video(base + "/clip.mp4")
+        assert tuple(frames.shape) == (12, 64, 96, 3) and fps == 10.0
+        with pytest.raises(ValueError, match="could not fetch"):
+            TokenizerWorker.load_image(base + "/missing.png")
+        monkeypatch.setattr(TokenizerWorker, "_FETCH_MAX_BYTES", 100)
+        with pytest.raises(ValueError, match="larger than"):
+            TokenizerWorker.load_image(base + "/pic.png")
+        monkeypatch.setenv("MLLM_B200_FETCH_URLS", "0")
+        with pytest.raises(ValueError, match="disabled"):
+            TokenizerWorker.load_image(base + "/pic.png")
+    finally:
+        srv.shutdown()
