@@ -256,6 +256,8 @@ def test_remote_image_and_clip_urls_are_fetched_with_limits(tmp_path, monkeypatc
     srv = http.server.ThreadingHTTPServer(("127.0.0.1", 0), handler)
     threading.Thread(target=srv.serve_forever, daemon=True).start()
     base = f"http://127.0.0.1:{srv.server_address[1]}"
+    monkeypatch.setenv("no_proxy", "127.0.0.1")          # a proxy configured for the machine must not see this
+    monkeypatch.setenv("NO_PROXY", "127.0.0.1")
     try:
         got = np.asarray(TokenizerWorker.load_image(base + "/pic.png"))
         assert np.array_equal(got, img)
