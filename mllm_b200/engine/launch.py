@@ -33,6 +33,17 @@ logger = logging.getLogger(__name__)
 DEFAULT_MAX_NEW_TOKENS = 128
 
 
+def model_default_max_new_tokens(hf_config) -> Optional[int]:
+    """The output-length limit a checkpoint's config declares (``max_new_tokens`` / ``max_tokens`` /
+    ``max_completion_tokens``, as pymllm/engine/launch.py:110-127), used when a request gives none."""
+    for cfg in (hf_config, getattr(hf_config, "text_config", None)):
+        for name in ("max_new_tokens", "max_tokens", "max_completion_tokens"):
+            v = getattr(cfg, name, None) if cfg is not None else None
+            if isinstance(v, int) and not isinstance(v, bool) and v > 0:
+                return v
+    return None
+
+
 def _free_port() -> int:
     import socket
 
@@ -104,6 +115,7 @@ class Engine:
 
         if self.hf_config is None:
             self.hf_config = load_hf_config(self.server_config.model_path)
+        self._default_max_new_tokens = model_default_max_new_tokens(self.hf_config) or DEFAULT_MAX_NEW_TOKENS
         return int(getattr(text_config_of(self.hf_config), "vocab_size", 1024))
 
     def _mm_config(self):
@@ -333,7 +345,7 @@ class Engine:
         for i in range(obj.batch_size):
             one = obj[i]
             sp = dict(one.sampling_params or {})
-            sp.setdefault("max_new_tokens", sp.pop("max_tokens", DEFAULT_MAX_NEW_TOKENS))
+            sp.setdefault("max_new_tokens", sp.pop("max_tokens", getattr(self, "_default_max_new_tokens", DEFAULT_MAX_NEW_TOKENS)))
             req = one.to_request_dict()
             req["sampling_params"] = sp
             req["rid"] = one.rid

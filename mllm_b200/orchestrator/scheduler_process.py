@@ -417,17 +417,49 @@ def build_scheduler(server_config: ServerConfig, hf_config=None, quantization_me
                          kv_cache_dtype=kv_cache_dtype, device=device)
     runner.initialize()
     if eos_token_ids is None:
-        eos_token_ids = resolve_eos_token_ids(runner.hf_config)
+        eos_token_ids = resolve_eos_token_ids(runner.hf_config, server_config.model_path, server_config.tokenizer_path)
     mrp = ModelRunnerProcess(runner, disable_radix_cache=server_config.disable_radix_cache)
     return Scheduler(mrp, server_config, eos_token_ids)
 
 
-def resolve_eos_token_ids(hf_config) -> List[int]:
-    """config -> text_config -> generation defaults (pymllm/engine/launch.py:46-127)."""
+def _eos_list(eos) -> List[int]:
+    if isinstance(eos, bool) or eos is None:
+        return []
+    if isinstance(eos, int):
+        return [eos]
+    return [int(e) for e in eos if isinstance(e, int) and not isinstance(e, bool)] if isinstance(eos, (list, tuple)) else []
+
+
+def resolve_eos_token_ids(hf_config, model_path=None, tokenizer_path=None) -> List[int]:
+    """End-of-sequence ids in the reference's order of precedence (pymllm/engine/launch.py:57-107): the config, its
+    ``text_config`` (vision-language checkpoints), ``generation_config.json`` beside the checkpoint (many chat
+    checkpoints list several ids there), then the tokenizer's own id."""
+    import json
+    import os
+
     for cfg in (hf_config, getattr(hf_config, "text_config", None)):
-        eos = getattr(cfg, "eos_token_id", None) if cfg is not None else None
-        if eos is not None:
-            return [int(e) for e in eos] if isinstance(eos, (list, tuple)) else [int(eos)]
+        ids = _eos_list(getattr(cfg, "eos_token_id", None)) if cfg is not None else []
+        if ids:
+            return ids
+    local = None if model_path is None or str(model_path).startswith("preset:") else str(model_path)
+    if local is not None and os.path.isfile(os.path.join(local, "generation_config.json")):
+        try:
+            with open(os.path.join(local, "generation_config.json")) as f:
+                ids = _eos_list(json.load(f).get("eos_token_id"))
+            if ids:
+                return ids
+        except (OSError, ValueError):
+            pass
+    tok_path = tokenizer_path if tokenizer_path is not None else model_path
+    if tok_path is not None and not str(tok_path).startswith("preset:") and any(
+            os.path.isfile(os.path.join(str(tok_path), f)) for f in ("tokenizer.json", "tokenizer_config.json", "vocab.json")):
+        try:
+            from ..utils.tokenizer import get_tokenizer
+
+            eos = getattr(get_tokenizer(str(tok_path), 0), "eos_token_id", None)
+            return _eos_list(eos)
+        except Exception:  # a checkpoint without tokenizer files: no id from here
+            pass
     return []
 
 

@@ -55,3 +55,37 @@ def test_a_failed_download_names_the_reason(monkeypatch):
     monkeypatch.setattr(huggingface_hub, "snapshot_download", boom)
     with pytest.raises(FileNotFoundError, match="could not be downloaded: OSError: no route to host"):
         hub.resolve_model_path("someorg/tiny-model")
+
+
+def test_eos_ids_and_default_output_length_follow_the_checkpoint(tmp_path):
+    """Precedence of the end-of-sequence ids: config, text_config, generation_config.json; and the output-length
+    limit a config declares becomes the default of requests that give none."""
+    import types
+
+    from mllm_b200.engine.launch import model_default_max_new_tokens
+    from mllm_b200.orchestrator.scheduler_process import resolve_eos_token_ids
+
+    ns = types.SimpleNamespace
+    assert resolve_eos_token_ids(ns(eos_token_id=7)) == [7]
+    assert resolve_eos_token_ids(ns(eos_token_id=[7, 9])) == [7, 9]
+    assert resolve_eos_token_ids(ns(eos_token_id=None, text_config=ns(eos_token_id=11))) == [11]
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": [151645, 151643], "temperature": 0.7}))
+    assert resolve_eos_token_ids(ns(eos_token_id=None), tmp_path) == [151645, 151643]
+    assert resolve_eos_token_ids(ns(eos_token_id=3), tmp_path) == [3]                 # the config wins
+    assert resolve_eos_token_ids(ns(eos_token_id=None), "preset:qwen3-tiny") == []
+    (tmp_path / "generation_config.json").write_text("{not json")
+    assert resolve_eos_token_ids(ns(eos_token_id=None), tmp_path) == []
+    assert model_default_max_new_tokens(ns(max_new_tokens=None, max_tokens=512)) == 512
+    assert model_default_max_new_tokens(ns(text_config=ns(max_completion_tokens=64))) == 64
+    assert model_default_max_new_tokens(ns(max_new_tokens=0)) is None
+    # through the engine: a request without a length stops at the model's default
+    from mllm_b200.models.presets import get_preset
+
+    eng = Engine(ServerConfig(model_path="preset:qwen3-tiny", dtype="float32", max_running_requests=2, max_total_tokens=512,
+                              log_level="warning"), hf_config=get_preset("qwen3-tiny", max_new_tokens=5), device="cpu").launch()
+    try:
+        out = eng.generate("hello", {"temperature": 0.0, "ignore_eos": True})
+        assert len(out["output_ids"]) == 5
+        assert len(eng.generate("hello", {"temperature": 0.0, "ignore_eos": True, "max_new_tokens": 2})["output_ids"]) == 2
+    finally:
+        eng.shutdown()
